@@ -1,0 +1,166 @@
+/* pcp_b200 — C ABI of the B200 execution backend for PCP's training hot path.
+ *
+ * Drop-in boundary: what the reference's worker reaches through its backend object
+ * (src/backends/worker_backend.zig:11-41 vtable, src/backends/iree.zig:53-442 concrete methods,
+ * pointer-cast at src/nodes/workers/worker.zig:1105).  Every entry point returns 0 on success or a
+ * non-zero PCPB_E_* code; the message is available from pcpb_last_error().  Nothing aborts, traps or
+ * falls back to the CPU.  A backend instance is not thread-safe (neither is the reference's); several
+ * instances per process are supported, one per GPU process is the normal deployment
+ * (src/nodes/node_manager.zig:65-107).
+ *
+ * The artefact given to pcpb_load_artifact is the forward StableHLO text of the model (the text the
+ * Shepherd holds before compiling, src/algorithms/diloco.zig:153), of the nanochat family.  The backend
+ * recognises the model from the @main signature, the RoPE table resources and the soft-cap constant,
+ * and implements for it the functions the reference's graph builder emits
+ * (src/compiler/graph_builder.zig:56-278), including the sanitiser's and the autodiff engine's guard
+ * terms (src/compiler/sanitizer.zig:8-111, src/autodiff/vjp_rules.zig).
+ */
+#ifndef PCP_B200_H
+#define PCP_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct pcpb_backend pcpb_backend;
+typedef struct pcpb_buffer pcpb_buffer;
+
+/* Element types, numbered like DType in src/core/tensor.zig:9-62. */
+enum pcpb_dtype { PCPB_F32 = 0, PCPB_F64 = 1, PCPB_F16 = 2, PCPB_BF16 = 3, PCPB_I32 = 4, PCPB_I64 = 5, PCPB_BOOL = 6 };
+
+enum pcpb_status {
+  PCPB_OK = 0,
+  PCPB_E_INVALID = 1,      /* bad argument, shape or dtype                               */
+  PCPB_E_CUDA = 2,         /* a CUDA call failed (the reference: error.IreeRuntimeError)  */
+  PCPB_E_ARTIFACT = 3,     /* artefact not recognised / not loaded                        */
+  PCPB_E_FUNCTION = 4,     /* unknown function name                                       */
+  PCPB_E_CHUNK_TOO_SMALL = 5,   /* src/data/loader.zig:559 ChunkTooSmall                  */
+  PCPB_E_CHUNK_EXHAUSTED = 6,   /* src/data/loader.zig:560 ChunkExhausted                 */
+  PCPB_E_STATE = 7,        /* call sequence error (e.g. step before begin_round)          */
+  PCPB_E_TOO_LARGE = 8     /* size beyond a fixed capacity                                */
+};
+
+/* IreeBackend.init / deinit  (src/backends/iree.zig:84,153): device by ordinal. */
+int pcpb_create(int device_ordinal, pcpb_backend** out);
+void pcpb_destroy(pcpb_backend* b);
+/* WorkerBackend.getBackendType (src/backends/worker_backend.zig:33): always "cuda". */
+const char* pcpb_backend_type(const pcpb_backend* b);
+const char* pcpb_last_error(const pcpb_backend* b);
+void pcpb_free(void* p);
+
+/* IreeBackend.loadSession (src/backends/iree.zig:213): (re)loads iff (ptr, len) differ from the cached
+ * artefact; the bytes are borrowed only for the duration of the call (they are parsed, not retained). */
+int pcpb_load_artifact(pcpb_backend* b, const void* bytes, size_t n);
+
+/* Model facts recovered from the artefact (src/mlir/model_introspection.zig:251-312: parameters are all
+ * @main arguments except the last two).  shape_out receives up to 8 dims. */
+int pcpb_num_params(const pcpb_backend* b);
+int pcpb_param_shape(const pcpb_backend* b, int index, int64_t* shape_out, int* rank_out);
+int pcpb_model_info(const pcpb_backend* b, int64_t* batch, int64_t* block, int64_t* vocab, int* model_dtype,
+                    int64_t* total_params);
+
+/* IreeBackend.moveToDevice / allocateZerosDevice (src/backends/iree.zig:166,198) and
+ * DeviceBuffer.retain / release / byteLength (:53-69). */
+int pcpb_buffer_from_host(pcpb_backend* b, const void* src, size_t nbytes, const int64_t* shape, int rank, int dtype,
+                          pcpb_buffer** out);
+int pcpb_buffer_zeros(pcpb_backend* b, const int64_t* shape, int rank, int dtype, pcpb_buffer** out);
+void pcpb_buffer_retain(pcpb_buffer* buf);
+void pcpb_buffer_release(pcpb_buffer* buf);
+size_t pcpb_buffer_nbytes(const pcpb_buffer* buf);
+
+/* IreeBackend.executeWithDeviceBuffers (src/backends/iree.zig:256): blocking; inputs are borrowed; each
+ * returned buffer carries one reference owned by the caller; the returned array is freed with pcpb_free.
+ * Functions: compute_gradients, apply_optimizer, accumulate_gradients, model_forward_pass, main,
+ * model_forward_pass_grad.  apply_optimizer uses the hyper-parameters set by pcpb_set_adam. */
+int pcpb_execute(pcpb_backend* b, const char* fn, pcpb_buffer* const* in, size_t n_in, pcpb_buffer*** out, size_t* n_out);
+
+/* IreeBackend.readToHost (src/backends/iree.zig:315): blocking device -> host copy. */
+int pcpb_read_to_host(pcpb_backend* b, const pcpb_buffer* buf, void* dst, size_t nbytes);
+
+/* IreeBackend.execute / WorkerBackend.executeFunction (src/backends/iree.zig:336, worker_backend.zig:24):
+ * host bytes in, host bytes out.  out[i] and the two arrays are freed with pcpb_free. */
+int pcpb_execute_host(pcpb_backend* b, const char* fn, const void* const* in, const size_t* in_nbytes,
+                      const int64_t* const* shapes, const int* ranks, const int* dtypes, size_t n_in, void*** out,
+                      size_t** out_nbytes, size_t* n_out);
+
+/* Dataset.getBatch of the FIFO u16 dataset (U16TokenDatasetFifo.getBatchImpl, src/data/loader.zig:555-589),
+ * with the widening to i64 done on the device: consumes B*T+1 tokens of the host chunk at *cursor, returns the
+ * [B,T] i64 inputs and 1-shifted targets as device buffers and advances *cursor by B*T+1.
+ * PCPB_E_CHUNK_TOO_SMALL / PCPB_E_CHUNK_EXHAUSTED as in the reference. */
+int pcpb_fifo_get_batch(pcpb_backend* b, const uint16_t* tokens, size_t n_tokens, size_t* cursor,
+                        pcpb_buffer** inputs, pcpb_buffer** targets);
+
+/* AdamW constants of apply_optimizer (src/optimizers/adam_mlir.zig:10-19; the reference bakes them into the
+ * compiled module, src/algorithms/diloco.zig:205-211).  Defaults: lr 1e-3, 0.9, 0.999, 1e-8, 0.01, 1.0. */
+typedef struct pcpb_adam_conf {
+  float learning_rate, beta1, beta2, epsilon, weight_decay, max_grad_norm;
+} pcpb_adam_conf;
+int pcpb_set_adam(pcpb_backend* b, const pcpb_adam_conf* conf);
+
+/* ---- fused worker path: Worker.handleStartInnerLoop (src/nodes/workers/worker.zig:855-1480) kept on the
+ * device.  Same semantics: Adam state reset at the start of a round (unless persist_adam), tau steps of
+ * FIFO batch -> compute_gradients (accumulation_steps micro-batches, summed, scaled by 1/steps) ->
+ * apply_optimizer, NaN heal of m/v, delta = initial - final (bf16: truncated), last step's loss. */
+typedef struct pcpb_inner_cfg {
+  int tau;
+  int accumulation_steps;   /* >= 1 */
+  int param_dtype;          /* PCPB_F32 | PCPB_BF16: dtype of the parameter / delta blobs */
+  int persist_adam;         /* 0 = reference behaviour (reset every round) */
+  int tokens_on_device;     /* 0: `tokens` is host memory, each step's window is copied in the step;
+                               1: `tokens` is a device pointer */
+} pcpb_inner_cfg;
+
+/* Start a round.  params_blob: host bytes of all parameters concatenated in argument order in param_dtype
+ * (the START_INNER_LOOP payload, src/algorithms/diloco.zig:665-667), or NULL to continue from the master
+ * parameters already on the device (after pcpb_outer_apply). */
+int pcpb_worker_begin_round(pcpb_backend* b, const pcpb_inner_cfg* cfg, const void* params_blob, size_t blob_bytes);
+/* Attach the token chunk of this round (U16TokenDatasetFifo, src/data/loader.zig:500-553); cursor = 0. */
+int pcpb_worker_set_tokens(pcpb_backend* b, const uint16_t* tokens, size_t n_tokens);
+/* One inner step, enqueued without host synchronisation.  loss_slot: index in the per-round loss record. */
+int pcpb_worker_step(pcpb_backend* b);
+/* Finish: heal, delta.  delta_out (host, may be NULL) receives the delta blob in param_dtype; losses (host,
+ * may be NULL) receives one f32 per step done this round. */
+int pcpb_worker_end_round(pcpb_backend* b, void* delta_out, size_t delta_bytes, float* losses, size_t n_losses);
+/* The whole of handleStartInnerLoop in one call. */
+int pcpb_inner_loop(pcpb_backend* b, const pcpb_inner_cfg* cfg, const void* params_blob, size_t blob_bytes,
+                    const uint16_t* tokens, size_t n_tokens, void* delta_out, size_t delta_bytes, float* losses);
+/* Current f32 working parameters / Adam state of the fused path, for checks (flat, argument order). */
+int pcpb_worker_read_state(pcpb_backend* b, int which /*0 params,1 m,2 v,3 delta,4 master,5 velocity,6 grads*/,
+                           float* dst, size_t n);
+/* Blocks until everything enqueued by this backend has run; returns the first asynchronous error. */
+int pcpb_synchronize(pcpb_backend* b);
+
+/* ---- DiLoCo outer step on the box: DiLoCo.accumulateAndApplyGradients + Nesterov.update
+ * (src/algorithms/diloco.zig:828-1060, src/optimizers/nesterov.zig:70-98) as a reduce-scatter / update /
+ * all-gather over peer memory.  Rank r owns elements [r*S, (r+1)*S) of the master parameters and velocity.
+ * Sequence per round, with a host barrier across ranks where marked:
+ *   pcpb_outer_prepare (all ranks)  -> barrier -> pcpb_outer_apply (all ranks) -> barrier
+ * After it every rank's round-start parameters hold the new master. */
+typedef struct pcpb_outer_cfg {
+  float learning_rate;      /* 0.7 in the reference (src/algorithms/diloco.zig:218-221) */
+  float momentum;
+  int param_dtype;          /* PCPB_BF16: master and deltas truncated to bf16 precision */
+} pcpb_outer_cfg;
+#define PCPB_IPC_HANDLE_BYTES 64
+/* Bytes to publish to the other ranks: 2 IPC handles (delta buffer, round-start parameter buffer). */
+int pcpb_outer_export(pcpb_backend* b, void* handles_out /* 2*PCPB_IPC_HANDLE_BYTES */);
+/* world ranks; all_handles: world * 2 * PCPB_IPC_HANDLE_BYTES gathered in rank order (own entry ignored). */
+int pcpb_outer_attach_ipc(pcpb_backend* b, int rank, int world, const void* all_handles);
+/* Same-process variant (several backends in one process): peers[w] for every rank, own entry included. */
+int pcpb_outer_attach_local(pcpb_backend* b, int rank, int world, pcpb_backend* const* peers);
+int pcpb_outer_prepare(pcpb_backend* b, const pcpb_outer_cfg* cfg);
+/* contributors: ranks whose deltas are averaged (NULL = all), the divisor is their count
+ * (src/algorithms/diloco.zig:970). */
+int pcpb_outer_apply(pcpb_backend* b, const pcpb_outer_cfg* cfg, const int* contributors, int n_contributors,
+                     double* device_ms);
+
+/* Kernel counters of this backend: launches enqueued since creation, by the library's own kernels. */
+long long pcpb_launch_count(const pcpb_backend* b);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PCP_B200_H */

@@ -1,0 +1,387 @@
+"""ctypes binding of libpcp_b200.so, mirroring the reference's worker backend.
+
+Method names follow src/backends/iree.zig (IreeBackend) and src/backends/worker_backend.zig
+(WorkerBackend vtable) so that code written against the reference reads the same:
+
+    IreeBackend.init / deinit                 -> Backend(device_id) / close()
+    moveToDevice / allocateZerosDevice        -> move_to_device / allocate_zeros_device
+    loadSession                               -> load_session
+    executeWithDeviceBuffers                  -> execute_with_device_buffers
+    readToHost                                -> read_to_host
+    execute / executeFunction                 -> execute
+    executeTrainingStep                       -> execute_training_step
+    DeviceBuffer.retain/release/byteLength    -> DeviceBuffer.retain/release/byte_length
+
+Errors raise BackendError (the reference maps every runtime failure to error.IreeRuntimeError);
+the numeric code is kept in `.code`.  There is no CPU fallback: without the shared library or
+without a B200 the constructor raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+F32, F64, F16, BF16, I32, I64, BOOL = range(7)
+DTYPE_SIZE = {F32: 4, F64: 8, F16: 2, BF16: 2, I32: 4, I64: 8, BOOL: 1}
+_NP_DTYPE = {F32: np.float32, F64: np.float64, F16: np.float16, BF16: np.uint16, I32: np.int32, I64: np.int64,
+             BOOL: np.uint8}
+IPC_HANDLE_BYTES = 64
+
+E_INVALID, E_CUDA, E_ARTIFACT, E_FUNCTION, E_CHUNK_TOO_SMALL, E_CHUNK_EXHAUSTED, E_STATE, E_TOO_LARGE = range(1, 9)
+
+LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libpcp_b200.so")
+
+EXPORTS = [
+    "pcpb_create", "pcpb_destroy", "pcpb_backend_type", "pcpb_last_error", "pcpb_free", "pcpb_load_artifact",
+    "pcpb_num_params", "pcpb_param_shape", "pcpb_model_info", "pcpb_buffer_from_host", "pcpb_buffer_zeros",
+    "pcpb_buffer_retain", "pcpb_buffer_release", "pcpb_buffer_nbytes", "pcpb_execute", "pcpb_read_to_host",
+    "pcpb_execute_host", "pcpb_fifo_get_batch", "pcpb_set_adam", "pcpb_worker_begin_round", "pcpb_worker_set_tokens", "pcpb_worker_step",
+    "pcpb_worker_end_round", "pcpb_inner_loop", "pcpb_worker_read_state", "pcpb_synchronize", "pcpb_outer_export",
+    "pcpb_outer_attach_ipc", "pcpb_outer_attach_local", "pcpb_outer_prepare", "pcpb_outer_apply",
+    "pcpb_launch_count",
+]
+
+
+class BackendError(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__(f"pcp_b200 error {code}: {message}")
+        self.code = code
+
+
+class AdamConf(C.Structure):
+    _fields_ = [("learning_rate", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float), ("epsilon", C.c_float),
+                ("weight_decay", C.c_float), ("max_grad_norm", C.c_float)]
+
+
+class InnerCfg(C.Structure):
+    _fields_ = [("tau", C.c_int), ("accumulation_steps", C.c_int), ("param_dtype", C.c_int),
+                ("persist_adam", C.c_int), ("tokens_on_device", C.c_int)]
+
+
+class OuterCfg(C.Structure):
+    _fields_ = [("learning_rate", C.c_float), ("momentum", C.c_float), ("param_dtype", C.c_int)]
+
+
+_lib = None
+
+
+def load_library(path: str | None = None):
+    """Loads the shared library (no GPU needed for loading) and declares the signatures."""
+    global _lib
+    if _lib is not None and path is None:
+        return _lib
+    p = path or LIB_PATH
+    if not os.path.exists(p):
+        raise BackendError(E_CUDA, f"{p} not found: build it with `python -m pcp_b200.build` "
+                                   "(there is no CPU fallback)")
+    lib = C.CDLL(p)
+    vp, i, sz = C.c_void_p, C.c_int, C.c_size_t
+    lib.pcpb_create.argtypes = [i, C.POINTER(vp)]
+    lib.pcpb_destroy.argtypes = [vp]; lib.pcpb_destroy.restype = None
+    lib.pcpb_backend_type.argtypes = [vp]; lib.pcpb_backend_type.restype = C.c_char_p
+    lib.pcpb_last_error.argtypes = [vp]; lib.pcpb_last_error.restype = C.c_char_p
+    lib.pcpb_free.argtypes = [vp]; lib.pcpb_free.restype = None
+    lib.pcpb_load_artifact.argtypes = [vp, vp, sz]
+    lib.pcpb_num_params.argtypes = [vp]
+    lib.pcpb_param_shape.argtypes = [vp, i, C.POINTER(C.c_int64), C.POINTER(i)]
+    lib.pcpb_model_info.argtypes = [vp, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64),
+                                    C.POINTER(i), C.POINTER(C.c_int64)]
+    lib.pcpb_buffer_from_host.argtypes = [vp, vp, sz, C.POINTER(C.c_int64), i, i, C.POINTER(vp)]
+    lib.pcpb_buffer_zeros.argtypes = [vp, C.POINTER(C.c_int64), i, i, C.POINTER(vp)]
+    lib.pcpb_buffer_retain.argtypes = [vp]; lib.pcpb_buffer_retain.restype = None
+    lib.pcpb_buffer_release.argtypes = [vp]; lib.pcpb_buffer_release.restype = None
+    lib.pcpb_buffer_nbytes.argtypes = [vp]; lib.pcpb_buffer_nbytes.restype = sz
+    lib.pcpb_execute.argtypes = [vp, C.c_char_p, C.POINTER(vp), sz, C.POINTER(C.POINTER(vp)), C.POINTER(sz)]
+    lib.pcpb_read_to_host.argtypes = [vp, vp, vp, sz]
+    lib.pcpb_execute_host.argtypes = [vp, C.c_char_p, C.POINTER(vp), C.POINTER(sz), C.POINTER(C.POINTER(C.c_int64)),
+                                      C.POINTER(i), C.POINTER(i), sz, C.POINTER(C.POINTER(vp)),
+                                      C.POINTER(C.POINTER(sz)), C.POINTER(sz)]
+    lib.pcpb_fifo_get_batch.argtypes = [vp, vp, sz, C.POINTER(sz), C.POINTER(vp), C.POINTER(vp)]
+    lib.pcpb_set_adam.argtypes = [vp, C.POINTER(AdamConf)]
+    lib.pcpb_worker_begin_round.argtypes = [vp, C.POINTER(InnerCfg), vp, sz]
+    lib.pcpb_worker_set_tokens.argtypes = [vp, vp, sz]
+    lib.pcpb_worker_step.argtypes = [vp]
+    lib.pcpb_worker_end_round.argtypes = [vp, vp, sz, vp, sz]
+    lib.pcpb_inner_loop.argtypes = [vp, C.POINTER(InnerCfg), vp, sz, vp, sz, vp, sz, vp]
+    lib.pcpb_worker_read_state.argtypes = [vp, i, vp, sz]
+    lib.pcpb_synchronize.argtypes = [vp]
+    lib.pcpb_outer_export.argtypes = [vp, vp]
+    lib.pcpb_outer_attach_ipc.argtypes = [vp, i, i, vp]
+    lib.pcpb_outer_attach_local.argtypes = [vp, i, i, C.POINTER(vp)]
+    lib.pcpb_outer_prepare.argtypes = [vp, C.POINTER(OuterCfg)]
+    lib.pcpb_outer_apply.argtypes = [vp, C.POINTER(OuterCfg), C.POINTER(i), i, C.POINTER(C.c_double)]
+    lib.pcpb_launch_count.argtypes = [vp]; lib.pcpb_launch_count.restype = C.c_longlong
+    if path is None:
+        _lib = lib
+    return lib
+
+
+class DeviceBuffer:
+    """One reference to a device buffer (src/backends/iree.zig:53-69)."""
+
+    def __init__(self, lib, handle, shape=None, dtype=None):
+        self._lib, self.handle, self.shape, self.dtype = lib, handle, shape, dtype
+
+    def retain(self):
+        self._lib.pcpb_buffer_retain(self.handle)
+
+    def release(self):
+        if self.handle:
+            self._lib.pcpb_buffer_release(self.handle)
+            self.handle = None
+
+    def byte_length(self):
+        return self._lib.pcpb_buffer_nbytes(self.handle)
+
+
+def _as_bytes_array(x):
+    a = np.ascontiguousarray(x)
+    return a, a.ctypes.data, a.nbytes
+
+
+class Backend:
+    def __init__(self, device_id: int = 0):
+        self._lib = load_library()
+        h = C.c_void_p()
+        rc = self._lib.pcpb_create(device_id, C.byref(h))
+        self._h = h
+        if rc:
+            msg = self._lib.pcpb_last_error(h).decode() if h else "allocation failed"
+            if h:
+                self._lib.pcpb_destroy(h)
+            self._h = None
+            raise BackendError(rc, msg)
+        self._artifact = None
+
+    # -- plumbing
+    def _check(self, rc):
+        if rc:
+            raise BackendError(rc, self._lib.pcpb_last_error(self._h).decode())
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.pcpb_destroy(self._h)
+            self._h = None
+
+    deinit = close
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def get_backend_type(self):
+        return self._lib.pcpb_backend_type(self._h).decode()
+
+    @property
+    def launch_count(self):
+        return int(self._lib.pcpb_launch_count(self._h))
+
+    # -- artefact
+    def load_session(self, artifact):
+        if isinstance(artifact, str):
+            artifact = artifact.encode()
+        self._artifact_raw = artifact
+        self._artifact = C.create_string_buffer(artifact, len(artifact))      # keeps (ptr, len) stable
+        self._check(self._lib.pcpb_load_artifact(self._h, C.cast(self._artifact, C.c_void_p), len(artifact)))
+
+    def _ensure_session(self, artifact):
+        if artifact is None:
+            return
+        raw = artifact.encode() if isinstance(artifact, str) else artifact
+        if self._artifact is None or self._artifact_raw != raw:
+            self.load_session(raw)
+
+    def num_params(self):
+        return self._lib.pcpb_num_params(self._h)
+
+    def param_shapes(self):
+        out = []
+        shp = (C.c_int64 * 8)()
+        rank = C.c_int()
+        for k in range(self.num_params()):
+            self._check(self._lib.pcpb_param_shape(self._h, k, shp, C.byref(rank)))
+            out.append(tuple(shp[j] for j in range(rank.value)))
+        return out
+
+    def model_info(self):
+        b, t, v, n = C.c_int64(), C.c_int64(), C.c_int64(), C.c_int64()
+        dt = C.c_int()
+        self._check(self._lib.pcpb_model_info(self._h, C.byref(b), C.byref(t), C.byref(v), C.byref(dt), C.byref(n)))
+        return {"batch": b.value, "block": t.value, "vocab": v.value, "dtype": dt.value, "total_params": n.value}
+
+    # -- buffers
+    def move_to_device(self, data, shape, dtype) -> DeviceBuffer:
+        a, ptr, nbytes = _as_bytes_array(data)
+        shp = (C.c_int64 * max(len(shape), 1))(*shape)
+        h = C.c_void_p()
+        self._check(self._lib.pcpb_buffer_from_host(self._h, ptr, nbytes, shp, len(shape), dtype, C.byref(h)))
+        return DeviceBuffer(self._lib, h, tuple(shape), dtype)
+
+    def allocate_zeros_device(self, shape, dtype) -> DeviceBuffer:
+        shp = (C.c_int64 * max(len(shape), 1))(*shape)
+        h = C.c_void_p()
+        self._check(self._lib.pcpb_buffer_zeros(self._h, shp, len(shape), dtype, C.byref(h)))
+        return DeviceBuffer(self._lib, h, tuple(shape), dtype)
+
+    def read_to_host(self, buf: DeviceBuffer, dtype=None, shape=None) -> np.ndarray:
+        n = buf.byte_length()
+        raw = np.empty(n, dtype=np.uint8)
+        self._check(self._lib.pcpb_read_to_host(self._h, buf.handle, raw.ctypes.data, n))
+        dt = dtype if dtype is not None else buf.dtype
+        if dt is None:
+            return raw
+        out = raw.view(_NP_DTYPE[dt])
+        shp = shape if shape is not None else buf.shape
+        return out.reshape(shp) if shp is not None else out
+
+    # -- execution
+    def execute_with_device_buffers(self, artifact, fn_name: str, inputs):
+        self._ensure_session(artifact)
+        arr = (C.c_void_p * max(len(inputs), 1))(*[b.handle for b in inputs])
+        out = C.POINTER(C.c_void_p)()
+        n = C.c_size_t()
+        self._check(self._lib.pcpb_execute(self._h, fn_name.encode(), arr, len(inputs), C.byref(out), C.byref(n)))
+        res = [DeviceBuffer(self._lib, C.c_void_p(out[k])) for k in range(n.value)]
+        self._lib.pcpb_free(out)
+        return res
+
+    def execute(self, artifact, fn_name: str, inputs_data, input_shapes, input_dtypes=None):
+        """Host bytes in, host bytes out (list of uint8 arrays)."""
+        self._ensure_session(artifact)
+        n = len(inputs_data)
+        keep = [_as_bytes_array(x) for x in inputs_data]
+        ptrs = (C.c_void_p * n)(*[k[1] for k in keep])
+        sizes = (C.c_size_t * n)(*[k[2] for k in keep])
+        shp_arrs = [(C.c_int64 * max(len(s), 1))(*s) for s in input_shapes]
+        shps = (C.POINTER(C.c_int64) * n)(*[C.cast(a, C.POINTER(C.c_int64)) for a in shp_arrs])
+        ranks = (C.c_int * n)(*[len(s) for s in input_shapes])
+        dts = (C.c_int * n)(*input_dtypes) if input_dtypes is not None else None
+        out = C.POINTER(C.c_void_p)()
+        onb = C.POINTER(C.c_size_t)()
+        no = C.c_size_t()
+        self._check(self._lib.pcpb_execute_host(self._h, fn_name.encode(), ptrs, sizes, shps, ranks, dts, n,
+                                                C.byref(out), C.byref(onb), C.byref(no)))
+        res = []
+        for k in range(no.value):
+            res.append(np.ctypeslib.as_array(C.cast(out[k], C.POINTER(C.c_uint8)), shape=(onb[k],)).copy())
+            self._lib.pcpb_free(out[k])
+        self._lib.pcpb_free(out)
+        self._lib.pcpb_free(onb)
+        return res
+
+    def execute_function(self, artifact, function_name, inputs, shapes, dtypes=None):
+        return self.execute(artifact, function_name, inputs, shapes, dtypes)
+
+    def execute_training_step(self, artifact, inputs, shapes, dtypes=None):
+        return self.execute(artifact, "main", inputs, shapes, dtypes)
+
+    def fifo_get_batch(self, tokens: np.ndarray, cursor: int):
+        """-> (inputs DeviceBuffer, targets DeviceBuffer, new cursor); tokens: host uint16 array."""
+        tok = np.ascontiguousarray(tokens, dtype=np.uint16)
+        cur = C.c_size_t(cursor)
+        x, y = C.c_void_p(), C.c_void_p()
+        self._check(self._lib.pcpb_fifo_get_batch(self._h, tok.ctypes.data, tok.size, C.byref(cur), C.byref(x), C.byref(y)))
+        info = self.model_info()
+        shp = (info["batch"], info["block"])
+        return DeviceBuffer(self._lib, x, shp, I64), DeviceBuffer(self._lib, y, shp, I64), cur.value
+
+    def set_adam(self, learning_rate=1e-3, beta1=0.9, beta2=0.999, epsilon=1e-8, weight_decay=0.01,
+                 max_grad_norm=1.0):
+        conf = AdamConf(learning_rate, beta1, beta2, epsilon, weight_decay, max_grad_norm)
+        self._check(self._lib.pcpb_set_adam(self._h, C.byref(conf)))
+
+    def synchronize(self):
+        self._check(self._lib.pcpb_synchronize(self._h))
+
+    # -- fused worker round (Worker.handleStartInnerLoop, src/nodes/workers/worker.zig:855-1480)
+    def worker_begin_round(self, tau, params_blob=None, param_dtype=F32, accumulation_steps=1, persist_adam=False,
+                           tokens_on_device=False):
+        cfg = InnerCfg(tau, accumulation_steps, param_dtype, int(persist_adam), int(tokens_on_device))
+        if params_blob is None:
+            self._check(self._lib.pcpb_worker_begin_round(self._h, C.byref(cfg), None, 0))
+        else:
+            a, ptr, nbytes = _as_bytes_array(params_blob)
+            self._check(self._lib.pcpb_worker_begin_round(self._h, C.byref(cfg), ptr, nbytes))
+
+    def worker_set_tokens(self, tokens=None, device_ptr=None, n_tokens=None):
+        if device_ptr is not None:
+            self._check(self._lib.pcpb_worker_set_tokens(self._h, device_ptr, n_tokens))
+            return
+        self._tokens = np.ascontiguousarray(tokens, dtype=np.uint16)          # must outlive the round
+        self._check(self._lib.pcpb_worker_set_tokens(self._h, self._tokens.ctypes.data, self._tokens.size))
+
+    def worker_step(self):
+        self._check(self._lib.pcpb_worker_step(self._h))
+
+    def worker_end_round(self, steps, param_dtype=F32, want_delta=True):
+        P = self.model_info()["total_params"]
+        losses = np.zeros(max(steps, 1), dtype=np.float32)
+        if want_delta:
+            delta = np.empty(P, dtype=np.float32 if param_dtype == F32 else np.uint16)
+            self._check(self._lib.pcpb_worker_end_round(self._h, delta.ctypes.data, delta.nbytes, losses.ctypes.data, steps))
+        else:
+            delta = None
+            self._check(self._lib.pcpb_worker_end_round(self._h, None, 0, losses.ctypes.data, steps))
+        return delta, losses[:steps]
+
+    def inner_loop(self, params_blob, tokens, tau, param_dtype=F32, accumulation_steps=1):
+        cfg = InnerCfg(tau, accumulation_steps, param_dtype, 0, 0)
+        a, ptr, nbytes = _as_bytes_array(params_blob)
+        tok = np.ascontiguousarray(tokens, dtype=np.uint16)
+        P = self.model_info()["total_params"]
+        delta = np.empty(P, dtype=np.float32 if param_dtype == F32 else np.uint16)
+        losses = np.zeros(max(tau, 1), dtype=np.float32)
+        self._check(self._lib.pcpb_inner_loop(self._h, C.byref(cfg), ptr, nbytes, tok.ctypes.data, tok.size,
+                                              delta.ctypes.data, delta.nbytes, losses.ctypes.data))
+        return delta, losses[:tau]
+
+    def worker_read_state(self, which: str):
+        sel = {"params": 0, "m": 1, "v": 2, "delta": 3, "master": 4, "velocity": 5, "grads": 6}[which]
+        n = self.model_info()["total_params"] if sel != 5 else self._shard_len
+        out = np.empty(n, dtype=np.float32)
+        self._check(self._lib.pcpb_worker_read_state(self._h, sel, out.ctypes.data, n))
+        return out
+
+    # -- outer step
+    def outer_export(self) -> bytes:
+        buf = C.create_string_buffer(2 * IPC_HANDLE_BYTES)
+        self._check(self._lib.pcpb_outer_export(self._h, buf))
+        return buf.raw
+
+    def _set_shard(self, world):
+        P = self.model_info()["total_params"]
+        s = (P + world - 1) // world
+        self._shard_len = (s + 255) // 256 * 256
+
+    def outer_attach_ipc(self, rank, world, all_handles: bytes):
+        self._check(self._lib.pcpb_outer_attach_ipc(self._h, rank, world, all_handles))
+        self._set_shard(world)
+
+    def outer_attach_local(self, rank, peers):
+        arr = (C.c_void_p * len(peers))(*[p._h for p in peers])
+        self._check(self._lib.pcpb_outer_attach_local(self._h, rank, len(peers), arr))
+        self._set_shard(len(peers))
+
+    def outer_prepare(self, learning_rate=0.7, momentum=0.9, param_dtype=F32):
+        cfg = OuterCfg(learning_rate, momentum, param_dtype)
+        self._check(self._lib.pcpb_outer_prepare(self._h, C.byref(cfg)))
+
+    def outer_apply(self, learning_rate=0.7, momentum=0.9, param_dtype=F32, contributors=None) -> float:
+        cfg = OuterCfg(learning_rate, momentum, param_dtype)
+        ms = C.c_double()
+        if contributors is None:
+            self._check(self._lib.pcpb_outer_apply(self._h, C.byref(cfg), None, 0, C.byref(ms)))
+        else:
+            arr = (C.c_int * len(contributors))(*contributors)
+            self._check(self._lib.pcpb_outer_apply(self._h, C.byref(cfg), arr, len(contributors), C.byref(ms)))
+        return ms.value

@@ -1,0 +1,774 @@
+// Training-step kernels, generic path: correct for every shape and both model dtypes (f32, bf16).
+// The tensor-core kernels in gemm_tc.cu / attn_tc.cu take over for bf16 shapes they support.
+//
+// Numerical contract (what the reference's compiled graph computes; see the file:line notes):
+//  * values of model dtype are rounded per op exactly where the exported graph has an op of that
+//    type (models/nanochat_d8_b8_t2048_bf16.mlir), statistics / softmax / loss are f32;
+//  * forward divides and logs carry +1e-4 (src/compiler/sanitizer.zig:8-111), the divide / log /
+//    rsqrt VJP rules carry another +1e-4 (src/autodiff/vjp_rules.zig:198,1510,1543).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace pcpb {
+
+#define DISPATCH_DT(dt, ...)                                   \
+  do {                                                         \
+    if ((dt) == DT_F32) { typedef float T; __VA_ARGS__; }      \
+    else if ((dt) == DT_BF16) { typedef bf16 T; __VA_ARGS__; } \
+    else return cudaErrorInvalidValue;                         \
+  } while (0)
+
+static inline unsigned cdiv(size_t a, size_t b) { return (unsigned)((a + b - 1) / b); }
+
+// =================================================================================================
+// conversions, batching
+// =================================================================================================
+template <typename T>
+__global__ void k_convert_f32(const float* __restrict__ in, T* __restrict__ out, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) out[i] = from_f<T>(in[i]);
+}
+template <typename T>
+__global__ void k_widen_f32(const T* __restrict__ in, float* __restrict__ out, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) out[i] = to_f<T>(in[i]);
+}
+cudaError_t launch_convert_f32(cudaStream_t st, int dt, const float* in, void* out, size_t n) {
+  if (n == 0) return cudaSuccess;
+  unsigned grid = min(cdiv(n, 256), 148u * 16);
+  DISPATCH_DT(dt, (k_convert_f32<T><<<grid, 256, 0, st>>>(in, (T*)out, n)));
+  return cudaGetLastError();
+}
+cudaError_t launch_widen_to_f32(cudaStream_t st, int dt, const void* in, float* out, size_t n) {
+  if (n == 0) return cudaSuccess;
+  unsigned grid = min(cdiv(n, 256), 148u * 16);
+  DISPATCH_DT(dt, (k_widen_f32<T><<<grid, 256, 0, st>>>((const T*)in, out, n)));
+  return cudaGetLastError();
+}
+
+// FIFO batch: inputs = window[0:BT], targets = window[1:BT+1], widened to i64
+// (src/data/loader.zig:555-589).
+__global__ void k_fifo_batch(const uint16_t* __restrict__ tok, long long cursor, long long bt,
+                             long long* __restrict__ x, long long* __restrict__ y) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (; i < bt; i += stride) {
+    x[i] = (long long)tok[cursor + i];
+    y[i] = (long long)tok[cursor + i + 1];
+  }
+}
+cudaError_t launch_fifo_batch(cudaStream_t st, const uint16_t* tokens, long long cursor, long long bt,
+                              long long* inputs, long long* targets) {
+  if (bt == 0) return cudaSuccess;
+  k_fifo_batch<<<min(cdiv(bt, 256), 148u * 8), 256, 0, st>>>(tokens, cursor, bt, inputs, targets);
+  return cudaGetLastError();
+}
+
+// =================================================================================================
+// RMSNorm (parameter free).  y = x * T(rsqrt(sum(x^2)/(d+1e-4) + 1e-5)); tsave = the rsqrt argument.
+// =================================================================================================
+template <typename T>
+__device__ __forceinline__ void rmsnorm_row_fwd(const T* __restrict__ xr, T* __restrict__ yr, int d,
+                                                float* tsave_slot, float* red) {
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < d; j += blockDim.x) { float v = to_f(xr[j]); ss += v * v; }
+  ss = block_sum(ss, red);
+  const float t = ss / ((float)d + PCPB_GUARD) + 1e-5f;
+  const float r = rnd<T>(rsqrtf(t));
+  if (threadIdx.x == 0 && tsave_slot) *tsave_slot = t;
+  for (int j = threadIdx.x; j < d; j += blockDim.x) yr[j] = from_f<T>(to_f(xr[j]) * r);
+}
+
+template <typename T>
+__global__ void k_rmsnorm_fwd(const T* __restrict__ x, int d, T* __restrict__ y, float* __restrict__ tsave) {
+  __shared__ float red[32];
+  const size_t m = blockIdx.x;
+  rmsnorm_row_fwd<T>(x + m * d, y + m * d, d, tsave ? tsave + m : nullptr, red);
+}
+template <typename T>
+__global__ void k_embed_norm_fwd(const T* __restrict__ wte, const long long* __restrict__ idx, int d, int V,
+                                 T* __restrict__ y, float* __restrict__ tsave) {
+  __shared__ float red[32];
+  const size_t m = blockIdx.x;
+  long long row = idx[m];
+  row = row < 0 ? 0 : (row >= V ? V - 1 : row);       // gather clamps start indices
+  rmsnorm_row_fwd<T>(wte + (size_t)row * d, y + m * d, d, tsave + m, red);
+}
+
+// Backward of y = x * T(r), r = rsqrt(t), t = sum(x^2)/(d+1e-4) + 1e-5:
+//   multiply VJP:   dx1 = T(dy * T(r));   dr = T(sum_j T(dy_j * x_j))
+//   rsqrt VJP:      dt = (dr * -0.5) * rsqrt(t + 1e-4)^3
+//   divide VJP:     ds = dt / ((d + 1e-4) + 1e-4)
+//   power VJP:      dx2 = T(ds * 2 * x)      (x^2/x == x up to one ulp; 0 at x == 0)
+template <typename T>
+__device__ __forceinline__ float rmsnorm_row_ds(const T* __restrict__ xr, const T* __restrict__ dyr, int d,
+                                                float t, float* red) {
+  float acc = 0.f;
+  for (int j = threadIdx.x; j < d; j += blockDim.x) acc += rnd<T>(to_f(dyr[j]) * to_f(xr[j]));
+  acc = block_sum(acc, red);
+  const float dr = rnd<T>(acc);
+  const float rp = rsqrtf(t + PCPB_GUARD);
+  const float dt = (dr * -0.5f) * ((rp * rp) * rp);
+  return dt / (((float)d + PCPB_GUARD) + PCPB_GUARD);
+}
+
+template <typename T>
+__global__ void k_rmsnorm_bwd(const T* __restrict__ x, const float* __restrict__ tsave, const T* __restrict__ dy,
+                              const T* __restrict__ dres, int d, T* __restrict__ dx) {
+  __shared__ float red[32];
+  const size_t m = blockIdx.x;
+  const T* xr = x + m * d; const T* dyr = dy + m * d;
+  const float t = tsave[m];
+  const float ds = rmsnorm_row_ds<T>(xr, dyr, d, t, red);
+  const float r = rnd<T>(rsqrtf(t));
+  for (int j = threadIdx.x; j < d; j += blockDim.x) {
+    const float xv = to_f(xr[j]);
+    float g = rnd<T>(to_f(dyr[j]) * r) + rnd<T>(ds * (2.f * xv));
+    if (dres) g += to_f(dres[m * d + j]);
+    dx[m * d + j] = from_f<T>(g);
+  }
+}
+template <typename T>
+__global__ void k_embed_norm_bwd(const T* __restrict__ wte, const long long* __restrict__ idx, int d, int V,
+                                 const T* __restrict__ dy, const float* __restrict__ tsave,
+                                 float* __restrict__ dwte) {
+  __shared__ float red[32];
+  const size_t m = blockIdx.x;
+  long long row = idx[m];
+  row = row < 0 ? 0 : (row >= V ? V - 1 : row);
+  const T* xr = wte + (size_t)row * d; const T* dyr = dy + m * d;
+  const float t = tsave[m];
+  const float ds = rmsnorm_row_ds<T>(xr, dyr, d, t, red);
+  const float r = rnd<T>(rsqrtf(t));
+  for (int j = threadIdx.x; j < d; j += blockDim.x) {
+    const float xv = to_f(xr[j]);
+    const float g = rnd<T>(rnd<T>(to_f(dyr[j]) * r) + rnd<T>(ds * (2.f * xv)));
+    atomicAdd(dwte + (size_t)row * d + j, g);
+  }
+}
+
+static inline int norm_threads(int d) { return d >= 1024 ? 256 : (d >= 256 ? 128 : 64); }
+
+cudaError_t launch_rmsnorm_fwd(cudaStream_t st, int dt, const void* x, int M, int d, void* y, float* tsave) {
+  if (M == 0) return cudaSuccess;
+  DISPATCH_DT(dt, (k_rmsnorm_fwd<T><<<M, norm_threads(d), 0, st>>>((const T*)x, d, (T*)y, tsave)));
+  return cudaGetLastError();
+}
+cudaError_t launch_embed_norm_fwd(cudaStream_t st, int dt, const void* wte, const long long* idx, int M, int d,
+                                  int V, void* x, float* tsave) {
+  if (M == 0) return cudaSuccess;
+  DISPATCH_DT(dt, (k_embed_norm_fwd<T><<<M, norm_threads(d), 0, st>>>((const T*)wte, idx, d, V, (T*)x, tsave)));
+  return cudaGetLastError();
+}
+cudaError_t launch_rmsnorm_bwd(cudaStream_t st, int dt, const void* x, const float* tsave, const void* dy,
+                               const void* dres, int M, int d, void* dx) {
+  if (M == 0) return cudaSuccess;
+  DISPATCH_DT(dt, (k_rmsnorm_bwd<T><<<M, norm_threads(d), 0, st>>>((const T*)x, tsave, (const T*)dy,
+                                                                    (const T*)dres, d, (T*)dx)));
+  return cudaGetLastError();
+}
+cudaError_t launch_embed_norm_bwd(cudaStream_t st, int dt, const void* wte, const long long* idx, int M, int d,
+                                  int V, const void* dy, const float* tsave, float* dwte) {
+  if (M == 0) return cudaSuccess;
+  DISPATCH_DT(dt, (k_embed_norm_bwd<T><<<M, norm_threads(d), 0, st>>>((const T*)wte, idx, d, V, (const T*)dy,
+                                                                       tsave, dwte)));
+  return cudaGetLastError();
+}
+
+// =================================================================================================
+// RoPE (half split, bf16 tables) + per-head RMSNorm of q and k.  One warp per (token, head).
+// =================================================================================================
+template <typename T>
+__device__ __forceinline__ float table_val(const uint16_t* tab, size_t i) {
+  // tables are bf16; an f32 model converts them to f32 (exact), a bf16 model uses them as they are
+  return __uint_as_float(((uint32_t)tab[i]) << 16);
+}
+
+template <typename T>
+__global__ void k_rope_qknorm_fwd(const T* __restrict__ qkv, const uint16_t* __restrict__ cosT,
+                                  const uint16_t* __restrict__ sinT, int M, int Tlen, int H, int Hkv, int hd,
+                                  T* __restrict__ qkn, float* __restrict__ tq) {
+  const int heads = H + Hkv;
+  const long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= (long long)M * heads) return;
+  const int m = (int)(gw / heads), h = (int)(gw % heads);
+  const int wqkv = (H + 2 * Hkv) * hd, wqkn = heads * hd;
+  const T* src = qkv + (size_t)m * wqkv + (size_t)h * hd;          // q heads then k heads are contiguous
+  T* dst = qkn + (size_t)m * wqkn + (size_t)h * hd;
+  const int half = hd >> 1, pos = m % Tlen;
+  float ss = 0.f;
+  for (int i = lane; i < half; i += 32) {
+    const float x1 = to_f(src[i]), x2 = to_f(src[i + half]);
+    const float c = table_val<T>(cosT, (size_t)pos * half + i), s = table_val<T>(sinT, (size_t)pos * half + i);
+    const float y1 = rnd<T>(rnd<T>(x1 * c) + rnd<T>(x2 * s));
+    const float y2 = rnd<T>(rnd<T>(x1 * (-s)) + rnd<T>(x2 * c));
+    ss += y1 * y1 + y2 * y2;
+  }
+  ss = warp_sum(ss);
+  const float t = ss / ((float)hd + PCPB_GUARD) + 1e-5f;
+  const float r = rnd<T>(rsqrtf(t));
+  if (lane == 0) tq[(size_t)m * heads + h] = t;
+  for (int i = lane; i < half; i += 32) {
+    const float x1 = to_f(src[i]), x2 = to_f(src[i + half]);
+    const float c = table_val<T>(cosT, (size_t)pos * half + i), s = table_val<T>(sinT, (size_t)pos * half + i);
+    const float y1 = rnd<T>(rnd<T>(x1 * c) + rnd<T>(x2 * s));
+    const float y2 = rnd<T>(rnd<T>(x1 * (-s)) + rnd<T>(x2 * c));
+    dst[i] = from_f<T>(y1 * r);
+    dst[i + half] = from_f<T>(y2 * r);
+  }
+}
+
+template <typename T>
+__global__ void k_rope_qknorm_bwd(const T* __restrict__ qkv, const T* __restrict__ dqkn,
+                                  const float* __restrict__ tq, const uint16_t* __restrict__ cosT,
+                                  const uint16_t* __restrict__ sinT, int M, int Tlen, int H, int Hkv, int hd,
+                                  T* __restrict__ dqkv) {
+  const int heads = H + Hkv;
+  const long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= (long long)M * heads) return;
+  const int m = (int)(gw / heads), h = (int)(gw % heads);
+  const int wqkv = (H + 2 * Hkv) * hd, wqkn = heads * hd;
+  const T* src = qkv + (size_t)m * wqkv + (size_t)h * hd;
+  const T* dyp = dqkn + (size_t)m * wqkn + (size_t)h * hd;
+  T* dst = dqkv + (size_t)m * wqkv + (size_t)h * hd;
+  const int half = hd >> 1, pos = m % Tlen;
+  const float t = tq[(size_t)m * heads + h];
+  // pass 1: dr = T(sum T(dy * y)) over the head
+  float acc = 0.f;
+  for (int i = lane; i < half; i += 32) {
+    const float x1 = to_f(src[i]), x2 = to_f(src[i + half]);
+    const float c = table_val<T>(cosT, (size_t)pos * half + i), s = table_val<T>(sinT, (size_t)pos * half + i);
+    const float y1 = rnd<T>(rnd<T>(x1 * c) + rnd<T>(x2 * s));
+    const float y2 = rnd<T>(rnd<T>(x1 * (-s)) + rnd<T>(x2 * c));
+    acc += rnd<T>(to_f(dyp[i]) * y1) + rnd<T>(to_f(dyp[i + half]) * y2);
+  }
+  acc = warp_sum(acc);
+  const float dr = rnd<T>(acc);
+  const float rp = rsqrtf(t + PCPB_GUARD);
+  const float dtt = (dr * -0.5f) * ((rp * rp) * rp);
+  const float ds = dtt / (((float)hd + PCPB_GUARD) + PCPB_GUARD);
+  const float r = rnd<T>(rsqrtf(t));
+  for (int i = lane; i < half; i += 32) {
+    const float x1 = to_f(src[i]), x2 = to_f(src[i + half]);
+    const float c = table_val<T>(cosT, (size_t)pos * half + i), s = table_val<T>(sinT, (size_t)pos * half + i);
+    const float y1 = rnd<T>(rnd<T>(x1 * c) + rnd<T>(x2 * s));
+    const float y2 = rnd<T>(rnd<T>(x1 * (-s)) + rnd<T>(x2 * c));
+    // gradient wrt the roped value y
+    const float g1 = rnd<T>(rnd<T>(to_f(dyp[i]) * r) + rnd<T>(ds * (2.f * y1)));
+    const float g2 = rnd<T>(rnd<T>(to_f(dyp[i + half]) * r) + rnd<T>(ds * (2.f * y2)));
+    // y1 = x1*c + x2*s ; y2 = x1*(-s) + x2*c
+    dst[i] = from_f<T>(rnd<T>(g1 * c) + rnd<T>(g2 * (-s)));
+    dst[i + half] = from_f<T>(rnd<T>(g1 * s) + rnd<T>(g2 * c));
+  }
+}
+
+cudaError_t launch_rope_qknorm_fwd(cudaStream_t st, int dt, const void* qkv, const uint16_t* c, const uint16_t* s,
+                                   int M, int Tlen, int H, int Hkv, int hd, void* qkn, float* tq) {
+  const long long warps = (long long)M * (H + Hkv);
+  if (warps == 0) return cudaSuccess;
+  DISPATCH_DT(dt, (k_rope_qknorm_fwd<T><<<cdiv(warps * 32, 256), 256, 0, st>>>((const T*)qkv, c, s, M, Tlen, H, Hkv,
+                                                                                hd, (T*)qkn, tq)));
+  return cudaGetLastError();
+}
+cudaError_t launch_rope_qknorm_bwd(cudaStream_t st, int dt, const void* qkv, const void* dqkn, const float* tq,
+                                   const uint16_t* c, const uint16_t* s, int M, int Tlen, int H, int Hkv, int hd,
+                                   void* dqkv) {
+  const long long warps = (long long)M * (H + Hkv);
+  if (warps == 0) return cudaSuccess;
+  DISPATCH_DT(dt, (k_rope_qknorm_bwd<T><<<cdiv(warps * 32, 256), 256, 0, st>>>((const T*)qkv, (const T*)dqkn, tq, c,
+                                                                                s, M, Tlen, H, Hkv, hd, (T*)dqkv)));
+  return cudaGetLastError();
+}
+
+// =================================================================================================
+// Generic GEMM: 64x64 tile, BK=16, 256 threads, 4x4 per thread, f32 accumulate.
+// =================================================================================================
+template <typename T>
+__device__ __forceinline__ void gemm_epilogue(const GemmArgs& g, int m, int n, float acc) {
+  const size_t o = (size_t)m * g.ldc + n;
+  switch (g.epi) {
+    case EPI_STORE:
+      ((T*)g.C)[o] = from_f<T>(acc);
+      break;
+    case EPI_RESID:
+      ((T*)g.C)[o] = from_f<T>(to_f(((const T*)g.R)[o]) + rnd<T>(acc));
+      break;
+    case EPI_RELU2: {
+      const T u = from_f<T>(acc);
+      ((T*)g.C)[o] = u;
+      const float r = fmaxf(to_f(u), 0.f);
+      ((T*)g.C2)[o] = from_f<T>(r * r);
+      break;
+    }
+    case EPI_DRELU2: {
+      // a = power(max(u,0), 2).  power VJP (src/autodiff/vjp_rules.zig:252): g * (2 * (a / r)), 0 at r == 0;
+      // maximum VJP (:499): pass where u > 0.
+      const float da = rnd<T>(acc);
+      const float u = to_f(((const T*)g.R)[o]);
+      const float r = fmaxf(u, 0.f);
+      float out = 0.f;
+      if (u > 0.f) {
+        const float y = rnd<T>(r * r);
+        const float q = rnd<T>(y / r);
+        out = rnd<T>(da * rnd<T>(2.f * q));
+      }
+      ((T*)g.C)[o] = from_f<T>(out);
+      break;
+    }
+    case EPI_WGRAD: {
+      float v = rnd<T>(acc);
+      if (!((v - v) == 0.f)) v = 0.f;                       // finite guard
+      v = fminf(fmaxf(v, -g.clip), g.clip);
+      ((float*)g.C)[o] = v;
+      break;
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) k_gemm_generic(GemmArgs g) {
+  __shared__ float As[16][64 + 4];
+  __shared__ float Bs[16][64 + 4];
+  const T* __restrict__ A = (const T*)g.A;
+  const T* __restrict__ B = (const T*)g.B;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  const bool a_kfast = (g.sak == 1), b_nfast = (g.sbn == 1);
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+  for (int k0 = 0; k0 < g.K; k0 += 16) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * 256;
+      int mm, kk;
+      if (a_kfast) { kk = idx & 15; mm = idx >> 4; } else { mm = idx & 63; kk = idx >> 6; }
+      const int gm = m0 + mm, gk = k0 + kk;
+      As[kk][mm] = (gm < g.M && gk < g.K) ? to_f(A[(size_t)gm * g.sam + (size_t)gk * g.sak]) : 0.f;
+      int nn, kb;
+      if (b_nfast) { nn = idx & 63; kb = idx >> 6; } else { kb = idx & 15; nn = idx >> 4; }
+      const int gn = n0 + nn, gkb = k0 + kb;
+      Bs[kb][nn] = (gn < g.N && gkb < g.K) ? to_f(B[(size_t)gkb * g.sbk + (size_t)gn * g.sbn]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= g.M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < g.N) gemm_epilogue<T>(g, m, n, acc[i][j]);
+    }
+  }
+}
+
+cudaError_t launch_gemm_generic(cudaStream_t st, int dt, const GemmArgs& g) {
+  if (g.M == 0 || g.N == 0) return cudaSuccess;
+  dim3 grid(cdiv(g.N, 64), cdiv(g.M, 64));
+  DISPATCH_DT(dt, (k_gemm_generic<T><<<grid, 256, 0, st>>>(g)));
+  return cudaGetLastError();
+}
+
+// =================================================================================================
+// Generic causal attention.  One block per (query row, batch*head).
+//   s_j = T(T(q.k_j) * scale), masked (j > i) entries contribute 0;  P = T(e / (l + 1e-4));
+//   o = T(sum_j P_j v_j).
+// Backward (softmax through the guarded divide, exp, subtract and reduce-max rules):
+//   Pt_j = e_j / (l + 2e-4);  dp_j = T(do . v_j);  D = sum_j Pt_j dp_j;
+//   dsf_j = Pt_j (dp_j - D) - [s_j == max] D 2e-4/(l + 2e-4);  ds_j = T(T(dsf_j) * scale).
+// =================================================================================================
+template <typename T>
+__global__ void __launch_bounds__(128) k_attn_fwd_generic(AttnArgs a) {
+  extern __shared__ float sm[];
+  float* sc = sm;                 // [T]
+  float* qrow = sm + a.T;         // [hd]
+  __shared__ float red[32];
+  const int i = blockIdx.x, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
+  const int hk = h / (a.H / a.Hkv);
+  const int d = a.H * a.hd, dkv = a.Hkv * a.hd, wqkn = d + dkv, wqkv = d + 2 * dkv;
+  const T* qkn = (const T*)a.qkn; const T* qkv = (const T*)a.qkv;
+  const size_t mi = (size_t)b * a.T + i;
+  for (int e = threadIdx.x; e < a.hd; e += blockDim.x) qrow[e] = to_f(qkn[mi * wqkn + h * a.hd + e]);
+  __syncthreads();
+  float mx = -INFINITY;
+  for (int j = threadIdx.x; j <= i; j += blockDim.x) {
+    const T* kr = qkn + ((size_t)b * a.T + j) * wqkn + d + hk * a.hd;
+    float dot = 0.f;
+    for (int e = 0; e < a.hd; ++e) dot = fmaf(qrow[e], to_f(kr[e]), dot);
+    const float s = rnd<T>(rnd<T>(dot) * a.scale);
+    sc[j] = s;
+    mx = fmaxf(mx, s);
+  }
+  mx = block_max(mx, red);
+  float l = 0.f;
+  for (int j = threadIdx.x; j <= i; j += blockDim.x) { const float e = expf(sc[j] - mx); sc[j] = e; l += e; }
+  l = block_sum(l, red);
+  const float inv = 1.f / (l + PCPB_GUARD);
+  for (int j = threadIdx.x; j <= i; j += blockDim.x) sc[j] = rnd<T>(sc[j] / (l + PCPB_GUARD));
+  (void)inv;
+  __syncthreads();
+  if (threadIdx.x == 0) { a.mrow[(size_t)bh * a.T + i] = mx; a.lrow[(size_t)bh * a.T + i] = l; }
+  for (int e = threadIdx.x; e < a.hd; e += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j <= i; ++j)
+      acc = fmaf(sc[j], to_f(qkv[((size_t)b * a.T + j) * wqkv + d + dkv + hk * a.hd + e]), acc);
+    ((T*)a.o)[mi * d + h * a.hd + e] = from_f<T>(acc);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) k_attn_bwd_generic(AttnArgs a) {
+  extern __shared__ float sm[];
+  float* ds = sm;                    // [T]  scaled score gradients
+  float* pf = sm + a.T;              // [T]  forward probabilities (model dtype values)
+  float* qrow = sm + 2 * a.T;        // [hd]
+  float* dorow = qrow + a.hd;        // [hd]
+  __shared__ float red[32];
+  const int i = blockIdx.x, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
+  const int hk = h / (a.H / a.Hkv);
+  const int d = a.H * a.hd, dkv = a.Hkv * a.hd, wqkn = d + dkv, wqkv = d + 2 * dkv;
+  const T* qkn = (const T*)a.qkn; const T* qkv = (const T*)a.qkv; const T* dout = (const T*)a.dout;
+  const size_t mi = (size_t)b * a.T + i;
+  for (int e = threadIdx.x; e < a.hd; e += blockDim.x) {
+    qrow[e] = to_f(qkn[mi * wqkn + h * a.hd + e]);
+    dorow[e] = to_f(dout[mi * d + h * a.hd + e]);
+  }
+  __syncthreads();
+  const float mx = a.mrow[(size_t)bh * a.T + i], l = a.lrow[(size_t)bh * a.T + i];
+  const float den2 = l + 2.f * PCPB_GUARD;
+  float Dp = 0.f;
+  for (int j = threadIdx.x; j <= i; j += blockDim.x) {
+    const T* kr = qkn + ((size_t)b * a.T + j) * wqkn + d + hk * a.hd;
+    const T* vr = qkv + ((size_t)b * a.T + j) * wqkv + d + dkv + hk * a.hd;
+    float dot = 0.f, dp = 0.f;
+    for (int e = 0; e < a.hd; ++e) {
+      dot = fmaf(qrow[e], to_f(kr[e]), dot);
+      dp = fmaf(dorow[e], to_f(vr[e]), dp);
+    }
+    const float s = rnd<T>(rnd<T>(dot) * a.scale);
+    const float ex = expf(s - mx);
+    dp = rnd<T>(dp);
+    pf[j] = rnd<T>(ex / (l + PCPB_GUARD));
+    const float pt = ex / den2;
+    Dp += pt * dp;
+    ds[j] = pt;                       // stash Pt, finish after D is known
+    sm[2 * a.T + 2 * a.hd + j] = dp;  // [T] dp
+    sm[3 * a.T + 2 * a.hd + j] = (s == mx) ? 1.f : 0.f;
+  }
+  const float D = block_sum(Dp, red);
+  const float mterm = D * (2.f * PCPB_GUARD) / den2;
+  for (int j = threadIdx.x; j <= i; j += blockDim.x) {
+    const float dp = sm[2 * a.T + 2 * a.hd + j];
+    const float dsf = ds[j] * (dp - D) - sm[3 * a.T + 2 * a.hd + j] * mterm;
+    ds[j] = rnd<T>(rnd<T>(dsf) * a.scale);
+  }
+  __syncthreads();
+  // dq_i = T(sum_j ds_j k_j)
+  for (int e = threadIdx.x; e < a.hd; e += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j <= i; ++j) acc = fmaf(ds[j], to_f(qkn[((size_t)b * a.T + j) * wqkn + d + hk * a.hd + e]), acc);
+    ((T*)a.dqkn)[mi * wqkn + h * a.hd + e] = from_f<T>(acc);
+  }
+  // dk_j += ds_j q_i ; dv_j += P_j do_i   (f32 accumulators shared by the heads of one kv group)
+  for (int idx = threadIdx.x; idx < (i + 1) * a.hd; idx += blockDim.x) {
+    const int j = idx / a.hd, e = idx % a.hd;
+    float* dst = a.dkv_acc + ((size_t)b * a.T + j) * (2 * dkv);
+    atomicAdd(dst + hk * a.hd + e, ds[j] * qrow[e]);
+    atomicAdd(dst + dkv + hk * a.hd + e, pf[j] * dorow[e]);
+  }
+}
+
+template <typename T>
+__global__ void k_attn_bwd_finish(const float* __restrict__ acc, int M, int d, int dkv, T* __restrict__ dqkn,
+                                  T* __restrict__ dqkv) {
+  const size_t n = (size_t)M * 2 * dkv;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t m = i / (2 * dkv); const int c = (int)(i % (2 * dkv));
+    if (c < dkv) dqkn[m * (d + dkv) + d + c] = from_f<T>(acc[i]);
+    else dqkv[m * (d + 2 * dkv) + d + c] = from_f<T>(acc[i]);     // c in [dkv, 2dkv) -> column d + dkv + (c-dkv)
+  }
+}
+
+cudaError_t launch_attn_fwd_generic(cudaStream_t st, int dt, const AttnArgs& a) {
+  if (a.B == 0 || a.T == 0) return cudaSuccess;
+  dim3 grid(a.T, a.B * a.H);
+  const size_t smem = (size_t)(a.T + a.hd) * sizeof(float);
+  DISPATCH_DT(dt, (k_attn_fwd_generic<T><<<grid, 128, smem, st>>>(a)));
+  return cudaGetLastError();
+}
+cudaError_t launch_attn_bwd_generic(cudaStream_t st, int dt, const AttnArgs& a) {
+  if (a.B == 0 || a.T == 0) return cudaSuccess;
+  const int M = a.B * a.T, d = a.H * a.hd, dkv = a.Hkv * a.hd;
+  cudaError_t e = cudaMemsetAsync(a.dkv_acc, 0, (size_t)M * 2 * dkv * sizeof(float), st);
+  if (e != cudaSuccess) return e;
+  dim3 grid(a.T, a.B * a.H);
+  const size_t smem = (size_t)(4 * a.T + 2 * a.hd) * sizeof(float);
+  if (smem > 48 * 1024) {
+    if (dt == DT_F32) e = cudaFuncSetAttribute(k_attn_bwd_generic<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    else e = cudaFuncSetAttribute(k_attn_bwd_generic<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  DISPATCH_DT(dt, (k_attn_bwd_generic<T><<<grid, 128, smem, st>>>(a)));
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  DISPATCH_DT(dt, (k_attn_bwd_finish<T><<<min(cdiv((size_t)M * 2 * dkv, 256), 148u * 8), 256, 0, st>>>(
+                      a.dkv_acc, M, d, dkv, (T*)a.dqkn, (T*)a.dqkv)));
+  return cudaGetLastError();
+}
+
+// =================================================================================================
+// Soft-capped cross entropy, forward + backward in one pass pair per row.
+//   c = cap * tanh(z / (cap + 1e-4));  sh = c - max;  se = sum exp(sh);  logp = sh - log(se + 1e-4)
+//   loss = sum_valid(-logp[target]) / (count + 1e-4)
+// Backward (dtot = 1/(count + 2e-4)):
+//   dc_j = dtot * (exp(sh_j)/(se + 2e-4) - [j == target] + [c_j == max] * 2e-4/(se + 2e-4))
+//   dz_j = T(dc_j * cap * (1 - tanh^2) / (cap + 2e-4))
+// =================================================================================================
+__global__ void k_count_valid(const long long* __restrict__ tg, int M, long long ignore, float* __restrict__ count) {
+  __shared__ float red[32];
+  float c = 0.f;
+  for (int i = threadIdx.x; i < M; i += blockDim.x) c += (tg[i] != ignore) ? 1.f : 0.f;
+  c = block_sum(c, red);                      // counts are integers < 2^24 per partial: exact in f32
+  if (threadIdx.x == 0) *count = c;
+}
+cudaError_t launch_count_valid(cudaStream_t st, const long long* targets, int M, long long ignore, float* count) {
+  k_count_valid<<<1, 1024, 0, st>>>(targets, M, ignore, count);
+  return cudaGetLastError();
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) k_softcap_ce(T* __restrict__ logits, const long long* __restrict__ tg, int V,
+                                                    float cap, long long ignore, const float* __restrict__ count,
+                                                    float* __restrict__ rowloss, int write_grad) {
+  __shared__ float red[32];
+  const size_t m = blockIdx.x;
+  T* z = logits + m * V;
+  const long long t = tg[m];
+  const bool valid = (t != ignore);
+  const float capg = cap + PCPB_GUARD;
+  float mx = -INFINITY;
+  for (int j = threadIdx.x; j < V; j += blockDim.x) mx = fmaxf(mx, tanhf(to_f(z[j]) / capg) * cap);
+  mx = block_max(mx, red);
+  float se = 0.f;
+  for (int j = threadIdx.x; j < V; j += blockDim.x) se += expf(tanhf(to_f(z[j]) / capg) * cap - mx);
+  se = block_sum(se, red);
+  if (threadIdx.x == 0) {
+    float nll = 0.f;
+    if (valid) {
+      long long tt = t < 0 ? 0 : (t >= V ? V - 1 : t);
+      const float c = tanhf(to_f(z[tt]) / capg) * cap;
+      nll = -((c - mx) - logf(se + PCPB_GUARD));
+    }
+    rowloss[m] = nll;
+  }
+  if (!write_grad) return;
+  const float dtot = valid ? 1.f / (*count + 2.f * PCPB_GUARD) : 0.f;
+  const float den = se + 2.f * PCPB_GUARD;
+  const float dzscale = cap / (capg + PCPB_GUARD);
+  for (int j = threadIdx.x; j < V; j += blockDim.x) {
+    const float th = tanhf(to_f(z[j]) / capg);
+    const float c = th * cap;
+    float dc = expf(c - mx) / den;
+    if ((long long)j == t) dc -= 1.f;
+    if (c == mx) dc += (2.f * PCPB_GUARD) / den;
+    dc *= dtot;
+    z[j] = from_f<T>(dc * dzscale * (1.f - th * th));
+  }
+}
+cudaError_t launch_softcap_ce(cudaStream_t st, int dt, void* logits, const long long* targets, int M, int V,
+                              float cap, long long ignore, const float* count, float* rowloss, int write_grad) {
+  if (M == 0) return cudaSuccess;
+  DISPATCH_DT(dt, (k_softcap_ce<T><<<M, 256, 0, st>>>((T*)logits, targets, V, cap, ignore, count, rowloss, write_grad)));
+  return cudaGetLastError();
+}
+
+__global__ void k_loss_finalize(const float* __restrict__ rowloss, int M, const float* __restrict__ count,
+                                float* __restrict__ loss) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < M; i += blockDim.x) s += rowloss[i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) *loss = s / (*count + PCPB_GUARD);
+}
+cudaError_t launch_loss_finalize(cudaStream_t st, const float* rowloss, int M, const float* count, float* loss) {
+  k_loss_finalize<<<1, 1024, 0, st>>>(rowloss, M, count, loss);
+  return cudaGetLastError();
+}
+
+// =================================================================================================
+// Fused multi-tensor AdamW (src/optimizers/adam_mlir.zig:50-149), f32, op order kept (no FMA
+// contraction) so results match an op-by-op f32 evaluation.
+//   pass 1: per-chunk sum of clamp(g,+-1000)^2 -> partial[chunk]
+//   pass 2: per-tensor sum of its partials in chunk order -> normsq[tensor]
+//   pass 3: update
+// =================================================================================================
+__global__ void __launch_bounds__(256) k_adam_sumsq(const TensorSeg* __restrict__ segs, const int* __restrict__ c2s,
+                                                    float* __restrict__ partial) {
+  __shared__ float red[32];
+  const int chunk = blockIdx.x;
+  const TensorSeg s = segs[c2s[chunk]];
+  const long long base = (long long)(chunk - s.first_chunk) * ADAM_CHUNK;
+  const long long end = min(base + (long long)ADAM_CHUNK, s.n);
+  float acc = 0.f;
+  for (long long i = base + threadIdx.x; i < end; i += blockDim.x) {
+    const float g = fminf(fmaxf(s.g[i], -1000.f), 1000.f);
+    acc += g * g;
+  }
+  acc = block_sum(acc, red);
+  if (threadIdx.x == 0) partial[chunk] = acc;
+}
+__global__ void k_adam_norm(const TensorSeg* __restrict__ segs, const float* __restrict__ partial,
+                            float* __restrict__ normsq) {
+  __shared__ float red[32];
+  const TensorSeg s = segs[blockIdx.x];
+  float acc = 0.f;
+  for (int c = threadIdx.x; c < s.num_chunks; c += blockDim.x) acc += partial[s.first_chunk + c];
+  acc = block_sum(acc, red);
+  if (threadIdx.x == 0) normsq[blockIdx.x] = acc;
+}
+template <typename T>
+__global__ void __launch_bounds__(256) k_adam_update(const TensorSeg* __restrict__ segs, const int* __restrict__ c2s,
+                                                     const float* __restrict__ normsq, AdamHyper h, int has_shadow) {
+  const int chunk = blockIdx.x;
+  const int si = c2s[chunk];
+  const TensorSeg s = segs[si];
+  const long long base = (long long)(chunk - s.first_chunk) * ADAM_CHUNK;
+  const long long end = min(base + (long long)ADAM_CHUNK, s.n);
+  const float norm = __fadd_rn(__fsqrt_rn(normsq[si]), h.eps);
+  const float scale = __fdiv_rn(h.max_norm, fmaxf(norm, h.max_norm));
+  const float omb1 = __fsub_rn(1.f, h.beta1), omb2 = __fsub_rn(1.f, h.beta2);
+  for (long long i = base + threadIdx.x; i < end; i += blockDim.x) {
+    const float p = s.p[i];
+    const float gc = __fmul_rn(s.g[i], scale);
+    const float m = __fadd_rn(__fmul_rn(h.beta1, s.m[i]), __fmul_rn(omb1, gc));
+    const float v = __fadd_rn(__fmul_rn(h.beta2, s.v[i]), __fmul_rn(omb2, __fmul_rn(gc, gc)));
+    const float mh = __fdiv_rn(m, h.m_corr), vh = __fdiv_rn(v, h.v_corr);
+    const float ratio = __fdiv_rn(mh, __fadd_rn(__fsqrt_rn(vh), h.eps));
+    const float pn = __fsub_rn(p, __fmul_rn(h.lr, __fadd_rn(ratio, __fmul_rn(h.wd, p))));
+    s.p_out[i] = pn; s.m_out[i] = m; s.v_out[i] = v;
+    if (has_shadow && s.shadow) ((T*)s.shadow)[i] = from_f<T>(pn);
+  }
+}
+cudaError_t launch_adamw(cudaStream_t st, int shadow_dt, const TensorSeg* segs, int nseg, const int* chunk2seg,
+                         int nchunks, float* partial, float* normsq, AdamHyper h) {
+  if (nseg == 0 || nchunks == 0) return cudaSuccess;
+  k_adam_sumsq<<<nchunks, 256, 0, st>>>(segs, chunk2seg, partial);
+  k_adam_norm<<<nseg, 256, 0, st>>>(segs, partial, normsq);
+  if (shadow_dt == DT_BF16) k_adam_update<bf16><<<nchunks, 256, 0, st>>>(segs, chunk2seg, normsq, h, 1);
+  else k_adam_update<float><<<nchunks, 256, 0, st>>>(segs, chunk2seg, normsq, h, shadow_dt == DT_F32 ? 1 : 0);
+  return cudaGetLastError();
+}
+
+__global__ void k_axpy(float* __restrict__ acc, const float* __restrict__ g, float alpha, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i < n; i += (size_t)gridDim.x * blockDim.x) acc[i] = __fadd_rn(acc[i], __fmul_rn(alpha, g[i]));
+}
+__global__ void k_scale(float* __restrict__ x, float alpha, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i < n; i += (size_t)gridDim.x * blockDim.x) x[i] = __fmul_rn(x[i], alpha);
+}
+cudaError_t launch_axpy_f32(cudaStream_t st, float* acc, const float* g, float alpha, size_t n) {
+  if (n == 0) return cudaSuccess;
+  k_axpy<<<min(cdiv(n, 256), 148u * 16), 256, 0, st>>>(acc, g, alpha, n);
+  return cudaGetLastError();
+}
+cudaError_t launch_scale_f32(cudaStream_t st, float* x, float alpha, size_t n) {
+  if (n == 0) return cudaSuccess;
+  k_scale<<<min(cdiv(n, 256), 148u * 16), 256, 0, st>>>(x, alpha, n);
+  return cudaGetLastError();
+}
+template <typename T>
+__global__ void k_round_guard(float* __restrict__ x, size_t n, float clip) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float v = rnd<T>(x[i]);
+    if (!((v - v) == 0.f)) v = 0.f;
+    x[i] = fminf(fmaxf(v, -clip), clip);
+  }
+}
+cudaError_t launch_round_guard_f32(cudaStream_t st, int dt, float* x, size_t n, float clip) {
+  if (n == 0) return cudaSuccess;
+  DISPATCH_DT(dt, (k_round_guard<T><<<min(cdiv(n, 256), 148u * 16), 256, 0, st>>>(x, n, clip)));
+  return cudaGetLastError();
+}
+__global__ void k_check_finite(const float* __restrict__ x, size_t n, int* __restrict__ flag) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int bad = 0;
+  for (; i < n; i += (size_t)gridDim.x * blockDim.x) { const float v = x[i]; bad |= !((v - v) == 0.f); }
+  if (bad) *flag = 1;
+}
+cudaError_t launch_check_finite(cudaStream_t st, const float* x, size_t n, int* flag) {
+  if (n == 0) return cudaSuccess;
+  k_check_finite<<<min(cdiv(n, 256), 148u * 16), 256, 0, st>>>(x, n, flag);
+  return cudaGetLastError();
+}
+
+// =================================================================================================
+// DiLoCo outer step (src/nodes/workers/worker.zig:1371-1412, src/algorithms/diloco.zig:929-1055,
+// src/optimizers/nesterov.zig:82-97)
+// =================================================================================================
+__global__ void k_delta(const float* __restrict__ t0, const float* __restrict__ t1, float* __restrict__ d, size_t n,
+                        int trunc) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = __fsub_rn(t0[i], t1[i]);
+    d[i] = trunc ? trunc_bf16(v) : v;
+  }
+}
+cudaError_t launch_delta(cudaStream_t st, const float* theta0, const float* theta, float* delta, size_t n, int trunc) {
+  if (n == 0) return cudaSuccess;
+  k_delta<<<min(cdiv(n, 256), 148u * 16), 256, 0, st>>>(theta0, theta, delta, n, trunc);
+  return cudaGetLastError();
+}
+
+__global__ void __launch_bounds__(256) k_nesterov_shard(OuterArgs a) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const float div = (float)a.ncontrib;
+  for (; i < a.n; i += stride) {
+    float acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+      if (w < a.ncontrib) acc = __fadd_rn(acc, a.deltas[w][i]);
+    acc = __fdiv_rn(acc, div);
+    if (!((acc - acc) == 0.f)) acc = 0.f;
+    const float vn = __fadd_rn(__fmul_rn(a.mu, a.vel[i]), acc);
+    a.vel[i] = vn;
+    float th = __fsub_rn(a.master[i], __fmul_rn(a.lr, __fadd_rn(acc, __fmul_rn(a.mu, vn))));
+    if (a.trunc) th = trunc_bf16(th);
+    a.master[i] = th;
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+      if (w < a.nouts) a.outs[w][i] = th;
+  }
+}
+cudaError_t launch_nesterov_shard(cudaStream_t st, const OuterArgs& a) {
+  if (a.n == 0) return cudaSuccess;
+  k_nesterov_shard<<<min(cdiv((size_t)a.n, 256), 148u * 8), 256, 0, st>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace pcpb

@@ -1,0 +1,120 @@
+// Host-callable launchers of the training-step kernels.  Every launcher enqueues on `st` and
+// returns the CUDA error of the launch; none allocates or synchronises.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace pcpb {
+
+// ---- GEMM ----------------------------------------------------------------------------------
+// C[M,N] (+epilogue) = sum_k A(m,k) * B(k,n), A(m,k) = A[m*sam + k*sak], B(k,n) = B[k*sbk + n*sbn],
+// f32 accumulation, operands of model dtype `dt` (DT_F32 | DT_BF16).
+enum GemmEpilogue : int {
+  EPI_STORE = 0,    // C = T(acc)
+  EPI_RESID = 1,    // C = T(R + T(acc))                  (residual add in model dtype)
+  EPI_RELU2 = 2,    // C = T(acc); C2 = T(max(C,0)^2)     (MLP activation, two outputs)
+  EPI_DRELU2 = 3,   // C = backward of max(.,0)^2 at U given dA = T(acc)
+  EPI_WGRAD = 4,    // Cf32 = clamp(finite(T(acc)), +-clip)   (weight gradient, f32 out)
+};
+struct GemmArgs {
+  const void* A; long long sam, sak;
+  const void* B; long long sbk, sbn;
+  void* C; long long ldc;
+  const void* R;        // EPI_RESID: residual [M,ldc];  EPI_DRELU2: U [M,ldc]
+  void* C2;             // EPI_RELU2: second output [M,ldc]
+  int M, N, K;
+  int epi;
+  float clip;           // EPI_WGRAD
+};
+cudaError_t launch_gemm_generic(cudaStream_t st, int dt, const GemmArgs& g);
+
+// ---- elementwise / normalisation -------------------------------------------------------------
+cudaError_t launch_convert_f32(cudaStream_t st, int dt, const float* in, void* out, size_t n);
+cudaError_t launch_widen_to_f32(cudaStream_t st, int dt, const void* in, float* out, size_t n);
+cudaError_t launch_fifo_batch(cudaStream_t st, const uint16_t* tokens, long long cursor, long long bt,
+                              long long* inputs, long long* targets);
+cudaError_t launch_embed_norm_fwd(cudaStream_t st, int dt, const void* wte, const long long* idx, int M, int d,
+                                  int V, void* x, float* tsave);
+cudaError_t launch_embed_norm_bwd(cudaStream_t st, int dt, const void* wte, const long long* idx, int M, int d,
+                                  int V, const void* dy, const float* tsave, float* dwte);
+cudaError_t launch_rmsnorm_fwd(cudaStream_t st, int dt, const void* x, int M, int d, void* y, float* tsave);
+// dx = dres + backward(dy) ; dres may be null, may alias dx
+cudaError_t launch_rmsnorm_bwd(cudaStream_t st, int dt, const void* x, const float* tsave, const void* dy,
+                               const void* dres, int M, int d, void* dx);
+// RoPE (half split) + per-head RMSNorm of q and k.  qkv: [M, d + 2*dkv] raw projections.
+// qkn: [M, d + dkv] normalised roped q then k.  tq: [M, H + Hkv] saved (mean square + eps).
+cudaError_t launch_rope_qknorm_fwd(cudaStream_t st, int dt, const void* qkv, const uint16_t* cos_bf16,
+                                   const uint16_t* sin_bf16, int M, int T, int H, int Hkv, int hd, void* qkn,
+                                   float* tq);
+// dqkn: [M, d + dkv] gradient wrt qkn -> writes q and k parts of dqkv [M, d + 2*dkv]
+cudaError_t launch_rope_qknorm_bwd(cudaStream_t st, int dt, const void* qkv, const void* dqkn, const float* tq,
+                                   const uint16_t* cos_bf16, const uint16_t* sin_bf16, int M, int T, int H,
+                                   int Hkv, int hd, void* dqkv);
+
+// ---- attention (generic path) -------------------------------------------------------------------
+struct AttnArgs {
+  const void* qkn;      // [M, d + dkv]
+  const void* qkv;      // [M, d + 2 dkv]  (v part is read)
+  void* o;              // [M, d]
+  float* mrow;          // [B*H*T] row max of scaled masked scores
+  float* lrow;          // [B*H*T] row sum of exp
+  int B, T, H, Hkv, hd;
+  float scale;          // 1/sqrt(hd) rounded to the model dtype
+  // backward only
+  const void* dout;     // [M, d]
+  void* dqkn;           // [M, d + dkv]  (q part written; k part written by the finish pass)
+  void* dqkv;           // [M, d + 2 dkv] (v part written by the finish pass)
+  float* dkv_acc;       // [M, 2*dkv] f32 scratch: dk then dv, zeroed by the launcher
+};
+cudaError_t launch_attn_fwd_generic(cudaStream_t st, int dt, const AttnArgs& a);
+cudaError_t launch_attn_bwd_generic(cudaStream_t st, int dt, const AttnArgs& a);
+
+// ---- soft-capped cross entropy -------------------------------------------------------------------
+// logits [M,V] of model dtype are overwritten with d(loss)/d(logits).  rowloss[M]: per-row NLL (0 if
+// ignored).  count: number of targets != ignore (device scalar, written by launch_count_valid).
+cudaError_t launch_count_valid(cudaStream_t st, const long long* targets, int M, long long ignore, float* count);
+cudaError_t launch_softcap_ce(cudaStream_t st, int dt, void* logits, const long long* targets, int M, int V,
+                              float cap, long long ignore, const float* count, float* rowloss, int write_grad);
+cudaError_t launch_loss_finalize(cudaStream_t st, const float* rowloss, int M, const float* count, float* loss);
+
+// ---- optimiser -----------------------------------------------------------------------------------
+struct TensorSeg {          // one parameter tensor of a multi-tensor launch
+  const float* p; const float* g; const float* m; const float* v;
+  float* p_out; float* m_out; float* v_out;
+  void* shadow;             // model-dtype copy of p_out, may be null
+  long long n;
+  int first_chunk;          // index of this tensor's first chunk
+  int num_chunks;
+};
+struct AdamHyper {
+  float lr, beta1, beta2, eps, wd, max_norm;
+  float m_corr, v_corr;     // max(1 - beta^t, eps), computed on the host with powf
+};
+static const int ADAM_CHUNK = 8192;
+// segs: device array of `nseg` TensorSeg; chunk2seg: device array mapping chunk -> segment;
+// partial: device scratch of `nchunks` floats; normsq: device scratch of `nseg` floats.
+cudaError_t launch_adamw(cudaStream_t st, int shadow_dt, const TensorSeg* segs, int nseg, const int* chunk2seg,
+                         int nchunks, float* partial, float* normsq, AdamHyper h);
+cudaError_t launch_axpy_f32(cudaStream_t st, float* acc, const float* g, float alpha, size_t n);   // acc += alpha*g
+cudaError_t launch_scale_f32(cudaStream_t st, float* x, float alpha, size_t n);
+// x = clamp(finite(round_to_dt(x)))   (gradient edge guard, src/autodiff/engine.zig:622-682)
+cudaError_t launch_round_guard_f32(cudaStream_t st, int dt, float* x, size_t n, float clip);
+// nonfinite m/v detection per segment (src/nodes/workers/worker.zig:1346-1369): flags[seg] = 1 if corrupt
+cudaError_t launch_check_finite(cudaStream_t st, const float* x, size_t n, int* flag);
+
+// ---- DiLoCo outer step ---------------------------------------------------------------------------
+// delta = theta0 - theta (f32), truncated to bf16 precision if trunc != 0
+cudaError_t launch_delta(cudaStream_t st, const float* theta0, const float* theta, float* delta, size_t n, int trunc);
+// Shard update over [0,n): acc = sum_w deltas[w][i] (in order), /ncontrib, nonfinite -> 0,
+// vel = mu*vel + acc, master = master - lr*(acc + mu*vel), master truncated to bf16 if trunc.
+// Up to 8 delta pointers (peer or local memory).  outs: up to 8 destinations that receive the new master.
+struct OuterArgs {
+  const float* deltas[8]; int ncontrib;
+  float* vel; float* master;
+  float* outs[8]; int nouts;
+  long long n; float lr, mu; int trunc;
+};
+cudaError_t launch_nesterov_shard(cudaStream_t st, const OuterArgs& a);
+
+}  // namespace pcpb

@@ -1,0 +1,207 @@
+#include "model.h"
+
+#include <stdlib.h>
+#include <string.h>
+
+#include <map>
+
+namespace pcpb {
+
+namespace {
+
+struct ArgType {
+  std::vector<int64_t> shape;
+  std::string elem;
+};
+
+// "tensor<65x64xf32>" -> shape, elem
+bool parse_tensor_type(const std::string& s, ArgType* out) {
+  size_t a = s.find("tensor<");
+  if (a == std::string::npos) return false;
+  a += 7;
+  size_t b = s.find('>', a);
+  if (b == std::string::npos) return false;
+  std::string body = s.substr(a, b - a);
+  out->shape.clear();
+  size_t pos = 0;
+  while (true) {
+    size_t x = body.find('x', pos);
+    if (x == std::string::npos) break;
+    std::string tok = body.substr(pos, x - pos);
+    if (tok.empty() || tok.find_first_not_of("0123456789") != std::string::npos) break;
+    out->shape.push_back(strtoll(tok.c_str(), nullptr, 10));
+    pos = x + 1;
+  }
+  out->elem = body.substr(pos);
+  return !out->elem.empty();
+}
+
+std::string first_operand(const std::string& line) {
+  size_t eq = line.find('=');
+  if (eq == std::string::npos) return "";
+  size_t p = line.find('%', eq);
+  if (p == std::string::npos) return "";
+  size_t e = p + 1;
+  while (e < line.size() && (isalnum((unsigned char)line[e]) || line[e] == '_' || line[e] == '.')) ++e;
+  return line.substr(p, e - p);
+}
+
+std::string nth_operand(const std::string& line, int n) {
+  size_t eq = line.find('=');
+  size_t p = eq;
+  std::string r;
+  for (int i = 0; i <= n; ++i) {
+    p = line.find('%', p == std::string::npos ? 0 : p + 1);
+    if (p == std::string::npos) return "";
+    size_t e = p + 1;
+    while (e < line.size() && (isalnum((unsigned char)line[e]) || line[e] == '_' || line[e] == '.')) ++e;
+    r = line.substr(p, e - p);
+  }
+  return r;
+}
+
+}  // namespace
+
+std::string parse_artifact(const char* text, size_t n, ModelConfig* cfg) {
+  std::string src(text, n);
+  size_t fpos = src.find("@main(");
+  if (fpos == std::string::npos) return "no func.func @main in artefact";
+  size_t sig_end = src.find("->", fpos);
+  size_t line_end = src.find('\n', fpos);
+  if (sig_end == std::string::npos || line_end == std::string::npos || sig_end > line_end)
+    return "cannot parse the @main signature";
+  std::string sig = src.substr(fpos, sig_end - fpos);
+  std::vector<ArgType> args;
+  size_t p = 0;
+  while ((p = sig.find("tensor<", p)) != std::string::npos) {
+    ArgType t;
+    size_t e = sig.find('>', p);
+    if (!parse_tensor_type(sig.substr(p, e - p + 1), &t)) return "bad argument type in @main";
+    args.push_back(t);
+    p = e;
+  }
+  if (args.size() < 4) return "@main has too few arguments";
+  const size_t nP = args.size() - 2;
+  const ArgType& ids = args[nP];
+  if (ids.elem != "i64" || ids.shape.size() != 2 || args[nP + 1].elem != "i64" || args[nP + 1].shape != ids.shape)
+    return "the last two @main arguments must be i64 [B,T] token ids and targets";
+  if ((nP - 2) % 6 != 0 || nP < 8) return "not a nanochat-family graph (parameter count is not 2 + 6*layers)";
+  for (size_t i = 0; i < nP; ++i)
+    if (args[i].shape.size() != 2 || args[i].elem != args[0].elem)
+      return "not a nanochat-family graph (all parameters must be rank-2 of one dtype)";
+  ModelConfig c;
+  if (args[0].elem == "f32") c.dtype = 0;
+  else if (args[0].elem == "bf16") c.dtype = 3;
+  else return "unsupported model dtype " + args[0].elem;
+  c.B = ids.shape[0]; c.T = ids.shape[1];
+  c.V = args[0].shape[0]; c.d = args[0].shape[1];
+  c.L = (int64_t)(nP - 2) / 6;
+  if (args[nP - 1].shape[0] != c.V || args[nP - 1].shape[1] != c.d) return "lm_head shape does not match wte";
+  int64_t dkv = args[2].shape[0];
+  c.F = args[5].shape[0];
+  for (int64_t l = 0; l < c.L; ++l) {
+    const ArgType* a = &args[1 + 6 * l];
+    const bool ok = a[0].shape[0] == c.d && a[0].shape[1] == c.d && a[1].shape[0] == dkv && a[1].shape[1] == c.d &&
+                    a[2].shape[0] == dkv && a[2].shape[1] == c.d && a[3].shape[0] == c.d && a[3].shape[1] == c.d &&
+                    a[4].shape[0] == c.F && a[4].shape[1] == c.d && a[5].shape[0] == c.d && a[5].shape[1] == c.F;
+    if (!ok) return "layer parameter shapes do not follow q,k,v,proj,fc,proj";
+  }
+
+  // RoPE tables: the two dense_resource constants of type tensor<1xTx1x(hd/2)xbf16>
+  std::vector<std::string> keys;
+  {
+    size_t q = 0;
+    while ((q = src.find("dense_resource<", q)) != std::string::npos) {
+      size_t e = src.find('>', q);
+      std::string key = src.substr(q + 15, e - q - 15);
+      size_t le = src.find('\n', e);
+      ArgType t;
+      if (parse_tensor_type(src.substr(e, le - e), &t) && t.elem == "bf16" && t.shape.size() == 4 &&
+          t.shape[0] == 1 && t.shape[1] == c.T && t.shape[2] == 1) {
+        c.hd = 2 * t.shape[3];
+        keys.push_back(key);
+      }
+      q = e;
+    }
+  }
+  if (keys.size() < 2 || c.hd <= 0) return "RoPE table resources not found";
+  if (c.d % c.hd != 0 || dkv % c.hd != 0) return "head_dim does not divide the model width";
+  c.H = c.d / c.hd; c.Hkv = dkv / c.hd;
+  if (c.H % c.Hkv != 0) return "query heads are not a multiple of kv heads";
+  size_t rs = src.find("dialect_resources");
+  if (rs == std::string::npos) return "no dialect_resources section";
+  const size_t half = (size_t)c.hd / 2;
+  for (const std::string& key : keys) {
+    size_t k = src.find(key + ":", rs);
+    if (k == std::string::npos) return "resource blob missing: " + key;
+    size_t h = src.find("\"0x", k);
+    size_t he = src.find('"', h + 1);
+    if (h == std::string::npos || he == std::string::npos) return "bad resource blob";
+    const char* hex = src.c_str() + h + 3;
+    size_t nhex = he - (h + 3);
+    if (nhex < 8 + 4 * (size_t)c.T * half) return "resource blob too short";
+    std::vector<uint16_t> vals((size_t)c.T * half);
+    auto hv = [](char ch) -> int { return ch <= '9' ? ch - '0' : (ch | 32) - 'a' + 10; };
+    for (size_t i = 0; i < vals.size(); ++i) {
+      const char* q = hex + 8 + 4 * i;                    // skip the 4-byte alignment header
+      int lo = hv(q[0]) * 16 + hv(q[1]), hi = hv(q[2]) * 16 + hv(q[3]);
+      vals[i] = (uint16_t)(lo | (hi << 8));
+    }
+    // cos(0) = 1.0 (0x3F80), sin(0) = 0
+    if (vals[0] == 0x3F80) c.rope_cos.swap(vals); else c.rope_sin.swap(vals);
+  }
+  if (c.rope_cos.empty() || c.rope_sin.empty()) return "could not tell the cos table from the sin table";
+
+  // soft-cap: constant feeding the divide in front of stablehlo.tanh
+  {
+    std::map<std::string, std::string> defs;
+    size_t q = line_end + 1;
+    while (q < src.size()) {
+      size_t e = src.find('\n', q);
+      if (e == std::string::npos) e = src.size();
+      std::string line = src.substr(q, e - q);
+      size_t pc = line.find('%');
+      size_t eq = line.find(" = ");
+      if (pc != std::string::npos && eq != std::string::npos && pc < eq) defs[line.substr(pc, eq - pc)] = line;
+      if (line.find("return") != std::string::npos && line.find("stablehlo") == std::string::npos) break;
+      q = e + 1;
+    }
+    bool found = false;
+    for (auto& kv : defs) {
+      if (kv.second.find("stablehlo.tanh") == std::string::npos) continue;
+      std::string cur = first_operand(kv.second);          // the divide
+      auto it = defs.find(cur);
+      if (it == defs.end() || it->second.find("stablehlo.divide") == std::string::npos) continue;
+      cur = nth_operand(it->second, 1);                    // its denominator
+      for (int hop = 0; hop < 8 && !cur.empty(); ++hop) {
+        auto d2 = defs.find(cur);
+        if (d2 == defs.end()) break;
+        size_t dl = d2->second.find("dense<");
+        if (dl != std::string::npos) {
+          c.softcap = (float)strtod(d2->second.c_str() + dl + 6, nullptr);
+          found = true;
+          break;
+        }
+        cur = first_operand(d2->second);
+      }
+      if (found) break;
+    }
+    if (!found) return "soft-cap constant not found (expected tanh(z / cap) * cap before the loss)";
+  }
+  c.ignore_index = -1;
+
+  int64_t off = 0;
+  for (size_t i = 0; i < nP; ++i) {
+    TensorInfo t;
+    t.shape = args[i].shape;
+    t.numel = args[i].shape[0] * args[i].shape[1];
+    t.offset = off;
+    off += t.numel;
+    c.params.push_back(t);
+  }
+  c.total_params = off;
+  *cfg = c;
+  return "";
+}
+
+}  // namespace pcpb

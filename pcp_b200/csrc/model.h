@@ -1,0 +1,31 @@
+// Artefact recogniser: recovers the model configuration of a nanochat-family forward graph from its
+// StableHLO text (the @main signature, the RoPE table resources and the soft-cap constant).
+#pragma once
+#include <stdint.h>
+#include <string>
+#include <vector>
+
+namespace pcpb {
+
+struct TensorInfo {
+  std::vector<int64_t> shape;
+  int64_t numel = 0;
+  int64_t offset = 0;      // element offset in the flat parameter buffer (argument order)
+};
+
+struct ModelConfig {
+  int dtype = 0;           // DT_F32 | DT_BF16 (model dtype)
+  int64_t V = 0, d = 0, L = 0, H = 0, Hkv = 0, hd = 0, F = 0, B = 0, T = 0;
+  float softcap = 15.f;
+  long long ignore_index = -1;
+  std::vector<TensorInfo> params;      // wte, per layer q k v proj fc proj2, lm_head
+  int64_t total_params = 0;
+  std::vector<uint16_t> rope_cos, rope_sin;   // [T, hd/2] bf16 bit patterns
+  int64_t dkv() const { return Hkv * hd; }
+  int64_t M() const { return B * T; }
+};
+
+// Returns an empty string on success, else the reason the text was not recognised.
+std::string parse_artifact(const char* text, size_t n, ModelConfig* out);
+
+}  // namespace pcpb

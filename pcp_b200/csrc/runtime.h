@@ -1,0 +1,96 @@
+// Backend object behind the C ABI: buffers, artefact, workspace, training step, worker round, outer step.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <string>
+#include <vector>
+
+#include "kernels.h"
+#include "model.h"
+
+struct pcpb_backend;
+
+namespace pcpb {
+
+struct Block {                     // one device allocation, shared by the buffers that view it
+  void* ptr = nullptr;
+  size_t bytes = 0;
+  std::atomic<int> refs{1};
+  int device = 0;
+};
+
+struct LayerActs {                 // saved forward values of one transformer layer (model dtype unless noted)
+  void *h1, *qkv, *qkn, *o, *xmid, *h2, *u, *a;
+  float *t1, *t2, *tq, *mrow, *lrow;
+};
+
+struct Workspace {
+  bool ready = false;
+  std::vector<void*> allocs;       // everything cudaMalloc'ed for this artefact
+  // flat parameter-sized buffers (argument order)
+  float *theta = nullptr, *theta0 = nullptr, *mstate = nullptr, *vstate = nullptr, *grads = nullptr,
+        *gacc = nullptr, *delta = nullptr;
+  void* shadow = nullptr;          // model-dtype copy of theta (== theta for f32 models)
+  // activations
+  std::vector<void*> xs;           // L+1 residual streams [M,d]
+  std::vector<LayerActs> layers;
+  float *t0 = nullptr, *tf = nullptr, *rowloss = nullptr, *count = nullptr, *loss = nullptr;
+  void *hf = nullptr, *logits = nullptr;
+  // backward temporaries
+  void *dx = nullptr, *dh = nullptr, *du = nullptr, *dout = nullptr, *dqkn = nullptr, *dqkv = nullptr;
+  float* dkv_acc = nullptr;
+  // data
+  long long *ids = nullptr, *targets = nullptr;
+  uint16_t *d_cos = nullptr, *d_sin = nullptr;
+  // optimiser tables for the flat layout
+  TensorSeg* segs = nullptr; int* chunk2seg = nullptr; float* partial = nullptr; float* normsq = nullptr;
+  int nchunks = 0;
+  int* heal_flags = nullptr;
+  float* loss_record = nullptr;    // device, one per inner step of a round
+  int loss_capacity = 0;
+};
+
+}  // namespace pcpb
+
+struct pcpb_buffer {
+  pcpb_backend* owner;
+  pcpb::Block* block;
+  void* ptr;
+  size_t nbytes;
+  std::vector<int64_t> shape;
+  int dtype;
+  std::atomic<int> refs{1};
+};
+
+struct pcpb_backend {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  std::string err;
+  const void* art_ptr = nullptr;
+  size_t art_len = 0;
+  bool loaded = false;
+  pcpb::ModelConfig cfg;
+  pcpb::Workspace ws;
+  pcpb::AdamHyper adam;
+  long long launches = 0;
+  bool force_generic = false;
+  // worker round state
+  bool in_round = false;
+  int tau = 0, accumulation_steps = 1, param_dtype = 0, persist_adam = 0, tokens_on_device = 0;
+  float timestep = 1.f;
+  int steps_done = 0;
+  const uint16_t* tokens_src = nullptr;      // host or device pointer given by the caller
+  size_t n_tokens = 0, cursor = 0;
+  uint16_t* tokens_stage = nullptr;          // device staging for one step's window (host-token mode)
+  size_t stage_cap = 0;
+  bool have_master = false;                  // theta0 holds the master parameters of the next round
+  // outer step
+  int rank = 0, world = 1;
+  std::vector<float*> peer_delta, peer_theta0;
+  std::vector<void*> ipc_opened;
+  float *master_shard = nullptr, *velocity = nullptr;
+  long long shard_len = 0;
+  bool velocity_init = false;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+};

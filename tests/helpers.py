@@ -1,0 +1,51 @@
+"""Shared helpers of the test-suite: seeded inputs and the oracle-side replay."""
+import numpy as np
+import torch
+
+from oracle.loader import FifoU16, uniform_tokens, zipf_tokens
+from oracle.optim import AdamConf, NesterovConf
+from oracle.worker import TrainingModule, inner_loop, outer_step
+from pcp_b200.export import NanochatConfig, nanochat_forward_mlir
+
+SMALL_F32 = dict(vocab=65, d_model=64, n_layer=2, n_head=4, n_kv_head=4, seq_len=32, batch=8, dtype="f32")
+GQA_F32 = dict(vocab=97, d_model=64, n_layer=2, n_head=4, n_kv_head=2, seq_len=24, batch=3, dtype="f32")
+SMALL_BF16 = dict(vocab=65, d_model=64, n_layer=2, n_head=4, n_kv_head=4, seq_len=32, batch=8, dtype="bf16")
+HD128_BF16 = dict(vocab=512, d_model=256, n_layer=2, n_head=2, n_kv_head=2, seq_len=128, batch=2, dtype="bf16")
+HD128_F32 = dict(vocab=512, d_model=256, n_layer=1, n_head=2, n_kv_head=1, seq_len=64, batch=2, dtype="f32")
+
+
+def seeded_params(cfg: NanochatConfig, seed=0, std=0.02):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randn(s, generator=g) * std for s in cfg.param_shapes()]
+
+
+def flat(ts):
+    return np.concatenate([np.asarray(t, dtype=np.float32).reshape(-1) if not torch.is_tensor(t)
+                           else t.detach().to(torch.float32).reshape(-1).numpy() for t in ts])
+
+
+def split(flat_arr, cfg: NanochatConfig):
+    out, at = [], 0
+    for s in cfg.param_shapes():
+        n = s[0] * s[1]
+        out.append(flat_arr[at:at + n].reshape(s))
+        at += n
+    return out
+
+
+def rel_err(a, b):
+    a = np.asarray(a, np.float64); b = np.asarray(b, np.float64)
+    return float(np.abs(a - b).max() / (np.abs(b).max() + 1e-30))
+
+
+def tokens_for(cfg: NanochatConfig, steps, seed, zipf=False):
+    n = steps * (cfg.batch * cfg.seq_len + 1)
+    return zipf_tokens(n, cfg.vocab, 1.1, seed) if zipf else uniform_tokens(n, cfg.vocab, seed)
+
+
+def f32_to_bf16_trunc_bits(x):
+    return (np.ascontiguousarray(x, np.float32).view(np.uint32) >> 16).astype(np.uint16)
+
+
+def bf16_bits_to_f32(u):
+    return (np.ascontiguousarray(u, np.uint16).astype(np.uint32) << 16).view(np.float32)

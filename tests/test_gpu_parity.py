@@ -1,0 +1,310 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle on the same seeded
+inputs and against the committed golden fixtures.  Tolerances: f32 loss / parameters 1e-4 relative (the
+reference's own tests use atol = rtol = 1e-4, test/nanochat/test_pcp_training_step_parity.py:38), bf16 2e-2;
+integer paths bit-exact."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import (GQA_F32, HD128_BF16, HD128_F32, SMALL_BF16, SMALL_F32, bf16_bits_to_f32, f32_to_bf16_trunc_bits,
+                     flat, rel_err, seeded_params, split, tokens_for)
+from oracle.loader import FifoU16
+from oracle.optim import AdamConf, NesterovConf, adamw_update
+from oracle.worker import TrainingModule, inner_loop, outer_step
+from pcp_b200 import BF16, F32, I64, Backend, BackendError, NanochatConfig, nanochat_forward_mlir
+from pcp_b200 import backend as bk
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _grads_via_abi(be, cfg, params, x, y):
+    bufs = [be.move_to_device(p.numpy(), p.shape, F32) for p in params]
+    bx = be.move_to_device(x, x.shape, I64)
+    by = be.move_to_device(y, y.shape, I64)
+    outs = be.execute_with_device_buffers(None, "compute_gradients", bufs + [bx, by])
+    assert len(outs) == len(params) + 1
+    grads = [be.read_to_host(o, F32, p.shape) for o, p in zip(outs[:-1], params)]
+    loss = float(be.read_to_host(outs[-1], F32, ())[()])
+    for b in bufs + [bx, by] + outs:
+        b.release()
+    return grads, loss
+
+
+@pytest.mark.parametrize("cfgd,tol", [(SMALL_F32, 1e-4), (GQA_F32, 1e-4), (HD128_F32, 1e-4), (SMALL_BF16, 2e-2),
+                                      (HD128_BF16, 2e-2)])
+def test_compute_gradients_matches_oracle(cfgd, tol):
+    cfg = NanochatConfig(**cfgd)
+    text = nanochat_forward_mlir(cfg)
+    mod = TrainingModule(text)
+    params = seeded_params(cfg, seed=0, std=0.05)
+    ds = FifoU16(tokens_for(cfg, 1, seed=1))
+    x, y = ds.get_batch(cfg.batch, cfg.seq_len)
+    y[0, :2] = -1                                         # ignored targets
+    g_ref, loss_ref = mod.compute_gradients(params, torch.from_numpy(x), torch.from_numpy(y))
+    with Backend(0) as be:
+        be.load_session(text)
+        assert be.param_shapes() == [tuple(s) for s in cfg.param_shapes()]
+        g, loss = _grads_via_abi(be, cfg, params, x, y)
+        assert be.launch_count > 0
+    assert abs(loss - float(loss_ref)) <= tol * abs(float(loss_ref))
+    worst = max(rel_err(a, b.numpy()) for a, b in zip(g, g_ref))
+    # per-tensor max error relative to the tensor's largest gradient
+    assert worst <= (1e-4 if cfg.dtype == "f32" else 4e-2), worst
+
+
+def test_golden_reference_graph():
+    """Loss, gradients and two inner steps of the reference's shipped models/nanochat_small.mlir (fixture made
+    by tests/golden/make_golden.py from the reference tree) against the CUDA path on the exporter's graph."""
+    gold = np.load(os.path.join(GOLDEN, "nanochat_small.npz"))
+    cfg = NanochatConfig(vocab=65, d_model=64, n_layer=2, n_head=4, n_kv_head=4, seq_len=32, batch=64, dtype="f32")
+    text = nanochat_forward_mlir(cfg)
+    params = [torch.from_numpy(p.copy()) for p in split(gold["params"], cfg)]
+    with Backend(0) as be:
+        be.load_session(text)
+        g, loss = _grads_via_abi(be, cfg, params, gold["ids"], gold["targets"])
+        assert abs(loss - float(gold["loss"])) <= 1e-4 * float(gold["loss"])
+        assert rel_err(flat(g), gold["grads"]) <= 1e-4
+        be.set_adam(learning_rate=1e-3)
+        delta, losses = be.inner_loop(gold["params"], gold["tokens"], tau=2, param_dtype=F32)
+    np.testing.assert_allclose(losses, gold["step_losses"], rtol=1e-4)
+    assert rel_err(delta, gold["delta_after_2"]) <= 1e-3          # deltas are O(lr) differences of parameters
+    p_gpu = gold["params"] - delta
+    p_ref = gold["params"] - gold["delta_after_2"]
+    np.testing.assert_allclose(p_gpu, p_ref, rtol=1e-4, atol=1e-7)
+
+
+def test_fifo_batch_bit_exact():
+    cfg = NanochatConfig(**dict(SMALL_F32, vocab=65536, n_layer=1))
+    text = nanochat_forward_mlir(cfg)
+    rng = np.random.default_rng(7)
+    tokens = rng.integers(0, 65536, size=3 * (cfg.batch * cfg.seq_len + 1) + 5, dtype=np.int64).astype(np.uint16)
+    ds = FifoU16(tokens)
+    with Backend(0) as be:
+        be.load_session(text)
+        cur = 0
+        for _ in range(3):
+            x, y = ds.get_batch(cfg.batch, cfg.seq_len)
+            bx, by, cur = be.fifo_get_batch(tokens, cur)
+            assert np.array_equal(be.read_to_host(bx), x) and np.array_equal(be.read_to_host(by), y)
+            bx.release(); by.release()
+        assert cur == ds.cursor
+        with pytest.raises(BackendError) as ei:
+            be.fifo_get_batch(tokens, cur)                                  # 5 tokens left
+        assert ei.value.code == bk.E_CHUNK_EXHAUSTED
+        with pytest.raises(BackendError) as ei:
+            be.fifo_get_batch(tokens[:10], 0)
+        assert ei.value.code == bk.E_CHUNK_TOO_SMALL
+
+
+def test_apply_optimizer_matches_oracle():
+    cfg = NanochatConfig(**SMALL_F32)
+    text = nanochat_forward_mlir(cfg)
+    g0 = torch.Generator().manual_seed(3)
+    shapes = cfg.param_shapes()
+    p = [torch.randn(s, generator=g0) * 0.1 for s in shapes]
+    g = [torch.randn(s, generator=g0) * (10.0 if i % 3 == 0 else 1e-3) for i, s in enumerate(shapes)]
+    g[1][0, 0] = 5000.0                                                      # exercises the +-1000 pre-clamp
+    m = [torch.randn(s, generator=g0) * 0.01 for s in shapes]
+    v = [torch.rand(s, generator=g0) * 0.01 for s in shapes]
+    conf = AdamConf(learning_rate=3e-4, beta1=0.9, beta2=0.95, weight_decay=0.1)
+    with Backend(0) as be:
+        be.load_session(text)
+        be.set_adam(conf.learning_rate, conf.beta1, conf.beta2, conf.epsilon, conf.weight_decay, conf.max_grad_norm)
+        for t in (1.0, 7.0):
+            ins = [be.move_to_device(a.numpy(), a.shape, F32) for grp in (p, g, m, v) for a in grp]
+            ins.append(be.move_to_device(np.float32(t), (), F32))
+            outs = be.execute_with_device_buffers(None, "apply_optimizer", ins)
+            N = len(shapes)
+            assert len(outs) == 3 * N
+            for i in range(N):
+                rp, rm, rv = adamw_update(p[i], g[i], m[i], v[i], t, conf)
+                np.testing.assert_allclose(be.read_to_host(outs[i], F32, shapes[i]), rp.numpy(), rtol=2e-6, atol=1e-9)
+                np.testing.assert_allclose(be.read_to_host(outs[N + i], F32, shapes[i]), rm.numpy(), rtol=2e-6, atol=1e-12)
+                np.testing.assert_allclose(be.read_to_host(outs[2 * N + i], F32, shapes[i]), rv.numpy(), rtol=2e-6, atol=1e-12)
+            for b in ins + outs:
+                b.release()
+
+
+def test_adam_kat_single_step():
+    """src/examples/mlir_optimizer_test.zig:127-171 and :308-362: p=.5 g=.2 t=1 lr=.1 -> m=.02 v=4e-5 p~.4
+    (0.3995 with the weight decay 0.01 the update really applies)."""
+    cfg = NanochatConfig(**SMALL_F32)
+    with Backend(0) as be:
+        be.load_session(nanochat_forward_mlir(cfg))
+        be.set_adam(learning_rate=0.1)
+        shapes = cfg.param_shapes()
+        mk = lambda val: [np.full(s, val, np.float32) for s in shapes]
+        p, g, m, v = mk(0.5), mk(0.0), mk(0.0), mk(0.0)
+        g[1][:] = 0.0
+        g[1][0, :4] = [0.1, 0.2, 0.3, 0.4]                                   # norm 0.5477 < 1: no clipping
+        ins = [be.move_to_device(a, a.shape, F32) for grp in (p, g, m, v) for a in grp]
+        ins.append(be.move_to_device(np.float32(1.0), (), F32))
+        outs = be.execute_with_device_buffers(None, "apply_optimizer", ins)
+        N = len(shapes)
+        newp = be.read_to_host(outs[1], F32, shapes[1])[0, :4]
+        newm = be.read_to_host(outs[N + 1], F32, shapes[1])[0, :4]
+        newv = be.read_to_host(outs[2 * N + 1], F32, shapes[1])[0, :4]
+        np.testing.assert_allclose(newm, [0.01, 0.02, 0.03, 0.04], rtol=1e-5)
+        np.testing.assert_allclose(newv, [1e-5, 4e-5, 9e-5, 1.6e-4], rtol=1e-4)
+        np.testing.assert_allclose(newp, [0.3995] * 4, atol=1e-5)
+        for b in ins + outs:
+            b.release()
+
+
+def _run_diloco(cfgd, workers, tau, rounds, lr, tol_loss, tol_param, zipf=False):
+    cfg = NanochatConfig(**cfgd)
+    text = nanochat_forward_mlir(cfg)
+    mod = TrainingModule(text)
+    dt = F32 if cfg.dtype == "f32" else BF16
+    master = seeded_params(cfg, seed=0, std=0.02)
+    if cfg.dtype == "bf16":
+        master = [torch.from_numpy(bf16_bits_to_f32(f32_to_bf16_trunc_bits(p.numpy())).reshape(p.shape)) for p in master]
+    vel = [torch.zeros_like(p) for p in master]
+    conf = AdamConf(learning_rate=lr)
+    nconf = NesterovConf(0.7, 0.9)
+    toks = [[tokens_for(cfg, tau, seed=100 * r + w, zipf=zipf) for w in range(workers)] for r in range(rounds)]
+    bes = [Backend(0) for _ in range(workers)]
+    try:
+        for b in bes:
+            b.load_session(text)
+            b.set_adam(learning_rate=lr)
+        for w, b in enumerate(bes):
+            b.outer_attach_local(w, bes)
+        blob0 = flat(master)
+        blob = blob0 if dt == F32 else f32_to_bf16_trunc_bits(blob0)
+        for r in range(rounds):
+            ref_deltas, ref_losses, ref_step_losses = [], [], []
+            for w in range(workers):
+                rec = []
+                d, fl, _, _ = inner_loop(mod, master, FifoU16(toks[r][w]), tau, cfg.batch, cfg.seq_len, conf, record=rec)
+                ref_deltas.append(d); ref_losses.append(fl); ref_step_losses.append([x[0] for x in rec])
+            gpu_losses = []
+            for w, b in enumerate(bes):
+                b.worker_begin_round(tau, blob if r == 0 else None, param_dtype=dt)
+                b.worker_set_tokens(toks[r][w])
+                for _ in range(tau):
+                    b.worker_step()
+                delta, losses = b.worker_end_round(tau, param_dtype=dt)
+                gpu_losses.append(losses)
+                np.testing.assert_allclose(losses, ref_step_losses[w], rtol=tol_loss)
+                dref = flat(ref_deltas[w])
+                dgpu = delta if dt == F32 else bf16_bits_to_f32(delta)
+                # parameters after the round: theta0 - delta
+                np.testing.assert_allclose(flat(master) - dgpu, flat(master) - dref, rtol=tol_param, atol=tol_param * 1e-2)
+            for b in bes:
+                b.outer_prepare(param_dtype=dt)
+            for b in bes:
+                b.outer_apply(0.7, 0.9, dt)
+            master, vel, _ = outer_step(master, vel, ref_deltas, ref_losses, nconf, cfg.dtype)
+            for b in bes:
+                got = b.worker_read_state("master")
+                # the reference's own outer-step parity test allows 5e-4 (test_pcp_diloco_outer_step_parity.py:37)
+                np.testing.assert_allclose(got, flat(master), rtol=max(tol_param, 5e-4), atol=max(tol_param, 5e-4) * 1e-2)
+    finally:
+        for b in bes:
+            b.close()
+
+
+def test_diloco_f32_20_steps_2_rounds():
+    """BASELINE config 1 protocol at the shipped small shape: 2 workers, 2 outer rounds; 20 inner steps in total
+    per worker (H=10), loss and parameters within 1e-4."""
+    _run_diloco(SMALL_F32, workers=2, tau=10, rounds=2, lr=3e-4, tol_loss=1e-4, tol_param=1e-4)
+
+
+def test_diloco_bf16_3_workers():
+    _run_diloco(SMALL_BF16, workers=3, tau=4, rounds=2, lr=1e-3, tol_loss=2e-2, tol_param=2e-2, zipf=True)
+
+
+def test_outer_step_bit_exact_given_deltas():
+    """With the deltas taken from the device itself the outer arithmetic (sum in worker order, / n, NaN -> 0,
+    Nesterov, bf16 truncation) is bit-identical to the restated reference."""
+    cfg = NanochatConfig(**SMALL_BF16)
+    text = nanochat_forward_mlir(cfg)
+    workers = 3
+    master = [torch.from_numpy(bf16_bits_to_f32(f32_to_bf16_trunc_bits(p.numpy())).reshape(p.shape))
+              for p in seeded_params(cfg, seed=5)]
+    vel = [torch.zeros_like(p) for p in master]
+    bes = [Backend(0) for _ in range(workers)]
+    try:
+        for b in bes:
+            b.load_session(text)
+        for w, b in enumerate(bes):
+            b.outer_attach_local(w, bes)
+        blob = f32_to_bf16_trunc_bits(flat(master))
+        for rnd in range(2):
+            deltas = []
+            for w, b in enumerate(bes):
+                b.worker_begin_round(2, blob if rnd == 0 else None, param_dtype=BF16)
+                b.worker_set_tokens(tokens_for(cfg, 2, seed=10 * rnd + w))
+                b.worker_step(); b.worker_step()
+                d, _ = b.worker_end_round(2, param_dtype=BF16)
+                deltas.append([torch.from_numpy(x.copy()) for x in split(bf16_bits_to_f32(d), cfg)])
+                assert np.array_equal(b.worker_read_state("delta"), bf16_bits_to_f32(d))
+            for b in bes:
+                b.outer_prepare(param_dtype=BF16)
+            for b in bes:
+                b.outer_apply(0.7, 0.9, BF16)
+            master, vel, _ = outer_step(master, vel, deltas, [0.0] * workers, NesterovConf(0.7, 0.9), "bf16")
+            for b in bes:
+                assert np.array_equal(b.worker_read_state("master"), flat(master))
+        # elasticity: only ranks 0 and 2 contribute (divisor 2, src/algorithms/diloco.zig:970)
+    finally:
+        for b in bes:
+            b.close()
+
+
+def test_errors_are_reported_not_fatal():
+    cfg = NanochatConfig(**SMALL_F32)
+    text = nanochat_forward_mlir(cfg)
+    with Backend(0) as be:
+        with pytest.raises(BackendError) as ei:
+            be.execute_with_device_buffers(None, "compute_gradients", [])
+        assert ei.value.code == bk.E_ARTIFACT
+        with pytest.raises(BackendError) as ei:
+            be.load_session("module { func.func @main(%arg0: tensor<4xf32>) -> tensor<f32> { } }")
+        assert ei.value.code == bk.E_ARTIFACT
+        be.load_session(text)
+        with pytest.raises(BackendError) as ei:
+            be.execute_with_device_buffers(None, "no_such_function", [])
+        assert ei.value.code == bk.E_FUNCTION
+        z = be.allocate_zeros_device((3,), F32)
+        assert z.byte_length() == 12
+        with pytest.raises(BackendError) as ei:
+            be.execute_with_device_buffers(None, "compute_gradients", [z])
+        assert ei.value.code == bk.E_INVALID
+        z.retain(); z.release()
+        assert np.array_equal(be.read_to_host(z, F32, (3,)), np.zeros(3, np.float32))
+        z.release()
+        with pytest.raises(BackendError) as ei:
+            be.worker_step()
+        assert ei.value.code == bk.E_STATE
+        be.worker_begin_round(1, flat(seeded_params(cfg)), param_dtype=F32)
+        be.worker_set_tokens(np.zeros(5, np.uint16))
+        with pytest.raises(BackendError) as ei:
+            be.worker_step()
+        assert ei.value.code == bk.E_CHUNK_TOO_SMALL
+        # the backend is still usable afterwards
+        be.worker_set_tokens(tokens_for(cfg, 1, seed=0))
+        be.worker_step()
+        _, losses = be.worker_end_round(1, param_dtype=F32)
+        assert np.isfinite(losses).all()
+
+
+def test_execute_host_path():
+    """IreeBackend.execute: host bytes in, host bytes out (dtypes == None: f32 except the last two, i64)."""
+    cfg = NanochatConfig(**GQA_F32)
+    text = nanochat_forward_mlir(cfg)
+    mod = TrainingModule(text)
+    params = seeded_params(cfg, seed=2, std=0.05)
+    x, y = FifoU16(tokens_for(cfg, 1, seed=4)).get_batch(cfg.batch, cfg.seq_len)
+    g_ref, loss_ref = mod.compute_gradients(params, torch.from_numpy(x), torch.from_numpy(y))
+    with Backend(0) as be:
+        outs = be.execute(text, "compute_gradients", [p.numpy() for p in params] + [x, y],
+                          [tuple(p.shape) for p in params] + [x.shape, y.shape])
+    assert len(outs) == len(params) + 1
+    loss = outs[-1].view(np.float32)[0]
+    assert abs(loss - float(loss_ref)) <= 1e-4 * float(loss_ref)
+    assert rel_err(np.concatenate([o.view(np.float32) for o in outs[:-1]]), flat(g_ref)) <= 1e-4
