@@ -55,6 +55,11 @@ void pcpb_free(void* p);
  * artefact; the bytes are borrowed only for the duration of the call (they are parsed, not retained). */
 int pcpb_load_artifact(pcpb_backend* b, const void* bytes, size_t n);
 
+/* ModelInspector.inspect without a device (src/mlir/model_introspection.zig:251-312): parses the artefact and
+ * writes vocab, d_model, layers, heads, kv_heads, head_dim, mlp width, batch, block, model dtype, number of
+ * parameter tensors, total parameter count into facts[12].  err (may be NULL) receives the reason on failure. */
+int pcpb_inspect_artifact(const void* bytes, size_t n, int64_t* facts, char* err, size_t err_cap);
+
 /* Model facts recovered from the artefact (src/mlir/model_introspection.zig:251-312: parameters are all
  * @main arguments except the last two).  shape_out receives up to 8 dims. */
 int pcpb_num_params(const pcpb_backend* b);
@@ -85,6 +90,15 @@ int pcpb_read_to_host(pcpb_backend* b, const pcpb_buffer* buf, void* dst, size_t
 int pcpb_execute_host(pcpb_backend* b, const char* fn, const void* const* in, const size_t* in_nbytes,
                       const int64_t* const* shapes, const int* ranks, const int* dtypes, size_t n_in, void*** out,
                       size_t** out_nbytes, size_t* n_out);
+
+/* One contraction of the op surface (stablehlo.dot_general as the reference's graphs use it, src/core/ops.zig and
+ * matmulVJP src/autodiff/vjp_rules.zig:426-496), on device buffers of the loaded model's dtype:
+ *   C[M,N] = epilogue(sum_k A(m,k) B(k,n)),  A(m,k) = A[m*sam + k*sak],  B(k,n) = B[k*sbk + n*sbn]
+ * epilogue: 0 store, 1 residual add (R), 2 store + relu^2 into C2, 3 relu^2 backward at R, 4 weight gradient (f32 C).
+ * path: 0 = pick (tensor cores when the shape allows), 1 = generic kernel, 2 = tensor-core kernel or error. */
+int pcpb_op_gemm(pcpb_backend* b, int path, const pcpb_buffer* A, long long sam, long long sak, const pcpb_buffer* B,
+                 long long sbk, long long sbn, pcpb_buffer* C, long long ldc, const pcpb_buffer* R, pcpb_buffer* C2,
+                 int M, int N, int K, int epilogue);
 
 /* Dataset.getBatch of the FIFO u16 dataset (U16TokenDatasetFifo.getBatchImpl, src/data/loader.zig:555-589),
  * with the widening to i64 done on the device: consumes B*T+1 tokens of the host chunk at *cursor, returns the
@@ -156,6 +170,21 @@ int pcpb_outer_prepare(pcpb_backend* b, const pcpb_outer_cfg* cfg);
  * (src/algorithms/diloco.zig:970). */
 int pcpb_outer_apply(pcpb_backend* b, const pcpb_outer_cfg* cfg, const int* contributors, int n_contributors,
                      double* device_ms);
+
+/* Loss of the most recent pcpb_worker_step, read back to the host (blocks until that step has run): the
+ * per-step loss read of the reference's inner loop (src/nodes/workers/worker.zig:1246). */
+int pcpb_worker_last_loss(pcpb_backend* b, float* loss);
+
+/* Device-side timing on the backend's own stream (CUDA events): start / stop bracket whatever the backend
+ * enqueues in between; stop blocks until the work has run and returns the elapsed milliseconds. */
+int pcpb_timer_start(pcpb_backend* b);
+int pcpb_timer_stop(pcpb_backend* b, double* ms);
+
+/* Per-kernel accounting of the tensor-core GEMM: while enabled every launch is bracketed by CUDA events.
+ * pcpb_profile_read blocks, then returns the number of launches, their summed duration and their summed
+ * algorithmic FLOPs (2*M*N*K each) since the last enable, and keeps profiling on. */
+int pcpb_profile_enable(pcpb_backend* b, int on);
+int pcpb_profile_read(pcpb_backend* b, long long* launches, double* total_ms, double* total_flops);
 
 /* Kernel counters of this backend: launches enqueued since creation, by the library's own kernels. */
 long long pcpb_launch_count(const pcpb_backend* b);

@@ -35,12 +35,13 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libpcp_b200
 
 EXPORTS = [
     "pcpb_create", "pcpb_destroy", "pcpb_backend_type", "pcpb_last_error", "pcpb_free", "pcpb_load_artifact",
-    "pcpb_num_params", "pcpb_param_shape", "pcpb_model_info", "pcpb_buffer_from_host", "pcpb_buffer_zeros",
+    "pcpb_inspect_artifact", "pcpb_num_params", "pcpb_param_shape", "pcpb_model_info", "pcpb_buffer_from_host", "pcpb_buffer_zeros",
     "pcpb_buffer_retain", "pcpb_buffer_release", "pcpb_buffer_nbytes", "pcpb_execute", "pcpb_read_to_host",
-    "pcpb_execute_host", "pcpb_fifo_get_batch", "pcpb_set_adam", "pcpb_worker_begin_round", "pcpb_worker_set_tokens", "pcpb_worker_step",
+    "pcpb_execute_host", "pcpb_op_gemm", "pcpb_fifo_get_batch", "pcpb_set_adam", "pcpb_worker_begin_round", "pcpb_worker_set_tokens", "pcpb_worker_step",
     "pcpb_worker_end_round", "pcpb_inner_loop", "pcpb_worker_read_state", "pcpb_synchronize", "pcpb_outer_export",
     "pcpb_outer_attach_ipc", "pcpb_outer_attach_local", "pcpb_outer_prepare", "pcpb_outer_apply",
-    "pcpb_launch_count",
+    "pcpb_launch_count", "pcpb_worker_last_loss", "pcpb_timer_start", "pcpb_timer_stop", "pcpb_profile_enable",
+    "pcpb_profile_read",
 ]
 
 
@@ -84,6 +85,7 @@ def load_library(path: str | None = None):
     lib.pcpb_last_error.argtypes = [vp]; lib.pcpb_last_error.restype = C.c_char_p
     lib.pcpb_free.argtypes = [vp]; lib.pcpb_free.restype = None
     lib.pcpb_load_artifact.argtypes = [vp, vp, sz]
+    lib.pcpb_inspect_artifact.argtypes = [vp, sz, C.POINTER(C.c_int64), C.c_char_p, sz]
     lib.pcpb_num_params.argtypes = [vp]
     lib.pcpb_param_shape.argtypes = [vp, i, C.POINTER(C.c_int64), C.POINTER(i)]
     lib.pcpb_model_info.argtypes = [vp, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64),
@@ -98,6 +100,8 @@ def load_library(path: str | None = None):
     lib.pcpb_execute_host.argtypes = [vp, C.c_char_p, C.POINTER(vp), C.POINTER(sz), C.POINTER(C.POINTER(C.c_int64)),
                                       C.POINTER(i), C.POINTER(i), sz, C.POINTER(C.POINTER(vp)),
                                       C.POINTER(C.POINTER(sz)), C.POINTER(sz)]
+    ll = C.c_longlong
+    lib.pcpb_op_gemm.argtypes = [vp, i, vp, ll, ll, vp, ll, ll, vp, ll, vp, vp, i, i, i, i]
     lib.pcpb_fifo_get_batch.argtypes = [vp, vp, sz, C.POINTER(sz), C.POINTER(vp), C.POINTER(vp)]
     lib.pcpb_set_adam.argtypes = [vp, C.POINTER(AdamConf)]
     lib.pcpb_worker_begin_round.argtypes = [vp, C.POINTER(InnerCfg), vp, sz]
@@ -113,9 +117,28 @@ def load_library(path: str | None = None):
     lib.pcpb_outer_prepare.argtypes = [vp, C.POINTER(OuterCfg)]
     lib.pcpb_outer_apply.argtypes = [vp, C.POINTER(OuterCfg), C.POINTER(i), i, C.POINTER(C.c_double)]
     lib.pcpb_launch_count.argtypes = [vp]; lib.pcpb_launch_count.restype = C.c_longlong
+    lib.pcpb_worker_last_loss.argtypes = [vp, C.POINTER(C.c_float)]
+    lib.pcpb_timer_start.argtypes = [vp]
+    lib.pcpb_timer_stop.argtypes = [vp, C.POINTER(C.c_double)]
+    lib.pcpb_profile_enable.argtypes = [vp, i]
+    lib.pcpb_profile_read.argtypes = [vp, C.POINTER(C.c_longlong), C.POINTER(C.c_double), C.POINTER(C.c_double)]
     if path is None:
         _lib = lib
     return lib
+
+
+def inspect_artifact(artifact) -> dict:
+    """Model facts of a forward graph, parsed on the host (no GPU needed)."""
+    lib = load_library()
+    raw = artifact.encode() if isinstance(artifact, str) else artifact
+    facts = (C.c_int64 * 12)()
+    err = C.create_string_buffer(512)
+    rc = lib.pcpb_inspect_artifact(raw, len(raw), facts, err, 512)
+    if rc:
+        raise BackendError(rc, err.value.decode())
+    keys = ["vocab", "d_model", "n_layer", "n_head", "n_kv_head", "head_dim", "d_ff", "batch", "block", "dtype",
+            "num_tensors", "total_params"]
+    return dict(zip(keys, [int(x) for x in facts]))
 
 
 class DeviceBuffer:
@@ -285,6 +308,10 @@ class Backend:
     def execute_training_step(self, artifact, inputs, shapes, dtypes=None):
         return self.execute(artifact, "main", inputs, shapes, dtypes)
 
+    def op_gemm(self, A, sam, sak, B, sbk, sbn, Cbuf, ldc, M, N, K, epilogue=0, R=None, C2=None, path=0):
+        self._check(self._lib.pcpb_op_gemm(self._h, path, A.handle, sam, sak, B.handle, sbk, sbn, Cbuf.handle, ldc,
+                                           R.handle if R else None, C2.handle if C2 else None, M, N, K, epilogue))
+
     def fifo_get_batch(self, tokens: np.ndarray, cursor: int):
         """-> (inputs DeviceBuffer, targets DeviceBuffer, new cursor); tokens: host uint16 array."""
         tok = np.ascontiguousarray(tokens, dtype=np.uint16)
@@ -322,6 +349,27 @@ class Backend:
 
     def worker_step(self):
         self._check(self._lib.pcpb_worker_step(self._h))
+
+    def worker_last_loss(self) -> float:
+        v = C.c_float()
+        self._check(self._lib.pcpb_worker_last_loss(self._h, C.byref(v)))
+        return v.value
+
+    def timer_start(self):
+        self._check(self._lib.pcpb_timer_start(self._h))
+
+    def timer_stop(self) -> float:
+        ms = C.c_double()
+        self._check(self._lib.pcpb_timer_stop(self._h, C.byref(ms)))
+        return ms.value
+
+    def profile_enable(self, on=True):
+        self._check(self._lib.pcpb_profile_enable(self._h, int(on)))
+
+    def profile_read(self):
+        n, ms, fl = C.c_longlong(), C.c_double(), C.c_double()
+        self._check(self._lib.pcpb_profile_read(self._h, C.byref(n), C.byref(ms), C.byref(fl)))
+        return {"launches": n.value, "ms": ms.value, "flops": fl.value}
 
     def worker_end_round(self, steps, param_dtype=F32, want_delta=True):
         P = self.model_info()["total_params"]

@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libpcp_b200.so")
-SOURCES = ["kernels.cu", "gemm_tc.cu", "runtime.cu", "model.cpp"]
+SOURCES = ["kernels.cu", "gemm_tc.cu", "attn_flash.cu", "runtime.cu", "model.cpp"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 
@@ -35,7 +35,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
                 print(" ".join(cmd), flush=True)
             subprocess.run(cmd, check=True)
     if force or _stale(OUT, objs):
-        cmd = [nvcc, "-shared", "-o", OUT] + objs + ["-lcuda"]
+        cmd = [nvcc, "-shared", "-o", OUT] + objs
         subprocess.run(cmd, check=True)
     return OUT
 

@@ -1,0 +1,525 @@
+// Causal attention for bf16 models with head_dim 128, tiled so that the [T,T] score matrix never leaves
+// the SM (forward) and is recomputed per tile (backward).  Tensor-core path: mma.sync m16n8k16 bf16 with
+// ldmatrix-fed fragments; shared-memory tiles are filled with cp.async and XOR-swizzled per 16-byte chunk.
+//
+// Numerics (models/nanochat_d8_b8_t2048_bf16.mlir %106-%151 and the VJP rules they go through):
+//   s = bf16(bf16(q.k) * scale_bf16); causal mask; softmax statistics in f32; l = sum exp(s - max)
+//   o = bf16( sum_j bf16(exp(s_j - max)) v_j / (l + 1e-4) )
+// One deliberate difference from the exported graph: the probability is rounded to bf16 before the division by
+// (l + 1e-4) instead of after it (a single pass cannot know l earlier); the two differ by at most one bf16
+// rounding of P.
+// Backward: Pt = e/(l + 2e-4), dp = bf16(do.v), D = rowsum(do*o) (l+1e-4)/(l+2e-4),
+//   dsf = Pt (dp - D) - [s == max] D 2e-4/(l+2e-4),  ds = bf16(bf16(dsf) * scale_bf16)
+//   dv_j = sum_i bf16(P_ij) do_i,  dk_j = sum_i ds_ij q_i,  dq_i = sum_j ds_ij k_j
+// dK/dV and dQ are produced by two kernels (one owns key blocks, one owns query blocks): no atomics, results
+// are deterministic.
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "attn_flash.h"
+#include "common.cuh"
+
+namespace pcpb {
+
+namespace {
+
+constexpr int HD = 128;                 // head dim
+constexpr int ROWB = HD * 2;            // bytes per tile row (256)
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// address of 16-byte chunk `chunk` (0..15) of row `row` in a [rows][128] bf16 tile
+__device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk) {
+  return base + (uint32_t)row * ROWB + (uint32_t)((chunk ^ (row & 7)) << 4);
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// Copy a [ROWS][128] bf16 tile from global (row pitch `pitch` elements) into a swizzled smem tile.
+template <int ROWS, int THREADS>
+__device__ __forceinline__ void load_tile(uint32_t sbase, const bf16* __restrict__ g, long long pitch) {
+#pragma unroll
+  for (int i = 0; i < ROWS * 16 / THREADS; ++i) {
+    const int idx = threadIdx.x + i * THREADS;
+    const int row = idx >> 4, chunk = idx & 15;
+    cp_async16(tile_addr(sbase, row, chunk), g + (long long)row * pitch + chunk * 8);
+  }
+}
+
+// A fragment (16 rows x 16 k) of a row-major tile: rows row0.., k chunk pair (2*ks, 2*ks+1)
+__device__ __forceinline__ void load_a(uint32_t sbase, int row0, int ks, uint32_t (&a)[4]) {
+  const int lane = threadIdx.x & 31, id = lane >> 3, r = lane & 7;
+  ldsm_x4(tile_addr(sbase, row0 + r + (id & 1) * 8, 2 * ks + (id >> 1)), a[0], a[1], a[2], a[3]);
+}
+// B fragments of two adjacent n-tiles (n0..n0+15) for k chunk pair ks, from a tile stored [n][k] (k contiguous)
+__device__ __forceinline__ void load_b_nk(uint32_t sbase, int n0, int ks, uint32_t (&b)[4]) {
+  const int lane = threadIdx.x & 31, id = lane >> 3, r = lane & 7;
+  ldsm_x4(tile_addr(sbase, n0 + r + (id >> 1) * 8, 2 * ks + (id & 1)), b[0], b[1], b[2], b[3]);
+}
+// B fragments of two adjacent n-tiles (n chunk nc, nc+1) for k rows k0..k0+15, from a tile stored [k][n] (n contiguous)
+__device__ __forceinline__ void load_b_kn(uint32_t sbase, int k0, int nc, uint32_t (&b)[4]) {
+  const int lane = threadIdx.x & 31, id = lane >> 3, r = lane & 7;
+  ldsm_x4_t(tile_addr(sbase, k0 + r + (id & 1) * 8, nc + (id >> 1)), b[0], b[1], b[2], b[3]);
+}
+
+__device__ __forceinline__ float quad_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
+// ------------------------------------------------------------------------------------------------
+// forward: CTA = 64 query rows of one (batch, head); 4 warps x 16 rows; key blocks of 64
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) k_flash_fwd(FlashArgs a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const uint32_t sQ = smem_u32(smem), sK = sQ + 64 * ROWB, sV = sK + 2 * 64 * ROWB;
+  const int qb = gridDim.x - 1 - blockIdx.x;                 // long rows first
+  const int bh = blockIdx.y, b = bh / a.H, h = bh % a.H, hk = h / (a.H / a.Hkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int d = a.H * HD, dkv = a.Hkv * HD;
+  const long long wqkn = d + dkv, wqkv = d + 2 * dkv;
+  const int q0 = qb * 64;
+  const bf16* Qg = (const bf16*)a.qkn + ((long long)b * a.T + q0) * wqkn + h * HD;
+  const bf16* Kg = (const bf16*)a.qkn + (long long)b * a.T * wqkn + d + hk * HD;
+  const bf16* Vg = (const bf16*)a.qkv + (long long)b * a.T * wqkv + d + dkv + hk * HD;
+
+  load_tile<64, 128>(sQ, Qg, wqkn);
+  load_tile<64, 128>(sK, Kg, wqkn);
+  load_tile<64, 128>(sV, Vg, wqkv);
+  cp_async_commit();
+
+  float o[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const int nkb = qb + 1;
+  const int row_lo = q0 + warp * 16 + g;                     // this thread's rows: row_lo and row_lo + 8
+
+  for (int kb = 0; kb < nkb; ++kb) {
+    const int buf = kb & 1;
+    if (kb + 1 < nkb) {
+      load_tile<64, 128>(sK + (buf ^ 1) * 64 * ROWB, Kg + (long long)(kb + 1) * 64 * wqkn, wqkn);
+      load_tile<64, 128>(sV + (buf ^ 1) * 64 * ROWB, Vg + (long long)(kb + 1) * 64 * wqkv, wqkv);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t cK = sK + buf * 64 * ROWB, cV = sV + buf * 64 * ROWB;
+
+    float s[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      uint32_t af[4];
+      load_a(sQ, warp * 16, ks, af);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t bfr[4];
+        load_b_nk(cK, np * 16, ks, bfr);
+        mma16816(s[2 * np], af[0], af[1], af[2], af[3], bfr[0], bfr[1]);
+        mma16816(s[2 * np + 1], af[0], af[1], af[2], af[3], bfr[2], bfr[3]);
+      }
+    }
+    // scale (both roundings of the exported graph), causal mask on the diagonal block
+    const bool diag = (kb == nkb - 1);
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v = bf16r(bf16r(s[nt][e]) * a.scale);
+        if (diag) {
+          const int col = kb * 64 + nt * 8 + 2 * t + (e & 1);
+          const int row = row_lo + (e >> 1) * 8;
+          if (col > row) v = -INFINITY;
+        }
+        s[nt][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    }
+    float alpha[2], mnew[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = quad_max(mx[r]);
+      mnew[r] = fmaxf(m_run[r], mx[r]);
+      alpha[r] = exp2f((m_run[r] - mnew[r]) * LOG2E);
+      m_run[r] = mnew[r];
+    }
+    float rs[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float p = exp2f((s[nt][e] - mnew[e >> 1]) * LOG2E);
+        s[nt][e] = p;
+        rs[e >> 1] += p;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * alpha[r] + quad_sum(rs[r]);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { o[i][0] *= alpha[0]; o[i][1] *= alpha[0]; o[i][2] *= alpha[1]; o[i][3] *= alpha[1]; }
+    // O += P V
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      const uint32_t a0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]), a1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      const uint32_t a2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), a3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int np = 0; np < 8; ++np) {
+        uint32_t bfr[4];
+        load_b_kn(cV, kk * 16, 2 * np, bfr);
+        mma16816(o[2 * np], a0, a1, a2, a3, bfr[0], bfr[1]);
+        mma16816(o[2 * np + 1], a0, a1, a2, a3, bfr[2], bfr[3]);
+      }
+    }
+    __syncthreads();
+  }
+  // finish: o / (l + 1e-4)
+  bf16* Og = (bf16*)a.o + ((long long)b * a.T) * d + h * HD;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = row_lo + r * 8;
+    const float inv = 1.f / (l_run[r] + PCPB_GUARD);
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      const uint32_t v = pack_bf16(o[nt][2 * r] * inv, o[nt][2 * r + 1] * inv);
+      *reinterpret_cast<uint32_t*>(Og + (long long)row * d + nt * 8 + 2 * t) = v;
+    }
+    if (t == 0) {
+      a.mrow[(long long)bh * a.T + row] = m_run[r];
+      a.lrow[(long long)bh * a.T + row] = l_run[r];
+    }
+  }
+}
+
+// D[b,h,i] = rowsum(do * o) * (l + 1e-4) / (l + 2e-4).  One warp per row.
+__global__ void k_flash_prep(FlashArgs a) {
+  const long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long rows = (long long)a.B * a.H * a.T;
+  if (gw >= rows) return;
+  const int i = (int)(gw % a.T), bh = (int)(gw / a.T), b = bh / a.H, h = bh % a.H;
+  const int d = a.H * HD;
+  const bf16* op = (const bf16*)a.o + ((long long)b * a.T + i) * d + h * HD;
+  const bf16* dp = (const bf16*)a.dout + ((long long)b * a.T + i) * d + h * HD;
+  float acc = 0.f;
+  for (int e = lane; e < HD; e += 32) acc += __bfloat162float(op[e]) * __bfloat162float(dp[e]);
+  acc = warp_sum(acc);
+  if (lane == 0) {
+    const float l = a.lrow[gw];
+    a.drow[gw] = acc * (l + PCPB_GUARD) / (l + 2.f * PCPB_GUARD);
+  }
+}
+
+// Shared by both backward kernels: turn raw scores / raw dp of one fragment element into (P_bf16, ds_bf16).
+__device__ __forceinline__ void bwd_elem(float sraw, float dpraw, float scale, float m, float l, float D, bool masked,
+                                         float& p_out, float& ds_out) {
+  const float s = bf16r(bf16r(sraw) * scale);
+  const float e = masked ? 0.f : exp2f((s - m) * LOG2E);
+  const float den2 = l + 2.f * PCPB_GUARD;
+  const float pt = e / den2;
+  const float dp = bf16r(dpraw);
+  float dsf = pt * (dp - D);
+  if (!masked && s == m) dsf -= D * (2.f * PCPB_GUARD) / den2;
+  p_out = masked ? 0.f : e / (l + PCPB_GUARD);
+  ds_out = masked ? 0.f : bf16r(bf16r(dsf) * scale);
+}
+
+// ------------------------------------------------------------------------------------------------
+// backward, dK / dV: CTA = 128 keys of one (batch, kv head); 8 warps x 16 keys; query blocks of 64.
+// Works on the transposed tiles S^T = K Q^T and dP^T = V dO^T so that P^T and dS^T come out of the tensor
+// cores already in the A-operand register layout of the next two products.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_flash_bwd_dkv(FlashArgs a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const uint32_t sK = smem_u32(smem), sV = sK + 128 * ROWB, sQ = sV + 128 * ROWB, sDO = sQ + 2 * 64 * ROWB;
+  float* sstat = reinterpret_cast<float*>(smem + 2 * 128 * ROWB + 4 * 64 * ROWB);       // [2 bufs][3][64]: m, l, D
+  const int kb = blockIdx.x;
+  const int bhk = blockIdx.y, b = bhk / a.Hkv, hk = bhk % a.Hkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int d = a.H * HD, dkv = a.Hkv * HD, grp = a.H / a.Hkv;
+  const long long wqkn = d + dkv, wqkv = d + 2 * dkv;
+  const int j0 = kb * 128;
+  const bf16* Kg = (const bf16*)a.qkn + ((long long)b * a.T + j0) * wqkn + d + hk * HD;
+  const bf16* Vg = (const bf16*)a.qkv + ((long long)b * a.T + j0) * wqkv + d + dkv + hk * HD;
+  load_tile<128, 256>(sK, Kg, wqkn);
+  load_tile<128, 256>(sV, Vg, wqkv);
+  cp_async_commit();
+
+  float dk[16][4], dv[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { dk[i][0] = dk[i][1] = dk[i][2] = dk[i][3] = 0.f; dv[i][0] = dv[i][1] = dv[i][2] = dv[i][3] = 0.f; }
+
+  const int nqb = a.T / 64, qb_first = j0 / 64;
+  const int per_head = nqb - qb_first;
+  const int total = per_head * grp;
+  const int key_lo = j0 + warp * 16 + g;                     // this thread's keys: key_lo and key_lo + 8
+
+  auto issue = [&](int it, int buf) {
+    const int h = hk * grp + it / per_head, qb = qb_first + it % per_head;
+    const bf16* Qg = (const bf16*)a.qkn + ((long long)b * a.T + qb * 64) * wqkn + h * HD;
+    const bf16* DOg = (const bf16*)a.dout + ((long long)b * a.T + qb * 64) * d + h * HD;
+    load_tile<64, 256>(sQ + buf * 64 * ROWB, Qg, wqkn);
+    load_tile<64, 256>(sDO + buf * 64 * ROWB, DOg, d);
+    if (threadIdx.x < 192) {
+      const int which = threadIdx.x >> 6, i = threadIdx.x & 63;
+      const float* src = which == 0 ? a.mrow : (which == 1 ? a.lrow : a.drow);
+      sstat[buf * 192 + which * 64 + i] = src[((long long)b * a.H + h) * a.T + qb * 64 + i];
+    }
+    cp_async_commit();
+  };
+  issue(0, 0);
+
+  for (int it = 0; it < total; ++it) {
+    const int buf = it & 1;
+    if (it + 1 < total) { issue(it + 1, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    __syncthreads();
+    const int qb = qb_first + it % per_head;
+    const uint32_t cQ = sQ + buf * 64 * ROWB, cDO = sDO + buf * 64 * ROWB;
+    const float* st = sstat + buf * 192;
+
+    float sT[8][4], dpT[8][4];                               // [16 keys] x [64 queries]
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { sT[i][0] = sT[i][1] = sT[i][2] = sT[i][3] = 0.f; dpT[i][0] = dpT[i][1] = dpT[i][2] = dpT[i][3] = 0.f; }
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      uint32_t ak[4], av[4];
+      load_a(sK, warp * 16, ks, ak);
+      load_a(sV, warp * 16, ks, av);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t bq[4], bd[4];
+        load_b_nk(cQ, np * 16, ks, bq);
+        load_b_nk(cDO, np * 16, ks, bd);
+        mma16816(sT[2 * np], ak[0], ak[1], ak[2], ak[3], bq[0], bq[1]);
+        mma16816(sT[2 * np + 1], ak[0], ak[1], ak[2], ak[3], bq[2], bq[3]);
+        mma16816(dpT[2 * np], av[0], av[1], av[2], av[3], bd[0], bd[1]);
+        mma16816(dpT[2 * np + 1], av[0], av[1], av[2], av[3], bd[2], bd[3]);
+      }
+    }
+    const bool diag = (qb * 64 < j0 + 128);                  // some (key, query) pairs of this tile are masked
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int qi = nt * 8 + 2 * t + (e & 1);             // query index inside the block (tile column)
+        const int key = key_lo + (e >> 1) * 8;
+        const bool masked = diag && (key > qb * 64 + qi);
+        float p, ds;
+        bwd_elem(sT[nt][e], dpT[nt][e], a.scale, st[qi], st[64 + qi], st[128 + qi], masked, p, ds);
+        sT[nt][e] = p; dpT[nt][e] = ds;
+      }
+    }
+    // dV += P^T dO ; dK += dS^T Q     (contraction over the 64 queries)
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      const uint32_t p0 = pack_bf16(sT[2 * kk][0], sT[2 * kk][1]), p1 = pack_bf16(sT[2 * kk][2], sT[2 * kk][3]);
+      const uint32_t p2 = pack_bf16(sT[2 * kk + 1][0], sT[2 * kk + 1][1]), p3 = pack_bf16(sT[2 * kk + 1][2], sT[2 * kk + 1][3]);
+      const uint32_t s0 = pack_bf16(dpT[2 * kk][0], dpT[2 * kk][1]), s1 = pack_bf16(dpT[2 * kk][2], dpT[2 * kk][3]);
+      const uint32_t s2 = pack_bf16(dpT[2 * kk + 1][0], dpT[2 * kk + 1][1]), s3 = pack_bf16(dpT[2 * kk + 1][2], dpT[2 * kk + 1][3]);
+#pragma unroll
+      for (int np = 0; np < 8; ++np) {
+        uint32_t bd[4], bq[4];
+        load_b_kn(cDO, kk * 16, 2 * np, bd);
+        load_b_kn(cQ, kk * 16, 2 * np, bq);
+        mma16816(dv[2 * np], p0, p1, p2, p3, bd[0], bd[1]);
+        mma16816(dv[2 * np + 1], p0, p1, p2, p3, bd[2], bd[3]);
+        mma16816(dk[2 * np], s0, s1, s2, s3, bq[0], bq[1]);
+        mma16816(dk[2 * np + 1], s0, s1, s2, s3, bq[2], bq[3]);
+      }
+    }
+    __syncthreads();
+  }
+  // dk -> k part of dqkn (gradient wrt the normalised roped k), dv -> v part of dqkv
+  bf16* dKg = (bf16*)a.dqkn + ((long long)b * a.T) * wqkn + d + hk * HD;
+  bf16* dVg = (bf16*)a.dqkv + ((long long)b * a.T) * wqkv + d + dkv + hk * HD;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int key = key_lo + r * 8;
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      *reinterpret_cast<uint32_t*>(dKg + (long long)key * wqkn + nt * 8 + 2 * t) = pack_bf16(dk[nt][2 * r], dk[nt][2 * r + 1]);
+      *reinterpret_cast<uint32_t*>(dVg + (long long)key * wqkv + nt * 8 + 2 * t) = pack_bf16(dv[nt][2 * r], dv[nt][2 * r + 1]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// backward, dQ: CTA = 64 query rows of one (batch, head); 4 warps x 16 rows; key blocks of 64
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) k_flash_bwd_dq(FlashArgs a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const uint32_t sQ = smem_u32(smem), sDO = sQ + 64 * ROWB, sK = sDO + 64 * ROWB, sV = sK + 2 * 64 * ROWB;
+  const int qb = gridDim.x - 1 - blockIdx.x;
+  const int bh = blockIdx.y, b = bh / a.H, h = bh % a.H, hk = h / (a.H / a.Hkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int d = a.H * HD, dkv = a.Hkv * HD;
+  const long long wqkn = d + dkv, wqkv = d + 2 * dkv;
+  const int q0 = qb * 64;
+  const bf16* Qg = (const bf16*)a.qkn + ((long long)b * a.T + q0) * wqkn + h * HD;
+  const bf16* DOg = (const bf16*)a.dout + ((long long)b * a.T + q0) * d + h * HD;
+  const bf16* Kg = (const bf16*)a.qkn + (long long)b * a.T * wqkn + d + hk * HD;
+  const bf16* Vg = (const bf16*)a.qkv + (long long)b * a.T * wqkv + d + dkv + hk * HD;
+  load_tile<64, 128>(sQ, Qg, wqkn);
+  load_tile<64, 128>(sDO, DOg, d);
+  load_tile<64, 128>(sK, Kg, wqkn);
+  load_tile<64, 128>(sV, Vg, wqkv);
+  cp_async_commit();
+
+  const int row_lo = q0 + warp * 16 + g;
+  float mrow[2], lrow[2], Drow[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const long long idx = (long long)bh * a.T + row_lo + r * 8;
+    mrow[r] = a.mrow[idx]; lrow[r] = a.lrow[idx]; Drow[r] = a.drow[idx];
+  }
+  float dq[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { dq[i][0] = dq[i][1] = dq[i][2] = dq[i][3] = 0.f; }
+  const int nkb = qb + 1;
+  for (int kb = 0; kb < nkb; ++kb) {
+    const int buf = kb & 1;
+    if (kb + 1 < nkb) {
+      load_tile<64, 128>(sK + (buf ^ 1) * 64 * ROWB, Kg + (long long)(kb + 1) * 64 * wqkn, wqkn);
+      load_tile<64, 128>(sV + (buf ^ 1) * 64 * ROWB, Vg + (long long)(kb + 1) * 64 * wqkv, wqkv);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t cK = sK + buf * 64 * ROWB, cV = sV + buf * 64 * ROWB;
+    float s[8][4], dp[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; dp[i][0] = dp[i][1] = dp[i][2] = dp[i][3] = 0.f; }
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      uint32_t aq[4], ad[4];
+      load_a(sQ, warp * 16, ks, aq);
+      load_a(sDO, warp * 16, ks, ad);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t bk[4], bv[4];
+        load_b_nk(cK, np * 16, ks, bk);
+        load_b_nk(cV, np * 16, ks, bv);
+        mma16816(s[2 * np], aq[0], aq[1], aq[2], aq[3], bk[0], bk[1]);
+        mma16816(s[2 * np + 1], aq[0], aq[1], aq[2], aq[3], bk[2], bk[3]);
+        mma16816(dp[2 * np], ad[0], ad[1], ad[2], ad[3], bv[0], bv[1]);
+        mma16816(dp[2 * np + 1], ad[0], ad[1], ad[2], ad[3], bv[2], bv[3]);
+      }
+    }
+    const bool diag = (kb == nkb - 1);
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = kb * 64 + nt * 8 + 2 * t + (e & 1);
+        const int r = e >> 1;
+        const bool masked = diag && (col > row_lo + r * 8);
+        float p, ds;
+        bwd_elem(s[nt][e], dp[nt][e], a.scale, mrow[r], lrow[r], Drow[r], masked, p, ds);
+        dp[nt][e] = ds;
+      }
+    }
+    // dQ += dS K    (contraction over the 64 keys)
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      const uint32_t a0 = pack_bf16(dp[2 * kk][0], dp[2 * kk][1]), a1 = pack_bf16(dp[2 * kk][2], dp[2 * kk][3]);
+      const uint32_t a2 = pack_bf16(dp[2 * kk + 1][0], dp[2 * kk + 1][1]), a3 = pack_bf16(dp[2 * kk + 1][2], dp[2 * kk + 1][3]);
+#pragma unroll
+      for (int np = 0; np < 8; ++np) {
+        uint32_t bk[4];
+        load_b_kn(cK, kk * 16, 2 * np, bk);
+        mma16816(dq[2 * np], a0, a1, a2, a3, bk[0], bk[1]);
+        mma16816(dq[2 * np + 1], a0, a1, a2, a3, bk[2], bk[3]);
+      }
+    }
+    __syncthreads();
+  }
+  bf16* dQg = (bf16*)a.dqkn + ((long long)b * a.T) * wqkn + h * HD;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = row_lo + r * 8;
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt)
+      *reinterpret_cast<uint32_t*>(dQg + (long long)row * wqkn + nt * 8 + 2 * t) = pack_bf16(dq[nt][2 * r], dq[nt][2 * r + 1]);
+  }
+}
+
+constexpr int FWD_SMEM = 64 * ROWB + 4 * 64 * ROWB;                          // Q + 2x(K,V) = 80 KB
+constexpr int DKV_SMEM = 2 * 128 * ROWB + 4 * 64 * ROWB + 2 * 192 * 4;       // K,V + 2x(Q,dO) + stats = 129.5 KB
+constexpr int DQ_SMEM = 2 * 64 * ROWB + 4 * 64 * ROWB;                       // Q,dO + 2x(K,V) = 96 KB
+
+}  // namespace
+
+bool flash_supported(const FlashArgs& a) {
+  return a.hd == HD && a.T % 128 == 0 && a.T >= 128 && a.H % a.Hkv == 0 && a.B > 0 &&
+         ((a.H * HD) % 8 == 0) && (long long)a.B * a.H <= 65535 && (long long)a.B * a.Hkv <= 65535;
+}
+
+static cudaError_t set_attrs() {
+  static bool attr[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !attr[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(k_flash_fwd, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_flash_bwd_dkv, cudaFuncAttributeMaxDynamicSharedMemorySize, DKV_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_flash_bwd_dq, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) attr[dev] = true;
+  }
+  return cudaSuccess;
+}
+
+cudaError_t launch_flash_fwd(cudaStream_t st, const FlashArgs& a) {
+  cudaError_t e0 = set_attrs();
+  if (e0 != cudaSuccess) return e0;
+  dim3 grid(a.T / 64, a.B * a.H);
+  k_flash_fwd<<<grid, 128, FWD_SMEM, st>>>(a);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_flash_bwd(cudaStream_t st, const FlashArgs& a) {
+  cudaError_t e0 = set_attrs();
+  if (e0 != cudaSuccess) return e0;
+  const long long rows = (long long)a.B * a.H * a.T;
+  k_flash_prep<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>(a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  dim3 g1(a.T / 128, a.B * a.Hkv);
+  k_flash_bwd_dkv<<<g1, 256, DKV_SMEM, st>>>(a);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  dim3 g2(a.T / 64, a.B * a.H);
+  k_flash_bwd_dq<<<g2, 128, DQ_SMEM, st>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace pcpb

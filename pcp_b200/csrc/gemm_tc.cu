@@ -1,7 +1,525 @@
+// bf16 GEMM on the 5th-generation tensor cores (sm_100a): tcgen05.mma with the accumulator in tensor
+// memory, operand tiles staged in shared memory by TMA (128-byte swizzle), one persistent CTA per SM.
+//
+//   C[M,N] = sum_k A(m,k) B(k,n)       A, B bf16; f32 accumulate; epilogues of kernels.h
+//
+// Tile 128 x BN (BN = 256 or 128) x 64.  Warp roles (192 threads):
+//   warp 0      TMA producer: fills the NSTAGE-deep ring of (A tile, B tile) pairs
+//   warp 1      allocates tensor memory; one elected lane issues tcgen05.mma and commits
+//   warps 2..5  epilogue: tcgen05.ld of one accumulator buffer (32 lanes per warp), epilogue math, stores
+// Two accumulator buffers of BN columns each let the epilogue of tile i overlap the MMAs of tile i+1.
+//
+// Operand layouts.  Either operand may be "K-major" (contraction index contiguous in memory) or
+// "MN-major" (the M / N index contiguous); the three GEMMs of a linear layer need all combinations:
+//   forward   Y = X W^T      A K-major,  B K-major
+//   dgrad     dX = dY W      A K-major,  B MN-major
+//   wgrad     dW = dY^T X    A MN-major, B MN-major      (long contraction: split over CTAs, f32 slabs)
+// K-major tile in shared memory: rows of 64 elements (128 B), 8-row groups 1024 B apart.
+// MN-major tile: chunks of 64 M/N-elements; inside a chunk one 128 B row per k, 8-row groups 1024 B apart,
+// chunks 8192 B apart.
+//
+// Every mbarrier wait is bounded: after the limit the kernel sets an error word, stops issuing work, waits
+// (bounded) for its own TMA copies still in flight, frees its tensor memory and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
 #include "gemm_tc.h"
 
 namespace pcpb {
-bool gemm_tc_supported(const GemmArgs&) { return false; }
-int gemm_tc_launches(const GemmArgs&) { return 1; }
-cudaError_t launch_gemm_tc(cudaStream_t, const GemmArgs&) { return cudaErrorNotSupported; }
+
+namespace {
+
+constexpr int BM = 128, BK = 64;
+constexpr int A_TILE_BYTES = BM * BK * 2;                 // 16 KB
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+struct TcParams {
+  int M, N, K;                 // output rows, output cols, contraction length
+  int tiles_m, tiles_n, splits, kb_per_split;
+  int epi;
+  void* C; long long ldc;
+  const void* R; void* C2;
+  float clip;
+  float* slab;                 // split-K partial sums [splits][M][N] (f32)
+  int* err;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (and records the error) when the limit is hit or another role failed.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
+  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+    if (mbar_try(bar, parity)) return true;
+    if ((it & 1023u) == 1023u && *((volatile int*)err) != 0) return false;
+  }
+  atomicCAS(err, 0, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);              // start address, 16-byte units
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;     // leading-dimension byte offset
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;     // stride-dimension byte offset
+  d |= (uint64_t)1 << 46;                                // descriptor version (Blackwell)
+  d |= (uint64_t)2 << 61;                                // 128-byte swizzle
+  return d;
+}
+
+__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accum) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+
+// Epilogue of 32 consecutive columns of one output row held as f32 bit patterns in r[].
+__device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, int col, const uint32_t (&r)[32]) {
+  float acc[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) acc[i] = __uint_as_float(r[i]);
+  const size_t o = (size_t)row * p.ldc + col;
+  if (p.epi == EPI_WGRAD || p.epi < 0) {                      // f32 outputs
+    float* dst = (p.epi < 0) ? p.slab + o : (float*)p.C + o;
+    if (p.epi == EPI_WGRAD) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float v = bf16_round(acc[i]);
+        if (!((v - v) == 0.f)) v = 0.f;
+        acc[i] = fminf(fmaxf(v, -p.clip), p.clip);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      reinterpret_cast<float4*>(dst)[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+    return;
+  }
+  __nv_bfloat16* C = (__nv_bfloat16*)p.C + o;
+  if (p.epi == EPI_RESID || p.epi == EPI_DRELU2) {
+    const uint4* rp = reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.R + o);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float x[8];
+      unpack8(rp[q], x);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float a = bf16_round(acc[8 * q + i]);
+        if (p.epi == EPI_RESID) {
+          acc[8 * q + i] = x[i] + a;
+        } else {
+          // backward of a = power(max(u,0), 2):  da * (2 * (bf16(r*r) / r)) where u > 0
+          const float u = x[i], rr = fmaxf(u, 0.f);
+          float out = 0.f;
+          if (u > 0.f) {
+            const float y = bf16_round(rr * rr);
+            const float qq = bf16_round(y / rr);
+            out = a * bf16_round(2.f * qq);
+          }
+          acc[8 * q + i] = out;
+        }
+      }
+    }
+  }
+  uint4 outv[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    outv[q].x = pack2(acc[8 * q + 0], acc[8 * q + 1]); outv[q].y = pack2(acc[8 * q + 2], acc[8 * q + 3]);
+    outv[q].z = pack2(acc[8 * q + 4], acc[8 * q + 5]); outv[q].w = pack2(acc[8 * q + 6], acc[8 * q + 7]);
+  }
+#pragma unroll
+  for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(C)[q] = outv[q];
+  if (p.epi == EPI_RELU2) {
+    __nv_bfloat16* C2 = (__nv_bfloat16*)p.C2 + o;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float x[8];
+      unpack8(outv[q], x);                                     // u as stored (bf16)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { const float rr = fmaxf(x[i], 0.f); x[i] = rr * rr; }
+      uint4 v;
+      v.x = pack2(x[0], x[1]); v.y = pack2(x[2], x[3]); v.z = pack2(x[4], x[5]); v.w = pack2(x[6], x[7]);
+      reinterpret_cast<uint4*>(C2)[q] = v;
+    }
+  }
+}
+
+template <int BN> struct TcCfg {
+  static constexpr int B_TILE_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+  static constexpr int NSTAGE = (BN == 256) ? 4 : 6;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(192, 1)
+k_gemm_tc(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const TcParams p) {
+  using Cfg = TcCfg<BN>;
+  constexpr int NSTAGE = Cfg::NSTAGE;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;          // 1024 B alignment for the swizzle atoms
+  const uint32_t bar_base = base + NSTAGE * Cfg::STAGE_BYTES;
+  // barrier layout (8 B each): full[NSTAGE], empty[NSTAGE], tmem_full[2], tmem_empty[2], then the tmem address
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (NSTAGE + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * NSTAGE + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * NSTAGE + 2 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * NSTAGE + 4);
+  uint8_t* smem_gen = smem_raw + (base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + NSTAGE * Cfg::STAGE_BYTES + 8 * (2 * NSTAGE + 4));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_items = p.tiles_m * p.tiles_n * p.splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NSTAGE; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_gen;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int armed[NSTAGE];
+#pragma unroll
+      for (int s = 0; s < NSTAGE; ++s) armed[s] = 0;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        const int tile = item / p.splits, split = item % p.splits;
+        const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, p.K / BK);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % NSTAGE;
+          const uint32_t ph = (it / NSTAGE) & 1u;
+          if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, p.err, 1))) break;
+          mbar_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
+          armed[s] += 1;
+          const uint32_t sa = base + s * Cfg::STAGE_BYTES, sb = sa + A_TILE_BYTES;
+          const int k0 = kb * BK;
+          if (!A_MN) tma_load_2d(sa, &tma_a, full_bar(s), k0, m0);
+          else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * 8192, &tma_a, full_bar(s), m0 + c * 64, k0);
+          }
+          if (!B_MN) tma_load_2d(sb, &tma_b, full_bar(s), k0, n0);
+          else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * 8192, &tma_b, full_bar(s), n0 + c * 64, k0);
+          }
+        }
+      }
+      if (!ok) {
+        // error path: let the copies already issued land before the CTA goes away (bounded)
+#pragma unroll
+        for (int s = 0; s < NSTAGE; ++s)
+          if (armed[s] > 0) {
+            const uint32_t ph = (uint32_t)(armed[s] - 1) & 1u;
+            for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(full_bar(s), ph)) break;
+          }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) |
+                                 ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      constexpr uint32_t A_LBO = A_MN ? 8192u : 16u, B_LBO = B_MN ? 8192u : 16u;
+      constexpr uint32_t A_KSTEP = A_MN ? 2048u : 32u, B_KSTEP = B_MN ? 2048u : 32u;
+      uint32_t it = 0;
+      int local = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local) {
+        const int split = item % p.splits;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, p.K / BK);
+        const int acc = local & 1;
+        const uint32_t aph = ((uint32_t)local >> 1) & 1u;
+        if (!(ok = mbar_wait(tempty_bar(acc), aph ^ 1u, p.err, 2))) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % NSTAGE;
+          const uint32_t ph = (it / NSTAGE) & 1u;
+          if (!(ok = mbar_wait(full_bar(s), ph, p.err, 3))) break;
+          tc_fence_after();
+          const uint32_t sa = base + s * Cfg::STAGE_BYTES, sb = sa + A_TILE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = make_desc(sa + k * A_KSTEP, A_LBO, 1024u);
+            const uint64_t db = make_desc(sb + k * B_KSTEP, B_LBO, 1024u);
+            mma_bf16(tmem_d, da, db, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          mma_commit(empty_bar(s));                 // frees the stage when these MMAs have read it
+        }
+        if (ok) mma_commit(tfull_bar(acc));         // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int q = warp & 3;                         // TMEM lane quarter this warp may access
+    int local = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local) {
+      const int tile = item / p.splits, split = item % p.splits;
+      const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
+      const int acc = local & 1;
+      const uint32_t aph = ((uint32_t)local >> 1) & 1u;
+      ok = mbar_wait(tfull_bar(acc), aph, p.err, 4);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      TcParams pe = p;
+      if (p.splits > 1) { pe.epi = -1; pe.slab = p.slab + (size_t)split * p.M * p.N; pe.ldc = p.N; }
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c), r);
+        epilogue_chunk(pe, row, n0 + c, r);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+  }
+}
+
+// Sum of the split-K slabs in split order, then the weight-gradient epilogue.
+__global__ void k_splitk_reduce(const float* __restrict__ slab, int splits, size_t mn, int N, float* __restrict__ C,
+                                long long ldc, int epi, float clip) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i < mn; i += (size_t)gridDim.x * blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += slab[(size_t)s * mn + i];
+    if (epi == EPI_WGRAD) {
+      float v = bf16_round(acc);
+      if (!((v - v) == 0.f)) v = 0.f;
+      acc = fminf(fmaxf(v, -clip), clip);
+    }
+    C[(i / N) * ldc + (i % N)] = acc;
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// 2-D bf16 row-major tensor [rows, cols] (cols contiguous, pitch ld elements), box [box_rows, 64 cols]
+bool make_map(CUtensorMap* map, const void* ptr, uint64_t cols, uint64_t rows, uint64_t ld, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t es[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct Plan {
+  bool ok = false;
+  bool a_mn = false, b_mn = false;
+  long long lda = 0, ldb = 0;
+  int bn = 0, splits = 1, kb_per_split = 0;
+};
+
+int g_sm_count = 0;
+
+Plan plan_for(const GemmArgs& g) {
+  Plan pl;
+  if (g.M <= 0 || g.N <= 0 || g.K <= 0) return pl;
+  if (g.M % BM || g.K % BK || g.N % 128) return pl;
+  if (g.sak == 1 && g.sam >= g.K) { pl.a_mn = false; pl.lda = g.sam; }
+  else if (g.sam == 1 && g.sak >= g.M) { pl.a_mn = true; pl.lda = g.sak; }
+  else return pl;
+  if (g.sbk == 1 && g.sbn >= g.K) { pl.b_mn = false; pl.ldb = g.sbn; }
+  else if (g.sbn == 1 && g.sbk >= g.N) { pl.b_mn = true; pl.ldb = g.sbk; }
+  else return pl;
+  if (pl.a_mn && !pl.b_mn) return pl;                            // combination not instantiated
+  if (pl.lda % 8 || pl.ldb % 8 || g.ldc % 8) return pl;
+  if (((uintptr_t)g.A | (uintptr_t)g.B | (uintptr_t)g.C) & 15) return pl;
+  if (g.R && ((uintptr_t)g.R & 15)) return pl;
+  if (g.C2 && ((uintptr_t)g.C2 & 15)) return pl;
+  if (g.epi < EPI_STORE || g.epi > EPI_WGRAD) return pl;
+  pl.bn = (g.N % 256 == 0) ? 256 : 128;
+  const int tiles = (g.M / BM) * (g.N / pl.bn), kblocks = g.K / BK;
+  pl.splits = 1;
+  if (g.epi == EPI_WGRAD && tiles < 2 * 148) {
+    int s = (2 * 148 + tiles - 1) / tiles;
+    if (s > 8) s = 8;
+    while (s > 1 && kblocks / s < 8) --s;
+    pl.splits = s;
+  }
+  // the f32 slabs must fit the caller's scratch
+  while (pl.splits > 1 && (size_t)pl.splits * g.M * g.N * sizeof(float) > g.scratch_bytes) --pl.splits;
+  pl.kb_per_split = (kblocks + pl.splits - 1) / pl.splits;
+  pl.splits = (kblocks + pl.kb_per_split - 1) / pl.kb_per_split;
+  pl.ok = true;
+  return pl;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+cudaError_t launch_variant(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int grid) {
+  auto kern = k_gemm_tc<BN, A_MN, B_MN>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<BN>::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) attr_set[dev] = true;
+  }
+  kern<<<grid, 192, TcCfg<BN>::SMEM_BYTES, st>>>(ma, mb, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool gemm_tc_supported(const GemmArgs& g) { return g.err_word != nullptr && plan_for(g).ok && encode_fn() != nullptr; }
+int gemm_tc_launches(const GemmArgs& g) { return plan_for(g).splits > 1 ? 2 : 1; }
+
+size_t gemm_tc_scratch_wanted(int M, int N, int K) {
+  if (M % BM || N % 128 || K % BK) return 0;
+  const int bn = (N % 256 == 0) ? 256 : 128;
+  const int tiles = (M / BM) * (N / bn), kblocks = K / BK;
+  if (tiles >= 2 * 148) return 0;
+  int s = (2 * 148 + tiles - 1) / tiles;
+  if (s > 8) s = 8;
+  while (s > 1 && kblocks / s < 8) --s;
+  return s > 1 ? (size_t)s * M * N * sizeof(float) : 0;
+}
+
+cudaError_t launch_gemm_tc(cudaStream_t st, const GemmArgs& g) {
+  const Plan pl = plan_for(g);
+  if (!pl.ok) return cudaErrorInvalidValue;
+  if (!g_sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (g_sm_count <= 0) g_sm_count = 148;
+  }
+  int* err = g.err_word;
+  if (!err) return cudaErrorInvalidValue;
+  cudaError_t e = cudaSuccess;
+  CUtensorMap ma, mb;
+  bool ok;
+  if (!pl.a_mn) ok = make_map(&ma, g.A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)pl.lda, BM);
+  else ok = make_map(&ma, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)pl.lda, 64);
+  if (!pl.b_mn) ok = ok && make_map(&mb, g.B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)pl.ldb, (uint32_t)pl.bn);
+  else ok = ok && make_map(&mb, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)pl.ldb, 64);
+  if (!ok) return cudaErrorInvalidValue;
+  TcParams p;
+  p.M = g.M; p.N = g.N; p.K = g.K;
+  p.tiles_m = g.M / BM; p.tiles_n = g.N / pl.bn; p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
+  p.epi = g.epi; p.C = g.C; p.ldc = g.ldc; p.R = g.R; p.C2 = g.C2; p.clip = g.clip; p.slab = nullptr; p.err = err;
+  if (pl.splits > 1) p.slab = (float*)g.scratch;
+  const int items = p.tiles_m * p.tiles_n * p.splits;
+  const int grid = items < g_sm_count ? items : g_sm_count;
+  if (pl.bn == 256) {
+    if (!pl.a_mn && !pl.b_mn) e = launch_variant<256, false, false>(st, ma, mb, p, grid);
+    else if (!pl.a_mn && pl.b_mn) e = launch_variant<256, false, true>(st, ma, mb, p, grid);
+    else e = launch_variant<256, true, true>(st, ma, mb, p, grid);
+  } else {
+    if (!pl.a_mn && !pl.b_mn) e = launch_variant<128, false, false>(st, ma, mb, p, grid);
+    else if (!pl.a_mn && pl.b_mn) e = launch_variant<128, false, true>(st, ma, mb, p, grid);
+    else e = launch_variant<128, true, true>(st, ma, mb, p, grid);
+  }
+  if (e != cudaSuccess) return e;
+  if (pl.splits > 1) {
+    const size_t mn = (size_t)g.M * g.N;
+    unsigned blocks = (unsigned)((mn + 255) / 256);
+    if (blocks > 148u * 16) blocks = 148u * 16;
+    k_splitk_reduce<<<blocks, 256, 0, st>>>((const float*)g.scratch, pl.splits, mn, g.N, (float*)g.C, g.ldc, g.epi, g.clip);
+    e = cudaGetLastError();
+  }
+  return e;
+}
+
 }  // namespace pcpb

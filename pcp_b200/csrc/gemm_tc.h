@@ -12,5 +12,7 @@ bool gemm_tc_supported(const GemmArgs& g);
 // Number of kernel launches launch_gemm_tc enqueues for this problem.
 int gemm_tc_launches(const GemmArgs& g);
 cudaError_t launch_gemm_tc(cudaStream_t st, const GemmArgs& g);
+// Scratch bytes a weight-gradient GEMM of this shape would like for its split-K slabs (0 = none).
+size_t gemm_tc_scratch_wanted(int M, int N, int K);
 
 }  // namespace pcpb

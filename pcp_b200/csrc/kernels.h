@@ -26,6 +26,8 @@ struct GemmArgs {
   int M, N, K;
   int epi;
   float clip;           // EPI_WGRAD
+  // tensor-core path only: split-K scratch of the caller (f32 slabs) and its device error word
+  void* scratch = nullptr; size_t scratch_bytes = 0; int* err_word = nullptr;
 };
 cudaError_t launch_gemm_generic(cudaStream_t st, int dt, const GemmArgs& g);
 

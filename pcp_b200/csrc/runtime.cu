@@ -8,6 +8,7 @@
 
 #include "../../include/pcp_b200.h"
 #include "common.cuh"
+#include "attn_flash.h"
 #include "gemm_tc.h"
 
 using namespace pcpb;
@@ -120,6 +121,7 @@ int build_workspace(pcpb_backend* b) {
   WS(b, w.hf, M * d * es); WS(b, w.logits, M * (size_t)c.V * es);
   WS(b, w.dx, M * d * es); WS(b, w.dh, M * d * es); WS(b, w.du, M * F * es); WS(b, w.dout, M * d * es);
   WS(b, w.dqkn, M * (d + dkv) * es); WS(b, w.dqkv, M * (d + 2 * dkv) * es); WS(b, w.dkv_acc, M * 2 * dkv * 4);
+  WS(b, w.drow, (size_t)c.B * c.H * c.T * 4);
   WS(b, w.ids, M * 8); WS(b, w.targets, M * 8);
   WS(b, w.d_cos, c.rope_cos.size() * 2); WS(b, w.d_sin, c.rope_sin.size() * 2);
   CK(b, cudaMemcpy(w.d_cos, c.rope_cos.data(), c.rope_cos.size() * 2, cudaMemcpyHostToDevice));
@@ -143,15 +145,64 @@ int build_workspace(pcpb_backend* b) {
   WS(b, w.partial, 4 * c2s.size()); WS(b, w.normsq, 4 * (size_t)nseg); WS(b, w.heal_flags, 4 * (size_t)nseg * 2);
   CK(b, cudaMemcpy(w.segs, segs.data(), sizeof(TensorSeg) * nseg, cudaMemcpyHostToDevice));
   CK(b, cudaMemcpy(w.chunk2seg, c2s.data(), sizeof(int) * c2s.size(), cudaMemcpyHostToDevice));
+  // tensor-core GEMM scratch (split-K slabs of the weight-gradient GEMMs) and error word
+  if (c.dtype == DT_BF16) {
+    const int Mi = (int)M, di = (int)d, Fi = (int)F, wqi = (int)(d + 2 * dkv), Vi = (int)c.V;
+    size_t want = 0;
+    const int shapes[5][2] = {{wqi, di}, {di, di}, {Fi, di}, {di, Fi}, {Vi, di}};
+    for (auto& s : shapes) { size_t x = gemm_tc_scratch_wanted(s[0], s[1], Mi); if (x > want) want = x; }
+    if (want) { WS(b, w.tc_scratch, want); w.tc_scratch_bytes = want; }
+  }
+  WS(b, w.tc_err, sizeof(int));
+  CK(b, cudaMemset(w.tc_err, 0, sizeof(int)));
   w.ready = true;
+  return PCPB_OK;
+}
+
+// The tensor-core GEMM records a non-zero code when one of its bounded waits ran out.
+int check_tc_error(pcpb_backend* b) {
+  int code = 0;
+  CK(b, cudaMemcpy(&code, b->ws.tc_err, sizeof(int), cudaMemcpyDeviceToHost));
+  if (code) {
+    cudaMemset(b->ws.tc_err, 0, sizeof(int));
+    return fail(b, PCPB_E_CUDA, "tensor-core GEMM gave up waiting on a barrier (role " + std::to_string(code) + "); results of this call are invalid");
+  }
+  return PCPB_OK;
+}
+
+// Collect the durations of the profiled launches recorded so far (blocks on the stream).
+int drain_profile(pcpb_backend* b) {
+  if (!b->prof_used) return PCPB_OK;
+  CK(b, cudaStreamSynchronize(b->stream));
+  for (size_t i = 0; i + 1 < b->prof_used; i += 2) {
+    float ms = 0.f;
+    CK(b, cudaEventElapsedTime(&ms, b->prof_events[i], b->prof_events[i + 1]));
+    b->prof_ms += ms;
+  }
+  b->prof_used = 0;
   return PCPB_OK;
 }
 
 // ------------------------------------------------------------------------------------------------
 // GEMM dispatch: tensor-core kernel when the shape qualifies, generic kernel otherwise
 // ------------------------------------------------------------------------------------------------
-int gemm(pcpb_backend* b, const GemmArgs& g) {
+int gemm(pcpb_backend* b, GemmArgs g) {
+  g.scratch = b->ws.tc_scratch; g.scratch_bytes = b->ws.tc_scratch_bytes; g.err_word = b->ws.tc_err;
   if (!b->force_generic && b->cfg.dtype == DT_BF16 && gemm_tc_supported(g)) {
+    if (b->profiling) {
+      if (b->prof_used + 2 > b->prof_events.size()) {
+        int r = drain_profile(b);
+        if (r) return r;
+      }
+      cudaEvent_t e0 = b->prof_events[b->prof_used], e1 = b->prof_events[b->prof_used + 1];
+      CK(b, cudaEventRecord(e0, b->stream));
+      KL(b, gemm_tc_launches(g), launch_gemm_tc(b->stream, g));
+      CK(b, cudaEventRecord(e1, b->stream));
+      b->prof_used += 2;
+      b->prof_flops += 2.0 * g.M * g.N * g.K;
+      b->prof_launches += 1;
+      return PCPB_OK;
+    }
     KL(b, gemm_tc_launches(g), launch_gemm_tc(b->stream, g));
     return PCPB_OK;
   }
@@ -196,10 +247,18 @@ int forward_backward(pcpb_backend* b, const void* wts, const long long* ids, con
     KL(b, 1, launch_rmsnorm_fwd(st, dt, w.xs[l], M, d, a.h1, a.t1));
     G(b, a.h1, d, 1, W(pq), 1, d, a.qkv, wq, M, wq, d, EPI_STORE);
     KL(b, 1, launch_rope_qknorm_fwd(st, dt, a.qkv, w.d_cos, w.d_sin, M, Tn, H, Hkv, hd, a.qkn, a.tq));
-    AttnArgs at{};
-    at.qkn = a.qkn; at.qkv = a.qkv; at.o = a.o; at.mrow = a.mrow; at.lrow = a.lrow;
-    at.B = (int)c.B; at.T = Tn; at.H = H; at.Hkv = Hkv; at.hd = hd; at.scale = scale;
-    KL(b, 1, launch_attn_fwd_generic(st, dt, at));
+    FlashArgs fa{};
+    fa.qkn = a.qkn; fa.qkv = a.qkv; fa.o = a.o; fa.mrow = a.mrow; fa.lrow = a.lrow;
+    fa.B = (int)c.B; fa.T = Tn; fa.H = H; fa.Hkv = Hkv; fa.hd = hd; fa.scale = scale;
+    const bool flash = !b->force_generic && dt == DT_BF16 && flash_supported(fa);
+    if (flash) {
+      KL(b, 1, launch_flash_fwd(st, fa));
+    } else {
+      AttnArgs at{};
+      at.qkn = a.qkn; at.qkv = a.qkv; at.o = a.o; at.mrow = a.mrow; at.lrow = a.lrow;
+      at.B = (int)c.B; at.T = Tn; at.H = H; at.Hkv = Hkv; at.hd = hd; at.scale = scale;
+      KL(b, 1, launch_attn_fwd_generic(st, dt, at));
+    }
     G(b, a.o, d, 1, W(pq + 3), 1, d, a.xmid, d, M, d, d, EPI_RESID, w.xs[l]);
     KL(b, 1, launch_rmsnorm_fwd(st, dt, a.xmid, M, d, a.h2, a.t2));
     G(b, a.h2, d, 1, W(pq + 4), 1, d, a.u, F, M, F, d, EPI_RELU2, nullptr, a.a);
@@ -230,11 +289,19 @@ int forward_backward(pcpb_backend* b, const void* wts, const long long* ids, con
     // attention
     G(b, w.dx, d, 1, W(pq + 3), d, 1, w.dout, d, M, d, d, EPI_STORE);               // d o
     G(b, w.dx, 1, d, a.o, d, 1, GR(pq + 3), d, d, d, M, EPI_WGRAD);                 // d c_proj
-    AttnArgs at{};
-    at.qkn = a.qkn; at.qkv = a.qkv; at.o = a.o; at.mrow = a.mrow; at.lrow = a.lrow;
-    at.B = (int)c.B; at.T = Tn; at.H = H; at.Hkv = Hkv; at.hd = hd; at.scale = scale;
-    at.dout = w.dout; at.dqkn = w.dqkn; at.dqkv = w.dqkv; at.dkv_acc = w.dkv_acc;
-    KL(b, 3, launch_attn_bwd_generic(st, dt, at));
+    FlashArgs fa{};
+    fa.qkn = a.qkn; fa.qkv = a.qkv; fa.o = a.o; fa.mrow = a.mrow; fa.lrow = a.lrow;
+    fa.B = (int)c.B; fa.T = Tn; fa.H = H; fa.Hkv = Hkv; fa.hd = hd; fa.scale = scale;
+    fa.dout = w.dout; fa.dqkn = w.dqkn; fa.dqkv = w.dqkv; fa.drow = w.drow;
+    if (!b->force_generic && dt == DT_BF16 && flash_supported(fa)) {
+      KL(b, 3, launch_flash_bwd(st, fa));
+    } else {
+      AttnArgs at{};
+      at.qkn = a.qkn; at.qkv = a.qkv; at.o = a.o; at.mrow = a.mrow; at.lrow = a.lrow;
+      at.B = (int)c.B; at.T = Tn; at.H = H; at.Hkv = Hkv; at.hd = hd; at.scale = scale;
+      at.dout = w.dout; at.dqkn = w.dqkn; at.dqkv = w.dqkv; at.dkv_acc = w.dkv_acc;
+      KL(b, 3, launch_attn_bwd_generic(st, dt, at));
+    }
     KL(b, 1, launch_rope_qknorm_bwd(st, dt, a.qkv, w.dqkn, a.tq, w.d_cos, w.d_sin, M, Tn, H, Hkv, hd, w.dqkv));
     G(b, w.dqkv, 1, wq, a.h1, d, 1, GR(pq), d, wq, d, M, EPI_WGRAD);                // d c_q,c_k,c_v (contiguous)
     G(b, w.dqkv, wq, 1, W(pq), d, 1, w.dh, d, M, d, wq, EPI_STORE);                 // d h1
@@ -290,6 +357,8 @@ int pcpb_create(int device_ordinal, pcpb_backend** out) {
   CK(b, cudaStreamCreateWithFlags(&b->stream, cudaStreamNonBlocking));
   CK(b, cudaEventCreate(&b->ev0));
   CK(b, cudaEventCreate(&b->ev1));
+  CK(b, cudaEventCreate(&b->tm0));
+  CK(b, cudaEventCreate(&b->tm1));
   return PCPB_OK;
 }
 
@@ -298,6 +367,9 @@ void pcpb_destroy(pcpb_backend* b) {
   DeviceGuard g(b->device);
   if (b->stream) cudaStreamSynchronize(b->stream);
   free_workspace(b);
+  for (cudaEvent_t e : b->prof_events) cudaEventDestroy(e);
+  if (b->tm0) cudaEventDestroy(b->tm0);
+  if (b->tm1) cudaEventDestroy(b->tm1);
   if (b->ev0) cudaEventDestroy(b->ev0);
   if (b->ev1) cudaEventDestroy(b->ev1);
   if (b->stream) cudaStreamDestroy(b->stream);
@@ -324,6 +396,20 @@ int pcpb_load_artifact(pcpb_backend* b, const void* bytes, size_t n) {
   int r = build_workspace(b);
   if (r) { free_workspace(b); return r; }
   b->art_ptr = bytes; b->art_len = n; b->loaded = true;
+  return PCPB_OK;
+}
+
+int pcpb_inspect_artifact(const void* bytes, size_t n, int64_t* facts, char* err, size_t err_cap) {
+  if (!bytes || !facts) return PCPB_E_INVALID;
+  ModelConfig c;
+  std::string why = parse_artifact((const char*)bytes, n, &c);
+  if (!why.empty()) {
+    if (err && err_cap) snprintf(err, err_cap, "%s", why.c_str());
+    return PCPB_E_ARTIFACT;
+  }
+  const int64_t f[12] = {c.V, c.d, c.L, c.H, c.Hkv, c.hd, c.F, c.B, c.T, c.dtype, (int64_t)c.params.size(), c.total_params};
+  memcpy(facts, f, sizeof f);
+  if (err && err_cap) err[0] = 0;
   return PCPB_OK;
 }
 
@@ -414,7 +500,7 @@ int pcpb_synchronize(pcpb_backend* b) {
   if (!b || !b->stream) return PCPB_E_INVALID;
   DeviceGuard g(b->device);
   CK(b, cudaStreamSynchronize(b->stream));
-  return PCPB_OK;
+  return (b->loaded && b->ws.ready) ? check_tc_error(b) : PCPB_OK;
 }
 
 // ---- execute -----------------------------------------------------------------------------------
@@ -472,6 +558,7 @@ int pcpb_execute(pcpb_backend* b, const char* fn, pcpb_buffer* const* in, size_t
                          (float*)lb->ptr, true);
     cudaError_t e = cudaStreamSynchronize(b->stream);
     if (r == PCPB_OK && e != cudaSuccess) r = fail(b, PCPB_E_CUDA, std::string("compute_gradients failed: ") + cudaGetErrorString(e));
+    if (r == PCPB_OK) r = check_tc_error(b);
     if (r) { block_release(gb); block_release(lb); return r; }
     pcpb_buffer** o = (pcpb_buffer**)malloc(sizeof(pcpb_buffer*) * (N + 1));
     flat_views(b, gb, PCPB_F32, o);
@@ -618,6 +705,38 @@ int pcpb_execute_host(pcpb_backend* b, const char* fn, const void* const* in, co
   if (r) { for (size_t i = 0; i < no; ++i) free(host[i]); free(host); free(nb); return r; }
   *out = host; *out_nbytes = nb; *n_out = no;
   return PCPB_OK;
+}
+
+int pcpb_op_gemm(pcpb_backend* b, int path, const pcpb_buffer* A, long long sam, long long sak, const pcpb_buffer* B,
+                 long long sbk, long long sbn, pcpb_buffer* C, long long ldc, const pcpb_buffer* R, pcpb_buffer* C2,
+                 int M, int N, int K, int epilogue) {
+  int r = require_loaded(b);
+  if (r) return r;
+  if (!A || !B || !C || M < 0 || N < 0 || K < 0 || epilogue < EPI_STORE || epilogue > EPI_WGRAD)
+    return fail(b, PCPB_E_INVALID, "bad gemm arguments");
+  if ((epilogue == EPI_RESID || epilogue == EPI_DRELU2) && !R) return fail(b, PCPB_E_INVALID, "this epilogue needs R");
+  if (epilogue == EPI_RELU2 && !C2) return fail(b, PCPB_E_INVALID, "this epilogue needs C2");
+  DeviceGuard g(b->device);
+  const size_t es = dtype_size(b->cfg.dtype);
+  // extents touched by the strided views must lie inside the buffers
+  auto span = [](long long r0, long long s0, long long r1, long long s1) { return (r0 > 0 ? (r0 - 1) * s0 : 0) + (r1 > 0 ? (r1 - 1) * s1 : 0) + 1; };
+  if (M && N && K) {
+    if ((size_t)span(M, sam, K, sak) * es > A->nbytes || (size_t)span(K, sbk, N, sbn) * es > B->nbytes)
+      return fail(b, PCPB_E_INVALID, "operand view exceeds its buffer");
+    const size_t ces = (epilogue == EPI_WGRAD) ? 4 : es;
+    if ((size_t)span(M, ldc, N, 1) * ces > C->nbytes) return fail(b, PCPB_E_INVALID, "output view exceeds its buffer");
+    if (R && (size_t)span(M, ldc, N, 1) * es > R->nbytes) return fail(b, PCPB_E_INVALID, "R view exceeds its buffer");
+    if (C2 && (size_t)span(M, ldc, N, 1) * es > C2->nbytes) return fail(b, PCPB_E_INVALID, "C2 view exceeds its buffer");
+  }
+  GemmArgs ga = mk(A->ptr, sam, sak, B->ptr, sbk, sbn, C->ptr, ldc, M, N, K, epilogue, R ? R->ptr : nullptr, C2 ? C2->ptr : nullptr);
+  ga.scratch = b->ws.tc_scratch; ga.scratch_bytes = b->ws.tc_scratch_bytes; ga.err_word = b->ws.tc_err;
+  if (path == 1) KL(b, 1, launch_gemm_generic(b->stream, b->cfg.dtype, ga));
+  else if (path == 2) {
+    if (b->cfg.dtype != DT_BF16 || !gemm_tc_supported(ga)) return fail(b, PCPB_E_INVALID, "shape not supported by the tensor-core kernel");
+    KL(b, gemm_tc_launches(ga), launch_gemm_tc(b->stream, ga));
+  } else if ((r = gemm(b, ga))) return r;
+  CK(b, cudaStreamSynchronize(b->stream));
+  return check_tc_error(b);
 }
 
 int pcpb_fifo_get_batch(pcpb_backend* b, const uint16_t* tokens, size_t n_tokens, size_t* cursor,
@@ -787,7 +906,7 @@ int pcpb_worker_end_round(pcpb_backend* b, void* delta_out, size_t delta_bytes, 
   }
   CK(b, cudaStreamSynchronize(b->stream));
   b->in_round = false;
-  return PCPB_OK;
+  return check_tc_error(b);
 }
 
 int pcpb_inner_loop(pcpb_backend* b, const pcpb_inner_cfg* cfg, const void* params_blob, size_t blob_bytes,
@@ -822,6 +941,60 @@ int pcpb_worker_read_state(pcpb_backend* b, int which, float* dst, size_t n) {
   if (n != len || !dst) return fail(b, PCPB_E_INVALID, "state length mismatch");
   CK(b, cudaMemcpyAsync(dst, src, n * 4, cudaMemcpyDeviceToHost, b->stream));
   CK(b, cudaStreamSynchronize(b->stream));
+  return PCPB_OK;
+}
+
+int pcpb_worker_last_loss(pcpb_backend* b, float* loss) {
+  int r = require_loaded(b);
+  if (r) return r;
+  if (!loss) return fail(b, PCPB_E_INVALID, "null loss pointer");
+  if (b->steps_done < 1) return fail(b, PCPB_E_STATE, "no step done in this round");
+  DeviceGuard g(b->device);
+  CK(b, cudaMemcpyAsync(loss, b->ws.loss_record + (b->steps_done - 1), 4, cudaMemcpyDeviceToHost, b->stream));
+  CK(b, cudaStreamSynchronize(b->stream));
+  return PCPB_OK;
+}
+
+int pcpb_timer_start(pcpb_backend* b) {
+  if (!b || !b->stream) return PCPB_E_INVALID;
+  DeviceGuard g(b->device);
+  CK(b, cudaEventRecord(b->tm0, b->stream));
+  return PCPB_OK;
+}
+
+int pcpb_timer_stop(pcpb_backend* b, double* ms) {
+  if (!b || !b->stream || !ms) return PCPB_E_INVALID;
+  DeviceGuard g(b->device);
+  CK(b, cudaEventRecord(b->tm1, b->stream));
+  CK(b, cudaEventSynchronize(b->tm1));
+  float f = 0.f;
+  CK(b, cudaEventElapsedTime(&f, b->tm0, b->tm1));
+  *ms = f;
+  return PCPB_OK;
+}
+
+int pcpb_profile_enable(pcpb_backend* b, int on) {
+  if (!b || !b->stream) return PCPB_E_INVALID;
+  DeviceGuard g(b->device);
+  if (on && b->prof_events.empty()) {
+    b->prof_events.resize(2048);
+    for (auto& e : b->prof_events) CK(b, cudaEventCreate(&e));
+  }
+  int r = drain_profile(b);
+  if (r) return r;
+  b->profiling = on != 0;
+  b->prof_flops = 0.0; b->prof_ms = 0.0; b->prof_launches = 0; b->prof_used = 0;
+  return PCPB_OK;
+}
+
+int pcpb_profile_read(pcpb_backend* b, long long* launches, double* total_ms, double* total_flops) {
+  if (!b || !b->stream) return PCPB_E_INVALID;
+  DeviceGuard g(b->device);
+  int r = drain_profile(b);
+  if (r) return r;
+  if (launches) *launches = b->prof_launches;
+  if (total_ms) *total_ms = b->prof_ms;
+  if (total_flops) *total_flops = b->prof_flops;
   return PCPB_OK;
 }
 

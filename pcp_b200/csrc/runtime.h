@@ -40,6 +40,7 @@ struct Workspace {
   // backward temporaries
   void *dx = nullptr, *dh = nullptr, *du = nullptr, *dout = nullptr, *dqkn = nullptr, *dqkv = nullptr;
   float* dkv_acc = nullptr;
+  float* drow = nullptr;           // [B*H*T] attention-backward row scratch
   // data
   long long *ids = nullptr, *targets = nullptr;
   uint16_t *d_cos = nullptr, *d_sin = nullptr;
@@ -47,6 +48,7 @@ struct Workspace {
   TensorSeg* segs = nullptr; int* chunk2seg = nullptr; float* partial = nullptr; float* normsq = nullptr;
   int nchunks = 0;
   int* heal_flags = nullptr;
+  void* tc_scratch = nullptr; size_t tc_scratch_bytes = 0; int* tc_err = nullptr;
   float* loss_record = nullptr;    // device, one per inner step of a round
   int loss_capacity = 0;
 };
@@ -92,5 +94,11 @@ struct pcpb_backend {
   float *master_shard = nullptr, *velocity = nullptr;
   long long shard_len = 0;
   bool velocity_init = false;
-  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr, tm0 = nullptr, tm1 = nullptr;
+  // tensor-core GEMM profiling
+  bool profiling = false;
+  std::vector<cudaEvent_t> prof_events;      // pairs
+  size_t prof_used = 0;
+  double prof_flops = 0.0, prof_ms = 0.0;
+  long long prof_launches = 0;
 };

@@ -1,0 +1,109 @@
+"""Tensor-core GEMM (tcgen05 / TMEM / TMA) against float64 numpy on the same bf16 inputs, all three operand
+layouts and every epilogue, plus agreement with the generic kernel.  Called through the C ABI (pcpb_op_gemm)."""
+import numpy as np
+import pytest
+
+from helpers import HD128_BF16, bf16_bits_to_f32
+from pcp_b200 import BF16, F32, Backend, NanochatConfig, nanochat_forward_mlir
+from pcp_b200.export import f32_to_bf16_rne
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf16(a):
+    bits = f32_to_bf16_rne(np.asarray(a, np.float32))
+    return bits, bf16_bits_to_f32(bits).reshape(np.shape(a))
+
+
+@pytest.fixture(scope="module")
+def be():
+    b = Backend(0)
+    b.load_session(nanochat_forward_mlir(NanochatConfig(**HD128_BF16)))
+    yield b
+    b.close()
+
+
+def _run(be, layout, M, N, K, epi, path, seed=0):
+    rng = np.random.default_rng(seed)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    bm = rng.standard_normal((K, N)).astype(np.float32)
+    if layout == "nt":       # forward: A [M,K] k-contiguous, B stored [N,K]
+        abits, av = _bf16(a); bbits, bv = _bf16(bm.T.copy()); bv = bv.T
+        sa, sb = (K, 1), (1, K)
+    elif layout == "nn":     # dgrad: A [M,K] k-contiguous, B stored [K,N]
+        abits, av = _bf16(a); bbits, bv = _bf16(bm)
+        sa, sb = (K, 1), (N, 1)
+    else:                    # "tn" wgrad: A stored [K,M], B stored [K,N]
+        abits, av = _bf16(a.T.copy()); av = av.T; bbits, bv = _bf16(bm)
+        sa, sb = (1, M), (N, 1)
+    ref = av.astype(np.float64) @ bv.astype(np.float64)
+    A = be.move_to_device(abits, abits.shape, BF16)
+    B = be.move_to_device(bbits, bbits.shape, BF16)
+    R = C2 = None
+    rv = None
+    if epi in (1, 3):
+        rbits, rv = _bf16(rng.standard_normal((M, N)))
+        R = be.move_to_device(rbits, (M, N), BF16)
+    if epi == 2:
+        C2 = be.allocate_zeros_device((M, N), BF16)
+    Cb = be.allocate_zeros_device((M, N), F32 if epi == 4 else BF16)
+    be.op_gemm(A, sa[0], sa[1], B, sb[0], sb[1], Cb, N, M, N, K, epilogue=epi, R=R, C2=C2, path=path)
+    out = be.read_to_host(Cb, F32 if epi == 4 else BF16, (M, N))
+    out = out if epi == 4 else bf16_bits_to_f32(out).reshape(M, N)
+    out2 = bf16_bits_to_f32(be.read_to_host(C2, BF16, (M, N))).reshape(M, N) if C2 else None
+    for x in (A, B, Cb, R, C2):
+        if x is not None:
+            x.release()
+    r32 = ref.astype(np.float32)
+    rb = lambda x: _bf16(x)[1]
+    if epi == 0:
+        want = rb(r32)
+    elif epi == 1:
+        want = rb(rv + rb(r32))
+    elif epi == 2:
+        want = rb(r32)
+    elif epi == 3:
+        u = rv; r = np.maximum(u, 0)
+        with np.errstate(divide="ignore", invalid="ignore"):
+            q = rb(np.where(r > 0, rb(r * r) / np.where(r > 0, r, 1), 0))
+        want = np.where(u > 0, rb(rb(r32) * rb(2 * q)), 0).astype(np.float32)
+    else:
+        want = np.clip(rb(r32), -100, 100)
+    return out, want, out2
+
+
+LAYOUTS = ["nt", "nn", "tn"]
+SHAPES = [(128, 256, 64), (256, 256, 256), (256, 768, 512), (384, 128, 192), (512, 1024, 256)]
+
+
+@pytest.mark.parametrize("layout", LAYOUTS)
+@pytest.mark.parametrize("shape", SHAPES)
+def test_tc_gemm_store(be, layout, shape):
+    M, N, K = shape
+    out, want, _ = _run(be, layout, M, N, K, epi=0, path=2)
+    # accumulation order differs from numpy: allow one bf16 ulp on the rounded result
+    np.testing.assert_allclose(out, want, rtol=2 ** -7, atol=2 ** -7 * np.sqrt(K) * 0.05)
+    assert np.abs(out - want).mean() < 2e-3 * np.sqrt(K)
+
+
+@pytest.mark.parametrize("layout,epi", [("nt", 1), ("nt", 2), ("nn", 3), ("tn", 4), ("nn", 0), ("nt", 4)])
+def test_tc_gemm_epilogues(be, layout, epi):
+    M, N, K = 256, 512, 320
+    out, want, out2 = _run(be, layout, M, N, K, epi=epi, path=2, seed=epi + 1)
+    gen, _, gen2 = _run(be, layout, M, N, K, epi=epi, path=1, seed=epi + 1)
+    np.testing.assert_allclose(out, want, rtol=2 ** -6, atol=0.15)
+    # tensor-core and generic kernels round the same f32 sums up to summation order
+    assert np.mean(out != gen) < 0.02
+    np.testing.assert_allclose(out, gen, rtol=2 ** -6, atol=0.15)
+    if epi == 2:
+        r = np.maximum(out, 0)
+        np.testing.assert_array_equal(out2, _bf16(r * r)[1])
+
+
+def test_tc_gemm_split_k(be):
+    """Weight-gradient shape: few output tiles and a long contraction -> split over CTAs with f32 slabs."""
+    M, N, K = 256, 256, 4096
+    out, want, _ = _run(be, "tn", M, N, K, epi=4, path=2, seed=11)
+    np.testing.assert_allclose(out, want, rtol=2 ** -6, atol=0.5)
+    out_b, _, _ = _run(be, "tn", M, N, K, epi=4, path=2, seed=11)
+    np.testing.assert_array_equal(out, out_b)        # deterministic: no atomics in the reduction
