@@ -75,7 +75,7 @@ def test_golden_reference_graph():
     assert rel_err(delta, gold["delta_after_2"]) <= 5e-3
     p_gpu = gold["params"] - delta
     p_ref = gold["params"] - gold["delta_after_2"]
-    np.testing.assert_allclose(p_gpu, p_ref, rtol=1e-4, atol=1e-7)
+    np.testing.assert_allclose(p_gpu, p_ref, rtol=1e-4, atol=2e-6)    # 1e-4 of the parameter scale (0.02)
 
 
 def test_fifo_batch_bit_exact():
