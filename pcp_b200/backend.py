@@ -146,14 +146,18 @@ class DeviceBuffer:
 
     def __init__(self, lib, handle, shape=None, dtype=None):
         self._lib, self.handle, self.shape, self.dtype = lib, handle, shape, dtype
+        self._refs = 1                      # references this object holds on the native buffer
 
     def retain(self):
         self._lib.pcpb_buffer_retain(self.handle)
+        self._refs += 1
 
     def release(self):
         if self.handle:
             self._lib.pcpb_buffer_release(self.handle)
-            self.handle = None
+            self._refs -= 1
+            if self._refs == 0:
+                self.handle = None
 
     def byte_length(self):
         return self._lib.pcpb_buffer_nbytes(self.handle)
