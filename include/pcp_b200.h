@@ -186,6 +186,29 @@ int pcpb_timer_stop(pcpb_backend* b, double* ms);
 int pcpb_profile_enable(pcpb_backend* b, int on);
 int pcpb_profile_read(pcpb_backend* b, long long* launches, double* total_ms, double* total_flops);
 
+/* AdamW step that allocates nothing.  It has no counterpart in the reference; it exists for hosts that cannot
+ * let a library allocate device memory on their behalf: runtimes that give out slices of one arena reserved up
+ * front and account for every byte (the reference's worker runs on such a runtime, the IREE HAL allocator with its
+ * allocation cap), and services whose step loop rules out allocation calls because they synchronise the device.
+ * The regular apply_optimizer entry allocates its outputs and a descriptor table per call; this one works on
+ * tensors the caller owns and keeps its reduction scratch in a fixed array inside the library image.
+ *
+ *   p, g, m, v        device pointers, n f32 elements each (one tensor); p_out, m_out, v_out receive the update
+ *                     (they may alias p, m, v)
+ *   stream            a cudaStream_t, or NULL for the default stream; the call enqueues and returns, it does not wait
+ *   conf, timestep    as pcpb_set_adam / the f32 step counter of apply_optimizer (1.0 at the first step)
+ *   err, err_cap      optional buffer for the error text
+ *
+ * n may not exceed PCPB_NOALLOC_MAX_ELEMS (PCPB_E_TOO_LARGE otherwise).  The scratch array (about 64 KB) is held
+ * by every GPU that loads the library until the process exits.  All calls share it and it keeps what the last call
+ * left: the call re-initialises everything it reads, but two calls whose GPU work overlaps race on it, so callers
+ * serialise them.  The first call on a device (the current device of the calling thread) looks up the array's
+ * device address once; make that first call before beginning any stream capture. */
+#define PCPB_NOALLOC_MAX_ELEMS (1ll << 26)
+int pcpb_adamw_step_noalloc(void* stream, const float* p, const float* g, const float* m, const float* v, float* p_out,
+                            float* m_out, float* v_out, long long n, const pcpb_adam_conf* conf, float timestep,
+                            char* err, size_t err_cap);
+
 /* Kernel counters of this backend: launches enqueued since creation, by the library's own kernels. */
 long long pcpb_launch_count(const pcpb_backend* b);
 

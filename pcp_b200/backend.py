@@ -41,7 +41,7 @@ EXPORTS = [
     "pcpb_worker_end_round", "pcpb_inner_loop", "pcpb_worker_read_state", "pcpb_synchronize", "pcpb_outer_export",
     "pcpb_outer_attach_ipc", "pcpb_outer_attach_local", "pcpb_outer_prepare", "pcpb_outer_apply",
     "pcpb_launch_count", "pcpb_worker_last_loss", "pcpb_timer_start", "pcpb_timer_stop", "pcpb_profile_enable",
-    "pcpb_profile_read",
+    "pcpb_profile_read", "pcpb_adamw_step_noalloc",
 ]
 
 
@@ -122,6 +122,8 @@ def load_library(path: str | None = None):
     lib.pcpb_timer_stop.argtypes = [vp, C.POINTER(C.c_double)]
     lib.pcpb_profile_enable.argtypes = [vp, i]
     lib.pcpb_profile_read.argtypes = [vp, C.POINTER(C.c_longlong), C.POINTER(C.c_double), C.POINTER(C.c_double)]
+    lib.pcpb_adamw_step_noalloc.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ll, C.POINTER(AdamConf), C.c_float,
+                                            C.c_char_p, sz]
     if path is None:
         _lib = lib
     return lib
@@ -139,6 +141,19 @@ def inspect_artifact(artifact) -> dict:
     keys = ["vocab", "d_model", "n_layer", "n_head", "n_kv_head", "head_dim", "d_ff", "batch", "block", "dtype",
             "num_tensors", "total_params"]
     return dict(zip(keys, [int(x) for x in facts]))
+
+
+NOALLOC_MAX_ELEMS = 1 << 26
+
+
+def adamw_step_noalloc(p, g, m, v, p_out, m_out, v_out, n, conf: AdamConf, timestep: float, stream=None):
+    """AdamW on caller-owned device memory without any allocation (see include/pcp_b200.h).  Arguments are raw
+    device addresses (ints); `stream` a cudaStream_t value or None.  The work is enqueued, not waited for."""
+    lib = load_library()
+    err = C.create_string_buffer(256)
+    rc = lib.pcpb_adamw_step_noalloc(stream, p, g, m, v, p_out, m_out, v_out, n, C.byref(conf), timestep, err, 256)
+    if rc:
+        raise BackendError(rc, err.value.decode())
 
 
 class DeviceBuffer:
