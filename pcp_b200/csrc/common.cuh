@@ -70,6 +70,43 @@ __device__ __forceinline__ float block_max(float v, float* red) {
   return r;
 }
 
+// 8-element vector access (16 bytes of bf16, 32 bytes of f32); p must be 16-byte aligned.
+template <typename T> __device__ __forceinline__ void ld8(const T* p, float (&f)[8]);
+template <> __device__ __forceinline__ void ld8<float>(const float* p, float (&f)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+template <> __device__ __forceinline__ void ld8<bf16>(const bf16* p, float (&f)[8]) {
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+}
+template <typename T> __device__ __forceinline__ void st8(T* p, const float (&f)[8]);
+template <> __device__ __forceinline__ void st8<float>(float* p, const float (&f)[8]) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(f[0], f[1], f[2], f[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
+}
+template <> __device__ __forceinline__ void st8<bf16>(bf16* p, const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162 h;
+  h = __floats2bfloat162_rn(f[0], f[1]); v.x = *reinterpret_cast<uint32_t*>(&h);
+  h = __floats2bfloat162_rn(f[2], f[3]); v.y = *reinterpret_cast<uint32_t*>(&h);
+  h = __floats2bfloat162_rn(f[4], f[5]); v.z = *reinterpret_cast<uint32_t*>(&h);
+  h = __floats2bfloat162_rn(f[6], f[7]); v.w = *reinterpret_cast<uint32_t*>(&h);
+  *reinterpret_cast<uint4*>(p) = v;
+}
+
+// Transcendentals: accurate for f32 models (1e-4 parity), hardware approximations for bf16 models.
+template <typename T> __device__ __forceinline__ float m_tanh(float x) { return tanhf(x); }
+template <> __device__ __forceinline__ float m_tanh<bf16>(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+template <typename T> __device__ __forceinline__ float m_exp(float x) { return expf(x); }
+template <> __device__ __forceinline__ float m_exp<bf16>(float x) { return __expf(x); }
+
 // Guard constant the reference adds to every divide / log denominator in the forward graph
 // (src/compiler/sanitizer.zig:8-111) and again inside the divide / log / rsqrt VJP rules
 // (src/autodiff/vjp_rules.zig:198,1510,1543).

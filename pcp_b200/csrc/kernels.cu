@@ -149,22 +149,131 @@ __global__ void k_embed_norm_bwd(const T* __restrict__ wte, const long long* __r
   }
 }
 
+
+// ---- vectorised variants: one warp per row, 16-byte accesses, used when d % 8 == 0 ------------------
+template <typename T>
+__global__ void __launch_bounds__(256) k_rmsnorm_fwd_vec(const T* __restrict__ x, const T* __restrict__ wte,
+                                                         const long long* __restrict__ idx, int M, int d, int V,
+                                                         T* __restrict__ y, float* __restrict__ tsave) {
+  const int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (m >= M) return;
+  const T* xr;
+  if (idx) {
+    long long row = idx[m];
+    row = row < 0 ? 0 : (row >= V ? V - 1 : row);
+    xr = wte + (size_t)row * d;
+  } else {
+    xr = x + (size_t)m * d;
+  }
+  const int nv = d >> 3;
+  float ss = 0.f;
+  for (int v = lane; v < nv; v += 32) {
+    float f[8];
+    ld8<T>(xr + v * 8, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+  }
+  ss = warp_sum(ss);
+  const float t = ss / ((float)d + PCPB_GUARD) + 1e-5f;
+  const float r = rnd<T>(rsqrtf(t));
+  if (lane == 0 && tsave) tsave[m] = t;
+  T* yr = y + (size_t)m * d;
+  for (int v = lane; v < nv; v += 32) {
+    float f[8];
+    ld8<T>(xr + v * 8, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] *= r;
+    st8<T>(yr + v * 8, f);
+  }
+}
+
+// dwte != nullptr: embedding variant (x rows come from wte[idx], gradient rows are atomically added to dwte)
+template <typename T>
+__global__ void __launch_bounds__(256) k_rmsnorm_bwd_vec(const T* __restrict__ x, const T* __restrict__ wte,
+                                                         const long long* __restrict__ idx, const float* __restrict__ tsave,
+                                                         const T* __restrict__ dy, const T* __restrict__ dres, int M, int d,
+                                                         int V, T* __restrict__ dx, float* __restrict__ dwte) {
+  const int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (m >= M) return;
+  const T* xr;
+  long long row = 0;
+  if (idx) {
+    row = idx[m];
+    row = row < 0 ? 0 : (row >= V ? V - 1 : row);
+    xr = wte + (size_t)row * d;
+  } else {
+    xr = x + (size_t)m * d;
+  }
+  const T* dyr = dy + (size_t)m * d;
+  const int nv = d >> 3;
+  float acc = 0.f;
+  for (int v = lane; v < nv; v += 32) {
+    float a[8], g[8];
+    ld8<T>(xr + v * 8, a);
+    ld8<T>(dyr + v * 8, g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc += rnd<T>(g[i] * a[i]);
+  }
+  acc = warp_sum(acc);
+  const float t = tsave[m];
+  const float dr = rnd<T>(acc);
+  const float rp = rsqrtf(t + PCPB_GUARD);
+  const float ds = ((dr * -0.5f) * ((rp * rp) * rp)) / (((float)d + PCPB_GUARD) + PCPB_GUARD);
+  const float r = rnd<T>(rsqrtf(t));
+  for (int v = lane; v < nv; v += 32) {
+    float a[8], g[8], o[8];
+    ld8<T>(xr + v * 8, a);
+    ld8<T>(dyr + v * 8, g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = rnd<T>(g[i] * r) + rnd<T>(ds * (2.f * a[i]));
+    if (dwte) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) atomicAdd(dwte + (size_t)row * d + v * 8 + i, rnd<T>(o[i]));
+    } else {
+      if (dres) {
+        float e[8];
+        ld8<T>(dres + (size_t)m * d + v * 8, e);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] += e[i];
+      }
+      st8<T>(dx + (size_t)m * d + v * 8, o);
+    }
+  }
+}
+
+static inline bool vec_ok(int d, const void* a, const void* b = nullptr, const void* c = nullptr, const void* e = nullptr) {
+  return d % 8 == 0 && ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)c) | ((uintptr_t)e)) & 15) == 0;
+}
+
 static inline int norm_threads(int d) { return d >= 1024 ? 256 : (d >= 256 ? 128 : 64); }
 
 cudaError_t launch_rmsnorm_fwd(cudaStream_t st, int dt, const void* x, int M, int d, void* y, float* tsave) {
   if (M == 0) return cudaSuccess;
+  if (vec_ok(d, x, y)) {
+    DISPATCH_DT(dt, (k_rmsnorm_fwd_vec<T><<<cdiv(M, 8), 256, 0, st>>>((const T*)x, nullptr, nullptr, M, d, 0, (T*)y, tsave)));
+    return cudaGetLastError();
+  }
   DISPATCH_DT(dt, (k_rmsnorm_fwd<T><<<M, norm_threads(d), 0, st>>>((const T*)x, d, (T*)y, tsave)));
   return cudaGetLastError();
 }
 cudaError_t launch_embed_norm_fwd(cudaStream_t st, int dt, const void* wte, const long long* idx, int M, int d,
                                   int V, void* x, float* tsave) {
   if (M == 0) return cudaSuccess;
+  if (vec_ok(d, wte, x)) {
+    DISPATCH_DT(dt, (k_rmsnorm_fwd_vec<T><<<cdiv(M, 8), 256, 0, st>>>(nullptr, (const T*)wte, idx, M, d, V, (T*)x, tsave)));
+    return cudaGetLastError();
+  }
   DISPATCH_DT(dt, (k_embed_norm_fwd<T><<<M, norm_threads(d), 0, st>>>((const T*)wte, idx, d, V, (T*)x, tsave)));
   return cudaGetLastError();
 }
 cudaError_t launch_rmsnorm_bwd(cudaStream_t st, int dt, const void* x, const float* tsave, const void* dy,
                                const void* dres, int M, int d, void* dx) {
   if (M == 0) return cudaSuccess;
+  if (vec_ok(d, x, dy, dres, dx)) {
+    DISPATCH_DT(dt, (k_rmsnorm_bwd_vec<T><<<cdiv(M, 8), 256, 0, st>>>((const T*)x, nullptr, nullptr, tsave, (const T*)dy,
+                                                                    (const T*)dres, M, d, 0, (T*)dx, nullptr)));
+    return cudaGetLastError();
+  }
   DISPATCH_DT(dt, (k_rmsnorm_bwd<T><<<M, norm_threads(d), 0, st>>>((const T*)x, tsave, (const T*)dy,
                                                                     (const T*)dres, d, (T*)dx)));
   return cudaGetLastError();
@@ -172,6 +281,11 @@ cudaError_t launch_rmsnorm_bwd(cudaStream_t st, int dt, const void* x, const flo
 cudaError_t launch_embed_norm_bwd(cudaStream_t st, int dt, const void* wte, const long long* idx, int M, int d,
                                   int V, const void* dy, const float* tsave, float* dwte) {
   if (M == 0) return cudaSuccess;
+  if (vec_ok(d, wte, dy)) {
+    DISPATCH_DT(dt, (k_rmsnorm_bwd_vec<T><<<cdiv(M, 8), 256, 0, st>>>(nullptr, (const T*)wte, idx, tsave, (const T*)dy,
+                                                                    nullptr, M, d, V, nullptr, dwte)));
+    return cudaGetLastError();
+  }
   DISPATCH_DT(dt, (k_embed_norm_bwd<T><<<M, norm_threads(d), 0, st>>>((const T*)wte, idx, d, V, (const T*)dy,
                                                                        tsave, dwte)));
   return cudaGetLastError();
@@ -266,10 +380,117 @@ __global__ void k_rope_qknorm_bwd(const T* __restrict__ qkv, const T* __restrict
   }
 }
 
+
+// ---- vectorised RoPE + QK-norm: each thread owns 8 rotation pairs; hd/16 threads per head ---------------
+template <typename T>
+__device__ __forceinline__ void rope8(const float (&x1)[8], const float (&x2)[8], const float (&c)[8], const float (&s)[8],
+                                      float (&y1)[8], float (&y2)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    y1[i] = rnd<T>(rnd<T>(x1[i] * c[i]) + rnd<T>(x2[i] * s[i]));
+    y2[i] = rnd<T>(rnd<T>(x1[i] * (-s[i])) + rnd<T>(x2[i] * c[i]));
+  }
+}
+__device__ __forceinline__ float group_sum(float v, int tph) {
+  for (int o = tph >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) k_rope_qknorm_fwd_vec(const T* __restrict__ qkv, const uint16_t* __restrict__ cosT,
+                                                             const uint16_t* __restrict__ sinT, int M, int Tlen, int H,
+                                                             int Hkv, int hd, T* __restrict__ qkn, float* __restrict__ tq) {
+  const int heads = H + Hkv, half = hd >> 1, tph = half >> 3;
+  const long long gt = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long slot = gt / tph;
+  const int sub = (int)(gt % tph);
+  const bool live = slot < (long long)M * heads;
+  const int m = live ? (int)(slot / heads) : 0, h = live ? (int)(slot % heads) : 0;
+  const T* src = qkv + (size_t)m * ((H + 2 * Hkv) * hd) + (size_t)h * hd + sub * 8;
+  const int pos = m % Tlen;
+  float x1[8], x2[8], c[8], s[8], y1[8], y2[8];
+  ld8<T>(src, x1);
+  ld8<T>(src + half, x2);
+  ld8<bf16>(reinterpret_cast<const bf16*>(cosT) + (size_t)pos * half + sub * 8, c);
+  ld8<bf16>(reinterpret_cast<const bf16*>(sinT) + (size_t)pos * half + sub * 8, s);
+  rope8<T>(x1, x2, c, s, y1, y2);
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ss += y1[i] * y1[i] + y2[i] * y2[i];
+  ss = group_sum(ss, tph);
+  const float t = ss / ((float)hd + PCPB_GUARD) + 1e-5f;
+  const float r = rnd<T>(rsqrtf(t));
+  if (!live) return;
+  if (sub == 0) tq[(size_t)m * heads + h] = t;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { y1[i] *= r; y2[i] *= r; }
+  T* dst = qkn + (size_t)m * (heads * hd) + (size_t)h * hd + sub * 8;
+  st8<T>(dst, y1);
+  st8<T>(dst + half, y2);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) k_rope_qknorm_bwd_vec(const T* __restrict__ qkv, const T* __restrict__ dqkn,
+                                                             const float* __restrict__ tq, const uint16_t* __restrict__ cosT,
+                                                             const uint16_t* __restrict__ sinT, int M, int Tlen, int H, int Hkv,
+                                                             int hd, T* __restrict__ dqkv) {
+  const int heads = H + Hkv, half = hd >> 1, tph = half >> 3;
+  const long long gt = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long slot = gt / tph;
+  const int sub = (int)(gt % tph);
+  const bool live = slot < (long long)M * heads;
+  const int m = live ? (int)(slot / heads) : 0, h = live ? (int)(slot % heads) : 0;
+  const size_t wqkv = (size_t)(H + 2 * Hkv) * hd;
+  const T* src = qkv + (size_t)m * wqkv + (size_t)h * hd + sub * 8;
+  const T* dyp = dqkn + (size_t)m * (heads * hd) + (size_t)h * hd + sub * 8;
+  const int pos = m % Tlen;
+  float x1[8], x2[8], c[8], s[8], y1[8], y2[8], d1[8], d2[8];
+  ld8<T>(src, x1);
+  ld8<T>(src + half, x2);
+  ld8<bf16>(reinterpret_cast<const bf16*>(cosT) + (size_t)pos * half + sub * 8, c);
+  ld8<bf16>(reinterpret_cast<const bf16*>(sinT) + (size_t)pos * half + sub * 8, s);
+  ld8<T>(dyp, d1);
+  ld8<T>(dyp + half, d2);
+  rope8<T>(x1, x2, c, s, y1, y2);
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc += rnd<T>(d1[i] * y1[i]) + rnd<T>(d2[i] * y2[i]);
+  acc = group_sum(acc, tph);
+  const float t = tq[(size_t)m * heads + h];
+  const float dr = rnd<T>(acc);
+  const float rp = rsqrtf(t + PCPB_GUARD);
+  const float ds = ((dr * -0.5f) * ((rp * rp) * rp)) / (((float)hd + PCPB_GUARD) + PCPB_GUARD);
+  const float r = rnd<T>(rsqrtf(t));
+  if (!live) return;
+  float o1[8], o2[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float g1 = rnd<T>(rnd<T>(d1[i] * r) + rnd<T>(ds * (2.f * y1[i])));
+    const float g2 = rnd<T>(rnd<T>(d2[i] * r) + rnd<T>(ds * (2.f * y2[i])));
+    o1[i] = rnd<T>(g1 * c[i]) + rnd<T>(g2 * (-s[i]));
+    o2[i] = rnd<T>(g1 * s[i]) + rnd<T>(g2 * c[i]);
+  }
+  T* dst = dqkv + (size_t)m * wqkv + (size_t)h * hd + sub * 8;
+  st8<T>(dst, o1);
+  st8<T>(dst + half, o2);
+}
+
+static inline bool rope_vec_ok(int hd, const void* a, const void* b, const void* c, const void* d) {
+  const int tph = hd / 16;
+  return hd % 16 == 0 && tph >= 1 && tph <= 32 && (tph & (tph - 1)) == 0 &&
+         ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)c) | ((uintptr_t)d)) & 15) == 0;
+}
+
 cudaError_t launch_rope_qknorm_fwd(cudaStream_t st, int dt, const void* qkv, const uint16_t* c, const uint16_t* s,
                                    int M, int Tlen, int H, int Hkv, int hd, void* qkn, float* tq) {
   const long long warps = (long long)M * (H + Hkv);
   if (warps == 0) return cudaSuccess;
+  if (rope_vec_ok(hd, qkv, qkn, c, s)) {
+    const long long threads = warps * (hd / 16);
+    DISPATCH_DT(dt, (k_rope_qknorm_fwd_vec<T><<<cdiv(threads, 256), 256, 0, st>>>((const T*)qkv, c, s, M, Tlen, H, Hkv, hd,
+                                                                                  (T*)qkn, tq)));
+    return cudaGetLastError();
+  }
   DISPATCH_DT(dt, (k_rope_qknorm_fwd<T><<<cdiv(warps * 32, 256), 256, 0, st>>>((const T*)qkv, c, s, M, Tlen, H, Hkv,
                                                                                 hd, (T*)qkn, tq)));
   return cudaGetLastError();
@@ -279,6 +500,12 @@ cudaError_t launch_rope_qknorm_bwd(cudaStream_t st, int dt, const void* qkv, con
                                    void* dqkv) {
   const long long warps = (long long)M * (H + Hkv);
   if (warps == 0) return cudaSuccess;
+  if (rope_vec_ok(hd, qkv, dqkn, dqkv, c) && (((uintptr_t)s) & 15) == 0) {
+    const long long threads = warps * (hd / 16);
+    DISPATCH_DT(dt, (k_rope_qknorm_bwd_vec<T><<<cdiv(threads, 256), 256, 0, st>>>((const T*)qkv, (const T*)dqkn, tq, c, s, M,
+                                                                                  Tlen, H, Hkv, hd, (T*)dqkv)));
+    return cudaGetLastError();
+  }
   DISPATCH_DT(dt, (k_rope_qknorm_bwd<T><<<cdiv(warps * 32, 256), 256, 0, st>>>((const T*)qkv, (const T*)dqkn, tq, c,
                                                                                 s, M, Tlen, H, Hkv, hd, (T*)dqkv)));
   return cudaGetLastError();
@@ -598,9 +825,75 @@ __global__ void __launch_bounds__(256) k_softcap_ce(T* __restrict__ logits, cons
     z[j] = from_f<T>(dc * dzscale * (1.f - th * th));
   }
 }
+
+// Vectorised variant (V % 8 == 0): online max / sum in one pass over the row, gradient in a second pass.
+template <typename T>
+__global__ void __launch_bounds__(512) k_softcap_ce_vec(T* __restrict__ logits, const long long* __restrict__ tg, int V,
+                                                        float cap, long long ignore, const float* __restrict__ count,
+                                                        float* __restrict__ rowloss, int write_grad) {
+  __shared__ float red[32];
+  const size_t m = blockIdx.x;
+  T* z = logits + m * V;
+  const long long t = tg[m];
+  const bool valid = (t != ignore);
+  const float capg = cap + PCPB_GUARD, icapg = 1.f / capg;
+  const int nv = V >> 3;
+  float mx = -INFINITY, se = 0.f;
+  for (int v = threadIdx.x; v < nv; v += blockDim.x) {
+    float f[8];
+    ld8<T>(z + v * 8, f);
+    float c[8], cm = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      c[i] = m_tanh<T>(sizeof(T) == 4 ? f[i] / capg : f[i] * icapg) * cap;
+      cm = fmaxf(cm, c[i]);
+    }
+    if (cm > mx) { se *= m_exp<T>(mx - cm); mx = cm; }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) se += m_exp<T>(c[i] - mx);
+  }
+  const float gmx = block_max(mx, red);
+  se *= (mx == -INFINITY) ? 0.f : m_exp<T>(mx - gmx);
+  se = block_sum(se, red);
+  mx = gmx;
+  if (threadIdx.x == 0) {
+    float nll = 0.f;
+    if (valid) {
+      long long tt = t < 0 ? 0 : (t >= V ? V - 1 : t);
+      const float zt = to_f(z[tt]);
+      const float c = m_tanh<T>(sizeof(T) == 4 ? zt / capg : zt * icapg) * cap;
+      nll = -((c - mx) - logf(se + PCPB_GUARD));
+    }
+    rowloss[m] = nll;
+  }
+  if (!write_grad) return;
+  __syncthreads();                                  // the target logit was read above before anyone overwrites it
+  const float dtot = valid ? 1.f / (*count + 2.f * PCPB_GUARD) : 0.f;
+  const float iden = 1.f / (se + 2.f * PCPB_GUARD);
+  const float dzscale = cap / (capg + PCPB_GUARD);
+  for (int v = threadIdx.x; v < nv; v += blockDim.x) {
+    float f[8], o[8];
+    ld8<T>(z + v * 8, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float th = m_tanh<T>(sizeof(T) == 4 ? f[i] / capg : f[i] * icapg);
+      const float c = th * cap;
+      float dc = m_exp<T>(c - mx) * iden;
+      if ((long long)(v * 8 + i) == t) dc -= 1.f;
+      if (c == mx) dc += (2.f * PCPB_GUARD) * iden;
+      o[i] = dc * dtot * dzscale * (1.f - th * th);
+    }
+    st8<T>(z + v * 8, o);
+  }
+}
 cudaError_t launch_softcap_ce(cudaStream_t st, int dt, void* logits, const long long* targets, int M, int V,
                               float cap, long long ignore, const float* count, float* rowloss, int write_grad) {
   if (M == 0) return cudaSuccess;
+  if (V % 8 == 0 && (((uintptr_t)logits) & 15) == 0) {
+    const int threads = V >= 16384 ? 512 : 128;
+    DISPATCH_DT(dt, (k_softcap_ce_vec<T><<<M, threads, 0, st>>>((T*)logits, targets, V, cap, ignore, count, rowloss, write_grad)));
+    return cudaGetLastError();
+  }
   DISPATCH_DT(dt, (k_softcap_ce<T><<<M, 256, 0, st>>>((T*)logits, targets, V, cap, ignore, count, rowloss, write_grad)));
   return cudaGetLastError();
 }
