@@ -9,6 +9,7 @@
 #include "../../include/pcp_b200.h"
 #include "common.cuh"
 #include "attn_flash.h"
+#include "attn_tc.h"
 #include "gemm_tc.h"
 
 using namespace pcpb;
@@ -165,7 +166,7 @@ int check_tc_error(pcpb_backend* b) {
   CK(b, cudaMemcpy(&code, b->ws.tc_err, sizeof(int), cudaMemcpyDeviceToHost));
   if (code) {
     cudaMemset(b->ws.tc_err, 0, sizeof(int));
-    return fail(b, PCPB_E_CUDA, "tensor-core GEMM gave up waiting on a barrier (role " + std::to_string(code) + "); results of this call are invalid");
+    return fail(b, PCPB_E_CUDA, "a tensor-core kernel gave up waiting on a barrier (role " + std::to_string(code) + "); results of this call are invalid");
   }
   return PCPB_OK;
 }
@@ -250,8 +251,10 @@ int forward_backward(pcpb_backend* b, const void* wts, const long long* ids, con
     FlashArgs fa{};
     fa.qkn = a.qkn; fa.qkv = a.qkv; fa.o = a.o; fa.mrow = a.mrow; fa.lrow = a.lrow;
     fa.B = (int)c.B; fa.T = Tn; fa.H = H; fa.Hkv = Hkv; fa.hd = hd; fa.scale = scale;
-    const bool flash = !b->force_generic && dt == DT_BF16 && flash_supported(fa);
-    if (flash) {
+    const bool fast = !b->force_generic && dt == DT_BF16 && b->attn_path != 2;
+    if (fast && b->attn_path == 0 && attn_tc_supported(fa)) {
+      KL(b, 1, launch_attn_tc_fwd(st, fa, w.tc_err));
+    } else if (fast && flash_supported(fa)) {
       KL(b, 1, launch_flash_fwd(st, fa));
     } else {
       AttnArgs at{};
@@ -293,7 +296,10 @@ int forward_backward(pcpb_backend* b, const void* wts, const long long* ids, con
     fa.qkn = a.qkn; fa.qkv = a.qkv; fa.o = a.o; fa.mrow = a.mrow; fa.lrow = a.lrow;
     fa.B = (int)c.B; fa.T = Tn; fa.H = H; fa.Hkv = Hkv; fa.hd = hd; fa.scale = scale;
     fa.dout = w.dout; fa.dqkn = w.dqkn; fa.dqkv = w.dqkv; fa.drow = w.drow;
-    if (!b->force_generic && dt == DT_BF16 && flash_supported(fa)) {
+    const bool fast = !b->force_generic && dt == DT_BF16 && b->attn_path != 2;
+    if (fast && b->attn_path == 0 && attn_tc_supported(fa)) {
+      KL(b, 3, launch_attn_tc_bwd(st, fa, w.tc_err));
+    } else if (fast && flash_supported(fa)) {
       KL(b, 3, launch_flash_bwd(st, fa));
     } else {
       AttnArgs at{};
@@ -344,6 +350,8 @@ int pcpb_create(int device_ordinal, pcpb_backend** out) {
   b->adam.max_norm = 1.0f; b->adam.m_corr = b->adam.v_corr = 1.f;
   const char* fg = getenv("PCPB_FORCE_GENERIC");
   b->force_generic = fg && fg[0] == '1';
+  const char* ap = getenv("PCPB_ATTN");                 // "flash": mma.sync kernels, "generic": SIMT kernels
+  b->attn_path = (ap && !strcmp(ap, "flash")) ? 1 : ((ap && !strcmp(ap, "generic")) ? 2 : 0);
   *out = b;                       // returned even on failure so that the message can be read
   if (e != cudaSuccess || ndev == 0)
     return fail(b, PCPB_E_CUDA, std::string("no CUDA device: ") + cudaGetErrorString(e));

@@ -77,6 +77,7 @@ struct pcpb_backend {
   pcpb::AdamHyper adam;
   long long launches = 0;
   bool force_generic = false;
+  int attn_path = 0;                         // 0 auto (tcgen05, else mma.sync, else generic), 1 mma.sync, 2 generic
   // worker round state
   bool in_round = false;
   int tau = 0, accumulation_steps = 1, param_dtype = 0, persist_adam = 0, tokens_on_device = 0;

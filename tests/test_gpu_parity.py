@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import (GQA_F32, HD128_BF16, HD128_F32, SMALL_BF16, SMALL_F32, bf16_bits_to_f32, f32_to_bf16_trunc_bits,
+from helpers import (GQA_F32, HD128_BF16, HD128_F32, HD128_GQA_BF16, SMALL_BF16, SMALL_F32, bf16_bits_to_f32, f32_to_bf16_trunc_bits,
                      flat, rel_err, seeded_params, split, tokens_for)
 from oracle.loader import FifoU16
 from oracle.optim import AdamConf, NesterovConf, adamw_update
@@ -53,6 +53,30 @@ def test_compute_gradients_matches_oracle(cfgd, tol):
     worst = max(rel_err(a, b.numpy()) for a, b in zip(g, g_ref))
     # per-tensor max error relative to the tensor's largest gradient
     assert worst <= (1e-4 if cfg.dtype == "f32" else 4e-2), worst
+
+
+@pytest.mark.parametrize("cfgd", [HD128_BF16, HD128_GQA_BF16])
+def test_attention_paths_agree(cfgd, monkeypatch):
+    """The three attention implementations (tcgen05 / tensor memory, mma.sync, generic) against the oracle and against
+    each other on a head_dim-128 bf16 model, GQA included."""
+    cfg = NanochatConfig(**cfgd)
+    text = nanochat_forward_mlir(cfg)
+    params = seeded_params(cfg, seed=3, std=0.05)
+    x, y = FifoU16(tokens_for(cfg, 1, seed=2)).get_batch(cfg.batch, cfg.seq_len)
+    g_ref, loss_ref = TrainingModule(text).compute_gradients(params, torch.from_numpy(x), torch.from_numpy(y))
+    res = {}
+    for path in ("", "flash", "generic"):
+        monkeypatch.setenv("PCPB_ATTN", path)
+        with Backend(0) as be:
+            be.load_session(text)
+            res[path] = _grads_via_abi(be, cfg, params, x, y)
+    for path, (g, loss) in res.items():
+        assert abs(loss - float(loss_ref)) <= 2e-2 * abs(float(loss_ref)), path
+        assert max(rel_err(a, b.numpy()) for a, b in zip(g, g_ref)) <= 4e-2, path
+    # the two tensor-core paths differ from the generic kernel only by bf16 rounding points
+    for path in ("", "flash"):
+        assert abs(res[path][1] - res["generic"][1]) <= 2e-3 * abs(res["generic"][1])
+        assert max(rel_err(a, b) for a, b in zip(res[path][0], res["generic"][0])) <= 3e-2, path
 
 
 def test_golden_reference_graph():
