@@ -8,8 +8,8 @@
 //   dQ        rows = queries; per sub-tile of keys:  S = Q K^T, dP = dO V^T  ->  dS  ->  dQ += dS K
 //   dK, dV    rows = keys;    per sub-tile of queries: S^T = K Q^T, dP^T = V dO^T -> P^T, dS^T
 //                                                       -> dV += P^T dO, dK += dS^T Q
-// Warp roles (192 threads): warp 0 TMA producer (3-stage ring of sub-tile pairs), warp 1 MMA issuer and owner of the
-// tensor-memory allocation, warps 2-5 element-wise: each thread owns one row, reads its 64 score values with
+// Warp roles (320 threads): warp 0 TMA producer (3-stage ring of sub-tile pairs), warp 1 MMA issuer and owner of the
+// tensor-memory allocation, warps 2-9 element-wise: each thread owns one row and half of the 64 score columns, reads them with
 // tcgen05.ld, does the softmax / softmax-backward arithmetic and writes the bf16 result into a 128-byte-swizzled
 // shared-memory tile that the next MMA consumes as its A operand.  Score tiles are double-buffered in tensor memory
 // so the MMAs of sub-tile i+1 overlap the arithmetic of sub-tile i.
@@ -50,7 +50,7 @@ struct AtcParams {
 template <int MODE> struct AtcCfg {
   static constexpr int N_RES = (MODE == MODE_FWD) ? 1 : 2;
   static constexpr int N_E = (MODE == MODE_DKV) ? 2 : 1;
-  static constexpr int STAT_BYTES = (MODE == MODE_DKV) ? 4 * 2 * 320 * 4 : 0;   // per warp, double-buffered
+  static constexpr int STAT_BYTES = (MODE == MODE_DKV) ? 8 * 2 * 160 * 4 : 2 * 128 * 2 * 4;   // DKV: per warp, double-buffered; FWD: row-half exchange
   static constexpr int OFF_RING = N_RES * TILE_BYTES;
   static constexpr int OFF_E = OFF_RING + NST * STAGE_BYTES;
   static constexpr int OFF_STAT = OFF_E + N_E * E_BYTES;
@@ -63,7 +63,13 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ float r16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+// f32 -> bf16 precision, round to nearest even, on the integer pipe (the conversion unit is the bottleneck of the
+// element-wise warps; inputs are finite or +-inf)
+__device__ __forceinline__ float r16(float x) {
+  uint32_t u = __float_as_uint(x);
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return __uint_as_float(u & 0xFFFF0000u);
+}
 
 // Write 32 consecutive k-values (columns c0 .. c0+31 of row r) of a [128 x 64] bf16 A-operand tile (one 128-byte
 // swizzle atom per row: 16-byte chunk j of row r lives at chunk position j ^ (r & 7)).
@@ -78,26 +84,26 @@ __device__ __forceinline__ void store_e32(uint32_t ebase, int r, int c0, const f
   }
 }
 
-// Store one output row (128 f32 accumulators in tensor memory at taddr) as bf16 to dst.
-__device__ __forceinline__ void store_out_row(uint32_t taddr, bf16* dst, float mul) {
+// Store 64 consecutive output columns of one row (f32 accumulators in tensor memory at taddr) as bf16 to dst.
+__device__ __forceinline__ void store_out_cols(uint32_t taddr, bf16* dst) {
 #pragma unroll 1
-  for (int c = 0; c < HD; c += 32) {
+  for (int c = 0; c < 64; c += 32) {
     uint32_t r[32];
     tmem_ld32(taddr + (uint32_t)c, r);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       uint4 v;
-      v.x = pack2(__uint_as_float(r[8 * j + 0]) * mul, __uint_as_float(r[8 * j + 1]) * mul);
-      v.y = pack2(__uint_as_float(r[8 * j + 2]) * mul, __uint_as_float(r[8 * j + 3]) * mul);
-      v.z = pack2(__uint_as_float(r[8 * j + 4]) * mul, __uint_as_float(r[8 * j + 5]) * mul);
-      v.w = pack2(__uint_as_float(r[8 * j + 6]) * mul, __uint_as_float(r[8 * j + 7]) * mul);
+      v.x = pack2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+      v.y = pack2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+      v.z = pack2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+      v.w = pack2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
       *reinterpret_cast<uint4*>(dst + c + 8 * j) = v;
     }
   }
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CUtensorMap tm_qkv,
           const __grid_constant__ CUtensorMap tm_do, const AtcParams p) {
   using Cfg = AtcCfg<MODE>;
@@ -111,8 +117,8 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
   auto tfull_bar = [&](int b) { return sBar + 8u * (2 * NST + b); };
   auto tempty_bar = [&](int b) { return sBar + 8u * (2 * NST + 2 + b); };
   const uint32_t efull_bar = sBar + 8u * (2 * NST + 4), eempty_bar = efull_bar + 8, out_bar = efull_bar + 16,
-                 res_bar = efull_bar + 24, tmem_slot = efull_bar + 32;
-  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + Cfg::OFF_BAR + 8 * (2 * NST + 4) + 32);
+                 res_bar = efull_bar + 24, comb_bar = efull_bar + 32, tmem_slot = efull_bar + 40;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + Cfg::OFF_BAR + 8 * (2 * NST + 4) + 40);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int grp = p.H / p.Hkv;
@@ -136,8 +142,8 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NST; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int t = 0; t < 2; ++t) { mbar_init(tfull_bar(t), 1); mbar_init(tempty_bar(t), 4); }
-    mbar_init(efull_bar, 4); mbar_init(eempty_bar, 1); mbar_init(out_bar, 1); mbar_init(res_bar, 1);
+    for (int t = 0; t < 2; ++t) { mbar_init(tfull_bar(t), 1); mbar_init(tempty_bar(t), 8); }
+    mbar_init(efull_bar, 8); mbar_init(eempty_bar, 1); mbar_init(out_bar, 1); mbar_init(res_bar, 1); mbar_init(comb_bar, 8);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -246,7 +252,9 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
     }
   } else {
     // =========================== element-wise warps ===========================
-    const int q = warp & 3, row = q * 32 + lane;
+    // Eight warps: two per tensor-memory lane quarter; each thread owns one row and one 32-column half of every
+    // 64-column score sub-tile.
+    const int q = warp & 3, row = q * 32 + lane, half = (warp - 2) >> 2, ch = half * 32;
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const int my = r0 + row;                                 // my query (FWD, DQ) or my key (DKV)
     bool ok = true;
@@ -259,122 +267,130 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
     }
     int g = 0;
     if (MODE == MODE_FWD) {
-      // ---- sweep 1: row max and row sum of exp over all keys ----
+      // ---- sweep 1: row max and row sum of exp over this thread's half of all keys ----
       for (; g < n_it; ++g) {
         const int buf = g & 1;
         ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(buf), ((uint32_t)g >> 1) & 1u, p.err, 16));
         if (!ok) break;
         tc_fence_after();
-        const int k0 = g * 64;
-        const bool diag = (k0 + 63 > r0);
-#pragma unroll 1
-        for (int c = 0; c < 64; c += 32) {
-          uint32_t r[32];
-          tmem_ld32(t1_col(buf) + lane_off + (uint32_t)c, r);
-          float sv[32], cm = -INFINITY;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float s = r16(r16(__uint_as_float(r[i])) * p.scale);
-            if (diag && (k0 + c + i > my)) s = -INFINITY;
-            sv[i] = s; cm = fmaxf(cm, s);
-          }
-          if (cm > m_run) { l_run *= ex2((m_run - cm) * LOG2E); m_run = cm; }
-          if (m_run > -INFINITY) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) l_run += ex2((sv[i] - m_run) * LOG2E);
-          }
-        }
+        const int k0 = g * 64 + ch;
+        const bool diag = (k0 + 31 > r0);
+        uint32_t r[32];
+        tmem_ld32(t1_col(buf) + lane_off + (uint32_t)ch, r);
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar(buf));
+        if (lane == 0) mbar_arrive(tempty_bar(buf));          // the values are in registers: release the buffer early
+        float sv[32], cm = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = r16(r16(__uint_as_float(r[i])) * p.scale);
+          if (diag && (k0 + i > my)) s = -INFINITY;
+          sv[i] = s; cm = fmaxf(cm, s);
+        }
+        if (cm > m_run) { l_run *= ex2((m_run - cm) * LOG2E); m_run = cm; }
+        if (m_run > -INFINITY) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) l_run += ex2((sv[i] - m_run) * LOG2E);
+        }
       }
-      inv1 = 1.f / (l_run + PCPB_GUARD);
+      // combine the two halves of each row through shared memory
+      if (ok) {
+        stat[(half * 128 + row) * 2] = m_run; stat[(half * 128 + row) * 2 + 1] = l_run;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(comb_bar);
+        ok = __all_sync(0xffffffffu, mbar_wait(comb_bar, 0, p.err, 20));
+      }
+      if (ok) {
+        const float mo = stat[((half ^ 1) * 128 + row) * 2], lo = stat[((half ^ 1) * 128 + row) * 2 + 1];
+        const float mn = fmaxf(m_run, mo);
+        l_run = l_run * ex2((m_run - mn) * LOG2E) + lo * ex2((mo - mn) * LOG2E);
+        m_run = mn;
+        inv1 = 1.f / (l_run + PCPB_GUARD);
+      }
     }
     const int g0 = g;
     for (int it = 0; it < n_it && ok; ++it) {
       const int gg = g0 + it, buf = gg & 1;
-      int c0 = 0;                                            // first column-side position of this sub-tile
+      int c0 = 0;                                            // first column-side position of this thread's half
       // per-warp copy of the column statistics (no cross-warp barrier: a warp that gave up cannot block the others)
-      float* st = stat + ((warp - 2) * 2 + (it & 1)) * 320;
+      float* st = stat + ((warp - 2) * 2 + (it & 1)) * 160;
       if (MODE == MODE_DKV) {
         const int hh = h + it / n_q;
-        c0 = r0 + (it % n_q) * 64;
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int cc = lane + 32 * u;
-          const long long idx = ((long long)b * p.H + hh) * p.T + c0 + cc;
-          const float mm = p.mrow[idx], ll = p.lrow[idx], dd = p.drow[idx];
-          const float i2 = 1.f / (ll + 2.f * PCPB_GUARD);
-          st[cc] = mm; st[64 + cc] = 1.f / (ll + PCPB_GUARD); st[128 + cc] = i2; st[192 + cc] = dd;
-          st[256 + cc] = dd * (2.f * PCPB_GUARD) * i2;
-        }
+        c0 = r0 + (it % n_q) * 64 + ch;
+        const long long idx = ((long long)b * p.H + hh) * p.T + c0 + lane;
+        const float mm = p.mrow[idx], ll = p.lrow[idx], dd = p.drow[idx];
+        const float i2 = 1.f / (ll + 2.f * PCPB_GUARD);
+        st[lane] = mm; st[32 + lane] = 1.f / (ll + PCPB_GUARD); st[64 + lane] = i2; st[96 + lane] = dd;
+        st[128 + lane] = dd * (2.f * PCPB_GUARD) * i2;
         __syncwarp();
       } else {
-        c0 = it * 64;
+        c0 = it * 64 + ch;
       }
       ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(buf), ((uint32_t)gg >> 1) & 1u, p.err, 17));
       if (!ok) break;
       tc_fence_after();
-      const bool diag = (MODE == MODE_DKV) ? (c0 < r0 + 128) : (c0 + 63 > r0);
-#pragma unroll 1
-      for (int c = 0; c < 64; c += 32) {
-        uint32_t r1[32];
-        tmem_ld32(t1_col(buf) + lane_off + (uint32_t)c, r1);
-        float ev[32], e2v[32];
-        if (MODE == MODE_FWD) {
+      const bool diag = (MODE == MODE_DKV) ? (c0 < r0 + 128) : (c0 + 31 > r0);
+      uint32_t r1[32];
+      tmem_ld32(t1_col(buf) + lane_off + (uint32_t)ch, r1);
+      float ev[32], e2v[32];
+      if (MODE == MODE_FWD) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(buf));
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float s = r16(r16(__uint_as_float(r1[i])) * p.scale);
-            const bool masked = diag && (c0 + c + i > my);
-            ev[i] = masked ? 0.f : ex2((s - m_run) * LOG2E) * inv1;
-          }
-        } else {
-          uint32_t r2[32];
-          tmem_ld32(t2_col(buf) + lane_off + (uint32_t)c, r2);
+        for (int i = 0; i < 32; ++i) {
+          const float s = r16(r16(__uint_as_float(r1[i])) * p.scale);
+          const bool masked = diag && (c0 + i > my);
+          ev[i] = masked ? 0.f : ex2((s - m_run) * LOG2E) * inv1;
+        }
+      } else {
+        uint32_t r2[32];
+        tmem_ld32(t2_col(buf) + lane_off + (uint32_t)ch, r2);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(buf));
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float s = r16(r16(__uint_as_float(r1[i])) * p.scale);
-            const float dp = r16(__uint_as_float(r2[i]));
-            float mm, i1, i2, dd, mt;
-            bool masked;
-            if (MODE == MODE_DQ) { mm = m_run; i1 = 0.f; i2 = inv2; dd = Dr; mt = mterm; masked = diag && (c0 + c + i > my); }
-            else { mm = st[c + i]; i1 = st[64 + c + i]; i2 = st[128 + c + i]; dd = st[192 + c + i]; mt = st[256 + c + i];
-                   masked = diag && (my > c0 + c + i); }
-            const float e = masked ? 0.f : ex2((s - mm) * LOG2E);
-            float dsf = e * i2 * (dp - dd);
-            if (!masked && s == mm) dsf -= mt;
-            const float ds = masked ? 0.f : r16(r16(dsf) * p.scale);
-            if (MODE == MODE_DQ) ev[i] = ds; else { ev[i] = e * i1; e2v[i] = ds; }
-          }
+        for (int i = 0; i < 32; ++i) {
+          const float s = r16(r16(__uint_as_float(r1[i])) * p.scale);
+          const float dp = r16(__uint_as_float(r2[i]));
+          float mm, i1, i2, dd, mt;
+          bool masked;
+          if (MODE == MODE_DQ) { mm = m_run; i1 = 0.f; i2 = inv2; dd = Dr; mt = mterm; masked = diag && (c0 + i > my); }
+          else { mm = st[i]; i1 = st[32 + i]; i2 = st[64 + i]; dd = st[96 + i]; mt = st[128 + i]; masked = diag && (my > c0 + i); }
+          const float e = masked ? 0.f : ex2((s - mm) * LOG2E);
+          float dsf = e * i2 * (dp - dd);
+          if (!masked && s == mm) dsf -= mt;
+          // the second rounding of ds happens when the value is packed to bf16 for the result tile
+          const float ds = masked ? 0.f : r16(dsf) * p.scale;
+          if (MODE == MODE_DQ) ev[i] = ds; else { ev[i] = e * i1; e2v[i] = ds; }
         }
-        if (c == 0) {
-          // the previous output products must have finished reading the result tile(s)
-          ok = __all_sync(0xffffffffu, mbar_wait(eempty_bar, ((uint32_t)it & 1u) ^ 1u, p.err, 18));
-          if (!ok) break;
-        }
-        store_e32(sE, row, c, ev);
-        if (MODE == MODE_DKV) store_e32(sE + E_BYTES, row, c, e2v);
       }
+      // the previous output products must have finished reading the result tile(s)
+      ok = __all_sync(0xffffffffu, mbar_wait(eempty_bar, ((uint32_t)it & 1u) ^ 1u, p.err, 18));
       if (!ok) break;
-      tc_fence_before();
+      store_e32(sE, row, ch, ev);
+      if (MODE == MODE_DKV) store_e32(sE + E_BYTES, row, ch, e2v);
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(tempty_bar(buf)); mbar_arrive(efull_bar); }
+      if (lane == 0) mbar_arrive(efull_bar);
     }
-    // ---- outputs ----
+    // ---- outputs: each warp stores 64 of the 128 output columns of its rows ----
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(out_bar, 0, p.err, 19));
     if (ok) {
       tc_fence_after();
       const long long grow = (long long)row_base + my;
+      const int oc = half * 64;
       if (MODE == MODE_FWD) {
-        store_out_row(out1 + lane_off, p.o + grow * p.d + xq, 1.f);
-        const long long idx = ((long long)b * p.H + h) * p.T + my;
-        p.mrow[idx] = m_run; p.lrow[idx] = l_run;
+        store_out_cols(out1 + lane_off + oc, p.o + grow * p.d + xq + oc);
+        if (half == 0) {
+          const long long idx = ((long long)b * p.H + h) * p.T + my;
+          p.mrow[idx] = m_run; p.lrow[idx] = l_run;
+        }
       } else if (MODE == MODE_DQ) {
-        store_out_row(out1 + lane_off, p.dqkn + grow * (p.d + p.dkv) + xq, 1.f);
+        store_out_cols(out1 + lane_off + oc, p.dqkn + grow * (p.d + p.dkv) + xq + oc);
       } else {
-        store_out_row(out1 + lane_off, p.dqkv + grow * (p.d + 2 * p.dkv) + xv, 1.f);
-        store_out_row(out2 + lane_off, p.dqkn + grow * (p.d + p.dkv) + xk, 1.f);
+        store_out_cols(out1 + lane_off + oc, p.dqkv + grow * (p.d + 2 * p.dkv) + xv + oc);
+        store_out_cols(out2 + lane_off + oc, p.dqkn + grow * (p.d + p.dkv) + xk + oc);
       }
     }
   }
@@ -418,7 +434,7 @@ cudaError_t launch_mode(cudaStream_t st, const CUtensorMap& a, const CUtensorMap
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) attr[dev] = true;
   }
-  kern<<<grid, 192, AtcCfg<MODE>::SMEM_BYTES, st>>>(a, b, c, p);
+  kern<<<grid, 320, AtcCfg<MODE>::SMEM_BYTES, st>>>(a, b, c, p);
   return cudaGetLastError();
 }
 

@@ -926,9 +926,18 @@ __global__ void __launch_bounds__(256) k_adam_sumsq(const TensorSeg* __restrict_
   const long long base = (long long)(chunk - s.first_chunk) * ADAM_CHUNK;
   const long long end = min(base + (long long)ADAM_CHUNK, s.n);
   float acc = 0.f;
-  for (long long i = base + threadIdx.x; i < end; i += blockDim.x) {
-    const float g = fminf(fmaxf(s.g[i], -1000.f), 1000.f);
-    acc += g * g;
+  if ((((uintptr_t)s.g) & 15) == 0 && ((end - base) & 3) == 0) {
+    for (long long i = base + 4 * threadIdx.x; i < end; i += 4 * blockDim.x) {
+      const float4 g4 = *reinterpret_cast<const float4*>(s.g + i);
+      const float a = fminf(fmaxf(g4.x, -1000.f), 1000.f), b = fminf(fmaxf(g4.y, -1000.f), 1000.f);
+      const float c = fminf(fmaxf(g4.z, -1000.f), 1000.f), d = fminf(fmaxf(g4.w, -1000.f), 1000.f);
+      acc += a * a; acc += b * b; acc += c * c; acc += d * d;
+    }
+  } else {
+    for (long long i = base + threadIdx.x; i < end; i += blockDim.x) {
+      const float g = fminf(fmaxf(s.g[i], -1000.f), 1000.f);
+      acc += g * g;
+    }
   }
   acc = block_sum(acc, red);
   if (threadIdx.x == 0) partial[chunk] = acc;
@@ -942,6 +951,16 @@ __global__ void k_adam_norm(const TensorSeg* __restrict__ segs, const float* __r
   acc = block_sum(acc, red);
   if (threadIdx.x == 0) normsq[blockIdx.x] = acc;
 }
+__device__ __forceinline__ void adam_elem(float p, float g, float m, float v, float scale, float omb1, float omb2,
+                                          const AdamHyper& h, float& pn, float& mn, float& vn) {
+  const float gc = __fmul_rn(g, scale);
+  mn = __fadd_rn(__fmul_rn(h.beta1, m), __fmul_rn(omb1, gc));
+  vn = __fadd_rn(__fmul_rn(h.beta2, v), __fmul_rn(omb2, __fmul_rn(gc, gc)));
+  const float mh = __fdiv_rn(mn, h.m_corr), vh = __fdiv_rn(vn, h.v_corr);
+  const float ratio = __fdiv_rn(mh, __fadd_rn(__fsqrt_rn(vh), h.eps));
+  pn = __fsub_rn(p, __fmul_rn(h.lr, __fadd_rn(ratio, __fmul_rn(h.wd, p))));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) k_adam_update(const TensorSeg* __restrict__ segs, const int* __restrict__ c2s,
                                                      const float* __restrict__ normsq, AdamHyper h, int has_shadow) {
@@ -953,16 +972,41 @@ __global__ void __launch_bounds__(256) k_adam_update(const TensorSeg* __restrict
   const float norm = __fadd_rn(__fsqrt_rn(normsq[si]), h.eps);
   const float scale = __fdiv_rn(h.max_norm, fmaxf(norm, h.max_norm));
   const float omb1 = __fsub_rn(1.f, h.beta1), omb2 = __fsub_rn(1.f, h.beta2);
+  const bool shadow = has_shadow && s.shadow;
+  const uintptr_t al = (uintptr_t)s.p | (uintptr_t)s.g | (uintptr_t)s.m | (uintptr_t)s.v | (uintptr_t)s.p_out |
+                       (uintptr_t)s.m_out | (uintptr_t)s.v_out | (shadow ? (uintptr_t)s.shadow : 0);
+  if ((al & 15) == 0 && ((end - base) & 3) == 0) {
+    // 16-byte path: four elements per thread and access
+    for (long long i = base + 4 * threadIdx.x; i < end; i += 4 * blockDim.x) {
+      const float4 p4 = *reinterpret_cast<const float4*>(s.p + i), g4 = *reinterpret_cast<const float4*>(s.g + i);
+      const float4 m4 = *reinterpret_cast<const float4*>(s.m + i), v4 = *reinterpret_cast<const float4*>(s.v + i);
+      float4 pn, mn, vn;
+      adam_elem(p4.x, g4.x, m4.x, v4.x, scale, omb1, omb2, h, pn.x, mn.x, vn.x);
+      adam_elem(p4.y, g4.y, m4.y, v4.y, scale, omb1, omb2, h, pn.y, mn.y, vn.y);
+      adam_elem(p4.z, g4.z, m4.z, v4.z, scale, omb1, omb2, h, pn.z, mn.z, vn.z);
+      adam_elem(p4.w, g4.w, m4.w, v4.w, scale, omb1, omb2, h, pn.w, mn.w, vn.w);
+      *reinterpret_cast<float4*>(s.p_out + i) = pn;
+      *reinterpret_cast<float4*>(s.m_out + i) = mn;
+      *reinterpret_cast<float4*>(s.v_out + i) = vn;
+      if (shadow) {
+        T* sh = (T*)s.shadow + i;
+        if (sizeof(T) == 2) {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(pn.x, pn.y), hi = __floats2bfloat162_rn(pn.z, pn.w);
+          uint2 pk;
+          pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(sh) = pk;
+        } else {
+          sh[0] = from_f<T>(pn.x); sh[1] = from_f<T>(pn.y); sh[2] = from_f<T>(pn.z); sh[3] = from_f<T>(pn.w);
+        }
+      }
+    }
+    return;
+  }
   for (long long i = base + threadIdx.x; i < end; i += blockDim.x) {
-    const float p = s.p[i];
-    const float gc = __fmul_rn(s.g[i], scale);
-    const float m = __fadd_rn(__fmul_rn(h.beta1, s.m[i]), __fmul_rn(omb1, gc));
-    const float v = __fadd_rn(__fmul_rn(h.beta2, s.v[i]), __fmul_rn(omb2, __fmul_rn(gc, gc)));
-    const float mh = __fdiv_rn(m, h.m_corr), vh = __fdiv_rn(v, h.v_corr);
-    const float ratio = __fdiv_rn(mh, __fadd_rn(__fsqrt_rn(vh), h.eps));
-    const float pn = __fsub_rn(p, __fmul_rn(h.lr, __fadd_rn(ratio, __fmul_rn(h.wd, p))));
-    s.p_out[i] = pn; s.m_out[i] = m; s.v_out[i] = v;
-    if (has_shadow && s.shadow) ((T*)s.shadow)[i] = from_f<T>(pn);
+    float pn, mn, vn;
+    adam_elem(s.p[i], s.g[i], s.m[i], s.v[i], scale, omb1, omb2, h, pn, mn, vn);
+    s.p_out[i] = pn; s.m_out[i] = mn; s.v_out[i] = vn;
+    if (shadow) ((T*)s.shadow)[i] = from_f<T>(pn);
   }
 }
 cudaError_t launch_adamw(cudaStream_t st, int shadow_dt, const TensorSeg* segs, int nseg, const int* chunk2seg,
