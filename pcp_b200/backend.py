@@ -31,7 +31,7 @@ IPC_HANDLE_BYTES = 64
 
 E_INVALID, E_CUDA, E_ARTIFACT, E_FUNCTION, E_CHUNK_TOO_SMALL, E_CHUNK_EXHAUSTED, E_STATE, E_TOO_LARGE = range(1, 9)
 
-LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libpcp_b200.so")
+LIB_PATH = os.environ.get("PCPB_LIBRARY") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "libpcp_b200.so")
 
 EXPORTS = [
     "pcpb_create", "pcpb_destroy", "pcpb_backend_type", "pcpb_last_error", "pcpb_free", "pcpb_load_artifact",

@@ -71,6 +71,21 @@ __device__ __forceinline__ float r16(float x) {
   return __uint_as_float(u & 0xFFFF0000u);
 }
 
+// Optional instrumentation (-DPCPB_ATC_TIMING): cycles spent in each bounded wait, summed over warps and CTAs.
+#ifdef PCPB_ATC_TIMING
+__device__ unsigned long long g_atc_t[32];
+#endif
+__device__ __forceinline__ bool twait(int code, uint32_t bar, uint32_t parity, int* err) {
+#ifdef PCPB_ATC_TIMING
+  const long long t0 = clock64();
+  const bool r = mbar_wait(bar, parity, err, code);
+  if ((threadIdx.x & 31) == 0) atomicAdd(&g_atc_t[code], (unsigned long long)(clock64() - t0));
+  return r;
+#else
+  return mbar_wait(bar, parity, err, code);
+#endif
+}
+
 // Write 32 consecutive k-values (columns c0 .. c0+31 of row r) of a [128 x 64] bf16 A-operand tile (one 128-byte
 // swizzle atom per row: 16-byte chunk j of row r lives at chunk position j ^ (r & 7)).
 __device__ __forceinline__ void store_e32(uint32_t ebase, int r, int c0, const float (&v)[32]) {
@@ -122,6 +137,9 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int grp = p.H / p.Hkv;
+#ifdef PCPB_ATC_TIMING
+  const long long t_cta0 = clock64();
+#endif
   // work of this CTA
   int b, h, hk, r0, n_it, n_q = 0;
   if (MODE == MODE_DKV) {
@@ -174,7 +192,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       bool ok = true;
       for (int g = 0; g < total_g && ok; ++g) {
         const int s = g % NST;
-        if (!(ok = mbar_wait(empty_bar(s), (((uint32_t)g / NST) & 1u) ^ 1u, p.err, 11))) break;
+        if (!(ok = twait(11, empty_bar(s), (((uint32_t)g / NST) & 1u) ^ 1u, p.err))) break;
         const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
         const bool stats_pass = (MODE == MODE_FWD) && g < n_it;
         mbar_expect_tx(full_bar(s), stats_pass ? SUB_BYTES : STAGE_BYTES);
@@ -204,11 +222,11 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       // score products: M=128, N=64, A and B K-major; output products: M=128, N=128, A K-major, B MN-major
       constexpr uint32_t ID_T = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
       constexpr uint32_t ID_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-      bool ok = mbar_wait(res_bar, 0, p.err, 12);
+      bool ok = twait(12, res_bar, 0, p.err);
       auto issue_T = [&](int g, bool release_stage) -> bool {
         const int s = g % NST, buf = g & 1;
-        if (!mbar_wait(full_bar(s), ((uint32_t)g / NST) & 1u, p.err, 13)) return false;
-        if (!mbar_wait(tempty_bar(buf), (((uint32_t)g >> 1) & 1u) ^ 1u, p.err, 14)) return false;
+        if (!twait(13, full_bar(s), ((uint32_t)g / NST) & 1u, p.err)) return false;
+        if (!twait(14, tempty_bar(buf), (((uint32_t)g >> 1) & 1u) ^ 1u, p.err)) return false;
         tc_fence_after();
         const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
 #pragma unroll
@@ -230,7 +248,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       if (ok) ok = issue_T(g0, false);
       for (int it = 0; it < n_it && ok; ++it) {
         if (it + 1 < n_it && !(ok = issue_T(g0 + it + 1, false))) break;
-        if (!(ok = mbar_wait(efull_bar, (uint32_t)it & 1u, p.err, 15))) break;
+        if (!(ok = twait(15, efull_bar, (uint32_t)it & 1u, p.err))) break;
         tc_fence_after();
         const int s = (g0 + it) % NST;
         const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
@@ -270,7 +288,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       // ---- sweep 1: row max and row sum of exp over this thread's half of all keys ----
       for (; g < n_it; ++g) {
         const int buf = g & 1;
-        ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(buf), ((uint32_t)g >> 1) & 1u, p.err, 16));
+        ok = __all_sync(0xffffffffu, twait(16, tfull_bar(buf), ((uint32_t)g >> 1) & 1u, p.err));
         if (!ok) break;
         tc_fence_after();
         const int k0 = g * 64 + ch;
@@ -298,7 +316,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
         stat[(half * 128 + row) * 2] = m_run; stat[(half * 128 + row) * 2 + 1] = l_run;
         __syncwarp();
         if (lane == 0) mbar_arrive(comb_bar);
-        ok = __all_sync(0xffffffffu, mbar_wait(comb_bar, 0, p.err, 20));
+        ok = __all_sync(0xffffffffu, twait(20, comb_bar, 0, p.err));
       }
       if (ok) {
         const float mo = stat[((half ^ 1) * 128 + row) * 2], lo = stat[((half ^ 1) * 128 + row) * 2 + 1];
@@ -326,7 +344,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       } else {
         c0 = it * 64 + ch;
       }
-      ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(buf), ((uint32_t)gg >> 1) & 1u, p.err, 17));
+      ok = __all_sync(0xffffffffu, twait(17, tfull_bar(buf), ((uint32_t)gg >> 1) & 1u, p.err));
       if (!ok) break;
       tc_fence_after();
       const bool diag = (MODE == MODE_DKV) ? (c0 < r0 + 128) : (c0 + 31 > r0);
@@ -366,7 +384,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
         }
       }
       // the previous output products must have finished reading the result tile(s)
-      ok = __all_sync(0xffffffffu, mbar_wait(eempty_bar, ((uint32_t)it & 1u) ^ 1u, p.err, 18));
+      ok = __all_sync(0xffffffffu, twait(18, eempty_bar, ((uint32_t)it & 1u) ^ 1u, p.err));
       if (!ok) break;
       store_e32(sE, row, ch, ev);
       if (MODE == MODE_DKV) store_e32(sE + E_BYTES, row, ch, e2v);
@@ -375,7 +393,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       if (lane == 0) mbar_arrive(efull_bar);
     }
     // ---- outputs: each warp stores 64 of the 128 output columns of its rows ----
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(out_bar, 0, p.err, 19));
+    if (ok) ok = __all_sync(0xffffffffu, twait(19, out_bar, 0, p.err));
     if (ok) {
       tc_fence_after();
       const long long grow = (long long)row_base + my;
@@ -394,6 +412,13 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       }
     }
   }
+#ifdef PCPB_ATC_TIMING
+  if (threadIdx.x == 64) {
+    atomicAdd(&g_atc_t[0], (unsigned long long)(clock64() - t_cta0));
+    atomicAdd(&g_atc_t[1], 1ull);
+    atomicAdd(&g_atc_t[2], (unsigned long long)n_it);
+  }
+#endif
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -452,6 +477,14 @@ bool fill(const FlashArgs& a, int* err, AtcParams* p, CUtensorMap* mq, CUtensorM
 }
 
 }  // namespace
+
+#ifdef PCPB_ATC_TIMING
+extern "C" int pcpb_debug_atc_timing(unsigned long long* out32, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out32, g_atc_t, sizeof(unsigned long long) * 32);
+  if (e == cudaSuccess && reset) { unsigned long long z[32] = {}; e = cudaMemcpyToSymbol(g_atc_t, z, sizeof z); }
+  return e == cudaSuccess ? 0 : 2;
+}
+#endif
 
 bool attn_tc_supported(const FlashArgs& a) {
   return a.hd == HD && a.T % 128 == 0 && a.T >= 128 && a.H % a.Hkv == 0 && a.B > 0 && (long long)a.B * a.H <= 65535 &&

@@ -553,6 +553,18 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs& g, int m, int n, f
       ((float*)g.C)[o] = v;
       break;
     }
+    case EPI_RELU: {
+      const T u = from_f<T>(acc);
+      ((T*)g.C)[o] = u;
+      ((T*)g.C2)[o] = from_f<T>(fmaxf(to_f(u), 0.f));
+      break;
+    }
+    case EPI_DRELU:
+      ((T*)g.C)[o] = (to_f(((const T*)g.R)[o]) > 0.f) ? from_f<T>(acc) : from_f<T>(0.f);
+      break;
+    case EPI_BIAS:
+      ((T*)g.C)[o] = from_f<T>(acc + to_f(((const T*)g.R)[n]));
+      break;
   }
 }
 
@@ -796,28 +808,31 @@ __global__ void __launch_bounds__(256) k_softcap_ce(T* __restrict__ logits, cons
   const long long t = tg[m];
   const bool valid = (t != ignore);
   const float capg = cap + PCPB_GUARD;
+  const bool capped = cap > 0.f;                      // cap == 0: plain cross entropy (nanoGPT family)
+  auto capf = [&](float x) { return capped ? tanhf(x / capg) * cap : x; };
   float mx = -INFINITY;
-  for (int j = threadIdx.x; j < V; j += blockDim.x) mx = fmaxf(mx, tanhf(to_f(z[j]) / capg) * cap);
+  for (int j = threadIdx.x; j < V; j += blockDim.x) mx = fmaxf(mx, capf(to_f(z[j])));
   mx = block_max(mx, red);
   float se = 0.f;
-  for (int j = threadIdx.x; j < V; j += blockDim.x) se += expf(tanhf(to_f(z[j]) / capg) * cap - mx);
+  for (int j = threadIdx.x; j < V; j += blockDim.x) se += expf(capf(to_f(z[j])) - mx);
   se = block_sum(se, red);
   if (threadIdx.x == 0) {
     float nll = 0.f;
     if (valid) {
       long long tt = t < 0 ? 0 : (t >= V ? V - 1 : t);
-      const float c = tanhf(to_f(z[tt]) / capg) * cap;
-      nll = -((c - mx) - logf(se + PCPB_GUARD));
+      nll = -((capf(to_f(z[tt])) - mx) - logf(se + PCPB_GUARD));
     }
     rowloss[m] = nll;
   }
   if (!write_grad) return;
+  __syncthreads();
   const float dtot = valid ? 1.f / (*count + 2.f * PCPB_GUARD) : 0.f;
   const float den = se + 2.f * PCPB_GUARD;
-  const float dzscale = cap / (capg + PCPB_GUARD);
+  const float dzscale = capped ? cap / (capg + PCPB_GUARD) : 1.f;
   for (int j = threadIdx.x; j < V; j += blockDim.x) {
-    const float th = tanhf(to_f(z[j]) / capg);
-    const float c = th * cap;
+    const float zj = to_f(z[j]);
+    const float th = capped ? tanhf(zj / capg) : 0.f;
+    const float c = capped ? th * cap : zj;
     float dc = expf(c - mx) / den;
     if ((long long)j == t) dc -= 1.f;
     if (c == mx) dc += (2.f * PCPB_GUARD) / den;
@@ -837,6 +852,7 @@ __global__ void __launch_bounds__(512) k_softcap_ce_vec(T* __restrict__ logits, 
   const long long t = tg[m];
   const bool valid = (t != ignore);
   const float capg = cap + PCPB_GUARD, icapg = 1.f / capg;
+  const bool capped = cap > 0.f;                      // cap == 0: plain cross entropy (nanoGPT family)
   const int nv = V >> 3;
   float mx = -INFINITY, se = 0.f;
   for (int v = threadIdx.x; v < nv; v += blockDim.x) {
@@ -845,7 +861,7 @@ __global__ void __launch_bounds__(512) k_softcap_ce_vec(T* __restrict__ logits, 
     float c[8], cm = -INFINITY;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      c[i] = m_tanh<T>(sizeof(T) == 4 ? f[i] / capg : f[i] * icapg) * cap;
+      c[i] = capped ? m_tanh<T>(sizeof(T) == 4 ? f[i] / capg : f[i] * icapg) * cap : f[i];
       cm = fmaxf(cm, c[i]);
     }
     if (cm > mx) { se *= m_exp<T>(mx - cm); mx = cm; }
@@ -861,7 +877,7 @@ __global__ void __launch_bounds__(512) k_softcap_ce_vec(T* __restrict__ logits, 
     if (valid) {
       long long tt = t < 0 ? 0 : (t >= V ? V - 1 : t);
       const float zt = to_f(z[tt]);
-      const float c = m_tanh<T>(sizeof(T) == 4 ? zt / capg : zt * icapg) * cap;
+      const float c = capped ? m_tanh<T>(sizeof(T) == 4 ? zt / capg : zt * icapg) * cap : zt;
       nll = -((c - mx) - logf(se + PCPB_GUARD));
     }
     rowloss[m] = nll;
@@ -870,14 +886,14 @@ __global__ void __launch_bounds__(512) k_softcap_ce_vec(T* __restrict__ logits, 
   __syncthreads();                                  // the target logit was read above before anyone overwrites it
   const float dtot = valid ? 1.f / (*count + 2.f * PCPB_GUARD) : 0.f;
   const float iden = 1.f / (se + 2.f * PCPB_GUARD);
-  const float dzscale = cap / (capg + PCPB_GUARD);
+  const float dzscale = capped ? cap / (capg + PCPB_GUARD) : 1.f;
   for (int v = threadIdx.x; v < nv; v += blockDim.x) {
     float f[8], o[8];
     ld8<T>(z + v * 8, f);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float th = m_tanh<T>(sizeof(T) == 4 ? f[i] / capg : f[i] * icapg);
-      const float c = th * cap;
+      const float th = capped ? m_tanh<T>(sizeof(T) == 4 ? f[i] / capg : f[i] * icapg) : 0.f;
+      const float c = capped ? th * cap : f[i];
       float dc = m_exp<T>(c - mx) * iden;
       if ((long long)(v * 8 + i) == t) dc -= 1.f;
       if (c == mx) dc += (2.f * PCPB_GUARD) * iden;

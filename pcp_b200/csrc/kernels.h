@@ -16,6 +16,9 @@ enum GemmEpilogue : int {
   EPI_RELU2 = 2,    // C = T(acc); C2 = T(max(C,0)^2)     (MLP activation, two outputs)
   EPI_DRELU2 = 3,   // C = backward of max(.,0)^2 at U given dA = T(acc)
   EPI_WGRAD = 4,    // Cf32 = clamp(finite(T(acc)), +-clip)   (weight gradient, f32 out)
+  EPI_RELU = 5,     // C = T(acc); C2 = max(C, 0)         (nanoGPT MLP activation, two outputs)
+  EPI_DRELU = 6,    // C = U > 0 ? T(acc) : 0             (backward of max(., 0), U in R)
+  EPI_BIAS = 7,     // C = T(acc + bias[n])               (lm_head with bias; bias of model dtype in R, length N)
 };
 struct GemmArgs {
   const void* A; long long sam, sak;
@@ -72,9 +75,28 @@ struct AttnArgs {
 cudaError_t launch_attn_fwd_generic(cudaStream_t st, int dt, const AttnArgs& a);
 cudaError_t launch_attn_bwd_generic(cudaStream_t st, int dt, const AttnArgs& a);
 
+// ---- nanoGPT family ---------------------------------------------------------------------------------
+cudaError_t launch_embed_pos_fwd(cudaStream_t st, int dt, const void* wte, const void* wpe, const long long* idx, int M,
+                                 int Tlen, int d, int V, void* x);
+// dwte must be zeroed by the caller (atomic accumulation); dwpe is overwritten
+cudaError_t launch_embed_pos_bwd(cudaStream_t st, int dt, const long long* idx, int B, int Tlen, int d, int V, const void* dx,
+                                 float* dwte, float* dwpe);
+cudaError_t launch_layernorm_fwd(cudaStream_t st, int dt, const void* x, const void* gamma, const void* beta, int M, int d,
+                                 void* y, float* mean, float* tsave, double* mean64);
+size_t layernorm_bwd_scratch_floats(int M, int d);
+// dx = dres + backward(dy); dgamma / dbeta: f32, rounded to the model dtype, guarded and clamped
+cudaError_t launch_layernorm_bwd(cudaStream_t st, int dt, const void* x, const void* gamma, const float* mean,
+                                 const float* tsave, const double* mean64, const void* dy, const void* dres, int M, int d,
+                                 void* dx, float* partial, float* dgamma, float* dbeta);
+size_t colsum_scratch_floats(int M, int V);
+cudaError_t launch_colsum(cudaStream_t st, int dt, const void* z, int M, int V, float* partial, float* out);
+cudaError_t launch_copy_cols(cudaStream_t st, int dt, const void* src, long long src_pitch, void* dst, long long dst_pitch,
+                             int M, int ncols);
+
 // ---- soft-capped cross entropy -------------------------------------------------------------------
 // logits [M,V] of model dtype are overwritten with d(loss)/d(logits).  rowloss[M]: per-row NLL (0 if
 // ignored).  count: number of targets != ignore (device scalar, written by launch_count_valid).
+// cap == 0 selects the plain cross entropy of the nanoGPT family (no soft-cap).
 cudaError_t launch_count_valid(cudaStream_t st, const long long* targets, int M, long long ignore, float* count);
 cudaError_t launch_softcap_ce(cudaStream_t st, int dt, void* logits, const long long* targets, int M, int V,
                               float cap, long long ignore, const float* count, float* rowloss, int write_grad);

@@ -1,5 +1,6 @@
 #include "model.h"
 
+#include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -85,7 +86,69 @@ std::string parse_artifact(const char* text, size_t n, ModelConfig* cfg) {
   const ArgType& ids = args[nP];
   if (ids.elem != "i64" || ids.shape.size() != 2 || args[nP + 1].elem != "i64" || args[nP + 1].shape != ids.shape)
     return "the last two @main arguments must be i64 [B,T] token ids and targets";
-  if ((nP - 2) % 6 != 0 || nP < 8) return "not a nanochat-family graph (parameter count is not 2 + 6*layers)";
+  // ---- nanoGPT family: wte [V,d], wpe [T,d], 8 tensors per layer (4 of them rank 1), ln_f w/b, head w/b ----
+  if (nP >= 14 && (nP - 6) % 8 == 0 && args[0].shape.size() == 2 && args[1].shape.size() == 2 &&
+      args[2].shape.size() == 1 && args[nP - 1].shape.size() == 1) {
+    ModelConfig c;
+    c.family = FAMILY_NANOGPT;
+    if (args[0].elem == "f32") c.dtype = 0;
+    else if (args[0].elem == "bf16") c.dtype = 3;
+    else return "unsupported model dtype " + args[0].elem;
+    c.B = ids.shape[0]; c.T = ids.shape[1];
+    c.V = args[0].shape[0]; c.d = args[0].shape[1];
+    c.L = (int64_t)(nP - 6) / 8;
+    if (args[1].shape[0] != c.T || args[1].shape[1] != c.d) return "wpe shape must be [T, d]";
+    c.F = args[8].shape[0];
+    for (int64_t l = 0; l < c.L; ++l) {
+      const ArgType* a = &args[2 + 8 * l];
+      auto v1 = [&](const ArgType& t) { return t.shape.size() == 1 && t.shape[0] == c.d; };
+      auto m2 = [&](const ArgType& t, int64_t r, int64_t k) { return t.shape.size() == 2 && t.shape[0] == r && t.shape[1] == k; };
+      if (!(v1(a[0]) && v1(a[1]) && m2(a[2], 3 * c.d, c.d) && m2(a[3], c.d, c.d) && v1(a[4]) && v1(a[5]) &&
+            m2(a[6], c.F, c.d) && m2(a[7], c.d, c.F)))
+        return "layer parameter shapes do not follow ln1,c_attn,c_proj,ln2,c_fc,c_proj";
+    }
+    const ArgType* t = &args[nP - 4];
+    if (!(t[0].shape.size() == 1 && t[0].shape[0] == c.d && t[1].shape.size() == 1 && t[1].shape[0] == c.d &&
+          t[2].shape.size() == 2 && t[2].shape[0] == c.V && t[2].shape[1] == c.d && t[3].shape[0] == c.V))
+      return "final LayerNorm / lm_head shapes not recognised";
+    for (size_t i = 0; i < nP; ++i) if (args[i].elem != args[0].elem) return "all parameters must share one dtype";
+    // heads: the first reshape to [B, T, H, hd]
+    {
+      char pat[64];
+      snprintf(pat, sizeof pat, "-> tensor<%lldx%lldx", (long long)c.B, (long long)c.T);
+      size_t q = 0;
+      while ((q = src.find(pat, q)) != std::string::npos) {
+        ArgType rt;
+        size_t e = src.find('>', q);
+        if (parse_tensor_type(src.substr(q + 3, e - q - 2), &rt) && rt.shape.size() == 4 && rt.shape[2] * rt.shape[3] == c.d) {
+          c.H = rt.shape[2]; c.hd = rt.shape[3];
+          break;
+        }
+        q = e;
+      }
+      if (c.H == 0) return "could not find the [B,T,H,hd] reshape";
+    }
+    c.Hkv = c.H;
+    if (src.find("stablehlo.tanh") != std::string::npos || src.find("stablehlo.power") != std::string::npos)
+      return "nanoGPT graph with an activation other than ReLU is not supported";
+    if (src.find("dense<-100>") == std::string::npos) return "expected ignore_index -100 in the loss";
+    c.ignore_index = -100;
+    c.softcap = 0.f;
+    int64_t off = 0;
+    for (size_t i = 0; i < nP; ++i) {
+      TensorInfo ti;
+      ti.shape = args[i].shape;
+      ti.numel = 1;
+      for (int64_t s : args[i].shape) ti.numel *= s;
+      ti.offset = off;
+      off += ti.numel;              // tight, like the reference's parameter blob (src/algorithms/diloco.zig:665-667)
+      c.params.push_back(ti);
+    }
+    c.total_params = off;
+    *cfg = c;
+    return "";
+  }
+  if ((nP - 2) % 6 != 0 || nP < 8) return "not a nanochat- or nanoGPT-family graph (unexpected parameter list)";
   for (size_t i = 0; i < nP; ++i)
     if (args[i].shape.size() != 2 || args[i].elem != args[0].elem)
       return "not a nanochat-family graph (all parameters must be rank-2 of one dtype)";

@@ -13,12 +13,17 @@ struct TensorInfo {
   int64_t offset = 0;      // element offset in the flat parameter buffer (argument order)
 };
 
+enum { FAMILY_NANOCHAT = 0, FAMILY_NANOGPT = 1 };
+
 struct ModelConfig {
+  int family = FAMILY_NANOCHAT;
   int dtype = 0;           // DT_F32 | DT_BF16 (model dtype)
   int64_t V = 0, d = 0, L = 0, H = 0, Hkv = 0, hd = 0, F = 0, B = 0, T = 0;
   float softcap = 15.f;
   long long ignore_index = -1;
-  std::vector<TensorInfo> params;      // wte, per layer q k v proj fc proj2, lm_head
+  // nanochat: wte, per layer q k v proj fc proj2, lm_head
+  // nanoGPT:  wte, wpe, per layer ln1.w ln1.b c_attn c_proj ln2.w ln2.b c_fc mlp.c_proj, ln_f.w ln_f.b lm_head.w lm_head.b
+  std::vector<TensorInfo> params;
   int64_t total_params = 0;
   std::vector<uint16_t> rope_cos, rope_sin;   // [T, hd/2] bf16 bit patterns
   int64_t dkv() const { return Hkv * hd; }

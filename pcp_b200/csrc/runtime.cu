@@ -117,6 +117,14 @@ int build_workspace(pcpb_backend* b) {
     WS(b, l.u, M * F * es); WS(b, l.a, M * F * es);
     WS(b, l.t1, M * 4); WS(b, l.t2, M * 4); WS(b, l.tq, M * (size_t)(c.H + c.Hkv) * 4);
     WS(b, l.mrow, (size_t)c.B * c.H * c.T * 4); WS(b, l.lrow, (size_t)c.B * c.H * c.T * 4);
+    if (c.family == FAMILY_NANOGPT) {
+      WS(b, l.mu1, M * 4); WS(b, l.mu2, M * 4); WS(b, l.m64_1, M * 8); WS(b, l.m64_2, M * 8);
+    }
+  }
+  if (c.family == FAMILY_NANOGPT) {
+    WS(b, w.muf, M * 4); WS(b, w.m64f, M * 8);
+    WS(b, w.ln_partial, layernorm_bwd_scratch_floats((int)M, (int)d) * 4);
+    WS(b, w.cs_partial, colsum_scratch_floats((int)M, (int)c.V) * 4);
   }
   WS(b, w.t0, M * 4); WS(b, w.tf, M * 4); WS(b, w.rowloss, M * 4); WS(b, w.count, 4); WS(b, w.loss, 4);
   WS(b, w.hf, M * d * es); WS(b, w.logits, M * (size_t)c.V * es);
@@ -124,9 +132,11 @@ int build_workspace(pcpb_backend* b) {
   WS(b, w.dqkn, M * (d + dkv) * es); WS(b, w.dqkv, M * (d + 2 * dkv) * es); WS(b, w.dkv_acc, M * 2 * dkv * 4);
   WS(b, w.drow, (size_t)c.B * c.H * c.T * 4);
   WS(b, w.ids, M * 8); WS(b, w.targets, M * 8);
-  WS(b, w.d_cos, c.rope_cos.size() * 2); WS(b, w.d_sin, c.rope_sin.size() * 2);
-  CK(b, cudaMemcpy(w.d_cos, c.rope_cos.data(), c.rope_cos.size() * 2, cudaMemcpyHostToDevice));
-  CK(b, cudaMemcpy(w.d_sin, c.rope_sin.data(), c.rope_sin.size() * 2, cudaMemcpyHostToDevice));
+  if (!c.rope_cos.empty()) {
+    WS(b, w.d_cos, c.rope_cos.size() * 2); WS(b, w.d_sin, c.rope_sin.size() * 2);
+    CK(b, cudaMemcpy(w.d_cos, c.rope_cos.data(), c.rope_cos.size() * 2, cudaMemcpyHostToDevice));
+    CK(b, cudaMemcpy(w.d_sin, c.rope_sin.data(), c.rope_sin.size() * 2, cudaMemcpyHostToDevice));
+  }
   // optimiser tables of the flat layout
   const int nseg = (int)c.params.size();
   std::vector<TensorSeg> segs(nseg);
@@ -223,8 +233,12 @@ GemmArgs mk(const void* A, long long sam, long long sak, const void* B, long lon
 // ------------------------------------------------------------------------------------------------
 // one forward (+ backward) of the model on the parameters in `wts` (model dtype, flat)
 // ------------------------------------------------------------------------------------------------
+int forward_backward_gpt(pcpb_backend* b, const void* wts, const long long* ids, const long long* targets, float* grads,
+                         float* loss_out, bool backward);
+
 int forward_backward(pcpb_backend* b, const void* wts, const long long* ids, const long long* targets, float* grads,
                      float* loss_out, bool backward) {
+  if (b->cfg.family == FAMILY_NANOGPT) return forward_backward_gpt(b, wts, ids, targets, grads, loss_out, backward);
   const ModelConfig& c = b->cfg;
   Workspace& w = b->ws;
   cudaStream_t st = b->stream;
@@ -316,6 +330,113 @@ int forward_backward(pcpb_backend* b, const void* wts, const long long* ids, con
   CK(b, cudaMemsetAsync(GR(0), 0, (size_t)c.params[0].numel * 4, st));
   KL(b, 1, launch_embed_norm_bwd(st, dt, W(0), ids, M, d, V, w.dx, w.t0, GR(0)));
   KL(b, 1, launch_round_guard_f32(st, dt, GR(0), (size_t)c.params[0].numel, 100.f));
+  return PCPB_OK;
+}
+
+
+// Attention of either family on the (qkn, qkv) buffers; picks tcgen05, mma.sync or the generic kernels.
+int attention_fwd(pcpb_backend* b, LayerActs& a, float scale) {
+  const ModelConfig& c = b->cfg;
+  Workspace& w = b->ws;
+  const int dt = c.dtype;
+  FlashArgs fa{};
+  fa.qkn = a.qkn; fa.qkv = a.qkv; fa.o = a.o; fa.mrow = a.mrow; fa.lrow = a.lrow;
+  fa.B = (int)c.B; fa.T = (int)c.T; fa.H = (int)c.H; fa.Hkv = (int)c.Hkv; fa.hd = (int)c.hd; fa.scale = scale;
+  const bool fast = !b->force_generic && dt == DT_BF16 && b->attn_path != 2;
+  if (fast && b->attn_path == 0 && attn_tc_supported(fa)) { KL(b, 1, launch_attn_tc_fwd(b->stream, fa, w.tc_err)); return PCPB_OK; }
+  if (fast && flash_supported(fa)) { KL(b, 1, launch_flash_fwd(b->stream, fa)); return PCPB_OK; }
+  AttnArgs at{};
+  at.qkn = a.qkn; at.qkv = a.qkv; at.o = a.o; at.mrow = a.mrow; at.lrow = a.lrow;
+  at.B = fa.B; at.T = fa.T; at.H = fa.H; at.Hkv = fa.Hkv; at.hd = fa.hd; at.scale = scale;
+  KL(b, 1, launch_attn_fwd_generic(b->stream, dt, at));
+  return PCPB_OK;
+}
+int attention_bwd(pcpb_backend* b, LayerActs& a, float scale) {
+  const ModelConfig& c = b->cfg;
+  Workspace& w = b->ws;
+  const int dt = c.dtype;
+  FlashArgs fa{};
+  fa.qkn = a.qkn; fa.qkv = a.qkv; fa.o = a.o; fa.mrow = a.mrow; fa.lrow = a.lrow;
+  fa.B = (int)c.B; fa.T = (int)c.T; fa.H = (int)c.H; fa.Hkv = (int)c.Hkv; fa.hd = (int)c.hd; fa.scale = scale;
+  fa.dout = w.dout; fa.dqkn = w.dqkn; fa.dqkv = w.dqkv; fa.drow = w.drow;
+  const bool fast = !b->force_generic && dt == DT_BF16 && b->attn_path != 2;
+  if (fast && b->attn_path == 0 && attn_tc_supported(fa)) { KL(b, 3, launch_attn_tc_bwd(b->stream, fa, w.tc_err)); return PCPB_OK; }
+  if (fast && flash_supported(fa)) { KL(b, 3, launch_flash_bwd(b->stream, fa)); return PCPB_OK; }
+  AttnArgs at{};
+  at.qkn = a.qkn; at.qkv = a.qkv; at.o = a.o; at.mrow = a.mrow; at.lrow = a.lrow;
+  at.B = fa.B; at.T = fa.T; at.H = fa.H; at.Hkv = fa.Hkv; at.hd = fa.hd; at.scale = scale;
+  at.dout = w.dout; at.dqkn = w.dqkn; at.dqkv = w.dqkv; at.dkv_acc = w.dkv_acc;
+  KL(b, 3, launch_attn_bwd_generic(b->stream, dt, at));
+  return PCPB_OK;
+}
+
+// nanoGPT family: learned position embedding, LayerNorm (gamma, beta), fused c_attn, ReLU MLP, lm_head with bias,
+// plain cross entropy ignoring targets == -100 (models/nanogpt_small.mlir, models/nanogpt_medium_bf16.mlir).
+int forward_backward_gpt(pcpb_backend* b, const void* wts, const long long* ids, const long long* targets, float* grads,
+                         float* loss_out, bool backward) {
+  const ModelConfig& c = b->cfg;
+  Workspace& w = b->ws;
+  cudaStream_t st = b->stream;
+  const int dt = c.dtype, M = (int)c.M(), d = (int)c.d, F = (int)c.F, V = (int)c.V, L = (int)c.L, Tn = (int)c.T;
+  const int wq = 3 * d, Bn = (int)c.B;
+  const size_t es = dtype_size(dt);
+  auto W = [&](int i) { return (const void*)((const char*)wts + (size_t)c.params[i].offset * es); };
+  auto GR = [&](int i) { return grads + c.params[i].offset; };
+  float scale = (float)(1.0 / sqrt((double)c.hd));
+  if (dt == DT_BF16) {
+    uint32_t u; memcpy(&u, &scale, 4);
+    u = (u + 0x7FFFu + ((u >> 16) & 1u)) & 0xFFFF0000u;
+    memcpy(&scale, &u, 4);
+  }
+  KL(b, 1, launch_embed_pos_fwd(st, dt, W(0), W(1), ids, M, Tn, d, V, w.xs[0]));
+  for (int l = 0; l < L; ++l) {
+    LayerActs& a = w.layers[l];
+    const int p0 = 2 + 8 * l;                       // ln1.w ln1.b c_attn c_proj ln2.w ln2.b c_fc mlp.c_proj
+    KL(b, 1, launch_layernorm_fwd(st, dt, w.xs[l], W(p0), W(p0 + 1), M, d, a.h1, a.mu1, a.t1, a.m64_1));
+    G(b, a.h1, d, 1, W(p0 + 2), 1, d, a.qkv, wq, M, wq, d, EPI_STORE);
+    KL(b, 1, launch_copy_cols(st, dt, a.qkv, wq, a.qkn, 2 * d, M, 2 * d));          // q|k in the attention layout
+    int r = attention_fwd(b, a, scale);
+    if (r) return r;
+    G(b, a.o, d, 1, W(p0 + 3), 1, d, a.xmid, d, M, d, d, EPI_RESID, w.xs[l]);
+    KL(b, 1, launch_layernorm_fwd(st, dt, a.xmid, W(p0 + 4), W(p0 + 5), M, d, a.h2, a.mu2, a.t2, a.m64_2));
+    G(b, a.h2, d, 1, W(p0 + 6), 1, d, a.u, F, M, F, d, EPI_RELU, nullptr, a.a);
+    G(b, a.a, F, 1, W(p0 + 7), 1, F, w.xs[l + 1], d, M, d, F, EPI_RESID, a.xmid);
+  }
+  const int pf = 2 + 8 * L;                         // ln_f.w ln_f.b lm_head.w lm_head.b
+  KL(b, 1, launch_layernorm_fwd(st, dt, w.xs[L], W(pf), W(pf + 1), M, d, w.hf, w.muf, w.tf, w.m64f));
+  G(b, w.hf, d, 1, W(pf + 2), 1, d, w.logits, V, M, V, d, EPI_BIAS, W(pf + 3));
+  KL(b, 1, launch_count_valid(st, targets, M, c.ignore_index, w.count));
+  KL(b, 1, launch_softcap_ce(st, dt, w.logits, targets, M, V, 0.f, c.ignore_index, w.count, w.rowloss, backward ? 1 : 0));
+  KL(b, 1, launch_loss_finalize(st, w.rowloss, M, w.count, loss_out));
+  if (!backward) return PCPB_OK;
+
+  KL(b, 2, launch_colsum(st, dt, w.logits, M, V, w.cs_partial, GR(pf + 3)));       // d lm_head.b
+  G(b, w.logits, V, 1, W(pf + 2), d, 1, w.dh, d, M, d, V, EPI_STORE);              // d hf
+  G(b, w.logits, 1, V, w.hf, d, 1, GR(pf + 2), d, V, d, M, EPI_WGRAD);             // d lm_head.w
+  KL(b, 2, launch_layernorm_bwd(st, dt, w.xs[L], W(pf), w.muf, w.tf, w.m64f, w.dh, nullptr, M, d, w.dx, w.ln_partial,
+                                GR(pf), GR(pf + 1)));
+  for (int l = L - 1; l >= 0; --l) {
+    LayerActs& a = w.layers[l];
+    const int p0 = 2 + 8 * l;
+    G(b, w.dx, d, 1, W(p0 + 7), F, 1, w.du, F, M, F, d, EPI_DRELU, a.u);           // du
+    G(b, w.dx, 1, d, a.a, F, 1, GR(p0 + 7), F, d, F, M, EPI_WGRAD);                // d mlp.c_proj
+    G(b, w.du, 1, F, a.h2, d, 1, GR(p0 + 6), d, F, d, M, EPI_WGRAD);               // d c_fc
+    G(b, w.du, F, 1, W(p0 + 6), d, 1, w.dh, d, M, d, F, EPI_STORE);                // d h2
+    KL(b, 2, launch_layernorm_bwd(st, dt, a.xmid, W(p0 + 4), a.mu2, a.t2, a.m64_2, w.dh, w.dx, M, d, w.dx, w.ln_partial,
+                                  GR(p0 + 4), GR(p0 + 5)));
+    G(b, w.dx, d, 1, W(p0 + 3), d, 1, w.dout, d, M, d, d, EPI_STORE);              // d o
+    G(b, w.dx, 1, d, a.o, d, 1, GR(p0 + 3), d, d, d, M, EPI_WGRAD);                // d c_proj
+    int r = attention_bwd(b, a, scale);
+    if (r) return r;
+    KL(b, 1, launch_copy_cols(st, dt, w.dqkn, 2 * d, w.dqkv, wq, M, 2 * d));       // dq|dk next to dv
+    G(b, w.dqkv, 1, wq, a.h1, d, 1, GR(p0 + 2), d, wq, d, M, EPI_WGRAD);           // d c_attn
+    G(b, w.dqkv, wq, 1, W(p0 + 2), d, 1, w.dh, d, M, d, wq, EPI_STORE);            // d h1
+    KL(b, 2, launch_layernorm_bwd(st, dt, w.xs[l], W(p0), a.mu1, a.t1, a.m64_1, w.dh, w.dx, M, d, w.dx, w.ln_partial,
+                                  GR(p0), GR(p0 + 1)));
+  }
+  CK(b, cudaMemsetAsync(GR(0), 0, (size_t)c.params[0].numel * 4, st));
+  KL(b, 1, launch_embed_pos_bwd(st, dt, ids, Bn, Tn, d, V, w.dx, GR(0), GR(1)));
+  KL(b, 1, launch_round_guard_f32(st, dt, GR(0), (size_t)(c.params[0].numel + c.params[1].numel), 100.f));
   return PCPB_OK;
 }
 

@@ -23,6 +23,8 @@ struct Block {                     // one device allocation, shared by the buffe
 struct LayerActs {                 // saved forward values of one transformer layer (model dtype unless noted)
   void *h1, *qkv, *qkn, *o, *xmid, *h2, *u, *a;
   float *t1, *t2, *tq, *mrow, *lrow;
+  float *mu1 = nullptr, *mu2 = nullptr;          // nanoGPT: LayerNorm means (f32)
+  double *m64_1 = nullptr, *m64_2 = nullptr;     // nanoGPT: LayerNorm means of the f64 variance branch
 };
 
 struct Workspace {
@@ -41,6 +43,8 @@ struct Workspace {
   void *dx = nullptr, *dh = nullptr, *du = nullptr, *dout = nullptr, *dqkn = nullptr, *dqkv = nullptr;
   float* dkv_acc = nullptr;
   float* drow = nullptr;           // [B*H*T] attention-backward row scratch
+  float *muf = nullptr, *ln_partial = nullptr, *cs_partial = nullptr;   // nanoGPT: final LN mean, reduction scratch
+  double* m64f = nullptr;
   // data
   long long *ids = nullptr, *targets = nullptr;
   uint16_t *d_cos = nullptr, *d_sin = nullptr;

@@ -308,3 +308,159 @@ def nanochat_forward_mlir(cfg: NanochatConfig) -> str:
             f'      rope_cos: "0x{hdr}{cos_b.astype("<u2").tobytes().hex().upper()}"',
             "    }", "  }", "#-}", ""]
     return "\n".join(out)
+
+
+# ------------------------------------------------------------------------------------------------
+# nanoGPT family (tools/generate_nanogpt_small.py, tools/generate_nanogpt_medium_bf16.py)
+# ------------------------------------------------------------------------------------------------
+@dataclass
+class NanoGPTConfig:
+    vocab: int = 65
+    d_model: int = 64
+    n_layer: int = 2
+    n_head: int = 4
+    seq_len: int = 32
+    batch: int = 64
+    dtype: str = "f32"            # "f32" | "bf16"
+    mlp_ratio: int = 4
+
+    @property
+    def head_dim(self):
+        return self.d_model // self.n_head
+
+    def param_shapes(self):
+        d, f = self.d_model, self.mlp_ratio * self.d_model
+        s = [(self.vocab, d), (self.seq_len, d)]
+        for _ in range(self.n_layer):
+            s += [(d,), (d,), (3 * d, d), (d, d), (d,), (d,), (f, d), (d, f)]
+        s += [(d,), (d,), (self.vocab, d), (self.vocab,)]
+        return s
+
+    def num_params(self):
+        return int(sum(int(np.prod(x)) for x in self.param_shapes()))
+
+
+def nanogpt_forward_mlir(cfg: NanoGPTConfig) -> str:
+    """Forward graph of the nanoGPT family with the op sequence and cast points of models/nanogpt_small.mlir (f32)
+    and models/nanogpt_medium_bf16.mlir (bf16): learned token + position embeddings, pre-LayerNorm whose variance
+    is computed in f64, fused qkv projection split on the last dim, causal softmax (f32), ReLU MLP, final
+    LayerNorm, lm_head with bias computed in f32, cross entropy ignoring targets == -100."""
+    e = _Emitter()
+    B, T, d, V, H, hd = cfg.batch, cfg.seq_len, cfg.d_model, cfg.vocab, cfg.n_head, cfg.head_dim
+    F, dt, M = cfg.mlp_ratio * d, cfg.dtype, cfg.batch * cfg.seq_len
+    assert d % H == 0 and dt in ("f32", "bf16")
+    shapes = cfg.param_shapes()
+    nP = len(shapes)
+    args = [f"%arg{i}: {e.ty(s, dt)}" for i, s in enumerate(shapes)]
+    args += [f"%arg{nP}: {e.ty((B, T), 'i64')}", f"%arg{nP + 1}: {e.ty((B, T), 'i64')}"]
+    P = [(f"%arg{i}", tuple(s), dt) for i, s in enumerate(shapes)]
+    idx = (f"%arg{nP}", (B, T), "i64")
+    tgt = (f"%arg{nP + 1}", (B, T), "i64")
+
+    zero_f32 = e.const("0.000000e+00", (), "f32")
+    zero_f64 = e.const("0.000000e+00", (), "f64")
+    ninf_f32 = e.const("0xFF800000", (), "f32")
+    mask_fill = e.const("-6.553600e+04", (), "bf16") if dt == "bf16" else ninf_f32
+    eps_f32 = e.scalar("1.000000e-05", "f64", "f32")
+    d_f64 = e.splat(e.scalar(str(d), "i64", "f64"), (B, T, 1))
+    d_f32 = e.splat(e.scalar(str(d), "i64", "f32"), (B, T, 1))
+
+    def layernorm(x, w, b):
+        xf = e.convert(x, "f32") if dt != "f32" else x
+        x64 = e.convert(xf, "f64")
+        mean64 = e.bin("divide", e.reshape(e.reduce("add", x64, zero_f64, [2]), (B, T, 1)), d_f64)
+        c64 = e.bin("subtract", x64, e.bcast(mean64, (B, T, d), [0, 1, 2]))
+        var64 = e.bin("divide", e.reshape(e.reduce("add", e.bin("multiply", c64, c64), zero_f64, [2]), (B, T, 1)), d_f64)
+        var = e.convert(var64, "f32")
+        mean = e.bin("divide", e.reshape(e.reduce("add", xf, zero_f32, [2]), (B, T, 1)), d_f32)
+        r = e.un("rsqrt", e.bin("add", var, e.splat(eps_f32, (B, T, 1))))
+        y = e.bin("multiply", e.bin("subtract", xf, e.bcast(mean, (B, T, d), [0, 1, 2])), e.bcast(r, (B, T, d), [0, 1, 2]))
+        wf = e.convert(w, "f32") if dt != "f32" else w
+        bf = e.convert(b, "f32") if dt != "f32" else b
+        y = e.bin("add", e.bin("multiply", y, e.bcast(wf, (B, T, d), [2])), e.bcast(bf, (B, T, d), [2]))
+        return e.convert(y, dt) if dt != "f32" else y
+
+    def linear(x2d, w):
+        return e.dot(x2d, e.transpose(w, [1, 0]))
+
+    def gather_rows(table, indices, out_shape, offset_dim, ivd):
+        rows, width = table[1]
+        return e.emit(
+            f'"stablehlo.gather"({table[0]}, {indices[0]}) <{{dimension_numbers = #stablehlo.gather<offset_dims = [{offset_dim}], '
+            f'collapsed_slice_dims = [0], start_index_map = [0], index_vector_dim = {ivd}>, indices_are_sorted = false, '
+            f'slice_sizes = array<i64: 1, {width}>}}>', out_shape, table[2],
+            f"({e.ty(table[1], table[2])}, {e.ty(indices[1], 'i64')}) -> {e.ty(out_shape, table[2])}")
+
+    tok = gather_rows(P[0], idx, (B, T, d), 2, 2)
+    pos = gather_rows(P[1], e.iota((T,), 0), (T, d), 1, 1)
+    x = e.bin("add", tok, e.bcast(pos, (B, T, d), [1, 2]))
+
+    # masked_fill(tril == 0, fill): tril[i, j] = 1 where j <= i
+    tril = e.select(e.compare("LE", e.iota((T, T), 1), e.iota((T, T), 0)), e.const("1.000000e+00", (T, T), "f32"),
+                    e.const("0.000000e+00", (T, T), "f32"))
+    m4 = e.compare("EQ", e.reshape(tril, (1, 1, T, T)), e.splat(zero_f32, (1, 1, T, T)), kind="FLOAT")
+    mask = e.bcast(m4, (B, H, T, T), [0, 1, 2, 3])
+    fill = e.splat(mask_fill, (B, H, T, T))
+    scale = e.scalar(repr(1.0 / math.sqrt(hd)), "f64", dt)
+
+    for l in range(cfg.n_layer):
+        ln1w, ln1b, wqkv, wo, ln2w, ln2b, wfc, wpr = P[2 + 8 * l: 10 + 8 * l]
+        h = e.reshape(layernorm(x, ln1w, ln1b), (M, d))
+        qkv = e.reshape(linear(h, wqkv), (B, T, 3 * d))
+        q = e.slice(qkv, [(0, B), (0, T), (0, d)])
+        k = e.slice(qkv, [(0, B), (0, T), (d, 2 * d)])
+        v = e.slice(qkv, [(0, B), (0, T), (2 * d, 3 * d)])
+        heads = lambda t: e.transpose(e.reshape(t, (B, T, H, hd)), [0, 2, 1, 3])
+        k, q, v = heads(k), heads(q), heads(v)
+        kt = e.transpose(k, [0, 1, 3, 2])
+        s = e.dot(e.reshape(q, (B * H, T, hd)), e.reshape(kt, (B * H, hd, T)), batched=True)
+        s = e.bin("multiply", e.reshape(s, (B, H, T, T)), e.splat(scale, (B, H, T, T)))
+        s = e.select(mask, fill, s)
+        sf = e.convert(s, "f32") if dt != "f32" else s
+        mx = e.reshape(e.reduce("maximum", sf, ninf_f32, [3]), (B, H, T, 1))
+        ex = e.un("exponential", e.bin("subtract", sf, e.bcast(mx, (B, H, T, T), [0, 1, 2, 3])))
+        sm = e.reshape(e.reduce("add", ex, zero_f32, [3]), (B, H, T, 1))
+        p = e.bin("divide", ex, e.bcast(sm, (B, H, T, T), [0, 1, 2, 3]))
+        if dt != "f32":
+            p = e.convert(p, dt)
+        o = e.dot(e.reshape(p, (B * H, T, T)), e.reshape(v, (B * H, T, hd)), batched=True)
+        o = e.reshape(e.transpose(e.reshape(o, (B, H, T, hd)), [0, 2, 1, 3]), (B, T, d))
+        x = e.bin("add", x, e.reshape(linear(e.reshape(o, (M, d)), wo), (B, T, d)))
+        h = e.reshape(layernorm(x, ln2w, ln2b), (M, d))
+        u = e.reshape(linear(h, wfc), (B, T, F))
+        a = e.bin("maximum", u, e.const("0.000000e+00", (B, T, F), dt))
+        x = e.bin("add", x, e.reshape(linear(e.reshape(a, (M, F)), wpr), (B, T, d)))
+
+    lnfw, lnfb, wh, bh = P[-4:]
+    hf = e.reshape(layernorm(x, lnfw, lnfb), (M, d))
+    wt = e.transpose(wh, [1, 0])
+    if dt != "f32":                                   # the head runs in f32 (addmm on upcast operands), result -> bf16 -> f32
+        bhf = e.convert(bh, "f32")
+        z = e.dot(e.convert(hf, "f32"), e.convert(wt, "f32"))
+    else:
+        bhf = bh
+        z = e.dot(hf, wt)
+    one = e.scalar("1", "i64", "f32")
+    z = e.bin("multiply", z, e.splat(one, (M, V)))
+    z = e.bin("add", z, e.bcast(e.bin("multiply", bhf, e.splat(one, (V,))), (M, V), [1]))
+    if dt != "f32":
+        z = e.convert(e.convert(z, dt), "f32")
+    t1 = e.reshape(tgt, (M,))
+    mx = e.bcast(e.reshape(e.reduce("maximum", z, ninf_f32, [1]), (M, 1)), (M, V), [0, 1])
+    sh = e.bin("subtract", z, mx)
+    se = e.reshape(e.reduce("add", e.un("exponential", sh), zero_f32, [1]), (M, 1))
+    logp = e.bin("subtract", sh, e.bcast(e.un("log", se), (M, V), [0, 1]))
+    valid = e.compare("NE", t1, e.const("-100", (M,), "i64"))
+    safe_t = e.select(valid, t1, e.const("0", (M,), "i64"))
+    ij = e.concat(e.iota((M, 1, 1), 0), e.reshape(e.reshape(safe_t, (M, 1)), (M, 1, 1)), 2)
+    picked = e.emit(
+        f'"stablehlo.gather"({logp[0]}, {ij[0]}) <{{dimension_numbers = #stablehlo.gather<collapsed_slice_dims = [0, 1], '
+        f'start_index_map = [0, 1], index_vector_dim = 2>, slice_sizes = array<i64: 1, 1>}}>', (M, 1), "f32",
+        f"({e.ty((M, V), 'f32')}, {e.ty((M, 1, 2), 'i64')}) -> {e.ty((M, 1), 'f32')}")
+    nll = e.select(valid, e.un("negate", e.reshape(picked, (M,))), e.splat(zero_f32, (M,)))
+    cnt = e.convert(e.reduce("add", e.convert(valid, "i64"), e.const("0", (), "i64"), [0]), "f32")
+    loss = e.bin("divide", e.reduce("add", nll, zero_f32, [0]), cnt)
+    out = ["module {", f"  func.func @main({', '.join(args)}) -> tensor<f32> {{"]
+    out += e.lines
+    out += [f"    return {loss[0]} : tensor<f32>", "  }", "}", ""]
+    return "\n".join(out)

@@ -5,7 +5,7 @@ import torch
 from oracle.loader import FifoU16, uniform_tokens, zipf_tokens
 from oracle.optim import AdamConf, NesterovConf
 from oracle.worker import TrainingModule, inner_loop, outer_step
-from pcp_b200.export import NanochatConfig, nanochat_forward_mlir
+from pcp_b200.export import NanochatConfig, NanoGPTConfig, nanochat_forward_mlir, nanogpt_forward_mlir
 
 SMALL_F32 = dict(vocab=65, d_model=64, n_layer=2, n_head=4, n_kv_head=4, seq_len=32, batch=8, dtype="f32")
 GQA_F32 = dict(vocab=97, d_model=64, n_layer=2, n_head=4, n_kv_head=2, seq_len=24, batch=3, dtype="f32")
@@ -15,9 +15,29 @@ HD128_GQA_BF16 = dict(vocab=512, d_model=512, n_layer=1, n_head=4, n_kv_head=2, 
 HD128_F32 = dict(vocab=512, d_model=256, n_layer=1, n_head=2, n_kv_head=1, seq_len=64, batch=2, dtype="f32")
 
 
-def seeded_params(cfg: NanochatConfig, seed=0, std=0.02):
+GPT_SMALL_F32 = dict(vocab=65, d_model=64, n_layer=2, n_head=4, seq_len=32, batch=8, dtype="f32")
+GPT_ODD_F32 = dict(vocab=97, d_model=48, n_layer=1, n_head=3, seq_len=20, batch=3, dtype="f32")
+GPT_SMALL_BF16 = dict(vocab=256, d_model=64, n_layer=2, n_head=4, seq_len=32, batch=4, dtype="bf16")
+
+
+def make_model(cfgd):
+    """(config, forward graph text) of either family; nanoGPT configs have no n_kv_head."""
+    if "n_kv_head" in cfgd:
+        cfg = NanochatConfig(**cfgd)
+        return cfg, nanochat_forward_mlir(cfg)
+    cfg = NanoGPTConfig(**cfgd)
+    return cfg, nanogpt_forward_mlir(cfg)
+
+
+def seeded_params(cfg, seed=0, std=0.02):
     g = torch.Generator().manual_seed(seed)
-    return [torch.randn(s, generator=g) * std for s in cfg.param_shapes()]
+    out = []
+    for s in cfg.param_shapes():
+        p = torch.randn(s, generator=g) * std
+        if len(s) == 1 and isinstance(cfg, NanoGPTConfig):
+            p = p + 1.0 if len(out) % 2 == 0 else p        # LayerNorm weights near 1 (even slots are .w in every group)
+        out.append(p)
+    return out
 
 
 def flat(ts):
@@ -25,10 +45,10 @@ def flat(ts):
                            else t.detach().to(torch.float32).reshape(-1).numpy() for t in ts])
 
 
-def split(flat_arr, cfg: NanochatConfig):
+def split(flat_arr, cfg):
     out, at = [], 0
     for s in cfg.param_shapes():
-        n = s[0] * s[1]
+        n = int(np.prod(s))
         out.append(flat_arr[at:at + n].reshape(s))
         at += n
     return out
@@ -39,7 +59,7 @@ def rel_err(a, b):
     return float(np.abs(a - b).max() / (np.abs(b).max() + 1e-30))
 
 
-def tokens_for(cfg: NanochatConfig, steps, seed, zipf=False):
+def tokens_for(cfg, steps, seed, zipf=False):
     n = steps * (cfg.batch * cfg.seq_len + 1)
     return zipf_tokens(n, cfg.vocab, 1.1, seed) if zipf else uniform_tokens(n, cfg.vocab, seed)
 

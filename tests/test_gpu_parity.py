@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import (GQA_F32, HD128_BF16, HD128_F32, HD128_GQA_BF16, SMALL_BF16, SMALL_F32, bf16_bits_to_f32, f32_to_bf16_trunc_bits,
+from helpers import (GPT_ODD_F32, GPT_SMALL_BF16, GPT_SMALL_F32, GQA_F32, HD128_BF16, HD128_F32, HD128_GQA_BF16, make_model, SMALL_BF16, SMALL_F32, bf16_bits_to_f32, f32_to_bf16_trunc_bits,
                      flat, rel_err, seeded_params, split, tokens_for)
 from oracle.loader import FifoU16
 from oracle.optim import AdamConf, NesterovConf, adamw_update
@@ -34,15 +34,15 @@ def _grads_via_abi(be, cfg, params, x, y):
 
 
 @pytest.mark.parametrize("cfgd,tol", [(SMALL_F32, 1e-4), (GQA_F32, 1e-4), (HD128_F32, 1e-4), (SMALL_BF16, 2e-2),
-                                      (HD128_BF16, 2e-2)])
+                                      (HD128_BF16, 2e-2), (GPT_SMALL_F32, 1e-4), (GPT_ODD_F32, 1e-4),
+                                      (GPT_SMALL_BF16, 2e-2)])
 def test_compute_gradients_matches_oracle(cfgd, tol):
-    cfg = NanochatConfig(**cfgd)
-    text = nanochat_forward_mlir(cfg)
+    cfg, text = make_model(cfgd)
     mod = TrainingModule(text)
     params = seeded_params(cfg, seed=0, std=0.05)
     ds = FifoU16(tokens_for(cfg, 1, seed=1))
     x, y = ds.get_batch(cfg.batch, cfg.seq_len)
-    y[0, :2] = -1                                         # ignored targets
+    y[0, :2] = -1 if "n_kv_head" in cfgd else -100        # ignored targets
     g_ref, loss_ref = mod.compute_gradients(params, torch.from_numpy(x), torch.from_numpy(y))
     with Backend(0) as be:
         be.load_session(text)
@@ -191,23 +191,22 @@ def _close(got, want, tol, dtype):
         assert err <= tol, err
 
 
-def _run_diloco(cfgd, workers, tau, rounds, lr, tol_loss, tol_param, zipf=False):
-    cfg = NanochatConfig(**cfgd)
-    text = nanochat_forward_mlir(cfg)
+def _run_diloco(cfgd, workers, tau, rounds, lr, tol_loss, tol_param, zipf=False, adam=None):
+    cfg, text = make_model(cfgd)
     mod = TrainingModule(text)
     dt = F32 if cfg.dtype == "f32" else BF16
     master = seeded_params(cfg, seed=0, std=0.02)
     if cfg.dtype == "bf16":
         master = [torch.from_numpy(bf16_bits_to_f32(f32_to_bf16_trunc_bits(p.numpy())).reshape(p.shape)) for p in master]
     vel = [torch.zeros_like(p) for p in master]
-    conf = AdamConf(learning_rate=lr)
+    conf = AdamConf(learning_rate=lr, **(adam or {}))
     nconf = NesterovConf(0.7, 0.9)
     toks = [[tokens_for(cfg, tau, seed=100 * r + w, zipf=zipf) for w in range(workers)] for r in range(rounds)]
     bes = [Backend(0) for _ in range(workers)]
     try:
         for b in bes:
             b.load_session(text)
-            b.set_adam(learning_rate=lr)
+            b.set_adam(conf.learning_rate, conf.beta1, conf.beta2, conf.epsilon, conf.weight_decay, conf.max_grad_norm)
         for w, b in enumerate(bes):
             b.outer_attach_local(w, bes)
         blob0 = flat(master)
@@ -249,6 +248,14 @@ def test_diloco_f32_20_steps_2_rounds():
     """BASELINE config 1 protocol at the shipped small shape: 2 workers, 2 outer rounds; 20 inner steps in total
     per worker (H=10), loss and parameters within 1e-4."""
     _run_diloco(SMALL_F32, workers=2, tau=10, rounds=2, lr=3e-4, tol_loss=1e-4, tol_param=1e-4)
+
+
+def test_diloco_nanogpt_small_f32_baseline_config():
+    """BASELINE config 1 at the shipped nanoGPT-small shape (2L / 64 wide / T=32): fp32, AdamW lr 3e-4, betas
+    (0.9, 0.95), weight decay 0.1, DiLoCo with 2 workers, H=10 inner steps, Nesterov 0.7 / 0.9, two outer rounds
+    (20 inner steps per worker): per-step loss and parameters within 1e-4."""
+    _run_diloco(GPT_SMALL_F32, workers=2, tau=10, rounds=2, lr=3e-4, tol_loss=1e-4, tol_param=1e-4,
+                adam=dict(beta1=0.9, beta2=0.95, weight_decay=0.1))
 
 
 def test_diloco_bf16_3_workers():

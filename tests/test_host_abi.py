@@ -54,8 +54,10 @@ def test_inspect_shipped_reference_graphs(lib_built):
     assert f["total_params"] == 39321600
     f = inspect_artifact(open(os.path.join(REF, "models", "nanochat_d12_b6_t2048.mlir")).read())
     assert (f["d_model"], f["n_layer"], f["head_dim"], f["dtype"], f["total_params"]) == (768, 12, 128, bk.F32, 185597952)
-    with pytest.raises(BackendError):
-        inspect_artifact(open(os.path.join(REF, "models", "nanogpt_small.mlir")).read())
+    f = inspect_artifact(open(os.path.join(REF, "models", "nanogpt_small.mlir")).read())          # nanoGPT family
+    assert (f["d_model"], f["n_layer"], f["n_head"], f["head_dim"], f["num_tensors"], f["total_params"]) == (64, 2, 4, 16, 22, 109377)
+    f = inspect_artifact(open(os.path.join(REF, "models", "nanogpt_medium_bf16.mlir")).read())
+    assert (f["d_model"], f["n_layer"], f["n_head"], f["dtype"], f["total_params"]) == (256, 4, 8, bk.BF16, 3314432)
 
 
 def test_no_cpu_fallback(lib_built):

@@ -11,7 +11,7 @@ from oracle import sanitizer
 from oracle.loader import ChunkExhausted, ChunkTooSmall, FifoU16
 from oracle.optim import AdamConf
 from oracle.worker import TrainingModule, inner_loop
-from pcp_b200 import NanochatConfig, nanochat_forward_mlir
+from pcp_b200 import NanochatConfig, NanoGPTConfig, nanochat_forward_mlir, nanogpt_forward_mlir
 from pcp_b200.export import rope_tables
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
@@ -109,3 +109,24 @@ def test_recorded_forward_loss_scale():
     ids = torch.randint(0, 65, (64, 32), generator=g)
     loss = float(mod.forward(params, ids, ids))
     assert 4.0 < loss < 4.5
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "models")), reason="reference tree not present")
+def test_nanogpt_exporter_equals_shipped_graph():
+    """models/nanogpt_small.mlir (f32, LayerNorm variance in f64, ReLU MLP, lm_head bias, ignore_index -100): loss and
+    all 22 gradients bit-identical between the shipped graph and the exporter's.  (The bf16 graph
+    models/nanogpt_medium_bf16.mlir was checked the same way once; it takes 20 s on the CPU.)"""
+    cfg = NanoGPTConfig(vocab=65, d_model=64, n_layer=2, n_head=4, seq_len=32, batch=64, dtype="f32")
+    shipped = TrainingModule(open(os.path.join(REF, "models", "nanogpt_small.mlir")).read())
+    mine = TrainingModule(nanogpt_forward_mlir(cfg))
+    assert shipped.param_shapes == mine.param_shapes and cfg.num_params() == 109377
+    g = torch.Generator().manual_seed(4)
+    params = [torch.randn(s, generator=g) * 0.05 for s in cfg.param_shapes()]
+    ids = torch.randint(0, 65, (64, 32), generator=g)
+    tg = torch.randint(0, 65, (64, 32), generator=g)
+    tg[1, :4] = -100
+    ga, la = shipped.compute_gradients(params, ids, tg)
+    gb, lb = mine.compute_gradients(params, ids, tg)
+    assert float(la) == float(lb)
+    for x, y in zip(ga, gb):
+        assert torch.equal(x, y)
