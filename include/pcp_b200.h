@@ -94,7 +94,8 @@ int pcpb_execute_host(pcpb_backend* b, const char* fn, const void* const* in, co
 /* One contraction of the op surface (stablehlo.dot_general as the reference's graphs use it, src/core/ops.zig and
  * matmulVJP src/autodiff/vjp_rules.zig:426-496), on device buffers of the loaded model's dtype:
  *   C[M,N] = epilogue(sum_k A(m,k) B(k,n)),  A(m,k) = A[m*sam + k*sak],  B(k,n) = B[k*sbk + n*sbn]
- * epilogue: 0 store, 1 residual add (R), 2 store + relu^2 into C2, 3 relu^2 backward at R, 4 weight gradient (f32 C).
+ * epilogue: 0 store, 1 residual add (R), 2 store + relu^2 into C2, 3 relu^2 backward at R, 4 weight gradient (f32 C),
+ *           5 store + relu into C2, 6 relu backward at R, 7 add bias R[N].
  * path: 0 = pick (tensor cores when the shape allows), 1 = generic kernel, 2 = tensor-core kernel or error. */
 int pcpb_op_gemm(pcpb_backend* b, int path, const pcpb_buffer* A, long long sam, long long sak, const pcpb_buffer* B,
                  long long sbk, long long sbn, pcpb_buffer* C, long long ldc, const pcpb_buffer* R, pcpb_buffer* C2,

@@ -8,11 +8,13 @@
 //   dQ        rows = queries; per sub-tile of keys:  S = Q K^T, dP = dO V^T  ->  dS  ->  dQ += dS K
 //   dK, dV    rows = keys;    per sub-tile of queries: S^T = K Q^T, dP^T = V dO^T -> P^T, dS^T
 //                                                       -> dV += P^T dO, dK += dS^T Q
-// Warp roles (320 threads): warp 0 TMA producer (3-stage ring of sub-tile pairs), warp 1 MMA issuer and owner of the
-// tensor-memory allocation, warps 2-9 element-wise: each thread owns one row and half of the 64 score columns, reads them with
-// tcgen05.ld, does the softmax / softmax-backward arithmetic and writes the bf16 result into a 128-byte-swizzled
+// Warp roles (576 threads): warp 0 TMA producer (3-stage ring of sub-tile pairs), warp 1 MMA issuer and owner of the
+// tensor-memory allocation, warps 2-17 element-wise: each thread owns one row and 16 of the 64 score columns, reads them
+// with tcgen05.ld, does the softmax / softmax-backward arithmetic and writes the bf16 result into a 128-byte-swizzled
 // shared-memory tile that the next MMA consumes as its A operand.  Score tiles are double-buffered in tensor memory
-// so the MMAs of sub-tile i+1 overlap the arithmetic of sub-tile i.
+// so the MMAs of sub-tile i+1 overlap the arithmetic of sub-tile i.  The element-wise arithmetic is the bottleneck of
+// the kernel (about 8192 exponentials per sub-tile against 0.4 us of tensor work), so it works on bf16 pairs: one
+// cvt.rn.bf16x2 and one mul.bf16x2 reproduce the two roundings of a score, one more pair of them the rounding of dS.
 //
 // A streamed [64 x 128] sub-tile serves two roles with the same bytes: "K-major" B operand of the score product
 // (contraction over head_dim) and "MN-major" B operand of the output product (contraction over its 64 rows).
@@ -29,12 +31,19 @@ namespace pcpb {
 namespace {
 
 constexpr int HD = 128;
-constexpr int NST = 3;                         // ring stages
+#ifndef PCPB_ATC_NST_FWD
+#define PCPB_ATC_NST_FWD 3
+#endif
+#ifndef PCPB_ATC_NST_DQ
+#define PCPB_ATC_NST_DQ 3
+#endif
 constexpr int SUB_BYTES = 64 * HD * 2;         // one streamed sub-tile: 16 KB
 constexpr int STAGE_BYTES = 2 * SUB_BYTES;     // (C1, C2)
 constexpr int TILE_BYTES = 128 * HD * 2;       // one resident tile: 32 KB
 constexpr int E_BYTES = 128 * 64 * 2;          // one element-wise result tile: 16 KB
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr int N_EW = 16;                       // element-wise warps
+constexpr int N_THREADS = 64 + 32 * N_EW;
 
 enum { MODE_FWD = 0, MODE_DQ = 1, MODE_DKV = 2 };
 
@@ -48,14 +57,17 @@ struct AtcParams {
 };
 
 template <int MODE> struct AtcCfg {
+  static constexpr int NST = (MODE == MODE_FWD) ? PCPB_ATC_NST_FWD : (MODE == MODE_DQ) ? PCPB_ATC_NST_DQ : 3;   // ring stages
   static constexpr int N_RES = (MODE == MODE_FWD) ? 1 : 2;
   static constexpr int N_E = (MODE == MODE_DKV) ? 2 : 1;
-  static constexpr int STAT_BYTES = (MODE == MODE_DKV) ? 8 * 2 * 160 * 4 : 2 * 128 * 2 * 4;   // DKV: per warp, double-buffered; FWD: row-half exchange
+  // DKV: per warp, double-buffered, six statistics of 16 columns; FWD: exchange of the four partial (max, sum) of a row
+  static constexpr int STAT_BYTES = (MODE == MODE_DKV) ? N_EW * 2 * 96 * 4 : 4 * 128 * 2 * 4;
   static constexpr int OFF_RING = N_RES * TILE_BYTES;
   static constexpr int OFF_E = OFF_RING + NST * STAGE_BYTES;
   static constexpr int OFF_STAT = OFF_E + N_E * E_BYTES;
   static constexpr int OFF_BAR = OFF_STAT + STAT_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+  static_assert(SMEM_BYTES <= 232448, "more shared memory than one CTA can have");
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -63,65 +75,60 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// f32 -> bf16 precision, round to nearest even, on the integer pipe (the conversion unit is the bottleneck of the
-// element-wise warps; inputs are finite or +-inf)
-__device__ __forceinline__ float r16(float x) {
-  uint32_t u = __float_as_uint(x);
-  u += 0x7FFFu + ((u >> 16) & 1u);
-  return __uint_as_float(u & 0xFFFF0000u);
-}
-
-// Optional instrumentation (-DPCPB_ATC_TIMING): cycles spent in each bounded wait, summed over warps and CTAs.
+// Optional instrumentation (-DPCPB_ATC_TIMING): cycles spent in each bounded wait (and in the two MMA issue loops),
+// accumulated in registers and added to global counters once per warp when the CTA ends.
 #ifdef PCPB_ATC_TIMING
-__device__ unsigned long long g_atc_t[32];
+__device__ unsigned long long g_atc_t[96];            // 32 counters per kernel mode
+#define ATC_T0() const long long t_sec0 = clock64()
+#define ATC_T1(slot) tacc[slot] += clock64() - t_sec0
+#else
+#define ATC_T0()
+#define ATC_T1(slot)
 #endif
-__device__ __forceinline__ bool twait(int code, uint32_t bar, uint32_t parity, int* err) {
+__device__ __forceinline__ bool twait(int code, uint32_t bar, uint32_t parity, int* err, long long& acc) {
 #ifdef PCPB_ATC_TIMING
   const long long t0 = clock64();
   const bool r = mbar_wait(bar, parity, err, code);
-  if ((threadIdx.x & 31) == 0) atomicAdd(&g_atc_t[code], (unsigned long long)(clock64() - t0));
+  acc += clock64() - t0;
   return r;
 #else
   return mbar_wait(bar, parity, err, code);
 #endif
 }
 
-// Write 32 consecutive k-values (columns c0 .. c0+31 of row r) of a [128 x 64] bf16 A-operand tile (one 128-byte
-// swizzle atom per row: 16-byte chunk j of row r lives at chunk position j ^ (r & 7)).
-__device__ __forceinline__ void store_e32(uint32_t ebase, int r, int c0, const float (&v)[32]) {
+// Write 16 consecutive k-values (columns c0 .. c0+15 of row r, as eight bf16 pairs) of a [128 x 64] bf16 A-operand
+// tile (one 128-byte swizzle atom per row: 16-byte chunk j of row r lives at chunk position j ^ (r & 7)).
+__device__ __forceinline__ void store_e16(uint32_t ebase, int r, int c0, const uint32_t (&w)[8]) {
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
+  for (int j = 0; j < 2; ++j) {
     const int kc = (c0 >> 3) + j;
     const uint32_t addr = ebase + (uint32_t)r * 128u + (uint32_t)((kc ^ (r & 7)) << 4);
-    const uint32_t w0 = pack2(v[8 * j + 0], v[8 * j + 1]), w1 = pack2(v[8 * j + 2], v[8 * j + 3]);
-    const uint32_t w2 = pack2(v[8 * j + 4], v[8 * j + 5]), w3 = pack2(v[8 * j + 6], v[8 * j + 7]);
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * j]), "r"(w[4 * j + 1]), "r"(w[4 * j + 2]),
+                 "r"(w[4 * j + 3]) : "memory");
   }
 }
 
-// Store 64 consecutive output columns of one row (f32 accumulators in tensor memory at taddr) as bf16 to dst.
+// Store 32 consecutive output columns of one row (f32 accumulators in tensor memory at taddr) as bf16 to dst.
 __device__ __forceinline__ void store_out_cols(uint32_t taddr, bf16* dst) {
-#pragma unroll 1
-  for (int c = 0; c < 64; c += 32) {
-    uint32_t r[32];
-    tmem_ld32(taddr + (uint32_t)c, r);
+  uint32_t r[32];
+  tmem_ld32(taddr, r);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      uint4 v;
-      v.x = pack2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
-      v.y = pack2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-      v.z = pack2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-      v.w = pack2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-      *reinterpret_cast<uint4*>(dst + c + 8 * j) = v;
-    }
+  for (int j = 0; j < 4; ++j) {
+    uint4 v;
+    v.x = pack2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+    v.y = pack2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+    v.z = pack2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+    v.w = pack2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+    *reinterpret_cast<uint4*>(dst + 8 * j) = v;
   }
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(N_THREADS, 1)
 k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CUtensorMap tm_qkv,
           const __grid_constant__ CUtensorMap tm_do, const AtcParams p) {
   using Cfg = AtcCfg<MODE>;
+  constexpr int NST = Cfg::NST;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
@@ -135,8 +142,9 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
                  res_bar = efull_bar + 24, comb_bar = efull_bar + 32, tmem_slot = efull_bar + 40;
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + Cfg::OFF_BAR + 8 * (2 * NST + 4) + 40);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = uniform_warp_idx(), lane = threadIdx.x & 31;
   const int grp = p.H / p.Hkv;
+  long long tacc[12] = {};                                   // wait cycles by role (instrumented builds only)
 #ifdef PCPB_ATC_TIMING
   const long long t_cta0 = clock64();
 #endif
@@ -160,8 +168,8 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NST; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int t = 0; t < 2; ++t) { mbar_init(tfull_bar(t), 1); mbar_init(tempty_bar(t), 8); }
-    mbar_init(efull_bar, 8); mbar_init(eempty_bar, 1); mbar_init(out_bar, 1); mbar_init(res_bar, 1); mbar_init(comb_bar, 8);
+    for (int t = 0; t < 2; ++t) { mbar_init(tfull_bar(t), 1); mbar_init(tempty_bar(t), N_EW); }
+    mbar_init(efull_bar, N_EW); mbar_init(eempty_bar, 1); mbar_init(out_bar, 1); mbar_init(res_bar, 1); mbar_init(comb_bar, N_EW);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -179,102 +187,105 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
 
   if (warp == 0) {
     // =========================== TMA producer ===========================
-    if (lane == 0) {
-      auto load_tile128 = [&](uint32_t dst, const CUtensorMap* m, int x, int y) {
-        tma_load_2d(dst, m, res_bar, x, y);           tma_load_2d(dst + 8192, m, res_bar, x, y + 64);
-        tma_load_2d(dst + 16384, m, res_bar, x + 64, y); tma_load_2d(dst + 24576, m, res_bar, x + 64, y + 64);
-      };
-      mbar_expect_tx(res_bar, Cfg::N_RES * TILE_BYTES);
-      if (MODE == MODE_FWD) load_tile128(sRes, &tm_qkn, xq, row_base + r0);
-      if (MODE == MODE_DQ) { load_tile128(sRes, &tm_qkn, xq, row_base + r0); load_tile128(sRes + TILE_BYTES, &tm_do, xq, row_base + r0); }
-      if (MODE == MODE_DKV) { load_tile128(sRes, &tm_qkn, xk, row_base + r0); load_tile128(sRes + TILE_BYTES, &tm_qkv, xv, row_base + r0); }
-      int armed[NST] = {0, 0, 0};
-      bool ok = true;
-      for (int g = 0; g < total_g && ok; ++g) {
-        const int s = g % NST;
-        if (!(ok = twait(11, empty_bar(s), (((uint32_t)g / NST) & 1u) ^ 1u, p.err))) break;
-        const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
-        const bool stats_pass = (MODE == MODE_FWD) && g < n_it;
-        mbar_expect_tx(full_bar(s), stats_pass ? SUB_BYTES : STAGE_BYTES);
-        armed[s] += 1;
-        if (MODE == MODE_DKV) {
-          const int hh = h + g / n_q, y = row_base + r0 + (g % n_q) * 64;
-          tma_load_2d(c1, &tm_qkn, full_bar(s), hh * HD, y); tma_load_2d(c1 + 8192, &tm_qkn, full_bar(s), hh * HD + 64, y);
-          tma_load_2d(c2, &tm_do, full_bar(s), hh * HD, y);  tma_load_2d(c2 + 8192, &tm_do, full_bar(s), hh * HD + 64, y);
-        } else {
-          const int y = row_base + ((MODE == MODE_FWD) ? (g % n_it) : g) * 64;
-          tma_load_2d(c1, &tm_qkn, full_bar(s), xk, y); tma_load_2d(c1 + 8192, &tm_qkn, full_bar(s), xk + 64, y);
-          if (!stats_pass) { tma_load_2d(c2, &tm_qkv, full_bar(s), xv, y); tma_load_2d(c2 + 8192, &tm_qkv, full_bar(s), xv + 64, y); }
-        }
+    // All 32 lanes run the loop (warp-uniform control flow and addresses); one elected lane issues.
+    auto load_tile128 = [&](uint32_t dst, const CUtensorMap* m, int x, int y) {
+      tma_load_2d_elect(dst, m, res_bar, x, y);              tma_load_2d_elect(dst + 8192, m, res_bar, x, y + 64);
+      tma_load_2d_elect(dst + 16384, m, res_bar, x + 64, y); tma_load_2d_elect(dst + 24576, m, res_bar, x + 64, y + 64);
+    };
+    mbar_expect_tx_elect(res_bar, Cfg::N_RES * TILE_BYTES);
+    if (MODE == MODE_FWD) load_tile128(sRes, &tm_qkn, xq, row_base + r0);
+    if (MODE == MODE_DQ) { load_tile128(sRes, &tm_qkn, xq, row_base + r0); load_tile128(sRes + TILE_BYTES, &tm_do, xq, row_base + r0); }
+    if (MODE == MODE_DKV) { load_tile128(sRes, &tm_qkn, xk, row_base + r0); load_tile128(sRes + TILE_BYTES, &tm_qkv, xv, row_base + r0); }
+    bool ok = true;
+    int g = 0;
+    for (; g < total_g; ++g) {
+      const int s = g % NST;
+      ok = __all_sync(0xffffffffu, twait(11, empty_bar(s), (((uint32_t)g / NST) & 1u) ^ 1u, p.err, tacc[0]));
+      if (!ok) break;
+      const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
+      const bool stats_pass = (MODE == MODE_FWD) && g < n_it;
+      mbar_expect_tx_elect(full_bar(s), stats_pass ? SUB_BYTES : STAGE_BYTES);
+      if (MODE == MODE_DKV) {
+        const int hh = h + g / n_q, y = row_base + r0 + (g % n_q) * 64;
+        tma_load_2d_elect(c1, &tm_qkn, full_bar(s), hh * HD, y); tma_load_2d_elect(c1 + 8192, &tm_qkn, full_bar(s), hh * HD + 64, y);
+        tma_load_2d_elect(c2, &tm_do, full_bar(s), hh * HD, y);  tma_load_2d_elect(c2 + 8192, &tm_do, full_bar(s), hh * HD + 64, y);
+      } else {
+        const int y = row_base + ((MODE == MODE_FWD) ? (g % n_it) : g) * 64;
+        tma_load_2d_elect(c1, &tm_qkn, full_bar(s), xk, y); tma_load_2d_elect(c1 + 8192, &tm_qkn, full_bar(s), xk + 64, y);
+        if (!stats_pass) { tma_load_2d_elect(c2, &tm_qkv, full_bar(s), xv, y); tma_load_2d_elect(c2 + 8192, &tm_qkv, full_bar(s), xv + 64, y); }
       }
-      if (!ok) {
-        for (int s = 0; s < NST; ++s)
-          if (armed[s] > 0) {
-            const uint32_t ph = (uint32_t)(armed[s] - 1) & 1u;
-            for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(full_bar(s), ph)) break;
-          }
-        for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(res_bar, 0)) break;
+    }
+    if (!ok) {
+      // gave up after g loads were armed: wait (bounded) for the copies still in flight before the CTA may exit
+      for (int j = (g > NST ? g - NST : 0); j < g; ++j) {
+        const uint32_t ph = ((uint32_t)j / NST) & 1u;
+        for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(full_bar(j % NST), ph)) break;
       }
+      for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(res_bar, 0)) break;
     }
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
-    if (lane == 0) {
-      // score products: M=128, N=64, A and B K-major; output products: M=128, N=128, A K-major, B MN-major
-      constexpr uint32_t ID_T = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-      constexpr uint32_t ID_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-      bool ok = twait(12, res_bar, 0, p.err);
-      auto issue_T = [&](int g, bool release_stage) -> bool {
-        const int s = g % NST, buf = g & 1;
-        if (!twait(13, full_bar(s), ((uint32_t)g / NST) & 1u, p.err)) return false;
-        if (!twait(14, tempty_bar(buf), (((uint32_t)g >> 1) & 1u) ^ 1u, p.err)) return false;
-        tc_fence_after();
-        const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
+    // All 32 lanes run the loops and the waits; one elected lane issues the MMAs and the commits.
+    // score products: M=128, N=64, A and B K-major; output products: M=128, N=128, A K-major, B MN-major
+    constexpr uint32_t ID_T = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    constexpr uint32_t ID_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    bool ok = __all_sync(0xffffffffu, twait(12, res_bar, 0, p.err, tacc[1]));
+    auto issue_T = [&](int g, bool release_stage) -> bool {
+      const int s = g % NST, buf = g & 1;
+      if (!__all_sync(0xffffffffu, twait(13, full_bar(s), ((uint32_t)g / NST) & 1u, p.err, tacc[2]))) return false;
+      if (!__all_sync(0xffffffffu, twait(14, tempty_bar(buf), (((uint32_t)g >> 1) & 1u) ^ 1u, p.err, tacc[3]))) return false;
+      tc_fence_after();
+      ATC_T0();
+      const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t ao = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
-          const uint32_t bo = (uint32_t)(ks >> 2) * 8192u + (uint32_t)(ks & 3) * 32u;
-          mma_bf16(t1_col(buf), make_desc(sRes + ao, 16, 1024), make_desc(c1 + bo, 16, 1024), ID_T, ks > 0);
-          if (MODE != MODE_FWD)
-            mma_bf16(t2_col(buf), make_desc(sRes + TILE_BYTES + ao, 16, 1024), make_desc(c2 + bo, 16, 1024), ID_T, ks > 0);
-        }
-        if (release_stage) mma_commit(empty_bar(s));
-        mma_commit(tfull_bar(buf));
-        return true;
-      };
-      int g = 0;
-      if (MODE == MODE_FWD)
-        for (; g < n_it && ok; ++g) ok = issue_T(g, true);
-      const int g0 = g;
-      if (ok) ok = issue_T(g0, false);
-      for (int it = 0; it < n_it && ok; ++it) {
-        if (it + 1 < n_it && !(ok = issue_T(g0 + it + 1, false))) break;
-        if (!(ok = twait(15, efull_bar, (uint32_t)it & 1u, p.err))) break;
-        tc_fence_after();
-        const int s = (g0 + it) % NST;
-        const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
-          const uint64_t e1 = make_desc(sE + ks * 32u, 16, 1024);
-          if (MODE == MODE_FWD) mma_bf16(out1, e1, make_desc(c2 + ks * 2048u, 8192, 1024), ID_O, acc);
-          if (MODE == MODE_DQ) mma_bf16(out1, e1, make_desc(c1 + ks * 2048u, 8192, 1024), ID_O, acc);
-          if (MODE == MODE_DKV) {
-            mma_bf16(out1, e1, make_desc(c2 + ks * 2048u, 8192, 1024), ID_O, acc);
-            mma_bf16(out2, make_desc(sE + E_BYTES + ks * 32u, 16, 1024), make_desc(c1 + ks * 2048u, 8192, 1024), ID_O, acc);
-          }
-        }
-        mma_commit(empty_bar(s));
-        mma_commit(eempty_bar);
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t ao = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
+        const uint32_t bo = (uint32_t)(ks >> 2) * 8192u + (uint32_t)(ks & 3) * 32u;
+        mma_bf16_elect(t1_col(buf), make_desc(sRes + ao, 16, 1024), make_desc(c1 + bo, 16, 1024), ID_T, ks > 0);
+        if (MODE != MODE_FWD)
+          mma_bf16_elect(t2_col(buf), make_desc(sRes + TILE_BYTES + ao, 16, 1024), make_desc(c2 + bo, 16, 1024), ID_T, ks > 0);
       }
-      if (ok) mma_commit(out_bar);
+      if (release_stage) mma_commit_elect(empty_bar(s));
+      mma_commit_elect(tfull_bar(buf));
+      ATC_T1(10);
+      return true;
+    };
+    int g = 0;
+    if (MODE == MODE_FWD)
+      for (; g < n_it && ok; ++g) ok = issue_T(g, true);
+    const int g0 = g;
+    if (ok) ok = issue_T(g0, false);
+    for (int it = 0; it < n_it && ok; ++it) {
+      if (it + 1 < n_it && !(ok = issue_T(g0 + it + 1, false))) break;
+      if (!(ok = __all_sync(0xffffffffu, twait(15, efull_bar, (uint32_t)it & 1u, p.err, tacc[4])))) break;
+      tc_fence_after();
+      ATC_T0();
+      const int s = (g0 + it) % NST;
+      const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
+        const uint64_t e1 = make_desc(sE + ks * 32u, 16, 1024);
+        if (MODE == MODE_FWD) mma_bf16_elect(out1, e1, make_desc(c2 + ks * 2048u, 8192, 1024), ID_O, acc);
+        if (MODE == MODE_DQ) mma_bf16_elect(out1, e1, make_desc(c1 + ks * 2048u, 8192, 1024), ID_O, acc);
+        if (MODE == MODE_DKV) {
+          mma_bf16_elect(out1, e1, make_desc(c2 + ks * 2048u, 8192, 1024), ID_O, acc);
+          mma_bf16_elect(out2, make_desc(sE + E_BYTES + ks * 32u, 16, 1024), make_desc(c1 + ks * 2048u, 8192, 1024), ID_O, acc);
+        }
+      }
+      mma_commit_elect(empty_bar(s));
+      mma_commit_elect(eempty_bar);
+      ATC_T1(11);
     }
+    if (ok) mma_commit_elect(out_bar);
   } else {
     // =========================== element-wise warps ===========================
-    // Eight warps: two per tensor-memory lane quarter; each thread owns one row and one 32-column half of every
-    // 64-column score sub-tile.
-    const int q = warp & 3, row = q * 32 + lane, half = (warp - 2) >> 2, ch = half * 32;
+    // Sixteen warps: four per tensor-memory lane quarter; each thread owns one row and 16 of the 64 columns of every
+    // score sub-tile.
+    const int q = warp & 3, row = q * 32 + lane, cg = (warp - 2) >> 2, ch = cg * 16;
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const int my = r0 + row;                                 // my query (FWD, DQ) or my key (DKV)
+    const uint32_t scale2 = pack2(p.scale, p.scale);
     bool ok = true;
     float m_run = -INFINITY, l_run = 0.f, inv1 = 0.f, inv2 = 0.f, Dr = 0.f, mterm = 0.f;
     if (MODE == MODE_DQ) {
@@ -285,122 +296,164 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
     }
     int g = 0;
     if (MODE == MODE_FWD) {
-      // ---- sweep 1: row max and row sum of exp over this thread's half of all keys ----
+      // ---- sweep 1: row max and row sum of exp over this thread's quarter of all keys ----
       for (; g < n_it; ++g) {
         const int buf = g & 1;
-        ok = __all_sync(0xffffffffu, twait(16, tfull_bar(buf), ((uint32_t)g >> 1) & 1u, p.err));
+        ok = __all_sync(0xffffffffu, twait(16, tfull_bar(buf), ((uint32_t)g >> 1) & 1u, p.err, tacc[5]));
         if (!ok) break;
         tc_fence_after();
         const int k0 = g * 64 + ch;
-        const bool diag = (k0 + 31 > r0);
-        uint32_t r[32];
-        tmem_ld32(t1_col(buf) + lane_off + (uint32_t)ch, r);
+        const bool diag = (k0 + 15 > r0);
+        uint32_t r[16];
+        tmem_ld16(t1_col(buf) + lane_off + (uint32_t)ch, r);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar(buf));          // the values are in registers: release the buffer early
-        float sv[32], cm = -INFINITY;
+        float sv[16], cm = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = r16(r16(__uint_as_float(r[i])) * p.scale);
-          if (diag && (k0 + i > my)) s = -INFINITY;
-          sv[i] = s; cm = fmaxf(cm, s);
+        for (int j = 0; j < 8; ++j) {
+          // bf16(bf16(acc) * scale), two at a time
+          const uint32_t s2 = bmul2(pack2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])), scale2);
+          float s0 = bf_lo(s2), s1 = bf_hi(s2);
+          if (diag) {
+            if (k0 + 2 * j > my) s0 = -INFINITY;
+            if (k0 + 2 * j + 1 > my) s1 = -INFINITY;
+          }
+          sv[2 * j] = s0; sv[2 * j + 1] = s1;
+          cm = fmaxf(cm, fmaxf(s0, s1));
         }
         if (cm > m_run) { l_run *= ex2((m_run - cm) * LOG2E); m_run = cm; }
         if (m_run > -INFINITY) {
+          const float mL = m_run * LOG2E;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) l_run += ex2((sv[i] - m_run) * LOG2E);
+          for (int i = 0; i < 16; ++i) l_run += ex2(fmaf(sv[i], LOG2E, -mL));
         }
       }
-      // combine the two halves of each row through shared memory
+      // combine the four partial results of each row through shared memory (every warp sums them in the same order)
       if (ok) {
-        stat[(half * 128 + row) * 2] = m_run; stat[(half * 128 + row) * 2 + 1] = l_run;
+        stat[(cg * 128 + row) * 2] = m_run; stat[(cg * 128 + row) * 2 + 1] = l_run;
         __syncwarp();
         if (lane == 0) mbar_arrive(comb_bar);
-        ok = __all_sync(0xffffffffu, twait(20, comb_bar, 0, p.err));
+        ok = __all_sync(0xffffffffu, twait(20, comb_bar, 0, p.err, tacc[9]));
       }
       if (ok) {
-        const float mo = stat[((half ^ 1) * 128 + row) * 2], lo = stat[((half ^ 1) * 128 + row) * 2 + 1];
-        const float mn = fmaxf(m_run, mo);
-        l_run = l_run * ex2((m_run - mn) * LOG2E) + lo * ex2((mo - mn) * LOG2E);
-        m_run = mn;
+        float mn = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) mn = fmaxf(mn, stat[(c * 128 + row) * 2]);
+        float l = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) l += stat[(c * 128 + row) * 2 + 1] * ex2((stat[(c * 128 + row) * 2] - mn) * LOG2E);
+        m_run = mn; l_run = l;
         inv1 = 1.f / (l_run + PCPB_GUARD);
       }
     }
     const int g0 = g;
+    const float mL_row = m_run * LOG2E;
     for (int it = 0; it < n_it && ok; ++it) {
       const int gg = g0 + it, buf = gg & 1;
-      int c0 = 0;                                            // first column-side position of this thread's half
+      int c0 = 0;                                            // first column-side position of this thread's columns
       // per-warp copy of the column statistics (no cross-warp barrier: a warp that gave up cannot block the others)
-      float* st = stat + ((warp - 2) * 2 + (it & 1)) * 160;
+      float* st = stat + ((warp - 2) * 2 + (it & 1)) * 96;
       if (MODE == MODE_DKV) {
         const int hh = h + it / n_q;
         c0 = r0 + (it % n_q) * 64 + ch;
-        const long long idx = ((long long)b * p.H + hh) * p.T + c0 + lane;
-        const float mm = p.mrow[idx], ll = p.lrow[idx], dd = p.drow[idx];
-        const float i2 = 1.f / (ll + 2.f * PCPB_GUARD);
-        st[lane] = mm; st[32 + lane] = 1.f / (ll + PCPB_GUARD); st[64 + lane] = i2; st[96 + lane] = dd;
-        st[128 + lane] = dd * (2.f * PCPB_GUARD) * i2;
+        if (lane < 16) {
+          const long long idx = ((long long)b * p.H + hh) * p.T + c0 + lane;
+          const float mm = p.mrow[idx], ll = p.lrow[idx], dd = p.drow[idx];
+          const float i2 = 1.f / (ll + 2.f * PCPB_GUARD);
+          st[lane] = mm; st[16 + lane] = 1.f / (ll + PCPB_GUARD); st[32 + lane] = i2; st[48 + lane] = dd;
+          st[64 + lane] = dd * (2.f * PCPB_GUARD) * i2; st[80 + lane] = mm * LOG2E;
+        }
         __syncwarp();
       } else {
         c0 = it * 64 + ch;
       }
-      ok = __all_sync(0xffffffffu, twait(17, tfull_bar(buf), ((uint32_t)gg >> 1) & 1u, p.err));
+      ok = __all_sync(0xffffffffu, twait(17, tfull_bar(buf), ((uint32_t)gg >> 1) & 1u, p.err, tacc[6]));
       if (!ok) break;
       tc_fence_after();
-      const bool diag = (MODE == MODE_DKV) ? (c0 < r0 + 128) : (c0 + 31 > r0);
-      uint32_t r1[32];
-      tmem_ld32(t1_col(buf) + lane_off + (uint32_t)ch, r1);
-      float ev[32], e2v[32];
+      // does the causal boundary cross this thread block of 32 rows x 16 columns?
+      const bool diag = (MODE == MODE_DKV) ? (c0 < r0 + 128) : (c0 + 15 > r0);
+      uint32_t r1[16];
+      tmem_ld16(t1_col(buf) + lane_off + (uint32_t)ch, r1);
+      uint32_t ew[8], pw[8];
       if (MODE == MODE_FWD) {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar(buf));
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s = r16(r16(__uint_as_float(r1[i])) * p.scale);
-          const bool masked = diag && (c0 + i > my);
-          ev[i] = masked ? 0.f : ex2((s - m_run) * LOG2E) * inv1;
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t s2 = bmul2(pack2(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1])), scale2);
+          float e0 = ex2(fmaf(bf_lo(s2), LOG2E, -mL_row)) * inv1, e1 = ex2(fmaf(bf_hi(s2), LOG2E, -mL_row)) * inv1;
+          if (diag) {
+            if (c0 + 2 * j > my) e0 = 0.f;
+            if (c0 + 2 * j + 1 > my) e1 = 0.f;
+          }
+          ew[j] = pack2(e0, e1);
         }
       } else {
-        uint32_t r2[32];
-        tmem_ld32(t2_col(buf) + lane_off + (uint32_t)ch, r2);
+        uint32_t r2[16];
+        tmem_ld16(t2_col(buf) + lane_off + (uint32_t)ch, r2);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar(buf));
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s = r16(r16(__uint_as_float(r1[i])) * p.scale);
-          const float dp = r16(__uint_as_float(r2[i]));
-          float mm, i1, i2, dd, mt;
-          bool masked;
-          if (MODE == MODE_DQ) { mm = m_run; i1 = 0.f; i2 = inv2; dd = Dr; mt = mterm; masked = diag && (c0 + i > my); }
-          else { mm = st[i]; i1 = st[32 + i]; i2 = st[64 + i]; dd = st[96 + i]; mt = st[128 + i]; masked = diag && (my > c0 + i); }
-          const float e = masked ? 0.f : ex2((s - mm) * LOG2E);
-          float dsf = e * i2 * (dp - dd);
-          if (!masked && s == mm) dsf -= mt;
-          // the second rounding of ds happens when the value is packed to bf16 for the result tile
-          const float ds = masked ? 0.f : r16(dsf) * p.scale;
-          if (MODE == MODE_DQ) ev[i] = ds; else { ev[i] = e * i1; e2v[i] = ds; }
+        for (int j4 = 0; j4 < 4; ++j4) {
+          // statistics of the four columns of this group: broadcast row values (dQ) or per-column values (dK, dV)
+          float mm[4], i1[4], i2[4], dd[4], mt[4], mL[4];
+          if (MODE == MODE_DQ) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { mm[e] = m_run; i1[e] = 0.f; i2[e] = inv2; dd[e] = Dr; mt[e] = mterm; mL[e] = mL_row; }
+          } else {
+            const float4* s4 = reinterpret_cast<const float4*>(st) + j4;
+            const float4 a = s4[0], bq = s4[4], c = s4[8], d4 = s4[12], e4 = s4[16], f = s4[20];
+            mm[0] = a.x; mm[1] = a.y; mm[2] = a.z; mm[3] = a.w;
+            i1[0] = bq.x; i1[1] = bq.y; i1[2] = bq.z; i1[3] = bq.w;
+            i2[0] = c.x; i2[1] = c.y; i2[2] = c.z; i2[3] = c.w;
+            dd[0] = d4.x; dd[1] = d4.y; dd[2] = d4.z; dd[3] = d4.w;
+            mt[0] = e4.x; mt[1] = e4.y; mt[2] = e4.z; mt[3] = e4.w;
+            mL[0] = f.x; mL[1] = f.y; mL[2] = f.z; mL[3] = f.w;
+          }
+#pragma unroll
+          for (int jj = 0; jj < 2; ++jj) {
+            const int j = j4 * 2 + jj, e0i = jj * 2, e1i = jj * 2 + 1;
+            const uint32_t s2 = bmul2(pack2(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1])), scale2);
+            const uint32_t d2 = pack2(__uint_as_float(r2[2 * j]), __uint_as_float(r2[2 * j + 1]));
+            const float s0 = bf_lo(s2), s1 = bf_hi(s2), dp0 = bf_lo(d2), dp1 = bf_hi(d2);
+            float e0 = ex2(fmaf(s0, LOG2E, -mL[e0i])), e1 = ex2(fmaf(s1, LOG2E, -mL[e1i]));
+            bool k0 = true, k1 = true;                        // not masked
+            if (diag) {
+              if (MODE == MODE_DQ) { k0 = !(c0 + 2 * j > my); k1 = !(c0 + 2 * j + 1 > my); }
+              else { k0 = !(my > c0 + 2 * j); k1 = !(my > c0 + 2 * j + 1); }
+              if (!k0) e0 = 0.f;
+              if (!k1) e1 = 0.f;
+            }
+            float ds0 = e0 * i2[e0i] * (dp0 - dd[e0i]), ds1 = e1 * i2[e1i] * (dp1 - dd[e1i]);
+            if (k0 && s0 == mm[e0i]) ds0 -= mt[e0i];
+            if (k1 && s1 == mm[e1i]) ds1 -= mt[e1i];
+            // bf16(bf16(ds) * scale)
+            ew[j] = bmul2(pack2(ds0, ds1), scale2);
+            if (MODE == MODE_DKV) pw[j] = pack2(e0 * i1[e0i], e1 * i1[e1i]);
+          }
         }
       }
       // the previous output products must have finished reading the result tile(s)
-      ok = __all_sync(0xffffffffu, twait(18, eempty_bar, ((uint32_t)it & 1u) ^ 1u, p.err));
+      ok = __all_sync(0xffffffffu, twait(18, eempty_bar, ((uint32_t)it & 1u) ^ 1u, p.err, tacc[7]));
       if (!ok) break;
-      store_e32(sE, row, ch, ev);
-      if (MODE == MODE_DKV) store_e32(sE + E_BYTES, row, ch, e2v);
+      if (MODE == MODE_DKV) { store_e16(sE, row, ch, pw); store_e16(sE + E_BYTES, row, ch, ew); }
+      else store_e16(sE, row, ch, ew);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(efull_bar);
     }
-    // ---- outputs: each warp stores 64 of the 128 output columns of its rows ----
-    if (ok) ok = __all_sync(0xffffffffu, twait(19, out_bar, 0, p.err));
+    // ---- outputs: each warp stores 32 of the 128 output columns of its rows ----
+    if (ok) ok = __all_sync(0xffffffffu, twait(19, out_bar, 0, p.err, tacc[8]));
     if (ok) {
       tc_fence_after();
       const long long grow = (long long)row_base + my;
-      const int oc = half * 64;
+      const int oc = cg * 32;
       if (MODE == MODE_FWD) {
         store_out_cols(out1 + lane_off + oc, p.o + grow * p.d + xq + oc);
-        if (half == 0) {
+        if (cg == 0) {
           const long long idx = ((long long)b * p.H + h) * p.T + my;
           p.mrow[idx] = m_run; p.lrow[idx] = l_run;
         }
@@ -413,10 +466,15 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
     }
   }
 #ifdef PCPB_ATC_TIMING
+  if (lane == 0) {
+#pragma unroll
+    for (int c = 0; c < 12; ++c)
+      if (tacc[c]) atomicAdd(&g_atc_t[MODE * 32 + 11 + c], (unsigned long long)tacc[c]);
+  }
   if (threadIdx.x == 64) {
-    atomicAdd(&g_atc_t[0], (unsigned long long)(clock64() - t_cta0));
-    atomicAdd(&g_atc_t[1], 1ull);
-    atomicAdd(&g_atc_t[2], (unsigned long long)n_it);
+    atomicAdd(&g_atc_t[MODE * 32 + 0], (unsigned long long)(clock64() - t_cta0));
+    atomicAdd(&g_atc_t[MODE * 32 + 1], 1ull);
+    atomicAdd(&g_atc_t[MODE * 32 + 2], (unsigned long long)n_it);
   }
 #endif
   tc_fence_before();
@@ -459,7 +517,7 @@ cudaError_t launch_mode(cudaStream_t st, const CUtensorMap& a, const CUtensorMap
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) attr[dev] = true;
   }
-  kern<<<grid, 320, AtcCfg<MODE>::SMEM_BYTES, st>>>(a, b, c, p);
+  kern<<<grid, N_THREADS, AtcCfg<MODE>::SMEM_BYTES, st>>>(a, b, c, p);
   return cudaGetLastError();
 }
 
@@ -479,9 +537,9 @@ bool fill(const FlashArgs& a, int* err, AtcParams* p, CUtensorMap* mq, CUtensorM
 }  // namespace
 
 #ifdef PCPB_ATC_TIMING
-extern "C" int pcpb_debug_atc_timing(unsigned long long* out32, int reset) {
-  cudaError_t e = cudaMemcpyFromSymbol(out32, g_atc_t, sizeof(unsigned long long) * 32);
-  if (e == cudaSuccess && reset) { unsigned long long z[32] = {}; e = cudaMemcpyToSymbol(g_atc_t, z, sizeof z); }
+extern "C" int pcpb_debug_atc_timing(unsigned long long* out96, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out96, g_atc_t, sizeof(unsigned long long) * 96);
+  if (e == cudaSuccess && reset) { unsigned long long z[96] = {}; e = cudaMemcpyToSymbol(g_atc_t, z, sizeof z); }
   return e == cudaSuccess ? 0 : 2;
 }
 #endif

@@ -67,6 +67,26 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, int c
     return;
   }
   __nv_bfloat16* C = (__nv_bfloat16*)p.C + o;
+  if (p.epi == EPI_BIAS) {
+    const uint4* bp = reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.R + col);      // bias[N], model dtype
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float x[8];
+      unpack8(bp[q], x);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[8 * q + i] += x[i];
+    }
+  }
+  if (p.epi == EPI_DRELU) {
+    const uint4* rp = reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.R + o);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float x[8];
+      unpack8(rp[q], x);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[8 * q + i] = x[i] > 0.f ? acc[8 * q + i] : 0.f;
+    }
+  }
   if (p.epi == EPI_RESID || p.epi == EPI_DRELU2) {
     const uint4* rp = reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.R + o);
 #pragma unroll
@@ -100,14 +120,15 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, int c
   }
 #pragma unroll
   for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(C)[q] = outv[q];
-  if (p.epi == EPI_RELU2) {
+  if (p.epi == EPI_RELU2 || p.epi == EPI_RELU) {
     __nv_bfloat16* C2 = (__nv_bfloat16*)p.C2 + o;
+    const bool sq = (p.epi == EPI_RELU2);
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       float x[8];
       unpack8(outv[q], x);                                     // u as stored (bf16)
 #pragma unroll
-      for (int i = 0; i < 8; ++i) { const float rr = fmaxf(x[i], 0.f); x[i] = rr * rr; }
+      for (int i = 0; i < 8; ++i) { const float rr = fmaxf(x[i], 0.f); x[i] = sq ? rr * rr : rr; }
       uint4 v;
       v.x = pack2(x[0], x[1]); v.y = pack2(x[2], x[3]); v.z = pack2(x[4], x[5]); v.w = pack2(x[6], x[7]);
       reinterpret_cast<uint4*>(C2)[q] = v;
@@ -140,7 +161,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUt
   uint8_t* smem_gen = smem_raw + (base - smem_u32(smem_raw));
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + NSTAGE * Cfg::STAGE_BYTES + 8 * (2 * NSTAGE + 4));
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = uniform_warp_idx(), lane = threadIdx.x & 31;
   const int total_items = p.tiles_m * p.tiles_n * p.splits;
 
   if (threadIdx.x == 0) {
@@ -159,82 +180,74 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUt
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
-      int armed[NSTAGE];
+    // All 32 lanes run the loop, so its addresses and coordinates are warp-uniform values; one elected lane issues.
+    uint32_t it = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      const int tile = item / p.splits, split = item % p.splits;
+      const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
+      const int kb0 = split * p.kb_per_split;
+      const int kb1 = min(kb0 + p.kb_per_split, p.K / BK);
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % NSTAGE;
+        const uint32_t ph = (it / NSTAGE) & 1u;
+        if (!(ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ph ^ 1u, p.err, 1)))) break;
+        mbar_expect_tx_elect(full_bar(s), Cfg::STAGE_BYTES);
+        const uint32_t sa = base + s * Cfg::STAGE_BYTES, sb = sa + A_TILE_BYTES;
+        const int k0 = kb * BK;
+        if (!A_MN) tma_load_2d_elect(sa, &tma_a, full_bar(s), k0, m0);
+        else {
 #pragma unroll
-      for (int s = 0; s < NSTAGE; ++s) armed[s] = 0;
-      uint32_t it = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-        const int tile = item / p.splits, split = item % p.splits;
-        const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
-        const int kb0 = split * p.kb_per_split;
-        const int kb1 = min(kb0 + p.kb_per_split, p.K / BK);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % NSTAGE;
-          const uint32_t ph = (it / NSTAGE) & 1u;
-          if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, p.err, 1))) break;
-          mbar_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
-          armed[s] += 1;
-          const uint32_t sa = base + s * Cfg::STAGE_BYTES, sb = sa + A_TILE_BYTES;
-          const int k0 = kb * BK;
-          if (!A_MN) tma_load_2d(sa, &tma_a, full_bar(s), k0, m0);
-          else {
+          for (int c = 0; c < BM / 64; ++c) tma_load_2d_elect(sa + c * 8192, &tma_a, full_bar(s), m0 + c * 64, k0);
+        }
+        if (!B_MN) tma_load_2d_elect(sb, &tma_b, full_bar(s), k0, n0);
+        else {
 #pragma unroll
-            for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * 8192, &tma_a, full_bar(s), m0 + c * 64, k0);
-          }
-          if (!B_MN) tma_load_2d(sb, &tma_b, full_bar(s), k0, n0);
-          else {
-#pragma unroll
-            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * 8192, &tma_b, full_bar(s), n0 + c * 64, k0);
-          }
+          for (int c = 0; c < BN / 64; ++c) tma_load_2d_elect(sb + c * 8192, &tma_b, full_bar(s), n0 + c * 64, k0);
         }
       }
-      if (!ok) {
-        // error path: let the copies already issued land before the CTA goes away (bounded)
-#pragma unroll
-        for (int s = 0; s < NSTAGE; ++s)
-          if (armed[s] > 0) {
-            const uint32_t ph = (uint32_t)(armed[s] - 1) & 1u;
-            for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(full_bar(s), ph)) break;
-          }
+    }
+    if (!ok) {
+      // error path: `it` loads were armed; let the ones still in flight land before the CTA goes away (bounded)
+      for (uint32_t j = (it > (uint32_t)NSTAGE ? it - NSTAGE : 0u); j < it; ++j) {
+        const uint32_t ph = (j / NSTAGE) & 1u;
+        for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(full_bar(j % NSTAGE), ph)) break;
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
-      constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) |
-                                 ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-      constexpr uint32_t A_LBO = A_MN ? 8192u : 16u, B_LBO = B_MN ? 8192u : 16u;
-      constexpr uint32_t A_KSTEP = A_MN ? 2048u : 32u, B_KSTEP = B_MN ? 2048u : 32u;
-      uint32_t it = 0;
-      int local = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local) {
-        const int split = item % p.splits;
-        const int kb0 = split * p.kb_per_split;
-        const int kb1 = min(kb0 + p.kb_per_split, p.K / BK);
-        const int acc = local & 1;
-        const uint32_t aph = ((uint32_t)local >> 1) & 1u;
-        if (!(ok = mbar_wait(tempty_bar(acc), aph ^ 1u, p.err, 2))) break;
+    // All 32 lanes run the loops and the waits; one elected lane issues the MMAs and the commits.
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) |
+                               ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    constexpr uint32_t A_LBO = A_MN ? 8192u : 16u, B_LBO = B_MN ? 8192u : 16u;
+    constexpr uint32_t A_KSTEP = A_MN ? 2048u : 32u, B_KSTEP = B_MN ? 2048u : 32u;
+    uint32_t it = 0;
+    int local = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local) {
+      const int split = item % p.splits;
+      const int kb0 = split * p.kb_per_split;
+      const int kb1 = min(kb0 + p.kb_per_split, p.K / BK);
+      const int acc = local & 1;
+      const uint32_t aph = ((uint32_t)local >> 1) & 1u;
+      if (!(ok = __all_sync(0xffffffffu, mbar_wait(tempty_bar(acc), aph ^ 1u, p.err, 2)))) break;
+      tc_fence_after();
+      const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % NSTAGE;
+        const uint32_t ph = (it / NSTAGE) & 1u;
+        if (!(ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, p.err, 3)))) break;
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % NSTAGE;
-          const uint32_t ph = (it / NSTAGE) & 1u;
-          if (!(ok = mbar_wait(full_bar(s), ph, p.err, 3))) break;
-          tc_fence_after();
-          const uint32_t sa = base + s * Cfg::STAGE_BYTES, sb = sa + A_TILE_BYTES;
+        const uint32_t sa = base + s * Cfg::STAGE_BYTES, sb = sa + A_TILE_BYTES;
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t da = make_desc(sa + k * A_KSTEP, A_LBO, 1024u);
-            const uint64_t db = make_desc(sb + k * B_KSTEP, B_LBO, 1024u);
-            mma_bf16(tmem_d, da, db, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
-          }
-          mma_commit(empty_bar(s));                 // frees the stage when these MMAs have read it
+        for (int k = 0; k < BK / 16; ++k) {
+          const uint64_t da = make_desc(sa + k * A_KSTEP, A_LBO, 1024u);
+          const uint64_t db = make_desc(sb + k * B_KSTEP, B_LBO, 1024u);
+          mma_bf16_elect(tmem_d, da, db, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
         }
-        if (ok) mma_commit(tfull_bar(acc));         // accumulator complete
+        mma_commit_elect(empty_bar(s));               // frees the stage when these MMAs have read it
       }
+      if (ok) mma_commit_elect(tfull_bar(acc));       // accumulator complete
     }
   } else {
     // ------------------------------ epilogue ------------------------------
@@ -312,7 +325,7 @@ Plan plan_for(const GemmArgs& g) {
   if (((uintptr_t)g.A | (uintptr_t)g.B | (uintptr_t)g.C) & 15) return pl;
   if (g.R && ((uintptr_t)g.R & 15)) return pl;
   if (g.C2 && ((uintptr_t)g.C2 & 15)) return pl;
-  if (g.epi < EPI_STORE || g.epi > EPI_WGRAD) return pl;
+  if (g.epi < EPI_STORE || g.epi > EPI_BIAS) return pl;
   pl.bn = (g.N % 256 == 0) ? 256 : 128;
   const int tiles = (g.M / BM) * (g.N / pl.bn), kblocks = g.K / BK;
   pl.splits = 1;

@@ -841,10 +841,11 @@ int pcpb_op_gemm(pcpb_backend* b, int path, const pcpb_buffer* A, long long sam,
                  int M, int N, int K, int epilogue) {
   int r = require_loaded(b);
   if (r) return r;
-  if (!A || !B || !C || M < 0 || N < 0 || K < 0 || epilogue < EPI_STORE || epilogue > EPI_WGRAD)
+  if (!A || !B || !C || M < 0 || N < 0 || K < 0 || epilogue < EPI_STORE || epilogue > EPI_BIAS)
     return fail(b, PCPB_E_INVALID, "bad gemm arguments");
-  if ((epilogue == EPI_RESID || epilogue == EPI_DRELU2) && !R) return fail(b, PCPB_E_INVALID, "this epilogue needs R");
-  if (epilogue == EPI_RELU2 && !C2) return fail(b, PCPB_E_INVALID, "this epilogue needs C2");
+  if ((epilogue == EPI_RESID || epilogue == EPI_DRELU2 || epilogue == EPI_DRELU || epilogue == EPI_BIAS) && !R)
+    return fail(b, PCPB_E_INVALID, "this epilogue needs R");
+  if ((epilogue == EPI_RELU2 || epilogue == EPI_RELU) && !C2) return fail(b, PCPB_E_INVALID, "this epilogue needs C2");
   DeviceGuard g(b->device);
   const size_t es = dtype_size(b->cfg.dtype);
   // extents touched by the strided views must lie inside the buffers
@@ -854,7 +855,8 @@ int pcpb_op_gemm(pcpb_backend* b, int path, const pcpb_buffer* A, long long sam,
       return fail(b, PCPB_E_INVALID, "operand view exceeds its buffer");
     const size_t ces = (epilogue == EPI_WGRAD) ? 4 : es;
     if ((size_t)span(M, ldc, N, 1) * ces > C->nbytes) return fail(b, PCPB_E_INVALID, "output view exceeds its buffer");
-    if (R && (size_t)span(M, ldc, N, 1) * es > R->nbytes) return fail(b, PCPB_E_INVALID, "R view exceeds its buffer");
+    const size_t r_need = (epilogue == EPI_BIAS) ? (size_t)N * es : (size_t)span(M, ldc, N, 1) * es;
+    if (R && r_need > R->nbytes) return fail(b, PCPB_E_INVALID, "R view exceeds its buffer");
     if (C2 && (size_t)span(M, ldc, N, 1) * es > C2->nbytes) return fail(b, PCPB_E_INVALID, "C2 view exceeds its buffer");
   }
   GemmArgs ga = mk(A->ptr, sam, sak, B->ptr, sbk, sbn, C->ptr, ldc, M, N, K, epilogue, R ? R->ptr : nullptr, C2 ? C2->ptr : nullptr);

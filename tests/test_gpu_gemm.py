@@ -41,10 +41,13 @@ def _run(be, layout, M, N, K, epi, path, seed=0):
     B = be.move_to_device(bbits, bbits.shape, BF16)
     R = C2 = None
     rv = None
-    if epi in (1, 3):
+    if epi in (1, 3, 6):
         rbits, rv = _bf16(rng.standard_normal((M, N)))
         R = be.move_to_device(rbits, (M, N), BF16)
-    if epi == 2:
+    if epi == 7:
+        rbits, rv = _bf16(rng.standard_normal((N,)))
+        R = be.move_to_device(rbits, (N,), BF16)
+    if epi in (2, 5):
         C2 = be.allocate_zeros_device((M, N), BF16)
     Cb = be.allocate_zeros_device((M, N), F32 if epi == 4 else BF16)
     be.op_gemm(A, sa[0], sa[1], B, sb[0], sb[1], Cb, N, M, N, K, epilogue=epi, R=R, C2=C2, path=path)
@@ -67,8 +70,14 @@ def _run(be, layout, M, N, K, epi, path, seed=0):
         with np.errstate(divide="ignore", invalid="ignore"):
             q = rb(np.where(r > 0, rb(r * r) / np.where(r > 0, r, 1), 0))
         want = np.where(u > 0, rb(rb(r32) * rb(2 * q)), 0).astype(np.float32)
-    else:
+    elif epi == 4:
         want = np.clip(rb(r32), -100, 100)
+    elif epi == 5:
+        want = rb(r32)
+    elif epi == 6:
+        want = np.where(rv > 0, rb(r32), 0).astype(np.float32)
+    else:
+        want = rb(r32 + rv[None, :])
     return out, want, out2
 
 
@@ -86,7 +95,8 @@ def test_tc_gemm_store(be, layout, shape):
     assert np.abs(out - want).mean() < 2e-3 * np.sqrt(K)
 
 
-@pytest.mark.parametrize("layout,epi", [("nt", 1), ("nt", 2), ("nn", 3), ("tn", 4), ("nn", 0), ("nt", 4)])
+@pytest.mark.parametrize("layout,epi", [("nt", 1), ("nt", 2), ("nn", 3), ("tn", 4), ("nn", 0), ("nt", 4), ("nt", 5),
+                                        ("nn", 6), ("nt", 7)])
 def test_tc_gemm_epilogues(be, layout, epi):
     M, N, K = 256, 512, 320
     out, want, out2 = _run(be, layout, M, N, K, epi=epi, path=2, seed=epi + 1)
@@ -98,6 +108,8 @@ def test_tc_gemm_epilogues(be, layout, epi):
     if epi == 2:
         r = np.maximum(out, 0)
         np.testing.assert_array_equal(out2, _bf16(r * r)[1])
+    if epi == 5:
+        np.testing.assert_array_equal(out2, np.maximum(out, 0))
 
 
 def test_tc_gemm_split_k(be):
