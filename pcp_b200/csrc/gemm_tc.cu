@@ -3,10 +3,11 @@
 //
 //   C[M,N] = sum_k A(m,k) B(k,n)       A, B bf16; f32 accumulate; epilogues of kernels.h
 //
-// Tile 128 x BN (BN = 256 or 128) x 64.  Warp roles (192 threads):
+// Tile 128 x BN (BN = 256 or 128) x 64.  Warp roles (320 threads):
 //   warp 0      TMA producer: fills the NSTAGE-deep ring of (A tile, B tile) pairs
 //   warp 1      allocates tensor memory; one elected lane issues tcgen05.mma and commits
-//   warps 2..5  epilogue: tcgen05.ld of one accumulator buffer (32 lanes per warp), epilogue math, stores
+//   warps 2..9  epilogue: tcgen05.ld of one accumulator buffer (32 lanes per warp, half of the columns), epilogue
+//               math, stores; the residual / pre-activation operand is prefetched while the MMAs run
 // Two accumulator buffers of BN columns each let the epilogue of tile i overlap the MMAs of tile i+1.
 //
 // Operand layouts.  Either operand may be "K-major" (contraction index contiguous in memory) or
@@ -32,11 +33,14 @@ namespace pcpb {
 namespace {
 
 constexpr int BM = 128, BK = 64;
+constexpr int N_EPI = 8;                                  // epilogue warps
+constexpr int GEMM_THREADS = 64 + 32 * N_EPI;
 constexpr int A_TILE_BYTES = BM * BK * 2;                 // 16 KB
 
 struct TcParams {
   int M, N, K;                 // output rows, output cols, contraction length
   int tiles_m, tiles_n, splits, kb_per_split;
+  int group_m;                 // row tiles per group of the tile order (1 = plain row-major order)
   int epi;
   void* C; long long ldc;
   const void* R; void* C2;
@@ -46,7 +50,9 @@ struct TcParams {
 };
 
 // Epilogue of 32 consecutive columns of one output row held as f32 bit patterns in r[].
-__device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, int col, const uint32_t (&r)[32]) {
+// rpre: the 32 values of the per-element operand R for these columns (residual / pre-activation), loaded by the
+// caller ahead of time; only read by the epilogues that have such an operand.
+__device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, int col, const uint32_t (&r)[32], const uint4* rpre) {
   float acc[32];
 #pragma unroll
   for (int i = 0; i < 32; ++i) acc[i] = __uint_as_float(r[i]);
@@ -78,7 +84,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, int c
     }
   }
   if (p.epi == EPI_DRELU) {
-    const uint4* rp = reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.R + o);
+    const uint4* rp = rpre;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       float x[8];
@@ -88,7 +94,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, int c
     }
   }
   if (p.epi == EPI_RESID || p.epi == EPI_DRELU2) {
-    const uint4* rp = reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.R + o);
+    const uint4* rp = rpre;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       float x[8];
@@ -136,6 +142,18 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, int c
   }
 }
 
+// Output tile of a work item.  Tiles are numbered so that tiles running at the same time share operands in L2: when
+// there are many column tiles (the LM head: every row tile would otherwise stream the whole weight matrix through
+// L2), groups of 8 row tiles walk the columns together; otherwise columns vary fastest.
+__device__ __forceinline__ void tile_coords(const TcParams& p, int tile, int* tm, int* tn) {
+  if (p.group_m <= 1) { *tm = tile / p.tiles_n; *tn = tile % p.tiles_n; return; }
+  const int per_group = p.group_m * p.tiles_n;
+  const int g = tile / per_group, rem = tile % per_group;
+  const int gm = min(p.group_m, p.tiles_m - g * p.group_m);       // the last group may be short
+  *tm = g * p.group_m + rem % gm;
+  *tn = rem / gm;
+}
+
 template <int BN> struct TcCfg {
   static constexpr int B_TILE_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
@@ -145,7 +163,7 @@ template <int BN> struct TcCfg {
 };
 
 template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const TcParams p) {
   using Cfg = TcCfg<BN>;
   constexpr int NSTAGE = Cfg::NSTAGE;
@@ -166,7 +184,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUt
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NSTAGE; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), N_EPI); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -185,7 +203,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUt
     bool ok = true;
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
       const int tile = item / p.splits, split = item % p.splits;
-      const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
+      int tm, tn;
+      tile_coords(p, tile, &tm, &tn);
+      const int m0 = tm * BM, n0 = tn * BN;
       const int kb0 = split * p.kb_per_split;
       const int kb1 = min(kb0 + p.kb_per_split, p.K / BK);
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
@@ -251,26 +271,39 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUt
     }
   } else {
     // ------------------------------ epilogue ------------------------------
-    const int q = warp & 3;                         // TMEM lane quarter this warp may access
+    // Eight warps: two per tensor-memory lane quarter, each with one half of the BN accumulator columns; a thread owns
+    // one output row.  The per-element operand of the epilogue (residual or pre-activation) does not depend on the
+    // accumulator, so it is fetched before the wait and its latency is spent under the MMAs of the tile.
+    constexpr int NCH = BN / 64;                    // 32-column chunks per warp
+    const int q = warp & 3, half = (warp - 2) >> 2;
+    const bool reads_r = (p.splits == 1) && (p.epi == EPI_RESID || p.epi == EPI_DRELU2 || p.epi == EPI_DRELU);
     int local = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local) {
       const int tile = item / p.splits, split = item % p.splits;
-      const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
+      int tm, tn;
+      tile_coords(p, tile, &tm, &tn);
+      const int m0 = tm * BM, n0 = tn * BN + half * (BN / 2);
       const int acc = local & 1;
       const uint32_t aph = ((uint32_t)local >> 1) & 1u;
+      const int row = m0 + q * 32 + lane;
+      uint4 rpre[NCH * 4];
+      if (reads_r) {
+        const uint4* rp = reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.R + (size_t)row * p.ldc + n0);
+#pragma unroll
+        for (int i = 0; i < NCH * 4; ++i) rpre[i] = __ldg(rp + i);
+      }
       ok = mbar_wait(tfull_bar(acc), aph, p.err, 4);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
       TcParams pe = p;
       if (p.splits > 1) { pe.epi = -1; pe.slab = p.slab + (size_t)split * p.M * p.N; pe.ldc = p.N; }
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c), r);
-        epilogue_chunk(pe, row, n0 + c, r);
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * (BN / 2) + c * 32), r);
+        epilogue_chunk(pe, row, n0 + c * 32, r, rpre + c * 4);
       }
       tc_fence_before();
       __syncwarp();
@@ -354,7 +387,7 @@ cudaError_t launch_variant(cudaStream_t st, const CUtensorMap& ma, const CUtenso
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) attr_set[dev] = true;
   }
-  kern<<<grid, 192, TcCfg<BN>::SMEM_BYTES, st>>>(ma, mb, p);
+  kern<<<grid, GEMM_THREADS, TcCfg<BN>::SMEM_BYTES, st>>>(ma, mb, p);
   return cudaGetLastError();
 }
 
@@ -396,6 +429,7 @@ cudaError_t launch_gemm_tc(cudaStream_t st, const GemmArgs& g) {
   TcParams p;
   p.M = g.M; p.N = g.N; p.K = g.K;
   p.tiles_m = g.M / BM; p.tiles_n = g.N / pl.bn; p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
+  p.group_m = (p.tiles_n >= 32 && p.splits == 1) ? 8 : 1;
   p.epi = g.epi; p.C = g.C; p.ldc = g.ldc; p.R = g.R; p.C2 = g.C2; p.clip = g.clip; p.slab = nullptr; p.err = err;
   if (pl.splits > 1) p.slab = (float*)g.scratch;
   const int items = p.tiles_m * p.tiles_n * p.splits;
