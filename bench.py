@@ -218,7 +218,7 @@ def run_ours(args):
         at += n
     blob = f32_to_bf16_trunc_bits(blob32.numpy())
     del blob32
-    n_tok = (K + W + 2) * (BT + 1)
+    n_tok = (max(K + W, H_INNER) + 2) * (BT + 1)
     tokens = zipf_tokens(n_tok, cfg.vocab, 1.1, seed=rank)
     pinned = torch.empty(n_tok, dtype=torch.int16).pin_memory() if torch.cuda.is_available() else torch.empty(n_tok, dtype=torch.int16)
     pinned.numpy().view(np.uint16)[:] = tokens
@@ -284,7 +284,11 @@ def run_ours(args):
                  "P2P push of the new master, host barriers on both sides"}
 
     # ---------------- e2e: host buffers through the C ABI ----------------
-    Ke = max(1, min(K, 5))
+    # one DiLoCo round as the worker sees it: blob in, H inner steps from host token windows, delta out.  The default
+    # run times a full round of H_INNER steps; short runs (--steps < 8) time K steps and amortise the blobs over those.
+    Ke = H_INNER if K >= 8 else max(1, K)
+    if n_tok < Ke * BT + 1:
+        Ke = max(1, (n_tok - 1) // BT)
     barrier()
     be.timer_start()
     be.worker_begin_round(Ke, blob, param_dtype=BF16, tokens_on_device=False)

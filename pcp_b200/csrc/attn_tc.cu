@@ -40,7 +40,6 @@ constexpr int HD = 128;
 constexpr int SUB_BYTES = 64 * HD * 2;         // one streamed sub-tile: 16 KB
 constexpr int STAGE_BYTES = 2 * SUB_BYTES;     // (C1, C2)
 constexpr int TILE_BYTES = 128 * HD * 2;       // one resident tile: 32 KB
-constexpr int E_BYTES = 128 * 64 * 2;          // one element-wise result tile: 16 KB
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int N_EW = 16;                       // element-wise warps
 constexpr int N_THREADS = 64 + 32 * N_EW;
@@ -51,6 +50,7 @@ struct AtcParams {
   int B, T, H, Hkv;
   float scale;
   int d, dkv;                                  // model width, kv width
+  const bf16* qkn; const bf16* dout;           // row-side tiles that the element-wise warps load themselves
   bf16* o; float* mrow; float* lrow; const float* drow;
   bf16* dqkn; bf16* dqkv;
   int* err;
@@ -58,13 +58,12 @@ struct AtcParams {
 
 template <int MODE> struct AtcCfg {
   static constexpr int NST = (MODE == MODE_FWD) ? PCPB_ATC_NST_FWD : (MODE == MODE_DQ) ? PCPB_ATC_NST_DQ : 3;   // ring stages
-  static constexpr int N_RES = (MODE == MODE_FWD) ? 1 : 2;
-  static constexpr int N_E = (MODE == MODE_DKV) ? 2 : 1;
-  // DKV: per warp, double-buffered, six statistics of 16 columns; FWD: exchange of the four partial (max, sum) of a row
-  static constexpr int STAT_BYTES = (MODE == MODE_DKV) ? N_EW * 2 * 96 * 4 : 4 * 128 * 2 * 4;
+  // resident row-side tiles in shared memory: K and V of the dK/dV kernel (the other kernels keep theirs in tensor memory)
+  static constexpr int N_RES = (MODE == MODE_DKV) ? 2 : 0;
+  // DKV: per warp, double-buffered, six statistics of 32 columns; FWD: exchange of the four partial (max, sum) of a row
+  static constexpr int STAT_BYTES = (MODE == MODE_DKV) ? N_EW * 2 * 192 * 4 : (MODE == MODE_FWD) ? 4 * 128 * 2 * 4 : 16;
   static constexpr int OFF_RING = N_RES * TILE_BYTES;
-  static constexpr int OFF_E = OFF_RING + NST * STAGE_BYTES;
-  static constexpr int OFF_STAT = OFF_E + N_E * E_BYTES;
+  static constexpr int OFF_STAT = OFF_RING + NST * STAGE_BYTES;
   static constexpr int OFF_BAR = OFF_STAT + STAT_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
   static_assert(SMEM_BYTES <= 232448, "more shared memory than one CTA can have");
@@ -96,18 +95,6 @@ __device__ __forceinline__ bool twait(int code, uint32_t bar, uint32_t parity, i
 #endif
 }
 
-// Write 16 consecutive k-values (columns c0 .. c0+15 of row r, as eight bf16 pairs) of a [128 x 64] bf16 A-operand
-// tile (one 128-byte swizzle atom per row: 16-byte chunk j of row r lives at chunk position j ^ (r & 7)).
-__device__ __forceinline__ void store_e16(uint32_t ebase, int r, int c0, const uint32_t (&w)[8]) {
-#pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const int kc = (c0 >> 3) + j;
-    const uint32_t addr = ebase + (uint32_t)r * 128u + (uint32_t)((kc ^ (r & 7)) << 4);
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * j]), "r"(w[4 * j + 1]), "r"(w[4 * j + 2]),
-                 "r"(w[4 * j + 3]) : "memory");
-  }
-}
-
 // Store 32 consecutive output columns of one row (f32 accumulators in tensor memory at taddr) as bf16 to dst.
 __device__ __forceinline__ void store_out_cols(uint32_t taddr, bf16* dst) {
   uint32_t r[32];
@@ -132,15 +119,16 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t sRes = base, sRing = base + Cfg::OFF_RING, sE = base + Cfg::OFF_E, sBar = base + Cfg::OFF_BAR;
+  const uint32_t sRes = base, sRing = base + Cfg::OFF_RING, sBar = base + Cfg::OFF_BAR;
   float* stat = reinterpret_cast<float*>(gen + Cfg::OFF_STAT);
   auto full_bar = [&](int s) { return sBar + 8u * s; };
   auto empty_bar = [&](int s) { return sBar + 8u * (NST + s); };
   auto tfull_bar = [&](int b) { return sBar + 8u * (2 * NST + b); };
   auto tempty_bar = [&](int b) { return sBar + 8u * (2 * NST + 2 + b); };
-  const uint32_t efull_bar = sBar + 8u * (2 * NST + 4), eempty_bar = efull_bar + 8, out_bar = efull_bar + 16,
-                 res_bar = efull_bar + 24, comb_bar = efull_bar + 32, tmem_slot = efull_bar + 40;
-  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + Cfg::OFF_BAR + 8 * (2 * NST + 4) + 40);
+  auto efull_bar = [&](int e) { return sBar + 8u * (2 * NST + 4 + e); };
+  auto eempty_bar = [&](int e) { return sBar + 8u * (2 * NST + 6 + e); };
+  const uint32_t out_bar = sBar + 8u * (2 * NST + 8), res_bar = out_bar + 8, comb_bar = out_bar + 16, tmem_slot = out_bar + 24;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + Cfg::OFF_BAR + 8 * (2 * NST + 8) + 24);
 
   const int warp = uniform_warp_idx(), lane = threadIdx.x & 31;
   const int grp = p.H / p.Hkv;
@@ -168,8 +156,10 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NST; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int t = 0; t < 2; ++t) { mbar_init(tfull_bar(t), 1); mbar_init(tempty_bar(t), N_EW); }
-    mbar_init(efull_bar, N_EW); mbar_init(eempty_bar, 1); mbar_init(out_bar, 1); mbar_init(res_bar, 1); mbar_init(comb_bar, N_EW);
+    for (int t = 0; t < 2; ++t) { mbar_init(tfull_bar(t), 1); mbar_init(tempty_bar(t), N_EW / 2); }
+    for (int e = 0; e < 2; ++e) { mbar_init(efull_bar(e), N_EW / 2); mbar_init(eempty_bar(e), 1); }
+    // the row-side tiles arrive by TMA (dK/dV) or are written to tensor memory by the element-wise warps
+    mbar_init(out_bar, 1); mbar_init(res_bar, MODE == MODE_DKV ? 1 : N_EW); mbar_init(comb_bar, N_EW);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -180,10 +170,16 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_gen;
-  // tensor-memory columns: score buffers at 0 / 128 (T1 at +0, T2 at +64), outputs at 256 and 384
+  // Tensor-memory columns (512): score buffers at 0 / 128 (T1 at +0, T2 at +64), first output at 256.
+  //   forward   Q (bf16 pairs, 64 columns) at 384, P double-buffered at 448 / 480
+  //   dQ        Q at 384, dO at 448; dS overwrites the T1 buffer it was computed from
+  //   dK, dV    second output at 384; P^T and dS^T overwrite the T1 / T2 buffers they were computed from
+  // A 16-bit tile written over a score buffer goes where its writer read: warp group cg owns columns 16cg .. 16cg+15
+  // of the buffer and puts its 16 k-values (8 columns) at 16cg, which is also where the MMA of k-step cg looks for them.
   auto t1_col = [&](int buf) { return tmem + (uint32_t)(buf * 128); };
   auto t2_col = [&](int buf) { return tmem + (uint32_t)(buf * 128 + 64); };
-  const uint32_t out1 = tmem + 256u, out2 = tmem + 384u;
+  const uint32_t out1 = tmem + 256u, out2 = tmem + 384u, qcol = tmem + 384u, docol = tmem + 448u;
+  auto pcol = [&](int e) { return tmem + 448u + (uint32_t)(e * 32); };
 
   if (warp == 0) {
     // =========================== TMA producer ===========================
@@ -192,10 +188,11 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       tma_load_2d_elect(dst, m, res_bar, x, y);              tma_load_2d_elect(dst + 8192, m, res_bar, x, y + 64);
       tma_load_2d_elect(dst + 16384, m, res_bar, x + 64, y); tma_load_2d_elect(dst + 24576, m, res_bar, x + 64, y + 64);
     };
-    mbar_expect_tx_elect(res_bar, Cfg::N_RES * TILE_BYTES);
-    if (MODE == MODE_FWD) load_tile128(sRes, &tm_qkn, xq, row_base + r0);
-    if (MODE == MODE_DQ) { load_tile128(sRes, &tm_qkn, xq, row_base + r0); load_tile128(sRes + TILE_BYTES, &tm_do, xq, row_base + r0); }
-    if (MODE == MODE_DKV) { load_tile128(sRes, &tm_qkn, xk, row_base + r0); load_tile128(sRes + TILE_BYTES, &tm_qkv, xv, row_base + r0); }
+    if (MODE == MODE_DKV) {
+      mbar_expect_tx_elect(res_bar, Cfg::N_RES * TILE_BYTES);
+      load_tile128(sRes, &tm_qkn, xk, row_base + r0);
+      load_tile128(sRes + TILE_BYTES, &tm_qkv, xv, row_base + r0);
+    }
     bool ok = true;
     int g = 0;
     for (; g < total_g; ++g) {
@@ -221,7 +218,8 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
         const uint32_t ph = ((uint32_t)j / NST) & 1u;
         for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(full_bar(j % NST), ph)) break;
       }
-      for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(res_bar, 0)) break;
+      if (MODE == MODE_DKV)
+        for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(res_bar, 0)) break;
     }
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
@@ -241,9 +239,19 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       for (int ks = 0; ks < 8; ++ks) {
         const uint32_t ao = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
         const uint32_t bo = (uint32_t)(ks >> 2) * 8192u + (uint32_t)(ks & 3) * 32u;
-        mma_bf16_elect(t1_col(buf), make_desc(sRes + ao, 16, 1024), make_desc(c1 + bo, 16, 1024), ID_T, ks > 0);
-        if (MODE != MODE_FWD)
-          mma_bf16_elect(t2_col(buf), make_desc(sRes + TILE_BYTES + ao, 16, 1024), make_desc(c2 + bo, 16, 1024), ID_T, ks > 0);
+        // A from tensor memory (forward, dQ): k-step ks = head dimensions 16ks .. 16ks+15 = 8 columns of bf16 pairs
+        if (MODE == MODE_DKV) mma_bf16_elect(t1_col(buf), make_desc(sRes + ao, 16, 1024), make_desc(c1 + bo, 16, 1024), ID_T, ks > 0);
+        else mma_bf16_ts_elect(t1_col(buf), qcol + 8u * ks, make_desc(c1 + bo, 16, 1024), ID_T, ks > 0);
+      }
+      if (MODE != MODE_FWD) {
+        // the second product after the first, not interleaved with it: one accumulator chain at a time
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t ao = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
+          const uint32_t bo = (uint32_t)(ks >> 2) * 8192u + (uint32_t)(ks & 3) * 32u;
+          if (MODE == MODE_DKV) mma_bf16_elect(t2_col(buf), make_desc(sRes + TILE_BYTES + ao, 16, 1024), make_desc(c2 + bo, 16, 1024), ID_T, ks > 0);
+          else mma_bf16_ts_elect(t2_col(buf), docol + 8u * ks, make_desc(c2 + bo, 16, 1024), ID_T, ks > 0);
+        }
       }
       if (release_stage) mma_commit_elect(empty_bar(s));
       mma_commit_elect(tfull_bar(buf));
@@ -257,32 +265,35 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
     if (ok) ok = issue_T(g0, false);
     for (int it = 0; it < n_it && ok; ++it) {
       if (it + 1 < n_it && !(ok = issue_T(g0 + it + 1, false))) break;
-      if (!(ok = __all_sync(0xffffffffu, twait(15, efull_bar, (uint32_t)it & 1u, p.err, tacc[4])))) break;
+      // sub-tile `it` belongs to element-wise group it & 1; P is double-buffered (forward), the backward tiles live in
+      // the score buffer of their sub-tile
+      const int eb = it & 1;
+      const uint32_t eph = ((uint32_t)it >> 1) & 1u;
+      if (!(ok = __all_sync(0xffffffffu, twait(15, efull_bar(eb), eph, p.err, tacc[4])))) break;
       tc_fence_after();
       ATC_T0();
-      const int s = (g0 + it) % NST;
+      const int s = (g0 + it) % NST, buf = (g0 + it) & 1;
       const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) {
         const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
-        const uint64_t e1 = make_desc(sE + ks * 32u, 16, 1024);
-        if (MODE == MODE_FWD) mma_bf16_elect(out1, e1, make_desc(c2 + ks * 2048u, 8192, 1024), ID_O, acc);
-        if (MODE == MODE_DQ) mma_bf16_elect(out1, e1, make_desc(c1 + ks * 2048u, 8192, 1024), ID_O, acc);
+        if (MODE == MODE_FWD) mma_bf16_ts_elect(out1, pcol(eb) + 8u * ks, make_desc(c2 + ks * 2048u, 8192, 1024), ID_O, acc);
+        if (MODE == MODE_DQ) mma_bf16_ts_elect(out1, t1_col(buf) + 16u * ks, make_desc(c1 + ks * 2048u, 8192, 1024), ID_O, acc);
         if (MODE == MODE_DKV) {
-          mma_bf16_elect(out1, e1, make_desc(c2 + ks * 2048u, 8192, 1024), ID_O, acc);
-          mma_bf16_elect(out2, make_desc(sE + E_BYTES + ks * 32u, 16, 1024), make_desc(c1 + ks * 2048u, 8192, 1024), ID_O, acc);
+          mma_bf16_ts_elect(out1, t1_col(buf) + 16u * ks, make_desc(c2 + ks * 2048u, 8192, 1024), ID_O, acc);
+          mma_bf16_ts_elect(out2, t2_col(buf) + 16u * ks, make_desc(c1 + ks * 2048u, 8192, 1024), ID_O, acc);
         }
       }
       mma_commit_elect(empty_bar(s));
-      mma_commit_elect(eempty_bar);
+      if (MODE == MODE_FWD) mma_commit_elect(eempty_bar(eb));
       ATC_T1(11);
     }
     if (ok) mma_commit_elect(out_bar);
   } else {
     // =========================== element-wise warps ===========================
-    // Sixteen warps: four per tensor-memory lane quarter; each thread owns one row and 16 of the 64 columns of every
-    // score sub-tile.
-    const int q = warp & 3, row = q * 32 + lane, cg = (warp - 2) >> 2, ch = cg * 16;
+    // Sixteen warps, four per tensor-memory lane quarter.  cg = 0..3 numbers the four warps of a quarter: it picks the
+    // 32 head dimensions / output columns a thread moves, and splits into the sub-tile group and the column half.
+    const int q = warp & 3, row = q * 32 + lane, cg = (warp - 2) >> 2, grp2 = cg >> 1, half = cg & 1;
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const int my = r0 + row;                                 // my query (FWD, DQ) or my key (DKV)
     const uint32_t scale2 = pack2(p.scale, p.scale);
@@ -294,39 +305,66 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       inv2 = 1.f / (l_run + 2.f * PCPB_GUARD);
       mterm = Dr * (2.f * PCPB_GUARD) * inv2;
     }
-    int g = 0;
+    if (MODE != MODE_DKV) {
+      // ---- my 32 head dimensions of my row of Q (and of dO) go to tensor memory as bf16 pairs ----
+      const uint32_t dst = lane_off + (uint32_t)(cg * 16);
+      uint32_t w[16];
+      const uint4* src = reinterpret_cast<const uint4*>(p.qkn + (size_t)(row_base + my) * (p.d + p.dkv) + xq + cg * 32);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const uint4 v = __ldg(src + j); w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w; }
+      tmem_st16(qcol + dst, w);
+      if (MODE == MODE_DQ) {
+        src = reinterpret_cast<const uint4*>(p.dout + (size_t)(row_base + my) * p.d + xq + cg * 32);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const uint4 v = __ldg(src + j); w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w; }
+        tmem_st16(docol + dst, w);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(res_bar);
+    }
+    // Two groups of eight warps take the sub-tiles in turn (group = parity of the sub-tile = its score buffer), so the
+    // tensor-memory and barrier latencies of one group are spent under the arithmetic of the other.  Within a group a
+    // thread owns one row and 32 of the 64 columns, in two passes of 16.
+    int g = grp2;
     if (MODE == MODE_FWD) {
-      // ---- sweep 1: row max and row sum of exp over this thread's quarter of all keys ----
-      for (; g < n_it; ++g) {
+      // ---- sweep 1: row max and row sum of exp over this thread's share of the keys ----
+      for (; g < n_it; g += 2) {
         const int buf = g & 1;
         ok = __all_sync(0xffffffffu, twait(16, tfull_bar(buf), ((uint32_t)g >> 1) & 1u, p.err, tacc[5]));
         if (!ok) break;
         tc_fence_after();
-        const int k0 = g * 64 + ch;
-        const bool diag = (k0 + 15 > r0);
-        uint32_t r[16];
-        tmem_ld16(t1_col(buf) + lane_off + (uint32_t)ch, r);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar(buf));          // the values are in registers: release the buffer early
-        float sv[16], cm = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          // bf16(bf16(acc) * scale), two at a time
-          const uint32_t s2 = bmul2(pack2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])), scale2);
-          float s0 = bf_lo(s2), s1 = bf_hi(s2);
-          if (diag) {
-            if (k0 + 2 * j > my) s0 = -INFINITY;
-            if (k0 + 2 * j + 1 > my) s1 = -INFINITY;
+        for (int pass = 0; pass < 2; ++pass) {
+          const int ch = half * 32 + pass * 16, k0 = g * 64 + ch;
+          const bool diag = (k0 + 15 > r0);
+          uint32_t r[16];
+          tmem_ld16(t1_col(buf) + lane_off + (uint32_t)ch, r);
+          if (pass == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(buf));      // the values are in registers: release the buffer early
           }
-          sv[2 * j] = s0; sv[2 * j + 1] = s1;
-          cm = fmaxf(cm, fmaxf(s0, s1));
-        }
-        if (cm > m_run) { l_run *= ex2((m_run - cm) * LOG2E); m_run = cm; }
-        if (m_run > -INFINITY) {
-          const float mL = m_run * LOG2E;
+          float sv[16], cm = -INFINITY;
 #pragma unroll
-          for (int i = 0; i < 16; ++i) l_run += ex2(fmaf(sv[i], LOG2E, -mL));
+          for (int j = 0; j < 8; ++j) {
+            // bf16(bf16(acc) * scale), two at a time
+            const uint32_t s2 = bmul2(pack2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])), scale2);
+            float s0 = bf_lo(s2), s1 = bf_hi(s2);
+            if (diag) {
+              if (k0 + 2 * j > my) s0 = -INFINITY;
+              if (k0 + 2 * j + 1 > my) s1 = -INFINITY;
+            }
+            sv[2 * j] = s0; sv[2 * j + 1] = s1;
+            cm = fmaxf(cm, fmaxf(s0, s1));
+          }
+          if (cm > m_run) { l_run *= ex2((m_run - cm) * LOG2E); m_run = cm; }
+          if (m_run > -INFINITY) {
+            const float mL = m_run * LOG2E;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) l_run += ex2(fmaf(sv[i], LOG2E, -mL));
+          }
         }
       }
       // combine the four partial results of each row through shared memory (every warp sums them in the same order)
@@ -347,103 +385,119 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
         inv1 = 1.f / (l_run + PCPB_GUARD);
       }
     }
-    const int g0 = g;
+    const int g0 = (MODE == MODE_FWD) ? n_it : 0;            // n_it is even: the buffer of sub-tile `it` is it & 1
     const float mL_row = m_run * LOG2E;
-    for (int it = 0; it < n_it && ok; ++it) {
-      const int gg = g0 + it, buf = gg & 1;
-      int c0 = 0;                                            // first column-side position of this thread's columns
+    for (int it = grp2; it < n_it && ok; it += 2) {
+      const int gg = g0 + it, buf = it & 1;
+      int cbase = 0;                                         // first column-side position of this thread's 32 columns
       // per-warp copy of the column statistics (no cross-warp barrier: a warp that gave up cannot block the others)
-      float* st = stat + ((warp - 2) * 2 + (it & 1)) * 96;
+      float* st = stat + ((warp - 2) * 2 + ((it >> 1) & 1)) * 192;
       if (MODE == MODE_DKV) {
         const int hh = h + it / n_q;
-        c0 = r0 + (it % n_q) * 64 + ch;
-        if (lane < 16) {
-          const long long idx = ((long long)b * p.H + hh) * p.T + c0 + lane;
-          const float mm = p.mrow[idx], ll = p.lrow[idx], dd = p.drow[idx];
-          const float i2 = 1.f / (ll + 2.f * PCPB_GUARD);
-          st[lane] = mm; st[16 + lane] = 1.f / (ll + PCPB_GUARD); st[32 + lane] = i2; st[48 + lane] = dd;
-          st[64 + lane] = dd * (2.f * PCPB_GUARD) * i2; st[80 + lane] = mm * LOG2E;
-        }
+        cbase = r0 + (it % n_q) * 64 + half * 32;
+        const long long idx = ((long long)b * p.H + hh) * p.T + cbase + lane;
+        const float mm = p.mrow[idx], ll = p.lrow[idx], dd = p.drow[idx];
+        const float i2 = 1.f / (ll + 2.f * PCPB_GUARD);
+        st[lane] = mm; st[32 + lane] = 1.f / (ll + PCPB_GUARD); st[64 + lane] = i2; st[96 + lane] = dd;
+        st[128 + lane] = dd * (2.f * PCPB_GUARD) * i2; st[160 + lane] = mm * LOG2E;
         __syncwarp();
       } else {
-        c0 = it * 64 + ch;
+        cbase = it * 64 + half * 32;
       }
       ok = __all_sync(0xffffffffu, twait(17, tfull_bar(buf), ((uint32_t)gg >> 1) & 1u, p.err, tacc[6]));
       if (!ok) break;
       tc_fence_after();
-      // does the causal boundary cross this thread block of 32 rows x 16 columns?
-      const bool diag = (MODE == MODE_DKV) ? (c0 < r0 + 128) : (c0 + 15 > r0);
-      uint32_t r1[16];
-      tmem_ld16(t1_col(buf) + lane_off + (uint32_t)ch, r1);
-      uint32_t ew[8], pw[8];
-      if (MODE == MODE_FWD) {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar(buf));
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t s2 = bmul2(pack2(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1])), scale2);
-          float e0 = ex2(fmaf(bf_lo(s2), LOG2E, -mL_row)) * inv1, e1 = ex2(fmaf(bf_hi(s2), LOG2E, -mL_row)) * inv1;
-          if (diag) {
-            if (c0 + 2 * j > my) e0 = 0.f;
-            if (c0 + 2 * j + 1 > my) e1 = 0.f;
-          }
-          ew[j] = pack2(e0, e1);
-        }
-      } else {
-        uint32_t r2[16];
-        tmem_ld16(t2_col(buf) + lane_off + (uint32_t)ch, r2);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar(buf));
-#pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          // statistics of the four columns of this group: broadcast row values (dQ) or per-column values (dK, dV)
-          float mm[4], i1[4], i2[4], dd[4], mt[4], mL[4];
-          if (MODE == MODE_DQ) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) { mm[e] = m_run; i1[e] = 0.f; i2[e] = inv2; dd[e] = Dr; mt[e] = mterm; mL[e] = mL_row; }
-          } else {
-            const float4* s4 = reinterpret_cast<const float4*>(st) + j4;
-            const float4 a = s4[0], bq = s4[4], c = s4[8], d4 = s4[12], e4 = s4[16], f = s4[20];
-            mm[0] = a.x; mm[1] = a.y; mm[2] = a.z; mm[3] = a.w;
-            i1[0] = bq.x; i1[1] = bq.y; i1[2] = bq.z; i1[3] = bq.w;
-            i2[0] = c.x; i2[1] = c.y; i2[2] = c.z; i2[3] = c.w;
-            dd[0] = d4.x; dd[1] = d4.y; dd[2] = d4.z; dd[3] = d4.w;
-            mt[0] = e4.x; mt[1] = e4.y; mt[2] = e4.z; mt[3] = e4.w;
-            mL[0] = f.x; mL[1] = f.y; mL[2] = f.z; mL[3] = f.w;
+      for (int pass = 0; pass < 2; ++pass) {
+        const int ch = half * 32 + pass * 16, c0 = cbase + pass * 16;
+        // does the causal boundary cross this block of 32 rows x 16 columns?
+        const bool diag = (MODE == MODE_DKV) ? (c0 < r0 + 128) : (c0 + 15 > r0);
+        uint32_t r1[16];
+        tmem_ld16(t1_col(buf) + lane_off + (uint32_t)ch, r1);
+        uint32_t ew[8], pw[8];
+        if (MODE == MODE_FWD) {
+          if (pass == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(buf));
           }
 #pragma unroll
-          for (int jj = 0; jj < 2; ++jj) {
-            const int j = j4 * 2 + jj, e0i = jj * 2, e1i = jj * 2 + 1;
+          for (int j = 0; j < 8; ++j) {
             const uint32_t s2 = bmul2(pack2(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1])), scale2);
-            const uint32_t d2 = pack2(__uint_as_float(r2[2 * j]), __uint_as_float(r2[2 * j + 1]));
-            const float s0 = bf_lo(s2), s1 = bf_hi(s2), dp0 = bf_lo(d2), dp1 = bf_hi(d2);
-            float e0 = ex2(fmaf(s0, LOG2E, -mL[e0i])), e1 = ex2(fmaf(s1, LOG2E, -mL[e1i]));
-            bool k0 = true, k1 = true;                        // not masked
+            float e0 = ex2(fmaf(bf_lo(s2), LOG2E, -mL_row)) * inv1, e1 = ex2(fmaf(bf_hi(s2), LOG2E, -mL_row)) * inv1;
             if (diag) {
-              if (MODE == MODE_DQ) { k0 = !(c0 + 2 * j > my); k1 = !(c0 + 2 * j + 1 > my); }
-              else { k0 = !(my > c0 + 2 * j); k1 = !(my > c0 + 2 * j + 1); }
-              if (!k0) e0 = 0.f;
-              if (!k1) e1 = 0.f;
+              if (c0 + 2 * j > my) e0 = 0.f;
+              if (c0 + 2 * j + 1 > my) e1 = 0.f;
             }
-            float ds0 = e0 * i2[e0i] * (dp0 - dd[e0i]), ds1 = e1 * i2[e1i] * (dp1 - dd[e1i]);
-            if (k0 && s0 == mm[e0i]) ds0 -= mt[e0i];
-            if (k1 && s1 == mm[e1i]) ds1 -= mt[e1i];
-            // bf16(bf16(ds) * scale)
-            ew[j] = bmul2(pack2(ds0, ds1), scale2);
-            if (MODE == MODE_DKV) pw[j] = pack2(e0 * i1[e0i], e1 * i1[e1i]);
+            ew[j] = pack2(e0, e1);
           }
+        } else {
+          uint32_t r2[16];
+          tmem_ld16(t2_col(buf) + lane_off + (uint32_t)ch, r2);
+          if (pass == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(buf));
+          }
+#pragma unroll
+          for (int j4 = 0; j4 < 4; ++j4) {
+            // statistics of the four columns of this group: broadcast row values (dQ) or per-column values (dK, dV)
+            float mm[4], i1[4], i2[4], dd[4], mt[4], mL[4];
+            if (MODE == MODE_DQ) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) { mm[e] = m_run; i1[e] = 0.f; i2[e] = inv2; dd[e] = Dr; mt[e] = mterm; mL[e] = mL_row; }
+            } else {
+              const float4* s4 = reinterpret_cast<const float4*>(st) + pass * 4 + j4;
+              const float4 a = s4[0], bq = s4[8], c = s4[16], d4 = s4[24], e4 = s4[32], f = s4[40];
+              mm[0] = a.x; mm[1] = a.y; mm[2] = a.z; mm[3] = a.w;
+              i1[0] = bq.x; i1[1] = bq.y; i1[2] = bq.z; i1[3] = bq.w;
+              i2[0] = c.x; i2[1] = c.y; i2[2] = c.z; i2[3] = c.w;
+              dd[0] = d4.x; dd[1] = d4.y; dd[2] = d4.z; dd[3] = d4.w;
+              mt[0] = e4.x; mt[1] = e4.y; mt[2] = e4.z; mt[3] = e4.w;
+              mL[0] = f.x; mL[1] = f.y; mL[2] = f.z; mL[3] = f.w;
+            }
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj) {
+              const int j = j4 * 2 + jj, e0i = jj * 2, e1i = jj * 2 + 1;
+              const uint32_t s2 = bmul2(pack2(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1])), scale2);
+              const uint32_t d2 = pack2(__uint_as_float(r2[2 * j]), __uint_as_float(r2[2 * j + 1]));
+              const float s0 = bf_lo(s2), s1 = bf_hi(s2), dp0 = bf_lo(d2), dp1 = bf_hi(d2);
+              float e0 = ex2(fmaf(s0, LOG2E, -mL[e0i])), e1 = ex2(fmaf(s1, LOG2E, -mL[e1i]));
+              bool k0 = true, k1 = true;                      // not masked
+              if (diag) {
+                if (MODE == MODE_DQ) { k0 = !(c0 + 2 * j > my); k1 = !(c0 + 2 * j + 1 > my); }
+                else { k0 = !(my > c0 + 2 * j); k1 = !(my > c0 + 2 * j + 1); }
+                if (!k0) e0 = 0.f;
+                if (!k1) e1 = 0.f;
+              }
+              float ds0 = e0 * i2[e0i] * (dp0 - dd[e0i]), ds1 = e1 * i2[e1i] * (dp1 - dd[e1i]);
+              if (k0 && s0 == mm[e0i]) ds0 -= mt[e0i];
+              if (k1 && s1 == mm[e1i]) ds1 -= mt[e1i];
+              // bf16(bf16(ds) * scale)
+              ew[j] = bmul2(pack2(ds0, ds1), scale2);
+              if (MODE == MODE_DKV) pw[j] = pack2(e0 * i1[e0i], e1 * i1[e1i]);
+            }
+          }
+        }
+        if (MODE == MODE_FWD) {
+          // the output product that read this P buffer two sub-tiles ago must have finished
+          if (pass == 0) {
+            ok = __all_sync(0xffffffffu, twait(18, eempty_bar(buf), (((uint32_t)it >> 1) & 1u) ^ 1u, p.err, tacc[7]));
+            if (!ok) break;
+          }
+          tmem_st8(pcol(buf) + lane_off + (uint32_t)(ch >> 1), ew);
+        } else {
+          // over my own columns of the score buffer(s): nobody else reads them, and the next score product into this
+          // buffer is issued after the output product that consumes these tiles
+          if (MODE == MODE_DKV) tmem_st8(t1_col(buf) + lane_off + (uint32_t)ch, pw);
+          tmem_st8((MODE == MODE_DKV ? t2_col(buf) : t1_col(buf)) + lane_off + (uint32_t)ch, ew);
         }
       }
-      // the previous output products must have finished reading the result tile(s)
-      ok = __all_sync(0xffffffffu, twait(18, eempty_bar, ((uint32_t)it & 1u) ^ 1u, p.err, tacc[7]));
       if (!ok) break;
-      if (MODE == MODE_DKV) { store_e16(sE, row, ch, pw); store_e16(sE + E_BYTES, row, ch, ew); }
-      else store_e16(sE, row, ch, ew);
-      fence_proxy_async_smem();
+      tmem_st_wait();
+      tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(efull_bar);
+      if (lane == 0) mbar_arrive(efull_bar(buf));
     }
     // ---- outputs: each warp stores 32 of the 128 output columns of its rows ----
     if (ok) ok = __all_sync(0xffffffffu, twait(19, out_bar, 0, p.err, tacc[8]));
@@ -525,6 +579,7 @@ bool fill(const FlashArgs& a, int* err, AtcParams* p, CUtensorMap* mq, CUtensorM
   const int d = a.H * HD, dkv = a.Hkv * HD;
   const uint64_t M = (uint64_t)a.B * a.T;
   p->B = a.B; p->T = a.T; p->H = a.H; p->Hkv = a.Hkv; p->scale = a.scale; p->d = d; p->dkv = dkv;
+  p->qkn = (const bf16*)a.qkn; p->dout = (const bf16*)a.dout;
   p->o = (bf16*)a.o; p->mrow = a.mrow; p->lrow = a.lrow; p->drow = a.drow; p->dqkn = (bf16*)a.dqkn; p->dqkv = (bf16*)a.dqkv;
   p->err = err;
   bool ok = make_map(mq, a.qkn, (uint64_t)(d + dkv), M, (uint64_t)(d + dkv), 64) &&

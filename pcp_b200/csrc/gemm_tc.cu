@@ -42,6 +42,7 @@ struct TcParams {
   int tiles_m, tiles_n, splits, kb_per_split;
   int group_m;                 // row tiles per group of the tile order (1 = plain row-major order)
   int epi;
+  int wide;                    // 1: rows of C / C2 / R start on 32-byte boundaries, so 256-bit accesses may be used
   void* C; long long ldc;
   const void* R; void* C2;
   float clip;
@@ -66,6 +67,15 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, int c
         if (!((v - v) == 0.f)) v = 0.f;
         acc[i] = fminf(fmaxf(v, -p.clip), p.clip);
       }
+    }
+    if (p.wide) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 lo = make_uint4(__float_as_uint(acc[8 * i]), __float_as_uint(acc[8 * i + 1]), __float_as_uint(acc[8 * i + 2]), __float_as_uint(acc[8 * i + 3]));
+        const uint4 hi = make_uint4(__float_as_uint(acc[8 * i + 4]), __float_as_uint(acc[8 * i + 5]), __float_as_uint(acc[8 * i + 6]), __float_as_uint(acc[8 * i + 7]));
+        st_global_256(dst + 8 * i, lo, hi);
+      }
+      return;
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i)
@@ -124,20 +134,27 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, int c
     outv[q].x = pack2(acc[8 * q + 0], acc[8 * q + 1]); outv[q].y = pack2(acc[8 * q + 2], acc[8 * q + 3]);
     outv[q].z = pack2(acc[8 * q + 4], acc[8 * q + 5]); outv[q].w = pack2(acc[8 * q + 6], acc[8 * q + 7]);
   }
+  if (p.wide) { st_global_256(C, outv[0], outv[1]); st_global_256(C + 16, outv[2], outv[3]); }
+  else {
 #pragma unroll
-  for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(C)[q] = outv[q];
+    for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(C)[q] = outv[q];
+  }
   if (p.epi == EPI_RELU2 || p.epi == EPI_RELU) {
     __nv_bfloat16* C2 = (__nv_bfloat16*)p.C2 + o;
     const bool sq = (p.epi == EPI_RELU2);
+    uint4 av[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       float x[8];
       unpack8(outv[q], x);                                     // u as stored (bf16)
 #pragma unroll
       for (int i = 0; i < 8; ++i) { const float rr = fmaxf(x[i], 0.f); x[i] = sq ? rr * rr : rr; }
-      uint4 v;
-      v.x = pack2(x[0], x[1]); v.y = pack2(x[2], x[3]); v.z = pack2(x[4], x[5]); v.w = pack2(x[6], x[7]);
-      reinterpret_cast<uint4*>(C2)[q] = v;
+      av[q].x = pack2(x[0], x[1]); av[q].y = pack2(x[2], x[3]); av[q].z = pack2(x[4], x[5]); av[q].w = pack2(x[6], x[7]);
+    }
+    if (p.wide) { st_global_256(C2, av[0], av[1]); st_global_256(C2 + 16, av[2], av[3]); }
+    else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(C2)[q] = av[q];
     }
   }
 }
@@ -290,8 +307,13 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUt
       uint4 rpre[NCH * 4];
       if (reads_r) {
         const uint4* rp = reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.R + (size_t)row * p.ldc + n0);
+        if (p.wide) {
 #pragma unroll
-        for (int i = 0; i < NCH * 4; ++i) rpre[i] = __ldg(rp + i);
+          for (int i = 0; i < NCH * 2; ++i) ld_global_256(rp + 2 * i, rpre[2 * i], rpre[2 * i + 1]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < NCH * 4; ++i) rpre[i] = __ldg(rp + i);
+        }
       }
       ok = mbar_wait(tfull_bar(acc), aph, p.err, 4);
       ok = __all_sync(0xffffffffu, ok);
@@ -430,6 +452,11 @@ cudaError_t launch_gemm_tc(cudaStream_t st, const GemmArgs& g) {
   p.M = g.M; p.N = g.N; p.K = g.K;
   p.tiles_m = g.M / BM; p.tiles_n = g.N / pl.bn; p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
   p.group_m = (p.tiles_n >= 32 && p.splits == 1) ? 8 : 1;
+  {
+    // 256-bit epilogue accesses need every row segment to start on a 32-byte boundary (16 bf16 / 8 f32 elements)
+    const uintptr_t all = (uintptr_t)g.C | (uintptr_t)g.R | (uintptr_t)g.C2 | (uintptr_t)g.scratch;
+    p.wide = ((all & 31) == 0 && g.ldc % 16 == 0 && g.N % 16 == 0) ? 1 : 0;
+  }
   p.epi = g.epi; p.C = g.C; p.ldc = g.ldc; p.R = g.R; p.C2 = g.C2; p.clip = g.clip; p.slab = nullptr; p.err = err;
   if (pl.splits > 1) p.slab = (float*)g.scratch;
   const int items = p.tiles_m * p.tiles_n * p.splits;
