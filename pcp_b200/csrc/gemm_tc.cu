@@ -82,79 +82,67 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, int c
       reinterpret_cast<float4*>(dst)[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
     return;
   }
+  // bf16 outputs, two per 32-bit word.  Every step after the packing is one bf16 operation of the exported graph:
+  // the dot result is rounded to bf16, and add / mul / max on bf16 pairs round their exact result once, as its ops do.
   __nv_bfloat16* C = (__nv_bfloat16*)p.C + o;
   if (p.epi == EPI_BIAS) {
+    // the graph adds the bias to the f32 dot result and rounds once
     const uint4* bp = reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.R + col);      // bias[N], model dtype
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      float x[8];
-      unpack8(bp[q], x);
+      float xb[8];
+      unpack8(bp[q], xb);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[8 * q + i] += x[i];
+      for (int i = 0; i < 8; ++i) acc[8 * q + i] += xb[i];
     }
   }
-  if (p.epi == EPI_DRELU) {
-    const uint4* rp = rpre;
+  uint32_t w[16];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      float x[8];
-      unpack8(rp[q], x);
+  for (int j = 0; j < 16; ++j) w[j] = pack2(acc[2 * j], acc[2 * j + 1]);
+  const uint32_t* x = reinterpret_cast<const uint32_t*>(rpre);     // per-element operand, when the epilogue has one
+  if (p.epi == EPI_RESID) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[8 * q + i] = x[i] > 0.f ? acc[8 * q + i] : 0.f;
+    for (int j = 0; j < 16; ++j) w[j] = badd2(x[j], w[j]);
+  } else if (p.epi == EPI_DRELU) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const uint32_t lo = bf_lo(x[j]) > 0.f ? (w[j] & 0xFFFFu) : 0u, hi = bf_hi(x[j]) > 0.f ? (w[j] & 0xFFFF0000u) : 0u;
+      w[j] = lo | hi;
+    }
+  } else if (p.epi == EPI_DRELU2) {
+    // backward of a = power(max(u,0), 2):  da * bf16(2 * bf16(bf16(r*r) / r)), r = max(u, 0); zero where u <= 0.
+    // The quotient of two bf16 values is never a rounding tie of bf16 and is at least 2^-17 (relative) away from
+    // one, so y * rcp(r) (2 ulp of f32) rounds to the same bf16 as the exact division.
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const uint32_t r2 = bmax2(x[j], 0u);
+      const uint32_t y2 = bmul2(r2, r2);
+      const float q0 = bf_lo(y2) * rcp_approx(fmaxf(bf_lo(r2), 1e-30f)), q1 = bf_hi(y2) * rcp_approx(fmaxf(bf_hi(r2), 1e-30f));
+      const uint32_t t2 = bmul2(pack2(q0, q1), 0x40004000u);           // 2 * q
+      w[j] = bmul2(w[j], t2);
     }
   }
-  if (p.epi == EPI_RESID || p.epi == EPI_DRELU2) {
-    const uint4* rp = rpre;
+  if (p.wide) {
+    st_global_256(C, make_uint4(w[0], w[1], w[2], w[3]), make_uint4(w[4], w[5], w[6], w[7]));
+    st_global_256(C + 16, make_uint4(w[8], w[9], w[10], w[11]), make_uint4(w[12], w[13], w[14], w[15]));
+  } else {
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      float x[8];
-      unpack8(rp[q], x);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float a = bf16_round(acc[8 * q + i]);
-        if (p.epi == EPI_RESID) {
-          acc[8 * q + i] = x[i] + a;
-        } else {
-          // backward of a = power(max(u,0), 2):  da * (2 * (bf16(r*r) / r)) where u > 0
-          const float u = x[i], rr = fmaxf(u, 0.f);
-          float out = 0.f;
-          if (u > 0.f) {
-            const float y = bf16_round(rr * rr);
-            const float qq = bf16_round(y / rr);
-            out = a * bf16_round(2.f * qq);
-          }
-          acc[8 * q + i] = out;
-        }
-      }
-    }
-  }
-  uint4 outv[4];
-#pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    outv[q].x = pack2(acc[8 * q + 0], acc[8 * q + 1]); outv[q].y = pack2(acc[8 * q + 2], acc[8 * q + 3]);
-    outv[q].z = pack2(acc[8 * q + 4], acc[8 * q + 5]); outv[q].w = pack2(acc[8 * q + 6], acc[8 * q + 7]);
-  }
-  if (p.wide) { st_global_256(C, outv[0], outv[1]); st_global_256(C + 16, outv[2], outv[3]); }
-  else {
-#pragma unroll
-    for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(C)[q] = outv[q];
+    for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(C)[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
   }
   if (p.epi == EPI_RELU2 || p.epi == EPI_RELU) {
+    // second output: max(u, 0) or its square, from u as stored
     __nv_bfloat16* C2 = (__nv_bfloat16*)p.C2 + o;
-    const bool sq = (p.epi == EPI_RELU2);
-    uint4 av[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      float x[8];
-      unpack8(outv[q], x);                                     // u as stored (bf16)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) { const float rr = fmaxf(x[i], 0.f); x[i] = sq ? rr * rr : rr; }
-      av[q].x = pack2(x[0], x[1]); av[q].y = pack2(x[2], x[3]); av[q].z = pack2(x[4], x[5]); av[q].w = pack2(x[6], x[7]);
+    for (int j = 0; j < 16; ++j) {
+      const uint32_t r2 = bmax2(w[j], 0u);
+      w[j] = (p.epi == EPI_RELU2) ? bmul2(r2, r2) : r2;
     }
-    if (p.wide) { st_global_256(C2, av[0], av[1]); st_global_256(C2 + 16, av[2], av[3]); }
-    else {
+    if (p.wide) {
+      st_global_256(C2, make_uint4(w[0], w[1], w[2], w[3]), make_uint4(w[4], w[5], w[6], w[7]));
+      st_global_256(C2 + 16, make_uint4(w[8], w[9], w[10], w[11]), make_uint4(w[12], w[13], w[14], w[15]));
+    } else {
 #pragma unroll
-      for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(C2)[q] = av[q];
+      for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(C2)[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
     }
   }
 }

@@ -190,14 +190,18 @@ def test_adam_kat_single_step():
 
 
 def _close(got, want, tol, dtype):
-    """f32: element-wise, atol at 1e-1 of the tolerance (the reference's own parity test uses atol = rtol = 1e-4; the
-    embedding gradients are accumulated with float atomics, so the last bits vary from run to run).  bf16: relative L2 error of the whole parameter vector —
-    Adam's m/sqrt(v) turns bf16 rounding noise of near-zero gradients into +-lr steps on single elements, so an
-    element-wise bound is not meaningful there (the reference states its bf16 tolerance on the loss curve)."""
+    """f32: element-wise with atol = rtol = tol, the criterion of the reference's own parity test
+    (test/nanochat/test_pcp_training_step_parity.py:38), plus the same bound on the relative L2 error of the
+    whole vector.  (A tighter element-wise atol is not stable from run to run: embedding and generic-attention
+    gradients are accumulated with float atomics, and Adam's m/sqrt(v) turns last-bit differences of near-zero
+    gradients into differences of a fraction of a step on single elements.)  bf16: relative L2 error of the whole
+    parameter vector — the same amplification acts on bf16 rounding noise, so an element-wise bound is not
+    meaningful there (the reference states its bf16 tolerance on the loss curve)."""
+    err = np.linalg.norm(got.astype(np.float64) - want.astype(np.float64)) / np.linalg.norm(want.astype(np.float64))
     if dtype == "f32":
-        np.testing.assert_allclose(got, want, rtol=tol, atol=tol * 1e-1)
+        np.testing.assert_allclose(got, want, rtol=tol, atol=tol)
+        assert err <= tol, err
     else:
-        err = np.linalg.norm(got.astype(np.float64) - want.astype(np.float64)) / np.linalg.norm(want.astype(np.float64))
         assert err <= tol, err
 
 
