@@ -43,12 +43,19 @@ WORKLOADS = {
     # d8 geometry at a quarter of the batch: small enough for an `ncu --set full` capture
     "d8b2": dict(vocab=65536, d_model=512, n_layer=8, n_head=4, n_kv_head=4, seq_len=2048, batch=2, dtype="bf16"),
     "tiny": dict(vocab=4096, d_model=256, n_layer=2, n_head=2, n_kv_head=2, seq_len=256, batch=4, dtype="bf16"),
+    # d20 layer geometry at profiling sizes (the kernels and their shapes per token are those of d20)
+    "d20l1b8": dict(vocab=4096, d_model=1280, n_layer=1, n_head=10, n_kv_head=10, seq_len=2048, batch=8, dtype="bf16"),
+    "d20l2b2": dict(vocab=65536, d_model=1280, n_layer=2, n_head=10, n_kv_head=10, seq_len=2048, batch=2, dtype="bf16"),
+    "d20l2b4": dict(vocab=65536, d_model=1280, n_layer=2, n_head=10, n_kv_head=10, seq_len=2048, batch=4, dtype="bf16"),
 }
 DESCR = {
     "d20": "nanochat-d20 bf16 DiLoCo inner step, B=32/GPU, T=2048, AdamW(lr 1e-3, 0.9/0.95, wd 0.1), H=50",
     "d8": "nanochat-d8 (d=512) bf16 inner step, B=8, T=2048, AdamW lr 1e-3",
     "d8b2": "nanochat-d8 (d=512) bf16 inner step, B=2, T=2048 (profiling size)",
     "tiny": "nanochat tiny bf16 inner step (smoke size)",
+    "d20l1b8": "one d20 layer (d=1280, 10 heads x 128), V=4096, B=8, T=2048 (attention profiling size)",
+    "d20l2b2": "two d20 layers + the d20 LM head, B=2, T=2048 (GEMM DRAM-traffic profiling size)",
+    "d20l2b4": "two d20 layers + the d20 LM head, B=4, T=2048 (GEMM DRAM-traffic profiling size)",
 }
 H_INNER = 50
 PEAKS_FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
