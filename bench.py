@@ -319,6 +319,16 @@ def run_ours(args):
     peak_burst = peaks.get("bf16_tflops", PEAKS_FALLBACK["bf16_tflops"]) * 1e12
     peak_sust = peaks.get("bf16_tflops_sustained", PEAKS_FALLBACK["bf16_tflops_sustained"]) * 1e12
     achieved = prof["flops"] / (prof["ms"] / 1e3) / 1e12 if prof["ms"] > 0 else 0.0
+    # DRAM traffic of the largest k_gemm_tc launch of the step, the LM-head forward [B*T x V x d]: ncu measured
+    # 1.180 GB (B=2) and 2.398 GB (B=4) of dram read + write for it at the d20 width and vocabulary
+    # (profiles/k_gemm_tc_d8b2_ncu_full.md); it grows in proportion to the rows, 0.29 MB per row.
+    traffic, traffic_note = None, None
+    if (cfgd["d_model"], cfgd["vocab"]) == (1280, 65536):
+        rows = cfgd["batch"] * cfgd["seq_len"]
+        traffic = 0.29e6 * rows
+        alg = 2.0 * (rows * cfgd["d_model"] + cfgd["vocab"] * cfgd["d_model"] + rows * cfgd["vocab"])
+        traffic_note = (f"bytes of the LM-head forward launch ({rows}x{cfgd['vocab']}x{cfgd['d_model']}), scaled by rows from "
+                        f"ncu captures at B=2 and B=4; algorithmic bytes of that launch {alg:.4g}")
     line = {
         "metric": "train_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
@@ -333,7 +343,8 @@ def run_ours(args):
                 "mfu_palm_convention_vs_measured_burst": per_gpu_tps * fpalm / peak_burst, "peaks": peak_src},
         "roofline": {"kernel": "k_gemm_tc (tcgen05 bf16 GEMM)", "bound": "tensor", "achieved": achieved,
                      "peak": peak_sust / 1e12, "unit": "TFLOP/s", "frac": achieved / (peak_sust / 1e12) if peak_sust else None,
-                     "traffic": None, "launches": prof["launches"], "kernel_ms_share_of_step": prof["ms"] / ms if ms else None,
+                     "traffic": traffic, "traffic_note": traffic_note,
+                     "launches": prof["launches"], "kernel_ms_share_of_step": prof["ms"] / ms if ms else None,
                      "peak_source": f"{peak_src} sustained bf16"},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": Ke, "how": "pcpb_worker_begin_round(host blob) + per step: host token window -> pcpb_worker_step -> "
