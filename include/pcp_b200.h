@@ -172,6 +172,36 @@ int pcpb_outer_prepare(pcpb_backend* b, const pcpb_outer_cfg* cfg);
 int pcpb_outer_apply(pcpb_backend* b, const pcpb_outer_cfg* cfg, const int* contributors, int n_contributors,
                      double* device_ms);
 
+/* ---- Streaming DiLoCo: fragment-wise outer step --------------------------------------------------------------
+ * Replaces the worker's extractAndSendFragment / receiveAndMergeFragment (src/nodes/workers/worker.zig:2396-2479,
+ * 2482-2610) and the Shepherd's accumulateFragmentGradients / applyFragmentUpdate
+ * (src/algorithms/streaming_diloco.zig:425-520).  Tensor i (artefact argument order) belongs to fragment
+ * i % num_fragments (worker.zig:2417).  The calls are made inside a round opened with pcpb_worker_begin_round
+ * (tau = the number of streaming steps; Adam state persists over the whole loop as in worker.zig:2249-2345), between
+ * pcpb_worker_step calls, on the schedule of worker.zig:2213-2239 (pcp_b200/diloco.py restates it):
+ *   pcpb_stream_begin   once after pcpb_worker_begin_round: snapshot <- parameters (worker.zig:2124-2176); the
+ *                       round-start buffer serves as this rank's replica of the master parameters
+ *   pcpb_stream_send    delta[fragment] = snapshot - parameters, snapshot <- parameters; returns when the delta
+ *                       is visible to the peers
+ *   (barrier)
+ *   pcpb_stream_outer   this rank's shard of the fragment: sum of the ranks' deltas in rank order / world,
+ *                       Nesterov on master and velocity (no non-finite filter, no truncation: f32 as the
+ *                       reference's streaming path), new master written into every rank's replica
+ *   (barrier)
+ *   pcpb_stream_merge   overlap_tau steps later: parameters[fragment] <- alpha*parameters + (1-alpha)*master,
+ *                       snapshot <- the blend
+ * Needs pcpb_outer_attach_* first (same peer mapping and sharding as the DiLoCo outer step). */
+typedef struct pcpb_stream_cfg {
+  int num_fragments;        /* 4 in the reference (worker.zig:179) */
+  float alpha;              /* blend weight of the local parameters */
+  float learning_rate;      /* Nesterov, as pcpb_outer_cfg */
+  float momentum;
+} pcpb_stream_cfg;
+int pcpb_stream_begin(pcpb_backend* b, const pcpb_stream_cfg* cfg);
+int pcpb_stream_send(pcpb_backend* b, int fragment);
+int pcpb_stream_outer(pcpb_backend* b, int fragment, double* device_ms);
+int pcpb_stream_merge(pcpb_backend* b, int fragment);
+
 /* Loss of the most recent pcpb_worker_step, read back to the host (blocks until that step has run): the
  * per-step loss read of the reference's inner loop (src/nodes/workers/worker.zig:1246). */
 int pcpb_worker_last_loss(pcpb_backend* b, float* loss);

@@ -10,6 +10,8 @@ outer_step       src/algorithms/diloco.zig:828-1060 (f32 sum of deltas, / collec
 """
 from __future__ import annotations
 
+import math
+
 import torch
 
 from . import autodiff, sanitizer, stablehlo as hlo
@@ -125,3 +127,87 @@ def outer_step(master, velocities, worker_deltas, worker_losses, conf: NesterovC
         new_vel.append(ve)
     loss = float(sum(worker_losses) / n) if n else 0.0
     return new_master, new_vel, loss
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Streaming DiLoCo (src/nodes/workers/worker.zig:2207-2610, src/algorithms/streaming_diloco.zig:425-466)
+# ---------------------------------------------------------------------------------------------------------
+def fragment_phase_start(p: int, inner_steps: int, num_fragments: int) -> int:
+    """First step of fragment p's cycle: floor(p * H / P) (worker.zig:2367-2373)."""
+    return int(math.floor(float(p) * float(inner_steps) / float(num_fragments)))
+
+
+def streaming_schedule(t: int, num_fragments: int, inner_steps: int, overlap_tau: int, max_rounds: int):
+    """(receives, sends) of step t (1-based), each a list of (fragment, fragment_round) in fragment order.
+    Receives happen before the step's compute, sends after it (worker.zig:2213-2239); rounds past max_rounds are
+    skipped (:2219, :2235)."""
+    recv, send = [], []
+    for p in range(num_fragments):
+        tp = fragment_phase_start(p, inner_steps, num_fragments)
+        if t > tp + overlap_tau and (t - tp - overlap_tau) % inner_steps == 0:
+            r = (t - tp - overlap_tau) // inner_steps - 1                 # fragmentReceiveRound, :2380-2383
+            if r < max_rounds:
+                recv.append((p, r))
+        if t > tp and (t - tp) % inner_steps == 0:
+            r = (t - tp) // inner_steps - 1                               # fragmentSendRound, :2375-2378
+            if r < max_rounds:
+                send.append((p, r))
+    return recv, send
+
+
+def streaming_loop(mod: TrainingModule, master, datasets, num_fragments: int, inner_steps: int, overlap_tau: int,
+                   alpha: float, max_rounds: int, batch: int, block: int, conf: AdamConf, nconf: NesterovConf,
+                   record=None):
+    """W workers (one dataset each) and the Shepherd's fragment state, stepped in lock-step.
+
+    Worker: tensor i belongs to fragment i % P (worker.zig:2417).  Every step: merge the fragments due
+    (blend = alpha*current + (1-alpha)*global, snapshot <- blend, :2583-2600), one compute_gradients +
+    apply_optimizer with persistent m, v and an increasing timestep (:2249-2345), then send the fragments due
+    (delta = snapshot - current, snapshot <- current, :2433-2437).  Shepherd: per fragment, deltas summed in
+    arrival order, divided by the worker count, Nesterov on the master tensors, the new master tensors broadcast
+    (streaming_diloco.zig:425-466); no non-finite filter and no truncation on this path.  All f32.
+    Returns (final params per worker, master, velocities, per-step losses per worker)."""
+    W = len(datasets)
+    P = num_fragments
+    a = torch.tensor(alpha, dtype=torch.float32)
+    one_minus_a = torch.tensor(1.0, dtype=torch.float32) - a
+    master = [p.clone().to(torch.float32) for p in master]
+    vel = [torch.zeros_like(p) for p in master]
+    params = [[p.clone() for p in master] for _ in range(W)]
+    snap = [[p.clone() for p in master] for _ in range(W)]
+    m = [[torch.zeros_like(p) for p in master] for _ in range(W)]
+    v = [[torch.zeros_like(p) for p in master] for _ in range(W)]
+    tstep = [1.0] * W
+    merged = {}                                                            # (fragment, round) -> {tensor index: tensor}
+    losses = [[] for _ in range(W)]
+    max_steps = max_rounds * inner_steps + fragment_phase_start(P - 1, inner_steps, P) + overlap_tau   # :2202-2203
+    divisor = torch.tensor(float(W), dtype=torch.float32)
+    for t in range(1, max_steps + 1):
+        recv, send = streaming_schedule(t, P, inner_steps, overlap_tau, max_rounds)
+        for w in range(W):
+            for (p, r) in recv:
+                for i, g in merged[(p, r)].items():
+                    blended = a * params[w][i] + one_minus_a * g
+                    params[w][i] = blended
+                    snap[w][i] = blended.clone()
+            x, y = datasets[w].get_batch(batch, block)
+            grads, loss = mod.compute_gradients(params[w], torch.from_numpy(x), torch.from_numpy(y))
+            params[w], m[w], v[w] = mod.apply_optimizer(params[w], grads, m[w], v[w], tstep[w], conf)
+            tstep[w] += 1.0
+            losses[w].append(float(loss.to(torch.float32)))
+        for (p, r) in send:
+            out = {}
+            for i in range(len(master)):
+                if i % P != p:
+                    continue
+                acc = torch.zeros_like(master[i])
+                for w in range(W):
+                    acc = acc + (snap[w][i] - params[w][i])
+                    snap[w][i] = params[w][i].clone()
+                acc = acc / divisor
+                master[i], vel[i] = nesterov_update(master[i], vel[i], acc, nconf)
+                out[i] = master[i].clone()
+            merged[(p, r)] = out
+        if record is not None:
+            record.append([[q.clone() for q in params[w]] for w in range(W)])
+    return params, master, vel, losses

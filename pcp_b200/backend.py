@@ -41,7 +41,8 @@ EXPORTS = [
     "pcpb_worker_end_round", "pcpb_inner_loop", "pcpb_worker_read_state", "pcpb_synchronize", "pcpb_outer_export",
     "pcpb_outer_attach_ipc", "pcpb_outer_attach_local", "pcpb_outer_prepare", "pcpb_outer_apply",
     "pcpb_launch_count", "pcpb_worker_last_loss", "pcpb_timer_start", "pcpb_timer_stop", "pcpb_profile_enable",
-    "pcpb_profile_read", "pcpb_adamw_step_noalloc",
+    "pcpb_profile_read", "pcpb_adamw_step_noalloc", "pcpb_stream_begin", "pcpb_stream_send", "pcpb_stream_outer",
+    "pcpb_stream_merge",
 ]
 
 
@@ -63,6 +64,10 @@ class InnerCfg(C.Structure):
 
 class OuterCfg(C.Structure):
     _fields_ = [("learning_rate", C.c_float), ("momentum", C.c_float), ("param_dtype", C.c_int)]
+
+
+class StreamCfg(C.Structure):
+    _fields_ = [("num_fragments", C.c_int), ("alpha", C.c_float), ("learning_rate", C.c_float), ("momentum", C.c_float)]
 
 
 _lib = None
@@ -120,6 +125,10 @@ def load_library(path: str | None = None):
     lib.pcpb_worker_last_loss.argtypes = [vp, C.POINTER(C.c_float)]
     lib.pcpb_timer_start.argtypes = [vp]
     lib.pcpb_timer_stop.argtypes = [vp, C.POINTER(C.c_double)]
+    lib.pcpb_stream_begin.argtypes = [vp, C.POINTER(StreamCfg)]
+    lib.pcpb_stream_send.argtypes = [vp, i]
+    lib.pcpb_stream_outer.argtypes = [vp, i, C.POINTER(C.c_double)]
+    lib.pcpb_stream_merge.argtypes = [vp, i]
     lib.pcpb_profile_enable.argtypes = [vp, i]
     lib.pcpb_profile_read.argtypes = [vp, C.POINTER(C.c_longlong), C.POINTER(C.c_double), C.POINTER(C.c_double)]
     lib.pcpb_adamw_step_noalloc.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ll, C.POINTER(AdamConf), C.c_float,
@@ -442,6 +451,22 @@ class Backend:
     def outer_prepare(self, learning_rate=0.7, momentum=0.9, param_dtype=F32):
         cfg = OuterCfg(learning_rate, momentum, param_dtype)
         self._check(self._lib.pcpb_outer_prepare(self._h, C.byref(cfg)))
+
+    # ---- streaming DiLoCo (worker.zig:2207-2610): fragment-wise send / outer step / merge inside a round ----
+    def stream_begin(self, num_fragments=4, alpha=0.5, learning_rate=0.7, momentum=0.9):
+        cfg = StreamCfg(num_fragments, alpha, learning_rate, momentum)
+        self._check(self._lib.pcpb_stream_begin(self._h, C.byref(cfg)))
+
+    def stream_send(self, fragment: int):
+        self._check(self._lib.pcpb_stream_send(self._h, int(fragment)))
+
+    def stream_outer(self, fragment: int) -> float:
+        ms = C.c_double()
+        self._check(self._lib.pcpb_stream_outer(self._h, int(fragment), C.byref(ms)))
+        return ms.value
+
+    def stream_merge(self, fragment: int):
+        self._check(self._lib.pcpb_stream_merge(self._h, int(fragment)))
 
     def outer_apply(self, learning_rate=0.7, momentum=0.9, param_dtype=F32, contributors=None) -> float:
         cfg = OuterCfg(learning_rate, momentum, param_dtype)

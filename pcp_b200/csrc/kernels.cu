@@ -1107,7 +1107,7 @@ __global__ void __launch_bounds__(256) k_nesterov_shard(OuterArgs a) {
     for (int w = 0; w < 8; ++w)
       if (w < a.ncontrib) acc = __fadd_rn(acc, a.deltas[w][i]);
     acc = __fdiv_rn(acc, div);
-    if (!((acc - acc) == 0.f)) acc = 0.f;
+    if (!a.keep_nonfinite && !((acc - acc) == 0.f)) acc = 0.f;
     const float vn = __fadd_rn(__fmul_rn(a.mu, a.vel[i]), acc);
     a.vel[i] = vn;
     float th = __fsub_rn(a.master[i], __fmul_rn(a.lr, __fadd_rn(acc, __fmul_rn(a.mu, vn))));
@@ -1118,6 +1118,36 @@ __global__ void __launch_bounds__(256) k_nesterov_shard(OuterArgs a) {
       if (w < a.nouts) a.outs[w][i] = th;
   }
 }
+// Streaming DiLoCo worker side (src/nodes/workers/worker.zig:2433-2437 and :2583-2600), f32, no FMA contraction.
+__global__ void k_stream_delta(float* __restrict__ snap, const float* __restrict__ theta, float* __restrict__ d, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float cur = theta[i];
+    d[i] = __fsub_rn(snap[i], cur);
+    snap[i] = cur;
+  }
+}
+__global__ void k_stream_merge(float* __restrict__ theta, const float* __restrict__ glob, float* __restrict__ snap, float alpha,
+                               size_t n) {
+  const float om = __fsub_rn(1.0f, alpha);
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = __fadd_rn(__fmul_rn(alpha, theta[i]), __fmul_rn(om, glob[i]));
+    theta[i] = v;
+    snap[i] = v;
+  }
+}
+cudaError_t launch_stream_delta(cudaStream_t st, float* snapshot, const float* theta, float* delta, size_t n) {
+  if (n == 0) return cudaSuccess;
+  k_stream_delta<<<min(cdiv(n, 256), 148u * 16), 256, 0, st>>>(snapshot, theta, delta, n);
+  return cudaGetLastError();
+}
+cudaError_t launch_stream_merge(cudaStream_t st, float* theta, const float* global, float* snapshot, float alpha, size_t n) {
+  if (n == 0) return cudaSuccess;
+  k_stream_merge<<<min(cdiv(n, 256), 148u * 16), 256, 0, st>>>(theta, global, snapshot, alpha, n);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_nesterov_shard(cudaStream_t st, const OuterArgs& a) {
   if (a.n == 0) return cudaSuccess;
   k_nesterov_shard<<<min(cdiv((size_t)a.n, 256), 148u * 8), 256, 0, st>>>(a);

@@ -138,7 +138,12 @@ struct OuterArgs {
   float* vel; float* master;
   float* outs[8]; int nouts;
   long long n; float lr, mu; int trunc;
+  int keep_nonfinite;          // 0: a non-finite mean becomes 0 (DiLoCo outer step); 1: passed on (streaming path)
 };
 cudaError_t launch_nesterov_shard(cudaStream_t st, const OuterArgs& a);
+// Streaming DiLoCo, worker side: delta = snapshot - theta, snapshot <- theta;  theta <- alpha*theta + (1-alpha)*global,
+// snapshot <- theta.
+cudaError_t launch_stream_delta(cudaStream_t st, float* snapshot, const float* theta, float* delta, size_t n);
+cudaError_t launch_stream_merge(cudaStream_t st, float* theta, const float* global, float* snapshot, float alpha, size_t n);
 
 }  // namespace pcpb

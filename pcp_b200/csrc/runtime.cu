@@ -82,6 +82,7 @@ void free_workspace(pcpb_backend* b) {
   b->ipc_opened.clear(); b->peer_delta.clear(); b->peer_theta0.clear();
   if (b->velocity) { cudaFree(b->velocity); b->velocity = nullptr; }
   b->velocity_init = false; b->have_master = false; b->in_round = false;
+  b->snapshot = nullptr; b->stream_fragments = 0;      // the snapshot lived in the workspace
 }
 
 template <typename P>
@@ -1251,6 +1252,91 @@ int pcpb_outer_apply(pcpb_backend* b, const pcpb_outer_cfg* cfg, const int* cont
   CK(b, cudaStreamSynchronize(b->stream));
   if (device_ms) { float ms = 0.f; CK(b, cudaEventElapsedTime(&ms, b->ev0, b->ev1)); *device_ms = ms; }
   b->have_master = true;
+  return PCPB_OK;
+}
+
+// ---- streaming DiLoCo ----------------------------------------------------------------------------------------
+static int stream_check(pcpb_backend* b, int fragment) {
+  int r = require_loaded(b);
+  if (r) return r;
+  if (!b->snapshot || b->stream_fragments < 1) return fail(b, PCPB_E_STATE, "streaming not started (pcpb_stream_begin)");
+  if (!b->in_round) return fail(b, PCPB_E_STATE, "streaming calls belong inside a round");
+  if (fragment < 0 || fragment >= b->stream_fragments) return fail(b, PCPB_E_INVALID, "fragment index out of range");
+  return PCPB_OK;
+}
+
+int pcpb_stream_begin(pcpb_backend* b, const pcpb_stream_cfg* cfg) {
+  int r = require_loaded(b);
+  if (r) return r;
+  if (!cfg || cfg->num_fragments < 1) return fail(b, PCPB_E_INVALID, "bad streaming configuration");
+  if (!b->in_round) return fail(b, PCPB_E_STATE, "pcpb_stream_begin must follow pcpb_worker_begin_round");
+  if (!b->velocity_init) return fail(b, PCPB_E_STATE, "outer step not attached (pcpb_outer_attach_*)");
+  DeviceGuard g(b->device);
+  const size_t P = (size_t)b->cfg.total_params;
+  if (!b->snapshot) WS(b, b->snapshot, P * 4);
+  CK(b, cudaMemcpyAsync(b->snapshot, b->ws.theta, P * 4, cudaMemcpyDeviceToDevice, b->stream));
+  b->stream_fragments = cfg->num_fragments; b->stream_alpha = cfg->alpha;
+  b->stream_lr = cfg->learning_rate; b->stream_mu = cfg->momentum;
+  return PCPB_OK;
+}
+
+int pcpb_stream_send(pcpb_backend* b, int fragment) {
+  int r = stream_check(b, fragment);
+  if (r) return r;
+  DeviceGuard g(b->device);
+  Workspace& w = b->ws;
+  const auto& ps = b->cfg.params;
+  for (size_t i = (size_t)fragment; i < ps.size(); i += (size_t)b->stream_fragments) {
+    const size_t off = (size_t)ps[i].offset, n = (size_t)ps[i].numel;
+    KL(b, 1, launch_stream_delta(b->stream, b->snapshot + off, w.theta + off, w.delta + off, n));
+  }
+  CK(b, cudaStreamSynchronize(b->stream));
+  return PCPB_OK;
+}
+
+int pcpb_stream_outer(pcpb_backend* b, int fragment, double* device_ms) {
+  int r = stream_check(b, fragment);
+  if (r) return r;
+  DeviceGuard g(b->device);
+  const long long P = b->cfg.total_params, S = b->shard_len;
+  const long long s_lo = (long long)b->rank * S < P ? (long long)b->rank * S : P;
+  const long long s_hi = s_lo + S < P ? s_lo + S : P;
+  for (int w = 0; w < b->world; ++w)
+    if (!b->peer_delta[w]) return fail(b, PCPB_E_STATE, "a peer is not attached");
+  const auto& ps = b->cfg.params;
+  CK(b, cudaEventRecord(b->ev0, b->stream));
+  for (size_t i = (size_t)fragment; i < ps.size(); i += (size_t)b->stream_fragments) {
+    // the part of tensor i that lies in this rank's shard
+    const long long lo = ps[i].offset > s_lo ? ps[i].offset : s_lo;
+    const long long t_hi = ps[i].offset + ps[i].numel;
+    const long long hi = t_hi < s_hi ? t_hi : s_hi;
+    if (hi <= lo) continue;
+    OuterArgs a{};
+    for (int w = 0; w < b->world; ++w) a.deltas[a.ncontrib++] = b->peer_delta[w] + lo;
+    a.vel = b->velocity + (lo - s_lo); a.master = b->ws.theta0 + lo;
+    for (int w = 0; w < b->world; ++w)
+      if (w != b->rank) a.outs[a.nouts++] = b->peer_theta0[w] + lo;
+    a.n = hi - lo; a.lr = b->stream_lr; a.mu = b->stream_mu; a.trunc = 0; a.keep_nonfinite = 1;
+    KL(b, 1, launch_nesterov_shard(b->stream, a));
+  }
+  CK(b, cudaEventRecord(b->ev1, b->stream));
+  CK(b, cudaStreamSynchronize(b->stream));
+  if (device_ms) { float ms = 0.f; CK(b, cudaEventElapsedTime(&ms, b->ev0, b->ev1)); *device_ms = ms; }
+  return PCPB_OK;
+}
+
+int pcpb_stream_merge(pcpb_backend* b, int fragment) {
+  int r = stream_check(b, fragment);
+  if (r) return r;
+  DeviceGuard g(b->device);
+  Workspace& w = b->ws;
+  const ModelConfig& c = b->cfg;
+  for (size_t i = (size_t)fragment; i < c.params.size(); i += (size_t)b->stream_fragments) {
+    const size_t off = (size_t)c.params[i].offset, n = (size_t)c.params[i].numel;
+    KL(b, 1, launch_stream_merge(b->stream, w.theta + off, w.theta0 + off, b->snapshot + off, b->stream_alpha, n));
+    if (c.dtype != DT_F32)
+      KL(b, 1, launch_convert_f32(b->stream, c.dtype, w.theta + off, (char*)w.shadow + off * dtype_size(c.dtype), n));
+  }
   return PCPB_OK;
 }
 

@@ -99,6 +99,10 @@ struct pcpb_backend {
   float *master_shard = nullptr, *velocity = nullptr;
   long long shard_len = 0;
   bool velocity_init = false;
+  // streaming DiLoCo
+  float* snapshot = nullptr;                 // last synchronised value of every parameter (f32, flat)
+  int stream_fragments = 0;
+  float stream_alpha = 0.5f, stream_lr = 0.7f, stream_mu = 0.9f;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr, tm0 = nullptr, tm1 = nullptr;
   // tensor-core GEMM profiling
   bool profiling = false;

@@ -72,3 +72,76 @@ class DilocoGroup:
         ms = self.be.outer_apply(self.lr, self.mu, self.dt, contributors)
         self.tr.barrier()
         return self.tr.all_reduce_mean(final_loss), ms
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Streaming DiLoCo: the worker's step schedule (src/nodes/workers/worker.zig:2207-2240, 2367-2383)
+# ---------------------------------------------------------------------------------------------------------
+def fragment_phase_start(fragment: int, inner_steps: int, num_fragments: int) -> int:
+    """floor(p * H / P): the step offset of fragment p's cycle."""
+    return (fragment * inner_steps) // num_fragments
+
+
+def streaming_max_steps(num_fragments: int, inner_steps: int, overlap_tau: int, max_rounds: int) -> int:
+    """Steps of the loop: max_rounds * H plus the time for the last fragment's last merge (worker.zig:2202-2203)."""
+    return max_rounds * inner_steps + fragment_phase_start(num_fragments - 1, inner_steps, num_fragments) + overlap_tau
+
+
+def streaming_schedule(t: int, num_fragments: int, inner_steps: int, overlap_tau: int, max_rounds: int):
+    """(fragments to merge before step t, fragments to send after step t), t counted from 1, each entry a
+    (fragment, fragment_round) pair."""
+    recv, send = [], []
+    for p in range(num_fragments):
+        tp = fragment_phase_start(p, inner_steps, num_fragments)
+        if t > tp + overlap_tau and (t - tp - overlap_tau) % inner_steps == 0:
+            r = (t - tp - overlap_tau) // inner_steps - 1
+            if r < max_rounds:
+                recv.append((p, r))
+        if t > tp and (t - tp) % inner_steps == 0:
+            r = (t - tp) // inner_steps - 1
+            if r < max_rounds:
+                send.append((p, r))
+    return recv, send
+
+
+class StreamingGroup:
+    """One rank's view of a streaming-DiLoCo run.  `backend` needs worker_step / stream_begin / stream_send /
+    stream_outer / stream_merge and the outer-step attachment (pcp_b200.Backend, or a stand-in in tests).
+
+    A fragment's outer step runs right after it is sent (every rank sends, barrier, every rank updates its shard of
+    the fragment and writes it into all replicas of the master, barrier); the merge into the working parameters
+    happens overlap_tau steps later, as in the reference, where that time hides the network round trip."""
+
+    def __init__(self, backend, transport, num_fragments=4, inner_steps=50, overlap_tau=1, alpha=0.5,
+                 learning_rate=0.7, momentum=0.9, max_rounds=1):
+        if overlap_tau < 1:
+            raise ValueError("overlap_tau must be at least 1: a fragment cannot be merged in the step it was sent")
+        self.be, self.tr = backend, transport
+        self.P, self.H, self.tau, self.alpha = num_fragments, inner_steps, overlap_tau, alpha
+        self.lr, self.mu, self.max_rounds = learning_rate, momentum, max_rounds
+        self.t = 0
+        self.outer_ms = 0.0
+
+    @property
+    def max_steps(self) -> int:
+        return streaming_max_steps(self.P, self.H, self.tau, self.max_rounds)
+
+    def begin(self):
+        """After the backend's round has been opened (worker_begin_round with tau = max_steps)."""
+        self.be.stream_begin(self.P, self.alpha, self.lr, self.mu)
+        self.tr.barrier()
+        self.t = 0
+
+    def step(self):
+        """Merges due, one training step, sends (+ their outer steps) due.  Returns (merged, sent) fragment lists."""
+        self.t += 1
+        recv, send = streaming_schedule(self.t, self.P, self.H, self.tau, self.max_rounds)
+        for p, _ in recv:
+            self.be.stream_merge(p)
+        self.be.worker_step()
+        for p, _ in send:
+            self.be.stream_send(p)
+            self.tr.barrier()
+            self.outer_ms += self.be.stream_outer(p)
+            self.tr.barrier()
+        return [p for p, _ in recv], [p for p, _ in send]

@@ -276,6 +276,55 @@ def test_diloco_bf16_3_workers():
     _run_diloco(SMALL_BF16, workers=3, tau=4, rounds=2, lr=1e-3, tol_loss=2e-2, tol_param=2e-2, zipf=True)
 
 
+@pytest.mark.parametrize("cfgd,P,H,tau", [(SMALL_F32, 4, 4, 1), (GPT_ODD_F32, 3, 5, 2)])
+def test_streaming_diloco_matches_oracle(cfgd, P, H, tau):
+    """Streaming DiLoCo (fragment i % P, send every H steps at offset floor(pH/P), merge tau steps later with
+    alpha = 0.5): two workers, two rounds per fragment, against the restated worker / Shepherd loop.  Per-step
+    losses, final worker parameters and the master within 1e-4."""
+    from oracle.worker import streaming_loop
+    from pcp_b200.diloco import streaming_max_steps, streaming_schedule
+    cfg, text = make_model(cfgd)
+    mod = TrainingModule(text)
+    workers, rounds, alpha = 2, 2, 0.5
+    steps = streaming_max_steps(P, H, tau, rounds)
+    master = seeded_params(cfg, seed=3, std=0.02)
+    toks = [tokens_for(cfg, steps, seed=50 + w) for w in range(workers)]
+    conf = AdamConf(learning_rate=3e-4)
+    ref_params, ref_master, _, ref_losses = streaming_loop(mod, master, [FifoU16(t) for t in toks], P, H, tau, alpha, rounds,
+                                                           cfg.batch, cfg.seq_len, conf, NesterovConf(0.7, 0.9))
+    bes = [Backend(0) for _ in range(workers)]
+    try:
+        for b in bes:
+            b.load_session(text)
+            b.set_adam(conf.learning_rate, conf.beta1, conf.beta2, conf.epsilon, conf.weight_decay, conf.max_grad_norm)
+        for w, b in enumerate(bes):
+            b.outer_attach_local(w, bes)
+        for w, b in enumerate(bes):
+            b.worker_begin_round(steps, flat(master), param_dtype=F32)
+            b.worker_set_tokens(toks[w])
+            b.stream_begin(P, alpha, 0.7, 0.9)
+        losses = [[] for _ in bes]
+        for t in range(1, steps + 1):
+            recv, send = streaming_schedule(t, P, H, tau, rounds)
+            for w, b in enumerate(bes):
+                for p, _ in recv:
+                    b.stream_merge(p)
+                b.worker_step()
+                losses[w].append(b.worker_last_loss())
+            for p, _ in send:
+                for b in bes:
+                    b.stream_send(p)
+                for b in bes:
+                    b.stream_outer(p)
+        for w, b in enumerate(bes):
+            np.testing.assert_allclose(losses[w], ref_losses[w], rtol=1e-4)
+            _close(b.worker_read_state("params"), flat(ref_params[w]), 1e-4, "f32")
+            _close(b.worker_read_state("master"), flat(ref_master), 1e-4, "f32")
+    finally:
+        for b in bes:
+            b.close()
+
+
 def test_outer_step_bit_exact_given_deltas():
     """With the deltas taken from the device itself the outer arithmetic (sum in worker order, / n, NaN -> 0,
     Nesterov, bf16 truncation) is bit-identical to the restated reference."""
