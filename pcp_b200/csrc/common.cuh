@@ -110,6 +110,39 @@ template <> __device__ __forceinline__ float m_exp<bf16>(float x) { return __exp
 // Guard constant the reference adds to every divide / log denominator in the forward graph
 // (src/compiler/sanitizer.zig:8-111) and again inside the divide / log / rsqrt VJP rules
 // (src/autodiff/vjp_rules.zig:198,1510,1543).
+// ---- bf16 pairs in one 32-bit word (low half = first element) ------------------------------------------
+// add / mul / max on pairs are single bf16 operations: exact result rounded once to nearest even, which is what
+// an op of the exported bf16 graphs computes.
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+// Two bf16 products at once: each lane of d = bf16(a * b), round to nearest even.
+__device__ __forceinline__ uint32_t bmul2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t badd2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t bmax2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+
 #define PCPB_GUARD 1e-4f
 
 }  // namespace pcpb

@@ -353,6 +353,21 @@ struct Plan {
 
 int g_sm_count = 0;
 
+// Split-K factor of a weight-gradient GEMM with few output tiles: the one (1..8, at least 8 k-blocks per split) whose
+// tiles x splits work items fill whole rounds of 148 CTAs best; each extra split costs a little for its f32 slab.
+int pick_splits(int tiles, int kblocks) {
+  if (tiles >= 2 * 148) return 1;
+  int best = 1;
+  double best_score = -1.0;
+  for (int s = 1; s <= 8; ++s) {
+    if (s > 1 && kblocks / s < 8) break;
+    const int items = tiles * s, rounds = (items + 147) / 148;
+    const double score = (double)items / (rounds * 148.0) - 0.01 * s;
+    if (score > best_score) { best_score = score; best = s; }
+  }
+  return best;
+}
+
 Plan plan_for(const GemmArgs& g) {
   Plan pl;
   if (g.M <= 0 || g.N <= 0 || g.K <= 0) return pl;
@@ -371,13 +386,7 @@ Plan plan_for(const GemmArgs& g) {
   if (g.epi < EPI_STORE || g.epi > EPI_BIAS) return pl;
   pl.bn = (g.N % 256 == 0) ? 256 : 128;
   const int tiles = (g.M / BM) * (g.N / pl.bn), kblocks = g.K / BK;
-  pl.splits = 1;
-  if (g.epi == EPI_WGRAD && tiles < 2 * 148) {
-    int s = (2 * 148 + tiles - 1) / tiles;
-    if (s > 8) s = 8;
-    while (s > 1 && kblocks / s < 8) --s;
-    pl.splits = s;
-  }
+  pl.splits = (g.epi == EPI_WGRAD) ? pick_splits(tiles, kblocks) : 1;
   // the f32 slabs must fit the caller's scratch
   while (pl.splits > 1 && (size_t)pl.splits * g.M * g.N * sizeof(float) > g.scratch_bytes) --pl.splits;
   pl.kb_per_split = (kblocks + pl.splits - 1) / pl.splits;
@@ -410,10 +419,7 @@ size_t gemm_tc_scratch_wanted(int M, int N, int K) {
   if (M % BM || N % 128 || K % BK) return 0;
   const int bn = (N % 256 == 0) ? 256 : 128;
   const int tiles = (M / BM) * (N / bn), kblocks = K / BK;
-  if (tiles >= 2 * 148) return 0;
-  int s = (2 * 148 + tiles - 1) / tiles;
-  if (s > 8) s = 8;
-  while (s > 1 && kblocks / s < 8) --s;
+  const int s = pick_splits(tiles, kblocks);
   return s > 1 ? (size_t)s * M * N * sizeof(float) : 0;
 }
 

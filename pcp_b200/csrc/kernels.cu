@@ -475,6 +475,98 @@ __global__ void __launch_bounds__(256) k_rope_qknorm_bwd_vec(const T* __restrict
   st8<T>(dst + half, o2);
 }
 
+// ---- bf16 RoPE + QK-norm on bf16 pairs: the same op sequence as the templates above (each mul / add of the graph
+// is one mul.bf16x2 / add.bf16x2), a third of their instruction count.  Eight rotation pairs per thread.
+__global__ void __launch_bounds__(256) k_rope_qknorm_fwd_bf16x2(const bf16* __restrict__ qkv, const uint16_t* __restrict__ cosT,
+                                                                const uint16_t* __restrict__ sinT, int M, int Tlen, int H,
+                                                                int Hkv, int hd, bf16* __restrict__ qkn, float* __restrict__ tq) {
+  const int heads = H + Hkv, half = hd >> 1, tph = half >> 3;
+  const long long gt = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long slot = gt / tph;
+  const int sub = (int)(gt % tph);
+  const bool live = slot < (long long)M * heads;
+  const int m = live ? (int)(slot / heads) : 0, h = live ? (int)(slot % heads) : 0;
+  const bf16* src = qkv + (size_t)m * ((H + 2 * Hkv) * hd) + (size_t)h * hd + sub * 8;
+  const int pos = m % Tlen;
+  const uint4 X1 = *reinterpret_cast<const uint4*>(src), X2 = *reinterpret_cast<const uint4*>(src + half);
+  const uint4 Cw = *reinterpret_cast<const uint4*>(cosT + (size_t)pos * half + sub * 8);
+  const uint4 Sw = *reinterpret_cast<const uint4*>(sinT + (size_t)pos * half + sub * 8);
+  const uint32_t x1[4] = {X1.x, X1.y, X1.z, X1.w}, x2[4] = {X2.x, X2.y, X2.z, X2.w};
+  const uint32_t c[4] = {Cw.x, Cw.y, Cw.z, Cw.w}, sn[4] = {Sw.x, Sw.y, Sw.z, Sw.w};
+  uint32_t y1[4], y2[4];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    y1[i] = badd2(bmul2(x1[i], c[i]), bmul2(x2[i], sn[i]));
+    y2[i] = badd2(bmul2(x1[i], sn[i] ^ 0x80008000u), bmul2(x2[i], c[i]));
+    const float a0 = bf_lo(y1[i]), b0 = bf_lo(y2[i]), a1 = bf_hi(y1[i]), b1 = bf_hi(y2[i]);
+    ss += a0 * a0 + b0 * b0;
+    ss += a1 * a1 + b1 * b1;
+  }
+  ss = group_sum(ss, tph);
+  const float t = ss / ((float)hd + PCPB_GUARD) + 1e-5f;
+  const uint32_t r2 = pack2(rsqrtf(t), rsqrtf(t));
+  if (!live) return;
+  if (sub == 0) tq[(size_t)m * heads + h] = t;
+  bf16* dst = qkn + (size_t)m * (heads * hd) + (size_t)h * hd + sub * 8;
+  *reinterpret_cast<uint4*>(dst) = make_uint4(bmul2(y1[0], r2), bmul2(y1[1], r2), bmul2(y1[2], r2), bmul2(y1[3], r2));
+  *reinterpret_cast<uint4*>(dst + half) = make_uint4(bmul2(y2[0], r2), bmul2(y2[1], r2), bmul2(y2[2], r2), bmul2(y2[3], r2));
+}
+
+__global__ void __launch_bounds__(256) k_rope_qknorm_bwd_bf16x2(const bf16* __restrict__ qkv, const bf16* __restrict__ dqkn,
+                                                                const float* __restrict__ tq, const uint16_t* __restrict__ cosT,
+                                                                const uint16_t* __restrict__ sinT, int M, int Tlen, int H, int Hkv,
+                                                                int hd, bf16* __restrict__ dqkv) {
+  const int heads = H + Hkv, half = hd >> 1, tph = half >> 3;
+  const long long gt = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long slot = gt / tph;
+  const int sub = (int)(gt % tph);
+  const bool live = slot < (long long)M * heads;
+  const int m = live ? (int)(slot / heads) : 0, h = live ? (int)(slot % heads) : 0;
+  const size_t wqkv = (size_t)(H + 2 * Hkv) * hd;
+  const bf16* src = qkv + (size_t)m * wqkv + (size_t)h * hd + sub * 8;
+  const bf16* dyp = dqkn + (size_t)m * (heads * hd) + (size_t)h * hd + sub * 8;
+  const int pos = m % Tlen;
+  const uint4 X1 = *reinterpret_cast<const uint4*>(src), X2 = *reinterpret_cast<const uint4*>(src + half);
+  const uint4 Cw = *reinterpret_cast<const uint4*>(cosT + (size_t)pos * half + sub * 8);
+  const uint4 Sw = *reinterpret_cast<const uint4*>(sinT + (size_t)pos * half + sub * 8);
+  const uint4 D1 = *reinterpret_cast<const uint4*>(dyp), D2 = *reinterpret_cast<const uint4*>(dyp + half);
+  const uint32_t x1[4] = {X1.x, X1.y, X1.z, X1.w}, x2[4] = {X2.x, X2.y, X2.z, X2.w};
+  const uint32_t c[4] = {Cw.x, Cw.y, Cw.z, Cw.w}, sn[4] = {Sw.x, Sw.y, Sw.z, Sw.w};
+  const uint32_t d1[4] = {D1.x, D1.y, D1.z, D1.w}, d2[4] = {D2.x, D2.y, D2.z, D2.w};
+  uint32_t y1[4], y2[4];
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    y1[i] = badd2(bmul2(x1[i], c[i]), bmul2(x2[i], sn[i]));
+    y2[i] = badd2(bmul2(x1[i], sn[i] ^ 0x80008000u), bmul2(x2[i], c[i]));
+    const uint32_t p1 = bmul2(d1[i], y1[i]), p2 = bmul2(d2[i], y2[i]);
+    acc += bf_lo(p1) + bf_lo(p2);
+    acc += bf_hi(p1) + bf_hi(p2);
+  }
+  acc = group_sum(acc, tph);
+  const float t = tq[(size_t)m * heads + h];
+  const float dr = rnd<bf16>(acc);
+  const float rp = rsqrtf(t + PCPB_GUARD);
+  const float ds = ((dr * -0.5f) * ((rp * rp) * rp)) / (((float)hd + PCPB_GUARD) + PCPB_GUARD);
+  const uint32_t r2 = pack2(rsqrtf(t), rsqrtf(t));
+  if (!live) return;
+  uint32_t o1[4], o2[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    // gradient wrt the roped value: bf16(bf16(d * r) + bf16(ds * (2 * y))), ds in f32
+    const uint32_t t1 = pack2(ds * (2.f * bf_lo(y1[i])), ds * (2.f * bf_hi(y1[i])));
+    const uint32_t t2 = pack2(ds * (2.f * bf_lo(y2[i])), ds * (2.f * bf_hi(y2[i])));
+    const uint32_t g1 = badd2(bmul2(d1[i], r2), t1), g2 = badd2(bmul2(d2[i], r2), t2);
+    // y1 = x1*c + x2*s ; y2 = x1*(-s) + x2*c
+    o1[i] = badd2(bmul2(g1, c[i]), bmul2(g2, sn[i] ^ 0x80008000u));
+    o2[i] = badd2(bmul2(g1, sn[i]), bmul2(g2, c[i]));
+  }
+  bf16* dst = dqkv + (size_t)m * wqkv + (size_t)h * hd + sub * 8;
+  *reinterpret_cast<uint4*>(dst) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+  *reinterpret_cast<uint4*>(dst + half) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+}
+
 static inline bool rope_vec_ok(int hd, const void* a, const void* b, const void* c, const void* d) {
   const int tph = hd / 16;
   return hd % 16 == 0 && tph >= 1 && tph <= 32 && (tph & (tph - 1)) == 0 &&
@@ -487,6 +579,10 @@ cudaError_t launch_rope_qknorm_fwd(cudaStream_t st, int dt, const void* qkv, con
   if (warps == 0) return cudaSuccess;
   if (rope_vec_ok(hd, qkv, qkn, c, s)) {
     const long long threads = warps * (hd / 16);
+    if (dt == DT_BF16) {
+      k_rope_qknorm_fwd_bf16x2<<<cdiv(threads, 256), 256, 0, st>>>((const bf16*)qkv, c, s, M, Tlen, H, Hkv, hd, (bf16*)qkn, tq);
+      return cudaGetLastError();
+    }
     DISPATCH_DT(dt, (k_rope_qknorm_fwd_vec<T><<<cdiv(threads, 256), 256, 0, st>>>((const T*)qkv, c, s, M, Tlen, H, Hkv, hd,
                                                                                   (T*)qkn, tq)));
     return cudaGetLastError();
@@ -502,6 +598,11 @@ cudaError_t launch_rope_qknorm_bwd(cudaStream_t st, int dt, const void* qkv, con
   if (warps == 0) return cudaSuccess;
   if (rope_vec_ok(hd, qkv, dqkn, dqkv, c) && (((uintptr_t)s) & 15) == 0) {
     const long long threads = warps * (hd / 16);
+    if (dt == DT_BF16) {
+      k_rope_qknorm_bwd_bf16x2<<<cdiv(threads, 256), 256, 0, st>>>((const bf16*)qkv, (const bf16*)dqkn, tq, c, s, M, Tlen, H, Hkv,
+                                                                   hd, (bf16*)dqkv);
+      return cudaGetLastError();
+    }
     DISPATCH_DT(dt, (k_rope_qknorm_bwd_vec<T><<<cdiv(threads, 256), 256, 0, st>>>((const T*)qkv, (const T*)dqkn, tq, c, s, M,
                                                                                   Tlen, H, Hkv, hd, (T*)dqkv)));
     return cudaGetLastError();
