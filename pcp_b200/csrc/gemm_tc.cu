@@ -24,6 +24,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "gemm_tc.h"
 #include "tc_common.cuh"
@@ -328,6 +329,186 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUt
   }
 }
 
+// =====================================================================================================
+// Two-CTA variant: a cluster of two CTAs (one SM each) computes a 256 x 256 tile with tcgen05.mma.cta_group::2.
+// CTA r of the pair holds rows [128r, 128r+128) of the A tile, rows [128r, 128r+128) of the B tile (its half of
+// the N columns) and the accumulators of its 128 output rows, so every operand byte is loaded once per pair and
+// each SM reads half as much shared memory per FLOP as in the one-CTA kernel.
+//   warp 0 (both CTAs)   TMA producer for its own halves; the bytes of both CTAs are counted on CTA 0's full barrier
+//   warp 1, CTA 0        waits for a full stage, issues the MMAs for the pair; the commit arrives on the empty /
+//                        accumulator-full barriers of both CTAs
+//   warps 2..9 (both)    epilogue of the CTA's 128 rows; release the accumulator on CTA 0's barrier
+// =====================================================================================================
+constexpr int NSTAGE2 = 6;
+constexpr int STAGE2_BYTES = 2 * A_TILE_BYTES;                  // A half + B half: 32 KB
+constexpr int SMEM2_BYTES = NSTAGE2 * STAGE2_BYTES + 1024 + 256;
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+k_gemm_tc2(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const TcParams p) {
+  constexpr int BN = 256, NSTAGE = NSTAGE2;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = base + NSTAGE * STAGE2_BYTES;
+  // barriers (8 B each): full[NSTAGE] (used in CTA 0), empty[NSTAGE], tmem_full[2], tmem_empty[2] (CTA 0), tmem address
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (2 * NSTAGE + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (3 * NSTAGE + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (3 * NSTAGE + 2 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (3 * NSTAGE + 4);
+  uint8_t* smem_gen = smem_raw + (base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + NSTAGE * STAGE2_BYTES + 8 * (3 * NSTAGE + 4));
+
+  const int warp = uniform_warp_idx(), lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();                      // 0 = leader
+  const int n_clusters = gridDim.x >> 1, cluster_id = blockIdx.x >> 1;
+  const int total_items = p.tiles_m * p.tiles_n * p.splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NSTAGE; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 2 * N_EPI); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  cluster_sync_all();                                           // barriers of both CTAs initialised, tensor memory allocated
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_gen;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (own halves) ------------------------------
+    uint32_t it = 0;
+    bool ok = true;
+    const uint32_t full0 = map_to_cta(full_bar(0), 0);          // CTA 0's full barriers, cluster address
+    for (int item = cluster_id; item < total_items && ok; item += n_clusters) {
+      const int tile = item / p.splits, split = item % p.splits;
+      int tm, tn;
+      tile_coords(p, tile, &tm, &tn);
+      const int m0 = tm * 256 + (int)rank * 128, n0 = tn * BN + (int)rank * 128;
+      const int kb0 = split * p.kb_per_split;
+      const int kb1 = min(kb0 + p.kb_per_split, p.K / BK);
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % NSTAGE;
+        const uint32_t ph = (it / NSTAGE) & 1u;
+        if (!(ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ph ^ 1u, p.err, 1)))) break;
+        // CTA 0 arms its barrier with the bytes of both CTAs; CTA 1's copies count on it as well (its own stage is
+        // free: the commit that freed it came after CTA 0's barrier had completed the previous use of this stage)
+        if (rank == 0) mbar_expect_tx_elect(full_bar(s), 2 * STAGE2_BYTES);
+        const uint32_t fb = full0 + 8u * s;
+        const uint32_t sa = base + s * STAGE2_BYTES, sb = sa + A_TILE_BYTES;
+        const int k0 = kb * BK;
+        if (!A_MN) tma_load_2d_pair_elect(sa, &tma_a, fb, k0, m0);
+        else {
+          tma_load_2d_pair_elect(sa, &tma_a, fb, m0, k0);
+          tma_load_2d_pair_elect(sa + 8192, &tma_a, fb, m0 + 64, k0);
+        }
+        if (!B_MN) tma_load_2d_pair_elect(sb, &tma_b, fb, k0, n0);
+        else {
+          tma_load_2d_pair_elect(sb, &tma_b, fb, n0, k0);
+          tma_load_2d_pair_elect(sb + 8192, &tma_b, fb, n0 + 64, k0);
+        }
+      }
+    }
+    if (!ok && rank == 0) {
+      // error path: let the copies already issued (by both CTAs) land before the pair goes away (bounded)
+      for (uint32_t j = (it > (uint32_t)NSTAGE ? it - NSTAGE : 0u); j < it; ++j) {
+        const uint32_t ph = (j / NSTAGE) & 1u;
+        for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(full_bar(j % NSTAGE), ph)) break;
+      }
+    }
+  } else if (warp == 1) {
+    uint32_t it = 0;
+    int local = 0;
+    bool ok = true;
+    if (rank != 0) {
+      // CTA 1 has no MMA work: CTA 0 issues for the pair
+    } else {
+      // ------------------------------ CTA 0: MMA issuer for the pair ------------------------------
+      constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) |
+                                 ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+      constexpr uint32_t A_LBO = A_MN ? 8192u : 16u, B_LBO = B_MN ? 8192u : 16u;
+      constexpr uint32_t A_KSTEP = A_MN ? 2048u : 32u, B_KSTEP = B_MN ? 2048u : 32u;
+      for (int item = cluster_id; item < total_items && ok; item += n_clusters, ++local) {
+        const int split = item % p.splits;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, p.K / BK);
+        const int acc = local & 1;
+        const uint32_t aph = ((uint32_t)local >> 1) & 1u;
+        if (!(ok = __all_sync(0xffffffffu, mbar_wait_cluster(tempty_bar(acc), aph ^ 1u, p.err, 2)))) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % NSTAGE;
+          const uint32_t ph = (it / NSTAGE) & 1u;
+          if (!(ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, p.err, 3)))) break;
+          tc_fence_after();
+          const uint32_t sa = base + s * STAGE2_BYTES, sb = sa + A_TILE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = make_desc(sa + k * A_KSTEP, A_LBO, 1024u);
+            const uint64_t db = make_desc(sb + k * B_KSTEP, B_LBO, 1024u);
+            mma2_bf16_elect(tmem_d, da, db, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          mma2_commit_multicast_elect(empty_bar(s), 3);         // frees the stage in both CTAs
+        }
+        if (ok) mma2_commit_multicast_elect(tfull_bar(acc), 3); // accumulators of both CTAs complete
+      }
+    }
+  } else {
+    // ------------------------------ epilogue of this CTA's 128 rows ------------------------------
+    constexpr int NCH = BN / 64;
+    const int q = warp & 3, half = (warp - 2) >> 2;
+    const bool reads_r = (p.splits == 1) && (p.epi == EPI_RESID || p.epi == EPI_DRELU2 || p.epi == EPI_DRELU);
+    const uint32_t tempty_leader = map_to_cta(tempty_bar(0), 0);  // tempty_bar(a) of CTA 0 = this + 8a
+    int local = 0;
+    bool ok = true;
+    for (int item = cluster_id; item < total_items && ok; item += n_clusters, ++local) {
+      const int tile = item / p.splits, split = item % p.splits;
+      int tm, tn;
+      tile_coords(p, tile, &tm, &tn);
+      const int m0 = tm * 256 + (int)rank * 128, n0 = tn * BN + half * (BN / 2);
+      const int acc = local & 1;
+      const uint32_t aph = ((uint32_t)local >> 1) & 1u;
+      const int row = m0 + q * 32 + lane;
+      uint4 rpre[NCH * 4];
+      if (reads_r) {
+        const uint4* rp = reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.R + (size_t)row * p.ldc + n0);
+        if (p.wide) {
+#pragma unroll
+          for (int i = 0; i < NCH * 2; ++i) ld_global_256(rp + 2 * i, rpre[2 * i], rpre[2 * i + 1]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < NCH * 4; ++i) rpre[i] = __ldg(rp + i);
+        }
+      }
+      ok = mbar_wait(tfull_bar(acc), aph, p.err, 4);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      TcParams pe = p;
+      if (p.splits > 1) { pe.epi = -1; pe.slab = p.slab + (size_t)split * p.M * p.N; pe.ldc = p.N; }
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * (BN / 2) + c * 32), r);
+        epilogue_chunk(pe, row, n0 + c * 32, r, rpre + c * 4);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_leader + 8u * acc);
+    }
+  }
+  tc_fence_before();
+  cluster_sync_all();                                           // nobody may still be signalling this CTA's barriers
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
 // Sum of the split-K slabs in split order, then the weight-gradient epilogue.
 __global__ void k_splitk_reduce(const float* __restrict__ slab, int splits, size_t mn, int N, float* __restrict__ C,
                                 long long ldc, int epi, float clip) {
@@ -346,6 +527,7 @@ __global__ void k_splitk_reduce(const float* __restrict__ slab, int splits, size
 
 struct Plan {
   bool ok = false;
+  bool pair = false;            // two-CTA kernel (256 x 256 tiles)
   bool a_mn = false, b_mn = false;
   long long lda = 0, ldb = 0;
   int bn = 0, splits = 1, kb_per_split = 0;
@@ -355,14 +537,21 @@ int g_sm_count = 0;
 
 // Split-K factor of a weight-gradient GEMM with few output tiles: the one (1..8, at least 8 k-blocks per split) whose
 // tiles x splits work items fill whole rounds of 148 CTAs best; each extra split costs a little for its f32 slab.
-int pick_splits(int tiles, int kblocks) {
-  if (tiles >= 2 * 148) return 1;
+// PCPB_GEMM_PAIR=0 keeps every GEMM on the one-CTA kernel.
+bool pair_enabled() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("PCPB_GEMM_PAIR"); v = (e && e[0] == '0') ? 0 : 1; }
+  return v == 1;
+}
+
+int pick_splits(int tiles, int kblocks, int slots = 148) {
+  if (tiles >= 2 * slots) return 1;
   int best = 1;
   double best_score = -1.0;
   for (int s = 1; s <= 8; ++s) {
     if (s > 1 && kblocks / s < 8) break;
-    const int items = tiles * s, rounds = (items + 147) / 148;
-    const double score = (double)items / (rounds * 148.0) - 0.01 * s;
+    const int items = tiles * s, rounds = (items + slots - 1) / slots;
+    const double score = (double)items / ((double)rounds * slots) - 0.01 * s;
     if (score > best_score) { best_score = score; best = s; }
   }
   return best;
@@ -385,8 +574,9 @@ Plan plan_for(const GemmArgs& g) {
   if (g.C2 && ((uintptr_t)g.C2 & 15)) return pl;
   if (g.epi < EPI_STORE || g.epi > EPI_BIAS) return pl;
   pl.bn = (g.N % 256 == 0) ? 256 : 128;
-  const int tiles = (g.M / BM) * (g.N / pl.bn), kblocks = g.K / BK;
-  pl.splits = (g.epi == EPI_WGRAD) ? pick_splits(tiles, kblocks) : 1;
+  pl.pair = pair_enabled() && g.M % 256 == 0 && g.N % 256 == 0;
+  const int tiles = (g.M / (pl.pair ? 256 : BM)) * (g.N / pl.bn), kblocks = g.K / BK;
+  pl.splits = (g.epi == EPI_WGRAD) ? pick_splits(tiles, kblocks, pl.pair ? 74 : 148) : 1;
   // the f32 slabs must fit the caller's scratch
   while (pl.splits > 1 && (size_t)pl.splits * g.M * g.N * sizeof(float) > g.scratch_bytes) --pl.splits;
   pl.kb_per_split = (kblocks + pl.splits - 1) / pl.splits;
@@ -410,6 +600,35 @@ cudaError_t launch_variant(cudaStream_t st, const CUtensorMap& ma, const CUtenso
   return cudaGetLastError();
 }
 
+template <bool A_MN, bool B_MN>
+cudaError_t launch_pair(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int items) {
+  auto kern = k_gemm_tc2<A_MN, B_MN>;
+  static bool attr_set[64] = {};
+  static int max_clusters[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(GEMM_THREADS); cfg.dynamicSmemBytes = SMEM2_BYTES; cfg.stream = st; cfg.attrs = at; cfg.numAttrs = 1;
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
+    if (e != cudaSuccess) return e;
+    cfg.gridDim = dim3(2 * 74);
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+    if (e != cudaSuccess) return e;
+    if (n < 1) return cudaErrorInvalidConfiguration;
+    max_clusters[dev] = n < 74 ? n : 74;
+    attr_set[dev] = true;
+  }
+  const int clusters = items < max_clusters[dev] ? items : max_clusters[dev];
+  cfg.gridDim = dim3(2 * clusters);
+  return cudaLaunchKernelEx(&cfg, kern, ma, mb, p);
+}
+
 }  // namespace
 
 bool gemm_tc_supported(const GemmArgs& g) { return g.err_word != nullptr && plan_for(g).ok && encode_fn() != nullptr; }
@@ -419,7 +638,8 @@ size_t gemm_tc_scratch_wanted(int M, int N, int K) {
   if (M % BM || N % 128 || K % BK) return 0;
   const int bn = (N % 256 == 0) ? 256 : 128;
   const int tiles = (M / BM) * (N / bn), kblocks = K / BK;
-  const int s = pick_splits(tiles, kblocks);
+  int s = pick_splits(tiles, kblocks);
+  if (M % 256 == 0 && N % 256 == 0) { const int s2 = pick_splits((M / 256) * (N / 256), kblocks, 74); if (s2 > s) s = s2; }
   return s > 1 ? (size_t)s * M * N * sizeof(float) : 0;
 }
 
@@ -439,12 +659,12 @@ cudaError_t launch_gemm_tc(cudaStream_t st, const GemmArgs& g) {
   bool ok;
   if (!pl.a_mn) ok = make_map(&ma, g.A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)pl.lda, BM);
   else ok = make_map(&ma, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)pl.lda, 64);
-  if (!pl.b_mn) ok = ok && make_map(&mb, g.B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)pl.ldb, (uint32_t)pl.bn);
+  if (!pl.b_mn) ok = ok && make_map(&mb, g.B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)pl.ldb, pl.pair ? 128u : (uint32_t)pl.bn);
   else ok = ok && make_map(&mb, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)pl.ldb, 64);
   if (!ok) return cudaErrorInvalidValue;
   TcParams p;
   p.M = g.M; p.N = g.N; p.K = g.K;
-  p.tiles_m = g.M / BM; p.tiles_n = g.N / pl.bn; p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
+  p.tiles_m = g.M / (pl.pair ? 256 : BM); p.tiles_n = g.N / pl.bn; p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
   p.group_m = (p.tiles_n >= 32 && p.splits == 1) ? 8 : 1;
   {
     // 256-bit epilogue accesses need every row segment to start on a 32-byte boundary (16 bf16 / 8 f32 elements)
@@ -455,7 +675,11 @@ cudaError_t launch_gemm_tc(cudaStream_t st, const GemmArgs& g) {
   if (pl.splits > 1) p.slab = (float*)g.scratch;
   const int items = p.tiles_m * p.tiles_n * p.splits;
   const int grid = items < g_sm_count ? items : g_sm_count;
-  if (pl.bn == 256) {
+  if (pl.pair) {
+    if (!pl.a_mn && !pl.b_mn) e = launch_pair<false, false>(st, ma, mb, p, items);
+    else if (!pl.a_mn && pl.b_mn) e = launch_pair<false, true>(st, ma, mb, p, items);
+    else e = launch_pair<true, true>(st, ma, mb, p, items);
+  } else if (pl.bn == 256) {
     if (!pl.a_mn && !pl.b_mn) e = launch_variant<256, false, false>(st, ma, mb, p, grid);
     else if (!pl.a_mn && pl.b_mn) e = launch_variant<256, false, true>(st, ma, mb, p, grid);
     else e = launch_variant<256, true, true>(st, ma, mb, p, grid);
