@@ -132,7 +132,10 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
 
   const int warp = uniform_warp_idx(), lane = threadIdx.x & 31;
   const int grp = p.H / p.Hkv;
-  long long tacc[12] = {};                                   // wait cycles by role (instrumented builds only)
+  long long tacc[16] = {};
+#ifdef PCPB_ATC_TIMING
+  __shared__ long long ts_tcommit[2], ts_efull[2];           // clock at: T commit issued (per buffer), E published (per group)
+#endif                                   // wait cycles by role (instrumented builds only)
 #ifdef PCPB_ATC_TIMING
   const long long t_cta0 = clock64();
 #endif
@@ -235,26 +238,26 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       tc_fence_after();
       ATC_T0();
       const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
+      // Consecutive MMAs into one accumulator wait for each other (about 125 cycles each, whatever N is), so the two
+      // independent products of the backward kernels are issued alternately: one accumulator chain hides the other.
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         const uint32_t ao = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
         const uint32_t bo = (uint32_t)(ks >> 2) * 8192u + (uint32_t)(ks & 3) * 32u;
-        // A from tensor memory (forward, dQ): k-step ks = head dimensions 16ks .. 16ks+15 = 8 columns of bf16 pairs
-        if (MODE == MODE_DKV) mma_bf16_elect(t1_col(buf), make_desc(sRes + ao, 16, 1024), make_desc(c1 + bo, 16, 1024), ID_T, ks > 0);
-        else mma_bf16_ts_elect(t1_col(buf), qcol + 8u * ks, make_desc(c1 + bo, 16, 1024), ID_T, ks > 0);
-      }
-      if (MODE != MODE_FWD) {
-        // the second product after the first, not interleaved with it: one accumulator chain at a time
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t ao = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
-          const uint32_t bo = (uint32_t)(ks >> 2) * 8192u + (uint32_t)(ks & 3) * 32u;
-          if (MODE == MODE_DKV) mma_bf16_elect(t2_col(buf), make_desc(sRes + TILE_BYTES + ao, 16, 1024), make_desc(c2 + bo, 16, 1024), ID_T, ks > 0);
-          else mma_bf16_ts_elect(t2_col(buf), docol + 8u * ks, make_desc(c2 + bo, 16, 1024), ID_T, ks > 0);
+        if (MODE == MODE_DKV) {
+          mma_bf16_elect(t1_col(buf), make_desc(sRes + ao, 16, 1024), make_desc(c1 + bo, 16, 1024), ID_T, ks > 0);
+          mma_bf16_elect(t2_col(buf), make_desc(sRes + TILE_BYTES + ao, 16, 1024), make_desc(c2 + bo, 16, 1024), ID_T, ks > 0);
+        } else {
+          // A from tensor memory (forward, dQ): k-step ks = head dimensions 16ks .. 16ks+15 = 8 columns of bf16 pairs
+          mma_bf16_ts_elect(t1_col(buf), qcol + 8u * ks, make_desc(c1 + bo, 16, 1024), ID_T, ks > 0);
+          if (MODE == MODE_DQ) mma_bf16_ts_elect(t2_col(buf), docol + 8u * ks, make_desc(c2 + bo, 16, 1024), ID_T, ks > 0);
         }
       }
       if (release_stage) mma_commit_elect(empty_bar(s));
       mma_commit_elect(tfull_bar(buf));
+#ifdef PCPB_ATC_TIMING
+      if (lane == 0) ts_tcommit[buf] = clock64();
+#endif
       ATC_T1(10);
       return true;
     };
@@ -270,6 +273,9 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       const int eb = it & 1;
       const uint32_t eph = ((uint32_t)it >> 1) & 1u;
       if (!(ok = __all_sync(0xffffffffu, twait(15, efull_bar(eb), eph, p.err, tacc[4])))) break;
+#ifdef PCPB_ATC_TIMING
+      tacc[14] += clock64() - *(volatile long long*)&ts_efull[eb];     // E published -> MMA warp awake
+#endif
       tc_fence_after();
       ATC_T0();
       const int s = (g0 + it) % NST, buf = (g0 + it) & 1;
@@ -335,17 +341,19 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
         ok = __all_sync(0xffffffffu, twait(16, tfull_bar(buf), ((uint32_t)g >> 1) & 1u, p.err, tacc[5]));
         if (!ok) break;
         tc_fence_after();
+        // both passes' score columns are fetched at once (one exposed tensor-memory latency per sub-tile)
+        uint32_t rr[2][16];
+        tmem_ld16_issue(t1_col(buf) + lane_off + (uint32_t)(half * 32), rr[0]);
+        tmem_ld16_issue(t1_col(buf) + lane_off + (uint32_t)(half * 32 + 16), rr[1]);
+        tmem_ld_wait16(rr[0]); tmem_ld_wait16(rr[1]);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(buf));          // the values are in registers: release the buffer early
 #pragma unroll
         for (int pass = 0; pass < 2; ++pass) {
           const int ch = half * 32 + pass * 16, k0 = g * 64 + ch;
           const bool diag = (k0 + 15 > r0);
-          uint32_t r[16];
-          tmem_ld16(t1_col(buf) + lane_off + (uint32_t)ch, r);
-          if (pass == 1) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(buf));      // the values are in registers: release the buffer early
-          }
+          const uint32_t (&r)[16] = rr[pass];
           float sv[16], cm = -INFINITY;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
@@ -406,21 +414,37 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       }
       ok = __all_sync(0xffffffffu, twait(17, tfull_bar(buf), ((uint32_t)gg >> 1) & 1u, p.err, tacc[6]));
       if (!ok) break;
+#ifdef PCPB_ATC_TIMING
+      tacc[15] += clock64() - *(volatile long long*)&ts_tcommit[buf];  // T commit issued -> element-wise warp awake
+#endif
       tc_fence_after();
+      ATC_T0();
+      // Fetch the score (and dP) columns of both passes at once where the registers allow it (forward, dQ): one
+      // exposed tensor-memory latency per sub-tile instead of one per load.
+      constexpr bool BATCH = (MODE != MODE_DKV);
+      uint32_t q1[2][16], q2[2][16];
+      if (BATCH) {
+        tmem_ld16_issue(t1_col(buf) + lane_off + (uint32_t)(half * 32), q1[0]);
+        tmem_ld16_issue(t1_col(buf) + lane_off + (uint32_t)(half * 32 + 16), q1[1]);
+        if (MODE == MODE_DQ) {
+          tmem_ld16_issue(t2_col(buf) + lane_off + (uint32_t)(half * 32), q2[0]);
+          tmem_ld16_issue(t2_col(buf) + lane_off + (uint32_t)(half * 32 + 16), q2[1]);
+        }
+        tmem_ld_wait16(q1[0]); tmem_ld_wait16(q1[1]);
+        if (MODE == MODE_DQ) { tmem_ld_wait16(q2[0]); tmem_ld_wait16(q2[1]); }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(buf));
+      }
 #pragma unroll
       for (int pass = 0; pass < 2; ++pass) {
         const int ch = half * 32 + pass * 16, c0 = cbase + pass * 16;
         // does the causal boundary cross this block of 32 rows x 16 columns?
         const bool diag = (MODE == MODE_DKV) ? (c0 < r0 + 128) : (c0 + 15 > r0);
-        uint32_t r1[16];
-        tmem_ld16(t1_col(buf) + lane_off + (uint32_t)ch, r1);
+        uint32_t (&r1)[16] = q1[pass];
+        if (!BATCH) tmem_ld16(t1_col(buf) + lane_off + (uint32_t)ch, r1);
         uint32_t ew[8], pw[8];
         if (MODE == MODE_FWD) {
-          if (pass == 1) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(buf));
-          }
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const uint32_t s2 = bmul2(pack2(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1])), scale2);
@@ -432,12 +456,14 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
             ew[j] = pack2(e0, e1);
           }
         } else {
-          uint32_t r2[16];
-          tmem_ld16(t2_col(buf) + lane_off + (uint32_t)ch, r2);
-          if (pass == 1) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(buf));
+          uint32_t (&r2)[16] = q2[pass];
+          if (!BATCH) {
+            tmem_ld16(t2_col(buf) + lane_off + (uint32_t)ch, r2);
+            if (pass == 1) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(tempty_bar(buf));
+            }
           }
 #pragma unroll
           for (int j4 = 0; j4 < 4; ++j4) {
@@ -497,7 +523,11 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
+#ifdef PCPB_ATC_TIMING
+      if (lane == 0 && (warp == 2 || warp == 10)) ts_efull[buf] = clock64();
+#endif
       if (lane == 0) mbar_arrive(efull_bar(buf));
+      ATC_T1(12);
     }
     // ---- outputs: each warp stores 32 of the 128 output columns of its rows ----
     if (ok) ok = __all_sync(0xffffffffu, twait(19, out_bar, 0, p.err, tacc[8]));
@@ -522,7 +552,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
 #ifdef PCPB_ATC_TIMING
   if (lane == 0) {
 #pragma unroll
-    for (int c = 0; c < 12; ++c)
+    for (int c = 0; c < 16; ++c)
       if (tacc[c]) atomicAdd(&g_atc_t[MODE * 32 + 11 + c], (unsigned long long)tacc[c]);
   }
   if (threadIdx.x == 64) {
