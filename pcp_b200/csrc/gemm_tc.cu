@@ -544,6 +544,13 @@ bool pair_enabled() {
   return v == 1;
 }
 
+// Longest contraction the two-CTA kernel is used for (PCPB_GEMM_PAIR_MAXK overrides).
+int pair_max_k() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("PCPB_GEMM_PAIR_MAXK"); v = e ? atoi(e) : (1 << 30); if (v <= 0) v = 1 << 30; }
+  return v;
+}
+
 int pick_splits(int tiles, int kblocks, int slots = 148) {
   if (tiles >= 2 * slots) return 1;
   int best = 1;
@@ -574,7 +581,7 @@ Plan plan_for(const GemmArgs& g) {
   if (g.C2 && ((uintptr_t)g.C2 & 15)) return pl;
   if (g.epi < EPI_STORE || g.epi > EPI_BIAS) return pl;
   pl.bn = (g.N % 256 == 0) ? 256 : 128;
-  pl.pair = pair_enabled() && g.M % 256 == 0 && g.N % 256 == 0;
+  pl.pair = pair_enabled() && g.M % 256 == 0 && g.N % 256 == 0 && g.K <= pair_max_k();
   const int tiles = (g.M / (pl.pair ? 256 : BM)) * (g.N / pl.bn), kblocks = g.K / BK;
   pl.splits = (g.epi == EPI_WGRAD) ? pick_splits(tiles, kblocks, pl.pair ? 74 : 148) : 1;
   // the f32 slabs must fit the caller's scratch
