@@ -8,13 +8,18 @@
 //   dQ        rows = queries; per sub-tile of keys:  S = Q K^T, dP = dO V^T  ->  dS  ->  dQ += dS K
 //   dK, dV    rows = keys;    per sub-tile of queries: S^T = K Q^T, dP^T = V dO^T -> P^T, dS^T
 //                                                       -> dV += P^T dO, dK += dS^T Q
-// Warp roles (576 threads): warp 0 TMA producer (3-stage ring of sub-tile pairs), warp 1 MMA issuer and owner of the
-// tensor-memory allocation, warps 2-17 element-wise: each thread owns one row and 16 of the 64 score columns, reads them
-// with tcgen05.ld, does the softmax / softmax-backward arithmetic and writes the bf16 result into a 128-byte-swizzled
-// shared-memory tile that the next MMA consumes as its A operand.  Score tiles are double-buffered in tensor memory
-// so the MMAs of sub-tile i+1 overlap the arithmetic of sub-tile i.  The element-wise arithmetic is the bottleneck of
-// the kernel (about 8192 exponentials per sub-tile against 0.4 us of tensor work), so it works on bf16 pairs: one
-// cvt.rn.bf16x2 and one mul.bf16x2 reproduce the two roundings of a score, one more pair of them the rounding of dS.
+// Warp roles: warp 0 TMA producer (ring of sub-tile pairs), warp 1 MMA issuer and owner of the tensor-memory
+// allocation, then the element-wise warps: each thread owns one row and 16-column passes of the 64 score columns, reads
+// them with tcgen05.ld, does the softmax / softmax-backward arithmetic and writes the bf16 result over the score buffer
+// it came from (tcgen05.st), where the next MMA finds it as its A operand (TS form).  Score tiles are double-buffered
+// in tensor memory and two groups of element-wise warps take the sub-tiles in turn, so the MMAs of sub-tile i+1
+// overlap the arithmetic of sub-tile i.  The backward kernels use 16 element-wise warps and the whole SM (512
+// tensor-memory columns, Q and dO of the dQ kernel in tensor memory as well); the forward kernel uses 8, half of the
+// tensor memory and 100 KB of shared memory, and runs two CTAs per SM: four sub-tiles in flight per SM, and one
+// CTA's prologue / epilogue under the other's main loop.  What limits these kernels is the latency of the hand-offs
+// MMA -> element-wise -> MMA (commit, wake-up, tcgen05.ld / st), not the tensor pipe, hence the concurrency.
+// The element-wise arithmetic works on bf16 pairs: one cvt.rn.bf16x2 and one mul.bf16x2 reproduce the two roundings
+// of a score, one more pair of them the rounding of dS.
 //
 // A streamed [64 x 128] sub-tile serves two roles with the same bytes: "K-major" B operand of the score product
 // (contraction over head_dim) and "MN-major" B operand of the output product (contraction over its 64 rows).
@@ -32,7 +37,7 @@ namespace {
 
 constexpr int HD = 128;
 #ifndef PCPB_ATC_NST_FWD
-#define PCPB_ATC_NST_FWD 3
+#define PCPB_ATC_NST_FWD 2
 #endif
 #ifndef PCPB_ATC_NST_DQ
 #define PCPB_ATC_NST_DQ 3
@@ -41,8 +46,9 @@ constexpr int SUB_BYTES = 64 * HD * 2;         // one streamed sub-tile: 16 KB
 constexpr int STAGE_BYTES = 2 * SUB_BYTES;     // (C1, C2)
 constexpr int TILE_BYTES = 128 * HD * 2;       // one resident tile: 32 KB
 constexpr float LOG2E = 1.4426950408889634f;
-constexpr int N_EW = 16;                       // element-wise warps
-constexpr int N_THREADS = 64 + 32 * N_EW;
+// Element-wise warps per CTA: 16 (two groups of 8) in the backward kernels, which fill the SM alone; 8 (two groups of 4)
+// in the forward kernel, which needs half of the tensor memory and half of the shared memory and runs two CTAs per SM
+// so that four sub-tiles are in flight per SM and one CTA's prologue / epilogue overlaps the other's main loop.
 
 enum { MODE_FWD = 0, MODE_DQ = 1, MODE_DKV = 2 };
 
@@ -57,16 +63,23 @@ struct AtcParams {
 };
 
 template <int MODE> struct AtcCfg {
+  static constexpr int N_EW = (MODE == MODE_FWD) ? 8 : 16;
+  static constexpr int THREADS = 64 + 32 * N_EW;
+  static constexpr int CTAS_PER_SM = (MODE == MODE_FWD) ? 2 : 1;
+  static constexpr int NCG = N_EW / 4;                       // warps per tensor-memory lane quarter
+  static constexpr int PASSES = (NCG == 4) ? 2 : 4;          // 16-column passes of a thread over its share of a sub-tile
+  static constexpr uint32_t TMEM_COLS = (MODE == MODE_FWD) ? 256u : 512u;
   static constexpr int NST = (MODE == MODE_FWD) ? PCPB_ATC_NST_FWD : (MODE == MODE_DQ) ? PCPB_ATC_NST_DQ : 3;   // ring stages
-  // resident row-side tiles in shared memory: K and V of the dK/dV kernel (the other kernels keep theirs in tensor memory)
-  static constexpr int N_RES = (MODE == MODE_DKV) ? 2 : 0;
+  // resident row-side tiles in shared memory: K and V of the dK/dV kernel, Q of the forward kernel (the dQ kernel keeps
+  // Q and dO in tensor memory)
+  static constexpr int N_RES = (MODE == MODE_DKV) ? 2 : (MODE == MODE_FWD) ? 1 : 0;
   // DKV: per warp, double-buffered, six statistics of 32 columns; FWD: exchange of the four partial (max, sum) of a row
-  static constexpr int STAT_BYTES = (MODE == MODE_DKV) ? N_EW * 2 * 192 * 4 : (MODE == MODE_FWD) ? 4 * 128 * 2 * 4 : 16;
+  static constexpr int STAT_BYTES = (MODE == MODE_DKV) ? N_EW * 2 * 192 * 4 : (MODE == MODE_FWD) ? NCG * 128 * 2 * 4 : 16;
   static constexpr int OFF_RING = N_RES * TILE_BYTES;
   static constexpr int OFF_STAT = OFF_RING + NST * STAGE_BYTES;
   static constexpr int OFF_BAR = OFF_STAT + STAT_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-  static_assert(SMEM_BYTES <= 232448, "more shared memory than one CTA can have");
+  static_assert(SMEM_BYTES <= 232448 / CTAS_PER_SM - 1024 * (CTAS_PER_SM - 1), "more shared memory than the CTAs of one SM can have");
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -111,11 +124,11 @@ __device__ __forceinline__ void store_out_cols(uint32_t taddr, bf16* dst) {
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(N_THREADS, 1)
+__global__ void __launch_bounds__(AtcCfg<MODE>::THREADS, AtcCfg<MODE>::CTAS_PER_SM)
 k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CUtensorMap tm_qkv,
           const __grid_constant__ CUtensorMap tm_do, const AtcParams p) {
   using Cfg = AtcCfg<MODE>;
-  constexpr int NST = Cfg::NST;
+  constexpr int NST = Cfg::NST, N_EW = Cfg::N_EW, NCG = Cfg::NCG, PASSES = Cfg::PASSES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
@@ -126,8 +139,11 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
   auto tfull_bar = [&](int b) { return sBar + 8u * (2 * NST + b); };
   auto tempty_bar = [&](int b) { return sBar + 8u * (2 * NST + 2 + b); };
   auto efull_bar = [&](int e) { return sBar + 8u * (2 * NST + 4 + e); };
-  auto eempty_bar = [&](int e) { return sBar + 8u * (2 * NST + 6 + e); };
   const uint32_t out_bar = sBar + 8u * (2 * NST + 8), res_bar = out_bar + 8, comb_bar = out_bar + 16, tmem_slot = out_bar + 24;
+  // forward kernel: the K half of a ring stage is free once the score product has read it and the V half once the
+  // output product has, so the two halves have their own full / empty barriers (full_bar / empty_bar serve K)
+  auto vfull_bar = [&](int s) { return out_bar + 32u + 8u * s; };
+  auto vempty_bar = [&](int s) { return out_bar + 32u + 8u * (NST + s); };
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + Cfg::OFF_BAR + 8 * (2 * NST + 8) + 24);
 
   const int warp = uniform_warp_idx(), lane = threadIdx.x & 31;
@@ -160,29 +176,31 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
   if (threadIdx.x == 0) {
     for (int s = 0; s < NST; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int t = 0; t < 2; ++t) { mbar_init(tfull_bar(t), 1); mbar_init(tempty_bar(t), N_EW / 2); }
-    for (int e = 0; e < 2; ++e) { mbar_init(efull_bar(e), N_EW / 2); mbar_init(eempty_bar(e), 1); }
+    for (int e = 0; e < 2; ++e) mbar_init(efull_bar(e), N_EW / 2);
+    if (MODE == MODE_FWD)
+      for (int s = 0; s < NST; ++s) { mbar_init(vfull_bar(s), 1); mbar_init(vempty_bar(s), 1); }
     // the row-side tiles arrive by TMA (dK/dV) or are written to tensor memory by the element-wise warps
-    mbar_init(out_bar, 1); mbar_init(res_bar, MODE == MODE_DKV ? 1 : N_EW); mbar_init(comb_bar, N_EW);
+    mbar_init(out_bar, 1); mbar_init(res_bar, MODE == MODE_DQ ? N_EW : 1); mbar_init(comb_bar, N_EW);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512u) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(Cfg::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_gen;
-  // Tensor-memory columns (512): score buffers at 0 / 128 (T1 at +0, T2 at +64), first output at 256.
-  //   forward   Q (bf16 pairs, 64 columns) at 384, P double-buffered at 448 / 480
-  //   dQ        Q at 384, dO at 448; dS overwrites the T1 buffer it was computed from
-  //   dK, dV    second output at 384; P^T and dS^T overwrite the T1 / T2 buffers they were computed from
+  // Tensor-memory columns:
+  //   forward   (256 per CTA) score buffers at 0 / 64, output at 128; P overwrites the score buffer it was computed from
+  //   dQ        (512) score buffers at 0 / 128 (T1 at +0, T2 at +64), output at 256, Q (bf16 pairs, 64 columns) at 384,
+  //             dO at 448; dS overwrites the T1 buffer it was computed from
+  //   dK, dV    (512) as dQ, second output at 384; P^T and dS^T overwrite the T1 / T2 buffers they were computed from
   // A 16-bit tile written over a score buffer goes where its writer read: warp group cg owns columns 16cg .. 16cg+15
   // of the buffer and puts its 16 k-values (8 columns) at 16cg, which is also where the MMA of k-step cg looks for them.
-  auto t1_col = [&](int buf) { return tmem + (uint32_t)(buf * 128); };
+  auto t1_col = [&](int buf) { return tmem + (uint32_t)(buf * (MODE == MODE_FWD ? 64 : 128)); };
   auto t2_col = [&](int buf) { return tmem + (uint32_t)(buf * 128 + 64); };
-  const uint32_t out1 = tmem + 256u, out2 = tmem + 384u, qcol = tmem + 384u, docol = tmem + 448u;
-  auto pcol = [&](int e) { return tmem + 448u + (uint32_t)(e * 32); };
+  const uint32_t out1 = tmem + (MODE == MODE_FWD ? 128u : 256u), out2 = tmem + 384u, qcol = tmem + 384u, docol = tmem + 448u;
 
   if (warp == 0) {
     // =========================== TMA producer ===========================
@@ -196,6 +214,10 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       load_tile128(sRes, &tm_qkn, xk, row_base + r0);
       load_tile128(sRes + TILE_BYTES, &tm_qkv, xv, row_base + r0);
     }
+    if (MODE == MODE_FWD) {
+      mbar_expect_tx_elect(res_bar, Cfg::N_RES * TILE_BYTES);
+      load_tile128(sRes, &tm_qkn, xq, row_base + r0);
+    }
     bool ok = true;
     int g = 0;
     for (; g < total_g; ++g) {
@@ -203,25 +225,45 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       ok = __all_sync(0xffffffffu, twait(11, empty_bar(s), (((uint32_t)g / NST) & 1u) ^ 1u, p.err, tacc[0]));
       if (!ok) break;
       const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
-      const bool stats_pass = (MODE == MODE_FWD) && g < n_it;
-      mbar_expect_tx_elect(full_bar(s), stats_pass ? SUB_BYTES : STAGE_BYTES);
-      if (MODE == MODE_DKV) {
+      if (MODE == MODE_FWD) {
+        // K of key sub-tile g % n_it (both sweeps); V of sub-tile it = g - n_it (second sweep) through its own barriers
+        const int y = row_base + (g % n_it) * 64;
+        mbar_expect_tx_elect(full_bar(s), SUB_BYTES);
+        tma_load_2d_elect(c1, &tm_qkn, full_bar(s), xk, y); tma_load_2d_elect(c1 + 8192, &tm_qkn, full_bar(s), xk + 64, y);
+        if (g >= n_it) {
+          const int it = g - n_it, sv = it % NST;
+          ok = __all_sync(0xffffffffu, twait(11, vempty_bar(sv), (((uint32_t)it / NST) & 1u) ^ 1u, p.err, tacc[0]));
+          if (!ok) { ++g; break; }
+          const uint32_t cv = sRing + sv * STAGE_BYTES + SUB_BYTES;
+          mbar_expect_tx_elect(vfull_bar(sv), SUB_BYTES);
+          tma_load_2d_elect(cv, &tm_qkv, vfull_bar(sv), xv, y); tma_load_2d_elect(cv + 8192, &tm_qkv, vfull_bar(sv), xv + 64, y);
+        }
+      } else if (MODE == MODE_DKV) {
+        mbar_expect_tx_elect(full_bar(s), STAGE_BYTES);
         const int hh = h + g / n_q, y = row_base + r0 + (g % n_q) * 64;
         tma_load_2d_elect(c1, &tm_qkn, full_bar(s), hh * HD, y); tma_load_2d_elect(c1 + 8192, &tm_qkn, full_bar(s), hh * HD + 64, y);
         tma_load_2d_elect(c2, &tm_do, full_bar(s), hh * HD, y);  tma_load_2d_elect(c2 + 8192, &tm_do, full_bar(s), hh * HD + 64, y);
       } else {
-        const int y = row_base + ((MODE == MODE_FWD) ? (g % n_it) : g) * 64;
+        mbar_expect_tx_elect(full_bar(s), STAGE_BYTES);
+        const int y = row_base + g * 64;
         tma_load_2d_elect(c1, &tm_qkn, full_bar(s), xk, y); tma_load_2d_elect(c1 + 8192, &tm_qkn, full_bar(s), xk + 64, y);
-        if (!stats_pass) { tma_load_2d_elect(c2, &tm_qkv, full_bar(s), xv, y); tma_load_2d_elect(c2 + 8192, &tm_qkv, full_bar(s), xv + 64, y); }
+        tma_load_2d_elect(c2, &tm_qkv, full_bar(s), xv, y); tma_load_2d_elect(c2 + 8192, &tm_qkv, full_bar(s), xv + 64, y);
       }
     }
     if (!ok) {
-      // gave up after g loads were armed: wait (bounded) for the copies still in flight before the CTA may exit
+      // gave up after g K (or K+V) loads were armed: wait (bounded) for the copies still in flight before the CTA may exit
       for (int j = (g > NST ? g - NST : 0); j < g; ++j) {
         const uint32_t ph = ((uint32_t)j / NST) & 1u;
         for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(full_bar(j % NST), ph)) break;
       }
-      if (MODE == MODE_DKV)
+      if (MODE == MODE_FWD) {
+        const int nv = g > n_it ? g - n_it : 0;                  // V loads armed so far (at most; the last may not be)
+        for (int j = (nv > NST ? nv - NST : 0); j < nv; ++j) {
+          const uint32_t ph = ((uint32_t)j / NST) & 1u;
+          for (uint32_t w = 0; w < (1u << 16); ++w) if (mbar_try(vfull_bar(j % NST), ph)) break;
+        }
+      }
+      if (MODE != MODE_DQ)
         for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(res_bar, 0)) break;
     }
   } else if (warp == 1) {
@@ -247,13 +289,15 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
         if (MODE == MODE_DKV) {
           mma_bf16_elect(t1_col(buf), make_desc(sRes + ao, 16, 1024), make_desc(c1 + bo, 16, 1024), ID_T, ks > 0);
           mma_bf16_elect(t2_col(buf), make_desc(sRes + TILE_BYTES + ao, 16, 1024), make_desc(c2 + bo, 16, 1024), ID_T, ks > 0);
+        } else if (MODE == MODE_FWD) {
+          mma_bf16_elect(t1_col(buf), make_desc(sRes + ao, 16, 1024), make_desc(c1 + bo, 16, 1024), ID_T, ks > 0);
         } else {
-          // A from tensor memory (forward, dQ): k-step ks = head dimensions 16ks .. 16ks+15 = 8 columns of bf16 pairs
+          // A from tensor memory (dQ): k-step ks = head dimensions 16ks .. 16ks+15 = 8 columns of bf16 pairs
           mma_bf16_ts_elect(t1_col(buf), qcol + 8u * ks, make_desc(c1 + bo, 16, 1024), ID_T, ks > 0);
-          if (MODE == MODE_DQ) mma_bf16_ts_elect(t2_col(buf), docol + 8u * ks, make_desc(c2 + bo, 16, 1024), ID_T, ks > 0);
+          mma_bf16_ts_elect(t2_col(buf), docol + 8u * ks, make_desc(c2 + bo, 16, 1024), ID_T, ks > 0);
         }
       }
-      if (release_stage) mma_commit_elect(empty_bar(s));
+      if (release_stage || MODE == MODE_FWD) mma_commit_elect(empty_bar(s));   // forward: the K half is free after the score product
       mma_commit_elect(tfull_bar(buf));
 #ifdef PCPB_ATC_TIMING
       if (lane == 0) ts_tcommit[buf] = clock64();
@@ -278,28 +322,34 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
 #endif
       tc_fence_after();
       ATC_T0();
-      const int s = (g0 + it) % NST, buf = (g0 + it) & 1;
+      const int s = (MODE == MODE_FWD) ? (it % NST) : ((g0 + it) % NST), buf = (g0 + it) & 1;
       const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
+      if (MODE == MODE_FWD) {
+        if (!(ok = __all_sync(0xffffffffu, twait(13, vfull_bar(s), ((uint32_t)it / NST) & 1u, p.err, tacc[2])))) break;
+        tc_fence_after();
+      }
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) {
         const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
-        if (MODE == MODE_FWD) mma_bf16_ts_elect(out1, pcol(eb) + 8u * ks, make_desc(c2 + ks * 2048u, 8192, 1024), ID_O, acc);
+        if (MODE == MODE_FWD) mma_bf16_ts_elect(out1, t1_col(buf) + 16u * ks, make_desc(c2 + ks * 2048u, 8192, 1024), ID_O, acc);
         if (MODE == MODE_DQ) mma_bf16_ts_elect(out1, t1_col(buf) + 16u * ks, make_desc(c1 + ks * 2048u, 8192, 1024), ID_O, acc);
         if (MODE == MODE_DKV) {
           mma_bf16_ts_elect(out1, t1_col(buf) + 16u * ks, make_desc(c2 + ks * 2048u, 8192, 1024), ID_O, acc);
           mma_bf16_ts_elect(out2, t2_col(buf) + 16u * ks, make_desc(c1 + ks * 2048u, 8192, 1024), ID_O, acc);
         }
       }
-      mma_commit_elect(empty_bar(s));
-      if (MODE == MODE_FWD) mma_commit_elect(eempty_bar(eb));
+      mma_commit_elect(MODE == MODE_FWD ? vempty_bar(s) : empty_bar(s));
       ATC_T1(11);
     }
     if (ok) mma_commit_elect(out_bar);
   } else {
     // =========================== element-wise warps ===========================
-    // Sixteen warps, four per tensor-memory lane quarter.  cg = 0..3 numbers the four warps of a quarter: it picks the
-    // 32 head dimensions / output columns a thread moves, and splits into the sub-tile group and the column half.
-    const int q = warp & 3, row = q * 32 + lane, cg = (warp - 2) >> 2, grp2 = cg >> 1, half = cg & 1;
+    // NCG warps per tensor-memory lane quarter (4 in the backward kernels, 2 in the forward kernel).  cg numbers the
+    // warps of a quarter: it picks the head dimensions / output columns a thread moves, and splits into the sub-tile
+    // group (two groups) and, with 4 warps per quarter, the half of the 64 score columns a thread owns.
+    const int q = warp & 3, row = q * 32 + lane, cg = (warp - 2) >> 2;
+    const int grp2 = (NCG == 4) ? (cg >> 1) : cg, half = (NCG == 4) ? (cg & 1) : 0;
+    constexpr int SHARE = 16 * PASSES;                       // score columns of a sub-tile a thread owns
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const int my = r0 + row;                                 // my query (FWD, DQ) or my key (DKV)
     const uint32_t scale2 = pack2(p.scale, p.scale);
@@ -311,28 +361,26 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       inv2 = 1.f / (l_run + 2.f * PCPB_GUARD);
       mterm = Dr * (2.f * PCPB_GUARD) * inv2;
     }
-    if (MODE != MODE_DKV) {
-      // ---- my 32 head dimensions of my row of Q (and of dO) go to tensor memory as bf16 pairs ----
+    if (MODE == MODE_DQ) {
+      // ---- my 32 head dimensions of my row of Q and of dO go to tensor memory as bf16 pairs (all loads first) ----
       const uint32_t dst = lane_off + (uint32_t)(cg * 16);
-      uint32_t w[16];
+      uint32_t w[16], w2[16];
       const uint4* src = reinterpret_cast<const uint4*>(p.qkn + (size_t)(row_base + my) * (p.d + p.dkv) + xq + cg * 32);
+      const uint4* src2 = reinterpret_cast<const uint4*>(p.dout + (size_t)(row_base + my) * p.d + xq + cg * 32);
 #pragma unroll
       for (int j = 0; j < 4; ++j) { const uint4 v = __ldg(src + j); w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w; }
-      tmem_st16(qcol + dst, w);
-      if (MODE == MODE_DQ) {
-        src = reinterpret_cast<const uint4*>(p.dout + (size_t)(row_base + my) * p.d + xq + cg * 32);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { const uint4 v = __ldg(src + j); w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w; }
-        tmem_st16(docol + dst, w);
-      }
+      for (int j = 0; j < 4; ++j) { const uint4 v = __ldg(src2 + j); w2[4 * j] = v.x; w2[4 * j + 1] = v.y; w2[4 * j + 2] = v.z; w2[4 * j + 3] = v.w; }
+      tmem_st16(qcol + dst, w);
+      tmem_st16(docol + dst, w2);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(res_bar);
     }
-    // Two groups of eight warps take the sub-tiles in turn (group = parity of the sub-tile = its score buffer), so the
+    // Two groups of warps take the sub-tiles in turn (group = parity of the sub-tile = its score buffer), so the
     // tensor-memory and barrier latencies of one group are spent under the arithmetic of the other.  Within a group a
-    // thread owns one row and 32 of the 64 columns, in two passes of 16.
+    // thread owns one row and SHARE (32 or 64) of the 64 columns, in passes of 16.
     int g = grp2;
     if (MODE == MODE_FWD) {
       // ---- sweep 1: row max and row sum of exp over this thread's share of the keys ----
@@ -342,16 +390,17 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
         if (!ok) break;
         tc_fence_after();
         // both passes' score columns are fetched at once (one exposed tensor-memory latency per sub-tile)
-        uint32_t rr[2][16];
-        tmem_ld16_issue(t1_col(buf) + lane_off + (uint32_t)(half * 32), rr[0]);
-        tmem_ld16_issue(t1_col(buf) + lane_off + (uint32_t)(half * 32 + 16), rr[1]);
-        tmem_ld_wait16(rr[0]); tmem_ld_wait16(rr[1]);
+        uint32_t rr[PASSES][16];
+#pragma unroll
+        for (int pass = 0; pass < PASSES; ++pass) tmem_ld16_issue(t1_col(buf) + lane_off + (uint32_t)(half * SHARE + pass * 16), rr[pass]);
+#pragma unroll
+        for (int pass = 0; pass < PASSES; ++pass) tmem_ld_wait16(rr[pass]);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar(buf));          // the values are in registers: release the buffer early
 #pragma unroll
-        for (int pass = 0; pass < 2; ++pass) {
-          const int ch = half * 32 + pass * 16, k0 = g * 64 + ch;
+        for (int pass = 0; pass < PASSES; ++pass) {
+          const int ch = half * SHARE + pass * 16, k0 = g * 64 + ch;
           const bool diag = (k0 + 15 > r0);
           const uint32_t (&r)[16] = rr[pass];
           float sv[16], cm = -INFINITY;
@@ -375,7 +424,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
           }
         }
       }
-      // combine the four partial results of each row through shared memory (every warp sums them in the same order)
+      // combine the partial results of each row through shared memory (every warp sums them in the same order)
       if (ok) {
         stat[(cg * 128 + row) * 2] = m_run; stat[(cg * 128 + row) * 2 + 1] = l_run;
         __syncwarp();
@@ -385,10 +434,10 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       if (ok) {
         float mn = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) mn = fmaxf(mn, stat[(c * 128 + row) * 2]);
+        for (int c = 0; c < NCG; ++c) mn = fmaxf(mn, stat[(c * 128 + row) * 2]);
         float l = 0.f;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) l += stat[(c * 128 + row) * 2 + 1] * ex2((stat[(c * 128 + row) * 2] - mn) * LOG2E);
+        for (int c = 0; c < NCG; ++c) l += stat[(c * 128 + row) * 2 + 1] * ex2((stat[(c * 128 + row) * 2] - mn) * LOG2E);
         m_run = mn; l_run = l;
         inv1 = 1.f / (l_run + PCPB_GUARD);
       }
@@ -402,7 +451,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       float* st = stat + ((warp - 2) * 2 + ((it >> 1) & 1)) * 192;
       if (MODE == MODE_DKV) {
         const int hh = h + it / n_q;
-        cbase = r0 + (it % n_q) * 64 + half * 32;
+        cbase = r0 + (it % n_q) * 64 + half * SHARE;
         const long long idx = ((long long)b * p.H + hh) * p.T + cbase + lane;
         const float mm = p.mrow[idx], ll = p.lrow[idx], dd = p.drow[idx];
         const float i2 = 1.f / (ll + 2.f * PCPB_GUARD);
@@ -410,7 +459,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
         st[128 + lane] = dd * (2.f * PCPB_GUARD) * i2; st[160 + lane] = mm * LOG2E;
         __syncwarp();
       } else {
-        cbase = it * 64 + half * 32;
+        cbase = it * 64 + half * SHARE;
       }
       ok = __all_sync(0xffffffffu, twait(17, tfull_bar(buf), ((uint32_t)gg >> 1) & 1u, p.err, tacc[6]));
       if (!ok) break;
@@ -422,23 +471,24 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       // Fetch the score (and dP) columns of both passes at once where the registers allow it (forward, dQ): one
       // exposed tensor-memory latency per sub-tile instead of one per load.
       constexpr bool BATCH = (MODE != MODE_DKV);
-      uint32_t q1[2][16], q2[2][16];
+      uint32_t q1[PASSES][16], q2[2][16];
       if (BATCH) {
-        tmem_ld16_issue(t1_col(buf) + lane_off + (uint32_t)(half * 32), q1[0]);
-        tmem_ld16_issue(t1_col(buf) + lane_off + (uint32_t)(half * 32 + 16), q1[1]);
+#pragma unroll
+        for (int pass = 0; pass < PASSES; ++pass) tmem_ld16_issue(t1_col(buf) + lane_off + (uint32_t)(half * SHARE + pass * 16), q1[pass]);
         if (MODE == MODE_DQ) {
           tmem_ld16_issue(t2_col(buf) + lane_off + (uint32_t)(half * 32), q2[0]);
           tmem_ld16_issue(t2_col(buf) + lane_off + (uint32_t)(half * 32 + 16), q2[1]);
         }
-        tmem_ld_wait16(q1[0]); tmem_ld_wait16(q1[1]);
+#pragma unroll
+        for (int pass = 0; pass < PASSES; ++pass) tmem_ld_wait16(q1[pass]);
         if (MODE == MODE_DQ) { tmem_ld_wait16(q2[0]); tmem_ld_wait16(q2[1]); }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar(buf));
       }
 #pragma unroll
-      for (int pass = 0; pass < 2; ++pass) {
-        const int ch = half * 32 + pass * 16, c0 = cbase + pass * 16;
+      for (int pass = 0; pass < PASSES; ++pass) {
+        const int ch = half * SHARE + pass * 16, c0 = cbase + pass * 16;
         // does the causal boundary cross this block of 32 rows x 16 columns?
         const bool diag = (MODE == MODE_DKV) ? (c0 < r0 + 128) : (c0 + 15 > r0);
         uint32_t (&r1)[16] = q1[pass];
@@ -456,7 +506,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
             ew[j] = pack2(e0, e1);
           }
         } else {
-          uint32_t (&r2)[16] = q2[pass];
+          uint32_t (&r2)[16] = q2[pass & 1];
           if (!BATCH) {
             tmem_ld16(t2_col(buf) + lane_off + (uint32_t)ch, r2);
             if (pass == 1) {
@@ -505,19 +555,10 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
             }
           }
         }
-        if (MODE == MODE_FWD) {
-          // the output product that read this P buffer two sub-tiles ago must have finished
-          if (pass == 0) {
-            ok = __all_sync(0xffffffffu, twait(18, eempty_bar(buf), (((uint32_t)it >> 1) & 1u) ^ 1u, p.err, tacc[7]));
-            if (!ok) break;
-          }
-          tmem_st8(pcol(buf) + lane_off + (uint32_t)(ch >> 1), ew);
-        } else {
-          // over my own columns of the score buffer(s): nobody else reads them, and the next score product into this
-          // buffer is issued after the output product that consumes these tiles
-          if (MODE == MODE_DKV) tmem_st8(t1_col(buf) + lane_off + (uint32_t)ch, pw);
-          tmem_st8((MODE == MODE_DKV ? t2_col(buf) : t1_col(buf)) + lane_off + (uint32_t)ch, ew);
-        }
+        // over my own columns of the score buffer(s): nobody else reads them, and the next score product into this
+        // buffer is issued after the output product that consumes these tiles
+        if (MODE == MODE_DKV) tmem_st8(t1_col(buf) + lane_off + (uint32_t)ch, pw);
+        tmem_st8((MODE == MODE_DKV ? t2_col(buf) : t1_col(buf)) + lane_off + (uint32_t)ch, ew);
       }
       if (!ok) break;
       tmem_st_wait();
@@ -529,23 +570,26 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       if (lane == 0) mbar_arrive(efull_bar(buf));
       ATC_T1(12);
     }
-    // ---- outputs: each warp stores 32 of the 128 output columns of its rows ----
+    // ---- outputs: each warp stores 128 / NCG of the 128 output columns of its rows ----
     if (ok) ok = __all_sync(0xffffffffu, twait(19, out_bar, 0, p.err, tacc[8]));
     if (ok) {
       tc_fence_after();
       const long long grow = (long long)row_base + my;
-      const int oc = cg * 32;
-      if (MODE == MODE_FWD) {
-        store_out_cols(out1 + lane_off + oc, p.o + grow * p.d + xq + oc);
-        if (cg == 0) {
-          const long long idx = ((long long)b * p.H + h) * p.T + my;
-          p.mrow[idx] = m_run; p.lrow[idx] = l_run;
+#pragma unroll
+      for (int part = 0; part < 4 / NCG; ++part) {
+        const int oc = (cg * (4 / NCG) + part) * 32;
+        if (MODE == MODE_FWD) {
+          store_out_cols(out1 + lane_off + oc, p.o + grow * p.d + xq + oc);
+        } else if (MODE == MODE_DQ) {
+          store_out_cols(out1 + lane_off + oc, p.dqkn + grow * (p.d + p.dkv) + xq + oc);
+        } else {
+          store_out_cols(out1 + lane_off + oc, p.dqkv + grow * (p.d + 2 * p.dkv) + xv + oc);
+          store_out_cols(out2 + lane_off + oc, p.dqkn + grow * (p.d + p.dkv) + xk + oc);
         }
-      } else if (MODE == MODE_DQ) {
-        store_out_cols(out1 + lane_off + oc, p.dqkn + grow * (p.d + p.dkv) + xq + oc);
-      } else {
-        store_out_cols(out1 + lane_off + oc, p.dqkv + grow * (p.d + 2 * p.dkv) + xv + oc);
-        store_out_cols(out2 + lane_off + oc, p.dqkn + grow * (p.d + p.dkv) + xk + oc);
+      }
+      if (MODE == MODE_FWD && cg == 0) {
+        const long long idx = ((long long)b * p.H + h) * p.T + my;
+        p.mrow[idx] = m_run; p.lrow[idx] = l_run;
       }
     }
   }
@@ -565,7 +609,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(Cfg::TMEM_COLS) : "memory");
   }
 }
 
@@ -599,9 +643,12 @@ cudaError_t launch_mode(cudaStream_t st, const CUtensorMap& a, const CUtensorMap
   if (dev < 0 || dev >= 64 || !attr[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AtcCfg<MODE>::SMEM_BYTES);
     if (e != cudaSuccess) return e;
+    // all of the SM's L1 / shared-memory array as shared memory: the forward kernel needs it to fit two CTAs per SM
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) attr[dev] = true;
   }
-  kern<<<grid, N_THREADS, AtcCfg<MODE>::SMEM_BYTES, st>>>(a, b, c, p);
+  kern<<<grid, AtcCfg<MODE>::THREADS, AtcCfg<MODE>::SMEM_BYTES, st>>>(a, b, c, p);
   return cudaGetLastError();
 }
 
