@@ -1,7 +1,7 @@
 """Generates tests/golden/*.npz from the reference's shipped forward graphs.
 
-Run in a container that has the reference tree (default /root/reference); the fixtures are committed so
-that the GPU box, which does not have the tree, can check against them.
+Run where the reference tree is available (PCP_REFERENCE, default: the directory `reference` next to this
+repository); the fixtures are committed so that machines without the tree can check against them.
 
   nanochat_small.npz   models/nanochat_small.mlir (f32, V=65 d=64 L=2 H=4 T=32 B=64):
                        seeded parameters and one FIFO batch -> loss and all gradients of
@@ -21,7 +21,7 @@ from oracle.loader import FifoU16, uniform_tokens            # noqa: E402
 from oracle.optim import AdamConf                            # noqa: E402
 from oracle.worker import TrainingModule, inner_loop         # noqa: E402
 
-REF = os.environ.get("PCP_REFERENCE", "/root/reference")
+REF = os.environ.get("PCP_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference"))
 
 
 def main():

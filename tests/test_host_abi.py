@@ -10,7 +10,7 @@ from pcp_b200 import backend as bk
 from pcp_b200.backend import inspect_artifact, load_library
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = os.environ.get("PCP_REFERENCE", "/root/reference")
+REF = os.environ.get("PCP_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference"))
 
 
 def declared_functions():

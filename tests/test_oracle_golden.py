@@ -15,7 +15,7 @@ from pcp_b200 import NanochatConfig, NanoGPTConfig, nanochat_forward_mlir, nanog
 from pcp_b200.export import rope_tables
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-REF = os.environ.get("PCP_REFERENCE", "/root/reference")
+REF = os.environ.get("PCP_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"))
 SMALL = NanochatConfig(vocab=65, d_model=64, n_layer=2, n_head=4, n_kv_head=4, seq_len=32, batch=64, dtype="f32")
 
 
