@@ -428,6 +428,29 @@ class Backend:
         self._check(self._lib.pcpb_worker_read_state(self._h, sel, out.ctypes.data, n))
         return out
 
+    # -- checkpoints in the reference's file format (pcp_b200/formats.py)
+    def save_checkpoint(self, path: str, param_dtype=F32):
+        """Writes the master parameters on the device as a `checkpoint_<step>.bin` file of the reference
+        (src/algorithms/diloco.zig:590-628): f32, or bf16 bit patterns (truncated, as the Shepherd keeps them)."""
+        from . import formats
+        flat = self.worker_read_state("master")
+        if param_dtype == BF16:
+            flat = (flat.view(np.uint32) >> 16).astype(np.uint16)
+        formats.write_checkpoint(path, formats.split_flat(flat, self.param_shapes()))
+
+    def load_checkpoint(self, path: str):
+        """-> (parameter blob for worker_begin_round, its dtype code), checked against the loaded artefact's shapes."""
+        from . import formats
+        tensors = formats.read_checkpoint(path)
+        shapes = self.param_shapes()
+        if [tuple(t.shape) for t in tensors] != [tuple(s) for s in shapes]:
+            raise BackendError(1, "checkpoint shapes do not match the artefact")
+        dts = {t.dtype for t in tensors}
+        if len(dts) != 1:
+            raise BackendError(1, "checkpoint mixes parameter dtypes")
+        blob = np.concatenate([t.reshape(-1) for t in tensors])
+        return blob, (BF16 if blob.dtype == np.uint16 else F32)
+
     # -- outer step
     def outer_export(self) -> bytes:
         buf = C.create_string_buffer(2 * IPC_HANDLE_BYTES)

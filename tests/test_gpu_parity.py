@@ -329,6 +329,24 @@ def test_streaming_diloco_matches_oracle(cfgd, P, H, tau):
             b.close()
 
 
+def test_checkpoint_file_round_trip(tmp_path):
+    """Master parameters -> checkpoint file in the reference's format -> blob for the next round, bit for bit."""
+    cfg = NanochatConfig(**SMALL_BF16)
+    text = nanochat_forward_mlir(cfg)
+    master = flat(seeded_params(cfg, seed=9))
+    blob = f32_to_bf16_trunc_bits(master)
+    path = os.path.join(tmp_path, "checkpoint_3.bin")
+    with Backend(0) as be:
+        be.load_session(text)
+        be.worker_begin_round(1, blob, param_dtype=BF16)
+        be.worker_set_tokens(tokens_for(cfg, 1, seed=2))
+        be.worker_step()
+        be.worker_end_round(1, param_dtype=BF16)
+        be.save_checkpoint(path, BF16)
+        got, dt = be.load_checkpoint(path)
+    assert dt == BF16 and got.dtype == np.uint16 and np.array_equal(got, blob)     # the master is untouched by the inner loop
+
+
 def test_outer_step_bit_exact_given_deltas():
     """With the deltas taken from the device itself the outer arithmetic (sum in worker order, / n, NaN -> 0,
     Nesterov, bf16 truncation) is bit-identical to the restated reference."""
