@@ -14,7 +14,7 @@
 // it came from (tcgen05.st), where the next MMA finds it as its A operand (TS form).  Score tiles are double-buffered
 // in tensor memory and two groups of element-wise warps take the sub-tiles in turn, so the MMAs of sub-tile i+1
 // overlap the arithmetic of sub-tile i.  The backward kernels use 16 element-wise warps and the whole SM (512
-// tensor-memory columns, Q and dO of the dQ kernel in tensor memory as well); the forward kernel uses 8, half of the
+// tensor-memory columns); the forward kernel uses 8, half of the
 // tensor memory and 100 KB of shared memory, and runs two CTAs per SM: four sub-tiles in flight per SM, and one
 // CTA's prologue / epilogue under the other's main loop.  What limits these kernels is the latency of the hand-offs
 // MMA -> element-wise -> MMA (commit, wake-up, tcgen05.ld / st), not the tensor pipe, hence the concurrency.
@@ -40,7 +40,7 @@ constexpr int HD = 128;
 #define PCPB_ATC_NST_FWD 2
 #endif
 #ifndef PCPB_ATC_NST_DQ
-#define PCPB_ATC_NST_DQ 3
+#define PCPB_ATC_NST_DQ 4
 #endif
 constexpr int SUB_BYTES = 64 * HD * 2;         // one streamed sub-tile: 16 KB
 constexpr int STAGE_BYTES = 2 * SUB_BYTES;     // (C1, C2)
@@ -64,15 +64,18 @@ struct AtcParams {
 
 template <int MODE> struct AtcCfg {
   static constexpr int N_EW = (MODE == MODE_FWD) ? 8 : 16;
+  // score buffers in tensor memory = sub-tiles in flight = element-wise groups (one group per buffer)
+  static constexpr int NBUF = 2;
   static constexpr int THREADS = 64 + 32 * N_EW;
   static constexpr int CTAS_PER_SM = (MODE == MODE_FWD) ? 2 : 1;
   static constexpr int NCG = N_EW / 4;                       // warps per tensor-memory lane quarter
   static constexpr int PASSES = (NCG == 4) ? 2 : 4;          // 16-column passes of a thread over its share of a sub-tile
+  // passes whose score columns are fetched from tensor memory with one wait (0: one wait per pass)
+  static constexpr int LPR = (MODE == MODE_FWD) ? 4 : (MODE == MODE_DQ) ? 2 : 0;
   static constexpr uint32_t TMEM_COLS = (MODE == MODE_FWD) ? 256u : 512u;
   static constexpr int NST = (MODE == MODE_FWD) ? PCPB_ATC_NST_FWD : (MODE == MODE_DQ) ? PCPB_ATC_NST_DQ : 3;   // ring stages
-  // resident row-side tiles in shared memory: K and V of the dK/dV kernel, Q of the forward kernel (the dQ kernel keeps
-  // Q and dO in tensor memory)
-  static constexpr int N_RES = (MODE == MODE_DKV) ? 2 : (MODE == MODE_FWD) ? 1 : 0;
+  // resident row-side tiles in shared memory: K and V (dK/dV kernel), Q and dO (dQ kernel), Q (forward kernel)
+  static constexpr int N_RES = (MODE == MODE_FWD) ? 1 : 2;
   // DKV: per warp, double-buffered, six statistics of 32 columns; FWD: exchange of the four partial (max, sum) of a row
   static constexpr int STAT_BYTES = (MODE == MODE_DKV) ? N_EW * 2 * 192 * 4 : (MODE == MODE_FWD) ? NCG * 128 * 2 * 4 : 16;
   static constexpr int OFF_RING = N_RES * TILE_BYTES;
@@ -128,7 +131,7 @@ __global__ void __launch_bounds__(AtcCfg<MODE>::THREADS, AtcCfg<MODE>::CTAS_PER_
 k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CUtensorMap tm_qkv,
           const __grid_constant__ CUtensorMap tm_do, const AtcParams p) {
   using Cfg = AtcCfg<MODE>;
-  constexpr int NST = Cfg::NST, N_EW = Cfg::N_EW, NCG = Cfg::NCG, PASSES = Cfg::PASSES;
+  constexpr int NST = Cfg::NST, N_EW = Cfg::N_EW, NCG = Cfg::NCG, PASSES = Cfg::PASSES, NBUF = Cfg::NBUF, LPR = Cfg::LPR;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
@@ -137,14 +140,14 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
   auto full_bar = [&](int s) { return sBar + 8u * s; };
   auto empty_bar = [&](int s) { return sBar + 8u * (NST + s); };
   auto tfull_bar = [&](int b) { return sBar + 8u * (2 * NST + b); };
-  auto tempty_bar = [&](int b) { return sBar + 8u * (2 * NST + 2 + b); };
-  auto efull_bar = [&](int e) { return sBar + 8u * (2 * NST + 4 + e); };
-  const uint32_t out_bar = sBar + 8u * (2 * NST + 8), res_bar = out_bar + 8, comb_bar = out_bar + 16, tmem_slot = out_bar + 24;
+  auto tempty_bar = [&](int b) { return sBar + 8u * (2 * NST + 3 + b); };
+  auto efull_bar = [&](int e) { return sBar + 8u * (2 * NST + 6 + e); };
+  const uint32_t out_bar = sBar + 8u * (2 * NST + 9), res_bar = out_bar + 8, comb_bar = out_bar + 16, tmem_slot = out_bar + 24;
   // forward kernel: the K half of a ring stage is free once the score product has read it and the V half once the
   // output product has, so the two halves have their own full / empty barriers (full_bar / empty_bar serve K)
   auto vfull_bar = [&](int s) { return out_bar + 32u + 8u * s; };
   auto vempty_bar = [&](int s) { return out_bar + 32u + 8u * (NST + s); };
-  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + Cfg::OFF_BAR + 8 * (2 * NST + 8) + 24);
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + Cfg::OFF_BAR + 8 * (2 * NST + 9) + 24);
 
   const int warp = uniform_warp_idx(), lane = threadIdx.x & 31;
   const int grp = p.H / p.Hkv;
@@ -175,12 +178,11 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NST; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int t = 0; t < 2; ++t) { mbar_init(tfull_bar(t), 1); mbar_init(tempty_bar(t), N_EW / 2); }
-    for (int e = 0; e < 2; ++e) mbar_init(efull_bar(e), N_EW / 2);
+    for (int t = 0; t < NBUF; ++t) { mbar_init(tfull_bar(t), 1); mbar_init(tempty_bar(t), N_EW / NBUF); mbar_init(efull_bar(t), N_EW / NBUF); }
     if (MODE == MODE_FWD)
       for (int s = 0; s < NST; ++s) { mbar_init(vfull_bar(s), 1); mbar_init(vempty_bar(s), 1); }
     // the row-side tiles arrive by TMA (dK/dV) or are written to tensor memory by the element-wise warps
-    mbar_init(out_bar, 1); mbar_init(res_bar, MODE == MODE_DQ ? N_EW : 1); mbar_init(comb_bar, N_EW);
+    mbar_init(out_bar, 1); mbar_init(res_bar, 1); mbar_init(comb_bar, N_EW);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -193,14 +195,14 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
   const uint32_t tmem = *tmem_slot_gen;
   // Tensor-memory columns:
   //   forward   (256 per CTA) score buffers at 0 / 64, output at 128; P overwrites the score buffer it was computed from
-  //   dQ        (512) score buffers at 0 / 128 (T1 at +0, T2 at +64), output at 256, Q (bf16 pairs, 64 columns) at 384,
-  //             dO at 448; dS overwrites the T1 buffer it was computed from
-  //   dK, dV    (512) as dQ, second output at 384; P^T and dS^T overwrite the T1 / T2 buffers they were computed from
+  //   dQ        (512) two score buffers at 0 / 128 (T1 at +0, T2 at +64), output at 384; dS overwrites the T1 buffer it
+  //             was computed from
+  //   dK, dV    (512) two score buffers at 0 / 128, outputs at 256 and 384; P^T and dS^T overwrite the T1 / T2 buffers
   // A 16-bit tile written over a score buffer goes where its writer read: warp group cg owns columns 16cg .. 16cg+15
   // of the buffer and puts its 16 k-values (8 columns) at 16cg, which is also where the MMA of k-step cg looks for them.
   auto t1_col = [&](int buf) { return tmem + (uint32_t)(buf * (MODE == MODE_FWD ? 64 : 128)); };
   auto t2_col = [&](int buf) { return tmem + (uint32_t)(buf * 128 + 64); };
-  const uint32_t out1 = tmem + (MODE == MODE_FWD ? 128u : 256u), out2 = tmem + 384u, qcol = tmem + 384u, docol = tmem + 448u;
+  const uint32_t out1 = tmem + (MODE == MODE_FWD ? 128u : MODE == MODE_DQ ? 384u : 256u), out2 = tmem + 384u;
 
   if (warp == 0) {
     // =========================== TMA producer ===========================
@@ -217,6 +219,11 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
     if (MODE == MODE_FWD) {
       mbar_expect_tx_elect(res_bar, Cfg::N_RES * TILE_BYTES);
       load_tile128(sRes, &tm_qkn, xq, row_base + r0);
+    }
+    if (MODE == MODE_DQ) {
+      mbar_expect_tx_elect(res_bar, Cfg::N_RES * TILE_BYTES);
+      load_tile128(sRes, &tm_qkn, xq, row_base + r0);
+      load_tile128(sRes + TILE_BYTES, &tm_do, xq, row_base + r0);
     }
     bool ok = true;
     int g = 0;
@@ -263,8 +270,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
           for (uint32_t w = 0; w < (1u << 16); ++w) if (mbar_try(vfull_bar(j % NST), ph)) break;
         }
       }
-      if (MODE != MODE_DQ)
-        for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(res_bar, 0)) break;
+      for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(res_bar, 0)) break;
     }
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
@@ -274,9 +280,9 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
     constexpr uint32_t ID_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     bool ok = __all_sync(0xffffffffu, twait(12, res_bar, 0, p.err, tacc[1]));
     auto issue_T = [&](int g, bool release_stage) -> bool {
-      const int s = g % NST, buf = g & 1;
+      const int s = g % NST, buf = g % NBUF;
       if (!__all_sync(0xffffffffu, twait(13, full_bar(s), ((uint32_t)g / NST) & 1u, p.err, tacc[2]))) return false;
-      if (!__all_sync(0xffffffffu, twait(14, tempty_bar(buf), (((uint32_t)g >> 1) & 1u) ^ 1u, p.err, tacc[3]))) return false;
+      if (!__all_sync(0xffffffffu, twait(14, tempty_bar(buf), (((uint32_t)g / NBUF) & 1u) ^ 1u, p.err, tacc[3]))) return false;
       tc_fence_after();
       ATC_T0();
       const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
@@ -286,16 +292,10 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       for (int ks = 0; ks < 8; ++ks) {
         const uint32_t ao = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
         const uint32_t bo = (uint32_t)(ks >> 2) * 8192u + (uint32_t)(ks & 3) * 32u;
-        if (MODE == MODE_DKV) {
-          mma_bf16_elect(t1_col(buf), make_desc(sRes + ao, 16, 1024), make_desc(c1 + bo, 16, 1024), ID_T, ks > 0);
+        // first resident tile (Q or K) against the first streamed one; second (dO or V) against the second
+        mma_bf16_elect(t1_col(buf), make_desc(sRes + ao, 16, 1024), make_desc(c1 + bo, 16, 1024), ID_T, ks > 0);
+        if (MODE != MODE_FWD)
           mma_bf16_elect(t2_col(buf), make_desc(sRes + TILE_BYTES + ao, 16, 1024), make_desc(c2 + bo, 16, 1024), ID_T, ks > 0);
-        } else if (MODE == MODE_FWD) {
-          mma_bf16_elect(t1_col(buf), make_desc(sRes + ao, 16, 1024), make_desc(c1 + bo, 16, 1024), ID_T, ks > 0);
-        } else {
-          // A from tensor memory (dQ): k-step ks = head dimensions 16ks .. 16ks+15 = 8 columns of bf16 pairs
-          mma_bf16_ts_elect(t1_col(buf), qcol + 8u * ks, make_desc(c1 + bo, 16, 1024), ID_T, ks > 0);
-          mma_bf16_ts_elect(t2_col(buf), docol + 8u * ks, make_desc(c2 + bo, 16, 1024), ID_T, ks > 0);
-        }
       }
       if (release_stage || MODE == MODE_FWD) mma_commit_elect(empty_bar(s));   // forward: the K half is free after the score product
       mma_commit_elect(tfull_bar(buf));
@@ -309,20 +309,21 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
     if (MODE == MODE_FWD)
       for (; g < n_it && ok; ++g) ok = issue_T(g, true);
     const int g0 = g;
-    if (ok) ok = issue_T(g0, false);
+    // score products run NBUF - 1 sub-tiles ahead of the output products
+    for (int a = 0; a < NBUF - 1 && a < n_it && ok; ++a) ok = issue_T(g0 + a, false);
     for (int it = 0; it < n_it && ok; ++it) {
-      if (it + 1 < n_it && !(ok = issue_T(g0 + it + 1, false))) break;
+      if (it + NBUF - 1 < n_it && !(ok = issue_T(g0 + it + NBUF - 1, false))) break;
       // sub-tile `it` belongs to element-wise group it & 1; P is double-buffered (forward), the backward tiles live in
       // the score buffer of their sub-tile
-      const int eb = it & 1;
-      const uint32_t eph = ((uint32_t)it >> 1) & 1u;
+      const int eb = it % NBUF;
+      const uint32_t eph = ((uint32_t)it / NBUF) & 1u;
       if (!(ok = __all_sync(0xffffffffu, twait(15, efull_bar(eb), eph, p.err, tacc[4])))) break;
 #ifdef PCPB_ATC_TIMING
       tacc[14] += clock64() - *(volatile long long*)&ts_efull[eb];     // E published -> MMA warp awake
 #endif
       tc_fence_after();
       ATC_T0();
-      const int s = (MODE == MODE_FWD) ? (it % NST) : ((g0 + it) % NST), buf = (g0 + it) & 1;
+      const int s = (MODE == MODE_FWD) ? (it % NST) : ((g0 + it) % NST), buf = it % NBUF;   // g0 is a multiple of NBUF
       const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
       if (MODE == MODE_FWD) {
         if (!(ok = __all_sync(0xffffffffu, twait(13, vfull_bar(s), ((uint32_t)it / NST) & 1u, p.err, tacc[2])))) break;
@@ -348,7 +349,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
     // warps of a quarter: it picks the head dimensions / output columns a thread moves, and splits into the sub-tile
     // group (two groups) and, with 4 warps per quarter, the half of the 64 score columns a thread owns.
     const int q = warp & 3, row = q * 32 + lane, cg = (warp - 2) >> 2;
-    const int grp2 = (NCG == 4) ? (cg >> 1) : cg, half = (NCG == 4) ? (cg & 1) : 0;
+    const int grp2 = (NCG == 4) ? (cg >> 1) : cg, half = (NCG == 4) ? (cg & 1) : 0;   // NBUF groups
     constexpr int SHARE = 16 * PASSES;                       // score columns of a sub-tile a thread owns
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const int my = r0 + row;                                 // my query (FWD, DQ) or my key (DKV)
@@ -361,32 +362,15 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       inv2 = 1.f / (l_run + 2.f * PCPB_GUARD);
       mterm = Dr * (2.f * PCPB_GUARD) * inv2;
     }
-    if (MODE == MODE_DQ) {
-      // ---- my 32 head dimensions of my row of Q and of dO go to tensor memory as bf16 pairs (all loads first) ----
-      const uint32_t dst = lane_off + (uint32_t)(cg * 16);
-      uint32_t w[16], w2[16];
-      const uint4* src = reinterpret_cast<const uint4*>(p.qkn + (size_t)(row_base + my) * (p.d + p.dkv) + xq + cg * 32);
-      const uint4* src2 = reinterpret_cast<const uint4*>(p.dout + (size_t)(row_base + my) * p.d + xq + cg * 32);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) { const uint4 v = __ldg(src + j); w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w; }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) { const uint4 v = __ldg(src2 + j); w2[4 * j] = v.x; w2[4 * j + 1] = v.y; w2[4 * j + 2] = v.z; w2[4 * j + 3] = v.w; }
-      tmem_st16(qcol + dst, w);
-      tmem_st16(docol + dst, w2);
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(res_bar);
-    }
-    // Two groups of warps take the sub-tiles in turn (group = parity of the sub-tile = its score buffer), so the
+    // NBUF groups of warps take the sub-tiles in turn (group = sub-tile index mod NBUF = its score buffer), so the
     // tensor-memory and barrier latencies of one group are spent under the arithmetic of the other.  Within a group a
     // thread owns one row and SHARE (32 or 64) of the 64 columns, in passes of 16.
     int g = grp2;
     if (MODE == MODE_FWD) {
       // ---- sweep 1: row max and row sum of exp over this thread's share of the keys ----
-      for (; g < n_it; g += 2) {
-        const int buf = g & 1;
-        ok = __all_sync(0xffffffffu, twait(16, tfull_bar(buf), ((uint32_t)g >> 1) & 1u, p.err, tacc[5]));
+      for (; g < n_it; g += NBUF) {
+        const int buf = g % NBUF;
+        ok = __all_sync(0xffffffffu, twait(16, tfull_bar(buf), ((uint32_t)g / NBUF) & 1u, p.err, tacc[5]));
         if (!ok) break;
         tc_fence_after();
         // both passes' score columns are fetched at once (one exposed tensor-memory latency per sub-tile)
@@ -442,13 +426,13 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
         inv1 = 1.f / (l_run + PCPB_GUARD);
       }
     }
-    const int g0 = (MODE == MODE_FWD) ? n_it : 0;            // n_it is even: the buffer of sub-tile `it` is it & 1
+    const int g0 = (MODE == MODE_FWD) ? n_it : 0;            // a multiple of NBUF: the buffer of sub-tile `it` is it % NBUF
     const float mL_row = m_run * LOG2E;
-    for (int it = grp2; it < n_it && ok; it += 2) {
-      const int gg = g0 + it, buf = it & 1;
+    for (int it = grp2; it < n_it && ok; it += NBUF) {
+      const int gg = g0 + it, buf = it % NBUF;
       int cbase = 0;                                         // first column-side position of this thread's 32 columns
       // per-warp copy of the column statistics (no cross-warp barrier: a warp that gave up cannot block the others)
-      float* st = stat + ((warp - 2) * 2 + ((it >> 1) & 1)) * 192;
+      float* st = stat + ((warp - 2) * 2 + ((it / NBUF) & 1)) * 192;
       if (MODE == MODE_DKV) {
         const int hh = h + it / n_q;
         cbase = r0 + (it % n_q) * 64 + half * SHARE;
@@ -461,7 +445,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       } else {
         cbase = it * 64 + half * SHARE;
       }
-      ok = __all_sync(0xffffffffu, twait(17, tfull_bar(buf), ((uint32_t)gg >> 1) & 1u, p.err, tacc[6]));
+      ok = __all_sync(0xffffffffu, twait(17, tfull_bar(buf), ((uint32_t)gg / NBUF) & 1u, p.err, tacc[6]));
       if (!ok) break;
 #ifdef PCPB_ATC_TIMING
       tacc[15] += clock64() - *(volatile long long*)&ts_tcommit[buf];  // T commit issued -> element-wise warp awake
@@ -470,29 +454,32 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       ATC_T0();
       // Fetch the score (and dP) columns of both passes at once where the registers allow it (forward, dQ): one
       // exposed tensor-memory latency per sub-tile instead of one per load.
-      constexpr bool BATCH = (MODE != MODE_DKV);
-      uint32_t q1[PASSES][16], q2[2][16];
-      if (BATCH) {
-#pragma unroll
-        for (int pass = 0; pass < PASSES; ++pass) tmem_ld16_issue(t1_col(buf) + lane_off + (uint32_t)(half * SHARE + pass * 16), q1[pass]);
-        if (MODE == MODE_DQ) {
-          tmem_ld16_issue(t2_col(buf) + lane_off + (uint32_t)(half * 32), q2[0]);
-          tmem_ld16_issue(t2_col(buf) + lane_off + (uint32_t)(half * 32 + 16), q2[1]);
-        }
-#pragma unroll
-        for (int pass = 0; pass < PASSES; ++pass) tmem_ld_wait16(q1[pass]);
-        if (MODE == MODE_DQ) { tmem_ld_wait16(q2[0]); tmem_ld_wait16(q2[1]); }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar(buf));
-      }
+      // Forward and dQ fetch the score (and dP) columns of LPR passes with one tensor-memory wait (one exposed
+      // latency per round instead of one per load); the dK/dV kernel has no registers to spare and waits once per pass.
+      constexpr bool BATCH = (LPR > 0);
+      constexpr int NQ = BATCH ? LPR : 1;
+      uint32_t q1[NQ][16], q2[NQ][16];
 #pragma unroll
       for (int pass = 0; pass < PASSES; ++pass) {
+        if (BATCH && pass % NQ == 0) {
+#pragma unroll
+          for (int k = 0; k < NQ; ++k) {
+            tmem_ld16_issue(t1_col(buf) + lane_off + (uint32_t)(half * SHARE + (pass + k) * 16), q1[k]);
+            if (MODE == MODE_DQ) tmem_ld16_issue(t2_col(buf) + lane_off + (uint32_t)(half * SHARE + (pass + k) * 16), q2[k]);
+          }
+#pragma unroll
+          for (int k = 0; k < NQ; ++k) { tmem_ld_wait16(q1[k]); if (MODE == MODE_DQ) tmem_ld_wait16(q2[k]); }
+          if (pass + NQ == PASSES) {                          // everything this thread needs is in registers
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(buf));
+          }
+        }
         const int ch = half * SHARE + pass * 16, c0 = cbase + pass * 16;
         // does the causal boundary cross this block of 32 rows x 16 columns?
         const bool diag = (MODE == MODE_DKV) ? (c0 < r0 + 128) : (c0 + 15 > r0);
-        uint32_t (&r1)[16] = q1[pass];
-        if (!BATCH) tmem_ld16(t1_col(buf) + lane_off + (uint32_t)ch, r1);
+        uint32_t (&r1)[16] = q1[pass % NQ];
+        if (!BATCH) tmem_ld16_issue(t1_col(buf) + lane_off + (uint32_t)ch, r1);     // waited for together with T2 below
         uint32_t ew[8], pw[8];
         if (MODE == MODE_FWD) {
 #pragma unroll
@@ -506,10 +493,11 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
             ew[j] = pack2(e0, e1);
           }
         } else {
-          uint32_t (&r2)[16] = q2[pass & 1];
+          uint32_t (&r2)[16] = q2[pass % NQ];
           if (!BATCH) {
-            tmem_ld16(t2_col(buf) + lane_off + (uint32_t)ch, r2);
-            if (pass == 1) {
+            tmem_ld16_issue(t2_col(buf) + lane_off + (uint32_t)ch, r2);
+            tmem_ld_wait16(r1); tmem_ld_wait16(r2);
+            if (pass == PASSES - 1) {
               tc_fence_before();
               __syncwarp();
               if (lane == 0) mbar_arrive(tempty_bar(buf));
@@ -575,9 +563,12 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
     if (ok) {
       tc_fence_after();
       const long long grow = (long long)row_base + my;
+      // 128 output columns over the NCG warps of a lane quarter: 32 each (4 warps) or 64 each for the first two
+      constexpr int PARTS = (NCG == 4) ? 1 : 2;
 #pragma unroll
-      for (int part = 0; part < 4 / NCG; ++part) {
-        const int oc = (cg * (4 / NCG) + part) * 32;
+      for (int part = 0; part < PARTS; ++part) {
+        const int oc = (cg * PARTS + part) * 32;
+        if (oc >= 128) break;
         if (MODE == MODE_FWD) {
           store_out_cols(out1 + lane_off + oc, p.o + grow * p.d + xq + oc);
         } else if (MODE == MODE_DQ) {
