@@ -60,6 +60,7 @@ struct AtcParams {
   bf16* o; float* mrow; float* lrow; const float* drow;
   bf16* dqkn; bf16* dqkv;
   int* err;
+  int n_items, bh_count;                       // backward kernels: work items (row tile x batch-head), batch-heads
 };
 
 template <int MODE> struct AtcCfg {
@@ -71,6 +72,10 @@ template <int MODE> struct AtcCfg {
   static constexpr int NCG = N_EW / 4;                       // warps per tensor-memory lane quarter
   static constexpr int PASSES = (NCG == 4) ? 2 : 4;          // 16-column passes of a thread over its share of a sub-tile
   // passes whose score columns are fetched from tensor memory with one wait (0: one wait per pass)
+  // The backward kernels are persistent: a CTA takes work items L = blockIdx.x + k * gridDim.x (row tiles sorted from
+  // long to short), and keeps its rings and score buffers running across items, so the prologue and the first score
+  // products of the next item overlap the last output products and the epilogue of the current one.
+  static constexpr bool PERSIST = (MODE != MODE_FWD);
   static constexpr int LPR = (MODE == MODE_FWD) ? 4 : (MODE == MODE_DQ) ? 2 : 0;
   static constexpr uint32_t TMEM_COLS = (MODE == MODE_FWD) ? 256u : 512u;
   static constexpr int NST = (MODE == MODE_FWD) ? PCPB_ATC_NST_FWD : (MODE == MODE_DQ) ? PCPB_ATC_NST_DQ : 3;   // ring stages
@@ -147,6 +152,8 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
   // output product has, so the two halves have their own full / empty barriers (full_bar / empty_bar serve K)
   auto vfull_bar = [&](int s) { return out_bar + 32u + 8u * s; };
   auto vempty_bar = [&](int s) { return out_bar + 32u + 8u * (NST + s); };
+  // persistent kernels: resident tiles free for the next item / output accumulators drained by the epilogue
+  const uint32_t res_free_bar = out_bar + 32u + 8u * (2 * NST), out_free_bar = res_free_bar + 8u;
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + Cfg::OFF_BAR + 8 * (2 * NST + 9) + 24);
 
   const int warp = uniform_warp_idx(), lane = threadIdx.x & 31;
@@ -158,23 +165,34 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
 #ifdef PCPB_ATC_TIMING
   const long long t_cta0 = clock64();
 #endif
-  // work of this CTA
-  int b, h, hk, r0, n_it, n_q = 0;
-  if (MODE == MODE_DKV) {
-    const int bhk = blockIdx.y;
-    b = bhk / p.Hkv; hk = bhk % p.Hkv; h = hk * grp;
-    r0 = blockIdx.x * 128;                                   // first key of this CTA
-    n_q = (p.T - r0) / 64;
-    n_it = n_q * grp;
-  } else {
-    const int bh = blockIdx.y;
-    b = bh / p.H; h = bh % p.H; hk = h / grp;
-    r0 = (gridDim.x - 1 - blockIdx.x) * 128;                 // first query of this CTA, long rows first
-    n_it = (r0 + 128) / 64;
-  }
-  const int total_g = (MODE == MODE_FWD) ? 2 * n_it : n_it;
-  const int row_base = b * p.T;                              // first row of this batch element in [B*T, width]
-  const int xq = h * HD, xk = p.d + hk * HD, xv = p.d + p.dkv + hk * HD;
+  // work items of this CTA
+  constexpr bool PERSIST = Cfg::PERSIST;
+  const int nt = p.T / 128;
+  const int item0 = PERSIST ? (int)blockIdx.x : 0, item_step = PERSIST ? (int)gridDim.x : 1;
+  const int n_items = PERSIST ? p.n_items : 1;
+  int b, h, hk, r0, n_it, n_q = 0, total_g, row_base, xq, xk, xv;
+  auto decode = [&](int L) {
+    if (MODE == MODE_DKV) {
+      const int x = L / p.bh_count, bhk = L % p.bh_count;    // x ascending = more queries = longer
+      b = bhk / p.Hkv; hk = bhk % p.Hkv; h = hk * grp;
+      r0 = x * 128;                                          // first key of this item
+      n_q = (p.T - r0) / 64;
+      n_it = n_q * grp;
+    } else if (MODE == MODE_DQ) {
+      const int x = L / p.bh_count, bh = L % p.bh_count;
+      b = bh / p.H; h = bh % p.H; hk = h / grp;
+      r0 = (nt - 1 - x) * 128;                               // first query of this item, long rows first
+      n_it = (r0 + 128) / 64;
+    } else {
+      const int bh = blockIdx.y;
+      b = bh / p.H; h = bh % p.H; hk = h / grp;
+      r0 = (gridDim.x - 1 - blockIdx.x) * 128;               // first query of this CTA, long rows first
+      n_it = (r0 + 128) / 64;
+    }
+    total_g = (MODE == MODE_FWD) ? 2 * n_it : n_it;
+    row_base = b * p.T;                                      // first row of this batch element in [B*T, width]
+    xq = h * HD; xk = p.d + hk * HD; xv = p.d + p.dkv + hk * HD;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NST; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -183,6 +201,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       for (int s = 0; s < NST; ++s) { mbar_init(vfull_bar(s), 1); mbar_init(vempty_bar(s), 1); }
     // the row-side tiles arrive by TMA (dK/dV) or are written to tensor memory by the element-wise warps
     mbar_init(out_bar, 1); mbar_init(res_bar, 1); mbar_init(comb_bar, N_EW);
+    mbar_init(res_free_bar, 1); mbar_init(out_free_bar, N_EW);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -211,55 +230,63 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       tma_load_2d_elect(dst, m, res_bar, x, y);              tma_load_2d_elect(dst + 8192, m, res_bar, x, y + 64);
       tma_load_2d_elect(dst + 16384, m, res_bar, x + 64, y); tma_load_2d_elect(dst + 24576, m, res_bar, x + 64, y + 64);
     };
-    if (MODE == MODE_DKV) {
-      mbar_expect_tx_elect(res_bar, Cfg::N_RES * TILE_BYTES);
-      load_tile128(sRes, &tm_qkn, xk, row_base + r0);
-      load_tile128(sRes + TILE_BYTES, &tm_qkv, xv, row_base + r0);
-    }
-    if (MODE == MODE_FWD) {
-      mbar_expect_tx_elect(res_bar, Cfg::N_RES * TILE_BYTES);
-      load_tile128(sRes, &tm_qkn, xq, row_base + r0);
-    }
-    if (MODE == MODE_DQ) {
-      mbar_expect_tx_elect(res_bar, Cfg::N_RES * TILE_BYTES);
-      load_tile128(sRes, &tm_qkn, xq, row_base + r0);
-      load_tile128(sRes + TILE_BYTES, &tm_do, xq, row_base + r0);
-    }
     bool ok = true;
-    int g = 0;
-    for (; g < total_g; ++g) {
-      const int s = g % NST;
-      ok = __all_sync(0xffffffffu, twait(11, empty_bar(s), (((uint32_t)g / NST) & 1u) ^ 1u, p.err, tacc[0]));
-      if (!ok) break;
-      const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
-      if (MODE == MODE_FWD) {
-        // K of key sub-tile g % n_it (both sweeps); V of sub-tile it = g - n_it (second sweep) through its own barriers
-        const int y = row_base + (g % n_it) * 64;
-        mbar_expect_tx_elect(full_bar(s), SUB_BYTES);
-        tma_load_2d_elect(c1, &tm_qkn, full_bar(s), xk, y); tma_load_2d_elect(c1 + 8192, &tm_qkn, full_bar(s), xk + 64, y);
-        if (g >= n_it) {
-          const int it = g - n_it, sv = it % NST;
-          ok = __all_sync(0xffffffffu, twait(11, vempty_bar(sv), (((uint32_t)it / NST) & 1u) ^ 1u, p.err, tacc[0]));
-          if (!ok) { ++g; break; }
-          const uint32_t cv = sRing + sv * STAGE_BYTES + SUB_BYTES;
-          mbar_expect_tx_elect(vfull_bar(sv), SUB_BYTES);
-          tma_load_2d_elect(cv, &tm_qkv, vfull_bar(sv), xv, y); tma_load_2d_elect(cv + 8192, &tm_qkv, vfull_bar(sv), xv + 64, y);
-        }
-      } else if (MODE == MODE_DKV) {
-        mbar_expect_tx_elect(full_bar(s), STAGE_BYTES);
-        const int hh = h + g / n_q, y = row_base + r0 + (g % n_q) * 64;
-        tma_load_2d_elect(c1, &tm_qkn, full_bar(s), hh * HD, y); tma_load_2d_elect(c1 + 8192, &tm_qkn, full_bar(s), hh * HD + 64, y);
-        tma_load_2d_elect(c2, &tm_do, full_bar(s), hh * HD, y);  tma_load_2d_elect(c2 + 8192, &tm_do, full_bar(s), hh * HD + 64, y);
-      } else {
-        mbar_expect_tx_elect(full_bar(s), STAGE_BYTES);
-        const int y = row_base + g * 64;
-        tma_load_2d_elect(c1, &tm_qkn, full_bar(s), xk, y); tma_load_2d_elect(c1 + 8192, &tm_qkn, full_bar(s), xk + 64, y);
-        tma_load_2d_elect(c2, &tm_qkv, full_bar(s), xv, y); tma_load_2d_elect(c2 + 8192, &tm_qkv, full_bar(s), xv + 64, y);
+    int gb = 0, g = 0, k = 0;                                // ring positions run on gb + g across the items
+    for (int L = item0; L < n_items; ++k, L += item_step) {
+      decode(L);
+      if (PERSIST && k > 0) {
+        // the last score product of the previous item has read the resident tiles
+        ok = __all_sync(0xffffffffu, twait(11, res_free_bar, (uint32_t)(k - 1) & 1u, p.err, tacc[0]));
+        if (!ok) break;
       }
+      mbar_expect_tx_elect(res_bar, Cfg::N_RES * TILE_BYTES);
+      if (MODE == MODE_DKV) {
+        load_tile128(sRes, &tm_qkn, xk, row_base + r0);
+        load_tile128(sRes + TILE_BYTES, &tm_qkv, xv, row_base + r0);
+      }
+      if (MODE == MODE_FWD) load_tile128(sRes, &tm_qkn, xq, row_base + r0);
+      if (MODE == MODE_DQ) {
+        load_tile128(sRes, &tm_qkn, xq, row_base + r0);
+        load_tile128(sRes + TILE_BYTES, &tm_do, xq, row_base + r0);
+      }
+      for (g = 0; g < total_g; ++g) {
+        const int G = gb + g, s = G % NST;
+        ok = __all_sync(0xffffffffu, twait(11, empty_bar(s), (((uint32_t)G / NST) & 1u) ^ 1u, p.err, tacc[0]));
+        if (!ok) break;
+        const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
+        if (MODE == MODE_FWD) {
+          // K of key sub-tile g % n_it (both sweeps); V of sub-tile it = g - n_it (second sweep) through its own barriers
+          const int y = row_base + (g % n_it) * 64;
+          mbar_expect_tx_elect(full_bar(s), SUB_BYTES);
+          tma_load_2d_elect(c1, &tm_qkn, full_bar(s), xk, y); tma_load_2d_elect(c1 + 8192, &tm_qkn, full_bar(s), xk + 64, y);
+          if (g >= n_it) {
+            const int it = g - n_it, sv = it % NST;
+            ok = __all_sync(0xffffffffu, twait(11, vempty_bar(sv), (((uint32_t)it / NST) & 1u) ^ 1u, p.err, tacc[0]));
+            if (!ok) { ++g; break; }
+            const uint32_t cv = sRing + sv * STAGE_BYTES + SUB_BYTES;
+            mbar_expect_tx_elect(vfull_bar(sv), SUB_BYTES);
+            tma_load_2d_elect(cv, &tm_qkv, vfull_bar(sv), xv, y); tma_load_2d_elect(cv + 8192, &tm_qkv, vfull_bar(sv), xv + 64, y);
+          }
+        } else if (MODE == MODE_DKV) {
+          mbar_expect_tx_elect(full_bar(s), STAGE_BYTES);
+          const int hh = h + g / n_q, y = row_base + r0 + (g % n_q) * 64;
+          tma_load_2d_elect(c1, &tm_qkn, full_bar(s), hh * HD, y); tma_load_2d_elect(c1 + 8192, &tm_qkn, full_bar(s), hh * HD + 64, y);
+          tma_load_2d_elect(c2, &tm_do, full_bar(s), hh * HD, y);  tma_load_2d_elect(c2 + 8192, &tm_do, full_bar(s), hh * HD + 64, y);
+        } else {
+          mbar_expect_tx_elect(full_bar(s), STAGE_BYTES);
+          const int y = row_base + g * 64;
+          tma_load_2d_elect(c1, &tm_qkn, full_bar(s), xk, y); tma_load_2d_elect(c1 + 8192, &tm_qkn, full_bar(s), xk + 64, y);
+          tma_load_2d_elect(c2, &tm_qkv, full_bar(s), xv, y); tma_load_2d_elect(c2 + 8192, &tm_qkv, full_bar(s), xv + 64, y);
+        }
+      }
+      if (!ok) break;
+      gb += total_g;
+      g = 0;
     }
     if (!ok) {
-      // gave up after g K (or K+V) loads were armed: wait (bounded) for the copies still in flight before the CTA may exit
-      for (int j = (g > NST ? g - NST : 0); j < g; ++j) {
+      // gave up after gb + g ring loads were armed: wait (bounded) for the copies still in flight before the CTA may exit
+      const int tot = gb + g;
+      for (int j = (tot > NST ? tot - NST : 0); j < tot; ++j) {
         const uint32_t ph = ((uint32_t)j / NST) & 1u;
         for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(full_bar(j % NST), ph)) break;
       }
@@ -270,7 +297,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
           for (uint32_t w = 0; w < (1u << 16); ++w) if (mbar_try(vfull_bar(j % NST), ph)) break;
         }
       }
-      for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(res_bar, 0)) break;
+      for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(res_bar, (uint32_t)k & 1u)) break;
     }
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
@@ -278,16 +305,17 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
     // score products: M=128, N=64, A and B K-major; output products: M=128, N=128, A K-major, B MN-major
     constexpr uint32_t ID_T = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     constexpr uint32_t ID_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-    bool ok = __all_sync(0xffffffffu, twait(12, res_bar, 0, p.err, tacc[1]));
+    bool ok = true;
+    int gb = 0;                                              // sub-tiles of the items done so far (a multiple of NBUF)
+    // g: position in the item (selects nothing here but the last-tile test); gb + g: ring / buffer position
     auto issue_T = [&](int g, bool release_stage) -> bool {
-      const int s = g % NST, buf = g % NBUF;
-      if (!__all_sync(0xffffffffu, twait(13, full_bar(s), ((uint32_t)g / NST) & 1u, p.err, tacc[2]))) return false;
-      if (!__all_sync(0xffffffffu, twait(14, tempty_bar(buf), (((uint32_t)g / NBUF) & 1u) ^ 1u, p.err, tacc[3]))) return false;
+      const int G = gb + g, s = G % NST, buf = G % NBUF;
+      if (!__all_sync(0xffffffffu, twait(13, full_bar(s), ((uint32_t)G / NST) & 1u, p.err, tacc[2]))) return false;
+      if (!__all_sync(0xffffffffu, twait(14, tempty_bar(buf), (((uint32_t)G / NBUF) & 1u) ^ 1u, p.err, tacc[3]))) return false;
       tc_fence_after();
       ATC_T0();
       const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
-      // Consecutive MMAs into one accumulator wait for each other (about 125 cycles each, whatever N is), so the two
-      // independent products of the backward kernels are issued alternately: one accumulator chain hides the other.
+      // The two independent products of the backward kernels are issued alternately.
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         const uint32_t ao = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
@@ -299,50 +327,63 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       }
       if (release_stage || MODE == MODE_FWD) mma_commit_elect(empty_bar(s));   // forward: the K half is free after the score product
       mma_commit_elect(tfull_bar(buf));
+      // persistent kernels: after the last score product of an item the resident tiles may be replaced
+      if (PERSIST && g == n_it - 1) mma_commit_elect(res_free_bar);
 #ifdef PCPB_ATC_TIMING
       if (lane == 0) ts_tcommit[buf] = clock64();
 #endif
       ATC_T1(10);
       return true;
     };
-    int g = 0;
-    if (MODE == MODE_FWD)
-      for (; g < n_it && ok; ++g) ok = issue_T(g, true);
-    const int g0 = g;
-    // score products run NBUF - 1 sub-tiles ahead of the output products
-    for (int a = 0; a < NBUF - 1 && a < n_it && ok; ++a) ok = issue_T(g0 + a, false);
-    for (int it = 0; it < n_it && ok; ++it) {
-      if (it + NBUF - 1 < n_it && !(ok = issue_T(g0 + it + NBUF - 1, false))) break;
-      // sub-tile `it` belongs to element-wise group it & 1; P is double-buffered (forward), the backward tiles live in
-      // the score buffer of their sub-tile
-      const int eb = it % NBUF;
-      const uint32_t eph = ((uint32_t)it / NBUF) & 1u;
-      if (!(ok = __all_sync(0xffffffffu, twait(15, efull_bar(eb), eph, p.err, tacc[4])))) break;
+    int k = 0;
+    for (int L = item0; L < n_items && ok; ++k, L += item_step) {
+      decode(L);
+      if (!(ok = __all_sync(0xffffffffu, twait(12, res_bar, (uint32_t)k & 1u, p.err, tacc[1])))) break;
+      int g = 0;
+      if (MODE == MODE_FWD)
+        for (; g < n_it && ok; ++g) ok = issue_T(g, true);
+      const int g0 = g;
+      // score products run NBUF - 1 sub-tiles ahead of the output products
+      for (int a = 0; a < NBUF - 1 && a < n_it && ok; ++a) ok = issue_T(g0 + a, false);
+      for (int it = 0; it < n_it && ok; ++it) {
+        if (it + NBUF - 1 < n_it && !(ok = issue_T(g0 + it + NBUF - 1, false))) break;
+        // sub-tile `it` belongs to the element-wise group of its score buffer; the result tile lives in that buffer
+        // G: ring / score-buffer position (counts the first sweep of the forward kernel too); result tiles are only
+        // published in the main sweep, so their barrier counts gb + it
+        const int G = gb + g0 + it, eb = G % NBUF;
+        const uint32_t eph = ((uint32_t)(gb + it) / NBUF) & 1u;
+        if (!(ok = __all_sync(0xffffffffu, twait(15, efull_bar(eb), eph, p.err, tacc[4])))) break;
 #ifdef PCPB_ATC_TIMING
-      tacc[14] += clock64() - *(volatile long long*)&ts_efull[eb];     // E published -> MMA warp awake
+        tacc[14] += clock64() - *(volatile long long*)&ts_efull[eb];     // E published -> MMA warp awake
 #endif
-      tc_fence_after();
-      ATC_T0();
-      const int s = (MODE == MODE_FWD) ? (it % NST) : ((g0 + it) % NST), buf = it % NBUF;   // g0 is a multiple of NBUF
-      const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
-      if (MODE == MODE_FWD) {
-        if (!(ok = __all_sync(0xffffffffu, twait(13, vfull_bar(s), ((uint32_t)it / NST) & 1u, p.err, tacc[2])))) break;
-        tc_fence_after();
-      }
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
-        if (MODE == MODE_FWD) mma_bf16_ts_elect(out1, t1_col(buf) + 16u * ks, make_desc(c2 + ks * 2048u, 8192, 1024), ID_O, acc);
-        if (MODE == MODE_DQ) mma_bf16_ts_elect(out1, t1_col(buf) + 16u * ks, make_desc(c1 + ks * 2048u, 8192, 1024), ID_O, acc);
-        if (MODE == MODE_DKV) {
-          mma_bf16_ts_elect(out1, t1_col(buf) + 16u * ks, make_desc(c2 + ks * 2048u, 8192, 1024), ID_O, acc);
-          mma_bf16_ts_elect(out2, t2_col(buf) + 16u * ks, make_desc(c1 + ks * 2048u, 8192, 1024), ID_O, acc);
+        if (PERSIST && it == 0 && k > 0) {
+          // the epilogue of the previous item must have read the output accumulators
+          if (!(ok = __all_sync(0xffffffffu, twait(15, out_free_bar, (uint32_t)(k - 1) & 1u, p.err, tacc[4])))) break;
         }
+        tc_fence_after();
+        ATC_T0();
+        const int s = (MODE == MODE_FWD) ? (it % NST) : (G % NST), buf = eb;
+        const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
+        if (MODE == MODE_FWD) {
+          if (!(ok = __all_sync(0xffffffffu, twait(13, vfull_bar(s), ((uint32_t)it / NST) & 1u, p.err, tacc[2])))) break;
+          tc_fence_after();
+        }
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
+          if (MODE == MODE_FWD) mma_bf16_ts_elect(out1, t1_col(buf) + 16u * ks, make_desc(c2 + ks * 2048u, 8192, 1024), ID_O, acc);
+          if (MODE == MODE_DQ) mma_bf16_ts_elect(out1, t1_col(buf) + 16u * ks, make_desc(c1 + ks * 2048u, 8192, 1024), ID_O, acc);
+          if (MODE == MODE_DKV) {
+            mma_bf16_ts_elect(out1, t1_col(buf) + 16u * ks, make_desc(c2 + ks * 2048u, 8192, 1024), ID_O, acc);
+            mma_bf16_ts_elect(out2, t2_col(buf) + 16u * ks, make_desc(c1 + ks * 2048u, 8192, 1024), ID_O, acc);
+          }
+        }
+        mma_commit_elect(MODE == MODE_FWD ? vempty_bar(s) : empty_bar(s));
+        ATC_T1(11);
       }
-      mma_commit_elect(MODE == MODE_FWD ? vempty_bar(s) : empty_bar(s));
-      ATC_T1(11);
+      if (ok) mma_commit_elect(out_bar);
+      gb += total_g;
     }
-    if (ok) mma_commit_elect(out_bar);
   } else {
     // =========================== element-wise warps ===========================
     // NCG warps per tensor-memory lane quarter (4 in the backward kernels, 2 in the forward kernel).  cg numbers the
@@ -352,9 +393,12 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
     const int grp2 = (NCG == 4) ? (cg >> 1) : cg, half = (NCG == 4) ? (cg & 1) : 0;   // NBUF groups
     constexpr int SHARE = 16 * PASSES;                       // score columns of a sub-tile a thread owns
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
-    const int my = r0 + row;                                 // my query (FWD, DQ) or my key (DKV)
     const uint32_t scale2 = pack2(p.scale, p.scale);
     bool ok = true;
+    int gb = 0, k = 0;                                       // sub-tiles of the items done so far (even), item count
+    for (int L = item0; L < n_items && ok; ++k, L += item_step) {
+    decode(L);
+    const int my = r0 + row;                                 // my query (FWD, DQ) or my key (DKV)
     float m_run = -INFINITY, l_run = 0.f, inv1 = 0.f, inv2 = 0.f, Dr = 0.f, mterm = 0.f;
     if (MODE == MODE_DQ) {
       const long long idx = ((long long)b * p.H + h) * p.T + my;
@@ -445,7 +489,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       } else {
         cbase = it * 64 + half * SHARE;
       }
-      ok = __all_sync(0xffffffffu, twait(17, tfull_bar(buf), ((uint32_t)gg / NBUF) & 1u, p.err, tacc[6]));
+      ok = __all_sync(0xffffffffu, twait(17, tfull_bar(buf), ((uint32_t)(gb + gg) / NBUF) & 1u, p.err, tacc[6]));
       if (!ok) break;
 #ifdef PCPB_ATC_TIMING
       tacc[15] += clock64() - *(volatile long long*)&ts_tcommit[buf];  // T commit issued -> element-wise warp awake
@@ -559,7 +603,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       ATC_T1(12);
     }
     // ---- outputs: each warp stores 128 / NCG of the 128 output columns of its rows ----
-    if (ok) ok = __all_sync(0xffffffffu, twait(19, out_bar, 0, p.err, tacc[8]));
+    if (ok) ok = __all_sync(0xffffffffu, twait(19, out_bar, (uint32_t)k & 1u, p.err, tacc[8]));
     if (ok) {
       tc_fence_after();
       const long long grow = (long long)row_base + my;
@@ -582,7 +626,15 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
         const long long idx = ((long long)b * p.H + h) * p.T + my;
         p.mrow[idx] = m_run; p.lrow[idx] = l_run;
       }
+      if (PERSIST) {
+        // the accumulators are in registers / stored: the first output product of the next item may overwrite them
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(out_free_bar);
+      }
     }
+    gb += total_g;
+    }                                                        // items
   }
 #ifdef PCPB_ATC_TIMING
   if (lane == 0) {
@@ -649,7 +701,7 @@ bool fill(const FlashArgs& a, int* err, AtcParams* p, CUtensorMap* mq, CUtensorM
   p->B = a.B; p->T = a.T; p->H = a.H; p->Hkv = a.Hkv; p->scale = a.scale; p->d = d; p->dkv = dkv;
   p->qkn = (const bf16*)a.qkn; p->dout = (const bf16*)a.dout;
   p->o = (bf16*)a.o; p->mrow = a.mrow; p->lrow = a.lrow; p->drow = a.drow; p->dqkn = (bf16*)a.dqkn; p->dqkv = (bf16*)a.dqkv;
-  p->err = err;
+  p->err = err; p->n_items = 1; p->bh_count = 1;
   bool ok = make_map(mq, a.qkn, (uint64_t)(d + dkv), M, (uint64_t)(d + dkv), 64) &&
             make_map(mv, a.qkv, (uint64_t)(d + 2 * dkv), M, (uint64_t)(d + 2 * dkv), 64);
   if (need_do) ok = ok && make_map(md, a.dout, (uint64_t)d, M, (uint64_t)d, 64);
@@ -688,9 +740,15 @@ cudaError_t launch_attn_tc_bwd(cudaStream_t st, const FlashArgs& a, int* err_wor
                                                                      a.T, a.H);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  e = launch_mode<MODE_DKV>(st, mq, mv, md, p, dim3(a.T / 128, a.B * a.Hkv));
+  // persistent backward kernels: one CTA per SM walks the work items, long row tiles first
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  p.bh_count = a.B * a.Hkv; p.n_items = (a.T / 128) * p.bh_count;
+  e = launch_mode<MODE_DKV>(st, mq, mv, md, p, dim3(p.n_items < sms ? p.n_items : sms));
   if (e != cudaSuccess) return e;
-  return launch_mode<MODE_DQ>(st, mq, mv, md, p, dim3(a.T / 128, a.B * a.H));
+  p.bh_count = a.B * a.H; p.n_items = (a.T / 128) * p.bh_count;
+  return launch_mode<MODE_DQ>(st, mq, mv, md, p, dim3(p.n_items < sms ? p.n_items : sms));
 }
 
 }  // namespace pcpb

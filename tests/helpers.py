@@ -12,6 +12,9 @@ GQA_F32 = dict(vocab=97, d_model=64, n_layer=2, n_head=4, n_kv_head=2, seq_len=2
 SMALL_BF16 = dict(vocab=65, d_model=64, n_layer=2, n_head=4, n_kv_head=4, seq_len=32, batch=8, dtype="bf16")
 HD128_BF16 = dict(vocab=512, d_model=256, n_layer=2, n_head=2, n_kv_head=2, seq_len=128, batch=2, dtype="bf16")
 HD128_GQA_BF16 = dict(vocab=512, d_model=512, n_layer=1, n_head=4, n_kv_head=2, seq_len=256, batch=1, dtype="bf16")
+# 160 (batch x head x row tile) work items: more than the 148 SMs, so the persistent attention kernels take several
+# items per CTA (resident-tile reload and accumulator hand-over between items)
+HD128_MANY_BF16 = dict(vocab=512, d_model=256, n_layer=1, n_head=2, n_kv_head=2, seq_len=256, batch=40, dtype="bf16")
 HD128_F32 = dict(vocab=512, d_model=256, n_layer=1, n_head=2, n_kv_head=1, seq_len=64, batch=2, dtype="f32")
 
 

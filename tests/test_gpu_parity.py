@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import (GPT_ODD_F32, GPT_SMALL_BF16, GPT_SMALL_F32, GQA_F32, HD128_BF16, HD128_F32, HD128_GQA_BF16, make_model, SMALL_BF16, SMALL_F32, bf16_bits_to_f32, f32_to_bf16_trunc_bits,
+from helpers import (GPT_ODD_F32, GPT_SMALL_BF16, GPT_SMALL_F32, GQA_F32, HD128_BF16, HD128_F32, HD128_GQA_BF16, HD128_MANY_BF16, make_model, SMALL_BF16, SMALL_F32, bf16_bits_to_f32, f32_to_bf16_trunc_bits,
                      flat, rel_err, seeded_params, split, tokens_for)
 from oracle.loader import FifoU16
 from oracle.optim import AdamConf, NesterovConf, adamw_update
@@ -64,7 +64,7 @@ def test_compute_gradients_matches_oracle(cfgd, tol):
         assert l2 <= 4e-2 and worst <= 0.25, (l2, worst)
 
 
-@pytest.mark.parametrize("cfgd", [HD128_BF16, HD128_GQA_BF16])
+@pytest.mark.parametrize("cfgd", [HD128_BF16, HD128_GQA_BF16, HD128_MANY_BF16])
 def test_attention_paths_agree(cfgd, monkeypatch):
     """The three attention implementations (tcgen05 / tensor memory, mma.sync, generic) against the oracle and against
     each other on a head_dim-128 bf16 model, GQA included."""
