@@ -14,10 +14,12 @@
 // it came from (tcgen05.st), where the next MMA finds it as its A operand (TS form).  Score tiles are double-buffered
 // in tensor memory and two groups of element-wise warps take the sub-tiles in turn, so the MMAs of sub-tile i+1
 // overlap the arithmetic of sub-tile i.  The backward kernels use 16 element-wise warps and the whole SM (512
-// tensor-memory columns); the forward kernel uses 8, half of the
-// tensor memory and 100 KB of shared memory, and runs two CTAs per SM: four sub-tiles in flight per SM, and one
-// CTA's prologue / epilogue under the other's main loop.  What limits these kernels is the latency of the hand-offs
-// MMA -> element-wise -> MMA (commit, wake-up, tcgen05.ld / st), not the tensor pipe, hence the concurrency.
+// tensor-memory columns); the forward kernel uses 8, half of the tensor memory and 100 KB of shared memory, and runs
+// two CTAs per SM (four sub-tiles in flight per SM).  All three are persistent: a CTA walks its work items (row tile
+// x batch x head, long row tiles first) and keeps rings, score buffers and barrier phases running across them, so
+// the resident-tile load and the first score products of the next item overlap the last output products and the
+// epilogue of the current one.  What limits these kernels is the latency of the hand-offs MMA -> element-wise -> MMA
+// (commit, wake-up, tcgen05.ld / st) and the fill / drain of that chain, not the tensor pipe, hence the concurrency.
 // The element-wise arithmetic works on bf16 pairs: one cvt.rn.bf16x2 and one mul.bf16x2 reproduce the two roundings
 // of a score, one more pair of them the rounding of dS.
 //
@@ -72,17 +74,17 @@ template <int MODE> struct AtcCfg {
   static constexpr int NCG = N_EW / 4;                       // warps per tensor-memory lane quarter
   static constexpr int PASSES = (NCG == 4) ? 2 : 4;          // 16-column passes of a thread over its share of a sub-tile
   // passes whose score columns are fetched from tensor memory with one wait (0: one wait per pass)
-  // The backward kernels are persistent: a CTA takes work items L = blockIdx.x + k * gridDim.x (row tiles sorted from
+  // The kernels are persistent: a CTA takes work items L = blockIdx.x + k * gridDim.x (row tiles sorted from
   // long to short), and keeps its rings and score buffers running across items, so the prologue and the first score
   // products of the next item overlap the last output products and the epilogue of the current one.
-  static constexpr bool PERSIST = (MODE != MODE_FWD);
+  static constexpr bool PERSIST = true;
   static constexpr int LPR = (MODE == MODE_FWD) ? 4 : (MODE == MODE_DQ) ? 2 : 0;
   static constexpr uint32_t TMEM_COLS = (MODE == MODE_FWD) ? 256u : 512u;
   static constexpr int NST = (MODE == MODE_FWD) ? PCPB_ATC_NST_FWD : (MODE == MODE_DQ) ? PCPB_ATC_NST_DQ : 3;   // ring stages
   // resident row-side tiles in shared memory: K and V (dK/dV kernel), Q and dO (dQ kernel), Q (forward kernel)
   static constexpr int N_RES = (MODE == MODE_FWD) ? 1 : 2;
   // DKV: per warp, double-buffered, six statistics of 32 columns; FWD: exchange of the four partial (max, sum) of a row
-  static constexpr int STAT_BYTES = (MODE == MODE_DKV) ? N_EW * 2 * 192 * 4 : (MODE == MODE_FWD) ? NCG * 128 * 2 * 4 : 16;
+  static constexpr int STAT_BYTES = (MODE == MODE_DKV) ? N_EW * 2 * 192 * 4 : (MODE == MODE_FWD) ? 2 * NCG * 128 * 2 * 4 : 16;
   static constexpr int OFF_RING = N_RES * TILE_BYTES;
   static constexpr int OFF_STAT = OFF_RING + NST * STAGE_BYTES;
   static constexpr int OFF_BAR = OFF_STAT + STAT_BYTES;
@@ -141,7 +143,8 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t sRes = base, sRing = base + Cfg::OFF_RING, sBar = base + Cfg::OFF_BAR;
-  float* stat = reinterpret_cast<float*>(gen + Cfg::OFF_STAT);
+  float* const stat_base = reinterpret_cast<float*>(gen + Cfg::OFF_STAT);
+  float* stat = stat_base;
   auto full_bar = [&](int s) { return sBar + 8u * s; };
   auto empty_bar = [&](int s) { return sBar + 8u * (NST + s); };
   auto tfull_bar = [&](int b) { return sBar + 8u * (2 * NST + b); };
@@ -178,7 +181,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       r0 = x * 128;                                          // first key of this item
       n_q = (p.T - r0) / 64;
       n_it = n_q * grp;
-    } else if (MODE == MODE_DQ) {
+    } else if (PERSIST) {
       const int x = L / p.bh_count, bh = L % p.bh_count;
       b = bh / p.H; h = bh % p.H; hk = h / grp;
       r0 = (nt - 1 - x) * 128;                               // first query of this item, long rows first
@@ -231,7 +234,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       tma_load_2d_elect(dst + 16384, m, res_bar, x + 64, y); tma_load_2d_elect(dst + 24576, m, res_bar, x + 64, y + 64);
     };
     bool ok = true;
-    int gb = 0, g = 0, k = 0;                                // ring positions run on gb + g across the items
+    int gb = 0, ge = 0, g = 0, k = 0;                        // ring positions run on gb + g (forward V ring: ge + it) across items
     for (int L = item0; L < n_items; ++k, L += item_step) {
       decode(L);
       if (PERSIST && k > 0) {
@@ -260,8 +263,8 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
           mbar_expect_tx_elect(full_bar(s), SUB_BYTES);
           tma_load_2d_elect(c1, &tm_qkn, full_bar(s), xk, y); tma_load_2d_elect(c1 + 8192, &tm_qkn, full_bar(s), xk + 64, y);
           if (g >= n_it) {
-            const int it = g - n_it, sv = it % NST;
-            ok = __all_sync(0xffffffffu, twait(11, vempty_bar(sv), (((uint32_t)it / NST) & 1u) ^ 1u, p.err, tacc[0]));
+            const int it = g - n_it, sv = (ge + it) % NST;
+            ok = __all_sync(0xffffffffu, twait(11, vempty_bar(sv), (((uint32_t)(ge + it) / NST) & 1u) ^ 1u, p.err, tacc[0]));
             if (!ok) { ++g; break; }
             const uint32_t cv = sRing + sv * STAGE_BYTES + SUB_BYTES;
             mbar_expect_tx_elect(vfull_bar(sv), SUB_BYTES);
@@ -280,7 +283,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
         }
       }
       if (!ok) break;
-      gb += total_g;
+      gb += total_g; ge += n_it;
       g = 0;
     }
     if (!ok) {
@@ -291,7 +294,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
         for (uint32_t w = 0; w < (1u << 20); ++w) if (mbar_try(full_bar(j % NST), ph)) break;
       }
       if (MODE == MODE_FWD) {
-        const int nv = g > n_it ? g - n_it : 0;                  // V loads armed so far (at most; the last may not be)
+        const int nv = ge + (g > n_it ? g - n_it : 0);           // V loads armed so far (at most; the last may not be)
         for (int j = (nv > NST ? nv - NST : 0); j < nv; ++j) {
           const uint32_t ph = ((uint32_t)j / NST) & 1u;
           for (uint32_t w = 0; w < (1u << 16); ++w) if (mbar_try(vfull_bar(j % NST), ph)) break;
@@ -306,7 +309,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
     constexpr uint32_t ID_T = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     constexpr uint32_t ID_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     bool ok = true;
-    int gb = 0;                                              // sub-tiles of the items done so far (a multiple of NBUF)
+    int gb = 0, ge = 0;                                      // score products / result tiles of the items done so far (even)
     // g: position in the item (selects nothing here but the last-tile test); gb + g: ring / buffer position
     auto issue_T = [&](int g, bool release_stage) -> bool {
       const int G = gb + g, s = G % NST, buf = G % NBUF;
@@ -328,7 +331,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       if (release_stage || MODE == MODE_FWD) mma_commit_elect(empty_bar(s));   // forward: the K half is free after the score product
       mma_commit_elect(tfull_bar(buf));
       // persistent kernels: after the last score product of an item the resident tiles may be replaced
-      if (PERSIST && g == n_it - 1) mma_commit_elect(res_free_bar);
+      if (PERSIST && g == total_g - 1) mma_commit_elect(res_free_bar);
 #ifdef PCPB_ATC_TIMING
       if (lane == 0) ts_tcommit[buf] = clock64();
 #endif
@@ -349,9 +352,9 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
         if (it + NBUF - 1 < n_it && !(ok = issue_T(g0 + it + NBUF - 1, false))) break;
         // sub-tile `it` belongs to the element-wise group of its score buffer; the result tile lives in that buffer
         // G: ring / score-buffer position (counts the first sweep of the forward kernel too); result tiles are only
-        // published in the main sweep, so their barrier counts gb + it
+        // published in the main sweep, so their barrier (and the forward kernel's V ring) counts ge + it
         const int G = gb + g0 + it, eb = G % NBUF;
-        const uint32_t eph = ((uint32_t)(gb + it) / NBUF) & 1u;
+        const uint32_t eph = ((uint32_t)(ge + it) / NBUF) & 1u;
         if (!(ok = __all_sync(0xffffffffu, twait(15, efull_bar(eb), eph, p.err, tacc[4])))) break;
 #ifdef PCPB_ATC_TIMING
         tacc[14] += clock64() - *(volatile long long*)&ts_efull[eb];     // E published -> MMA warp awake
@@ -362,10 +365,10 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
         }
         tc_fence_after();
         ATC_T0();
-        const int s = (MODE == MODE_FWD) ? (it % NST) : (G % NST), buf = eb;
+        const int s = (MODE == MODE_FWD) ? ((ge + it) % NST) : (G % NST), buf = eb;
         const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
         if (MODE == MODE_FWD) {
-          if (!(ok = __all_sync(0xffffffffu, twait(13, vfull_bar(s), ((uint32_t)it / NST) & 1u, p.err, tacc[2])))) break;
+          if (!(ok = __all_sync(0xffffffffu, twait(13, vfull_bar(s), ((uint32_t)(ge + it) / NST) & 1u, p.err, tacc[2])))) break;
           tc_fence_after();
         }
 #pragma unroll
@@ -382,7 +385,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
         ATC_T1(11);
       }
       if (ok) mma_commit_elect(out_bar);
-      gb += total_g;
+      gb += total_g; ge += n_it;
     }
   } else {
     // =========================== element-wise warps ===========================
@@ -414,7 +417,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       // ---- sweep 1: row max and row sum of exp over this thread's share of the keys ----
       for (; g < n_it; g += NBUF) {
         const int buf = g % NBUF;
-        ok = __all_sync(0xffffffffu, twait(16, tfull_bar(buf), ((uint32_t)g / NBUF) & 1u, p.err, tacc[5]));
+        ok = __all_sync(0xffffffffu, twait(16, tfull_bar(buf), ((uint32_t)(gb + g) / NBUF) & 1u, p.err, tacc[5]));
         if (!ok) break;
         tc_fence_after();
         // both passes' score columns are fetched at once (one exposed tensor-memory latency per sub-tile)
@@ -454,10 +457,11 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       }
       // combine the partial results of each row through shared memory (every warp sums them in the same order)
       if (ok) {
+        stat = stat_base + (k & 1) * (NCG * 128 * 2);              // per-item buffer: a fast warp may be one item ahead
         stat[(cg * 128 + row) * 2] = m_run; stat[(cg * 128 + row) * 2 + 1] = l_run;
         __syncwarp();
         if (lane == 0) mbar_arrive(comb_bar);
-        ok = __all_sync(0xffffffffu, twait(20, comb_bar, 0, p.err, tacc[9]));
+        ok = __all_sync(0xffffffffu, twait(20, comb_bar, (uint32_t)k & 1u, p.err, tacc[9]));
       }
       if (ok) {
         float mn = -INFINITY;
@@ -728,7 +732,13 @@ cudaError_t launch_attn_tc_fwd(cudaStream_t st, const FlashArgs& a, int* err_wor
   AtcParams p;
   CUtensorMap mq, mv, md;
   if (!err_word || !fill(a, err_word, &p, &mq, &mv, &md, false)) return cudaErrorInvalidValue;
-  return launch_mode<MODE_FWD>(st, mq, mv, md, p, dim3(a.T / 128, a.B * a.H));
+  // persistent: two CTAs per SM walk the work items, long row tiles first
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  p.bh_count = a.B * a.H; p.n_items = (a.T / 128) * p.bh_count;
+  const int slots = sms * AtcCfg<MODE_FWD>::CTAS_PER_SM;
+  return launch_mode<MODE_FWD>(st, mq, mv, md, p, dim3(p.n_items < slots ? p.n_items : slots));
 }
 
 cudaError_t launch_attn_tc_bwd(cudaStream_t st, const FlashArgs& a, int* err_word) {
