@@ -9,9 +9,10 @@
  * (src/nodes/node_manager.zig:65-107).
  *
  * The artefact given to pcpb_load_artifact is the forward StableHLO text of the model (the text the
- * Shepherd holds before compiling, src/algorithms/diloco.zig:153), of the nanochat family.  The backend
- * recognises the model from the @main signature, the RoPE table resources and the soft-cap constant,
- * and implements for it the functions the reference's graph builder emits
+ * Shepherd holds before compiling, src/algorithms/diloco.zig:153), of the nanochat family (RMSNorm, RoPE,
+ * QK-norm, ReLU^2, soft-capped loss) or the nanoGPT family (LayerNorm, learned positions, ReLU or tanh-GELU MLP,
+ * biased head).  The backend recognises the model from the @main signature, the RoPE table resources, the
+ * soft-cap constant and the activation's ops, refuses anything else with PCPB_E_ARTIFACT, and implements for it the functions the reference's graph builder emits
  * (src/compiler/graph_builder.zig:56-278), including the sanitiser's and the autodiff engine's guard
  * terms (src/compiler/sanitizer.zig:8-111, src/autodiff/vjp_rules.zig).
  */
@@ -95,7 +96,8 @@ int pcpb_execute_host(pcpb_backend* b, const char* fn, const void* const* in, co
  * matmulVJP src/autodiff/vjp_rules.zig:426-496), on device buffers of the loaded model's dtype:
  *   C[M,N] = epilogue(sum_k A(m,k) B(k,n)),  A(m,k) = A[m*sam + k*sak],  B(k,n) = B[k*sbk + n*sbn]
  * epilogue: 0 store, 1 residual add (R), 2 store + relu^2 into C2, 3 relu^2 backward at R, 4 weight gradient (f32 C),
- *           5 store + relu into C2, 6 relu backward at R, 7 add bias R[N].
+ *           5 store + relu into C2, 6 relu backward at R, 7 add bias R[N], 8 store + tanh-GELU into C2,
+ *           9 tanh-GELU backward at R (tanhVJP src/autodiff/vjp_rules.zig:1692 and the multiply / add rules, in closed form).
  * path: 0 = pick (tensor cores when the shape allows), 1 = generic kernel, 2 = tensor-core kernel or error. */
 int pcpb_op_gemm(pcpb_backend* b, int path, const pcpb_buffer* A, long long sam, long long sak, const pcpb_buffer* B,
                  long long sbk, long long sbn, pcpb_buffer* C, long long ldc, const pcpb_buffer* R, pcpb_buffer* C2,

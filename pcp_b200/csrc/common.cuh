@@ -143,6 +143,33 @@ __device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w <<
 __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
 
 
+// ---- tanh-approximated GELU (nanoGPT family, optional activation) ---------------------------------------
+// The exported graph writes it as nine ops of model dtype T:
+//   x2 = u*u; x3 = x2*u; k = c2*x3; s = u + k; z = c1*s; t = tanh(z); p = t + 1; h = 0.5*u; a = h*p
+// with c1 = T(sqrt(2/pi)), c2 = T(0.044715).  gelu_fwd rounds after every op as the graph does.  gelu_grad is
+// da/du of the same expression evaluated once in f32 (the reverse-mode graph of the reference sums five adjoint
+// contributions in T; for bf16 the single rounding here is the more accurate of the two and inside its tolerance).
+#define PCPB_GELU_C1 0.7978845608028654f
+#define PCPB_GELU_C2 0.044715f
+template <typename T> __device__ __forceinline__ float gelu_fwd(float u) {
+  const float c1 = rnd<T>(PCPB_GELU_C1), c2 = rnd<T>(PCPB_GELU_C2);
+  const float x2 = rnd<T>(u * u);
+  const float x3 = rnd<T>(x2 * u);
+  const float k = rnd<T>(c2 * x3);
+  const float s = rnd<T>(u + k);
+  const float z = rnd<T>(c1 * s);
+  const float t = rnd<T>(tanhf(z));                  // accurate also for bf16: the approximation would flip roundings of t
+  const float p = rnd<T>(t + 1.f);
+  const float h = rnd<T>(0.5f * u);
+  return rnd<T>(h * p);
+}
+template <typename T> __device__ __forceinline__ float gelu_grad(float u) {
+  const float c1 = rnd<T>(PCPB_GELU_C1), c2 = rnd<T>(PCPB_GELU_C2);
+  const float u2 = u * u;
+  const float t = m_tanh<T>(c1 * (u + c2 * u2 * u));
+  return 0.5f * (1.f + t) + 0.5f * u * (1.f - t * t) * c1 * (1.f + 3.f * c2 * u2);
+}
+
 #define PCPB_GUARD 1e-4f
 
 }  // namespace pcpb

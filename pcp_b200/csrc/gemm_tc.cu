@@ -122,6 +122,11 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, int c
       const uint32_t t2 = bmul2(pack2(q0, q1), 0x40004000u);           // 2 * q
       w[j] = bmul2(w[j], t2);
     }
+  } else if (p.epi == EPI_DGELU) {
+    // backward of the tanh GELU: bf16(da * gelu'(u)), the derivative evaluated once in f32
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      w[j] = pack2(bf_lo(w[j]) * gelu_grad<__nv_bfloat16>(bf_lo(x[j])), bf_hi(w[j]) * gelu_grad<__nv_bfloat16>(bf_hi(x[j])));
   }
   if (p.wide) {
     st_global_256(C, make_uint4(w[0], w[1], w[2], w[3]), make_uint4(w[4], w[5], w[6], w[7]));
@@ -130,13 +135,25 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, int c
 #pragma unroll
     for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(C)[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
   }
-  if (p.epi == EPI_RELU2 || p.epi == EPI_RELU) {
-    // second output: max(u, 0) or its square, from u as stored
+  if (p.epi == EPI_RELU2 || p.epi == EPI_RELU || p.epi == EPI_GELU) {
+    // second output: max(u, 0), its square, or the tanh GELU, from u as stored
     __nv_bfloat16* C2 = (__nv_bfloat16*)p.C2 + o;
+    if (p.epi == EPI_GELU) {
+      // the nine bf16 ops of the exported activation, two elements at a time; tanh in f32, rounded once
+      const uint32_t c1 = pack2(PCPB_GELU_C1, PCPB_GELU_C1), c2 = pack2(PCPB_GELU_C2, PCPB_GELU_C2);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const uint32_t r2 = bmax2(w[j], 0u);
-      w[j] = (p.epi == EPI_RELU2) ? bmul2(r2, r2) : r2;
+      for (int j = 0; j < 16; ++j) {
+        const uint32_t u = w[j];
+        const uint32_t z = bmul2(c1, badd2(u, bmul2(c2, bmul2(bmul2(u, u), u))));
+        const uint32_t t = pack2(tanhf(bf_lo(z)), tanhf(bf_hi(z)));
+        w[j] = bmul2(bmul2(0x3F003F00u, u), badd2(t, 0x3F803F80u));     // (0.5 * u) * (t + 1)
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const uint32_t r2 = bmax2(w[j], 0u);
+        w[j] = (p.epi == EPI_RELU2) ? bmul2(r2, r2) : r2;
+      }
     }
     if (p.wide) {
       st_global_256(C2, make_uint4(w[0], w[1], w[2], w[3]), make_uint4(w[4], w[5], w[6], w[7]));
@@ -282,7 +299,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUt
     // accumulator, so it is fetched before the wait and its latency is spent under the MMAs of the tile.
     constexpr int NCH = BN / 64;                    // 32-column chunks per warp
     const int q = warp & 3, half = (warp - 2) >> 2;
-    const bool reads_r = (p.splits == 1) && (p.epi == EPI_RESID || p.epi == EPI_DRELU2 || p.epi == EPI_DRELU);
+    const bool reads_r = (p.splits == 1) && (p.epi == EPI_RESID || p.epi == EPI_DRELU2 || p.epi == EPI_DRELU || p.epi == EPI_DGELU);
     int local = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local) {
@@ -461,7 +478,7 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     // ------------------------------ epilogue of this CTA's 128 rows ------------------------------
     constexpr int NCH = BN / 64;
     const int q = warp & 3, half = (warp - 2) >> 2;
-    const bool reads_r = (p.splits == 1) && (p.epi == EPI_RESID || p.epi == EPI_DRELU2 || p.epi == EPI_DRELU);
+    const bool reads_r = (p.splits == 1) && (p.epi == EPI_RESID || p.epi == EPI_DRELU2 || p.epi == EPI_DRELU || p.epi == EPI_DGELU);
     const uint32_t tempty_leader = map_to_cta(tempty_bar(0), 0);  // tempty_bar(a) of CTA 0 = this + 8a
     int local = 0;
     bool ok = true;
@@ -579,7 +596,7 @@ Plan plan_for(const GemmArgs& g) {
   if (((uintptr_t)g.A | (uintptr_t)g.B | (uintptr_t)g.C) & 15) return pl;
   if (g.R && ((uintptr_t)g.R & 15)) return pl;
   if (g.C2 && ((uintptr_t)g.C2 & 15)) return pl;
-  if (g.epi < EPI_STORE || g.epi > EPI_BIAS) return pl;
+  if (g.epi < EPI_STORE || g.epi > EPI_DGELU) return pl;
   pl.bn = (g.N % 256 == 0) ? 256 : 128;
   pl.pair = pair_enabled() && g.M % 256 == 0 && g.N % 256 == 0 && g.K <= pair_max_k();
   const int tiles = (g.M / (pl.pair ? 256 : BM)) * (g.N / pl.bn), kblocks = g.K / BK;

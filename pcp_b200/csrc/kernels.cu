@@ -666,6 +666,15 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs& g, int m, int n, f
     case EPI_BIAS:
       ((T*)g.C)[o] = from_f<T>(acc + to_f(((const T*)g.R)[n]));
       break;
+    case EPI_GELU: {
+      const T u = from_f<T>(acc);
+      ((T*)g.C)[o] = u;
+      ((T*)g.C2)[o] = from_f<T>(gelu_fwd<T>(to_f(u)));
+      break;
+    }
+    case EPI_DGELU:
+      ((T*)g.C)[o] = from_f<T>(rnd<T>(acc) * gelu_grad<T>(to_f(((const T*)g.R)[o])));
+      break;
   }
 }
 

@@ -19,13 +19,15 @@ enum GemmEpilogue : int {
   EPI_RELU = 5,     // C = T(acc); C2 = max(C, 0)         (nanoGPT MLP activation, two outputs)
   EPI_DRELU = 6,    // C = U > 0 ? T(acc) : 0             (backward of max(., 0), U in R)
   EPI_BIAS = 7,     // C = T(acc + bias[n])               (lm_head with bias; bias of model dtype in R, length N)
+  EPI_GELU = 8,     // C = T(acc); C2 = gelu_tanh(C), every op of the activation rounded to T (two outputs)
+  EPI_DGELU = 9,    // C = T(T(acc) * gelu_tanh'(U))      (backward of the tanh GELU, U in R)
 };
 struct GemmArgs {
   const void* A; long long sam, sak;
   const void* B; long long sbk, sbn;
   void* C; long long ldc;
-  const void* R;        // EPI_RESID: residual [M,ldc];  EPI_DRELU2: U [M,ldc]
-  void* C2;             // EPI_RELU2: second output [M,ldc]
+  const void* R;        // EPI_RESID: residual [M,ldc];  EPI_DRELU2 / EPI_DRELU / EPI_DGELU: U [M,ldc];  EPI_BIAS: bias [N]
+  void* C2;             // EPI_RELU2 / EPI_RELU / EPI_GELU: second output [M,ldc]
   int M, N, K;
   int epi;
   float clip;           // EPI_WGRAD

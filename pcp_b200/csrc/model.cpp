@@ -129,8 +129,21 @@ std::string parse_artifact(const char* text, size_t n, ModelConfig* cfg) {
       if (c.H == 0) return "could not find the [B,T,H,hd] reshape";
     }
     c.Hkv = c.H;
-    if (src.find("stablehlo.tanh") != std::string::npos || src.find("stablehlo.power") != std::string::npos)
-      return "nanoGPT graph with an activation other than ReLU is not supported";
+    // MLP activation: max(u, 0), or the tanh GELU written as u*u*u, 0.044715, sqrt(2/pi), tanh, +1, 0.5*u (one tanh
+    // per layer and no other use of tanh in this family).  Anything else is refused.
+    {
+      size_t n_tanh = 0;
+      for (size_t q = 0; (q = src.find("stablehlo.tanh", q)) != std::string::npos; ++q) ++n_tanh;
+      if (src.find("stablehlo.power") != std::string::npos || src.find("stablehlo.erf") != std::string::npos ||
+          src.find("stablehlo.logistic") != std::string::npos)
+        return "nanoGPT graph with an activation other than ReLU or tanh-GELU is not supported";
+      if (n_tanh == 0) c.activation = ACT_NATIVE;
+      else if ((int64_t)n_tanh == c.L && src.find("dense<4.47149985e-02>") != std::string::npos &&
+               src.find("dense<7.97884583e-01>") != std::string::npos)
+        c.activation = ACT_GELU_TANH;
+      else
+        return "nanoGPT graph with an activation other than ReLU or tanh-GELU is not supported";
+    }
     if (src.find("dense<-100>") == std::string::npos) return "expected ignore_index -100 in the loss";
     c.ignore_index = -100;
     c.softcap = 0.f;

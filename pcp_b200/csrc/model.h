@@ -14,11 +14,13 @@ struct TensorInfo {
 };
 
 enum { FAMILY_NANOCHAT = 0, FAMILY_NANOGPT = 1 };
+enum { ACT_NATIVE = 0, ACT_GELU_TANH = 1 };     // native: ReLU^2 (nanochat) / ReLU (nanoGPT)
 
 struct ModelConfig {
   int family = FAMILY_NANOCHAT;
   int dtype = 0;           // DT_F32 | DT_BF16 (model dtype)
   int64_t V = 0, d = 0, L = 0, H = 0, Hkv = 0, hd = 0, F = 0, B = 0, T = 0;
+  int activation = ACT_NATIVE;
   float softcap = 15.f;
   long long ignore_index = -1;
   // nanochat: wte, per layer q k v proj fc proj2, lm_head

@@ -375,7 +375,7 @@ int attention_bwd(pcpb_backend* b, LayerActs& a, float scale) {
   return PCPB_OK;
 }
 
-// nanoGPT family: learned position embedding, LayerNorm (gamma, beta), fused c_attn, ReLU MLP, lm_head with bias,
+// nanoGPT family: learned position embedding, LayerNorm (gamma, beta), fused c_attn, ReLU or tanh-GELU MLP, lm_head with bias,
 // plain cross entropy ignoring targets == -100 (models/nanogpt_small.mlir, models/nanogpt_medium_bf16.mlir).
 int forward_backward_gpt(pcpb_backend* b, const void* wts, const long long* ids, const long long* targets, float* grads,
                          float* loss_out, bool backward) {
@@ -385,6 +385,7 @@ int forward_backward_gpt(pcpb_backend* b, const void* wts, const long long* ids,
   const int dt = c.dtype, M = (int)c.M(), d = (int)c.d, F = (int)c.F, V = (int)c.V, L = (int)c.L, Tn = (int)c.T;
   const int wq = 3 * d, Bn = (int)c.B;
   const size_t es = dtype_size(dt);
+  const bool gelu = (c.activation == ACT_GELU_TANH);
   auto W = [&](int i) { return (const void*)((const char*)wts + (size_t)c.params[i].offset * es); };
   auto GR = [&](int i) { return grads + c.params[i].offset; };
   float scale = (float)(1.0 / sqrt((double)c.hd));
@@ -404,7 +405,7 @@ int forward_backward_gpt(pcpb_backend* b, const void* wts, const long long* ids,
     if (r) return r;
     G(b, a.o, d, 1, W(p0 + 3), 1, d, a.xmid, d, M, d, d, EPI_RESID, w.xs[l]);
     KL(b, 1, launch_layernorm_fwd(st, dt, a.xmid, W(p0 + 4), W(p0 + 5), M, d, a.h2, a.mu2, a.t2, a.m64_2));
-    G(b, a.h2, d, 1, W(p0 + 6), 1, d, a.u, F, M, F, d, EPI_RELU, nullptr, a.a);
+    G(b, a.h2, d, 1, W(p0 + 6), 1, d, a.u, F, M, F, d, gelu ? EPI_GELU : EPI_RELU, nullptr, a.a);
     G(b, a.a, F, 1, W(p0 + 7), 1, F, w.xs[l + 1], d, M, d, F, EPI_RESID, a.xmid);
   }
   const int pf = 2 + 8 * L;                         // ln_f.w ln_f.b lm_head.w lm_head.b
@@ -423,7 +424,7 @@ int forward_backward_gpt(pcpb_backend* b, const void* wts, const long long* ids,
   for (int l = L - 1; l >= 0; --l) {
     LayerActs& a = w.layers[l];
     const int p0 = 2 + 8 * l;
-    G(b, w.dx, d, 1, W(p0 + 7), F, 1, w.du, F, M, F, d, EPI_DRELU, a.u);           // du
+    G(b, w.dx, d, 1, W(p0 + 7), F, 1, w.du, F, M, F, d, gelu ? EPI_DGELU : EPI_DRELU, a.u);           // du
     G(b, w.dx, 1, d, a.a, F, 1, GR(p0 + 7), F, d, F, M, EPI_WGRAD);                // d mlp.c_proj
     G(b, w.du, 1, F, a.h2, d, 1, GR(p0 + 6), d, F, d, M, EPI_WGRAD);               // d c_fc
     G(b, w.du, F, 1, W(p0 + 6), d, 1, w.dh, d, M, d, F, EPI_STORE);                // d h2
@@ -846,11 +847,11 @@ int pcpb_op_gemm(pcpb_backend* b, int path, const pcpb_buffer* A, long long sam,
                  int M, int N, int K, int epilogue) {
   int r = require_loaded(b);
   if (r) return r;
-  if (!A || !B || !C || M < 0 || N < 0 || K < 0 || epilogue < EPI_STORE || epilogue > EPI_BIAS)
+  if (!A || !B || !C || M < 0 || N < 0 || K < 0 || epilogue < EPI_STORE || epilogue > EPI_DGELU)
     return fail(b, PCPB_E_INVALID, "bad gemm arguments");
-  if ((epilogue == EPI_RESID || epilogue == EPI_DRELU2 || epilogue == EPI_DRELU || epilogue == EPI_BIAS) && !R)
+  if ((epilogue == EPI_RESID || epilogue == EPI_DRELU2 || epilogue == EPI_DRELU || epilogue == EPI_BIAS || epilogue == EPI_DGELU) && !R)
     return fail(b, PCPB_E_INVALID, "this epilogue needs R");
-  if ((epilogue == EPI_RELU2 || epilogue == EPI_RELU) && !C2) return fail(b, PCPB_E_INVALID, "this epilogue needs C2");
+  if ((epilogue == EPI_RELU2 || epilogue == EPI_RELU || epilogue == EPI_GELU) && !C2) return fail(b, PCPB_E_INVALID, "this epilogue needs C2");
   DeviceGuard g(b->device);
   const size_t es = dtype_size(b->cfg.dtype);
   // extents touched by the strided views must lie inside the buffers

@@ -323,6 +323,7 @@ class NanoGPTConfig:
     batch: int = 64
     dtype: str = "f32"            # "f32" | "bf16"
     mlp_ratio: int = 4
+    activation: str = "relu"      # "relu" (the shipped graphs) | "gelu" (tanh approximation; no shipped graph has it)
 
     @property
     def head_dim(self):
@@ -428,7 +429,18 @@ def nanogpt_forward_mlir(cfg: NanoGPTConfig) -> str:
         x = e.bin("add", x, e.reshape(linear(e.reshape(o, (M, d)), wo), (B, T, d)))
         h = e.reshape(layernorm(x, ln2w, ln2b), (M, d))
         u = e.reshape(linear(h, wfc), (B, T, F))
-        a = e.bin("maximum", u, e.const("0.000000e+00", (B, T, F), dt))
+        if cfg.activation == "gelu":
+            # 0.5 * u * (1 + tanh(sqrt(2/pi) * (u + 0.044715 * u^3))), the cube as two multiplies; literals are
+            # the f32 values of the two constants to nine digits (the recogniser keys on them)
+            x3 = e.bin("multiply", e.bin("multiply", u, u), u)
+            s_ = e.bin("add", u, e.bin("multiply", e.const("4.47149985e-02", (B, T, F), dt), x3))
+            t = e.un("tanh", e.bin("multiply", e.const("7.97884583e-01", (B, T, F), dt), s_))
+            p1 = e.bin("add", t, e.const("1.000000e+00", (B, T, F), dt))
+            a = e.bin("multiply", e.bin("multiply", e.const("5.000000e-01", (B, T, F), dt), u), p1)
+        elif cfg.activation == "relu":
+            a = e.bin("maximum", u, e.const("0.000000e+00", (B, T, F), dt))
+        else:
+            raise ValueError(f"unknown activation {cfg.activation!r}")
         x = e.bin("add", x, e.reshape(linear(e.reshape(a, (M, F)), wpr), (B, T, d)))
 
     lnfw, lnfb, wh, bh = P[-4:]

@@ -41,13 +41,13 @@ def _run(be, layout, M, N, K, epi, path, seed=0):
     B = be.move_to_device(bbits, bbits.shape, BF16)
     R = C2 = None
     rv = None
-    if epi in (1, 3, 6):
+    if epi in (1, 3, 6, 9):
         rbits, rv = _bf16(rng.standard_normal((M, N)))
         R = be.move_to_device(rbits, (M, N), BF16)
     if epi == 7:
         rbits, rv = _bf16(rng.standard_normal((N,)))
         R = be.move_to_device(rbits, (N,), BF16)
-    if epi in (2, 5):
+    if epi in (2, 5, 8):
         C2 = be.allocate_zeros_device((M, N), BF16)
     Cb = be.allocate_zeros_device((M, N), F32 if epi == 4 else BF16)
     be.op_gemm(A, sa[0], sa[1], B, sb[0], sb[1], Cb, N, M, N, K, epilogue=epi, R=R, C2=C2, path=path)
@@ -76,9 +76,31 @@ def _run(be, layout, M, N, K, epi, path, seed=0):
         want = rb(r32)
     elif epi == 6:
         want = np.where(rv > 0, rb(r32), 0).astype(np.float32)
-    else:
+    elif epi == 7:
         want = rb(r32 + rv[None, :])
+    elif epi == 8:
+        want = rb(r32)
+    else:
+        want = rb(rb(r32).astype(np.float64) * _gelu_grad(rv))
     return out, want, out2
+
+
+GC1, GC2 = _bf16(np.float32(0.7978845608028654))[1], _bf16(np.float32(0.044715))[1]
+
+
+def _gelu_bf16(u):
+    """The nine ops of the exported tanh GELU, each rounded to bf16."""
+    rb = lambda x: _bf16(np.asarray(x, np.float32))[1]
+    z = rb(GC1 * rb(u + rb(GC2 * rb(rb(u * u) * u))))
+    t = rb(np.tanh(z.astype(np.float64)))
+    return rb(rb(np.float32(0.5) * u) * rb(t + np.float32(1)))
+
+
+def _gelu_grad(u):
+    u = u.astype(np.float64)
+    c1, c2 = float(GC1), float(GC2)
+    t = np.tanh(c1 * (u + c2 * u ** 3))
+    return 0.5 * (1 + t) + 0.5 * u * (1 - t * t) * c1 * (1 + 3 * c2 * u * u)
 
 
 LAYOUTS = ["nt", "nn", "tn"]
@@ -96,7 +118,7 @@ def test_tc_gemm_store(be, layout, shape):
 
 
 @pytest.mark.parametrize("layout,epi", [("nt", 1), ("nt", 2), ("nn", 3), ("tn", 4), ("nn", 0), ("nt", 4), ("nt", 5),
-                                        ("nn", 6), ("nt", 7)])
+                                        ("nn", 6), ("nt", 7), ("nt", 8), ("nn", 9)])
 def test_tc_gemm_epilogues(be, layout, epi):
     M, N, K = 256, 512, 320
     out, want, out2 = _run(be, layout, M, N, K, epi=epi, path=2, seed=epi + 1)
@@ -110,6 +132,12 @@ def test_tc_gemm_epilogues(be, layout, epi):
         np.testing.assert_array_equal(out2, _bf16(r * r)[1])
     if epi == 5:
         np.testing.assert_array_equal(out2, np.maximum(out, 0))
+    if epi == 8:
+        # second output from the first as stored; tanh is the only op that is not exactly rounded
+        want2 = _gelu_bf16(out)
+        assert np.mean(out2 != want2) < 1e-3
+        np.testing.assert_allclose(out2, want2, rtol=2 ** -7, atol=1e-6)
+        assert np.mean(gen2 != _gelu_bf16(gen)) < 1e-3
 
 
 def test_tc_gemm_split_k(be):
