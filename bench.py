@@ -43,6 +43,8 @@ WORKLOADS = {
     # d8 geometry at a quarter of the batch: small enough for an `ncu --set full` capture
     "d8b2": dict(vocab=65536, d_model=512, n_layer=8, n_head=4, n_kv_head=4, seq_len=2048, batch=2, dtype="bf16"),
     "tiny": dict(vocab=4096, d_model=256, n_layer=2, n_head=2, n_kv_head=2, seq_len=256, batch=4, dtype="bf16"),
+    # BASELINE.json configs[3] per GPU: nanoGPT-medium bf16 (head dim 64, tanh-GELU MLP, learned positions, LayerNorm)
+    "gptm": dict(vocab=50304, d_model=1024, n_layer=24, n_head=16, seq_len=1024, batch=16, dtype="bf16", activation="gelu"),
     # d20 layer geometry at profiling sizes (the kernels and their shapes per token are those of d20)
     "d20l1b8": dict(vocab=4096, d_model=1280, n_layer=1, n_head=10, n_kv_head=10, seq_len=2048, batch=8, dtype="bf16"),
     "d20l2b2": dict(vocab=65536, d_model=1280, n_layer=2, n_head=10, n_kv_head=10, seq_len=2048, batch=2, dtype="bf16"),
@@ -53,6 +55,7 @@ DESCR = {
     "d8": "nanochat-d8 (d=512) bf16 inner step, B=8, T=2048, AdamW lr 1e-3",
     "d8b2": "nanochat-d8 (d=512) bf16 inner step, B=2, T=2048 (profiling size)",
     "tiny": "nanochat tiny bf16 inner step (smoke size)",
+    "gptm": "nanoGPT-medium bf16 DiLoCo inner step (24L, d=1024, 16 heads x 64, GELU), B=16/GPU, T=1024, V=50304",
     "d20l1b8": "one d20 layer (d=1280, 10 heads x 128), V=4096, B=8, T=2048 (attention profiling size)",
     "d20l2b2": "two d20 layers + the d20 LM head, B=2, T=2048 (GEMM DRAM-traffic profiling size)",
     "d20l2b4": "two d20 layers + the d20 LM head, B=4, T=2048 (GEMM DRAM-traffic profiling size)",
@@ -61,9 +64,19 @@ H_INNER = 50
 PEAKS_FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
+def make_model(cfgd):
+    """(config, forward StableHLO text) of a workload: nanochat family when it names n_kv_head, else nanoGPT."""
+    from pcp_b200 import NanochatConfig, NanoGPTConfig, nanochat_forward_mlir, nanogpt_forward_mlir
+    if "n_kv_head" in cfgd:
+        cfg = NanochatConfig(**cfgd)
+        return cfg, nanochat_forward_mlir(cfg)
+    cfg = NanoGPTConfig(**cfgd)
+    return cfg, nanogpt_forward_mlir(cfg)
+
+
 def flops_per_token(c):
     d, L, T, V = c["d_model"], c["n_layer"], c["seq_len"], c["vocab"]
-    dkv = c["n_kv_head"] * (d // c["n_head"])
+    dkv = c.get("n_kv_head", c["n_head"]) * (d // c["n_head"])
     n_mm = L * (2 * d * d + 2 * d * dkv + 2 * d * 4 * d) + V * d
     return 6 * n_mm + 6 * L * T * d, 6 * n_mm + 12 * L * T * d
 
@@ -142,12 +155,10 @@ def cpu_oracle_tokens_per_s(cfgd, steps=1, threads=None, seq=256, batch=1):
     from oracle.loader import FifoU16, zipf_tokens
     from oracle.optim import AdamConf
     from oracle.worker import TrainingModule
-    from pcp_b200 import NanochatConfig, nanochat_forward_mlir
     if threads:
         torch.set_num_threads(threads)
-    c = dict(cfgd, batch=batch, seq_len=seq)
-    cfg = NanochatConfig(**c)
-    mod = TrainingModule(nanochat_forward_mlir(cfg))
+    cfg, text = make_model(dict(cfgd, batch=batch, seq_len=seq))
+    mod = TrainingModule(text)
     g = torch.Generator().manual_seed(0)
     params = [(torch.randn(s, generator=g) * 0.02) for s in cfg.param_shapes()]
     m = [torch.zeros_like(p) for p in params]
@@ -192,7 +203,7 @@ def run_reference(args):
 def run_ours(args):
     import torch
 
-    from pcp_b200 import BF16, Backend, NanochatConfig, nanochat_forward_mlir
+    from pcp_b200 import BF16, Backend
     from pcp_b200.synthetic import f32_to_bf16_trunc_bits, zipf_tokens
 
     rank, world, local = dist_env()
@@ -205,8 +216,7 @@ def run_ours(args):
         dist_mod.init_process_group("gloo", rank=rank, world_size=world)
         dist = dist_mod
     cfgd = WORKLOADS[args.workload]
-    cfg = NanochatConfig(**cfgd)
-    text = nanochat_forward_mlir(cfg)
+    cfg, text = make_model(cfgd)
     K, W = args.steps, max(args.warmup, 0)
     BT = cfg.batch * cfg.seq_len
     P = cfg.num_params()
@@ -220,7 +230,7 @@ def run_ours(args):
     blob32 = torch.empty(P, dtype=torch.float32)
     at = 0
     for s in cfg.param_shapes():
-        n = s[0] * s[1]
+        n = int(np.prod(s))
         blob32[at:at + n] = torch.randn(n, generator=g) * 0.02
         at += n
     blob = f32_to_bf16_trunc_bits(blob32.numpy())

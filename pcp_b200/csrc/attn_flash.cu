@@ -1,4 +1,4 @@
-// Causal attention for bf16 models with head_dim 128, tiled so that the [T,T] score matrix never leaves
+// Causal attention for bf16 models with head_dim 128 or 64, tiled so that the [T,T] score matrix never leaves
 // the SM (forward) and is recomputed per tile (backward).  Tensor-core path: mma.sync m16n8k16 bf16 with
 // ldmatrix-fed fragments; shared-memory tiles are filled with cp.async and XOR-swizzled per 16-byte chunk.
 //
@@ -23,15 +23,17 @@ namespace pcpb {
 
 namespace {
 
-constexpr int HD = 128;                 // head dim
-constexpr int ROWB = HD * 2;            // bytes per tile row (256)
+// Every kernel and tile helper below is a template over the head dim HD (128 or 64): a tile row is HD bf16 =
+// HD/8 chunks of 16 bytes, the contraction over the head dim takes HD/16 mma k-steps and an output row has HD/8
+// n-tiles of 8 columns.
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-// address of 16-byte chunk `chunk` (0..15) of row `row` in a [rows][128] bf16 tile
+// address of 16-byte chunk `chunk` (0..HD/8-1) of row `row` in a [rows][HD] bf16 tile
+template <int HD>
 __device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk) {
-  return base + (uint32_t)row * ROWB + (uint32_t)((chunk ^ (row & 7)) << 4);
+  return base + (uint32_t)row * (HD * 2) + (uint32_t)((chunk ^ (row & 7)) << 4);
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -55,31 +57,36 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 __device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
-// Copy a [ROWS][128] bf16 tile from global (row pitch `pitch` elements) into a swizzled smem tile.
-template <int ROWS, int THREADS>
+// Copy a [ROWS][HD] bf16 tile from global (row pitch `pitch` elements) into a swizzled smem tile.
+template <int HD, int ROWS, int THREADS>
 __device__ __forceinline__ void load_tile(uint32_t sbase, const bf16* __restrict__ g, long long pitch) {
+  constexpr int CPR = HD / 8;                                  // 16-byte chunks per row
+  static_assert((ROWS * CPR) % THREADS == 0, "tile does not divide over the threads");
 #pragma unroll
-  for (int i = 0; i < ROWS * 16 / THREADS; ++i) {
+  for (int i = 0; i < ROWS * CPR / THREADS; ++i) {
     const int idx = threadIdx.x + i * THREADS;
-    const int row = idx >> 4, chunk = idx & 15;
-    cp_async16(tile_addr(sbase, row, chunk), g + (long long)row * pitch + chunk * 8);
+    const int row = idx / CPR, chunk = idx % CPR;
+    cp_async16(tile_addr<HD>(sbase, row, chunk), g + (long long)row * pitch + chunk * 8);
   }
 }
 
 // A fragment (16 rows x 16 k) of a row-major tile: rows row0.., k chunk pair (2*ks, 2*ks+1)
+template <int HD>
 __device__ __forceinline__ void load_a(uint32_t sbase, int row0, int ks, uint32_t (&a)[4]) {
   const int lane = threadIdx.x & 31, id = lane >> 3, r = lane & 7;
-  ldsm_x4(tile_addr(sbase, row0 + r + (id & 1) * 8, 2 * ks + (id >> 1)), a[0], a[1], a[2], a[3]);
+  ldsm_x4(tile_addr<HD>(sbase, row0 + r + (id & 1) * 8, 2 * ks + (id >> 1)), a[0], a[1], a[2], a[3]);
 }
 // B fragments of two adjacent n-tiles (n0..n0+15) for k chunk pair ks, from a tile stored [n][k] (k contiguous)
+template <int HD>
 __device__ __forceinline__ void load_b_nk(uint32_t sbase, int n0, int ks, uint32_t (&b)[4]) {
   const int lane = threadIdx.x & 31, id = lane >> 3, r = lane & 7;
-  ldsm_x4(tile_addr(sbase, n0 + r + (id >> 1) * 8, 2 * ks + (id & 1)), b[0], b[1], b[2], b[3]);
+  ldsm_x4(tile_addr<HD>(sbase, n0 + r + (id >> 1) * 8, 2 * ks + (id & 1)), b[0], b[1], b[2], b[3]);
 }
 // B fragments of two adjacent n-tiles (n chunk nc, nc+1) for k rows k0..k0+15, from a tile stored [k][n] (n contiguous)
+template <int HD>
 __device__ __forceinline__ void load_b_kn(uint32_t sbase, int k0, int nc, uint32_t (&b)[4]) {
   const int lane = threadIdx.x & 31, id = lane >> 3, r = lane & 7;
-  ldsm_x4_t(tile_addr(sbase, k0 + r + (id & 1) * 8, nc + (id >> 1)), b[0], b[1], b[2], b[3]);
+  ldsm_x4_t(tile_addr<HD>(sbase, k0 + r + (id & 1) * 8, nc + (id >> 1)), b[0], b[1], b[2], b[3]);
 }
 
 __device__ __forceinline__ float quad_max(float v) {
@@ -94,7 +101,9 @@ __device__ __forceinline__ float quad_sum(float v) {
 // ------------------------------------------------------------------------------------------------
 // forward: CTA = 64 query rows of one (batch, head); 4 warps x 16 rows; key blocks of 64
 // ------------------------------------------------------------------------------------------------
+template <int HD>
 __global__ void __launch_bounds__(128) k_flash_fwd(FlashArgs a) {
+  constexpr int ROWB = HD * 2, KS = HD / 16, NO = HD / 8;    // row bytes, head-dim k-steps, output n-tiles
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sQ = smem_u32(smem), sK = sQ + 64 * ROWB, sV = sK + 2 * 64 * ROWB;
   const int qb = gridDim.x - 1 - blockIdx.x;                 // long rows first
@@ -107,14 +116,14 @@ __global__ void __launch_bounds__(128) k_flash_fwd(FlashArgs a) {
   const bf16* Kg = (const bf16*)a.qkn + (long long)b * a.T * wqkn + d + hk * HD;
   const bf16* Vg = (const bf16*)a.qkv + (long long)b * a.T * wqkv + d + dkv + hk * HD;
 
-  load_tile<64, 128>(sQ, Qg, wqkn);
-  load_tile<64, 128>(sK, Kg, wqkn);
-  load_tile<64, 128>(sV, Vg, wqkv);
+  load_tile<HD, 64, 128>(sQ, Qg, wqkn);
+  load_tile<HD, 64, 128>(sK, Kg, wqkn);
+  load_tile<HD, 64, 128>(sV, Vg, wqkv);
   cp_async_commit();
 
-  float o[16][4];
+  float o[NO][4];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  for (int i = 0; i < NO; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int nkb = qb + 1;
   const int row_lo = q0 + warp * 16 + g;                     // this thread's rows: row_lo and row_lo + 8
@@ -122,8 +131,8 @@ __global__ void __launch_bounds__(128) k_flash_fwd(FlashArgs a) {
   for (int kb = 0; kb < nkb; ++kb) {
     const int buf = kb & 1;
     if (kb + 1 < nkb) {
-      load_tile<64, 128>(sK + (buf ^ 1) * 64 * ROWB, Kg + (long long)(kb + 1) * 64 * wqkn, wqkn);
-      load_tile<64, 128>(sV + (buf ^ 1) * 64 * ROWB, Vg + (long long)(kb + 1) * 64 * wqkv, wqkv);
+      load_tile<HD, 64, 128>(sK + (buf ^ 1) * 64 * ROWB, Kg + (long long)(kb + 1) * 64 * wqkn, wqkn);
+      load_tile<HD, 64, 128>(sV + (buf ^ 1) * 64 * ROWB, Vg + (long long)(kb + 1) * 64 * wqkv, wqkv);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -136,13 +145,13 @@ __global__ void __launch_bounds__(128) k_flash_fwd(FlashArgs a) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
+    for (int ks = 0; ks < KS; ++ks) {
       uint32_t af[4];
-      load_a(sQ, warp * 16, ks, af);
+      load_a<HD>(sQ, warp * 16, ks, af);
 #pragma unroll
       for (int np = 0; np < 4; ++np) {
         uint32_t bfr[4];
-        load_b_nk(cK, np * 16, ks, bfr);
+        load_b_nk<HD>(cK, np * 16, ks, bfr);
         mma16816(s[2 * np], af[0], af[1], af[2], af[3], bfr[0], bfr[1]);
         mma16816(s[2 * np + 1], af[0], af[1], af[2], af[3], bfr[2], bfr[3]);
       }
@@ -185,16 +194,16 @@ __global__ void __launch_bounds__(128) k_flash_fwd(FlashArgs a) {
 #pragma unroll
     for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * alpha[r] + quad_sum(rs[r]);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) { o[i][0] *= alpha[0]; o[i][1] *= alpha[0]; o[i][2] *= alpha[1]; o[i][3] *= alpha[1]; }
+    for (int i = 0; i < NO; ++i) { o[i][0] *= alpha[0]; o[i][1] *= alpha[0]; o[i][2] *= alpha[1]; o[i][3] *= alpha[1]; }
     // O += P V
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
       const uint32_t a0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]), a1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
       const uint32_t a2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), a3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
-      for (int np = 0; np < 8; ++np) {
+      for (int np = 0; np < KS; ++np) {
         uint32_t bfr[4];
-        load_b_kn(cV, kk * 16, 2 * np, bfr);
+        load_b_kn<HD>(cV, kk * 16, 2 * np, bfr);
         mma16816(o[2 * np], a0, a1, a2, a3, bfr[0], bfr[1]);
         mma16816(o[2 * np + 1], a0, a1, a2, a3, bfr[2], bfr[3]);
       }
@@ -208,7 +217,7 @@ __global__ void __launch_bounds__(128) k_flash_fwd(FlashArgs a) {
     const int row = row_lo + r * 8;
     const float inv = 1.f / (l_run[r] + PCPB_GUARD);
 #pragma unroll
-    for (int nt = 0; nt < 16; ++nt) {
+    for (int nt = 0; nt < NO; ++nt) {
       const uint32_t v = pack_bf16(o[nt][2 * r] * inv, o[nt][2 * r + 1] * inv);
       *reinterpret_cast<uint32_t*>(Og + (long long)row * d + nt * 8 + 2 * t) = v;
     }
@@ -226,7 +235,7 @@ __global__ void k_flash_prep(FlashArgs a) {
   const long long rows = (long long)a.B * a.H * a.T;
   if (gw >= rows) return;
   const int i = (int)(gw % a.T), bh = (int)(gw / a.T), b = bh / a.H, h = bh % a.H;
-  const int d = a.H * HD;
+  const int HD = a.hd, d = a.H * HD;
   const bf16* op = (const bf16*)a.o + ((long long)b * a.T + i) * d + h * HD;
   const bf16* dp = (const bf16*)a.dout + ((long long)b * a.T + i) * d + h * HD;
   float acc = 0.f;
@@ -257,7 +266,9 @@ __device__ __forceinline__ void bwd_elem(float sraw, float dpraw, float scale, f
 // Works on the transposed tiles S^T = K Q^T and dP^T = V dO^T so that P^T and dS^T come out of the tensor
 // cores already in the A-operand register layout of the next two products.
 // ------------------------------------------------------------------------------------------------
+template <int HD>
 __global__ void __launch_bounds__(256) k_flash_bwd_dkv(FlashArgs a) {
+  constexpr int ROWB = HD * 2, KS = HD / 16, NO = HD / 8;    // row bytes, head-dim k-steps, output n-tiles
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sK = smem_u32(smem), sV = sK + 128 * ROWB, sQ = sV + 128 * ROWB, sDO = sQ + 2 * 64 * ROWB;
   float* sstat = reinterpret_cast<float*>(smem + 2 * 128 * ROWB + 4 * 64 * ROWB);       // [2 bufs][3][64]: m, l, D
@@ -269,13 +280,13 @@ __global__ void __launch_bounds__(256) k_flash_bwd_dkv(FlashArgs a) {
   const int j0 = kb * 128;
   const bf16* Kg = (const bf16*)a.qkn + ((long long)b * a.T + j0) * wqkn + d + hk * HD;
   const bf16* Vg = (const bf16*)a.qkv + ((long long)b * a.T + j0) * wqkv + d + dkv + hk * HD;
-  load_tile<128, 256>(sK, Kg, wqkn);
-  load_tile<128, 256>(sV, Vg, wqkv);
+  load_tile<HD, 128, 256>(sK, Kg, wqkn);
+  load_tile<HD, 128, 256>(sV, Vg, wqkv);
   cp_async_commit();
 
-  float dk[16][4], dv[16][4];
+  float dk[NO][4], dv[NO][4];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) { dk[i][0] = dk[i][1] = dk[i][2] = dk[i][3] = 0.f; dv[i][0] = dv[i][1] = dv[i][2] = dv[i][3] = 0.f; }
+  for (int i = 0; i < NO; ++i) { dk[i][0] = dk[i][1] = dk[i][2] = dk[i][3] = 0.f; dv[i][0] = dv[i][1] = dv[i][2] = dv[i][3] = 0.f; }
 
   const int nqb = a.T / 64, qb_first = j0 / 64;
   const int per_head = nqb - qb_first;
@@ -286,8 +297,8 @@ __global__ void __launch_bounds__(256) k_flash_bwd_dkv(FlashArgs a) {
     const int h = hk * grp + it / per_head, qb = qb_first + it % per_head;
     const bf16* Qg = (const bf16*)a.qkn + ((long long)b * a.T + qb * 64) * wqkn + h * HD;
     const bf16* DOg = (const bf16*)a.dout + ((long long)b * a.T + qb * 64) * d + h * HD;
-    load_tile<64, 256>(sQ + buf * 64 * ROWB, Qg, wqkn);
-    load_tile<64, 256>(sDO + buf * 64 * ROWB, DOg, d);
+    load_tile<HD, 64, 256>(sQ + buf * 64 * ROWB, Qg, wqkn);
+    load_tile<HD, 64, 256>(sDO + buf * 64 * ROWB, DOg, d);
     if (threadIdx.x < 192) {
       const int which = threadIdx.x >> 6, i = threadIdx.x & 63;
       const float* src = which == 0 ? a.mrow : (which == 1 ? a.lrow : a.drow);
@@ -309,15 +320,15 @@ __global__ void __launch_bounds__(256) k_flash_bwd_dkv(FlashArgs a) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) { sT[i][0] = sT[i][1] = sT[i][2] = sT[i][3] = 0.f; dpT[i][0] = dpT[i][1] = dpT[i][2] = dpT[i][3] = 0.f; }
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
+    for (int ks = 0; ks < KS; ++ks) {
       uint32_t ak[4], av[4];
-      load_a(sK, warp * 16, ks, ak);
-      load_a(sV, warp * 16, ks, av);
+      load_a<HD>(sK, warp * 16, ks, ak);
+      load_a<HD>(sV, warp * 16, ks, av);
 #pragma unroll
       for (int np = 0; np < 4; ++np) {
         uint32_t bq[4], bd[4];
-        load_b_nk(cQ, np * 16, ks, bq);
-        load_b_nk(cDO, np * 16, ks, bd);
+        load_b_nk<HD>(cQ, np * 16, ks, bq);
+        load_b_nk<HD>(cDO, np * 16, ks, bd);
         mma16816(sT[2 * np], ak[0], ak[1], ak[2], ak[3], bq[0], bq[1]);
         mma16816(sT[2 * np + 1], ak[0], ak[1], ak[2], ak[3], bq[2], bq[3]);
         mma16816(dpT[2 * np], av[0], av[1], av[2], av[3], bd[0], bd[1]);
@@ -345,10 +356,10 @@ __global__ void __launch_bounds__(256) k_flash_bwd_dkv(FlashArgs a) {
       const uint32_t s0 = pack_bf16(dpT[2 * kk][0], dpT[2 * kk][1]), s1 = pack_bf16(dpT[2 * kk][2], dpT[2 * kk][3]);
       const uint32_t s2 = pack_bf16(dpT[2 * kk + 1][0], dpT[2 * kk + 1][1]), s3 = pack_bf16(dpT[2 * kk + 1][2], dpT[2 * kk + 1][3]);
 #pragma unroll
-      for (int np = 0; np < 8; ++np) {
+      for (int np = 0; np < KS; ++np) {
         uint32_t bd[4], bq[4];
-        load_b_kn(cDO, kk * 16, 2 * np, bd);
-        load_b_kn(cQ, kk * 16, 2 * np, bq);
+        load_b_kn<HD>(cDO, kk * 16, 2 * np, bd);
+        load_b_kn<HD>(cQ, kk * 16, 2 * np, bq);
         mma16816(dv[2 * np], p0, p1, p2, p3, bd[0], bd[1]);
         mma16816(dv[2 * np + 1], p0, p1, p2, p3, bd[2], bd[3]);
         mma16816(dk[2 * np], s0, s1, s2, s3, bq[0], bq[1]);
@@ -364,7 +375,7 @@ __global__ void __launch_bounds__(256) k_flash_bwd_dkv(FlashArgs a) {
   for (int r = 0; r < 2; ++r) {
     const int key = key_lo + r * 8;
 #pragma unroll
-    for (int nt = 0; nt < 16; ++nt) {
+    for (int nt = 0; nt < NO; ++nt) {
       *reinterpret_cast<uint32_t*>(dKg + (long long)key * wqkn + nt * 8 + 2 * t) = pack_bf16(dk[nt][2 * r], dk[nt][2 * r + 1]);
       *reinterpret_cast<uint32_t*>(dVg + (long long)key * wqkv + nt * 8 + 2 * t) = pack_bf16(dv[nt][2 * r], dv[nt][2 * r + 1]);
     }
@@ -374,7 +385,9 @@ __global__ void __launch_bounds__(256) k_flash_bwd_dkv(FlashArgs a) {
 // ------------------------------------------------------------------------------------------------
 // backward, dQ: CTA = 64 query rows of one (batch, head); 4 warps x 16 rows; key blocks of 64
 // ------------------------------------------------------------------------------------------------
+template <int HD>
 __global__ void __launch_bounds__(128) k_flash_bwd_dq(FlashArgs a) {
+  constexpr int ROWB = HD * 2, KS = HD / 16, NO = HD / 8;    // row bytes, head-dim k-steps, output n-tiles
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sQ = smem_u32(smem), sDO = sQ + 64 * ROWB, sK = sDO + 64 * ROWB, sV = sK + 2 * 64 * ROWB;
   const int qb = gridDim.x - 1 - blockIdx.x;
@@ -387,10 +400,10 @@ __global__ void __launch_bounds__(128) k_flash_bwd_dq(FlashArgs a) {
   const bf16* DOg = (const bf16*)a.dout + ((long long)b * a.T + q0) * d + h * HD;
   const bf16* Kg = (const bf16*)a.qkn + (long long)b * a.T * wqkn + d + hk * HD;
   const bf16* Vg = (const bf16*)a.qkv + (long long)b * a.T * wqkv + d + dkv + hk * HD;
-  load_tile<64, 128>(sQ, Qg, wqkn);
-  load_tile<64, 128>(sDO, DOg, d);
-  load_tile<64, 128>(sK, Kg, wqkn);
-  load_tile<64, 128>(sV, Vg, wqkv);
+  load_tile<HD, 64, 128>(sQ, Qg, wqkn);
+  load_tile<HD, 64, 128>(sDO, DOg, d);
+  load_tile<HD, 64, 128>(sK, Kg, wqkn);
+  load_tile<HD, 64, 128>(sV, Vg, wqkv);
   cp_async_commit();
 
   const int row_lo = q0 + warp * 16 + g;
@@ -400,15 +413,15 @@ __global__ void __launch_bounds__(128) k_flash_bwd_dq(FlashArgs a) {
     const long long idx = (long long)bh * a.T + row_lo + r * 8;
     mrow[r] = a.mrow[idx]; lrow[r] = a.lrow[idx]; Drow[r] = a.drow[idx];
   }
-  float dq[16][4];
+  float dq[NO][4];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) { dq[i][0] = dq[i][1] = dq[i][2] = dq[i][3] = 0.f; }
+  for (int i = 0; i < NO; ++i) { dq[i][0] = dq[i][1] = dq[i][2] = dq[i][3] = 0.f; }
   const int nkb = qb + 1;
   for (int kb = 0; kb < nkb; ++kb) {
     const int buf = kb & 1;
     if (kb + 1 < nkb) {
-      load_tile<64, 128>(sK + (buf ^ 1) * 64 * ROWB, Kg + (long long)(kb + 1) * 64 * wqkn, wqkn);
-      load_tile<64, 128>(sV + (buf ^ 1) * 64 * ROWB, Vg + (long long)(kb + 1) * 64 * wqkv, wqkv);
+      load_tile<HD, 64, 128>(sK + (buf ^ 1) * 64 * ROWB, Kg + (long long)(kb + 1) * 64 * wqkn, wqkn);
+      load_tile<HD, 64, 128>(sV + (buf ^ 1) * 64 * ROWB, Vg + (long long)(kb + 1) * 64 * wqkv, wqkv);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -420,15 +433,15 @@ __global__ void __launch_bounds__(128) k_flash_bwd_dq(FlashArgs a) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; dp[i][0] = dp[i][1] = dp[i][2] = dp[i][3] = 0.f; }
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
+    for (int ks = 0; ks < KS; ++ks) {
       uint32_t aq[4], ad[4];
-      load_a(sQ, warp * 16, ks, aq);
-      load_a(sDO, warp * 16, ks, ad);
+      load_a<HD>(sQ, warp * 16, ks, aq);
+      load_a<HD>(sDO, warp * 16, ks, ad);
 #pragma unroll
       for (int np = 0; np < 4; ++np) {
         uint32_t bk[4], bv[4];
-        load_b_nk(cK, np * 16, ks, bk);
-        load_b_nk(cV, np * 16, ks, bv);
+        load_b_nk<HD>(cK, np * 16, ks, bk);
+        load_b_nk<HD>(cV, np * 16, ks, bv);
         mma16816(s[2 * np], aq[0], aq[1], aq[2], aq[3], bk[0], bk[1]);
         mma16816(s[2 * np + 1], aq[0], aq[1], aq[2], aq[3], bk[2], bk[3]);
         mma16816(dp[2 * np], ad[0], ad[1], ad[2], ad[3], bv[0], bv[1]);
@@ -454,9 +467,9 @@ __global__ void __launch_bounds__(128) k_flash_bwd_dq(FlashArgs a) {
       const uint32_t a0 = pack_bf16(dp[2 * kk][0], dp[2 * kk][1]), a1 = pack_bf16(dp[2 * kk][2], dp[2 * kk][3]);
       const uint32_t a2 = pack_bf16(dp[2 * kk + 1][0], dp[2 * kk + 1][1]), a3 = pack_bf16(dp[2 * kk + 1][2], dp[2 * kk + 1][3]);
 #pragma unroll
-      for (int np = 0; np < 8; ++np) {
+      for (int np = 0; np < KS; ++np) {
         uint32_t bk[4];
-        load_b_kn(cK, kk * 16, 2 * np, bk);
+        load_b_kn<HD>(cK, kk * 16, 2 * np, bk);
         mma16816(dq[2 * np], a0, a1, a2, a3, bk[0], bk[1]);
         mma16816(dq[2 * np + 1], a0, a1, a2, a3, bk[2], bk[3]);
       }
@@ -468,58 +481,69 @@ __global__ void __launch_bounds__(128) k_flash_bwd_dq(FlashArgs a) {
   for (int r = 0; r < 2; ++r) {
     const int row = row_lo + r * 8;
 #pragma unroll
-    for (int nt = 0; nt < 16; ++nt)
+    for (int nt = 0; nt < NO; ++nt)
       *reinterpret_cast<uint32_t*>(dQg + (long long)row * wqkn + nt * 8 + 2 * t) = pack_bf16(dq[nt][2 * r], dq[nt][2 * r + 1]);
   }
 }
 
-constexpr int FWD_SMEM = 64 * ROWB + 4 * 64 * ROWB;                          // Q + 2x(K,V) = 80 KB
-constexpr int DKV_SMEM = 2 * 128 * ROWB + 4 * 64 * ROWB + 2 * 192 * 4;       // K,V + 2x(Q,dO) + stats = 129.5 KB
-constexpr int DQ_SMEM = 2 * 64 * ROWB + 4 * 64 * ROWB;                       // Q,dO + 2x(K,V) = 96 KB
+template <int HD> struct FlashSmem {
+  static constexpr int ROWB = HD * 2;
+  static constexpr int FWD = 64 * ROWB + 4 * 64 * ROWB;                          // Q + 2x(K,V): 80 KB at HD = 128
+  static constexpr int DKV = 2 * 128 * ROWB + 4 * 64 * ROWB + 2 * 192 * 4;       // K,V + 2x(Q,dO) + stats: 129.5 KB
+  static constexpr int DQ = 2 * 64 * ROWB + 4 * 64 * ROWB;                       // Q,dO + 2x(K,V): 96 KB
+};
 
-}  // namespace
-
-bool flash_supported(const FlashArgs& a) {
-  return a.hd == HD && a.T % 128 == 0 && a.T >= 128 && a.H % a.Hkv == 0 && a.B > 0 &&
-         ((a.H * HD) % 8 == 0) && (long long)a.B * a.H <= 65535 && (long long)a.B * a.Hkv <= 65535;
-}
-
-static cudaError_t set_attrs() {
+template <int HD> cudaError_t set_attrs() {
   static bool attr[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !attr[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(k_flash_fwd, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_flash_bwd_dkv, cudaFuncAttributeMaxDynamicSharedMemorySize, DKV_SMEM);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_flash_bwd_dq, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(k_flash_fwd<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, FlashSmem<HD>::FWD);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_flash_bwd_dkv<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, FlashSmem<HD>::DKV);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_flash_bwd_dq<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, FlashSmem<HD>::DQ);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) attr[dev] = true;
   }
   return cudaSuccess;
 }
 
-cudaError_t launch_flash_fwd(cudaStream_t st, const FlashArgs& a) {
-  cudaError_t e0 = set_attrs();
+template <int HD> cudaError_t flash_fwd(cudaStream_t st, const FlashArgs& a) {
+  cudaError_t e0 = set_attrs<HD>();
   if (e0 != cudaSuccess) return e0;
   dim3 grid(a.T / 64, a.B * a.H);
-  k_flash_fwd<<<grid, 128, FWD_SMEM, st>>>(a);
+  k_flash_fwd<HD><<<grid, 128, FlashSmem<HD>::FWD, st>>>(a);
   return cudaGetLastError();
 }
 
-cudaError_t launch_flash_bwd(cudaStream_t st, const FlashArgs& a) {
-  cudaError_t e0 = set_attrs();
+template <int HD> cudaError_t flash_bwd(cudaStream_t st, const FlashArgs& a) {
+  cudaError_t e0 = set_attrs<HD>();
   if (e0 != cudaSuccess) return e0;
   const long long rows = (long long)a.B * a.H * a.T;
   k_flash_prep<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>(a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   dim3 g1(a.T / 128, a.B * a.Hkv);
-  k_flash_bwd_dkv<<<g1, 256, DKV_SMEM, st>>>(a);
+  k_flash_bwd_dkv<HD><<<g1, 256, FlashSmem<HD>::DKV, st>>>(a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   dim3 g2(a.T / 64, a.B * a.H);
-  k_flash_bwd_dq<<<g2, 128, DQ_SMEM, st>>>(a);
+  k_flash_bwd_dq<HD><<<g2, 128, FlashSmem<HD>::DQ, st>>>(a);
   return cudaGetLastError();
+}
+
+}  // namespace
+
+bool flash_supported(const FlashArgs& a) {
+  return (a.hd == 128 || a.hd == 64) && a.T % 128 == 0 && a.T >= 128 && a.H % a.Hkv == 0 && a.B > 0 &&
+         ((a.H * a.hd) % 8 == 0) && (long long)a.B * a.H <= 65535 && (long long)a.B * a.Hkv <= 65535;
+}
+
+cudaError_t launch_flash_fwd(cudaStream_t st, const FlashArgs& a) {
+  return a.hd == 128 ? flash_fwd<128>(st, a) : flash_fwd<64>(st, a);
+}
+
+cudaError_t launch_flash_bwd(cudaStream_t st, const FlashArgs& a) {
+  return a.hd == 128 ? flash_bwd<128>(st, a) : flash_bwd<64>(st, a);
 }
 
 }  // namespace pcpb

@@ -15,6 +15,8 @@ HD128_GQA_BF16 = dict(vocab=512, d_model=512, n_layer=1, n_head=4, n_kv_head=2, 
 # 160 (batch x head x row tile) work items: more than the 148 SMs, so the persistent attention kernels take several
 # items per CTA (resident-tile reload and accumulator hand-over between items)
 HD128_MANY_BF16 = dict(vocab=512, d_model=256, n_layer=1, n_head=2, n_kv_head=2, seq_len=256, batch=40, dtype="bf16")
+# head dim 64 (what the nanoGPT configurations of the baseline use): the mma.sync tiled attention kernels, GQA
+HD64_GQA_BF16 = dict(vocab=512, d_model=256, n_layer=2, n_head=4, n_kv_head=2, seq_len=256, batch=2, dtype="bf16")
 HD128_F32 = dict(vocab=512, d_model=256, n_layer=1, n_head=2, n_kv_head=1, seq_len=64, batch=2, dtype="f32")
 
 
@@ -22,9 +24,9 @@ GPT_SMALL_F32 = dict(vocab=65, d_model=64, n_layer=2, n_head=4, seq_len=32, batc
 GPT_ODD_F32 = dict(vocab=97, d_model=48, n_layer=1, n_head=3, seq_len=20, batch=3, dtype="f32")
 GPT_SMALL_BF16 = dict(vocab=256, d_model=64, n_layer=2, n_head=4, seq_len=32, batch=4, dtype="bf16")
 # tanh-GELU MLP (the activation the larger nanoGPT configurations name; no shipped graph has it).  The bf16 one is
-# sized for the tensor-core GEMM path (every GEMM dimension a multiple of 128).
+# sized for the tensor-core GEMM path (every GEMM dimension a multiple of 128) and the tiled attention (head dim 64).
 GPT_GELU_F32 = dict(GPT_SMALL_F32, activation="gelu")
-GPT_GELU_BF16 = dict(vocab=256, d_model=128, n_layer=2, n_head=4, seq_len=64, batch=4, dtype="bf16", activation="gelu")
+GPT_GELU_BF16 = dict(vocab=256, d_model=128, n_layer=2, n_head=2, seq_len=128, batch=4, dtype="bf16", activation="gelu")
 
 
 def make_model(cfgd):
