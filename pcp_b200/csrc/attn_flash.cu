@@ -243,21 +243,29 @@ __global__ void k_flash_prep(FlashArgs a) {
   acc = warp_sum(acc);
   if (lane == 0) {
     const float l = a.lrow[gw];
-    a.drow[gw] = acc * (l + PCPB_GUARD) / (l + 2.f * PCPB_GUARD);
+    const float D = acc * (l + PCPB_GUARD) / (l + 2.f * PCPB_GUARD);
+    a.drow[gw] = D;
+    // what the backward kernels need per query row, divisions done once here: max, 1/(l+1e-4), 1/(l+2e-4), D
+    a.stat4[gw] = make_float4(a.mrow[gw], 1.f / (l + PCPB_GUARD), 1.f / (l + 2.f * PCPB_GUARD), D);
   }
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // Shared by both backward kernels: turn raw scores / raw dp of one fragment element into (P_bf16, ds_bf16).
-__device__ __forceinline__ void bwd_elem(float sraw, float dpraw, float scale, float m, float l, float D, bool masked,
+// st = (m, 1/(l+1e-4), 1/(l+2e-4), D) of the element's query row.
+__device__ __forceinline__ void bwd_elem(float sraw, float dpraw, float scale, const float4 st, bool masked,
                                          float& p_out, float& ds_out) {
   const float s = bf16r(bf16r(sraw) * scale);
-  const float e = masked ? 0.f : exp2f((s - m) * LOG2E);
-  const float den2 = l + 2.f * PCPB_GUARD;
-  const float pt = e / den2;
+  const float e = masked ? 0.f : ex2_approx(fmaf(s, LOG2E, -st.x * LOG2E));
   const float dp = bf16r(dpraw);
-  float dsf = pt * (dp - D);
-  if (!masked && s == m) dsf -= D * (2.f * PCPB_GUARD) / den2;
-  p_out = masked ? 0.f : e / (l + PCPB_GUARD);
+  float dsf = e * st.z * (dp - st.w);
+  if (!masked && s == st.x) dsf -= st.w * (2.f * PCPB_GUARD) * st.z;
+  p_out = e * st.y;
   ds_out = masked ? 0.f : bf16r(bf16r(dsf) * scale);
 }
 
@@ -271,7 +279,7 @@ __global__ void __launch_bounds__(256) k_flash_bwd_dkv(FlashArgs a) {
   constexpr int ROWB = HD * 2, KS = HD / 16, NO = HD / 8;    // row bytes, head-dim k-steps, output n-tiles
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sK = smem_u32(smem), sV = sK + 128 * ROWB, sQ = sV + 128 * ROWB, sDO = sQ + 2 * 64 * ROWB;
-  float* sstat = reinterpret_cast<float*>(smem + 2 * 128 * ROWB + 4 * 64 * ROWB);       // [2 bufs][3][64]: m, l, D
+  float4* sstat = reinterpret_cast<float4*>(smem + 2 * 128 * ROWB + 4 * 64 * ROWB);     // [2 bufs][64] row records
   const int kb = blockIdx.x;
   const int bhk = blockIdx.y, b = bhk / a.Hkv, hk = bhk % a.Hkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -299,11 +307,8 @@ __global__ void __launch_bounds__(256) k_flash_bwd_dkv(FlashArgs a) {
     const bf16* DOg = (const bf16*)a.dout + ((long long)b * a.T + qb * 64) * d + h * HD;
     load_tile<HD, 64, 256>(sQ + buf * 64 * ROWB, Qg, wqkn);
     load_tile<HD, 64, 256>(sDO + buf * 64 * ROWB, DOg, d);
-    if (threadIdx.x < 192) {
-      const int which = threadIdx.x >> 6, i = threadIdx.x & 63;
-      const float* src = which == 0 ? a.mrow : (which == 1 ? a.lrow : a.drow);
-      sstat[buf * 192 + which * 64 + i] = src[((long long)b * a.H + h) * a.T + qb * 64 + i];
-    }
+    if (threadIdx.x < 64)
+      cp_async16(smem_u32(sstat + buf * 64 + threadIdx.x), a.stat4 + ((long long)b * a.H + h) * a.T + qb * 64 + threadIdx.x);
     cp_async_commit();
   };
   issue(0, 0);
@@ -314,7 +319,7 @@ __global__ void __launch_bounds__(256) k_flash_bwd_dkv(FlashArgs a) {
     __syncthreads();
     const int qb = qb_first + it % per_head;
     const uint32_t cQ = sQ + buf * 64 * ROWB, cDO = sDO + buf * 64 * ROWB;
-    const float* st = sstat + buf * 192;
+    const float4* st = sstat + buf * 64;
 
     float sT[8][4], dpT[8][4];                               // [16 keys] x [64 queries]
 #pragma unroll
@@ -344,7 +349,7 @@ __global__ void __launch_bounds__(256) k_flash_bwd_dkv(FlashArgs a) {
         const int key = key_lo + (e >> 1) * 8;
         const bool masked = diag && (key > qb * 64 + qi);
         float p, ds;
-        bwd_elem(sT[nt][e], dpT[nt][e], a.scale, st[qi], st[64 + qi], st[128 + qi], masked, p, ds);
+        bwd_elem(sT[nt][e], dpT[nt][e], a.scale, st[qi], masked, p, ds);
         sT[nt][e] = p; dpT[nt][e] = ds;
       }
     }
@@ -407,12 +412,9 @@ __global__ void __launch_bounds__(128) k_flash_bwd_dq(FlashArgs a) {
   cp_async_commit();
 
   const int row_lo = q0 + warp * 16 + g;
-  float mrow[2], lrow[2], Drow[2];
+  float4 rst[2];
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const long long idx = (long long)bh * a.T + row_lo + r * 8;
-    mrow[r] = a.mrow[idx]; lrow[r] = a.lrow[idx]; Drow[r] = a.drow[idx];
-  }
+  for (int r = 0; r < 2; ++r) rst[r] = a.stat4[(long long)bh * a.T + row_lo + r * 8];
   float dq[NO][4];
 #pragma unroll
   for (int i = 0; i < NO; ++i) { dq[i][0] = dq[i][1] = dq[i][2] = dq[i][3] = 0.f; }
@@ -457,7 +459,7 @@ __global__ void __launch_bounds__(128) k_flash_bwd_dq(FlashArgs a) {
         const int r = e >> 1;
         const bool masked = diag && (col > row_lo + r * 8);
         float p, ds;
-        bwd_elem(s[nt][e], dp[nt][e], a.scale, mrow[r], lrow[r], Drow[r], masked, p, ds);
+        bwd_elem(s[nt][e], dp[nt][e], a.scale, rst[r], masked, p, ds);
         dp[nt][e] = ds;
       }
     }
@@ -489,7 +491,7 @@ __global__ void __launch_bounds__(128) k_flash_bwd_dq(FlashArgs a) {
 template <int HD> struct FlashSmem {
   static constexpr int ROWB = HD * 2;
   static constexpr int FWD = 64 * ROWB + 4 * 64 * ROWB;                          // Q + 2x(K,V): 80 KB at HD = 128
-  static constexpr int DKV = 2 * 128 * ROWB + 4 * 64 * ROWB + 2 * 192 * 4;       // K,V + 2x(Q,dO) + stats: 129.5 KB
+  static constexpr int DKV = 2 * 128 * ROWB + 4 * 64 * ROWB + 2 * 64 * 16;       // K,V + 2x(Q,dO) + row records: 130 KB
   static constexpr int DQ = 2 * 64 * ROWB + 4 * 64 * ROWB;                       // Q,dO + 2x(K,V): 96 KB
 };
 

@@ -17,6 +17,7 @@ struct FlashArgs {
   void* dqkn;           // [B*T, d + dkv]   gradient wrt qkn (q and k parts written)
   void* dqkv;           // [B*T, d + 2 dkv] (v part written)
   float* drow;          // [B*H*T] scratch: rowsum(do*o) scaled
+  float4* stat4;        // [B*H*T] scratch: (max, 1/(l+1e-4), 1/(l+2e-4), D) per query row, written by the prep kernel
 };
 
 bool flash_supported(const FlashArgs& a);

@@ -135,7 +135,7 @@ int build_workspace(pcpb_backend* b) {
   WS(b, w.hf, M * d * es); WS(b, w.logits, M * (size_t)c.V * es);
   WS(b, w.dx, M * d * es); WS(b, w.dh, M * d * es); WS(b, w.du, M * F * es); WS(b, w.dout, M * d * es);
   WS(b, w.dqkn, M * (d + dkv) * es); WS(b, w.dqkv, M * (d + 2 * dkv) * es); WS(b, w.dkv_acc, M * 2 * dkv * 4);
-  WS(b, w.drow, (size_t)c.B * c.H * c.T * 4);
+  WS(b, w.drow, (size_t)c.B * c.H * c.T * 4 * 5);                    // D per row, then a float4 record per row
   WS(b, w.ids, M * 8); WS(b, w.targets, M * 8);
   if (!c.rope_cos.empty()) {
     WS(b, w.d_cos, c.rope_cos.size() * 2); WS(b, w.d_sin, c.rope_sin.size() * 2);
@@ -315,6 +315,7 @@ int forward_backward(pcpb_backend* b, const void* wts, const long long* ids, con
     fa.qkn = a.qkn; fa.qkv = a.qkv; fa.o = a.o; fa.mrow = a.mrow; fa.lrow = a.lrow;
     fa.B = (int)c.B; fa.T = Tn; fa.H = H; fa.Hkv = Hkv; fa.hd = hd; fa.scale = scale;
     fa.dout = w.dout; fa.dqkn = w.dqkn; fa.dqkv = w.dqkv; fa.drow = w.drow;
+    fa.stat4 = reinterpret_cast<float4*>(w.drow + (size_t)c.B * c.H * c.T);
     const bool fast = !b->force_generic && dt == DT_BF16 && b->attn_path != 2;
     if (fast && b->attn_path == 0 && attn_tc_supported(fa)) {
       KL(b, 3, launch_attn_tc_bwd(st, fa, w.tc_err));
@@ -364,6 +365,7 @@ int attention_bwd(pcpb_backend* b, LayerActs& a, float scale) {
   fa.qkn = a.qkn; fa.qkv = a.qkv; fa.o = a.o; fa.mrow = a.mrow; fa.lrow = a.lrow;
   fa.B = (int)c.B; fa.T = (int)c.T; fa.H = (int)c.H; fa.Hkv = (int)c.Hkv; fa.hd = (int)c.hd; fa.scale = scale;
   fa.dout = w.dout; fa.dqkn = w.dqkn; fa.dqkv = w.dqkv; fa.drow = w.drow;
+    fa.stat4 = reinterpret_cast<float4*>(w.drow + (size_t)c.B * c.H * c.T);
   const bool fast = !b->force_generic && dt == DT_BF16 && b->attn_path != 2;
   if (fast && b->attn_path == 0 && attn_tc_supported(fa)) { KL(b, 3, launch_attn_tc_bwd(b->stream, fa, w.tc_err)); return PCPB_OK; }
   if (fast && flash_supported(fa)) { KL(b, 3, launch_flash_bwd(b->stream, fa)); return PCPB_OK; }

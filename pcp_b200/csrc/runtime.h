@@ -42,7 +42,7 @@ struct Workspace {
   // backward temporaries
   void *dx = nullptr, *dh = nullptr, *du = nullptr, *dout = nullptr, *dqkn = nullptr, *dqkv = nullptr;
   float* dkv_acc = nullptr;
-  float* drow = nullptr;           // [B*H*T] attention-backward row scratch
+  float* drow = nullptr;           // [B*H*T] attention-backward row scratch, followed by [B*H*T] float4 row records
   float *muf = nullptr, *ln_partial = nullptr, *cs_partial = nullptr;   // nanoGPT: final LN mean, reduction scratch
   double* m64f = nullptr;
   // data
