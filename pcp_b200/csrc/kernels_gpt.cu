@@ -180,6 +180,85 @@ __global__ void __launch_bounds__(256) k_layernorm_bwd(const T* __restrict__ x, 
     partial[((size_t)blockIdx.x * 2 + which) * d + j] = acc;
   }
 }
+// Vectorised variant for d = 256 * NCH (NCH <= 4): a lane owns 8 consecutive columns of every 256-column chunk, reads
+// x and dy once with 16-byte loads and keeps them in registers between the statistics pass and the output pass; the
+// per-element arithmetic is that of k_layernorm_bwd.
+template <typename T, int NCH>
+__global__ void __launch_bounds__(256) k_layernorm_bwd_vec(const T* __restrict__ x, const T* __restrict__ gamma,
+                                                           const float* __restrict__ mean_in, const float* __restrict__ t_in,
+                                                           const double* __restrict__ mean64_in, const T* __restrict__ dy,
+                                                           const T* __restrict__ dres, int M, T* __restrict__ dx,
+                                                           float* __restrict__ partial) {
+  constexpr int d = 256 * NCH;
+  extern __shared__ float sm[];                  // [8 warps][2][d]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* dgw = sm + (size_t)(warp * 2 + 0) * d;
+  float* dbw = sm + (size_t)(warp * 2 + 1) * d;
+  for (int j = lane; j < d; j += 32) { dgw[j] = 0.f; dbw[j] = 0.f; }
+  __syncwarp();
+  const double dd2 = ((double)d + 1e-4) + 1e-4;
+  const float df2 = ((float)d + PCPB_GUARD) + PCPB_GUARD;
+  float gam[NCH][8];
+#pragma unroll
+  for (int k = 0; k < NCH; ++k) ld8<T>(gamma + k * 256 + lane * 8, gam[k]);
+  for (int rr = warp; rr < LN_ROWS; rr += 8) {
+    const int m = blockIdx.x * LN_ROWS + rr;
+    if (m >= M) break;
+    const T* xr = x + (size_t)m * d; const T* dyr = dy + (size_t)m * d;
+    const float mean = mean_in[m], t = t_in[m], r = rsqrtf(t);
+    const double mean64 = mean64_in[m];
+    float xv[NCH][8], g[NCH][8];
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) { ld8<T>(xr + k * 256 + lane * 8, xv[k]); ld8<T>(dyr + k * 256 + lane * 8, g[k]); }
+    float A = 0.f, Bc = 0.f;
+    double C64 = 0.0;
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      float4* pg = reinterpret_cast<float4*>(dgw + k * 256 + lane * 8);
+      float4* pb = reinterpret_cast<float4*>(dbw + k * 256 + lane * 8);
+      float ag[8], ab[8];
+      *reinterpret_cast<float4*>(ag) = pg[0]; *reinterpret_cast<float4*>(ag + 4) = pg[1];
+      *reinterpret_cast<float4*>(ab) = pb[0]; *reinterpret_cast<float4*>(ab + 4) = pb[1];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float dxh = g[k][e] * gam[k][e];
+        A += dxh * (xv[k][e] - mean);
+        Bc += dxh * r;
+        C64 += (double)xv[k][e] - mean64;
+        ag[e] += g[k][e] * ((xv[k][e] - mean) * r);
+        ab[e] += g[k][e];
+      }
+      pg[0] = *reinterpret_cast<float4*>(ag); pg[1] = *reinterpret_cast<float4*>(ag + 4);
+      pb[0] = *reinterpret_cast<float4*>(ab); pb[1] = *reinterpret_cast<float4*>(ab + 4);
+    }
+    A = warp_sum(A); Bc = warp_sum(Bc); C64 = warp_sum_d(C64);
+    const float rp = rsqrtf(t + PCPB_GUARD);
+    const float dtv = (A * -0.5f) * ((rp * rp) * rp);
+    const double dS2 = (double)dtv / dd2;
+    const double dsum64 = (-2.0 * dS2 * C64) / dd2;
+    const float dsum32 = (-Bc) / df2;
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      float o[8], res[8];
+      if (dres) ld8<T>(dres + (size_t)m * d + k * 256 + lane * 8, res);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float dc = (g[k][e] * gam[k][e]) * r;
+        const double dx64 = 2.0 * dS2 * ((double)xv[k][e] - mean64) + dsum64;
+        o[e] = rnd<T>(dc + dsum32 + (float)dx64);
+        if (dres) o[e] += res[e];
+      }
+      st8<T>(dx + (size_t)m * d + k * 256 + lane * 8, o);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) {
+    const int which = i / d, j = i % d;
+    float acc = 0.f;
+    for (int w = 0; w < 8; ++w) acc += sm[(w * 2 + which) * d + j];
+    partial[((size_t)blockIdx.x * 2 + which) * d + j] = acc;
+  }
+}
 // dgamma[j], dbeta[j] = sum over blocks (in block order), rounded to the model dtype, finite-guarded, clamped
 template <typename T>
 __global__ void k_ln_param_grads(const float* __restrict__ partial, int nblk, int d, float* __restrict__ dgamma,
@@ -209,8 +288,25 @@ cudaError_t launch_layernorm_bwd(cudaStream_t st, int dt, const void* x, const v
         : cudaFuncSetAttribute(k_layernorm_bwd<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  DISPATCH_DT(dt, (k_layernorm_bwd<T><<<nblk, 256, smem, st>>>((const T*)x, (const T*)gamma, mean, tsave, mean64,
-                                                               (const T*)dy, (const T*)dres, M, d, (T*)dx, partial)));
+  const bool aligned = ((((uintptr_t)x) | ((uintptr_t)dy) | ((uintptr_t)dx) | ((uintptr_t)gamma) | ((uintptr_t)dres)) & 31) == 0;
+  bool done = false;
+#define PCPB_LN_VEC(NCH)                                                                                                  \
+  if (!done && aligned && d == 256 * NCH) {                                                                               \
+    if (smem > 48 * 1024) {                                                                                               \
+      cudaError_t ea = (dt == DT_F32)                                                                                     \
+          ? cudaFuncSetAttribute(k_layernorm_bwd_vec<float, NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) \
+          : cudaFuncSetAttribute(k_layernorm_bwd_vec<bf16, NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (ea != cudaSuccess) return ea;                                                                                   \
+    }                                                                                                                     \
+    DISPATCH_DT(dt, (k_layernorm_bwd_vec<T, NCH><<<nblk, 256, smem, st>>>((const T*)x, (const T*)gamma, mean, tsave, mean64, \
+                                                                         (const T*)dy, (const T*)dres, M, (T*)dx, partial))); \
+    done = true;                                                                                                          \
+  }
+  PCPB_LN_VEC(1) PCPB_LN_VEC(2) PCPB_LN_VEC(3) PCPB_LN_VEC(4)
+#undef PCPB_LN_VEC
+  if (!done)
+    DISPATCH_DT(dt, (k_layernorm_bwd<T><<<nblk, 256, smem, st>>>((const T*)x, (const T*)gamma, mean, tsave, mean64,
+                                                                 (const T*)dy, (const T*)dres, M, d, (T*)dx, partial)));
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   DISPATCH_DT(dt, (k_ln_param_grads<T><<<cdiv(2 * d, 256), 256, 0, st>>>(partial, nblk, d, dgamma, dbeta, 100.f)));
@@ -260,9 +356,25 @@ __global__ void k_copy_cols(const T* __restrict__ src, long long sp, T* __restri
     dst[m * dp + c] = src[m * sp + c];
   }
 }
+// the same in 16-byte words (pitches, width and base addresses multiples of 16 bytes)
+__global__ void k_copy_cols16(const uint4* __restrict__ src, long long sp, uint4* __restrict__ dst, long long dp, int M, int nw) {
+  const size_t n = (size_t)M * nw;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t m = i / nw, c = i % nw;
+    dst[m * dp + c] = src[m * sp + c];
+  }
+}
 cudaError_t launch_copy_cols(cudaStream_t st, int dt, const void* src, long long src_pitch, void* dst, long long dst_pitch,
                              int M, int ncols) {
   if (M == 0 || ncols == 0) return cudaSuccess;
+  const size_t es = (dt == DT_F32) ? 4 : 2, per = 16 / es;
+  if (ncols % per == 0 && src_pitch % per == 0 && dst_pitch % per == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0) {
+    const int nw = (int)(ncols / per);
+    k_copy_cols16<<<min(cdiv((size_t)M * nw, 256), 148u * 16), 256, 0, st>>>((const uint4*)src, src_pitch / (long long)per, (uint4*)dst,
+                                                                             dst_pitch / (long long)per, M, nw);
+    return cudaGetLastError();
+  }
   DISPATCH_DT(dt, (k_copy_cols<T><<<min(cdiv((size_t)M * ncols, 256), 148u * 8), 256, 0, st>>>((const T*)src, src_pitch, (T*)dst,
                                                                                             dst_pitch, M, ncols)));
   return cudaGetLastError();

@@ -26,7 +26,9 @@ GPT_SMALL_BF16 = dict(vocab=256, d_model=64, n_layer=2, n_head=4, seq_len=32, ba
 # tanh-GELU MLP (the activation the larger nanoGPT configurations name; no shipped graph has it).  The bf16 one is
 # sized for the tensor-core GEMM path (every GEMM dimension a multiple of 128) and the tiled attention (head dim 64).
 GPT_GELU_F32 = dict(GPT_SMALL_F32, activation="gelu")
-GPT_GELU_BF16 = dict(vocab=256, d_model=128, n_layer=2, n_head=2, seq_len=128, batch=4, dtype="bf16", activation="gelu")
+GPT_GELU_BF16 = dict(vocab=256, d_model=256, n_layer=2, n_head=4, seq_len=128, batch=4, dtype="bf16", activation="gelu")
+# d_model a multiple of 256: the vectorised LayerNorm backward, f32
+GPT_D256_F32 = dict(vocab=97, d_model=256, n_layer=1, n_head=4, seq_len=32, batch=4, dtype="f32")
 
 
 def make_model(cfgd):
