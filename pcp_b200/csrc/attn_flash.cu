@@ -238,8 +238,15 @@ __global__ void k_flash_prep(FlashArgs a) {
   const int HD = a.hd, d = a.H * HD;
   const bf16* op = (const bf16*)a.o + ((long long)b * a.T + i) * d + h * HD;
   const bf16* dp = (const bf16*)a.dout + ((long long)b * a.T + i) * d + h * HD;
+  // a lane takes HD/32 consecutive elements (4 or 8 bytes of each row)
   float acc = 0.f;
-  for (int e = lane; e < HD; e += 32) acc += __bfloat162float(op[e]) * __bfloat162float(dp[e]);
+  if (HD == 128) {
+    const uint2 x = *reinterpret_cast<const uint2*>(op + lane * 4), y = *reinterpret_cast<const uint2*>(dp + lane * 4);
+    acc = bf_lo(x.x) * bf_lo(y.x) + bf_hi(x.x) * bf_hi(y.x) + bf_lo(x.y) * bf_lo(y.y) + bf_hi(x.y) * bf_hi(y.y);
+  } else {
+    const uint32_t x = *reinterpret_cast<const uint32_t*>(op + lane * 2), y = *reinterpret_cast<const uint32_t*>(dp + lane * 2);
+    acc = bf_lo(x) * bf_lo(y) + bf_hi(x) * bf_hi(y);
+  }
   acc = warp_sum(acc);
   if (lane == 0) {
     const float l = a.lrow[gw];
