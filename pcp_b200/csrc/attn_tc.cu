@@ -660,21 +660,27 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
   }
 }
 
-// D[b,h,i] = rowsum(do * o) * (l + 1e-4) / (l + 2e-4).  One warp per row.
-__global__ void k_attn_tc_prep(const bf16* __restrict__ o, const bf16* __restrict__ dout, const float* __restrict__ lrow,
-                               float* __restrict__ drow, int B, int T, int H) {
-  const long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+// D[b,h,i] = rowsum(do * o) * (l + 1e-4) / (l + 2e-4).  Eight lanes per row, 16 elements (two 16-byte loads of each
+// tensor) per lane: four rows per warp, 64 bytes in flight per thread.
+__global__ void __launch_bounds__(256) k_attn_tc_prep(const bf16* __restrict__ o, const bf16* __restrict__ dout,
+                                                      const float* __restrict__ lrow, float* __restrict__ drow, int B, int T, int H) {
+  const long long gt = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long gw = gt >> 3;                       // row index over (b, h, i); B*H*T is a multiple of 4: whole warps
+  const int sub = threadIdx.x & 7;
   if (gw >= (long long)B * H * T) return;
   const int i = (int)(gw % T), bh = (int)(gw / T), b = bh / H, h = bh % H;
-  const size_t off = ((size_t)b * T + i) * ((size_t)H * HD) + (size_t)h * HD + lane * 4;
-  const uint2 a = *reinterpret_cast<const uint2*>(o + off), c = *reinterpret_cast<const uint2*>(dout + off);
-  float acc = __uint_as_float(a.x << 16) * __uint_as_float(c.x << 16) +
-              __uint_as_float(a.x & 0xFFFF0000u) * __uint_as_float(c.x & 0xFFFF0000u) +
-              __uint_as_float(a.y << 16) * __uint_as_float(c.y << 16) +
-              __uint_as_float(a.y & 0xFFFF0000u) * __uint_as_float(c.y & 0xFFFF0000u);
-  acc = warp_sum(acc);
-  if (lane == 0) {
+  const size_t off = ((size_t)b * T + i) * ((size_t)H * HD) + (size_t)h * HD + sub * 16;
+  const uint4 a0 = *reinterpret_cast<const uint4*>(o + off), a1 = *reinterpret_cast<const uint4*>(o + off + 8);
+  const uint4 c0 = *reinterpret_cast<const uint4*>(dout + off), c1 = *reinterpret_cast<const uint4*>(dout + off + 8);
+  const uint32_t x[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+  const uint32_t y[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  float acc = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc += bf_lo(x[k]) * bf_lo(y[k]) + bf_hi(x[k]) * bf_hi(y[k]);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+  if (sub == 0) {
     const float l = lrow[gw];
     drow[gw] = acc * (l + PCPB_GUARD) / (l + 2.f * PCPB_GUARD);
   }
@@ -746,7 +752,7 @@ cudaError_t launch_attn_tc_bwd(cudaStream_t st, const FlashArgs& a, int* err_wor
   CUtensorMap mq, mv, md;
   if (!err_word || !fill(a, err_word, &p, &mq, &mv, &md, true)) return cudaErrorInvalidValue;
   const long long rows = (long long)a.B * a.H * a.T;
-  k_attn_tc_prep<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>((const bf16*)a.o, (const bf16*)a.dout, a.lrow, a.drow, a.B,
+  k_attn_tc_prep<<<(unsigned)((rows * 8 + 255) / 256), 256, 0, st>>>((const bf16*)a.o, (const bf16*)a.dout, a.lrow, a.drow, a.B,
                                                                      a.T, a.H);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
