@@ -192,6 +192,11 @@ int pcpb_outer_apply(pcpb_backend* b, const pcpb_outer_cfg* cfg, const int* cont
  *   (barrier)
  *   pcpb_stream_merge   overlap_tau steps later: parameters[fragment] <- alpha*parameters + (1-alpha)*master,
  *                       snapshot <- the blend
+ * pcpb_stream_outer_start / pcpb_stream_outer_wait split pcpb_stream_outer so that the fragment's reduction and
+ * Nesterov step run on a side stream under the next overlap_tau training steps, as the reference overlaps its
+ * network round trip with them (worker.zig:2213-2239): start after the barrier that follows the send; wait (then a
+ * barrier, since every rank writes into every replica) before the merge.  pcpb_stream_merge refuses a fragment whose
+ * outer step was started and not waited for.
  * Needs pcpb_outer_attach_* first (same peer mapping and sharding as the DiLoCo outer step). */
 typedef struct pcpb_stream_cfg {
   int num_fragments;        /* 4 in the reference (worker.zig:179) */
@@ -202,6 +207,8 @@ typedef struct pcpb_stream_cfg {
 int pcpb_stream_begin(pcpb_backend* b, const pcpb_stream_cfg* cfg);
 int pcpb_stream_send(pcpb_backend* b, int fragment);
 int pcpb_stream_outer(pcpb_backend* b, int fragment, double* device_ms);
+int pcpb_stream_outer_start(pcpb_backend* b, int fragment);
+int pcpb_stream_outer_wait(pcpb_backend* b, int fragment, double* device_ms);
 int pcpb_stream_merge(pcpb_backend* b, int fragment);
 
 /* Loss of the most recent pcpb_worker_step, read back to the host (blocks until that step has run): the

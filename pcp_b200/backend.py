@@ -42,6 +42,7 @@ EXPORTS = [
     "pcpb_outer_attach_ipc", "pcpb_outer_attach_local", "pcpb_outer_prepare", "pcpb_outer_apply",
     "pcpb_launch_count", "pcpb_worker_last_loss", "pcpb_timer_start", "pcpb_timer_stop", "pcpb_profile_enable",
     "pcpb_profile_read", "pcpb_adamw_step_noalloc", "pcpb_stream_begin", "pcpb_stream_send", "pcpb_stream_outer",
+    "pcpb_stream_outer_start", "pcpb_stream_outer_wait",
     "pcpb_stream_merge",
 ]
 
@@ -128,6 +129,8 @@ def load_library(path: str | None = None):
     lib.pcpb_stream_begin.argtypes = [vp, C.POINTER(StreamCfg)]
     lib.pcpb_stream_send.argtypes = [vp, i]
     lib.pcpb_stream_outer.argtypes = [vp, i, C.POINTER(C.c_double)]
+    lib.pcpb_stream_outer_start.argtypes = [vp, i]
+    lib.pcpb_stream_outer_wait.argtypes = [vp, i, C.POINTER(C.c_double)]
     lib.pcpb_stream_merge.argtypes = [vp, i]
     lib.pcpb_profile_enable.argtypes = [vp, i]
     lib.pcpb_profile_read.argtypes = [vp, C.POINTER(C.c_longlong), C.POINTER(C.c_double), C.POINTER(C.c_double)]
@@ -486,6 +489,15 @@ class Backend:
     def stream_outer(self, fragment: int) -> float:
         ms = C.c_double()
         self._check(self._lib.pcpb_stream_outer(self._h, int(fragment), C.byref(ms)))
+        return ms.value
+
+    def stream_outer_start(self, fragment: int):
+        """The fragment's outer step on a side stream; returns at once (pair with stream_outer_wait before the merge)."""
+        self._check(self._lib.pcpb_stream_outer_start(self._h, int(fragment)))
+
+    def stream_outer_wait(self, fragment: int) -> float:
+        ms = C.c_double(0.0)
+        self._check(self._lib.pcpb_stream_outer_wait(self._h, int(fragment), C.byref(ms)))
         return ms.value
 
     def stream_merge(self, fragment: int):

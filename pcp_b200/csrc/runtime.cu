@@ -75,6 +75,8 @@ int alloc_block(pcpb_backend* b, size_t bytes, Block** out) {
 // workspace
 // ------------------------------------------------------------------------------------------------
 void free_workspace(pcpb_backend* b) {
+  if (b->side_stream) cudaStreamSynchronize(b->side_stream);     // a fragment's outer step may still use the buffers
+  b->frag_pending.clear();
   for (void* p : b->ws.allocs) cudaFree(p);
   b->ws = Workspace();
   if (b->tokens_stage) { cudaFree(b->tokens_stage); b->tokens_stage = nullptr; b->stage_cap = 0; }
@@ -507,6 +509,8 @@ void pcpb_destroy(pcpb_backend* b) {
   for (cudaEvent_t e : b->prof_events) cudaEventDestroy(e);
   if (b->tm0) cudaEventDestroy(b->tm0);
   if (b->tm1) cudaEventDestroy(b->tm1);
+  for (cudaEvent_t e : b->frag_ev) if (e) cudaEventDestroy(e);
+  if (b->side_stream) cudaStreamDestroy(b->side_stream);
   if (b->ev0) cudaEventDestroy(b->ev0);
   if (b->ev1) cudaEventDestroy(b->ev1);
   if (b->stream) cudaStreamDestroy(b->stream);
@@ -1044,6 +1048,8 @@ int pcpb_worker_end_round(pcpb_backend* b, void* delta_out, size_t delta_bytes, 
     if (n) CK(b, cudaMemcpyAsync(losses, w.loss_record, n * 4, cudaMemcpyDeviceToHost, b->stream));
   }
   CK(b, cudaStreamSynchronize(b->stream));
+  if (b->side_stream) CK(b, cudaStreamSynchronize(b->side_stream));
+  b->frag_pending.assign(b->frag_pending.size(), 0);
   b->in_round = false;
   return check_tc_error(b);
 }
@@ -1301,17 +1307,15 @@ int pcpb_stream_send(pcpb_backend* b, int fragment) {
   return PCPB_OK;
 }
 
-int pcpb_stream_outer(pcpb_backend* b, int fragment, double* device_ms) {
-  int r = stream_check(b, fragment);
-  if (r) return r;
-  DeviceGuard g(b->device);
+// The fragment's outer step of this rank's shard, enqueued on `st` between the two events.
+static int stream_outer_enqueue(pcpb_backend* b, int fragment, cudaStream_t st, cudaEvent_t e0, cudaEvent_t e1) {
   const long long P = b->cfg.total_params, S = b->shard_len;
   const long long s_lo = (long long)b->rank * S < P ? (long long)b->rank * S : P;
   const long long s_hi = s_lo + S < P ? s_lo + S : P;
   for (int w = 0; w < b->world; ++w)
     if (!b->peer_delta[w]) return fail(b, PCPB_E_STATE, "a peer is not attached");
   const auto& ps = b->cfg.params;
-  CK(b, cudaEventRecord(b->ev0, b->stream));
+  CK(b, cudaEventRecord(e0, st));
   for (size_t i = (size_t)fragment; i < ps.size(); i += (size_t)b->stream_fragments) {
     // the part of tensor i that lies in this rank's shard
     const long long lo = ps[i].offset > s_lo ? ps[i].offset : s_lo;
@@ -1324,17 +1328,59 @@ int pcpb_stream_outer(pcpb_backend* b, int fragment, double* device_ms) {
     for (int w = 0; w < b->world; ++w)
       if (w != b->rank) a.outs[a.nouts++] = b->peer_theta0[w] + lo;
     a.n = hi - lo; a.lr = b->stream_lr; a.mu = b->stream_mu; a.trunc = 0; a.keep_nonfinite = 1;
-    KL(b, 1, launch_nesterov_shard(b->stream, a));
+    KL(b, 1, launch_nesterov_shard(st, a));
   }
-  CK(b, cudaEventRecord(b->ev1, b->stream));
+  CK(b, cudaEventRecord(e1, st));
+  return PCPB_OK;
+}
+
+static bool frag_is_pending(const pcpb_backend* b, int fragment) {
+  return (size_t)fragment < b->frag_pending.size() && b->frag_pending[fragment];
+}
+
+int pcpb_stream_outer(pcpb_backend* b, int fragment, double* device_ms) {
+  int r = stream_check(b, fragment);
+  if (r) return r;
+  if (frag_is_pending(b, fragment)) return fail(b, PCPB_E_STATE, "an outer step of this fragment is still pending (pcpb_stream_outer_wait)");
+  DeviceGuard g(b->device);
+  if ((r = stream_outer_enqueue(b, fragment, b->stream, b->ev0, b->ev1))) return r;
   CK(b, cudaStreamSynchronize(b->stream));
   if (device_ms) { float ms = 0.f; CK(b, cudaEventElapsedTime(&ms, b->ev0, b->ev1)); *device_ms = ms; }
+  return PCPB_OK;
+}
+
+int pcpb_stream_outer_start(pcpb_backend* b, int fragment) {
+  int r = stream_check(b, fragment);
+  if (r) return r;
+  if (frag_is_pending(b, fragment)) return fail(b, PCPB_E_STATE, "an outer step of this fragment is still pending (pcpb_stream_outer_wait)");
+  DeviceGuard g(b->device);
+  if (!b->side_stream) CK(b, cudaStreamCreateWithFlags(&b->side_stream, cudaStreamNonBlocking));
+  if (b->frag_ev.size() < 2 * (size_t)b->stream_fragments) {
+    const size_t old = b->frag_ev.size();
+    b->frag_ev.resize(2 * (size_t)b->stream_fragments, nullptr);
+    for (size_t i = old; i < b->frag_ev.size(); ++i) CK(b, cudaEventCreate(&b->frag_ev[i]));
+  }
+  if (b->frag_pending.size() < (size_t)b->stream_fragments) b->frag_pending.resize((size_t)b->stream_fragments, 0);
+  if ((r = stream_outer_enqueue(b, fragment, b->side_stream, b->frag_ev[2 * fragment], b->frag_ev[2 * fragment + 1]))) return r;
+  b->frag_pending[fragment] = 1;
+  return PCPB_OK;
+}
+
+int pcpb_stream_outer_wait(pcpb_backend* b, int fragment, double* device_ms) {
+  int r = stream_check(b, fragment);
+  if (r) return r;
+  if (!frag_is_pending(b, fragment)) return fail(b, PCPB_E_STATE, "no outer step of this fragment was started (pcpb_stream_outer_start)");
+  DeviceGuard g(b->device);
+  CK(b, cudaEventSynchronize(b->frag_ev[2 * fragment + 1]));
+  b->frag_pending[fragment] = 0;
+  if (device_ms) { float ms = 0.f; CK(b, cudaEventElapsedTime(&ms, b->frag_ev[2 * fragment], b->frag_ev[2 * fragment + 1])); *device_ms = ms; }
   return PCPB_OK;
 }
 
 int pcpb_stream_merge(pcpb_backend* b, int fragment) {
   int r = stream_check(b, fragment);
   if (r) return r;
+  if (frag_is_pending(b, fragment)) return fail(b, PCPB_E_STATE, "the fragment's outer step is still pending (pcpb_stream_outer_wait)");
   DeviceGuard g(b->device);
   Workspace& w = b->ws;
   const ModelConfig& c = b->cfg;

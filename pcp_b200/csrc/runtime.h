@@ -102,6 +102,9 @@ struct pcpb_backend {
   // streaming DiLoCo
   float* snapshot = nullptr;                 // last synchronised value of every parameter (f32, flat)
   int stream_fragments = 0;
+  cudaStream_t side_stream = nullptr;            // fragment outer steps that run under the following training steps
+  std::vector<cudaEvent_t> frag_ev;              // [2 * fragment + {0: start, 1: done}]
+  std::vector<char> frag_pending;                // an outer step of the fragment was started and not yet waited for
   float stream_alpha = 0.5f, stream_lr = 0.7f, stream_mu = 0.9f;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr, tm0 = nullptr, tm1 = nullptr;
   // tensor-core GEMM profiling

@@ -108,17 +108,20 @@ class StreamingGroup:
     """One rank's view of a streaming-DiLoCo run.  `backend` needs worker_step / stream_begin / stream_send /
     stream_outer / stream_merge and the outer-step attachment (pcp_b200.Backend, or a stand-in in tests).
 
-    A fragment's outer step runs right after it is sent (every rank sends, barrier, every rank updates its shard of
-    the fragment and writes it into all replicas of the master, barrier); the merge into the working parameters
-    happens overlap_tau steps later, as in the reference, where that time hides the network round trip."""
+    A fragment's outer step follows its send (every rank sends, barrier, every rank updates its shard of the fragment
+    and writes it into all replicas of the master); the merge into the working parameters happens overlap_tau steps
+    later, as in the reference, where that time hides the network round trip.  With overlap=True (backends that have
+    stream_outer_start / stream_outer_wait) the outer step runs on a side stream under those overlap_tau training
+    steps and is waited for, with a barrier, just before the merge; otherwise it runs to completion after the send."""
 
     def __init__(self, backend, transport, num_fragments=4, inner_steps=50, overlap_tau=1, alpha=0.5,
-                 learning_rate=0.7, momentum=0.9, max_rounds=1):
+                 learning_rate=0.7, momentum=0.9, max_rounds=1, overlap=False):
         if overlap_tau < 1:
             raise ValueError("overlap_tau must be at least 1: a fragment cannot be merged in the step it was sent")
         self.be, self.tr = backend, transport
         self.P, self.H, self.tau, self.alpha = num_fragments, inner_steps, overlap_tau, alpha
         self.lr, self.mu, self.max_rounds = learning_rate, momentum, max_rounds
+        self.overlap = bool(overlap)
         self.t = 0
         self.outer_ms = 0.0
 
@@ -136,12 +139,19 @@ class StreamingGroup:
         """Merges due, one training step, sends (+ their outer steps) due.  Returns (merged, sent) fragment lists."""
         self.t += 1
         recv, send = streaming_schedule(self.t, self.P, self.H, self.tau, self.max_rounds)
+        if self.overlap and recv:
+            for p, _ in recv:
+                self.outer_ms += self.be.stream_outer_wait(p)
+            self.tr.barrier()                              # every rank's writes into this replica have landed
         for p, _ in recv:
             self.be.stream_merge(p)
         self.be.worker_step()
         for p, _ in send:
             self.be.stream_send(p)
             self.tr.barrier()
-            self.outer_ms += self.be.stream_outer(p)
-            self.tr.barrier()
+            if self.overlap:
+                self.be.stream_outer_start(p)
+            else:
+                self.outer_ms += self.be.stream_outer(p)
+                self.tr.barrier()
         return [p for p, _ in recv], [p for p, _ in send]

@@ -282,11 +282,13 @@ def test_diloco_bf16_3_workers():
     _run_diloco(SMALL_BF16, workers=3, tau=4, rounds=2, lr=1e-3, tol_loss=2e-2, tol_param=2e-2, zipf=True)
 
 
-@pytest.mark.parametrize("cfgd,P,H,tau", [(SMALL_F32, 4, 4, 1), (GPT_ODD_F32, 3, 5, 2)])
-def test_streaming_diloco_matches_oracle(cfgd, P, H, tau):
+@pytest.mark.parametrize("cfgd,P,H,tau,overlap", [(SMALL_F32, 4, 4, 1, False), (GPT_ODD_F32, 3, 5, 2, False),
+                                                  (SMALL_F32, 4, 4, 1, True), (GPT_ODD_F32, 3, 5, 2, True)])
+def test_streaming_diloco_matches_oracle(cfgd, P, H, tau, overlap):
     """Streaming DiLoCo (fragment i % P, send every H steps at offset floor(pH/P), merge tau steps later with
     alpha = 0.5): two workers, two rounds per fragment, against the restated worker / Shepherd loop.  Per-step
-    losses, final worker parameters and the master within 1e-4."""
+    losses, final worker parameters and the master within 1e-4.  overlap: the fragment's outer step is started on the
+    side stream after the send and waited for before the merge, the training steps in between run beside it."""
     from oracle.worker import streaming_loop
     from pcp_b200.diloco import streaming_max_steps, streaming_schedule
     cfg, text = make_model(cfgd)
@@ -312,6 +314,10 @@ def test_streaming_diloco_matches_oracle(cfgd, P, H, tau):
         losses = [[] for _ in bes]
         for t in range(1, steps + 1):
             recv, send = streaming_schedule(t, P, H, tau, rounds)
+            if overlap:
+                for p, _ in recv:
+                    for b in bes:
+                        assert b.stream_outer_wait(p) >= 0.0
             for w, b in enumerate(bes):
                 for p, _ in recv:
                     b.stream_merge(p)
@@ -321,7 +327,13 @@ def test_streaming_diloco_matches_oracle(cfgd, P, H, tau):
                 for b in bes:
                     b.stream_send(p)
                 for b in bes:
-                    b.stream_outer(p)
+                    if overlap:
+                        b.stream_outer_start(p)
+                    else:
+                        b.stream_outer(p)
+        if overlap:                                       # protocol errors are refused, not executed
+            with pytest.raises(BackendError):
+                bes[0].stream_outer_wait(0)               # nothing pending
         for w, b in enumerate(bes):
             np.testing.assert_allclose(losses[w], ref_losses[w], rtol=1e-4)
             _close(b.worker_read_state("params"), flat(ref_params[w]), 1e-4, "f32")

@@ -119,6 +119,12 @@ class FakeStreamBackend:
                 m.flush()
         return 0.0
 
+    def stream_outer_start(self, fragment):            # the stand-in has no side stream: do it now
+        self.stream_outer(fragment)
+
+    def stream_outer_wait(self, fragment):
+        return 0.0
+
     def stream_merge(self, fragment):
         glob = np.array(np.memmap(os.path.join(self.tmp, f"master{self.rank}"), np.float32, "r", shape=(NP,)))
         for lo, hi in self._ranges(fragment):
@@ -141,14 +147,15 @@ def _oracle(world):
     return master0, [cat(p) for p in params], cat(master), cat(vel)
 
 
-def _rank(rank, world, tmp, port):
+def _rank(rank, world, tmp, port, overlap):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     master0, ref_params, ref_master, ref_vel = _oracle(world)
     be = FakeStreamBackend(tmp, rank, world, master0, TargetStream(100 + rank), CFG["lr_inner"])
     dist.barrier()                                             # every rank's files exist
-    grp = StreamingGroup(be, TorchDistTransport(dist), CFG["P"], CFG["H"], CFG["tau"], CFG["alpha"], 0.7, 0.9, CFG["rounds"])
+    grp = StreamingGroup(be, TorchDistTransport(dist), CFG["P"], CFG["H"], CFG["tau"], CFG["alpha"], 0.7, 0.9, CFG["rounds"],
+                         overlap=overlap)
     grp.begin()
     for _ in range(grp.max_steps):
         grp.step()
@@ -161,10 +168,10 @@ def _rank(rank, world, tmp, port):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2])
-def test_streaming_protocol_over_gloo(world):
+@pytest.mark.parametrize("world,overlap", [(2, False), (2, True)])
+def test_streaming_protocol_over_gloo(world, overlap):
     with tempfile.TemporaryDirectory() as tmp:
-        port = 31500 + (os.getpid() % 2000) + world
-        mp.spawn(_rank, args=(world, tmp, port), nprocs=world, join=True)
+        port = 31500 + (os.getpid() % 2000) + world + 7 * int(overlap)
+        mp.spawn(_rank, args=(world, tmp, port, overlap), nprocs=world, join=True)
         for r in range(world):
             assert open(os.path.join(tmp, f"ok{r}")).read() == "1"
