@@ -282,6 +282,30 @@ def test_diloco_bf16_3_workers():
     _run_diloco(SMALL_BF16, workers=3, tau=4, rounds=2, lr=1e-3, tol_loss=2e-2, tol_param=2e-2, zipf=True)
 
 
+def test_inner_loop_bf16_tensor_core_path_20_steps():
+    """The bf16 tolerance over 20 inner steps (the d8 protocol: one worker, AdamW lr 1e-3) on a model whose GEMMs and
+    attention run on the tcgen05 kernels (head dim 128, every GEMM dimension a multiple of 128), Zipf tokens; then one
+    outer step."""
+    _run_diloco(HD128_BF16, workers=1, tau=20, rounds=1, lr=1e-3, tol_loss=2e-2, tol_param=2e-2, zipf=True,
+                adam=dict(beta1=0.9, beta2=0.95, weight_decay=0.1))
+
+
+def test_diloco_bf16_tensor_core_path_20_steps_2_rounds():
+    """Two workers, 20 inner steps, two outer rounds on the same model.  lr 3e-4: with parameters drawn at 0.02 a larger
+    step moves them by their own size within one round, and the second round, which starts from each side's own master,
+    then measures how AdamW's sign-like early steps amplify bf16 rounding noise rather than kernel error (3.9e-2 at lr
+    1e-3 for the tensor-core kernels and the generic ones alike; one round at lr 1e-3 is within 4e-3)."""
+    _run_diloco(HD128_BF16, workers=2, tau=20, rounds=2, lr=3e-4, tol_loss=2e-2, tol_param=2e-2, zipf=True,
+                adam=dict(beta1=0.9, beta2=0.95, weight_decay=0.1))
+
+
+def test_diloco_nanogpt_gelu_bf16():
+    """nanoGPT family in bf16 with the tanh-GELU MLP, head dim 64 (tiled mma.sync attention), LayerNorm width 256
+    (vectorised backward): 2 workers, 5 inner steps, 2 outer rounds."""
+    _run_diloco(GPT_GELU_BF16, workers=2, tau=5, rounds=2, lr=3e-4, tol_loss=2e-2, tol_param=2e-2,
+                adam=dict(beta1=0.9, beta2=0.95, weight_decay=0.1))
+
+
 @pytest.mark.parametrize("cfgd,P,H,tau,overlap", [(SMALL_F32, 4, 4, 1, False), (GPT_ODD_F32, 3, 5, 2, False),
                                                   (SMALL_F32, 4, 4, 1, True), (GPT_ODD_F32, 3, 5, 2, True)])
 def test_streaming_diloco_matches_oracle(cfgd, P, H, tau, overlap):
