@@ -45,6 +45,8 @@ WORKLOADS = {
     "tiny": dict(vocab=4096, d_model=256, n_layer=2, n_head=2, n_kv_head=2, seq_len=256, batch=4, dtype="bf16"),
     # BASELINE.json configs[3] per GPU: nanoGPT-medium bf16 (head dim 64, tanh-GELU MLP, learned positions, LayerNorm)
     "gptm": dict(vocab=50304, d_model=1024, n_layer=24, n_head=16, seq_len=1024, batch=16, dtype="bf16", activation="gelu"),
+    # nanoGPT-medium layer geometry at a profiling size
+    "gptml2b8": dict(vocab=50304, d_model=1024, n_layer=2, n_head=16, seq_len=1024, batch=8, dtype="bf16", activation="gelu"),
     # d20 layer geometry at profiling sizes (the kernels and their shapes per token are those of d20)
     "d20l1b8": dict(vocab=4096, d_model=1280, n_layer=1, n_head=10, n_kv_head=10, seq_len=2048, batch=8, dtype="bf16"),
     "d20l2b2": dict(vocab=65536, d_model=1280, n_layer=2, n_head=10, n_kv_head=10, seq_len=2048, batch=2, dtype="bf16"),
@@ -56,6 +58,7 @@ DESCR = {
     "d8b2": "nanochat-d8 (d=512) bf16 inner step, B=2, T=2048 (profiling size)",
     "tiny": "nanochat tiny bf16 inner step (smoke size)",
     "gptm": "nanoGPT-medium bf16 DiLoCo inner step (24L, d=1024, 16 heads x 64, GELU), B=16/GPU, T=1024, V=50304",
+    "gptml2b8": "two nanoGPT-medium layers + its LM head, B=8, T=1024 (attention / LayerNorm profiling size)",
     "d20l1b8": "one d20 layer (d=1280, 10 heads x 128), V=4096, B=8, T=2048 (attention profiling size)",
     "d20l2b2": "two d20 layers + the d20 LM head, B=2, T=2048 (GEMM DRAM-traffic profiling size)",
     "d20l2b4": "two d20 layers + the d20 LM head, B=4, T=2048 (GEMM DRAM-traffic profiling size)",

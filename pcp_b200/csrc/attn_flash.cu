@@ -55,7 +55,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
-__device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
 // Copy a [ROWS][HD] bf16 tile from global (row pitch `pitch` elements) into a swizzled smem tile.
 template <int HD, int ROWS, int THREADS>
@@ -127,6 +126,7 @@ __global__ void __launch_bounds__(128) k_flash_fwd(FlashArgs a) {
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int nkb = qb + 1;
   const int row_lo = q0 + warp * 16 + g;                     // this thread's rows: row_lo and row_lo + 8
+  const uint32_t scale2 = pack2(a.scale, a.scale);
 
   for (int kb = 0; kb < nkb; ++kb) {
     const int buf = kb & 1;
@@ -162,15 +162,18 @@ __global__ void __launch_bounds__(128) k_flash_fwd(FlashArgs a) {
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float v = bf16r(bf16r(s[nt][e]) * a.scale);
+      for (int r = 0; r < 2; ++r) {
+        // two adjacent columns at a time: packed convert + bf16x2 multiply instead of four scalar converts
+        const uint32_t s2 = bmul2(pack2(s[nt][2 * r], s[nt][2 * r + 1]), scale2);
+        float v0 = bf_lo(s2), v1 = bf_hi(s2);
         if (diag) {
-          const int col = kb * 64 + nt * 8 + 2 * t + (e & 1);
-          const int row = row_lo + (e >> 1) * 8;
-          if (col > row) v = -INFINITY;
+          const int col = kb * 64 + nt * 8 + 2 * t;
+          const int row = row_lo + r * 8;
+          if (col > row) v0 = -INFINITY;
+          if (col + 1 > row) v1 = -INFINITY;
         }
-        s[nt][e] = v;
-        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        s[nt][2 * r] = v0; s[nt][2 * r + 1] = v1;
+        mx[r] = fmaxf(mx[r], fmaxf(v0, v1));
       }
     }
     float alpha[2], mnew[2];
@@ -263,17 +266,22 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-// Shared by both backward kernels: turn raw scores / raw dp of one fragment element into (P_bf16, ds_bf16).
-// st = (m, 1/(l+1e-4), 1/(l+2e-4), D) of the element's query row.
-__device__ __forceinline__ void bwd_elem(float sraw, float dpraw, float scale, const float4 st, bool masked,
-                                         float& p_out, float& ds_out) {
-  const float s = bf16r(bf16r(sraw) * scale);
-  const float e = masked ? 0.f : ex2_approx(fmaf(s, LOG2E, -st.x * LOG2E));
-  const float dp = bf16r(dpraw);
-  float dsf = e * st.z * (dp - st.w);
-  if (!masked && s == st.x) dsf -= st.w * (2.f * PCPB_GUARD) * st.z;
-  p_out = e * st.y;
-  ds_out = masked ? 0.f : bf16r(bf16r(dsf) * scale);
+// Shared by both backward kernels: two adjacent fragment elements (columns c, c+1 of one row) from raw scores / raw dp
+// to the packed bf16 pairs (P, P') and (ds, ds').  st0 / st1 = (m, 1/(l+1e-4), 1/(l+2e-4), D) of the query row of each
+// element.  Roundings to bf16 are done two at a time (one packed convert or one bf16x2 multiply per op of the graph):
+// scalar float -> bf16 converts run on the quarter-rate XU pipe, which they kept 70 % busy.
+__device__ __forceinline__ void bwd_pair(float s0raw, float s1raw, float dp0raw, float dp1raw, uint32_t scale2, const float4 st0,
+                                         const float4 st1, bool m0, bool m1, uint32_t& p2, uint32_t& ds2) {
+  const uint32_t s2 = bmul2(pack2(s0raw, s1raw), scale2);             // bf16(bf16(q.k) * scale)
+  const float s0 = bf_lo(s2), s1 = bf_hi(s2);
+  const float e0 = m0 ? 0.f : ex2_approx(fmaf(s0, LOG2E, -st0.x * LOG2E));
+  const float e1 = m1 ? 0.f : ex2_approx(fmaf(s1, LOG2E, -st1.x * LOG2E));
+  const uint32_t d2 = pack2(dp0raw, dp1raw);                          // bf16(do.v)
+  float f0 = e0 * st0.z * (bf_lo(d2) - st0.w), f1 = e1 * st1.z * (bf_hi(d2) - st1.w);
+  if (!m0 && s0 == st0.x) f0 -= st0.w * (2.f * PCPB_GUARD) * st0.z;
+  if (!m1 && s1 == st1.x) f1 -= st1.w * (2.f * PCPB_GUARD) * st1.z;
+  p2 = pack2(e0 * st0.y, e1 * st1.y);
+  ds2 = bmul2(pack2(m0 ? 0.f : f0, m1 ? 0.f : f1), scale2);           // bf16(bf16(dsf) * scale)
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -307,6 +315,7 @@ __global__ void __launch_bounds__(256) k_flash_bwd_dkv(FlashArgs a) {
   const int per_head = nqb - qb_first;
   const int total = per_head * grp;
   const int key_lo = j0 + warp * 16 + g;                     // this thread's keys: key_lo and key_lo + 8
+  const uint32_t scale2 = pack2(a.scale, a.scale);
 
   auto issue = [&](int it, int buf) {
     const int h = hk * grp + it / per_head, qb = qb_first + it % per_head;
@@ -348,25 +357,23 @@ __global__ void __launch_bounds__(256) k_flash_bwd_dkv(FlashArgs a) {
       }
     }
     const bool diag = (qb * 64 < j0 + 128);                  // some (key, query) pairs of this tile are masked
+    uint32_t P2[8][2], DS2[8][2];                            // packed pairs: [n-tile][row half]
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
+      const int qi = nt * 8 + 2 * t;                         // query index inside the block (tile column) of the pair
+      const float4 st0 = st[qi], st1 = st[qi + 1];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int qi = nt * 8 + 2 * t + (e & 1);             // query index inside the block (tile column)
-        const int key = key_lo + (e >> 1) * 8;
-        const bool masked = diag && (key > qb * 64 + qi);
-        float p, ds;
-        bwd_elem(sT[nt][e], dpT[nt][e], a.scale, st[qi], masked, p, ds);
-        sT[nt][e] = p; dpT[nt][e] = ds;
+      for (int r = 0; r < 2; ++r) {
+        const int key = key_lo + r * 8;
+        const bool m0 = diag && (key > qb * 64 + qi), m1 = diag && (key > qb * 64 + qi + 1);
+        bwd_pair(sT[nt][2 * r], sT[nt][2 * r + 1], dpT[nt][2 * r], dpT[nt][2 * r + 1], scale2, st0, st1, m0, m1, P2[nt][r], DS2[nt][r]);
       }
     }
     // dV += P^T dO ; dK += dS^T Q     (contraction over the 64 queries)
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
-      const uint32_t p0 = pack_bf16(sT[2 * kk][0], sT[2 * kk][1]), p1 = pack_bf16(sT[2 * kk][2], sT[2 * kk][3]);
-      const uint32_t p2 = pack_bf16(sT[2 * kk + 1][0], sT[2 * kk + 1][1]), p3 = pack_bf16(sT[2 * kk + 1][2], sT[2 * kk + 1][3]);
-      const uint32_t s0 = pack_bf16(dpT[2 * kk][0], dpT[2 * kk][1]), s1 = pack_bf16(dpT[2 * kk][2], dpT[2 * kk][3]);
-      const uint32_t s2 = pack_bf16(dpT[2 * kk + 1][0], dpT[2 * kk + 1][1]), s3 = pack_bf16(dpT[2 * kk + 1][2], dpT[2 * kk + 1][3]);
+      const uint32_t p0 = P2[2 * kk][0], p1 = P2[2 * kk][1], p2 = P2[2 * kk + 1][0], p3 = P2[2 * kk + 1][1];
+      const uint32_t s0 = DS2[2 * kk][0], s1 = DS2[2 * kk][1], s2 = DS2[2 * kk + 1][0], s3 = DS2[2 * kk + 1][1];
 #pragma unroll
       for (int np = 0; np < KS; ++np) {
         uint32_t bd[4], bq[4];
@@ -419,6 +426,7 @@ __global__ void __launch_bounds__(128) k_flash_bwd_dq(FlashArgs a) {
   cp_async_commit();
 
   const int row_lo = q0 + warp * 16 + g;
+  const uint32_t scale2 = pack2(a.scale, a.scale);
   float4 rst[2];
 #pragma unroll
   for (int r = 0; r < 2; ++r) rst[r] = a.stat4[(long long)bh * a.T + row_lo + r * 8];
@@ -458,23 +466,21 @@ __global__ void __launch_bounds__(128) k_flash_bwd_dq(FlashArgs a) {
       }
     }
     const bool diag = (kb == nkb - 1);
+    uint32_t DS2[8][2];                                      // packed pairs: [n-tile][row half]
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
+      const int col = kb * 64 + nt * 8 + 2 * t;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int col = kb * 64 + nt * 8 + 2 * t + (e & 1);
-        const int r = e >> 1;
-        const bool masked = diag && (col > row_lo + r * 8);
-        float p, ds;
-        bwd_elem(s[nt][e], dp[nt][e], a.scale, rst[r], masked, p, ds);
-        dp[nt][e] = ds;
+      for (int r = 0; r < 2; ++r) {
+        const bool m0 = diag && (col > row_lo + r * 8), m1 = diag && (col + 1 > row_lo + r * 8);
+        uint32_t p2;
+        bwd_pair(s[nt][2 * r], s[nt][2 * r + 1], dp[nt][2 * r], dp[nt][2 * r + 1], scale2, rst[r], rst[r], m0, m1, p2, DS2[nt][r]);
       }
     }
     // dQ += dS K    (contraction over the 64 keys)
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
-      const uint32_t a0 = pack_bf16(dp[2 * kk][0], dp[2 * kk][1]), a1 = pack_bf16(dp[2 * kk][2], dp[2 * kk][3]);
-      const uint32_t a2 = pack_bf16(dp[2 * kk + 1][0], dp[2 * kk + 1][1]), a3 = pack_bf16(dp[2 * kk + 1][2], dp[2 * kk + 1][3]);
+      const uint32_t a0 = DS2[2 * kk][0], a1 = DS2[2 * kk][1], a2 = DS2[2 * kk + 1][0], a3 = DS2[2 * kk + 1][1];
 #pragma unroll
       for (int np = 0; np < KS; ++np) {
         uint32_t bk[4];
