@@ -402,11 +402,19 @@ class Backend:
         self._check(self._lib.pcpb_profile_read(self._h, C.byref(n), C.byref(ms), C.byref(fl)))
         return {"launches": n.value, "ms": ms.value, "flops": fl.value}
 
-    def worker_end_round(self, steps, param_dtype=F32, want_delta=True):
+    def worker_end_round(self, steps, param_dtype=F32, want_delta=True, out=None):
+        """-> (delta blob, per-step losses).  `out`: a caller-owned array for the delta (e.g. a view of pinned host
+        memory, which the device -> host copy fills at full PCIe rate and without first-touch page faults)."""
         P = self.model_info()["total_params"]
         losses = np.zeros(max(steps, 1), dtype=np.float32)
         if want_delta:
-            delta = np.empty(P, dtype=np.float32 if param_dtype == F32 else np.uint16)
+            dt = np.float32 if param_dtype == F32 else np.uint16
+            if out is not None:
+                if out.dtype != dt or out.size != P or not out.flags["C_CONTIGUOUS"]:
+                    raise ValueError("out must be a contiguous array of the delta's dtype and length")
+                delta = out
+            else:
+                delta = np.empty(P, dtype=dt)
             self._check(self._lib.pcpb_worker_end_round(self._h, delta.ctypes.data, delta.nbytes, losses.ctypes.data, steps))
         else:
             delta = None
