@@ -158,8 +158,9 @@ def cpu_oracle_tokens_per_s(cfgd, steps=1, threads=None, seq=256, batch=1):
     from oracle.loader import FifoU16, zipf_tokens
     from oracle.optim import AdamConf
     from oracle.worker import TrainingModule
-    if threads:
-        torch.set_num_threads(threads)
+    # all host cores this process may use; a launcher (torchrun) that exports OMP_NUM_THREADS=1 must not turn the
+    # reference into a single-threaded run
+    torch.set_num_threads(threads or len(os.sched_getaffinity(0)))
     cfg, text = make_model(dict(cfgd, batch=batch, seq_len=seq))
     mod = TrainingModule(text)
     g = torch.Generator().manual_seed(0)

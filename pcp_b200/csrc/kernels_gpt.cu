@@ -105,9 +105,64 @@ __global__ void __launch_bounds__(256) k_layernorm_fwd(const T* __restrict__ x, 
   for (int j = lane; j < d; j += 32)
     yr[j] = from_f<T>(((to_f(xr[j]) - mean) * r) * to_f(gamma[j]) + to_f(beta[j]));
 }
+// Vectorised variant for d = 256 * NCH: a lane owns 8 consecutive columns of every 256-column chunk and keeps the row
+// in registers over the three passes (one 16-byte read per chunk); arithmetic per element as above.
+template <typename T, int NCH>
+__global__ void __launch_bounds__(256) k_layernorm_fwd_vec(const T* __restrict__ x, const T* __restrict__ gamma,
+                                                           const T* __restrict__ beta, int M, T* __restrict__ y,
+                                                           float* __restrict__ mean_out, float* __restrict__ t_out,
+                                                           double* __restrict__ mean64_out) {
+  constexpr int d = 256 * NCH;
+  const int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (m >= M) return;
+  const T* xr = x + (size_t)m * d;
+  float xv[NCH][8];
+#pragma unroll
+  for (int k = 0; k < NCH; ++k) ld8<T>(xr + k * 256 + lane * 8, xv[k]);
+  float s32 = 0.f;
+  double s64 = 0.0;
+#pragma unroll
+  for (int k = 0; k < NCH; ++k)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { s32 += xv[k][e]; s64 += (double)xv[k][e]; }
+  s32 = warp_sum(s32);
+  s64 = warp_sum_d(s64);
+  const double dd = (double)d + 1e-4;
+  const double mean64 = s64 / dd;
+  double v64 = 0.0;
+#pragma unroll
+  for (int k = 0; k < NCH; ++k)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { const double c = (double)xv[k][e] - mean64; v64 += c * c; }
+  v64 = warp_sum_d(v64) / dd;
+  const float var = (float)v64;
+  const float mean = s32 / ((float)d + PCPB_GUARD);
+  const float t = var + 1e-5f;
+  const float r = rsqrtf(t);
+  if (lane == 0) { mean_out[m] = mean; t_out[m] = t; mean64_out[m] = mean64; }
+  T* yr = y + (size_t)m * d;
+#pragma unroll
+  for (int k = 0; k < NCH; ++k) {
+    float g[8], bt[8], o[8];
+    ld8<T>(gamma + k * 256 + lane * 8, g);
+    ld8<T>(beta + k * 256 + lane * 8, bt);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = ((xv[k][e] - mean) * r) * g[e] + bt[e];
+    st8<T>(yr + k * 256 + lane * 8, o);
+  }
+}
 cudaError_t launch_layernorm_fwd(cudaStream_t st, int dt, const void* x, const void* gamma, const void* beta, int M, int d,
                                  void* y, float* mean, float* tsave, double* mean64) {
   if (M == 0) return cudaSuccess;
+  const bool aligned = ((((uintptr_t)x) | ((uintptr_t)y) | ((uintptr_t)gamma) | ((uintptr_t)beta)) & 31) == 0;
+#define PCPB_LNF_VEC(NCH)                                                                                              \
+  if (aligned && d == 256 * NCH) {                                                                                     \
+    DISPATCH_DT(dt, (k_layernorm_fwd_vec<T, NCH><<<cdiv(M, 8), 256, 0, st>>>((const T*)x, (const T*)gamma, (const T*)beta, M, \
+                                                                            (T*)y, mean, tsave, mean64)));             \
+    return cudaGetLastError();                                                                                         \
+  }
+  PCPB_LNF_VEC(1) PCPB_LNF_VEC(2) PCPB_LNF_VEC(3) PCPB_LNF_VEC(4)
+#undef PCPB_LNF_VEC
   DISPATCH_DT(dt, (k_layernorm_fwd<T><<<cdiv(M, 8), 256, 0, st>>>((const T*)x, (const T*)gamma, (const T*)beta, M, d, (T*)y,
                                                                   mean, tsave, mean64)));
   return cudaGetLastError();
@@ -260,18 +315,30 @@ __global__ void __launch_bounds__(256) k_layernorm_bwd_vec(const T* __restrict__
   }
 }
 // dgamma[j], dbeta[j] = sum over blocks (in block order), rounded to the model dtype, finite-guarded, clamped
+// Block = 32 columns x 8 row groups: a thread sums the partials b = group, group + 8, ... in that order, the eight group
+// sums are added in group order (a fixed summation tree: deterministic).
 template <typename T>
-__global__ void k_ln_param_grads(const float* __restrict__ partial, int nblk, int d, float* __restrict__ dgamma,
-                                 float* __restrict__ dbeta, float clip) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= 2 * d) return;
-  const int which = i / d, j = i % d;
+__global__ void __launch_bounds__(256) k_ln_param_grads(const float* __restrict__ partial, int nblk, int d,
+                                                        float* __restrict__ dgamma, float* __restrict__ dbeta, float clip) {
+  __shared__ float sm[8][33];
+  const int col = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const int i = blockIdx.x * 32 + col;                       // over 2 * d columns: dgamma then dbeta
   float acc = 0.f;
-  for (int b = 0; b < nblk; ++b) acc += partial[((size_t)b * 2 + which) * d + j];
-  float v = rnd<T>(acc);
-  if (!((v - v) == 0.f)) v = 0.f;
-  v = fminf(fmaxf(v, -clip), clip);
-  (which == 0 ? dgamma : dbeta)[j] = v;
+  if (i < 2 * d) {
+    const int which = i / d, j = i % d;
+    for (int b = grp; b < nblk; b += 8) acc += partial[((size_t)b * 2 + which) * d + j];
+  }
+  sm[grp][col] = acc;
+  __syncthreads();
+  if (grp == 0 && i < 2 * d) {
+    float tot = 0.f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) tot += sm[g][col];
+    float v = rnd<T>(tot);
+    if (!((v - v) == 0.f)) v = 0.f;
+    v = fminf(fmaxf(v, -clip), clip);
+    (i / d == 0 ? dgamma : dbeta)[i % d] = v;
+  }
 }
 size_t layernorm_bwd_scratch_floats(int M, int d) { return (size_t)((M + LN_ROWS - 1) / LN_ROWS) * 2 * d; }
 
@@ -309,7 +376,7 @@ cudaError_t launch_layernorm_bwd(cudaStream_t st, int dt, const void* x, const v
                                                                  (const T*)dy, (const T*)dres, M, d, (T*)dx, partial)));
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  DISPATCH_DT(dt, (k_ln_param_grads<T><<<cdiv(2 * d, 256), 256, 0, st>>>(partial, nblk, d, dgamma, dbeta, 100.f)));
+  DISPATCH_DT(dt, (k_ln_param_grads<T><<<cdiv(2 * d, 32), 256, 0, st>>>(partial, nblk, d, dgamma, dbeta, 100.f)));
   return cudaGetLastError();
 }
 
