@@ -314,6 +314,107 @@ __global__ void __launch_bounds__(256) k_layernorm_bwd_vec(const T* __restrict__
     partial[((size_t)blockIdx.x * 2 + which) * d + j] = acc;
   }
 }
+// bf16 form of the vectorised kernel: x, dy and gamma stay packed (four registers per eight elements), so a warp can hold
+// the next row's x and dy, fetched before the current row is worked on, beside the current one.
+__device__ __forceinline__ void unpack_bf16x8(const uint4& v, float (&f)[8]) {
+  f[0] = bf_lo(v.x); f[1] = bf_hi(v.x); f[2] = bf_lo(v.y); f[3] = bf_hi(v.y);
+  f[4] = bf_lo(v.z); f[5] = bf_hi(v.z); f[6] = bf_lo(v.w); f[7] = bf_hi(v.w);
+}
+template <int NCH>
+__global__ void __launch_bounds__(256) k_layernorm_bwd_bf16(const bf16* __restrict__ x, const bf16* __restrict__ gamma,
+                                                            const float* __restrict__ mean_in, const float* __restrict__ t_in,
+                                                            const double* __restrict__ mean64_in, const bf16* __restrict__ dy,
+                                                            const bf16* __restrict__ dres, int M, bf16* __restrict__ dx,
+                                                            float* __restrict__ partial) {
+  constexpr int d = 256 * NCH;
+  extern __shared__ float sm[];                  // [8 warps][2][d]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* dgw = sm + (size_t)(warp * 2 + 0) * d;
+  float* dbw = sm + (size_t)(warp * 2 + 1) * d;
+  for (int j = lane; j < d; j += 32) { dgw[j] = 0.f; dbw[j] = 0.f; }
+  __syncwarp();
+  const double dd2 = ((double)d + 1e-4) + 1e-4;
+  const float df2 = ((float)d + PCPB_GUARD) + PCPB_GUARD;
+  uint4 gam[NCH], nx[NCH], ny[NCH];
+#pragma unroll
+  for (int k = 0; k < NCH; ++k) gam[k] = *reinterpret_cast<const uint4*>(gamma + k * 256 + lane * 8);
+  const int m_first = blockIdx.x * LN_ROWS + warp;
+  if (m_first < M) {
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      nx[k] = *reinterpret_cast<const uint4*>(x + (size_t)m_first * d + k * 256 + lane * 8);
+      ny[k] = *reinterpret_cast<const uint4*>(dy + (size_t)m_first * d + k * 256 + lane * 8);
+    }
+  }
+  for (int rr = warp; rr < LN_ROWS; rr += 8) {
+    const int m = blockIdx.x * LN_ROWS + rr;
+    if (m >= M) break;
+    uint4 cx[NCH], cy[NCH];
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) { cx[k] = nx[k]; cy[k] = ny[k]; }
+    const int mn = m + 8;
+    if (rr + 8 < LN_ROWS && mn < M) {
+#pragma unroll
+      for (int k = 0; k < NCH; ++k) {
+        nx[k] = *reinterpret_cast<const uint4*>(x + (size_t)mn * d + k * 256 + lane * 8);
+        ny[k] = *reinterpret_cast<const uint4*>(dy + (size_t)mn * d + k * 256 + lane * 8);
+      }
+    }
+    const float mean = mean_in[m], t = t_in[m], r = rsqrtf(t);
+    const double mean64 = mean64_in[m];
+    float A = 0.f, Bc = 0.f;
+    double C64 = 0.0;
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      float xv[8], g[8], gm[8];
+      unpack_bf16x8(cx[k], xv); unpack_bf16x8(cy[k], g); unpack_bf16x8(gam[k], gm);
+      float4* pg = reinterpret_cast<float4*>(dgw + k * 256 + lane * 8);
+      float4* pb = reinterpret_cast<float4*>(dbw + k * 256 + lane * 8);
+      float ag[8], ab[8];
+      *reinterpret_cast<float4*>(ag) = pg[0]; *reinterpret_cast<float4*>(ag + 4) = pg[1];
+      *reinterpret_cast<float4*>(ab) = pb[0]; *reinterpret_cast<float4*>(ab + 4) = pb[1];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float dxh = g[e] * gm[e];
+        A += dxh * (xv[e] - mean);
+        Bc += dxh * r;
+        C64 += (double)xv[e] - mean64;
+        ag[e] += g[e] * ((xv[e] - mean) * r);
+        ab[e] += g[e];
+      }
+      pg[0] = *reinterpret_cast<float4*>(ag); pg[1] = *reinterpret_cast<float4*>(ag + 4);
+      pb[0] = *reinterpret_cast<float4*>(ab); pb[1] = *reinterpret_cast<float4*>(ab + 4);
+    }
+    A = warp_sum(A); Bc = warp_sum(Bc); C64 = warp_sum_d(C64);
+    const float rp = rsqrtf(t + PCPB_GUARD);
+    const float dtv = (A * -0.5f) * ((rp * rp) * rp);
+    const double dS2 = (double)dtv / dd2;
+    const double dsum64 = (-2.0 * dS2 * C64) / dd2;
+    const float dsum32 = (-Bc) / df2;
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      float xv[8], g[8], gm[8], o[8], res[8];
+      unpack_bf16x8(cx[k], xv); unpack_bf16x8(cy[k], g); unpack_bf16x8(gam[k], gm);
+      if (dres) ld8<bf16>(dres + (size_t)m * d + k * 256 + lane * 8, res);
+#pragma unroll
+      for (int e = 0; e < 8; e += 2) {
+        const float dc0 = (g[e] * gm[e]) * r, dc1 = (g[e + 1] * gm[e + 1]) * r;
+        const double a0 = 2.0 * dS2 * ((double)xv[e] - mean64) + dsum64, a1 = 2.0 * dS2 * ((double)xv[e + 1] - mean64) + dsum64;
+        const uint32_t o2 = pack2(dc0 + dsum32 + (float)a0, dc1 + dsum32 + (float)a1);      // the bf16 rounding of dx
+        o[e] = bf_lo(o2); o[e + 1] = bf_hi(o2);
+        if (dres) { o[e] += res[e]; o[e + 1] += res[e + 1]; }
+      }
+      st8<bf16>(dx + (size_t)m * d + k * 256 + lane * 8, o);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) {
+    const int which = i / d, j = i % d;
+    float acc = 0.f;
+    for (int w = 0; w < 8; ++w) acc += sm[(w * 2 + which) * d + j];
+    partial[((size_t)blockIdx.x * 2 + which) * d + j] = acc;
+  }
+}
 // dgamma[j], dbeta[j] = sum over blocks (in block order), rounded to the model dtype, finite-guarded, clamped
 // Block = 32 columns x 8 row groups: a thread sums the partials b = group, group + 8, ... in that order, the eight group
 // sums are added in group order (a fixed summation tree: deterministic).
@@ -369,6 +470,18 @@ cudaError_t launch_layernorm_bwd(cudaStream_t st, int dt, const void* x, const v
                                                                          (const T*)dy, (const T*)dres, M, (T*)dx, partial))); \
     done = true;                                                                                                          \
   }
+#define PCPB_LN_BF16(NCH)                                                                                                 \
+  if (!done && aligned && dt == DT_BF16 && d == 256 * NCH) {                                                              \
+    if (smem > 48 * 1024) {                                                                                               \
+      cudaError_t ea = cudaFuncSetAttribute(k_layernorm_bwd_bf16<NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (ea != cudaSuccess) return ea;                                                                                   \
+    }                                                                                                                     \
+    k_layernorm_bwd_bf16<NCH><<<nblk, 256, smem, st>>>((const bf16*)x, (const bf16*)gamma, mean, tsave, mean64, (const bf16*)dy, \
+                                                       (const bf16*)dres, M, (bf16*)dx, partial);                        \
+    done = true;                                                                                                          \
+  }
+  PCPB_LN_BF16(1) PCPB_LN_BF16(2) PCPB_LN_BF16(3) PCPB_LN_BF16(4)
+#undef PCPB_LN_BF16
   PCPB_LN_VEC(1) PCPB_LN_VEC(2) PCPB_LN_VEC(3) PCPB_LN_VEC(4)
 #undef PCPB_LN_VEC
   if (!done)
