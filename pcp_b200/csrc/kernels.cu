@@ -241,62 +241,6 @@ __global__ void __launch_bounds__(256) k_rmsnorm_bwd_vec(const T* __restrict__ x
   }
 }
 
-// bf16 form for d = 256 * NCH: the row's x and dy stay packed in registers (one 16-byte read of each per chunk, no
-// second pass over memory) and every bf16 rounding point of the graph is one operation on a pair (bf16x2 multiply or
-// packed convert); arithmetic per element as in k_rmsnorm_bwd_vec.
-template <int NCH>
-__global__ void __launch_bounds__(256) k_rmsnorm_bwd_bf16(const bf16* __restrict__ x, const float* __restrict__ tsave,
-                                                          const bf16* __restrict__ dy, const bf16* __restrict__ dres, int M,
-                                                          bf16* __restrict__ dx) {
-  constexpr int d = 256 * NCH;
-  const int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (m >= M) return;
-  const bf16* xr = x + (size_t)m * d;
-  const bf16* dyr = dy + (size_t)m * d;
-  uint4 xa[NCH], ga[NCH];
-#pragma unroll
-  for (int k = 0; k < NCH; ++k) {
-    xa[k] = *reinterpret_cast<const uint4*>(xr + k * 256 + lane * 8);
-    ga[k] = *reinterpret_cast<const uint4*>(dyr + k * 256 + lane * 8);
-  }
-  float acc = 0.f;
-#pragma unroll
-  for (int k = 0; k < NCH; ++k) {
-    const uint32_t xw[4] = {xa[k].x, xa[k].y, xa[k].z, xa[k].w}, gw[4] = {ga[k].x, ga[k].y, ga[k].z, ga[k].w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t p2 = bmul2(gw[i], xw[i]);                 // bf16(g * a), two at a time
-      acc += bf_lo(p2);
-      acc += bf_hi(p2);
-    }
-  }
-  acc = warp_sum(acc);
-  const float t = tsave[m];
-  const float dr = bf16_round(acc);
-  const float rp = rsqrtf(t + PCPB_GUARD);
-  const float ds = ((dr * -0.5f) * ((rp * rp) * rp)) / (((float)d + PCPB_GUARD) + PCPB_GUARD);
-  const uint32_t r2 = pack2(rsqrtf(t), rsqrtf(t));             // bf16(rsqrt(t))
-#pragma unroll
-  for (int k = 0; k < NCH; ++k) {
-    const uint32_t xw[4] = {xa[k].x, xa[k].y, xa[k].z, xa[k].w}, gw[4] = {ga[k].x, ga[k].y, ga[k].z, ga[k].w};
-    float o[8];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t a2 = bmul2(gw[i], r2);                                        // bf16(g * r)
-      const uint32_t b2 = pack2(ds * (2.f * bf_lo(xw[i])), ds * (2.f * bf_hi(xw[i])));   // bf16(ds * 2a)
-      o[2 * i] = bf_lo(a2) + bf_lo(b2);
-      o[2 * i + 1] = bf_hi(a2) + bf_hi(b2);
-    }
-    if (dres) {
-      float e[8];
-      ld8<bf16>(dres + (size_t)m * d + k * 256 + lane * 8, e);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) o[i] += e[i];
-    }
-    st8<bf16>(dx + (size_t)m * d + k * 256 + lane * 8, o);
-  }
-}
-
 static inline bool vec_ok(int d, const void* a, const void* b = nullptr, const void* c = nullptr, const void* e = nullptr) {
   return d % 8 == 0 && ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)c) | ((uintptr_t)e)) & 15) == 0;
 }
@@ -325,16 +269,6 @@ cudaError_t launch_embed_norm_fwd(cudaStream_t st, int dt, const void* wte, cons
 cudaError_t launch_rmsnorm_bwd(cudaStream_t st, int dt, const void* x, const float* tsave, const void* dy,
                                const void* dres, int M, int d, void* dx) {
   if (M == 0) return cudaSuccess;
-  if (dt == DT_BF16 && vec_ok(d, x, dy, dres, dx) && d % 256 == 0 && d / 256 <= 8) {
-#define PCPB_RMS_BF16(NCH)                                                                                         \
-    if (d == 256 * NCH) {                                                                                          \
-      k_rmsnorm_bwd_bf16<NCH><<<cdiv(M, 8), 256, 0, st>>>((const bf16*)x, tsave, (const bf16*)dy, (const bf16*)dres, M, \
-                                                          (bf16*)dx);                                              \
-      return cudaGetLastError();                                                                                   \
-    }
-    PCPB_RMS_BF16(1) PCPB_RMS_BF16(2) PCPB_RMS_BF16(3) PCPB_RMS_BF16(4) PCPB_RMS_BF16(5) PCPB_RMS_BF16(6) PCPB_RMS_BF16(8)
-#undef PCPB_RMS_BF16
-  }
   if (vec_ok(d, x, dy, dres, dx)) {
     DISPATCH_DT(dt, (k_rmsnorm_bwd_vec<T><<<cdiv(M, 8), 256, 0, st>>>((const T*)x, nullptr, nullptr, tsave, (const T*)dy,
                                                                     (const T*)dres, M, d, 0, (T*)dx, nullptr)));
