@@ -188,6 +188,11 @@ __global__ void __launch_bounds__(256) k_rmsnorm_fwd_vec(const T* __restrict__ x
 }
 
 // dwte != nullptr: embedding variant (x rows come from wte[idx], gradient rows are atomically added to dwte)
+// dst[0..3] += (a, b, c, e) as one reduction (dst 16-byte aligned); no value is returned, so the adds are performed at L2.
+__device__ __forceinline__ void red_add_v4(float* dst, float a, float b, float c, float e) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c), "f"(e) : "memory");
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) k_rmsnorm_bwd_vec(const T* __restrict__ x, const T* __restrict__ wte,
                                                          const long long* __restrict__ idx, const float* __restrict__ tsave,
@@ -227,8 +232,10 @@ __global__ void __launch_bounds__(256) k_rmsnorm_bwd_vec(const T* __restrict__ x
 #pragma unroll
     for (int i = 0; i < 8; ++i) o[i] = rnd<T>(g[i] * r) + rnd<T>(ds * (2.f * a[i]));
     if (dwte) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) atomicAdd(dwte + (size_t)row * d + v * 8 + i, rnd<T>(o[i]));
+      // scatter into the f32 embedding gradient: two 16-byte vector reductions instead of eight scalar atomics
+      float* dst = dwte + (size_t)row * d + v * 8;
+      red_add_v4(dst, rnd<T>(o[0]), rnd<T>(o[1]), rnd<T>(o[2]), rnd<T>(o[3]));
+      red_add_v4(dst + 4, rnd<T>(o[4]), rnd<T>(o[5]), rnd<T>(o[6]), rnd<T>(o[7]));
     } else {
       if (dres) {
         float e[8];
@@ -281,7 +288,7 @@ cudaError_t launch_rmsnorm_bwd(cudaStream_t st, int dt, const void* x, const flo
 cudaError_t launch_embed_norm_bwd(cudaStream_t st, int dt, const void* wte, const long long* idx, int M, int d,
                                   int V, const void* dy, const float* tsave, float* dwte) {
   if (M == 0) return cudaSuccess;
-  if (vec_ok(d, wte, dy)) {
+  if (vec_ok(d, wte, dy, dwte)) {
     DISPATCH_DT(dt, (k_rmsnorm_bwd_vec<T><<<cdiv(M, 8), 256, 0, st>>>(nullptr, (const T*)wte, idx, tsave, (const T*)dy,
                                                                     nullptr, M, d, V, nullptr, dwte)));
     return cudaGetLastError();
