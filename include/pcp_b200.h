@@ -79,8 +79,17 @@ size_t pcpb_buffer_nbytes(const pcpb_buffer* buf);
 
 /* IreeBackend.executeWithDeviceBuffers (src/backends/iree.zig:256): blocking; inputs are borrowed; each
  * returned buffer carries one reference owned by the caller; the returned array is freed with pcpb_free.
- * Functions: compute_gradients, apply_optimizer, accumulate_gradients, model_forward_pass, main,
- * model_forward_pass_grad.  apply_optimizer uses the hyper-parameters set by pcpb_set_adam. */
+ * Functions (the names src/compiler/graph_builder.zig:56-278 and :435-726 emit):
+ *   compute_gradients              (params f32..., ids[B,T], targets[B,T]) -> (grads f32..., loss)
+ *   compute_gradients_accumulated  (params f32..., ids[S,B,T], targets[S,B,T]) -> (sum of grads f32..., sum of losses);
+ *                                  S is taken from the byte length of ids; the caller divides by S
+ *                                  (src/nodes/workers/worker.zig:1134-1187)
+ *   apply_optimizer                (p..., g..., m..., v..., t) -> (p'..., m'..., v'...), hyper-parameters of pcpb_set_adam
+ *   accumulate_gradients           (acc..., grads...) -> (acc + grads ...)
+ *   model_forward_pass, main       (params model dtype..., ids, targets) -> loss
+ *   model_forward_pass_grad        (params model dtype..., ids, targets, dloss) -> (grads model dtype...)
+ * Every function except apply_optimizer and accumulate_gradients stages its parameters in the buffers of the fused
+ * worker path and is refused with PCPB_E_STATE between pcpb_worker_begin_round and pcpb_worker_end_round. */
 int pcpb_execute(pcpb_backend* b, const char* fn, pcpb_buffer* const* in, size_t n_in, pcpb_buffer*** out, size_t* n_out);
 
 /* IreeBackend.readToHost (src/backends/iree.zig:315): blocking device -> host copy. */
@@ -109,6 +118,38 @@ int pcpb_op_gemm(pcpb_backend* b, int path, const pcpb_buffer* A, long long sam,
  * PCPB_E_CHUNK_TOO_SMALL / PCPB_E_CHUNK_EXHAUSTED as in the reference. */
 int pcpb_fifo_get_batch(pcpb_backend* b, const uint16_t* tokens, size_t n_tokens, size_t* cursor,
                         pcpb_buffer** inputs, pcpb_buffer** targets);
+
+/* ---- random-window batching, character tokenizer, master initialisation (host side) ---------------------------
+ * The generator stands in for Zig 0.13's std.Random.DefaultPrng, which the reference draws from but does not ship:
+ * xoshiro256++ seeded through SplitMix64, bounded integers by Lemire's multiply-shift with rejection, normals by
+ * Box-Muller.  UNPINNED against the Zig standard library: the same distributions, not the same sequences. */
+typedef struct pcpb_prng { uint64_t s[4]; } pcpb_prng;
+void pcpb_prng_seed(pcpb_prng* g, uint64_t seed);                       /* std.Random.DefaultPrng.init(seed) */
+uint64_t pcpb_prng_next(pcpb_prng* g);
+uint64_t pcpb_prng_uint_at_most(pcpb_prng* g, uint64_t at_most);        /* random.uintAtMost(usize, at_most) */
+/* One window start per batch row, uniform in [0, n_tokens - block - 1]; PCPB_E_CHUNK_TOO_SMALL when
+ * n_tokens <= block + 1 (src/data/loader.zig:289-291, 379-381, 469-471). */
+int pcpb_random_window_starts(pcpb_prng* g, size_t n_tokens, size_t batch, size_t block, uint64_t* starts_out);
+/* Dataset.getBatch of the random-window datasets (U16TokenDataset, TextDataset, ByteTextDataset .getBatchImpl,
+ * src/data/loader.zig:457-486, 276-307, 366-397): draws the loaded model's B window starts from `g`, gathers the
+ * windows of the host chunk (token_bytes 2: u16 stream; 4: u32 tokens of the char / byte tokenizers) and returns the
+ * [B,T] i64 inputs and 1-shifted targets as device buffers (widening on the device). */
+int pcpb_random_get_batch(pcpb_backend* b, pcpb_prng* g, const void* tokens, int token_bytes, size_t n_tokens,
+                          pcpb_buffer** inputs, pcpb_buffer** targets);
+/* CharTokenizer (src/data/loader.zig:12-89): vocabulary = the distinct bytes of the text, ascending, at most 65
+ * (vocab_chars_out has room for PCPB_CHAR_VOCAB_MAX entries; *ignored_chars_out, optional, counts the bytes beyond);
+ * encode maps unknown bytes to token 0; decode refuses unknown tokens with PCPB_E_INVALID (UnknownToken). */
+#define PCPB_CHAR_VOCAB_MAX 65
+int pcpb_char_tokenizer_build(const uint8_t* text, size_t n, uint8_t* vocab_chars_out, int* vocab_size_out,
+                              int* ignored_chars_out);
+int pcpb_char_encode(const uint8_t* vocab_chars, int vocab_size, const uint8_t* text, size_t n, uint32_t* tokens_out);
+int pcpb_char_decode(const uint8_t* vocab_chars, int vocab_size, const uint32_t* tokens, size_t n, uint8_t* text_out);
+/* DiLoCo.initializeMasterParameters (src/algorithms/diloco.zig:513-586): every element of every tensor, in argument
+ * order from one generator, is 0.02 * N(0,1) in f32; PCPB_BF16 keeps the upper 16 bits (truncation).  The reference
+ * seeds with 12345.  pcpb_init_master fills the parameter blob of the loaded artefact (what
+ * pcpb_worker_begin_round takes); pcpb_init_master_elems needs no backend. */
+int pcpb_init_master_elems(uint64_t seed, int dtype, size_t n, void* out, size_t out_bytes);
+int pcpb_init_master(const pcpb_backend* b, uint64_t seed, int dtype, void* blob_out, size_t blob_bytes);
 
 /* AdamW constants of apply_optimizer (src/optimizers/adam_mlir.zig:10-19; the reference bakes them into the
  * compiled module, src/algorithms/diloco.zig:205-211).  Defaults: lr 1e-3, 0.9, 0.999, 1e-8, 0.01, 1.0. */
@@ -147,6 +188,15 @@ int pcpb_inner_loop(pcpb_backend* b, const pcpb_inner_cfg* cfg, const void* para
 /* Current f32 working parameters / Adam state of the fused path, for checks (flat, argument order). */
 int pcpb_worker_read_state(pcpb_backend* b, int which /*0 params,1 m,2 v,3 delta,4 master,5 velocity,6 grads*/,
                            float* dst, size_t n);
+/* Overwrites one of those states from host memory (same selectors and lengths; 3 = the delta this rank publishes to
+ * the outer step, 5 = this rank's velocity shard, which needs pcpb_outer_attach_* first).  This is how a run resumed
+ * from a recovery file restores the Nesterov velocities (src/algorithms/diloco.zig:1063-1107) and, for persist_adam,
+ * the Adam moments; writing the parameters (0) also refreshes their model-dtype copy. */
+int pcpb_worker_write_state(pcpb_backend* b, int which, const float* src, size_t n);
+/* Batch sampling of the fused path: 0 = FIFO (U16TokenDatasetFifo, the default, bit-exact), 1 = random windows
+ * (U16TokenDataset.getBatchImpl, src/data/loader.zig:457-486) drawn from a generator seeded with `seed`
+ * (src/data/loader.zig:439).  Takes effect at the next pcpb_worker_set_tokens. */
+int pcpb_worker_set_sampling(pcpb_backend* b, int mode, uint64_t seed);
 /* Blocks until everything enqueued by this backend has run; returns the first asynchronous error. */
 int pcpb_synchronize(pcpb_backend* b);
 
@@ -164,7 +214,11 @@ typedef struct pcpb_outer_cfg {
 #define PCPB_IPC_HANDLE_BYTES 64
 /* Bytes to publish to the other ranks: 2 IPC handles (delta buffer, round-start parameter buffer). */
 int pcpb_outer_export(pcpb_backend* b, void* handles_out /* 2*PCPB_IPC_HANDLE_BYTES */);
-/* world ranks; all_handles: world * 2 * PCPB_IPC_HANDLE_BYTES gathered in rank order (own entry ignored). */
+/* world ranks; all_handles: world * 2 * PCPB_IPC_HANDLE_BYTES gathered in rank order (own entry ignored).
+ * Attaching again with the same (rank, world) keeps this rank's velocity shard; a different membership starts the
+ * shard at zero and the host restores the re-sharded velocities with pcpb_worker_write_state(5)
+ * (pcp_b200/diloco.py: DilocoGroup.regroup), so that a worker leaving between rounds does not reset the momentum the
+ * reference's Shepherd would have kept (src/algorithms/diloco.zig:418-444, src/optimizers/nesterov.zig:70-98). */
 int pcpb_outer_attach_ipc(pcpb_backend* b, int rank, int world, const void* all_handles);
 /* Same-process variant (several backends in one process): peers[w] for every rank, own entry included. */
 int pcpb_outer_attach_local(pcpb_backend* b, int rank, int world, pcpb_backend* const* peers);

@@ -43,8 +43,11 @@ EXPORTS = [
     "pcpb_launch_count", "pcpb_worker_last_loss", "pcpb_timer_start", "pcpb_timer_stop", "pcpb_profile_enable",
     "pcpb_profile_read", "pcpb_adamw_step_noalloc", "pcpb_stream_begin", "pcpb_stream_send", "pcpb_stream_outer",
     "pcpb_stream_outer_start", "pcpb_stream_outer_wait",
-    "pcpb_stream_merge",
+    "pcpb_stream_merge", "pcpb_prng_seed", "pcpb_prng_next", "pcpb_prng_uint_at_most", "pcpb_random_window_starts",
+    "pcpb_random_get_batch", "pcpb_char_tokenizer_build", "pcpb_char_encode", "pcpb_char_decode",
+    "pcpb_init_master_elems", "pcpb_init_master", "pcpb_worker_write_state", "pcpb_worker_set_sampling",
 ]
+CHAR_VOCAB_MAX = 65
 
 
 class BackendError(RuntimeError):
@@ -65,6 +68,11 @@ class InnerCfg(C.Structure):
 
 class OuterCfg(C.Structure):
     _fields_ = [("learning_rate", C.c_float), ("momentum", C.c_float), ("param_dtype", C.c_int)]
+
+
+class Prng(C.Structure):
+    """pcpb_prng: the generator of the random-window datasets and of the master initialisation."""
+    _fields_ = [("s", C.c_uint64 * 4)]
 
 
 class StreamCfg(C.Structure):
@@ -136,9 +144,89 @@ def load_library(path: str | None = None):
     lib.pcpb_profile_read.argtypes = [vp, C.POINTER(C.c_longlong), C.POINTER(C.c_double), C.POINTER(C.c_double)]
     lib.pcpb_adamw_step_noalloc.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ll, C.POINTER(AdamConf), C.c_float,
                                             C.c_char_p, sz]
+    u64 = C.c_uint64
+    lib.pcpb_prng_seed.argtypes = [C.POINTER(Prng), u64]; lib.pcpb_prng_seed.restype = None
+    lib.pcpb_prng_next.argtypes = [C.POINTER(Prng)]; lib.pcpb_prng_next.restype = u64
+    lib.pcpb_prng_uint_at_most.argtypes = [C.POINTER(Prng), u64]; lib.pcpb_prng_uint_at_most.restype = u64
+    lib.pcpb_random_window_starts.argtypes = [C.POINTER(Prng), sz, sz, sz, C.POINTER(u64)]
+    lib.pcpb_random_get_batch.argtypes = [vp, C.POINTER(Prng), vp, i, sz, C.POINTER(vp), C.POINTER(vp)]
+    lib.pcpb_char_tokenizer_build.argtypes = [vp, sz, vp, C.POINTER(i), C.POINTER(i)]
+    lib.pcpb_char_encode.argtypes = [vp, i, vp, sz, vp]
+    lib.pcpb_char_decode.argtypes = [vp, i, vp, sz, vp]
+    lib.pcpb_init_master_elems.argtypes = [u64, i, sz, vp, sz]
+    lib.pcpb_init_master.argtypes = [vp, u64, i, vp, sz]
+    lib.pcpb_worker_write_state.argtypes = [vp, i, vp, sz]
+    lib.pcpb_worker_set_sampling.argtypes = [vp, i, u64]
     if path is None:
         _lib = lib
     return lib
+
+
+class RandomGenerator:
+    """std.Random.DefaultPrng stand-in of the library (xoshiro256++ / SplitMix64; unpinned against Zig's)."""
+
+    def __init__(self, seed: int):
+        self._lib = load_library()
+        self.state = Prng()
+        self._lib.pcpb_prng_seed(C.byref(self.state), seed)
+
+    def next(self) -> int:
+        return int(self._lib.pcpb_prng_next(C.byref(self.state)))
+
+    def uint_at_most(self, at_most: int) -> int:
+        return int(self._lib.pcpb_prng_uint_at_most(C.byref(self.state), at_most))
+
+    def window_starts(self, n_tokens: int, batch: int, block: int) -> np.ndarray:
+        out = np.empty(batch, np.uint64)
+        rc = self._lib.pcpb_random_window_starts(C.byref(self.state), n_tokens, batch, block,
+                                                 out.ctypes.data_as(C.POINTER(C.c_uint64)))
+        if rc:
+            raise BackendError(rc, "ChunkTooSmall" if rc == E_CHUNK_TOO_SMALL else "bad arguments")
+        return out
+
+
+class CharTokenizer:
+    """CharTokenizer of src/data/loader.zig:12-89 (host function of the library)."""
+
+    def __init__(self, text: bytes):
+        self._lib = load_library()
+        raw = np.frombuffer(text, np.uint8)
+        self._chars = np.zeros(CHAR_VOCAB_MAX, np.uint8)
+        n, ign = C.c_int(), C.c_int()
+        rc = self._lib.pcpb_char_tokenizer_build(raw.ctypes.data, raw.size, self._chars.ctypes.data, C.byref(n), C.byref(ign))
+        if rc:
+            raise BackendError(rc, "char tokenizer: bad arguments")
+        self.vocab_size, self.ignored = n.value, ign.value
+
+    @property
+    def chars(self):
+        return [int(c) for c in self._chars[: self.vocab_size]]
+
+    def encode(self, text: bytes) -> np.ndarray:
+        raw = np.frombuffer(text, np.uint8)
+        out = np.empty(raw.size, np.uint32)
+        rc = self._lib.pcpb_char_encode(self._chars.ctypes.data, self.vocab_size, raw.ctypes.data, raw.size, out.ctypes.data)
+        if rc:
+            raise BackendError(rc, "char encode: bad arguments")
+        return out
+
+    def decode(self, tokens) -> bytes:
+        tok = np.ascontiguousarray(tokens, np.uint32)
+        out = np.empty(tok.size, np.uint8)
+        rc = self._lib.pcpb_char_decode(self._chars.ctypes.data, self.vocab_size, tok.ctypes.data, tok.size, out.ctypes.data)
+        if rc:
+            raise BackendError(rc, "UnknownToken")
+        return out.tobytes()
+
+
+def init_master_elems(seed: int, n: int, dtype=F32) -> np.ndarray:
+    """n elements of 0.02 * N(0,1) (src/algorithms/diloco.zig:513-586): float32 values or bf16 bit patterns."""
+    lib = load_library()
+    out = np.empty(n, np.float32 if dtype == F32 else np.uint16)
+    rc = lib.pcpb_init_master_elems(seed, dtype, n, out.ctypes.data, out.nbytes)
+    if rc:
+        raise BackendError(rc, "init_master: bad arguments")
+    return out
 
 
 def inspect_artifact(artifact) -> dict:
@@ -353,6 +441,28 @@ class Backend:
         shp = (info["batch"], info["block"])
         return DeviceBuffer(self._lib, x, shp, I64), DeviceBuffer(self._lib, y, shp, I64), cur.value
 
+    def random_get_batch(self, gen: RandomGenerator, tokens: np.ndarray):
+        """-> (inputs DeviceBuffer, targets DeviceBuffer); tokens: host uint16 or uint32 array (the worker's chunk)."""
+        tok = np.ascontiguousarray(tokens)
+        if tok.dtype not in (np.uint16, np.uint32):
+            raise ValueError("tokens must be uint16 or uint32")
+        x, y = C.c_void_p(), C.c_void_p()
+        self._check(self._lib.pcpb_random_get_batch(self._h, C.byref(gen.state), tok.ctypes.data, tok.dtype.itemsize,
+                                                    tok.size, C.byref(x), C.byref(y)))
+        info = self.model_info()
+        shp = (info["batch"], info["block"])
+        return DeviceBuffer(self._lib, x, shp, I64), DeviceBuffer(self._lib, y, shp, I64)
+
+    def init_master(self, seed: int = 12345, param_dtype=F32) -> np.ndarray:
+        """The Shepherd's initial master parameters for the loaded model as a blob for worker_begin_round."""
+        P = self.model_info()["total_params"]
+        out = np.empty(P, np.float32 if param_dtype == F32 else np.uint16)
+        self._check(self._lib.pcpb_init_master(self._h, seed, param_dtype, out.ctypes.data, out.nbytes))
+        return out
+
+    def worker_set_sampling(self, mode: str = "fifo", seed: int = 0):
+        self._check(self._lib.pcpb_worker_set_sampling(self._h, {"fifo": 0, "random": 1}[mode], seed))
+
     def set_adam(self, learning_rate=1e-3, beta1=0.9, beta2=0.999, epsilon=1e-8, weight_decay=0.01,
                  max_grad_norm=1.0):
         conf = AdamConf(learning_rate, beta1, beta2, epsilon, weight_decay, max_grad_norm)
@@ -439,6 +549,32 @@ class Backend:
         self._check(self._lib.pcpb_worker_read_state(self._h, sel, out.ctypes.data, n))
         return out
 
+    def worker_write_state(self, which: str, values):
+        sel = {"params": 0, "m": 1, "v": 2, "delta": 3, "master": 4, "velocity": 5}[which]
+        a = np.ascontiguousarray(values, np.float32)
+        self._check(self._lib.pcpb_worker_write_state(self._h, sel, a.ctypes.data, a.size))
+
+    def load_recovery(self, path: str):
+        """Restores a run from the Shepherd's recovery file (src/algorithms/diloco.zig:1063-1107): the master
+        parameters become the next round's start and this rank's slice of the Nesterov velocities is written into
+        its shard (attach the outer step first).  -> (parameter blob dtype code, data-manager bytes)."""
+        from . import formats
+        from .diloco import shard_range
+        params, vels, data_manager = formats.read_recovery(path, self.param_shapes())
+        if not params:
+            raise BackendError(1, "recovery file holds no parameters")
+        flat = np.concatenate([t.reshape(-1) for t in params])
+        dt = BF16 if flat.dtype == np.uint16 else F32
+        master = (flat.astype(np.uint32) << 16).view(np.float32) if dt == BF16 else flat.astype(np.float32)
+        self.worker_write_state("master", master)
+        if vels is not None and hasattr(self, "_shard_len"):
+            v = np.concatenate([np.asarray(t, np.float32).reshape(-1) for t in vels])
+            lo, hi = shard_range(v.size, self._world, self._rank)
+            shard = np.zeros(self._shard_len, np.float32)
+            shard[: hi - lo] = v[lo:hi]
+            self.worker_write_state("velocity", shard)
+        return dt, data_manager
+
     # -- checkpoints in the reference's file format (pcp_b200/formats.py)
     def save_checkpoint(self, path: str, param_dtype=F32):
         """Writes the master parameters on the device as a `checkpoint_<step>.bin` file of the reference
@@ -468,19 +604,20 @@ class Backend:
         self._check(self._lib.pcpb_outer_export(self._h, buf))
         return buf.raw
 
-    def _set_shard(self, world):
+    def _set_shard(self, world, rank=0):
+        self._world, self._rank = world, rank
         P = self.model_info()["total_params"]
         s = (P + world - 1) // world
         self._shard_len = (s + 255) // 256 * 256
 
     def outer_attach_ipc(self, rank, world, all_handles: bytes):
         self._check(self._lib.pcpb_outer_attach_ipc(self._h, rank, world, all_handles))
-        self._set_shard(world)
+        self._set_shard(world, rank)
 
     def outer_attach_local(self, rank, peers):
         arr = (C.c_void_p * len(peers))(*[p._h for p in peers])
         self._check(self._lib.pcpb_outer_attach_local(self._h, rank, len(peers), arr))
-        self._set_shard(len(peers))
+        self._set_shard(len(peers), rank)
 
     def outer_prepare(self, learning_rate=0.7, momentum=0.9, param_dtype=F32):
         cfg = OuterCfg(learning_rate, momentum, param_dtype)

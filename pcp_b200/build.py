@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libpcp_b200.so")
-SOURCES = ["kernels.cu", "kernels_gpt.cu", "gemm_tc.cu", "attn_flash.cu", "attn_tc.cu", "runtime.cu", "noalloc.cu", "model.cpp"]
+SOURCES = ["kernels.cu", "kernels_gpt.cu", "gemm_tc.cu", "attn_flash.cu", "attn_tc.cu", "runtime.cu", "noalloc.cu", "model.cpp", "host_data.cpp"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 
@@ -24,7 +24,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     headers.append(os.path.join(HERE, "..", "include", "pcp_b200.h"))
-    objs = []
+    objs, jobs = [], []
     for src in SOURCES:
         s = os.path.join(CSRC, src)
         o = os.path.join(CSRC, os.path.splitext(src)[0] + ".o")
@@ -33,9 +33,14 @@ def build(verbose: bool = False, force: bool = False) -> str:
             cmd = [nvcc] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             if verbose:
                 print(" ".join(cmd), flush=True)
-            subprocess.run(cmd, check=True)
+            jobs.append(cmd)
+    # the translation units are independent: compile them side by side
+    procs = [subprocess.Popen(cmd) for cmd in jobs]
+    failed = [cmd for cmd, p in zip(jobs, procs) if p.wait() != 0]
+    if failed:
+        raise subprocess.CalledProcessError(1, failed[0])
     if force or _stale(OUT, objs):
-        cmd = [nvcc, "-shared", "-o", OUT] + objs
+        cmd = [nvcc, "-Wno-deprecated-gpu-targets", "-shared", "-o", OUT] + objs
         subprocess.run(cmd, check=True)
     return OUT
 

@@ -66,6 +66,32 @@ cudaError_t launch_fifo_batch(cudaStream_t st, const uint16_t* tokens, long long
   return cudaGetLastError();
 }
 
+// Random-window batch: row b takes `block` tokens from starts[b], targets are the same window shifted by one,
+// widened to i64 (U16TokenDataset / TextDataset / ByteTextDataset .getBatchImpl, src/data/loader.zig:276-307,
+// 366-397, 457-486).  TOK: uint16_t (pre-tokenised streams) or uint32_t (char / byte tokenizers).
+template <typename TOK>
+__global__ void k_window_batch(const TOK* __restrict__ tok, const unsigned long long* __restrict__ starts, int batch,
+                               long long block, long long* __restrict__ x, long long* __restrict__ y) {
+  const long long total = (long long)batch * block;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const long long b = i / block, t = i - b * block;
+    const unsigned long long s = starts[b] + (unsigned long long)t;
+    x[i] = (long long)tok[s];
+    y[i] = (long long)tok[s + 1];
+  }
+}
+cudaError_t launch_window_batch(cudaStream_t st, const void* tokens, int token_bytes, const unsigned long long* starts,
+                                int batch, long long block, long long* inputs, long long* targets) {
+  const long long total = (long long)batch * block;
+  if (total == 0) return cudaSuccess;
+  const unsigned grid = min(cdiv(total, 256), 148u * 8);
+  if (token_bytes == 2) k_window_batch<uint16_t><<<grid, 256, 0, st>>>((const uint16_t*)tokens, starts, batch, block, inputs, targets);
+  else k_window_batch<uint32_t><<<grid, 256, 0, st>>>((const uint32_t*)tokens, starts, batch, block, inputs, targets);
+  return cudaGetLastError();
+}
+
 // =================================================================================================
 // RMSNorm (parameter free).  y = x * T(rsqrt(sum(x^2)/(d+1e-4) + 1e-5)); tsave = the rsqrt argument.
 // =================================================================================================

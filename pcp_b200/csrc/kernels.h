@@ -41,6 +41,9 @@ cudaError_t launch_convert_f32(cudaStream_t st, int dt, const float* in, void* o
 cudaError_t launch_widen_to_f32(cudaStream_t st, int dt, const void* in, float* out, size_t n);
 cudaError_t launch_fifo_batch(cudaStream_t st, const uint16_t* tokens, long long cursor, long long bt,
                               long long* inputs, long long* targets);
+// tokens: device pointer to uint16_t (token_bytes 2) or uint32_t (4) tokens; starts: device array of `batch` offsets
+cudaError_t launch_window_batch(cudaStream_t st, const void* tokens, int token_bytes, const unsigned long long* starts,
+                                int batch, long long block, long long* inputs, long long* targets);
 cudaError_t launch_embed_norm_fwd(cudaStream_t st, int dt, const void* wte, const long long* idx, int M, int d,
                                   int V, void* x, float* tsave);
 cudaError_t launch_embed_norm_bwd(cudaStream_t st, int dt, const void* wte, const long long* idx, int M, int d,

@@ -264,6 +264,32 @@ std::string parse_artifact(const char* text, size_t n, ModelConfig* cfg) {
     }
     if (!found) return "soft-cap constant not found (expected tanh(z / cap) * cap before the loss)";
   }
+  // Body fingerprint.  The signature alone does not tell the family: a graph with these parameter shapes but, say, a
+  // GELU MLP or no QK-norm would otherwise be trained with the built-in nanochat arithmetic.  Per layer the family
+  // has four rsqrt (two block norms, the q and k norms), five power (their squares and the ReLU^2), one maximum, one
+  // exponential (softmax), eight dot_general and one select (causal mask); the head adds two rsqrt / power (embedding
+  // and final norm), one tanh (soft-cap), one exponential and one log (cross entropy), one dot_general and two
+  // selects (ignored targets), and names the ignore index -1.
+  {
+    auto count = [&](const char* op) {
+      size_t n = 0;
+      const std::string pat = std::string("= stablehlo.") + op + " ";
+      for (size_t q = 0; (q = src.find(pat, q)) != std::string::npos; ++q) ++n;
+      return (int64_t)n;
+    };
+    struct { const char* op; int64_t want; } expect[] = {
+        {"rsqrt", 4 * c.L + 2}, {"power", 5 * c.L + 2}, {"maximum", c.L}, {"tanh", 1}, {"exponential", c.L + 1},
+        {"log", 1}, {"dot_general", 8 * c.L + 1}, {"select", c.L + 2}, {"erf", 0}, {"logistic", 0}, {"sqrt", 0},
+        {"sine", 0}, {"cosine", 0}, {"abs", 0}, {"minimum", 0}, {"clamp", 0}, {"convolution", 0}};
+    for (auto& e : expect) {
+      const int64_t got = count(e.op);
+      if (got != e.want)
+        return std::string("not a nanochat-family body: ") + std::to_string(got) + " stablehlo." + e.op +
+               " ops where the family has " + std::to_string(e.want) +
+               " (RMSNorm + RoPE + QK-norm + ReLU^2 + soft-capped cross entropy expected)";
+    }
+    if (src.find("dense<-1>") == std::string::npos) return "expected ignore_index -1 in the loss";
+  }
   c.ignore_index = -1;
 
   int64_t off = 0;

@@ -80,6 +80,8 @@ void free_workspace(pcpb_backend* b) {
   for (void* p : b->ws.allocs) cudaFree(p);
   b->ws = Workspace();
   if (b->tokens_stage) { cudaFree(b->tokens_stage); b->tokens_stage = nullptr; b->stage_cap = 0; }
+  if (b->window_stage) { cudaFree(b->window_stage); b->window_stage = nullptr; b->window_stage_cap = 0; }
+  if (b->starts_dev) { cudaFree(b->starts_dev); b->starts_dev = nullptr; }
   for (void* p : b->ipc_opened) cudaIpcCloseMemHandle(p);
   b->ipc_opened.clear(); b->peer_delta.clear(); b->peer_theta0.clear();
   if (b->velocity) { cudaFree(b->velocity); b->velocity = nullptr; }
@@ -208,9 +210,12 @@ int gemm(pcpb_backend* b, GemmArgs g) {
   g.scratch = b->ws.tc_scratch; g.scratch_bytes = b->ws.tc_scratch_bytes; g.err_word = b->ws.tc_err;
   if (!b->force_generic && b->cfg.dtype == DT_BF16 && gemm_tc_supported(g)) {
     if (b->profiling) {
-      if (b->prof_used + 2 > b->prof_events.size()) {
-        int r = drain_profile(b);
-        if (r) return r;
+      // the pool grows instead of being drained: collecting durations needs a stream synchronisation, which must
+      // not land inside a region the caller is timing
+      while (b->prof_used + 2 > b->prof_events.size()) {
+        cudaEvent_t ev = nullptr;
+        CK(b, cudaEventCreate(&ev));
+        b->prof_events.push_back(ev);
       }
       cudaEvent_t e0 = b->prof_events[b->prof_used], e1 = b->prof_events[b->prof_used + 1];
       CK(b, cudaEventRecord(e0, b->stream));
@@ -450,6 +455,42 @@ int forward_backward_gpt(pcpb_backend* b, const void* wts, const long long* ids,
   return PCPB_OK;
 }
 
+// Random-window batch of the loaded model's [B,T] into (ids, targets): the starts come from `g` on the host, the
+// gather and the widening run on the device.  Host chunks: the B windows of T+1 tokens are gathered into a staging
+// buffer first, so that only (T+1)*B tokens cross PCIe.
+int random_batch_into(pcpb_backend* b, pcpb_prng* g, const void* tokens, int token_bytes, size_t n_tokens,
+                      bool on_device, long long* ids, long long* targets) {
+  const ModelConfig& c = b->cfg;
+  const size_t B = (size_t)c.B, T = (size_t)c.T;
+  std::vector<uint64_t> starts(B);
+  const int rc = pcpb_random_window_starts(g, n_tokens, B, T, starts.data());
+  if (rc == PCPB_E_CHUNK_TOO_SMALL) return fail(b, rc, "ChunkTooSmall: token chunk not longer than T+1");
+  if (rc) return fail(b, rc, "bad random-batch arguments");
+  if (!b->starts_dev) CK(b, cudaMalloc(&b->starts_dev, B * 8));
+  const void* base = tokens;
+  if (!on_device) {
+    const size_t wlen = T + 1, need = B * wlen * (size_t)token_bytes;
+    if (b->window_stage_cap < need) {
+      if (b->window_stage) { CK(b, cudaStreamSynchronize(b->stream)); cudaFree(b->window_stage); b->window_stage = nullptr; }
+      CK(b, cudaMalloc(&b->window_stage, need));
+      b->window_stage_cap = need;
+    }
+    // the previous step's copy out of the host gather buffer must have been issued completely: a copy from pageable
+    // memory is staged before cudaMemcpyAsync returns, so the buffer can be refilled here
+    b->window_host.resize((need + 1) / 2);
+    char* dst = (char*)b->window_host.data();
+    for (size_t i = 0; i < B; ++i) {
+      memcpy(dst + i * wlen * token_bytes, (const char*)tokens + starts[i] * (size_t)token_bytes, wlen * token_bytes);
+      starts[i] = i * wlen;
+    }
+    CK(b, cudaMemcpyAsync(b->window_stage, dst, need, cudaMemcpyHostToDevice, b->stream));
+    base = b->window_stage;
+  }
+  CK(b, cudaMemcpyAsync(b->starts_dev, starts.data(), B * 8, cudaMemcpyHostToDevice, b->stream));
+  KL(b, 1, launch_window_batch(b->stream, base, token_bytes, b->starts_dev, (int)B, (long long)T, ids, targets));
+  return PCPB_OK;
+}
+
 AdamHyper hyper_at(const pcpb_backend* b, float t) {
   AdamHyper h = b->adam;
   h.m_corr = fmaxf(1.f - powf(h.beta1, t), h.eps);
@@ -686,6 +727,52 @@ int pcpb_execute(pcpb_backend* b, const char* fn, pcpb_buffer* const* in, size_t
   const int64_t scalar_shape[1] = {0};
   auto data_ok = [&](const pcpb_buffer* x) { return x && x->dtype == PCPB_I64 && x->nbytes == (size_t)c.M() * 8; };
 
+  // These functions stage their inputs in the fused worker's live buffers (parameters, model-dtype copy,
+  // gradients).  Inside an open round that would silently replace the round's working parameters, so they are
+  // refused until pcpb_worker_end_round.
+  const bool stages_params = name == "compute_gradients" || name == "compute_gradients_accumulated" ||
+                             name == "model_forward_pass" || name == "main" || name == "model_forward_pass_grad";
+  if (stages_params && b->in_round)
+    return fail(b, PCPB_E_STATE, name + " cannot run inside an open worker round (it would overwrite the round's working "
+                                        "parameters): call pcpb_worker_end_round first");
+  if (name == "compute_gradients_accumulated") {
+    // GraphBuilder.buildAccumulatedTrainingGraph (src/compiler/graph_builder.zig:435-726): params f32..., ids and
+    // targets folded as [S, B, T]; an scf.for over the S micro-batches sums the f32 gradients and the losses.  The
+    // caller (src/nodes/workers/worker.zig:1134-1187) divides both by S afterwards.
+    if (n_in != N + 2) return fail(b, PCPB_E_INVALID, "compute_gradients_accumulated expects params..., ids[S,B,T], targets[S,B,T]");
+    if ((r = check_param_inputs(b, in, 0, PCPB_F32, "compute_gradients_accumulated"))) return r;
+    const size_t mb = (size_t)c.M() * 8;
+    const pcpb_buffer *bi = in[N], *bt = in[N + 1];
+    if (!bi || !bt || bi->dtype != PCPB_I64 || bt->dtype != PCPB_I64 || bi->nbytes == 0 || bi->nbytes % mb ||
+        bt->nbytes != bi->nbytes)
+      return fail(b, PCPB_E_INVALID, "ids/targets must be i64 [S,B,T] with S >= 1");
+    const size_t S = bi->nbytes / mb;
+    if ((r = gather_flat(b, in, 0, w.theta, 4))) return r;
+    if (c.dtype != DT_F32) KL(b, 1, launch_convert_f32(b->stream, c.dtype, w.theta, w.shadow, P));
+    Block *gb = nullptr, *lb = nullptr;
+    if ((r = alloc_block(b, P * 4, &gb))) return r;
+    if ((r = alloc_block(b, 4, &lb))) { block_release(gb); return r; }
+    cudaError_t e = cudaMemsetAsync(gb->ptr, 0, P * 4, b->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(lb->ptr, 0, 4, b->stream);
+    for (size_t s = 0; s < S && r == PCPB_OK && e == cudaSuccess; ++s) {
+      r = forward_backward(b, w.shadow, (const long long*)bi->ptr + s * (size_t)c.M(),
+                           (const long long*)bt->ptr + s * (size_t)c.M(), w.grads, w.loss, true);
+      if (r) break;
+      b->launches += 2;
+      e = launch_axpy_f32(b->stream, (float*)gb->ptr, w.grads, 1.f, P);
+      if (e == cudaSuccess) e = launch_axpy_f32(b->stream, (float*)lb->ptr, w.loss, 1.f, 1);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(b->stream);
+    if (r == PCPB_OK && e != cudaSuccess) r = fail(b, PCPB_E_CUDA, std::string("compute_gradients_accumulated failed: ") + cudaGetErrorString(e));
+    if (r == PCPB_OK) r = check_tc_error(b);
+    if (r) { block_release(gb); block_release(lb); return r; }
+    pcpb_buffer** o = (pcpb_buffer**)malloc(sizeof(pcpb_buffer*) * (N + 1));
+    flat_views(b, gb, PCPB_F32, o);
+    o[N] = make_view(b, lb, lb->ptr, 4, scalar_shape, 0, PCPB_F32);
+    block_release(gb); block_release(lb);
+    *out = o; *n_out = N + 1;
+    return PCPB_OK;
+  }
   if (name == "compute_gradients") {
     if (n_in != N + 2) return fail(b, PCPB_E_INVALID, "compute_gradients expects params..., ids, targets");
     if ((r = check_param_inputs(b, in, 0, PCPB_F32, "compute_gradients"))) return r;
@@ -909,6 +996,67 @@ int pcpb_fifo_get_batch(pcpb_backend* b, const uint16_t* tokens, size_t n_tokens
   return PCPB_OK;
 }
 
+int pcpb_random_get_batch(pcpb_backend* b, pcpb_prng* g, const void* tokens, int token_bytes, size_t n_tokens,
+                          pcpb_buffer** inputs, pcpb_buffer** targets) {
+  int r = require_loaded(b);
+  if (r) return r;
+  if (!g || !tokens || !inputs || !targets || (token_bytes != 2 && token_bytes != 4))
+    return fail(b, PCPB_E_INVALID, "bad get_batch arguments");
+  DeviceGuard dg(b->device);
+  const ModelConfig& c = b->cfg;
+  const size_t BT = (size_t)c.M();
+  Block *xb = nullptr, *yb = nullptr;
+  if ((r = alloc_block(b, BT * 8, &xb))) return r;
+  if ((r = alloc_block(b, BT * 8, &yb))) { block_release(xb); return r; }
+  r = random_batch_into(b, g, tokens, token_bytes, n_tokens, false, (long long*)xb->ptr, (long long*)yb->ptr);
+  if (r == PCPB_OK && cudaStreamSynchronize(b->stream) != cudaSuccess) r = fail(b, PCPB_E_CUDA, "get_batch failed");
+  if (r) { block_release(xb); block_release(yb); return r; }
+  const int64_t shp[2] = {c.B, c.T};
+  *inputs = make_view(b, xb, xb->ptr, BT * 8, shp, 2, PCPB_I64);
+  *targets = make_view(b, yb, yb->ptr, BT * 8, shp, 2, PCPB_I64);
+  block_release(xb); block_release(yb);
+  return PCPB_OK;
+}
+
+int pcpb_init_master(const pcpb_backend* b, uint64_t seed, int dtype, void* blob_out, size_t blob_bytes) {
+  if (!b || !b->loaded) return PCPB_E_ARTIFACT;
+  return pcpb_init_master_elems(seed, dtype, (size_t)b->cfg.total_params, blob_out, blob_bytes);
+}
+
+int pcpb_worker_set_sampling(pcpb_backend* b, int mode, uint64_t seed) {
+  if (!b) return PCPB_E_INVALID;
+  if (mode != 0 && mode != 1) return fail(b, PCPB_E_INVALID, "sampling mode must be 0 (fifo) or 1 (random)");
+  b->sampling = mode;
+  pcpb_prng_seed(reinterpret_cast<pcpb_prng*>(b->prng_state), seed);
+  return PCPB_OK;
+}
+
+int pcpb_worker_write_state(pcpb_backend* b, int which, const float* src, size_t n) {
+  int r = require_loaded(b);
+  if (r) return r;
+  DeviceGuard g(b->device);
+  Workspace& w = b->ws;
+  const size_t P = (size_t)b->cfg.total_params;
+  float* dst = nullptr;
+  size_t len = P;
+  switch (which) {
+    case 0: dst = w.theta; break;
+    case 1: dst = w.mstate; break;
+    case 2: dst = w.vstate; break;
+    case 3: dst = w.delta; break;
+    case 4: dst = w.theta0; break;
+    case 5: dst = b->velocity; len = (size_t)b->shard_len; break;
+    default: return fail(b, PCPB_E_INVALID, "this state cannot be written");
+  }
+  if (!dst) return fail(b, PCPB_E_STATE, "that state does not exist yet");
+  if (n != len || !src) return fail(b, PCPB_E_INVALID, "state length mismatch");
+  CK(b, cudaMemcpyAsync(dst, src, n * 4, cudaMemcpyHostToDevice, b->stream));
+  if (which == 0 && b->cfg.dtype != DT_F32) KL(b, 1, launch_convert_f32(b->stream, b->cfg.dtype, w.theta, w.shadow, P));
+  if (which == 4) b->have_master = true;
+  CK(b, cudaStreamSynchronize(b->stream));
+  return PCPB_OK;
+}
+
 // ---- fused worker round ---------------------------------------------------------------------------
 int pcpb_worker_begin_round(pcpb_backend* b, const pcpb_inner_cfg* cfg, const void* params_blob, size_t blob_bytes) {
   int r = require_loaded(b);
@@ -967,9 +1115,14 @@ int pcpb_worker_step(pcpb_backend* b) {
   const size_t P = (size_t)c.total_params, BT = (size_t)c.M(), needed = BT + 1;
   if (b->steps_done >= w.loss_capacity) return fail(b, PCPB_E_STATE, "more steps than tau in this round");
   const int acc = b->accumulation_steps;
-  if (b->n_tokens < needed) return fail(b, PCPB_E_CHUNK_TOO_SMALL, "ChunkTooSmall: token chunk shorter than B*T+1");
+  if (b->sampling == 0 && b->n_tokens < needed) return fail(b, PCPB_E_CHUNK_TOO_SMALL, "ChunkTooSmall: token chunk shorter than B*T+1");
   float* loss_slot = w.loss_record + b->steps_done;
   for (int a = 0; a < acc; ++a) {
+    if (b->sampling == 1) {
+      if ((r = random_batch_into(b, reinterpret_cast<pcpb_prng*>(b->prng_state), b->tokens_src, 2, b->n_tokens,
+                                 b->tokens_on_device != 0, w.ids, w.targets)))
+        return r;
+    } else {
     if (b->cursor + needed > b->n_tokens) return fail(b, PCPB_E_CHUNK_EXHAUSTED, "ChunkExhausted: not enough tokens left for a batch");
     const uint16_t* win;
     long long cur;
@@ -985,6 +1138,7 @@ int pcpb_worker_step(pcpb_backend* b) {
     }
     KL(b, 1, launch_fifo_batch(b->stream, win, cur, (long long)BT, w.ids, w.targets));
     b->cursor += needed;
+    }
     if ((r = forward_backward(b, w.shadow, w.ids, w.targets, w.grads, w.loss, true))) return r;
     KL(b, 1, launch_axpy_f32(b->stream, loss_slot, w.loss, 1.f, 1));
     if (acc > 1) {
@@ -1149,10 +1303,15 @@ static int setup_shard(pcpb_backend* b, int rank, int world) {
   const long long P = b->cfg.total_params;
   long long S = (P + world - 1) / world;
   S = (S + 255) / 256 * 256;                 // shard length, a multiple of 256 elements
+  // the same (rank, world) again: the shard, and with it the momentum of the outer optimiser, is kept; another
+  // membership starts at zero and the host writes the re-sharded velocities (pcpb_worker_write_state, selector 5)
+  const bool keep = b->velocity && b->velocity_init && b->rank == rank && b->world == world && b->shard_len == S;
   b->rank = rank; b->world = world; b->shard_len = S;
-  if (b->velocity) { cudaFree(b->velocity); b->velocity = nullptr; }
-  CK(b, cudaMalloc(&b->velocity, (size_t)S * 4));
-  CK(b, cudaMemset(b->velocity, 0, (size_t)S * 4));
+  if (!keep) {
+    if (b->velocity) { CK(b, cudaStreamSynchronize(b->stream)); cudaFree(b->velocity); b->velocity = nullptr; }
+    CK(b, cudaMalloc(&b->velocity, (size_t)S * 4));
+    CK(b, cudaMemset(b->velocity, 0, (size_t)S * 4));
+  }
   b->velocity_init = true;
   b->peer_delta.assign(world, nullptr); b->peer_theta0.assign(world, nullptr);
   b->peer_delta[rank] = b->ws.delta; b->peer_theta0[rank] = b->ws.theta0;

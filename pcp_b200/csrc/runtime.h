@@ -92,6 +92,12 @@ struct pcpb_backend {
   uint16_t* tokens_stage = nullptr;          // device staging for one step's window (host-token mode)
   size_t stage_cap = 0;
   bool have_master = false;                  // theta0 holds the master parameters of the next round
+  int sampling = 0;                          // 0 FIFO, 1 random windows
+  uint64_t prng_state[4] = {0, 0, 0, 0};     // generator of the random-window starts (pcpb_prng)
+  unsigned long long* starts_dev = nullptr;  // device: one window start per batch row
+  uint16_t* window_stage = nullptr;          // device staging of the gathered windows (host-token mode)
+  size_t window_stage_cap = 0;
+  std::vector<uint16_t> window_host;         // host gather buffer
   // outer step
   int rank = 0, world = 1;
   std::vector<float*> peer_delta, peer_theta0;

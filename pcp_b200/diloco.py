@@ -27,24 +27,48 @@ def shard_range(total_params: int, world: int, rank: int):
     return lo, min(lo + s, total_params)
 
 
+def reshard_velocity(old_shards, total_params: int, new_world: int, new_rank: int):
+    """The velocity shard of `new_rank` in a group of `new_world` ranks, cut from the shards of the previous group.
+
+    old_shards: one float32 array per previous rank (its shard as the backend returns it, padding included), or
+    None for a rank whose state was lost (it died without handing its shard over): that slice restarts at zero, the
+    rest of the momentum survives.  The reference keeps all velocities on the Shepherd, so a worker that leaves never
+    costs it any (src/algorithms/diloco.zig:418-444, src/optimizers/nesterov.zig:70-98); here they are spread over
+    the workers and have to be cut again when the membership changes."""
+    import numpy as np
+    old_world = len(old_shards)
+    full = np.zeros(total_params, np.float32)
+    for r, sh in enumerate(old_shards):
+        lo, hi = shard_range(total_params, old_world, r)
+        if sh is not None and hi > lo:
+            full[lo:hi] = np.asarray(sh, np.float32)[: hi - lo]
+    out = np.zeros(shard_len(total_params, new_world), np.float32)
+    lo, hi = shard_range(total_params, new_world, new_rank)
+    out[: hi - lo] = full[lo:hi]
+    return out
+
+
 class TorchDistTransport:
-    def __init__(self, dist):
+    """torch.distributed as the transport; `group` restricts it to a sub-group (ranks are then group ranks)."""
+
+    def __init__(self, dist, group=None):
         self.dist = dist
-        self.rank = dist.get_rank()
-        self.world = dist.get_world_size()
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
 
     def barrier(self):
-        self.dist.barrier()
+        self.dist.barrier(group=self.group)
 
     def all_gather_bytes(self, payload: bytes):
         out = [None] * self.world
-        self.dist.all_gather_object(out, payload)
+        self.dist.all_gather_object(out, payload, group=self.group)
         return out
 
     def all_reduce_mean(self, x: float) -> float:
         import torch
         t = torch.tensor([x], dtype=torch.float64)
-        self.dist.all_reduce(t)
+        self.dist.all_reduce(t, group=self.group)
         return float(t[0]) / self.world
 
 
@@ -62,6 +86,30 @@ class DilocoGroup:
         self.be.outer_attach_ipc(self.tr.rank, self.tr.world, b"".join(handles))
         self.tr.barrier()
         self.attached = True
+
+    def hand_over(self):
+        """What a rank publishes before the membership changes: the velocity shards of every rank of the current
+        group, gathered through the transport.  Every rank of the current group calls it, the ones that are about to
+        leave included (a rank leaves only between rounds, src/algorithms/diloco.zig:418-427)."""
+        import numpy as np
+        mine = np.ascontiguousarray(self.be.worker_read_state("velocity"), np.float32)
+        return [np.frombuffer(b, np.float32) for b in self.tr.all_gather_bytes(mine.tobytes())]
+
+    def regroup(self, new_transport, old_shards, total_params: int):
+        """Continue with another membership: attach over `new_transport` (the ranks that stay, renumbered) and restore
+        this rank's new velocity shard from the previous group's shards (`hand_over`; None entries = lost)."""
+        self.tr = new_transport
+        self.attach()
+        self.be.worker_write_state("velocity", reshard_velocity(old_shards, total_params, self.tr.world, self.tr.rank))
+        self.tr.barrier()
+
+    def master_checksum_agrees(self) -> bool:
+        """After an outer step every rank must hold the same master parameters: compares a checksum of each rank's
+        replica over the transport."""
+        import hashlib
+        import numpy as np
+        digest = hashlib.sha256(np.ascontiguousarray(self.be.worker_read_state("master")).tobytes()).digest()
+        return len(set(self.tr.all_gather_bytes(digest))) == 1
 
     def outer_step(self, final_loss: float, contributors=None):
         """-> (mean loss over contributors' ranks, device ms of the shard kernel)."""

@@ -17,6 +17,11 @@ HD128_GQA_BF16 = dict(vocab=512, d_model=512, n_layer=1, n_head=4, n_kv_head=2, 
 HD128_MANY_BF16 = dict(vocab=512, d_model=256, n_layer=1, n_head=2, n_kv_head=2, seq_len=256, batch=40, dtype="bf16")
 # head dim 64 (what the nanoGPT configurations of the baseline use): the mma.sync tiled attention kernels, GQA
 HD64_GQA_BF16 = dict(vocab=512, d_model=256, n_layer=2, n_head=4, n_kv_head=2, seq_len=256, batch=2, dtype="bf16")
+# The kernel shapes of BASELINE config 3 (nanochat d20: d_model 1280, 10 heads x 128, T = 2048, vocabulary 65536) at two
+# layers and batch 1: the two-CTA GEMM at K = 1280 / 5120 and N = 65536 with grouped tile order and split-K, the
+# tcgen05 attention with 16 row tiles per head, the loss kernel over 65536-wide rows, the vector-reduction embedding
+# scatter under Zipf tokens.  The oracle needs about two minutes and 25 GB of host memory for it.
+D20_SHAPES_BF16 = dict(vocab=65536, d_model=1280, n_layer=2, n_head=10, n_kv_head=10, seq_len=2048, batch=1, dtype="bf16")
 HD128_F32 = dict(vocab=512, d_model=256, n_layer=1, n_head=2, n_kv_head=1, seq_len=64, batch=2, dtype="f32")
 
 

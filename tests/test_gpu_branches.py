@@ -1,0 +1,381 @@
+"""GPU parity tests of the branches of the worker round and of the outer step that the main parity file does not
+reach: in-graph and in-code gradient accumulation, persistent Adam state, the NaN heal of the Adam moments, the
+NaN -> 0 filter of the averaged delta, a contributor subset, the refusal of staging calls inside a round, random-window
+batching, master initialisation, velocity hand-over when the membership changes, and the recovery file.  All through
+the C ABI; failures are made on the host (values written from host memory), never by faulting the GPU."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import (GPT_SMALL_F32, SMALL_BF16, SMALL_F32, bf16_bits_to_f32, f32_to_bf16_trunc_bits, flat, make_model,
+                     rel_err, seeded_params, split, tokens_for)
+from oracle.loader import FifoU16, RandomWindows
+from oracle.optim import AdamConf, NesterovConf
+from oracle.worker import TrainingModule, inner_loop, outer_step
+from pcp_b200 import BF16, F32, I64, Backend, BackendError
+from pcp_b200 import backend as bk
+from pcp_b200 import formats
+from pcp_b200.diloco import reshard_velocity, shard_range
+
+pytestmark = pytest.mark.gpu
+
+
+def _adam(be, conf):
+    be.set_adam(conf.learning_rate, conf.beta1, conf.beta2, conf.epsilon, conf.weight_decay, conf.max_grad_norm)
+
+
+def _close(got, want, tol=1e-4):
+    diff = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    bad = diff > tol + tol * np.abs(want)
+    assert bad.sum() <= max(1, got.size // 10000) and diff.max() <= 10 * tol, (int(bad.sum()), float(diff.max()))
+
+
+@pytest.mark.parametrize("cfgd", [SMALL_F32, GPT_SMALL_F32])
+def test_compute_gradients_accumulated_matches_oracle(cfgd):
+    """compute_gradients_accumulated (src/compiler/graph_builder.zig:435-726): ids / targets folded [S,B,T], outputs the
+    SUM of the micro-batch gradients and of the losses."""
+    cfg, text = make_model(cfgd)
+    mod = TrainingModule(text)
+    params = seeded_params(cfg, seed=0, std=0.05)
+    S = 3
+    ds = FifoU16(tokens_for(cfg, S, seed=4))
+    xs, ys = zip(*[ds.get_batch(cfg.batch, cfg.seq_len) for _ in range(S)])
+    ref_g = [torch.zeros_like(p) for p in params]
+    ref_loss = 0.0
+    for x, y in zip(xs, ys):
+        g, loss = mod.compute_gradients(params, torch.from_numpy(x), torch.from_numpy(y))
+        ref_g = [a + b for a, b in zip(ref_g, g)]
+        ref_loss += float(loss)
+    X, Y = np.stack(xs), np.stack(ys)
+    with Backend(0) as be:
+        be.load_session(text)
+        bufs = [be.move_to_device(p.numpy(), p.shape, F32) for p in params]
+        bufs += [be.move_to_device(X, X.shape, I64), be.move_to_device(Y, Y.shape, I64)]
+        outs = be.execute_with_device_buffers(None, "compute_gradients_accumulated", bufs)
+        assert len(outs) == len(params) + 1
+        got = [be.read_to_host(o, F32, p.shape) for o, p in zip(outs[:-1], params)]
+        loss = float(be.read_to_host(outs[-1], F32, ())[()])
+        short = be.move_to_device(Y[:2], Y[:2].shape, I64)
+        with pytest.raises(BackendError) as ei:                 # ids and targets of different S
+            be.execute_with_device_buffers(None, "compute_gradients_accumulated", bufs[:-1] + [short])
+        assert ei.value.code == bk.E_INVALID
+        for b in bufs + outs + [short]:
+            b.release()
+    assert abs(loss - ref_loss) <= 1e-4 * ref_loss
+    assert max(rel_err(a, b.numpy()) for a, b in zip(got, ref_g)) <= 1e-4
+
+
+def test_accumulation_steps_2_matches_oracle():
+    """In-code accumulation of the worker loop (src/nodes/workers/worker.zig:1189-1278): two micro-batches per inner
+    step, gradients summed then scaled by 1/2 on the host side of the reference, the loss averaged."""
+    cfg, text = make_model(SMALL_F32)
+    mod = TrainingModule(text)
+    master = seeded_params(cfg, seed=1)
+    conf = AdamConf(learning_rate=3e-4)
+    tau, acc = 4, 2
+    toks = tokens_for(cfg, tau * acc, seed=9)
+    rec = []
+    d_ref, _, p_ref, _ = inner_loop(mod, master, FifoU16(toks), tau, cfg.batch, cfg.seq_len, conf,
+                                    accumulation_steps=acc, record=rec)
+    with Backend(0) as be:
+        be.load_session(text)
+        _adam(be, conf)
+        be.worker_begin_round(tau, flat(master), param_dtype=F32, accumulation_steps=acc)
+        be.worker_set_tokens(toks)
+        for _ in range(tau):
+            be.worker_step()
+        delta, losses = be.worker_end_round(tau, param_dtype=F32)
+    np.testing.assert_allclose(losses, [r[0] for r in rec], rtol=1e-4)
+    _close(flat(master) - delta, flat(p_ref))
+
+
+def test_persist_adam_and_nan_heal():
+    """persist_adam keeps m, v and the timestep over rounds; a non-finite value in a tensor's moments at the end of a
+    round zeroes that tensor's m and v and resets the timestep (src/nodes/workers/worker.zig:1346-1369).  The NaN is
+    written into the state from the host."""
+    cfg, text = make_model(SMALL_F32)
+    mod = TrainingModule(text)
+    master = seeded_params(cfg, seed=2)
+    conf = AdamConf(learning_rate=3e-4)
+    tau = 3
+    toks = [tokens_for(cfg, tau, seed=20 + r) for r in range(3)]
+    # oracle: round 0 fresh, round 1 continues from round 0's state (parameters: theta0 - delta, as the Shepherd-less
+    # loop of this test keeps them)
+    d0, _, p0, st0 = inner_loop(mod, master, FifoU16(toks[0]), tau, cfg.batch, cfg.seq_len, conf)
+    d1, _, p1, st1 = inner_loop(mod, p0, FifoU16(toks[1]), tau, cfg.batch, cfg.seq_len, conf, adam_state=st0)
+    assert st1[2] == 1.0 + 2 * tau
+    with Backend(0) as be:
+        be.load_session(text)
+        _adam(be, conf)
+        be.worker_begin_round(tau, flat(master), param_dtype=F32, persist_adam=True)
+        be.worker_set_tokens(toks[0])
+        for _ in range(tau):
+            be.worker_step()
+        delta0, _ = be.worker_end_round(tau, param_dtype=F32)
+        _close(flat(master) - delta0, flat(p0))
+        _close(be.worker_read_state("m"), flat(st0[0]), 1e-5)
+        be.worker_begin_round(tau, flat(p0), param_dtype=F32, persist_adam=True)
+        be.worker_set_tokens(toks[1])
+        for _ in range(tau):
+            be.worker_step()
+        delta1, _ = be.worker_end_round(tau, param_dtype=F32)
+        _close(flat(p0) - delta1, flat(p1))                       # only right if m, v and t were carried over
+        _close(be.worker_read_state("v"), flat(st1[1]), 1e-7)
+        # heal: NaN in tensor 2's first moment, Inf in tensor 5's second moment
+        m, v = be.worker_read_state("m"), be.worker_read_state("v")
+        offs = np.cumsum([0] + [int(np.prod(s)) for s in cfg.param_shapes()])
+        m_bad, v_bad = m.copy(), v.copy()
+        m_bad[offs[2] + 3] = np.nan
+        v_bad[offs[5] + 1] = np.inf
+        be.worker_begin_round(0, flat(p1), param_dtype=F32, persist_adam=True)
+        be.worker_write_state("m", m_bad)
+        be.worker_write_state("v", v_bad)
+        be.worker_end_round(0, param_dtype=F32, want_delta=False)
+        m2, v2 = be.worker_read_state("m"), be.worker_read_state("v")
+        for i in range(len(offs) - 1):
+            sl = slice(offs[i], offs[i + 1])
+            if i in (2, 5):
+                assert not m2[sl].any() and not v2[sl].any()
+            else:
+                assert np.array_equal(m2[sl], m[sl]) and np.array_equal(v2[sl], v[sl])
+        # after a heal the timestep restarts at 1: one more step must equal the oracle's step with t = 1 on the healed state
+        m_h = [torch.from_numpy(x.copy()) for x in split(m2, cfg)]
+        v_h = [torch.from_numpy(x.copy()) for x in split(v2, cfg)]
+        _, _, p2, _ = inner_loop(mod, p1, FifoU16(toks[2]), 1, cfg.batch, cfg.seq_len, conf, adam_state=(m_h, v_h, 1.0))
+        be.worker_begin_round(1, flat(p1), param_dtype=F32, persist_adam=True)
+        be.worker_set_tokens(toks[2])
+        be.worker_step()
+        delta2, _ = be.worker_end_round(1, param_dtype=F32)
+        _close(flat(p1) - delta2, flat(p2))
+
+
+def _three_workers(cfg, text, dt):
+    bes = [Backend(0) for _ in range(3)]
+    for b in bes:
+        b.load_session(text)
+    for w, b in enumerate(bes):
+        b.outer_attach_local(w, bes)
+    return bes
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_outer_step_nan_delta_and_contributor_subset(dtype):
+    """The averaged delta's non-finite entries become 0 (src/algorithms/diloco.zig:975-979) and the divisor is the
+    number of contributing workers (:970): deltas written from the host, one of them holding NaN / Inf, first all
+    three workers, then workers 0 and 2 only; master and velocity bit-identical to the restated outer step."""
+    cfg, text = make_model(SMALL_BF16 if dtype == "bf16" else SMALL_F32)
+    dt = BF16 if dtype == "bf16" else F32
+    master = seeded_params(cfg, seed=5)
+    if dtype == "bf16":
+        master = [torch.from_numpy(bf16_bits_to_f32(f32_to_bf16_trunc_bits(p.numpy())).reshape(p.shape)) for p in master]
+    vel = [torch.zeros_like(p) for p in master]
+    P = flat(master).size
+    rng = np.random.default_rng(1)
+    bes = _three_workers(cfg, text, dt)
+    try:
+        for b in bes:
+            b.worker_write_state("master", flat(master))
+        for rnd, contributors in enumerate([None, [0, 2]]):
+            deltas = [(rng.standard_normal(P) * 1e-3).astype(np.float32) for _ in bes]
+            if dtype == "bf16":
+                deltas = [bf16_bits_to_f32(f32_to_bf16_trunc_bits(d)) for d in deltas]
+            deltas[0][7] = np.nan
+            deltas[2][11] = np.inf
+            deltas[1][13] = -np.inf                              # only counts while worker 1 contributes
+            for b, d in zip(bes, deltas):
+                b.worker_write_state("delta", d)
+            for b in bes:
+                b.outer_prepare(param_dtype=dt)
+            for b in bes:
+                b.outer_apply(0.7, 0.9, dt, contributors=contributors)
+            used = contributors if contributors is not None else [0, 1, 2]
+            ref_d = [[torch.from_numpy(x.copy()) for x in split(deltas[w], cfg)] for w in used]
+            master, vel, _ = outer_step(master, vel, ref_d, [0.0] * len(used), NesterovConf(0.7, 0.9), dtype)
+            want, want_v = flat(master), flat(vel)
+            assert np.isfinite(want).all()
+            for w, b in enumerate(bes):
+                assert np.array_equal(b.worker_read_state("master"), want), (rnd, w)
+                lo, hi = shard_range(P, 3, w)
+                assert np.array_equal(b.worker_read_state("velocity")[: hi - lo], want_v[lo:hi]), (rnd, w)
+    finally:
+        for b in bes:
+            b.close()
+
+
+def test_staging_calls_are_refused_inside_a_round():
+    """compute_gradients / model_forward_pass stage their parameters in the round's working buffers: inside an open
+    round they are refused (PCPB_E_STATE) and the round's delta is what it is without the attempt."""
+    cfg, text = make_model(SMALL_F32)
+    master = seeded_params(cfg, seed=3)
+    other = seeded_params(cfg, seed=4, std=0.5)
+    toks = tokens_for(cfg, 2, seed=1)
+    x, y = FifoU16(tokens_for(cfg, 1, seed=2)).get_batch(cfg.batch, cfg.seq_len)
+
+    def run(interleave):
+        with Backend(0) as be:
+            be.load_session(text)
+            be.worker_begin_round(2, flat(master), param_dtype=F32)
+            be.worker_set_tokens(toks)
+            be.worker_step()
+            if interleave:
+                bufs = [be.move_to_device(p.numpy(), p.shape, F32) for p in other]
+                bufs += [be.move_to_device(x, x.shape, I64), be.move_to_device(y, y.shape, I64)]
+                for fn in ("compute_gradients", "model_forward_pass", "main", "compute_gradients_accumulated"):
+                    with pytest.raises(BackendError) as ei:
+                        be.execute_with_device_buffers(None, fn, bufs)
+                    assert ei.value.code == bk.E_STATE, fn
+                for b in bufs:
+                    b.release()
+            be.worker_step()
+            return be.worker_end_round(2, param_dtype=F32)[0]
+
+    assert np.array_equal(run(False), run(True))
+
+
+@pytest.mark.parametrize("tok_dtype", [np.uint16, np.uint32])
+def test_random_window_batches_bit_exact(tok_dtype):
+    """getBatchImpl of the random-window datasets (src/data/loader.zig:457-486 u16 stream; :276-307, :366-397 u32 tokens
+    of the char / byte tokenizers) on the device against the restated batcher with the same generator."""
+    cfg, text = make_model(dict(SMALL_F32, vocab=300 if tok_dtype == np.uint32 else 65))
+    rng = np.random.default_rng(5)
+    tokens = rng.integers(0, cfg.vocab, size=4000).astype(tok_dtype)
+    ds = RandomWindows(tokens, seed=77)
+    gen = bk.RandomGenerator(77)
+    with Backend(0) as be:
+        be.load_session(text)
+        for _ in range(3):
+            x, y = ds.get_batch(cfg.batch, cfg.seq_len)
+            bx, by = be.random_get_batch(gen, tokens)
+            assert np.array_equal(be.read_to_host(bx), x) and np.array_equal(be.read_to_host(by), y)
+            bx.release(); by.release()
+        with pytest.raises(BackendError) as ei:
+            be.random_get_batch(gen, tokens[: cfg.seq_len + 1])
+        assert ei.value.code == bk.E_CHUNK_TOO_SMALL
+
+
+@pytest.mark.parametrize("on_device", [False, True])
+def test_worker_loop_with_random_sampling(on_device):
+    """The fused worker round fed by random windows (the char-vocab experiments of the reference use
+    "sampling": "random"): losses and parameters against the oracle's loop over the restated random batcher."""
+    cfg, text = make_model(SMALL_F32)
+    mod = TrainingModule(text)
+    master = seeded_params(cfg, seed=6)
+    conf = AdamConf(learning_rate=3e-4)
+    tau = 4
+    tokens = np.random.default_rng(8).integers(0, cfg.vocab, size=3000).astype(np.uint16)
+    rec = []
+    _, _, p_ref, _ = inner_loop(mod, master, RandomWindows(tokens, seed=31), tau, cfg.batch, cfg.seq_len, conf, record=rec)
+    with Backend(0) as be:
+        be.load_session(text)
+        _adam(be, conf)
+        be.worker_set_sampling("random", seed=31)
+        be.worker_begin_round(tau, flat(master), param_dtype=F32, tokens_on_device=on_device)
+        if on_device:
+            dev = torch.from_numpy(tokens.view(np.int16)).to("cuda:0")
+            be.worker_set_tokens(device_ptr=dev.data_ptr(), n_tokens=tokens.size)
+        else:
+            be.worker_set_tokens(tokens)
+        for _ in range(tau):
+            be.worker_step()
+        delta, losses = be.worker_end_round(tau, param_dtype=F32)
+    np.testing.assert_allclose(losses, [r[0] for r in rec], rtol=1e-4)
+    _close(flat(master) - delta, flat(p_ref))
+
+
+def test_init_master_on_the_backend():
+    cfg, text = make_model(SMALL_BF16)
+    with Backend(0) as be:
+        be.load_session(text)
+        P = be.model_info()["total_params"]
+        blob = be.init_master(12345, BF16)
+        assert np.array_equal(blob, bk.init_master_elems(12345, P, BF16))
+        be.worker_begin_round(1, blob, param_dtype=BF16)          # usable as the round's parameter blob
+        be.worker_set_tokens(tokens_for(cfg, 1, seed=0))
+        be.worker_step()
+        _, losses = be.worker_end_round(1, param_dtype=BF16)
+        assert np.isfinite(losses).all() and abs(losses[0] - np.log(cfg.vocab)) < 0.5
+        assert np.array_equal(be.worker_read_state("master"), bf16_bits_to_f32(blob))
+
+
+def test_velocity_survives_reattach_and_regroup():
+    """A worker that leaves between rounds must not reset the outer optimiser's momentum: three workers do one outer
+    step, worker 1 leaves, workers 0 and 2 re-attach as a group of two with the velocity shards cut again from the old
+    ones, and the next outer step equals the restated Shepherd step with the velocities carried (the Shepherd keeps
+    them across membership changes, src/algorithms/diloco.zig:418-444)."""
+    cfg, text = make_model(SMALL_F32)
+    master = seeded_params(cfg, seed=7)
+    vel = [torch.zeros_like(p) for p in master]
+    P = flat(master).size
+    rng = np.random.default_rng(2)
+    bes = _three_workers(cfg, text, F32)
+    try:
+        for b in bes:
+            b.worker_write_state("master", flat(master))
+        deltas = [(rng.standard_normal(P) * 1e-3).astype(np.float32) for _ in bes]
+        for b, d in zip(bes, deltas):
+            b.worker_write_state("delta", d)
+        for b in bes:
+            b.outer_prepare()
+        for b in bes:
+            b.outer_apply(0.7, 0.9, F32)
+        master, vel, _ = outer_step(master, vel, [[torch.from_numpy(x.copy()) for x in split(d, cfg)] for d in deltas],
+                                    [0.0] * 3, NesterovConf(0.7, 0.9), "f32")
+        # attaching again with the same membership keeps the shard
+        before = bes[0].worker_read_state("velocity")
+        bes[0].outer_attach_local(0, bes)
+        assert np.array_equal(bes[0].worker_read_state("velocity"), before) and before.any()
+        # hand-over, then the two that stay regroup
+        old = [b.worker_read_state("velocity") for b in bes]
+        stay = [bes[0], bes[2]]
+        for r, b in enumerate(stay):
+            b.outer_attach_local(r, stay)
+            assert not b.worker_read_state("velocity").any()       # another membership starts at zero ...
+            b.worker_write_state("velocity", reshard_velocity(old, P, 2, r))      # ... until the host restores it
+        deltas = [(rng.standard_normal(P) * 1e-3).astype(np.float32) for _ in stay]
+        for b, d in zip(stay, deltas):
+            b.worker_write_state("delta", d)
+        for b in stay:
+            b.outer_prepare()
+        for b in stay:
+            b.outer_apply(0.7, 0.9, F32)
+        master, vel, _ = outer_step(master, vel, [[torch.from_numpy(x.copy()) for x in split(d, cfg)] for d in deltas],
+                                    [0.0] * 2, NesterovConf(0.7, 0.9), "f32")
+        for r, b in enumerate(stay):
+            assert np.array_equal(b.worker_read_state("master"), flat(master))
+            lo, hi = shard_range(P, 2, r)
+            assert np.array_equal(b.worker_read_state("velocity")[: hi - lo], flat(vel)[lo:hi])
+    finally:
+        for b in bes:
+            b.close()
+
+
+def test_recovery_file_restores_master_and_velocity(tmp_path):
+    """recovery/shepherd_state.bin (src/algorithms/diloco.zig:1063-1107): parameters become the master, the Nesterov
+    velocities this rank's shard."""
+    cfg, text = make_model(SMALL_F32)
+    rng = np.random.default_rng(3)
+    shapes = cfg.param_shapes()
+    params = [rng.standard_normal(s).astype(np.float32) * 0.02 for s in shapes]
+    vels = [rng.standard_normal(s).astype(np.float32) * 1e-3 for s in shapes]
+    path = os.path.join(tmp_path, formats.RECOVERY_FILENAME)
+    formats.write_recovery(path, params, vels, b"dm-state")
+    bes = [Backend(0) for _ in range(2)]
+    try:
+        for b in bes:
+            b.load_session(text)
+        for r, b in enumerate(bes):
+            b.outer_attach_local(r, bes)
+        P = flat(params).size
+        for r, b in enumerate(bes):
+            dt, dm = b.load_recovery(path)
+            assert dt == F32 and dm == b"dm-state"
+            assert np.array_equal(b.worker_read_state("master"), flat(params))
+            lo, hi = shard_range(P, 2, r)
+            assert np.array_equal(b.worker_read_state("velocity")[: hi - lo], flat(vels)[lo:hi])
+            b.worker_begin_round(0, None, param_dtype=F32)        # the restored master starts the next round
+            b.worker_end_round(0, param_dtype=F32, want_delta=False)
+    finally:
+        for b in bes:
+            b.close()

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import (GPT_D256_F32, GPT_GELU_BF16, GPT_GELU_F32, GPT_ODD_F32, GPT_SMALL_BF16, GPT_SMALL_F32, GQA_F32, HD128_BF16, HD128_F32, HD128_GQA_BF16, HD128_MANY_BF16, HD64_GQA_BF16, make_model, SMALL_BF16, SMALL_F32, bf16_bits_to_f32, f32_to_bf16_trunc_bits,
+from helpers import (D20_SHAPES_BF16, GPT_D256_F32, GPT_GELU_BF16, GPT_GELU_F32, GPT_ODD_F32, GPT_SMALL_BF16, GPT_SMALL_F32, GQA_F32, HD128_BF16, HD128_F32, HD128_GQA_BF16, HD128_MANY_BF16, HD64_GQA_BF16, make_model, SMALL_BF16, SMALL_F32, bf16_bits_to_f32, f32_to_bf16_trunc_bits,
                      flat, rel_err, seeded_params, split, tokens_for)
 from oracle.loader import FifoU16
 from oracle.optim import AdamConf, NesterovConf, adamw_update
@@ -62,6 +62,31 @@ def test_compute_gradients_matches_oracle(cfgd, tol):
         # rounding noise; the per-tensor L2 error carries the bound and the element-wise one is loose
         l2 = max(float(np.linalg.norm(a - b.numpy()) / (np.linalg.norm(b.numpy()) + 1e-30)) for a, b in zip(g, g_ref))
         assert l2 <= 4e-2 and worst <= 0.25, (l2, worst)
+
+
+def test_d20_kernel_shapes_match_oracle():
+    """Loss and gradients at the shapes the benchmark's kernels run at (d_model 1280, 10 x 128 heads, T = 2048,
+    V = 65536; two layers, batch 1, Zipf(1.1) tokens) against the oracle: loss within 2e-2, every gradient tensor
+    within the bf16 bound of the small-shape tests (largest element error <= 4e-2 of the tensor's largest entry) and
+    within 4e-2 in relative L2."""
+    cfg, text = make_model(D20_SHAPES_BF16)
+    params = seeded_params(cfg, seed=0, std=0.02)
+    x, y = FifoU16(tokens_for(cfg, 1, seed=1, zipf=True)).get_batch(cfg.batch, cfg.seq_len)
+    y[0, :3] = -1
+    with Backend(0) as be:                                      # the GPU first: its errors are the cheap ones to see
+        be.load_session(text)
+        g, loss = _grads_via_abi(be, cfg, params, x, y)
+    g_ref, loss_ref = TrainingModule(text).compute_gradients(params, torch.from_numpy(x), torch.from_numpy(y))
+    loss_ref = float(loss_ref)
+    assert abs(loss - loss_ref) <= 2e-2 * abs(loss_ref), (loss, loss_ref)
+    worst, worst_l2 = 0.0, 0.0
+    for i, (a, b) in enumerate(zip(g, g_ref)):
+        b = b.to(torch.float32).numpy()
+        e_max = rel_err(a, b)
+        e_l2 = float(np.linalg.norm(a.astype(np.float64) - b) / (np.linalg.norm(b.astype(np.float64)) + 1e-30))
+        worst, worst_l2 = max(worst, e_max), max(worst_l2, e_l2)
+        assert e_max <= 4e-2 and e_l2 <= 4e-2, (i, a.shape, e_max, e_l2)
+    print(f"d20 shapes: loss {loss:.6f} vs {loss_ref:.6f}; worst max-rel {worst:.3e}, worst rel-L2 {worst_l2:.3e}")
 
 
 @pytest.mark.parametrize("cfgd", [HD128_BF16, HD128_GQA_BF16, HD128_MANY_BF16, HD64_GQA_BF16])
@@ -417,7 +442,6 @@ def test_outer_step_bit_exact_given_deltas():
             master, vel, _ = outer_step(master, vel, deltas, [0.0] * workers, NesterovConf(0.7, 0.9), "bf16")
             for b in bes:
                 assert np.array_equal(b.worker_read_state("master"), flat(master))
-        # elasticity: only ranks 0 and 2 contribute (divisor 2, src/algorithms/diloco.zig:970)
     finally:
         for b in bes:
             b.close()

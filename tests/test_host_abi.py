@@ -74,3 +74,34 @@ def test_d20_parameter_count():
     assert cfg.num_params() == 560_988_160 and len(cfg.param_shapes()) == 122
     d8 = NanochatConfig(vocab=65536, d_model=512, n_layer=8, n_head=4, n_kv_head=4, seq_len=2048, batch=8, dtype="bf16")
     assert d8.num_params() == 92_274_688
+
+
+def test_recogniser_refuses_same_signature_other_body(lib_built):
+    """A graph with the nanochat parameter list but another body (no ReLU^2, a norm dropped, GELU-like ops, another
+    ignore index) must be refused, not trained with the built-in nanochat arithmetic."""
+    cfg = NanochatConfig(vocab=97, d_model=64, n_layer=2, n_head=4, n_kv_head=2, seq_len=16, batch=2, dtype="f32")
+    good = nanochat_forward_mlir(cfg)
+    inspect_artifact(good)
+    lines = good.split("\n")
+
+    def replace_first(op_from, op_to):
+        out, done = [], False
+        for ln in lines:
+            if not done and f"= stablehlo.{op_from} " in ln:
+                ln = ln.replace(f"stablehlo.{op_from} ", f"stablehlo.{op_to} ", 1)
+                done = True
+            out.append(ln)
+        assert done
+        return "\n".join(out)
+
+    mutated = {
+        "relu -> abs (no ReLU)": replace_first("maximum", "abs"),
+        "one rsqrt -> sqrt (a norm changed)": replace_first("rsqrt", "sqrt"),
+        "soft-cap tanh -> logistic": replace_first("tanh", "logistic"),
+        "softmax exp -> tanh": replace_first("exponential", "tanh"),
+        "other ignore index": good.replace("dense<-1>", "dense<-7>"),
+    }
+    for what, text in mutated.items():
+        with pytest.raises(BackendError) as ei:
+            inspect_artifact(text)
+        assert ei.value.code == bk.E_ARTIFACT, what
