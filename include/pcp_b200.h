@@ -197,6 +197,21 @@ int pcpb_worker_write_state(pcpb_backend* b, int which, const float* src, size_t
  * (U16TokenDataset.getBatchImpl, src/data/loader.zig:457-486) drawn from a generator seeded with `seed`
  * (src/data/loader.zig:439).  Takes effect at the next pcpb_worker_set_tokens. */
 int pcpb_worker_set_sampling(pcpb_backend* b, int mode, uint64_t seed);
+/* Adjoint-edge status.  The reference's AD engine passes every adjoint through a finite guard (non-finite -> 0) and
+ * a clamp to [-100, 100] before accumulating it (src/autodiff/engine.zig:604-702).  The kernels do the same on every
+ * adjoint they hold as a value of its own: the loss gradient, the outputs of every backward GEMM (activation and weight
+ * gradients), the row and element values of the RMSNorm / QK-norm / RoPE / LayerNorm / activation backward, the
+ * attention gradients dQ, dK, dV.  Inside the fused attention backward dP and dS are not clamped edge by edge (its
+ * softmax backward is in closed form); their magnitude is checked instead.  flags receives, since the last clear and
+ * for the device of this backend (the word is shared by the backends on one device):
+ *   bit 0 (PCPB_ADJ_CLAMPED)   some adjoint was non-finite or beyond +-100 and was guarded / clamped: results follow the
+ *                              reference's clamped arithmetic at every edge listed above
+ *   bit 1 (PCPB_ADJ_INTERNAL)  an adjoint inside the fused attention backward was beyond +-100: from there on the
+ *                              gradients are those of the unclamped softmax backward, clamped where they leave the kernel
+ * 0 means no guard or clamp of the reference was active: gradients are those of the reference's engine.  Blocks. */
+#define PCPB_ADJ_CLAMPED 1
+#define PCPB_ADJ_INTERNAL 2
+int pcpb_adjoint_status(pcpb_backend* b, int* flags, int clear);
 /* Blocks until everything enqueued by this backend has run; returns the first asynchronous error. */
 int pcpb_synchronize(pcpb_backend* b);
 
@@ -282,8 +297,9 @@ int pcpb_profile_read(pcpb_backend* b, long long* launches, double* total_ms, do
 
 /* AdamW step that allocates nothing.  It has no counterpart in the reference; it exists for hosts that cannot
  * let a library allocate device memory on their behalf: runtimes that give out slices of one arena reserved up
- * front and account for every byte (the reference's worker runs on such a runtime, the IREE HAL allocator with its
- * allocation cap), and services whose step loop rules out allocation calls because they synchronise the device.
+ * front and account for every byte (memory-planned runtimes; the reference compiles for one and bounds the size of a
+ * single allocation at compile time, --iree-stream-resource-max-allocation-size in src/mlir/context.zig:238-239), and
+ * services whose step loop rules out allocation calls because cudaMalloc / cudaFree synchronise the device.
  * The regular apply_optimizer entry allocates its outputs and a descriptor table per call; this one works on
  * tensors the caller owns and keeps its reduction scratch in a fixed array inside the library image.
  *
@@ -298,10 +314,53 @@ int pcpb_profile_read(pcpb_backend* b, long long* launches, double* total_ms, do
  * left: the call re-initialises everything it reads, but two calls whose GPU work overlaps race on it, so callers
  * serialise them.  The first call on a device (the current device of the calling thread) looks up the array's
  * device address once; make that first call before beginning any stream capture. */
+/* 2^26 = 67,108,864 elements.  Large enough for every layer tensor of the models in scope (the biggest, the d20 MLP
+ * matrices, hold 5120 x 1280 = 6,553,600); NOT large enough for a 65536-row embedding or LM head at d_model 1280
+ * (83,886,080 elements): those two tensors of nanochat-d20 are refused, callers split them by rows (the clip norm is
+ * per tensor, so a split changes it) or use the regular entry point for them. */
 #define PCPB_NOALLOC_MAX_ELEMS (1ll << 26)
 int pcpb_adamw_step_noalloc(void* stream, const float* p, const float* g, const float* m, const float* v, float* p_out,
                             float* m_out, float* v_out, long long n, const pcpb_adam_conf* conf, float timestep,
                             char* err, size_t err_cap);
+
+/* ---- rollout generation: GenerationEngine.generateRolloutStreaming (src/nodes/workers/generation_engine.zig:174-332)
+ * with the sampler's greedy branch (src/core/math.zig:21-73), kept on the device.  The reference feeds one token per
+ * call to a compiled decode step of a Qwen3-shaped model (tools/export_qwen3_generation.py) and keeps a dense KV cache
+ * on the host; here all prompts of a batch are prefilled at once, the cache is paged and stays in HBM, and every
+ * further token is one CUDA graph launch.  The arithmetic per token is the exported step's, including its property
+ * that a token attends to the cache as it was before the step (its own slot reads as a zero key and zero value).
+ * bf16 model, greedy decoding only (temperature < 1e-6); up to 16 sequences per engine. */
+typedef struct pcpb_rollout pcpb_rollout;
+typedef struct pcpb_rollout_cfg {
+  int vocab, d_model, n_layer, n_head, n_kv_head, head_dim, d_ff;
+  int max_seq;              /* positions per sequence: prompt + generated (the reference's MAX_SEQ_LEN) */
+  int page_tokens;          /* tokens per KV-cache page */
+  int max_batch;            /* sequences generated together, <= 16 */
+  int max_prompt;           /* longest prompt; the prefill buffers hold max_batch * max_prompt token rows */
+  float rope_theta, rms_eps;
+} pcpb_rollout_cfg;
+/* Number of weights of a configuration, in the argument order of the exported function (= named_parameters() of the
+ * Hugging Face model): embed, per layer q k v o q_norm k_norm gate up down input_ln post_ln, norm, lm_head. */
+long long pcpb_rollout_num_params(const pcpb_rollout_cfg* cfg);
+int pcpb_rollout_create(int device_ordinal, const pcpb_rollout_cfg* cfg, pcpb_rollout** out);
+void pcpb_rollout_destroy(pcpb_rollout* r);
+const char* pcpb_rollout_last_error(const pcpb_rollout* r);
+/* GenerationEngine.ensureDeviceWeights (generation_engine.zig:80-122): the weight blob, tensor after tensor, PCPB_F32
+ * (the reference's blob; rounded to bf16 on the device) or PCPB_BF16. */
+int pcpb_rollout_load_weights(pcpb_rollout* r, const void* blob, size_t nbytes, int dtype);
+/* Benchmark set-up only: fills the matrices with N(0, std) and the norm weights with 1 on the device (the baseline
+ * configuration's random weights; 8 x 10^9 values would take minutes to draw on the host). */
+int pcpb_rollout_random_weights(pcpb_rollout* r, uint64_t seed, float std);
+/* prompts: batch rows of prompt_stride token ids, row b holding prompt_lens[b] of them (0 = empty prompt: generation
+ * starts from token 0 at position 0, generation_engine.zig:233-240).  tokens_out: batch x max_new_tokens, row b holds
+ * n_generated[b] tokens (the rest 0); finish_reason[b] (optional): 0 "length", 1 "stop" (eos_token was produced).
+ * prefill_ms / decode_ms (optional): device time of the prompt pass with the first token, and of the remaining steps. */
+int pcpb_rollout_generate(pcpb_rollout* r, const int64_t* prompts, const int* prompt_lens, int batch, int prompt_stride,
+                          int max_new_tokens, int64_t eos_token, float temperature, int64_t* tokens_out, int* n_generated,
+                          int* finish_reason, double* prefill_ms, double* decode_ms);
+/* Logits (as f32) of sequence `row` at the most recent step, for checks. */
+int pcpb_rollout_read_logits(pcpb_rollout* r, int row, float* dst, size_t n);
+long long pcpb_rollout_launch_count(const pcpb_rollout* r);
 
 /* Kernel counters of this backend: launches enqueued since creation, by the library's own kernels. */
 long long pcpb_launch_count(const pcpb_backend* b);

@@ -55,6 +55,19 @@ class TrainingModule:
             grads.append(g.to(torch.float32))
         return grads, loss
 
+    def model_forward_pass_grad(self, params_model, ids, targets, seed: float):
+        """The gradient function the AD engine emits next to the forward function (src/autodiff/engine.zig:196-330):
+        parameters in the model dtype, d(loss) = seed given by the caller, gradients in the model dtype.  The seed
+        passes through the guard and clamp of every edge like any other adjoint."""
+        ins = [p.to(t.torch_dtype) for p, t in zip(params_model, self.param_types)] + [ids, targets]
+        loss, env = hlo.evaluate(self.fn, ins, keep_env=True)
+        adj = autodiff.gradients(self.fn, env, torch.tensor(seed, dtype=loss.dtype), self.clip[0], self.clip[1], self.guards)
+        out = []
+        for (name, t) in self.fn.args[: self.num_params]:
+            g = adj[name]
+            out.append(g if g is not None else torch.zeros(t.shape, dtype=t.torch_dtype))
+        return out
+
     @staticmethod
     def apply_optimizer(params, grads, m, v, t, conf: AdamConf):
         out = [adamw_update(p, g, mi, vi, t, conf) for p, g, mi, vi in zip(params, grads, m, v)]

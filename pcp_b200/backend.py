@@ -46,7 +46,11 @@ EXPORTS = [
     "pcpb_stream_merge", "pcpb_prng_seed", "pcpb_prng_next", "pcpb_prng_uint_at_most", "pcpb_random_window_starts",
     "pcpb_random_get_batch", "pcpb_char_tokenizer_build", "pcpb_char_encode", "pcpb_char_decode",
     "pcpb_init_master_elems", "pcpb_init_master", "pcpb_worker_write_state", "pcpb_worker_set_sampling",
+    "pcpb_adjoint_status", "pcpb_rollout_num_params", "pcpb_rollout_create", "pcpb_rollout_destroy", "pcpb_rollout_last_error",
+    "pcpb_rollout_load_weights", "pcpb_rollout_random_weights", "pcpb_rollout_generate", "pcpb_rollout_read_logits",
+    "pcpb_rollout_launch_count",
 ]
+ADJ_CLAMPED, ADJ_INTERNAL = 1, 2
 CHAR_VOCAB_MAX = 65
 
 
@@ -73,6 +77,12 @@ class OuterCfg(C.Structure):
 class Prng(C.Structure):
     """pcpb_prng: the generator of the random-window datasets and of the master initialisation."""
     _fields_ = [("s", C.c_uint64 * 4)]
+
+
+class RolloutCfg(C.Structure):
+    _fields_ = [("vocab", C.c_int), ("d_model", C.c_int), ("n_layer", C.c_int), ("n_head", C.c_int), ("n_kv_head", C.c_int),
+                ("head_dim", C.c_int), ("d_ff", C.c_int), ("max_seq", C.c_int), ("page_tokens", C.c_int), ("max_batch", C.c_int),
+                ("max_prompt", C.c_int), ("rope_theta", C.c_float), ("rms_eps", C.c_float)]
 
 
 class StreamCfg(C.Structure):
@@ -157,6 +167,20 @@ def load_library(path: str | None = None):
     lib.pcpb_init_master.argtypes = [vp, u64, i, vp, sz]
     lib.pcpb_worker_write_state.argtypes = [vp, i, vp, sz]
     lib.pcpb_worker_set_sampling.argtypes = [vp, i, u64]
+    if hasattr(lib, "pcpb_rollout_create"):
+        rc = C.POINTER(RolloutCfg)
+        lib.pcpb_rollout_num_params.argtypes = [rc]; lib.pcpb_rollout_num_params.restype = C.c_longlong
+        lib.pcpb_rollout_create.argtypes = [i, rc, C.POINTER(vp)]
+        lib.pcpb_rollout_destroy.argtypes = [vp]; lib.pcpb_rollout_destroy.restype = None
+        lib.pcpb_rollout_last_error.argtypes = [vp]; lib.pcpb_rollout_last_error.restype = C.c_char_p
+        lib.pcpb_rollout_load_weights.argtypes = [vp, vp, sz, i]
+        lib.pcpb_rollout_random_weights.argtypes = [vp, u64, C.c_float]
+        lib.pcpb_rollout_generate.argtypes = [vp, vp, vp, i, i, i, C.c_int64, C.c_float, vp, vp, vp, C.POINTER(C.c_double),
+                                              C.POINTER(C.c_double)]
+        lib.pcpb_rollout_read_logits.argtypes = [vp, i, vp, sz]
+        lib.pcpb_rollout_launch_count.argtypes = [vp]; lib.pcpb_rollout_launch_count.restype = C.c_longlong
+    if hasattr(lib, "pcpb_adjoint_status"):              # absent from older builds of the library (PCPB_LIBRARY)
+        lib.pcpb_adjoint_status.argtypes = [vp, C.POINTER(i), i]
     if path is None:
         _lib = lib
     return lib
@@ -471,6 +495,13 @@ class Backend:
     def synchronize(self):
         self._check(self._lib.pcpb_synchronize(self._h))
 
+    def adjoint_status(self, clear=True) -> int:
+        """Bits ADJ_CLAMPED / ADJ_INTERNAL: whether the reference's finite guard or +-100 clamp on adjoint edges
+        (src/autodiff/engine.zig:604-702) was active since the last clear."""
+        f = C.c_int()
+        self._check(self._lib.pcpb_adjoint_status(self._h, C.byref(f), int(clear)))
+        return f.value
+
     # -- fused worker round (Worker.handleStartInnerLoop, src/nodes/workers/worker.zig:855-1480)
     def worker_begin_round(self, tau, params_blob=None, param_dtype=F32, accumulation_steps=1, persist_adam=False,
                            tokens_on_device=False):
@@ -657,3 +688,87 @@ class Backend:
             arr = (C.c_int * len(contributors))(*contributors)
             self._check(self._lib.pcpb_outer_apply(self._h, C.byref(cfg), arr, len(contributors), C.byref(ms)))
         return ms.value
+
+
+class Rollout:
+    """GenerationEngine of the reference (src/nodes/workers/generation_engine.zig) on the device: batched prefill, paged
+    KV cache, greedy decode, for a Qwen3-shaped bf16 model.  Method names follow the reference:
+    ensureDeviceWeights -> ensure_device_weights, generateRollout -> generate_rollout."""
+
+    def __init__(self, device_id: int, vocab, d_model, n_layer, n_head, n_kv_head, head_dim, d_ff, max_seq, max_batch=16,
+                 max_prompt=None, page_tokens=16, rope_theta=1e6, rms_eps=1e-6):
+        self._lib = load_library()
+        self.cfg = RolloutCfg(vocab, d_model, n_layer, n_head, n_kv_head, head_dim, d_ff, max_seq, page_tokens, max_batch,
+                              max_prompt if max_prompt is not None else max_seq, rope_theta, rms_eps)
+        h = C.c_void_p()
+        rc = self._lib.pcpb_rollout_create(device_id, C.byref(self.cfg), C.byref(h))
+        self._h = h
+        if rc:
+            msg = self._lib.pcpb_rollout_last_error(h).decode() if h else "allocation failed"
+            if h:
+                self._lib.pcpb_rollout_destroy(h)
+            self._h = None
+            raise BackendError(rc, msg)
+
+    def _check(self, rc):
+        if rc:
+            raise BackendError(rc, self._lib.pcpb_rollout_last_error(self._h).decode())
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.pcpb_rollout_destroy(self._h)
+            self._h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def num_params(self) -> int:
+        return int(self._lib.pcpb_rollout_num_params(C.byref(self.cfg)))
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.pcpb_rollout_launch_count(self._h))
+
+    def ensure_device_weights(self, blob: np.ndarray):
+        """blob: all weights concatenated in argument order, float32 or uint16 (bf16 bit patterns)."""
+        a = np.ascontiguousarray(blob)
+        if a.dtype not in (np.float32, np.uint16):
+            raise ValueError("weight blob must be float32 or bf16 bit patterns (uint16)")
+        self._check(self._lib.pcpb_rollout_load_weights(self._h, a.ctypes.data, a.nbytes, F32 if a.dtype == np.float32 else BF16))
+
+    def random_weights(self, seed: int = 0, std: float = 0.02):
+        self._check(self._lib.pcpb_rollout_random_weights(self._h, seed, std))
+
+    def generate_rollout(self, prompts, max_new_tokens: int, eos_token: int = -1, temperature: float = 0.0):
+        """prompts: list of token-id lists.  -> (list of generated token lists, list of finish reasons, (prefill ms,
+        decode ms))."""
+        B = len(prompts)
+        stride = max(1, max(len(p) for p in prompts))
+        buf = np.zeros((B, stride), np.int64)
+        lens = np.zeros(B, np.int32)
+        for b, p in enumerate(prompts):
+            buf[b, :len(p)] = p
+            lens[b] = len(p)
+        out = np.zeros((B, max_new_tokens), np.int64)
+        n = np.zeros(B, np.int32)
+        why = np.zeros(B, np.int32)
+        pm, dm = C.c_double(), C.c_double()
+        self._check(self._lib.pcpb_rollout_generate(self._h, buf.ctypes.data, lens.ctypes.data, B, stride, max_new_tokens, eos_token,
+                                                    temperature, out.ctypes.data, n.ctypes.data, why.ctypes.data, C.byref(pm),
+                                                    C.byref(dm)))
+        return ([out[b, :n[b]].tolist() for b in range(B)], ["stop" if w else "length" for w in why], (pm.value, dm.value))
+
+    def read_logits(self, row: int) -> np.ndarray:
+        out = np.empty(self.cfg.vocab, np.float32)
+        self._check(self._lib.pcpb_rollout_read_logits(self._h, row, out.ctypes.data, out.size))
+        return out

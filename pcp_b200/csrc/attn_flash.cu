@@ -16,6 +16,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 
+#define PCPB_ADJ_TU
 #include "attn_flash.h"
 #include "common.cuh"
 
@@ -242,21 +243,35 @@ __global__ void k_flash_prep(FlashArgs a) {
   const bf16* op = (const bf16*)a.o + ((long long)b * a.T + i) * d + h * HD;
   const bf16* dp = (const bf16*)a.dout + ((long long)b * a.T + i) * d + h * HD;
   // a lane takes HD/32 consecutive elements (4 or 8 bytes of each row)
-  float acc = 0.f;
+  // n_do, n_v: squared norms of the dO row and (kv heads) of the V row, for the bound on the adjoints dP = dO V^T and
+  // dS that stay in registers in the backward kernels
+  float acc = 0.f, n_do = 0.f, n_v = 0.f;
+  const bf16* vp = (const bf16*)a.qkv + ((long long)b * a.T + i) * (long long)(d + 2 * a.Hkv * HD) + d + a.Hkv * HD + h * HD;
   if (HD == 128) {
     const uint2 x = *reinterpret_cast<const uint2*>(op + lane * 4), y = *reinterpret_cast<const uint2*>(dp + lane * 4);
     acc = bf_lo(x.x) * bf_lo(y.x) + bf_hi(x.x) * bf_hi(y.x) + bf_lo(x.y) * bf_lo(y.y) + bf_hi(x.y) * bf_hi(y.y);
+    n_do = bf_lo(y.x) * bf_lo(y.x) + bf_hi(y.x) * bf_hi(y.x) + bf_lo(y.y) * bf_lo(y.y) + bf_hi(y.y) * bf_hi(y.y);
+    if (h < a.Hkv) {
+      const uint2 z = *reinterpret_cast<const uint2*>(vp + lane * 4);
+      n_v = bf_lo(z.x) * bf_lo(z.x) + bf_hi(z.x) * bf_hi(z.x) + bf_lo(z.y) * bf_lo(z.y) + bf_hi(z.y) * bf_hi(z.y);
+    }
   } else {
     const uint32_t x = *reinterpret_cast<const uint32_t*>(op + lane * 2), y = *reinterpret_cast<const uint32_t*>(dp + lane * 2);
     acc = bf_lo(x) * bf_lo(y) + bf_hi(x) * bf_hi(y);
+    n_do = bf_lo(y) * bf_lo(y) + bf_hi(y) * bf_hi(y);
+    if (h < a.Hkv) {
+      const uint32_t z = *reinterpret_cast<const uint32_t*>(vp + lane * 2);
+      n_v = bf_lo(z) * bf_lo(z) + bf_hi(z) * bf_hi(z);
+    }
   }
-  acc = warp_sum(acc);
+  acc = warp_sum(acc); n_do = warp_sum(n_do); n_v = warp_sum(n_v);
   if (lane == 0) {
     const float l = a.lrow[gw];
     const float D = acc * (l + PCPB_GUARD) / (l + 2.f * PCPB_GUARD);
     a.drow[gw] = D;
     // what the backward kernels need per query row, divisions done once here: max, 1/(l+1e-4), 1/(l+2e-4), D
     a.stat4[gw] = make_float4(a.mrow[gw], 1.f / (l + PCPB_GUARD), 1.f / (l + 2.f * PCPB_GUARD), D);
+    attn_bound_note(0, n_do); attn_bound_note(1, D); attn_bound_note(2, n_v);
   }
 }
 
@@ -291,6 +306,7 @@ __device__ __forceinline__ void bwd_pair(float s0raw, float s1raw, float dp0raw,
 // ------------------------------------------------------------------------------------------------
 template <int HD>
 __global__ void __launch_bounds__(256) k_flash_bwd_dkv(FlashArgs a) {
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) attn_bound_check_and_clear();   // bound gathered by k_flash_prep
   constexpr int ROWB = HD * 2, KS = HD / 16, NO = HD / 8;    // row bytes, head-dim k-steps, output n-tiles
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sK = smem_u32(smem), sV = sK + 128 * ROWB, sQ = sV + 128 * ROWB, sDO = sQ + 2 * 64 * ROWB;
@@ -395,8 +411,8 @@ __global__ void __launch_bounds__(256) k_flash_bwd_dkv(FlashArgs a) {
     const int key = key_lo + r * 8;
 #pragma unroll
     for (int nt = 0; nt < NO; ++nt) {
-      *reinterpret_cast<uint32_t*>(dKg + (long long)key * wqkn + nt * 8 + 2 * t) = pack_bf16(dk[nt][2 * r], dk[nt][2 * r + 1]);
-      *reinterpret_cast<uint32_t*>(dVg + (long long)key * wqkv + nt * 8 + 2 * t) = pack_bf16(dv[nt][2 * r], dv[nt][2 * r + 1]);
+      *reinterpret_cast<uint32_t*>(dKg + (long long)key * wqkn + nt * 8 + 2 * t) = adj_edge2(pack_bf16(dk[nt][2 * r], dk[nt][2 * r + 1]));
+      *reinterpret_cast<uint32_t*>(dVg + (long long)key * wqkv + nt * 8 + 2 * t) = adj_edge2(pack_bf16(dv[nt][2 * r], dv[nt][2 * r + 1]));
     }
   }
 }
@@ -497,7 +513,7 @@ __global__ void __launch_bounds__(128) k_flash_bwd_dq(FlashArgs a) {
     const int row = row_lo + r * 8;
 #pragma unroll
     for (int nt = 0; nt < NO; ++nt)
-      *reinterpret_cast<uint32_t*>(dQg + (long long)row * wqkn + nt * 8 + 2 * t) = pack_bf16(dq[nt][2 * r], dq[nt][2 * r + 1]);
+      *reinterpret_cast<uint32_t*>(dQg + (long long)row * wqkn + nt * 8 + 2 * t) = adj_edge2(pack_bf16(dq[nt][2 * r], dq[nt][2 * r + 1]));
   }
 }
 
@@ -560,5 +576,7 @@ cudaError_t launch_flash_fwd(cudaStream_t st, const FlashArgs& a) {
 cudaError_t launch_flash_bwd(cudaStream_t st, const FlashArgs& a) {
   return a.hd == 128 ? flash_bwd<128>(st, a) : flash_bwd<64>(st, a);
 }
+
+cudaError_t adj_status_fetch_attn_flash(cudaStream_t st, int* out, bool clear) { return adj_status_fetch_tu(st, out, clear); }
 
 }  // namespace pcpb

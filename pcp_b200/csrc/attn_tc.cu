@@ -29,6 +29,7 @@
 // Numerics are those of attn_flash.cu / the generic kernels (scores rounded twice to bf16, guard terms 1e-4 / 2e-4,
 // reduce-max term); D = rowsum(dO*O) (l+1e-4)/(l+2e-4) comes from k_attn_tc_prep.
 // Every mbarrier wait is bounded; on expiry an error word is set and the CTA drains and frees its tensor memory.
+#define PCPB_ADJ_TU
 #include "attn_tc.h"
 #include "common.cuh"
 #include "tc_common.cuh"
@@ -119,6 +120,9 @@ __device__ __forceinline__ bool twait(int code, uint32_t bar, uint32_t parity, i
 }
 
 // Store 32 consecutive output columns of one row (f32 accumulators in tensor memory at taddr) as bf16 to dst.
+// ADJ: the values are gradients (dQ, dK, dV: outputs of the dot_general VJP), passed through the adjoint-edge step of
+// the reference's engine (non-finite -> 0, clamp to +-100).
+template <bool ADJ>
 __device__ __forceinline__ void store_out_cols(uint32_t taddr, bf16* dst) {
   uint32_t r[32];
   tmem_ld32(taddr, r);
@@ -129,6 +133,11 @@ __device__ __forceinline__ void store_out_cols(uint32_t taddr, bf16* dst) {
     v.y = pack2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
     v.z = pack2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
     v.w = pack2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+    if (ADJ) {
+      uint32_t mx2 = 0u;
+      adj_track2(mx2, v.x); adj_track2(mx2, v.y); adj_track2(mx2, v.z); adj_track2(mx2, v.w);
+      if (adj_over2(mx2)) { v.x = adj_edge2(v.x); v.y = adj_edge2(v.y); v.z = adj_edge2(v.z); v.w = adj_edge2(v.w); }
+    }
     *reinterpret_cast<uint4*>(dst + 8 * j) = v;
   }
 }
@@ -168,6 +177,9 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
 #ifdef PCPB_ATC_TIMING
   const long long t_cta0 = clock64();
 #endif
+  // first backward kernel after the prepare kernel of this layer: evaluate (and clear) the bound on the adjoints that
+  // stay on the chip
+  if (MODE == MODE_DKV && blockIdx.x == 0 && threadIdx.x == 0) attn_bound_check_and_clear();
   // work items of this CTA
   constexpr bool PERSIST = Cfg::PERSIST;
   const int nt = p.T / 128;
@@ -618,12 +630,12 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
         const int oc = (cg * PARTS + part) * 32;
         if (oc >= 128) break;
         if (MODE == MODE_FWD) {
-          store_out_cols(out1 + lane_off + oc, p.o + grow * p.d + xq + oc);
+          store_out_cols<false>(out1 + lane_off + oc, p.o + grow * p.d + xq + oc);
         } else if (MODE == MODE_DQ) {
-          store_out_cols(out1 + lane_off + oc, p.dqkn + grow * (p.d + p.dkv) + xq + oc);
+          store_out_cols<true>(out1 + lane_off + oc, p.dqkn + grow * (p.d + p.dkv) + xq + oc);
         } else {
-          store_out_cols(out1 + lane_off + oc, p.dqkv + grow * (p.d + 2 * p.dkv) + xv + oc);
-          store_out_cols(out2 + lane_off + oc, p.dqkn + grow * (p.d + p.dkv) + xk + oc);
+          store_out_cols<true>(out1 + lane_off + oc, p.dqkv + grow * (p.d + 2 * p.dkv) + xv + oc);
+          store_out_cols<true>(out2 + lane_off + oc, p.dqkn + grow * (p.d + p.dkv) + xk + oc);
         }
       }
       if (MODE == MODE_FWD && cg == 0) {
@@ -663,7 +675,8 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
 // D[b,h,i] = rowsum(do * o) * (l + 1e-4) / (l + 2e-4).  Eight lanes per row, 16 elements (two 16-byte loads of each
 // tensor) per lane: four rows per warp, 64 bytes in flight per thread.
 __global__ void __launch_bounds__(256) k_attn_tc_prep(const bf16* __restrict__ o, const bf16* __restrict__ dout,
-                                                      const float* __restrict__ lrow, float* __restrict__ drow, int B, int T, int H) {
+                                                      const float* __restrict__ lrow, float* __restrict__ drow, int B, int T, int H,
+                                                      const bf16* __restrict__ qkv, int Hkv) {
   const long long gt = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long gw = gt >> 3;                       // row index over (b, h, i); B*H*T is a multiple of 4: whole warps
   const int sub = threadIdx.x & 7;
@@ -677,13 +690,39 @@ __global__ void __launch_bounds__(256) k_attn_tc_prep(const bf16* __restrict__ o
   float acc = 0.f;
 #pragma unroll
   for (int k = 0; k < 8; ++k) acc += bf_lo(x[k]) * bf_lo(y[k]) + bf_hi(x[k]) * bf_hi(y[k]);
-  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-  acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+  // squared norms of the dO row and (for the kv heads) of the V row: the bound on the on-chip adjoints dP, dS
+  float n_do = 0.f, n_v = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) n_do += bf_lo(y[k]) * bf_lo(y[k]) + bf_hi(y[k]) * bf_hi(y[k]);
+  if (h < Hkv) {
+    const size_t voff = ((size_t)b * T + i) * ((size_t)(H + 2 * Hkv) * HD) + (size_t)(H + Hkv + h) * HD + sub * 16;
+    const uint4 v0 = *reinterpret_cast<const uint4*>(qkv + voff), v1 = *reinterpret_cast<const uint4*>(qkv + voff + 8);
+    const uint32_t z[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) n_v += bf_lo(z[k]) * bf_lo(z[k]) + bf_hi(z[k]) * bf_hi(z[k]);
+  }
+#pragma unroll
+  for (int s = 1; s <= 4; s <<= 1) {
+    acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    n_do += __shfl_xor_sync(0xffffffffu, n_do, s);
+    n_v += __shfl_xor_sync(0xffffffffu, n_v, s);
+  }
+  float D = 0.f;
   if (sub == 0) {
     const float l = lrow[gw];
-    drow[gw] = acc * (l + PCPB_GUARD) / (l + 2.f * PCPB_GUARD);
+    D = acc * (l + PCPB_GUARD) / (l + 2.f * PCPB_GUARD);
+    drow[gw] = D;
   }
+  // largest values of the warp's four rows, then one conditional atomic per statistic
+  D = fabsf(D);
+#pragma unroll
+  for (int s = 8; s <= 16; s <<= 1) {
+    n_do = fmaxf(n_do, __shfl_xor_sync(0xffffffffu, n_do, s));
+    n_v = fmaxf(n_v, __shfl_xor_sync(0xffffffffu, n_v, s));
+    const float od = __shfl_xor_sync(0xffffffffu, D, s);
+    D = (od > D || od != od) ? od : D;
+  }
+  if ((threadIdx.x & 31) == 0) { attn_bound_note(0, n_do); attn_bound_note(1, D); attn_bound_note(2, n_v); }
 }
 
 template <int MODE>
@@ -753,7 +792,7 @@ cudaError_t launch_attn_tc_bwd(cudaStream_t st, const FlashArgs& a, int* err_wor
   if (!err_word || !fill(a, err_word, &p, &mq, &mv, &md, true)) return cudaErrorInvalidValue;
   const long long rows = (long long)a.B * a.H * a.T;
   k_attn_tc_prep<<<(unsigned)((rows * 8 + 255) / 256), 256, 0, st>>>((const bf16*)a.o, (const bf16*)a.dout, a.lrow, a.drow, a.B,
-                                                                     a.T, a.H);
+                                                                     a.T, a.H, (const bf16*)a.qkv, a.Hkv);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   // persistent backward kernels: one CTA per SM walks the work items, long row tiles first
@@ -766,5 +805,7 @@ cudaError_t launch_attn_tc_bwd(cudaStream_t st, const FlashArgs& a, int* err_wor
   p.bh_count = a.B * a.H; p.n_items = (a.T / 128) * p.bh_count;
   return launch_mode<MODE_DQ>(st, mq, mv, md, p, dim3(p.n_items < sms ? p.n_items : sms));
 }
+
+cudaError_t adj_status_fetch_attn_tc(cudaStream_t st, int* out, bool clear) { return adj_status_fetch_tu(st, out, clear); }
 
 }  // namespace pcpb

@@ -172,4 +172,79 @@ template <typename T> __device__ __forceinline__ float gelu_grad(float u) {
 
 #define PCPB_GUARD 1e-4f
 
+// ---- adjoint edges ------------------------------------------------------------------------------------------
+// The reference's AD engine passes every adjoint a VJP rule produces through the same three steps before it is
+// accumulated (src/autodiff/engine.zig:622-682): non-finite -> 0 (tested as (g - g) == 0 in the edge's element type),
+// clamp to [-100, 100] in f32, cast back to the element type.  adj_edge<T> is that step for a value computed in f32
+// that the rule would hold in T; adj_edge2 the same on a pair of bf16 values.  On healthy models the step changes
+// nothing; when it does, bit ADJ_CLAMPED of the status word is set so that the host can tell.  ADJ_INTERNAL is set
+// for the fused attention kernels when the adjoints that never leave the chip (dP, dS) cannot be shown to stay inside
+// the limit: those kernels use an algebraically fused backward that cannot apply the clamp per edge, so past that
+// point their gradients are those of the unclamped arithmetic, clamped where they leave the kernel.
+#define PCPB_ADJ_CLIP 100.f
+enum : int { ADJ_CLAMPED = 1, ADJ_INTERNAL = 2 };
+#ifdef PCPB_ADJ_TU
+static __device__ int g_adj_status = 0;       // one per translation unit and device; read through adj_status_fetch()
+__device__ __forceinline__ void adj_note(int bit) {
+  if (!(*(volatile int*)&g_adj_status & bit)) atomicOr(&g_adj_status, bit);
+}
+template <typename T> __device__ __forceinline__ float adj_edge(float v) {
+  const float r = rnd<T>(v);
+  const float c = fminf(fmaxf(((r - r) == 0.f) ? r : 0.f, -PCPB_ADJ_CLIP), PCPB_ADJ_CLIP);
+  if (c != r) adj_note(ADJ_CLAMPED);            // also taken for NaN (NaN != anything)
+  return c;
+}
+__device__ __forceinline__ uint32_t bmin2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("min.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t adj_edge2(uint32_t w) {
+  // 100.0 = 0x42C8 in bf16.  min / max return one of their operands, so an in-range finite pair comes back bit for bit
+  const uint32_t c = bmin2(bmax2(w, 0xC2C8C2C8u), 0x42C842C8u);
+  if (c == w) return w;
+  adj_note(ADJ_CLAMPED);
+  const float lo = bf_lo(w), hi = bf_hi(w);
+  const float cl = fminf(fmaxf(((lo - lo) == 0.f) ? lo : 0.f, -PCPB_ADJ_CLIP), PCPB_ADJ_CLIP);
+  const float ch = fminf(fmaxf(((hi - hi) == 0.f) ? hi : 0.f, -PCPB_ADJ_CLIP), PCPB_ADJ_CLIP);
+  return pack2(cl, ch);
+}
+// Cheap form for hot loops: compute without the guard while tracking the largest magnitude seen, and only when the
+// tracker ends beyond the limit (or saw a NaN / Inf) redo the row / chunk through adj_edge.  The tracker holds |v| as
+// a bit pattern: non-negative floats order like unsigned integers, NaN and Inf above every finite value.
+__device__ __forceinline__ void adj_track(uint32_t& mx, float v) { mx = max(mx, __float_as_uint(v) & 0x7FFFFFFFu); }
+__device__ __forceinline__ bool adj_over(uint32_t mx) { return mx > 0x42C80000u; }             // > 100.0f, NaN, Inf
+// the same on bf16 pairs: a packed running maximum of |lo|, |hi| that keeps NaN
+__device__ __forceinline__ void adj_track2(uint32_t& mx2, uint32_t w) {
+  asm("max.NaN.bf16x2 %0, %0, %1;" : "+r"(mx2) : "r"(w & 0x7FFF7FFFu));
+}
+__device__ __forceinline__ bool adj_over2(uint32_t mx2) { return (mx2 & 0xFFFFu) > 0x42C8u || (mx2 >> 16) > 0x42C8u; }
+// Bound for the adjoints that never leave the fused attention backward (dP = dO V^T and dS = P (dP - D)):
+// |dP_ij| <= |dO_i| |V_j| and |dS_ij| <= |dP_ij| + |D_i| (P <= 1), so max|dO_i| max|V_j| + max|D_i| <= 100 proves that
+// the reference's clamp on those edges is inactive without touching the kernels' inner loops.  The row statistics are
+// gathered by the kernel that prepares D (squared norms and |D| as float bit patterns, combined with atomicMax) and
+// evaluated, then cleared, by the first thread of the backward kernel that follows it on the stream.
+static __device__ unsigned g_attn_bound[3] = {0u, 0u, 0u};      // max |dO_i|^2, max |D_i|, max |V_j|^2
+__device__ __forceinline__ void attn_bound_note(int which, float v) {
+  const unsigned bits = __float_as_uint(fabsf(v));             // NaN sorts above every finite value
+  if (bits > *(volatile unsigned*)&g_attn_bound[which]) atomicMax(&g_attn_bound[which], bits);
+}
+__device__ __forceinline__ void attn_bound_check_and_clear() {
+  const float a = __uint_as_float(g_attn_bound[0]), dmax = __uint_as_float(g_attn_bound[1]), v = __uint_as_float(g_attn_bound[2]);
+  if (!(sqrtf(a) * sqrtf(v) + dmax <= PCPB_ADJ_CLIP)) adj_note(ADJ_INTERNAL);
+  g_attn_bound[0] = 0u; g_attn_bound[1] = 0u; g_attn_bound[2] = 0u;
+}
+// Host access to this translation unit's status word on the current device.
+static inline cudaError_t adj_status_fetch_tu(cudaStream_t st, int* out, bool clear) {
+  cudaError_t e = cudaMemcpyFromSymbolAsync(out, g_adj_status, sizeof(int), 0, cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e == cudaSuccess && clear && *out) {
+    const int zero = 0;
+    e = cudaMemcpyToSymbolAsync(g_adj_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  }
+  return e;
+}
+#endif
+
 }  // namespace pcpb

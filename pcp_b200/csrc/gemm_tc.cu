@@ -26,6 +26,7 @@
 #include <stdint.h>
 #include <stdlib.h>
 
+#define PCPB_ADJ_TU
 #include "gemm_tc.h"
 #include "tc_common.cuh"
 
@@ -43,6 +44,7 @@ struct TcParams {
   int tiles_m, tiles_n, splits, kb_per_split;
   int group_m;                 // row tiles per group of the tile order (1 = plain row-major order)
   int epi;
+  int adj;                     // EPI_STORE: the output is an activation gradient (an adjoint edge: guard + clamp)
   int wide;                    // 1: rows of C / C2 / R start on 32-byte boundaries, so 256-bit accesses may be used
   void* C; long long ldc;
   const void* R; void* C2;
@@ -101,6 +103,20 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, int c
 #pragma unroll
   for (int j = 0; j < 16; ++j) w[j] = pack2(acc[2 * j], acc[2 * j + 1]);
   const uint32_t* x = reinterpret_cast<const uint32_t*>(rpre);     // per-element operand, when the epilogue has one
+  // The product of a backward GEMM is an output of the dot_general VJP, i.e. an adjoint edge of the reference's engine
+  // (src/autodiff/engine.zig:622-682): non-finite -> 0, clamp to +-100.  One min and one max per pair when in range.
+  // Hot path: a running maximum of the magnitudes (two instructions per pair), one test per 32 columns; the guard and
+  // clamp themselves only run for a chunk that needs them.
+  const bool backward = p.adj || p.epi == EPI_DRELU || p.epi == EPI_DRELU2 || p.epi == EPI_DGELU;
+  if (backward) {
+    uint32_t mx2 = 0u;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) adj_track2(mx2, w[j]);
+    if (adj_over2(mx2)) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) w[j] = adj_edge2(w[j]);
+    }
+  }
   if (p.epi == EPI_RESID) {
 #pragma unroll
     for (int j = 0; j < 16; ++j) w[j] = badd2(x[j], w[j]);
@@ -120,13 +136,22 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, int c
       const uint32_t y2 = bmul2(r2, r2);
       const float q0 = bf_lo(y2) * rcp_approx(fmaxf(bf_lo(r2), 1e-30f)), q1 = bf_hi(y2) * rcp_approx(fmaxf(bf_hi(r2), 1e-30f));
       const uint32_t t2 = bmul2(pack2(q0, q1), 0x40004000u);           // 2 * q
-      w[j] = bmul2(w[j], t2);
+      w[j] = bmul2(w[j], t2);                                           // the power VJP's output: an edge, checked below
     }
   } else if (p.epi == EPI_DGELU) {
     // backward of the tanh GELU: bf16(da * gelu'(u)), the derivative evaluated once in f32
 #pragma unroll
     for (int j = 0; j < 16; ++j)
       w[j] = pack2(bf_lo(w[j]) * gelu_grad<__nv_bfloat16>(bf_lo(x[j])), bf_hi(w[j]) * gelu_grad<__nv_bfloat16>(bf_hi(x[j])));
+  }
+  if (p.epi == EPI_DRELU2 || p.epi == EPI_DGELU) {               // the activation VJP's output edge
+    uint32_t mx2 = 0u;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) adj_track2(mx2, w[j]);
+    if (adj_over2(mx2)) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) w[j] = adj_edge2(w[j]);
+    }
   }
   if (p.wide) {
     st_global_256(C, make_uint4(w[0], w[1], w[2], w[3]), make_uint4(w[4], w[5], w[6], w[7]));
@@ -695,7 +720,7 @@ cudaError_t launch_gemm_tc(cudaStream_t st, const GemmArgs& g) {
     const uintptr_t all = (uintptr_t)g.C | (uintptr_t)g.R | (uintptr_t)g.C2 | (uintptr_t)g.scratch;
     p.wide = ((all & 31) == 0 && g.ldc % 16 == 0 && g.N % 16 == 0) ? 1 : 0;
   }
-  p.epi = g.epi; p.C = g.C; p.ldc = g.ldc; p.R = g.R; p.C2 = g.C2; p.clip = g.clip; p.slab = nullptr; p.err = err;
+  p.epi = g.epi; p.C = g.C; p.ldc = g.ldc; p.R = g.R; p.C2 = g.C2; p.clip = g.clip; p.adj = g.adj; p.slab = nullptr; p.err = err;
   if (pl.splits > 1) p.slab = (float*)g.scratch;
   const int items = p.tiles_m * p.tiles_n * p.splits;
   const int grid = items < g_sm_count ? items : g_sm_count;
@@ -722,5 +747,7 @@ cudaError_t launch_gemm_tc(cudaStream_t st, const GemmArgs& g) {
   }
   return e;
 }
+
+cudaError_t adj_status_fetch_gemm_tc(cudaStream_t st, int* out, bool clear) { return adj_status_fetch_tu(st, out, clear); }
 
 }  // namespace pcpb

@@ -6,6 +6,7 @@
 //    type (models/nanochat_d8_b8_t2048_bf16.mlir), statistics / softmax / loss are f32;
 //  * forward divides and logs carry +1e-4 (src/compiler/sanitizer.zig:8-111), the divide / log /
 //    rsqrt VJP rules carry another +1e-4 (src/autodiff/vjp_rules.zig:198,1510,1543).
+#define PCPB_ADJ_TU
 #include "common.cuh"
 #include "kernels.h"
 
@@ -128,16 +129,18 @@ __global__ void k_embed_norm_fwd(const T* __restrict__ wte, const long long* __r
 //   rsqrt VJP:      dt = (dr * -0.5) * rsqrt(t + 1e-4)^3
 //   divide VJP:     ds = dt / ((d + 1e-4) + 1e-4)
 //   power VJP:      dx2 = T(ds * 2 * x)      (x^2/x == x up to one ulp; 0 at x == 0)
+// Every one of these values is an adjoint edge of the reference's engine (finite guard, clamp to +-100, cast:
+// adj_edge); the edges between them that only reshape, broadcast or convert repeat a clamp already applied.
 template <typename T>
 __device__ __forceinline__ float rmsnorm_row_ds(const T* __restrict__ xr, const T* __restrict__ dyr, int d,
                                                 float t, float* red) {
   float acc = 0.f;
-  for (int j = threadIdx.x; j < d; j += blockDim.x) acc += rnd<T>(to_f(dyr[j]) * to_f(xr[j]));
+  for (int j = threadIdx.x; j < d; j += blockDim.x) acc += adj_edge<T>(to_f(dyr[j]) * to_f(xr[j]));
   acc = block_sum(acc, red);
-  const float dr = rnd<T>(acc);
+  const float dr = adj_edge<T>(acc);
   const float rp = rsqrtf(t + PCPB_GUARD);
-  const float dt = (dr * -0.5f) * ((rp * rp) * rp);
-  return dt / (((float)d + PCPB_GUARD) + PCPB_GUARD);
+  const float dt = adj_edge<float>((dr * -0.5f) * ((rp * rp) * rp));
+  return adj_edge<float>(dt / (((float)d + PCPB_GUARD) + PCPB_GUARD));
 }
 
 template <typename T>
@@ -151,7 +154,7 @@ __global__ void k_rmsnorm_bwd(const T* __restrict__ x, const float* __restrict__
   const float r = rnd<T>(rsqrtf(t));
   for (int j = threadIdx.x; j < d; j += blockDim.x) {
     const float xv = to_f(xr[j]);
-    float g = rnd<T>(to_f(dyr[j]) * r) + rnd<T>(ds * (2.f * xv));
+    float g = adj_edge<T>(to_f(dyr[j]) * r) + adj_edge<T>(ds * (2.f * xv));
     if (dres) g += to_f(dres[m * d + j]);
     dx[m * d + j] = from_f<T>(g);
   }
@@ -170,7 +173,7 @@ __global__ void k_embed_norm_bwd(const T* __restrict__ wte, const long long* __r
   const float r = rnd<T>(rsqrtf(t));
   for (int j = threadIdx.x; j < d; j += blockDim.x) {
     const float xv = to_f(xr[j]);
-    const float g = rnd<T>(rnd<T>(to_f(dyr[j]) * r) + rnd<T>(ds * (2.f * xv)));
+    const float g = rnd<T>(adj_edge<T>(to_f(dyr[j]) * r) + adj_edge<T>(ds * (2.f * xv)));
     atomicAdd(dwte + (size_t)row * d + j, g);
   }
 }
@@ -237,26 +240,48 @@ __global__ void __launch_bounds__(256) k_rmsnorm_bwd_vec(const T* __restrict__ x
   }
   const T* dyr = dy + (size_t)m * d;
   const int nv = d >> 3;
+  // Adjoint edges (see rmsnorm_row_ds).  The element-wise ones are products of dy with x, with r and of ds with 2x:
+  // the largest |dy| and |x| of the row bound them all, so the guard / clamp code only runs for a row whose bound fails
+  // (then it is exact); a row inside the bound is untouched by it, as in the reference.
   float acc = 0.f;
+  uint32_t mg = 0u, ma = 0u;
   for (int v = lane; v < nv; v += 32) {
     float a[8], g[8];
     ld8<T>(xr + v * 8, a);
     ld8<T>(dyr + v * 8, g);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc += rnd<T>(g[i] * a[i]);
+    for (int i = 0; i < 8; ++i) { acc += rnd<T>(g[i] * a[i]); adj_track(mg, g[i]); adj_track(ma, a[i]); }
+  }
+  mg = __reduce_max_sync(0xffffffffu, mg); ma = __reduce_max_sync(0xffffffffu, ma);
+  const float gmax = __uint_as_float(mg), amax = __uint_as_float(ma);
+  if (!(gmax * amax <= PCPB_ADJ_CLIP)) {                         // some product may be beyond the clamp (or not finite)
+    acc = 0.f;
+    for (int v = lane; v < nv; v += 32) {
+      float a[8], g[8];
+      ld8<T>(xr + v * 8, a);
+      ld8<T>(dyr + v * 8, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc += adj_edge<T>(g[i] * a[i]);
+    }
   }
   acc = warp_sum(acc);
   const float t = tsave[m];
-  const float dr = rnd<T>(acc);
+  const float dr = adj_edge<T>(acc);
   const float rp = rsqrtf(t + PCPB_GUARD);
-  const float ds = ((dr * -0.5f) * ((rp * rp) * rp)) / (((float)d + PCPB_GUARD) + PCPB_GUARD);
+  const float ds = adj_edge<float>(adj_edge<float>((dr * -0.5f) * ((rp * rp) * rp)) / (((float)d + PCPB_GUARD) + PCPB_GUARD));
   const float r = rnd<T>(rsqrtf(t));
+  const bool plain = (gmax * r <= PCPB_ADJ_CLIP) && (fabsf(ds) * 2.f * amax <= PCPB_ADJ_CLIP);
   for (int v = lane; v < nv; v += 32) {
     float a[8], g[8], o[8];
     ld8<T>(xr + v * 8, a);
     ld8<T>(dyr + v * 8, g);
+    if (plain) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] = rnd<T>(g[i] * r) + rnd<T>(ds * (2.f * a[i]));
+      for (int i = 0; i < 8; ++i) o[i] = rnd<T>(g[i] * r) + rnd<T>(ds * (2.f * a[i]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = adj_edge<T>(g[i] * r) + adj_edge<T>(ds * (2.f * a[i]));
+    }
     if (dwte) {
       // scatter into the f32 embedding gradient: two 16-byte vector reductions instead of eight scalar atomics
       float* dst = dwte + (size_t)row * d + v * 8;
@@ -391,13 +416,13 @@ __global__ void k_rope_qknorm_bwd(const T* __restrict__ qkv, const T* __restrict
     const float c = table_val<T>(cosT, (size_t)pos * half + i), s = table_val<T>(sinT, (size_t)pos * half + i);
     const float y1 = rnd<T>(rnd<T>(x1 * c) + rnd<T>(x2 * s));
     const float y2 = rnd<T>(rnd<T>(x1 * (-s)) + rnd<T>(x2 * c));
-    acc += rnd<T>(to_f(dyp[i]) * y1) + rnd<T>(to_f(dyp[i + half]) * y2);
+    acc += adj_edge<T>(to_f(dyp[i]) * y1) + adj_edge<T>(to_f(dyp[i + half]) * y2);
   }
   acc = warp_sum(acc);
-  const float dr = rnd<T>(acc);
+  const float dr = adj_edge<T>(acc);
   const float rp = rsqrtf(t + PCPB_GUARD);
-  const float dtt = (dr * -0.5f) * ((rp * rp) * rp);
-  const float ds = dtt / (((float)hd + PCPB_GUARD) + PCPB_GUARD);
+  const float dtt = adj_edge<float>((dr * -0.5f) * ((rp * rp) * rp));
+  const float ds = adj_edge<float>(dtt / (((float)hd + PCPB_GUARD) + PCPB_GUARD));
   const float r = rnd<T>(rsqrtf(t));
   for (int i = lane; i < half; i += 32) {
     const float x1 = to_f(src[i]), x2 = to_f(src[i + half]);
@@ -405,11 +430,11 @@ __global__ void k_rope_qknorm_bwd(const T* __restrict__ qkv, const T* __restrict
     const float y1 = rnd<T>(rnd<T>(x1 * c) + rnd<T>(x2 * s));
     const float y2 = rnd<T>(rnd<T>(x1 * (-s)) + rnd<T>(x2 * c));
     // gradient wrt the roped value y
-    const float g1 = rnd<T>(rnd<T>(to_f(dyp[i]) * r) + rnd<T>(ds * (2.f * y1)));
-    const float g2 = rnd<T>(rnd<T>(to_f(dyp[i + half]) * r) + rnd<T>(ds * (2.f * y2)));
+    const float g1 = rnd<T>(adj_edge<T>(to_f(dyp[i]) * r) + adj_edge<T>(ds * (2.f * y1)));
+    const float g2 = rnd<T>(adj_edge<T>(to_f(dyp[i + half]) * r) + adj_edge<T>(ds * (2.f * y2)));
     // y1 = x1*c + x2*s ; y2 = x1*(-s) + x2*c
-    dst[i] = from_f<T>(rnd<T>(g1 * c) + rnd<T>(g2 * (-s)));
-    dst[i + half] = from_f<T>(rnd<T>(g1 * s) + rnd<T>(g2 * c));
+    dst[i] = from_f<T>(adj_edge<T>(g1 * c) + adj_edge<T>(g2 * (-s)));
+    dst[i + half] = from_f<T>(adj_edge<T>(g1 * s) + adj_edge<T>(g2 * c));
   }
 }
 
@@ -487,21 +512,21 @@ __global__ void __launch_bounds__(256) k_rope_qknorm_bwd_vec(const T* __restrict
   rope8<T>(x1, x2, c, s, y1, y2);
   float acc = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) acc += rnd<T>(d1[i] * y1[i]) + rnd<T>(d2[i] * y2[i]);
+  for (int i = 0; i < 8; ++i) acc += adj_edge<T>(d1[i] * y1[i]) + adj_edge<T>(d2[i] * y2[i]);
   acc = group_sum(acc, tph);
   const float t = tq[(size_t)m * heads + h];
-  const float dr = rnd<T>(acc);
+  const float dr = adj_edge<T>(acc);
   const float rp = rsqrtf(t + PCPB_GUARD);
-  const float ds = ((dr * -0.5f) * ((rp * rp) * rp)) / (((float)hd + PCPB_GUARD) + PCPB_GUARD);
+  const float ds = adj_edge<float>(adj_edge<float>((dr * -0.5f) * ((rp * rp) * rp)) / (((float)hd + PCPB_GUARD) + PCPB_GUARD));
   const float r = rnd<T>(rsqrtf(t));
   if (!live) return;
   float o1[8], o2[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const float g1 = rnd<T>(rnd<T>(d1[i] * r) + rnd<T>(ds * (2.f * y1[i])));
-    const float g2 = rnd<T>(rnd<T>(d2[i] * r) + rnd<T>(ds * (2.f * y2[i])));
-    o1[i] = rnd<T>(g1 * c[i]) + rnd<T>(g2 * (-s[i]));
-    o2[i] = rnd<T>(g1 * s[i]) + rnd<T>(g2 * c[i]);
+    const float g1 = rnd<T>(adj_edge<T>(d1[i] * r) + adj_edge<T>(ds * (2.f * y1[i])));
+    const float g2 = rnd<T>(adj_edge<T>(d2[i] * r) + adj_edge<T>(ds * (2.f * y2[i])));
+    o1[i] = adj_edge<T>(g1 * c[i]) + adj_edge<T>(g2 * (-s[i]));
+    o2[i] = adj_edge<T>(g1 * s[i]) + adj_edge<T>(g2 * c[i]);
   }
   T* dst = dqkv + (size_t)m * wqkv + (size_t)h * hd + sub * 8;
   st8<T>(dst, o1);
@@ -568,7 +593,11 @@ __global__ void __launch_bounds__(256) k_rope_qknorm_bwd_bf16x2(const bf16* __re
   const uint32_t c[4] = {Cw.x, Cw.y, Cw.z, Cw.w}, sn[4] = {Sw.x, Sw.y, Sw.z, Sw.w};
   const uint32_t d1[4] = {D1.x, D1.y, D1.z, D1.w}, d2[4] = {D2.x, D2.y, D2.z, D2.w};
   uint32_t y1[4], y2[4];
+  // Adjoint edges: d*y products, dr, ds, d*r, ds*2y, and the products with cos / sin (|cos|, |sin| <= 1).  The largest
+  // |d| and |y| of the head row bound all the element-wise ones; the guard / clamp code runs only for a head row whose
+  // bound fails (and is exact there).
   float acc = 0.f;
+  uint32_t md = 0u, my = 0u;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     y1[i] = badd2(bmul2(x1[i], c[i]), bmul2(x2[i], sn[i]));
@@ -576,24 +605,51 @@ __global__ void __launch_bounds__(256) k_rope_qknorm_bwd_bf16x2(const bf16* __re
     const uint32_t p1 = bmul2(d1[i], y1[i]), p2 = bmul2(d2[i], y2[i]);
     acc += bf_lo(p1) + bf_lo(p2);
     acc += bf_hi(p1) + bf_hi(p2);
+    adj_track2(md, d1[i]); adj_track2(md, d2[i]); adj_track2(my, y1[i]); adj_track2(my, y2[i]);
+  }
+  // largest |d|, |y| over the head row (the tph lanes of this group); NaN is kept by the packed maximum
+  for (int o = tph >> 1; o > 0; o >>= 1) {
+    adj_track2(md, __shfl_xor_sync(0xffffffffu, md, o));
+    adj_track2(my, __shfl_xor_sync(0xffffffffu, my, o));
+  }
+  const float dmax = fmaxf(bf_lo(md), bf_hi(md)), ymax = fmaxf(bf_lo(my), bf_hi(my));
+  const bool nan_in = (bf_lo(md) != bf_lo(md)) || (bf_hi(md) != bf_hi(md)) || (bf_lo(my) != bf_lo(my)) || (bf_hi(my) != bf_hi(my));
+  if (nan_in || !(dmax * ymax <= PCPB_ADJ_CLIP)) {
+    acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t p1 = adj_edge2(bmul2(d1[i], y1[i])), p2 = adj_edge2(bmul2(d2[i], y2[i]));
+      acc += bf_lo(p1) + bf_lo(p2);
+      acc += bf_hi(p1) + bf_hi(p2);
+    }
   }
   acc = group_sum(acc, tph);
   const float t = tq[(size_t)m * heads + h];
-  const float dr = rnd<bf16>(acc);
+  const float dr = adj_edge<bf16>(acc);
   const float rp = rsqrtf(t + PCPB_GUARD);
-  const float ds = ((dr * -0.5f) * ((rp * rp) * rp)) / (((float)hd + PCPB_GUARD) + PCPB_GUARD);
-  const uint32_t r2 = pack2(rsqrtf(t), rsqrtf(t));
+  const float ds = adj_edge<float>(adj_edge<float>((dr * -0.5f) * ((rp * rp) * rp)) / (((float)hd + PCPB_GUARD) + PCPB_GUARD));
+  const float rr = rsqrtf(t);
+  const uint32_t r2 = pack2(rr, rr);
   if (!live) return;
+  // bound on d*r, ds*2y and on their sum g (which the cos / sin products cannot exceed)
+  const bool plain = !nan_in && (dmax * rr + fabsf(ds) * 2.f * ymax <= PCPB_ADJ_CLIP);
   uint32_t o1[4], o2[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     // gradient wrt the roped value: bf16(bf16(d * r) + bf16(ds * (2 * y))), ds in f32
-    const uint32_t t1 = pack2(ds * (2.f * bf_lo(y1[i])), ds * (2.f * bf_hi(y1[i])));
-    const uint32_t t2 = pack2(ds * (2.f * bf_lo(y2[i])), ds * (2.f * bf_hi(y2[i])));
-    const uint32_t g1 = badd2(bmul2(d1[i], r2), t1), g2 = badd2(bmul2(d2[i], r2), t2);
-    // y1 = x1*c + x2*s ; y2 = x1*(-s) + x2*c
-    o1[i] = badd2(bmul2(g1, c[i]), bmul2(g2, sn[i] ^ 0x80008000u));
-    o2[i] = badd2(bmul2(g1, sn[i]), bmul2(g2, c[i]));
+    uint32_t t1 = pack2(ds * (2.f * bf_lo(y1[i])), ds * (2.f * bf_hi(y1[i])));
+    uint32_t t2 = pack2(ds * (2.f * bf_lo(y2[i])), ds * (2.f * bf_hi(y2[i])));
+    if (plain) {
+      const uint32_t g1 = badd2(bmul2(d1[i], r2), t1), g2 = badd2(bmul2(d2[i], r2), t2);
+      // y1 = x1*c + x2*s ; y2 = x1*(-s) + x2*c
+      o1[i] = badd2(bmul2(g1, c[i]), bmul2(g2, sn[i] ^ 0x80008000u));
+      o2[i] = badd2(bmul2(g1, sn[i]), bmul2(g2, c[i]));
+    } else {
+      t1 = adj_edge2(t1); t2 = adj_edge2(t2);
+      const uint32_t g1 = badd2(adj_edge2(bmul2(d1[i], r2)), t1), g2 = badd2(adj_edge2(bmul2(d2[i], r2)), t2);
+      o1[i] = badd2(adj_edge2(bmul2(g1, c[i])), adj_edge2(bmul2(g2, sn[i] ^ 0x80008000u)));
+      o2[i] = badd2(adj_edge2(bmul2(g1, sn[i])), adj_edge2(bmul2(g2, c[i])));
+    }
   }
   bf16* dst = dqkv + (size_t)m * wqkv + (size_t)h * hd + sub * 8;
   *reinterpret_cast<uint4*>(dst) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
@@ -653,7 +709,8 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs& g, int m, int n, f
   const size_t o = (size_t)m * g.ldc + n;
   switch (g.epi) {
     case EPI_STORE:
-      ((T*)g.C)[o] = from_f<T>(acc);
+      // g.adj: the product is an activation gradient (dot_general VJP output), i.e. an adjoint edge
+      ((T*)g.C)[o] = from_f<T>(g.adj ? adj_edge<T>(acc) : acc);
       break;
     case EPI_RESID:
       ((T*)g.C)[o] = from_f<T>(to_f(((const T*)g.R)[o]) + rnd<T>(acc));
@@ -668,14 +725,14 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs& g, int m, int n, f
     case EPI_DRELU2: {
       // a = power(max(u,0), 2).  power VJP (src/autodiff/vjp_rules.zig:252): g * (2 * (a / r)), 0 at r == 0;
       // maximum VJP (:499): pass where u > 0.
-      const float da = rnd<T>(acc);
+      const float da = adj_edge<T>(acc);
       const float u = to_f(((const T*)g.R)[o]);
       const float r = fmaxf(u, 0.f);
       float out = 0.f;
       if (u > 0.f) {
         const float y = rnd<T>(r * r);
         const float q = rnd<T>(y / r);
-        out = rnd<T>(da * rnd<T>(2.f * q));
+        out = adj_edge<T>(da * rnd<T>(2.f * q));
       }
       ((T*)g.C)[o] = from_f<T>(out);
       break;
@@ -694,7 +751,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs& g, int m, int n, f
       break;
     }
     case EPI_DRELU:
-      ((T*)g.C)[o] = (to_f(((const T*)g.R)[o]) > 0.f) ? from_f<T>(acc) : from_f<T>(0.f);
+      ((T*)g.C)[o] = (to_f(((const T*)g.R)[o]) > 0.f) ? from_f<T>(adj_edge<T>(acc)) : from_f<T>(0.f);
       break;
     case EPI_BIAS:
       ((T*)g.C)[o] = from_f<T>(acc + to_f(((const T*)g.R)[n]));
@@ -706,7 +763,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs& g, int m, int n, f
       break;
     }
     case EPI_DGELU:
-      ((T*)g.C)[o] = from_f<T>(rnd<T>(acc) * gelu_grad<T>(to_f(((const T*)g.R)[o])));
+      ((T*)g.C)[o] = from_f<T>(adj_edge<T>(adj_edge<T>(acc) * gelu_grad<T>(to_f(((const T*)g.R)[o]))));
       break;
   }
 }
@@ -851,7 +908,7 @@ __global__ void __launch_bounds__(128) k_attn_bwd_generic(AttnArgs a) {
     }
     const float s = rnd<T>(rnd<T>(dot) * a.scale);
     const float ex = expf(s - mx);
-    dp = rnd<T>(dp);
+    dp = adj_edge<T>(dp);                         // dP: an output of the dot_general VJP
     pf[j] = rnd<T>(ex / (l + PCPB_GUARD));
     const float pt = ex / den2;
     Dp += pt * dp;
@@ -864,14 +921,17 @@ __global__ void __launch_bounds__(128) k_attn_bwd_generic(AttnArgs a) {
   for (int j = threadIdx.x; j <= i; j += blockDim.x) {
     const float dp = sm[2 * a.T + 2 * a.hd + j];
     const float dsf = ds[j] * (dp - D) - sm[3 * a.T + 2 * a.hd + j] * mterm;
-    ds[j] = rnd<T>(rnd<T>(dsf) * a.scale);
+    // the softmax backward is evaluated in closed form: its inner edges cannot be clamped one by one, only noted
+    const float dsr = rnd<T>(dsf);
+    if (!(fabsf(dsr) <= PCPB_ADJ_CLIP)) adj_note(ADJ_INTERNAL);
+    ds[j] = adj_edge<T>(dsr * a.scale);
   }
   __syncthreads();
   // dq_i = T(sum_j ds_j k_j)
   for (int e = threadIdx.x; e < a.hd; e += blockDim.x) {
     float acc = 0.f;
     for (int j = 0; j <= i; ++j) acc = fmaf(ds[j], to_f(qkn[((size_t)b * a.T + j) * wqkn + d + hk * a.hd + e]), acc);
-    ((T*)a.dqkn)[mi * wqkn + h * a.hd + e] = from_f<T>(acc);
+    ((T*)a.dqkn)[mi * wqkn + h * a.hd + e] = from_f<T>(adj_edge<T>(acc));
   }
   // dk_j += ds_j q_i ; dv_j += P_j do_i   (f32 accumulators shared by the heads of one kv group)
   for (int idx = threadIdx.x; idx < (i + 1) * a.hd; idx += blockDim.x) {
@@ -889,8 +949,8 @@ __global__ void k_attn_bwd_finish(const float* __restrict__ acc, int M, int d, i
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   for (; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const size_t m = i / (2 * dkv); const int c = (int)(i % (2 * dkv));
-    if (c < dkv) dqkn[m * (d + dkv) + d + c] = from_f<T>(acc[i]);
-    else dqkv[m * (d + 2 * dkv) + d + c] = from_f<T>(acc[i]);     // c in [dkv, 2dkv) -> column d + dkv + (c-dkv)
+    if (c < dkv) dqkn[m * (d + dkv) + d + c] = from_f<T>(adj_edge<T>(acc[i]));
+    else dqkv[m * (d + 2 * dkv) + d + c] = from_f<T>(adj_edge<T>(acc[i]));     // c in [dkv, 2dkv) -> column d + dkv + (c-dkv)
   }
 }
 
@@ -944,7 +1004,7 @@ cudaError_t launch_count_valid(cudaStream_t st, const long long* targets, int M,
 template <typename T>
 __global__ void __launch_bounds__(256) k_softcap_ce(T* __restrict__ logits, const long long* __restrict__ tg, int V,
                                                     float cap, long long ignore, const float* __restrict__ count,
-                                                    float* __restrict__ rowloss, int write_grad) {
+                                                    float* __restrict__ rowloss, int write_grad, float seed) {
   __shared__ float red[32];
   const size_t m = blockIdx.x;
   T* z = logits + m * V;
@@ -969,7 +1029,9 @@ __global__ void __launch_bounds__(256) k_softcap_ce(T* __restrict__ logits, cons
   }
   if (!write_grad) return;
   __syncthreads();
-  const float dtot = valid ? 1.f / (*count + 2.f * PCPB_GUARD) : 0.f;
+  // seed = d(loss) given by the caller.  The factors that follow (softmax probabilities, 1 - tanh^2, cap / (cap + 2e-4))
+  // never exceed one in magnitude, so once this first edge is inside the clamp every later edge of the loss is too.
+  const float dtot = valid ? adj_edge<float>(seed / (*count + 2.f * PCPB_GUARD)) : 0.f;
   const float den = se + 2.f * PCPB_GUARD;
   const float dzscale = capped ? cap / (capg + PCPB_GUARD) : 1.f;
   for (int j = threadIdx.x; j < V; j += blockDim.x) {
@@ -980,7 +1042,7 @@ __global__ void __launch_bounds__(256) k_softcap_ce(T* __restrict__ logits, cons
     if ((long long)j == t) dc -= 1.f;
     if (c == mx) dc += (2.f * PCPB_GUARD) / den;
     dc *= dtot;
-    z[j] = from_f<T>(dc * dzscale * (1.f - th * th));
+    z[j] = from_f<T>(adj_edge<T>(dc * dzscale * (1.f - th * th)));
   }
 }
 
@@ -988,7 +1050,7 @@ __global__ void __launch_bounds__(256) k_softcap_ce(T* __restrict__ logits, cons
 template <typename T>
 __global__ void __launch_bounds__(512) k_softcap_ce_vec(T* __restrict__ logits, const long long* __restrict__ tg, int V,
                                                         float cap, long long ignore, const float* __restrict__ count,
-                                                        float* __restrict__ rowloss, int write_grad) {
+                                                        float* __restrict__ rowloss, int write_grad, float seed) {
   __shared__ float red[32];
   const size_t m = blockIdx.x;
   T* z = logits + m * V;
@@ -1027,7 +1089,8 @@ __global__ void __launch_bounds__(512) k_softcap_ce_vec(T* __restrict__ logits, 
   }
   if (!write_grad) return;
   __syncthreads();                                  // the target logit was read above before anyone overwrites it
-  const float dtot = valid ? 1.f / (*count + 2.f * PCPB_GUARD) : 0.f;
+  const float dtot = valid ? adj_edge<float>(seed / (*count + 2.f * PCPB_GUARD)) : 0.f;     // the one edge that can grow
+  uint32_t mxa = 0u;
   const float iden = 1.f / (se + 2.f * PCPB_GUARD);
   const float dzscale = capped ? cap / (capg + PCPB_GUARD) : 1.f;
   for (int v = threadIdx.x; v < nv; v += blockDim.x) {
@@ -1041,19 +1104,25 @@ __global__ void __launch_bounds__(512) k_softcap_ce_vec(T* __restrict__ logits, 
       if ((long long)(v * 8 + i) == t) dc -= 1.f;
       if (c == mx) dc += (2.f * PCPB_GUARD) * iden;
       o[i] = dc * dtot * dzscale * (1.f - th * th);
+      adj_track(mxa, o[i]);
     }
     st8<T>(z + v * 8, o);
   }
+  // every value above is bounded by |dtot| <= 100 unless a logit was not finite; only then the row is passed through
+  // the guard / clamp of the output edge (non-finite -> 0)
+  if (__syncthreads_or(adj_over(mxa))) {
+    for (int j = threadIdx.x; j < V; j += blockDim.x) z[j] = from_f<T>(adj_edge<T>(to_f(z[j])));
+  }
 }
 cudaError_t launch_softcap_ce(cudaStream_t st, int dt, void* logits, const long long* targets, int M, int V,
-                              float cap, long long ignore, const float* count, float* rowloss, int write_grad) {
+                              float cap, long long ignore, const float* count, float* rowloss, int write_grad, float seed) {
   if (M == 0) return cudaSuccess;
   if (V % 8 == 0 && (((uintptr_t)logits) & 15) == 0) {
     const int threads = V >= 16384 ? 512 : 128;
-    DISPATCH_DT(dt, (k_softcap_ce_vec<T><<<M, threads, 0, st>>>((T*)logits, targets, V, cap, ignore, count, rowloss, write_grad)));
+    DISPATCH_DT(dt, (k_softcap_ce_vec<T><<<M, threads, 0, st>>>((T*)logits, targets, V, cap, ignore, count, rowloss, write_grad, seed)));
     return cudaGetLastError();
   }
-  DISPATCH_DT(dt, (k_softcap_ce<T><<<M, 256, 0, st>>>((T*)logits, targets, V, cap, ignore, count, rowloss, write_grad)));
+  DISPATCH_DT(dt, (k_softcap_ce<T><<<M, 256, 0, st>>>((T*)logits, targets, V, cap, ignore, count, rowloss, write_grad, seed)));
   return cudaGetLastError();
 }
 
@@ -1065,6 +1134,8 @@ __global__ void k_loss_finalize(const float* __restrict__ rowloss, int M, const 
   s = block_sum(s, red);
   if (threadIdx.x == 0) *loss = s / (*count + PCPB_GUARD);
 }
+cudaError_t adj_status_fetch_kernels(cudaStream_t st, int* out, bool clear) { return adj_status_fetch_tu(st, out, clear); }
+
 cudaError_t launch_loss_finalize(cudaStream_t st, const float* rowloss, int M, const float* count, float* loss) {
   k_loss_finalize<<<1, 1024, 0, st>>>(rowloss, M, count, loss);
   return cudaGetLastError();

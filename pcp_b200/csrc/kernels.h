@@ -31,6 +31,9 @@ struct GemmArgs {
   int M, N, K;
   int epi;
   float clip;           // EPI_WGRAD
+  int adj = 0;          // EPI_STORE only: 1 = the output is an activation gradient, finite-guarded and clamped to +-100
+                        // like every adjoint edge of the reference's engine (src/autodiff/engine.zig:622-682); the
+                        // backward epilogues (EPI_D*) always do so
   // tensor-core path only: split-K scratch of the caller (f32 slabs) and its device error word
   void* scratch = nullptr; size_t scratch_bytes = 0; int* err_word = nullptr;
 };
@@ -104,7 +107,15 @@ cudaError_t launch_copy_cols(cudaStream_t st, int dt, const void* src, long long
 // cap == 0 selects the plain cross entropy of the nanoGPT family (no soft-cap).
 cudaError_t launch_count_valid(cudaStream_t st, const long long* targets, int M, long long ignore, float* count);
 cudaError_t launch_softcap_ce(cudaStream_t st, int dt, void* logits, const long long* targets, int M, int V,
-                              float cap, long long ignore, const float* count, float* rowloss, int write_grad);
+                              float cap, long long ignore, const float* count, float* rowloss, int write_grad,
+                              float seed = 1.f);       // seed: d(loss) of model_forward_pass_grad
+// Adjoint-edge status of the kernels in kernels.cu / kernels_gpt.cu / gemm_tc.cu / attn_tc.cu / attn_flash.cu on the
+// current device (bits ADJ_CLAMPED, ADJ_INTERNAL of common.cuh), optionally cleared.  Blocks on `st`.
+cudaError_t adj_status_fetch_kernels(cudaStream_t st, int* out, bool clear);
+cudaError_t adj_status_fetch_kernels_gpt(cudaStream_t st, int* out, bool clear);
+cudaError_t adj_status_fetch_gemm_tc(cudaStream_t st, int* out, bool clear);
+cudaError_t adj_status_fetch_attn_tc(cudaStream_t st, int* out, bool clear);
+cudaError_t adj_status_fetch_attn_flash(cudaStream_t st, int* out, bool clear);
 cudaError_t launch_loss_finalize(cudaStream_t st, const float* rowloss, int M, const float* count, float* loss);
 
 // ---- optimiser -----------------------------------------------------------------------------------

@@ -9,6 +9,7 @@
 //   dxhat = dy * gamma;  dc = dxhat * r;  dr = sum(dxhat * (xf - mean));  dt = -0.5 dr rsqrt(t + 1e-4)^3
 //   f64 branch: dS2 = dt / (d + 2e-4);  dc64 = 2 dS2 c64;  dmean64 = -sum(dc64);  dx64 = dc64 + dmean64 / (d + 2e-4)
 //   f32 branch: dmean = -sum(dc);  dx = dc + dmean / (f32(d) + 2e-4) + f32(dx64)
+#define PCPB_ADJ_TU
 #include "common.cuh"
 #include "kernels.h"
 
@@ -210,7 +211,7 @@ __global__ void __launch_bounds__(256) k_layernorm_bwd(const T* __restrict__ x, 
     }
     A = warp_sum(A); Bc = warp_sum(Bc); C64 = warp_sum_d(C64);
     const float rp = rsqrtf(t + PCPB_GUARD);
-    const float dtv = (A * -0.5f) * ((rp * rp) * rp);
+    const float dtv = adj_edge<float>((A * -0.5f) * ((rp * rp) * rp));      // rsqrt VJP output: an adjoint edge
     const double dS2 = (double)dtv / dd2;
     const double dsum64 = (-2.0 * dS2 * C64) / dd2;
     const float dsum32 = (-Bc) / df2;
@@ -220,8 +221,9 @@ __global__ void __launch_bounds__(256) k_layernorm_bwd(const T* __restrict__ x, 
         const float xv = to_f(xr[j]);
         const float dc = (to_f(dyr[j]) * to_f(gamma[j])) * r;
         const double dx64 = 2.0 * dS2 * ((double)xv - mean64) + dsum64;
-        float o = dc + dsum32 + (float)dx64;
-        o = rnd<T>(o);
+        // the three contributions are edges of the f32 statistics graph, their sum crosses the f32 -> T convert edge
+        float o = adj_edge<float>(dc) + adj_edge<float>(dsum32) + adj_edge<float>((float)dx64);
+        o = adj_edge<T>(o);
         if (dres) o += to_f(dres[(size_t)m * d + j]);
         dx[(size_t)m * d + j] = from_f<T>(o);
       }
@@ -288,7 +290,7 @@ __global__ void __launch_bounds__(256) k_layernorm_bwd_vec(const T* __restrict__
     }
     A = warp_sum(A); Bc = warp_sum(Bc); C64 = warp_sum_d(C64);
     const float rp = rsqrtf(t + PCPB_GUARD);
-    const float dtv = (A * -0.5f) * ((rp * rp) * rp);
+    const float dtv = adj_edge<float>((A * -0.5f) * ((rp * rp) * rp));      // rsqrt VJP output: an adjoint edge
     const double dS2 = (double)dtv / dd2;
     const double dsum64 = (-2.0 * dS2 * C64) / dd2;
     const float dsum32 = (-Bc) / df2;
@@ -300,7 +302,7 @@ __global__ void __launch_bounds__(256) k_layernorm_bwd_vec(const T* __restrict__
       for (int e = 0; e < 8; ++e) {
         const float dc = (g[k][e] * gam[k][e]) * r;
         const double dx64 = 2.0 * dS2 * ((double)xv[k][e] - mean64) + dsum64;
-        o[e] = rnd<T>(dc + dsum32 + (float)dx64);
+        o[e] = adj_edge<T>(adj_edge<float>(dc) + adj_edge<float>(dsum32) + adj_edge<float>((float)dx64));
         if (dres) o[e] += res[e];
       }
       st8<T>(dx + (size_t)m * d + k * 256 + lane * 8, o);
@@ -387,7 +389,7 @@ __global__ void __launch_bounds__(256) k_layernorm_bwd_bf16(const bf16* __restri
     }
     A = warp_sum(A); Bc = warp_sum(Bc); C64 = warp_sum_d(C64);
     const float rp = rsqrtf(t + PCPB_GUARD);
-    const float dtv = (A * -0.5f) * ((rp * rp) * rp);
+    const float dtv = adj_edge<float>((A * -0.5f) * ((rp * rp) * rp));      // rsqrt VJP output: an adjoint edge
     const double dS2 = (double)dtv / dd2;
     const double dsum64 = (-2.0 * dS2 * C64) / dd2;
     const float dsum32 = (-Bc) / df2;
@@ -400,7 +402,7 @@ __global__ void __launch_bounds__(256) k_layernorm_bwd_bf16(const bf16* __restri
       for (int e = 0; e < 8; e += 2) {
         const float dc0 = (g[e] * gm[e]) * r, dc1 = (g[e + 1] * gm[e + 1]) * r;
         const double a0 = 2.0 * dS2 * ((double)xv[e] - mean64) + dsum64, a1 = 2.0 * dS2 * ((double)xv[e + 1] - mean64) + dsum64;
-        const uint32_t o2 = pack2(dc0 + dsum32 + (float)a0, dc1 + dsum32 + (float)a1);      // the bf16 rounding of dx
+        const uint32_t o2 = adj_edge2(pack2(dc0 + dsum32 + (float)a0, dc1 + dsum32 + (float)a1));      // the bf16 rounding of dx, as an adjoint edge
         o[e] = bf_lo(o2); o[e + 1] = bf_hi(o2);
         if (dres) { o[e] += res[e]; o[e + 1] += res[e + 1]; }
       }
@@ -559,5 +561,7 @@ cudaError_t launch_copy_cols(cudaStream_t st, int dt, const void* src, long long
                                                                                             dst_pitch, M, ncols)));
   return cudaGetLastError();
 }
+
+cudaError_t adj_status_fetch_kernels_gpt(cudaStream_t st, int* out, bool clear) { return adj_status_fetch_tu(st, out, clear); }
 
 }  // namespace pcpb

@@ -3,9 +3,10 @@
 // The regular optimiser entry (pcpb_execute "apply_optimizer") allocates its output buffers and a small
 // descriptor table on every call, and the fused worker path keeps its reduction scratch in a workspace
 // obtained with cudaMalloc.  Some hosts cannot accept that: a runtime that hands this library slices of one
-// arena it reserved up front and accounts for every byte (the reference's worker sits on such a runtime: the
-// IREE HAL owns all device memory the worker sees and is capped, src/mlir/context.zig:236-239), or a service
-// whose step loop forbids allocation calls because they synchronise the whole device.  For them
+// arena it reserved up front and accounts for every byte (memory-planned runtimes work this way; the reference
+// compiles its modules for one and even bounds the size of a single allocation at compile time with
+// --iree-stream-resource-max-allocation-size, src/mlir/context.zig:238-239), or a service whose step loop
+// forbids allocation calls because cudaMalloc / cudaFree synchronise the whole device.  For them
 // pcpb_adamw_step_noalloc runs the same three AdamW kernels on caller-owned tensors with the per-chunk
 // reduction scratch and the launch descriptors placed in a fixed array inside the library image.
 //

@@ -241,16 +241,20 @@ GemmArgs mk(const void* A, long long sam, long long sak, const void* B, long lon
   return g;
 }
 #define G(b, ...) do { int r__ = gemm(b, mk(__VA_ARGS__)); if (r__) return r__; } while (0)
+// activation-gradient product (dot_general VJP output): stored through the adjoint-edge guard and clamp
+#define GA(b, ...) do { GemmArgs g__ = mk(__VA_ARGS__); g__.adj = 1; int r__ = gemm(b, g__); if (r__) return r__; } while (0)
 
 // ------------------------------------------------------------------------------------------------
 // one forward (+ backward) of the model on the parameters in `wts` (model dtype, flat)
 // ------------------------------------------------------------------------------------------------
 int forward_backward_gpt(pcpb_backend* b, const void* wts, const long long* ids, const long long* targets, float* grads,
-                         float* loss_out, bool backward);
+                         float* loss_out, bool backward, float seed);
 
+// seed: d(loss), 1 for compute_gradients; model_forward_pass_grad passes the caller's value, which then flows through
+// every adjoint edge (and its clamp) like in the reference's gradient function
 int forward_backward(pcpb_backend* b, const void* wts, const long long* ids, const long long* targets, float* grads,
-                     float* loss_out, bool backward) {
-  if (b->cfg.family == FAMILY_NANOGPT) return forward_backward_gpt(b, wts, ids, targets, grads, loss_out, backward);
+                     float* loss_out, bool backward, float seed = 1.f) {
+  if (b->cfg.family == FAMILY_NANOGPT) return forward_backward_gpt(b, wts, ids, targets, grads, loss_out, backward, seed);
   const ModelConfig& c = b->cfg;
   Workspace& w = b->ws;
   cudaStream_t st = b->stream;
@@ -298,12 +302,12 @@ int forward_backward(pcpb_backend* b, const void* wts, const long long* ids, con
   G(b, w.hf, d, 1, W(ph), 1, d, w.logits, V, M, V, d, EPI_STORE);
   KL(b, 1, launch_count_valid(st, targets, M, c.ignore_index, w.count));
   KL(b, 1, launch_softcap_ce(st, dt, w.logits, targets, M, V, c.softcap, c.ignore_index, w.count, w.rowloss,
-                             backward ? 1 : 0));
+                             backward ? 1 : 0, seed));
   KL(b, 1, launch_loss_finalize(st, w.rowloss, M, w.count, loss_out));
   if (!backward) return PCPB_OK;
 
   // ---- backward ----
-  G(b, w.logits, V, 1, W(ph), d, 1, w.dh, d, M, d, V, EPI_STORE);                  // d hf
+  GA(b, w.logits, V, 1, W(ph), d, 1, w.dh, d, M, d, V, EPI_STORE);                  // d hf
   G(b, w.logits, 1, V, w.hf, d, 1, GR(ph), d, V, d, M, EPI_WGRAD);                 // d lm_head
   KL(b, 1, launch_rmsnorm_bwd(st, dt, w.xs[L], w.tf, w.dh, nullptr, M, d, w.dx));
   for (int l = L - 1; l >= 0; --l) {
@@ -313,10 +317,10 @@ int forward_backward(pcpb_backend* b, const void* wts, const long long* ids, con
     G(b, w.dx, d, 1, W(pq + 5), F, 1, w.du, F, M, F, d, EPI_DRELU2, a.u);           // du
     G(b, w.dx, 1, d, a.a, F, 1, GR(pq + 5), F, d, F, M, EPI_WGRAD);                 // d mlp.c_proj [d,F]
     G(b, w.du, 1, F, a.h2, d, 1, GR(pq + 4), d, F, d, M, EPI_WGRAD);                // d c_fc [F,d]
-    G(b, w.du, F, 1, W(pq + 4), d, 1, w.dh, d, M, d, F, EPI_STORE);                 // d h2
+    GA(b, w.du, F, 1, W(pq + 4), d, 1, w.dh, d, M, d, F, EPI_STORE);                 // d h2
     KL(b, 1, launch_rmsnorm_bwd(st, dt, a.xmid, a.t2, w.dh, w.dx, M, d, w.dx));
     // attention
-    G(b, w.dx, d, 1, W(pq + 3), d, 1, w.dout, d, M, d, d, EPI_STORE);               // d o
+    GA(b, w.dx, d, 1, W(pq + 3), d, 1, w.dout, d, M, d, d, EPI_STORE);               // d o
     G(b, w.dx, 1, d, a.o, d, 1, GR(pq + 3), d, d, d, M, EPI_WGRAD);                 // d c_proj
     FlashArgs fa{};
     fa.qkn = a.qkn; fa.qkv = a.qkv; fa.o = a.o; fa.mrow = a.mrow; fa.lrow = a.lrow;
@@ -337,7 +341,7 @@ int forward_backward(pcpb_backend* b, const void* wts, const long long* ids, con
     }
     KL(b, 1, launch_rope_qknorm_bwd(st, dt, a.qkv, w.dqkn, a.tq, w.d_cos, w.d_sin, M, Tn, H, Hkv, hd, w.dqkv));
     G(b, w.dqkv, 1, wq, a.h1, d, 1, GR(pq), d, wq, d, M, EPI_WGRAD);                // d c_q,c_k,c_v (contiguous)
-    G(b, w.dqkv, wq, 1, W(pq), d, 1, w.dh, d, M, d, wq, EPI_STORE);                 // d h1
+    GA(b, w.dqkv, wq, 1, W(pq), d, 1, w.dh, d, M, d, wq, EPI_STORE);                 // d h1
     KL(b, 1, launch_rmsnorm_bwd(st, dt, w.xs[l], a.t1, w.dh, w.dx, M, d, w.dx));
   }
   CK(b, cudaMemsetAsync(GR(0), 0, (size_t)c.params[0].numel * 4, st));
@@ -387,7 +391,7 @@ int attention_bwd(pcpb_backend* b, LayerActs& a, float scale) {
 // nanoGPT family: learned position embedding, LayerNorm (gamma, beta), fused c_attn, ReLU or tanh-GELU MLP, lm_head with bias,
 // plain cross entropy ignoring targets == -100 (models/nanogpt_small.mlir, models/nanogpt_medium_bf16.mlir).
 int forward_backward_gpt(pcpb_backend* b, const void* wts, const long long* ids, const long long* targets, float* grads,
-                         float* loss_out, bool backward) {
+                         float* loss_out, bool backward, float seed) {
   const ModelConfig& c = b->cfg;
   Workspace& w = b->ws;
   cudaStream_t st = b->stream;
@@ -421,12 +425,12 @@ int forward_backward_gpt(pcpb_backend* b, const void* wts, const long long* ids,
   KL(b, 1, launch_layernorm_fwd(st, dt, w.xs[L], W(pf), W(pf + 1), M, d, w.hf, w.muf, w.tf, w.m64f));
   G(b, w.hf, d, 1, W(pf + 2), 1, d, w.logits, V, M, V, d, EPI_BIAS, W(pf + 3));
   KL(b, 1, launch_count_valid(st, targets, M, c.ignore_index, w.count));
-  KL(b, 1, launch_softcap_ce(st, dt, w.logits, targets, M, V, 0.f, c.ignore_index, w.count, w.rowloss, backward ? 1 : 0));
+  KL(b, 1, launch_softcap_ce(st, dt, w.logits, targets, M, V, 0.f, c.ignore_index, w.count, w.rowloss, backward ? 1 : 0, seed));
   KL(b, 1, launch_loss_finalize(st, w.rowloss, M, w.count, loss_out));
   if (!backward) return PCPB_OK;
 
   KL(b, 2, launch_colsum(st, dt, w.logits, M, V, w.cs_partial, GR(pf + 3)));       // d lm_head.b
-  G(b, w.logits, V, 1, W(pf + 2), d, 1, w.dh, d, M, d, V, EPI_STORE);              // d hf
+  GA(b, w.logits, V, 1, W(pf + 2), d, 1, w.dh, d, M, d, V, EPI_STORE);              // d hf
   G(b, w.logits, 1, V, w.hf, d, 1, GR(pf + 2), d, V, d, M, EPI_WGRAD);             // d lm_head.w
   KL(b, 2, launch_layernorm_bwd(st, dt, w.xs[L], W(pf), w.muf, w.tf, w.m64f, w.dh, nullptr, M, d, w.dx, w.ln_partial,
                                 GR(pf), GR(pf + 1)));
@@ -436,16 +440,16 @@ int forward_backward_gpt(pcpb_backend* b, const void* wts, const long long* ids,
     G(b, w.dx, d, 1, W(p0 + 7), F, 1, w.du, F, M, F, d, gelu ? EPI_DGELU : EPI_DRELU, a.u);           // du
     G(b, w.dx, 1, d, a.a, F, 1, GR(p0 + 7), F, d, F, M, EPI_WGRAD);                // d mlp.c_proj
     G(b, w.du, 1, F, a.h2, d, 1, GR(p0 + 6), d, F, d, M, EPI_WGRAD);               // d c_fc
-    G(b, w.du, F, 1, W(p0 + 6), d, 1, w.dh, d, M, d, F, EPI_STORE);                // d h2
+    GA(b, w.du, F, 1, W(p0 + 6), d, 1, w.dh, d, M, d, F, EPI_STORE);                // d h2
     KL(b, 2, launch_layernorm_bwd(st, dt, a.xmid, W(p0 + 4), a.mu2, a.t2, a.m64_2, w.dh, w.dx, M, d, w.dx, w.ln_partial,
                                   GR(p0 + 4), GR(p0 + 5)));
-    G(b, w.dx, d, 1, W(p0 + 3), d, 1, w.dout, d, M, d, d, EPI_STORE);              // d o
+    GA(b, w.dx, d, 1, W(p0 + 3), d, 1, w.dout, d, M, d, d, EPI_STORE);              // d o
     G(b, w.dx, 1, d, a.o, d, 1, GR(p0 + 3), d, d, d, M, EPI_WGRAD);                // d c_proj
     int r = attention_bwd(b, a, scale);
     if (r) return r;
     KL(b, 1, launch_copy_cols(st, dt, w.dqkn, 2 * d, w.dqkv, wq, M, 2 * d));       // dq|dk next to dv
     G(b, w.dqkv, 1, wq, a.h1, d, 1, GR(p0 + 2), d, wq, d, M, EPI_WGRAD);           // d c_attn
-    G(b, w.dqkv, wq, 1, W(p0 + 2), d, 1, w.dh, d, M, d, wq, EPI_STORE);            // d h1
+    GA(b, w.dqkv, wq, 1, W(p0 + 2), d, 1, w.dh, d, M, d, wq, EPI_STORE);            // d h1
     KL(b, 2, launch_layernorm_bwd(st, dt, w.xs[l], W(p0), a.mu1, a.t1, a.m64_1, w.dh, w.dx, M, d, w.dx, w.ln_partial,
                                   GR(p0), GR(p0 + 1)));
   }
@@ -678,6 +682,21 @@ int pcpb_read_to_host(pcpb_backend* b, const pcpb_buffer* buf, void* dst, size_t
   return PCPB_OK;
 }
 
+int pcpb_adjoint_status(pcpb_backend* b, int* flags, int clear) {
+  if (!b || !b->stream || !flags) return PCPB_E_INVALID;
+  DeviceGuard g(b->device);
+  int total = 0, one = 0;
+  cudaError_t (*fetch[])(cudaStream_t, int*, bool) = {adj_status_fetch_kernels, adj_status_fetch_kernels_gpt, adj_status_fetch_gemm_tc,
+                                                      adj_status_fetch_attn_tc, adj_status_fetch_attn_flash};
+  for (auto f : fetch) {
+    one = 0;
+    CK(b, f(b->stream, &one, clear != 0));
+    total |= one;
+  }
+  *flags = total;
+  return PCPB_OK;
+}
+
 int pcpb_synchronize(pcpb_backend* b) {
   if (!b || !b->stream) return PCPB_E_INVALID;
   DeviceGuard g(b->device);
@@ -801,18 +820,23 @@ int pcpb_execute(pcpb_backend* b, const char* fn, pcpb_buffer* const* in, size_t
     if ((r = check_param_inputs(b, in, 0, c.dtype, name.c_str()))) return r;
     if (!data_ok(in[N]) || !data_ok(in[N + 1])) return fail(b, PCPB_E_INVALID, "ids/targets must be i64 [B,T]");
     if ((r = gather_flat(b, in, 0, w.shadow, es))) return r;
+    // seed: d(loss) given by the caller (a scalar of the loss's type, f32); it enters at the loss and passes through
+    // the guard and clamp of every adjoint edge like any other adjoint
+    float seed = 1.f;
+    if (grad) {
+      if (!in[N + 2] || in[N + 2]->nbytes != 4 || in[N + 2]->dtype != PCPB_F32)
+        return fail(b, PCPB_E_INVALID, "model_forward_pass_grad: the loss gradient must be one f32");
+      CK(b, cudaMemcpyAsync(&seed, in[N + 2]->ptr, 4, cudaMemcpyDeviceToHost, b->stream));
+      CK(b, cudaStreamSynchronize(b->stream));
+    }
     Block* lb = nullptr;
     if ((r = alloc_block(b, 4, &lb))) return r;
     r = forward_backward(b, w.shadow, (const long long*)in[N]->ptr, (const long long*)in[N + 1]->ptr, w.grads,
-                         (float*)lb->ptr, grad);
+                         (float*)lb->ptr, grad, seed);
     if (r) { block_release(lb); return r; }
     pcpb_buffer** o = nullptr;
     if (grad) {
-      // seed: d(loss) given by the caller (f32 scalar); gradients are returned in the model dtype
-      float seed = 1.f;
-      if (in[N + 2] && in[N + 2]->nbytes == 4) CK(b, cudaMemcpyAsync(&seed, in[N + 2]->ptr, 4, cudaMemcpyDeviceToHost, b->stream));
-      CK(b, cudaStreamSynchronize(b->stream));
-      if (seed != 1.f) KL(b, 1, launch_scale_f32(b->stream, w.grads, seed, P));
+      // gradients are returned in the model dtype
       Block* gb = nullptr;
       if ((r = alloc_block(b, P * es, &gb))) { block_release(lb); return r; }
       if (c.dtype == DT_F32) CK(b, cudaMemcpyAsync(gb->ptr, w.grads, P * 4, cudaMemcpyDeviceToDevice, b->stream));

@@ -101,3 +101,108 @@ def test_shard_ranges_cover_exactly():
                 assert lo == min(at, total) and lo <= hi <= total
                 at = max(at, hi)
             assert at == total
+
+
+# ---------------------------------------------------------------------------------------------------------
+# a rank leaves between rounds: the velocity shards are handed over and cut again for the smaller group
+# ---------------------------------------------------------------------------------------------------------
+class ElasticFakeBackend(FakeBackend):
+    def worker_read_state(self, which):
+        if which == "master":
+            return np.array(np.memmap(os.path.join(self.tmp, f"master{self.file_id}"), np.float32, "r", shape=(P,)))
+        assert which == "velocity"
+        return self.vel.copy()
+
+    def worker_write_state(self, which, values):
+        assert which == "velocity" and len(values) == shard_len(P, self.world)
+        self.vel = np.array(values, np.float32)
+
+    def outer_attach_ipc(self, rank, world, handles):
+        # like the library: the same (rank, world) keeps the shard, another membership starts it at zero
+        if (rank, world) != (self.rank, self.world) or not hasattr(self, "peers"):
+            self.vel = np.zeros(shard_len(P, world), np.float32)
+        self.rank, self.world = rank, world
+        self.peers = [int(handles[w * 128:(w + 1) * 128].rstrip(b"\0")) for w in range(world)]
+
+    def outer_export(self):
+        return f"{self.file_id}".encode().ljust(128, b"\0")
+
+    def outer_apply(self, lr, mu, dt, contributors=None):
+        lo, hi = shard_range(P, self.world, self.rank)
+        acc = np.zeros(hi - lo, np.float32)
+        for fid in self.peers:
+            acc = acc + np.memmap(os.path.join(self.tmp, f"delta{fid}"), np.float32, "r", shape=(P,))[lo:hi]
+        acc = acc / np.float32(len(self.peers))
+        acc[~np.isfinite(acc)] = 0
+        lr, mu = np.float32(lr), np.float32(mu)
+        v = mu * self.vel[:hi - lo] + acc
+        self.vel[:hi - lo] = v
+        new = self.master[lo:hi] - lr * (acc + mu * v)
+        for fid in self.peers:
+            m = np.memmap(os.path.join(self.tmp, f"master{fid}"), np.float32, "r+", shape=(P,))
+            m[lo:hi] = new
+            m.flush()
+        return 0.0
+
+
+def _elastic_worker(rank, world, tmp, port):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    rng = np.random.default_rng(0)
+    master0 = rng.standard_normal(P).astype(np.float32)
+    deltas1 = [rng.standard_normal(P).astype(np.float32) * 0.01 for _ in range(world)]
+    deltas2 = [rng.standard_normal(P).astype(np.float32) * 0.01 for _ in range(world)]
+    be = ElasticFakeBackend(tmp, rank, world, master0, deltas1[rank])
+    be.file_id = rank
+    grp = DilocoGroup(be, TorchDistTransport(dist))
+    grp.outer_step(0.0)                                           # round 1: all three workers
+    stay = [0, 2]
+    shards = grp.hand_over()                                      # every rank of the old group, the leaver included
+    sub = dist.new_group(stay)                                    # collective over all processes
+    ok = True
+    if rank in stay:
+        be.delta[:] = deltas2[rank]; be.delta.flush()
+        grp.regroup(TorchDistTransport(dist, sub), shards, P)
+        grp.outer_step(0.0)                                       # round 2: two workers, momentum carried
+        m1, v1, _ = outer_step([torch.from_numpy(master0)], [torch.zeros(P)], [[torch.from_numpy(d)] for d in deltas1],
+                               [0.0] * world, NesterovConf(0.7, 0.9), "f32")
+        m2, v2, _ = outer_step(m1, v1, [[torch.from_numpy(deltas2[r])] for r in stay], [0.0] * 2, NesterovConf(0.7, 0.9), "f32")
+        got = np.array(np.memmap(os.path.join(tmp, f"master{rank}"), np.float32, "r", shape=(P,)))
+        lo, hi = shard_range(P, 2, stay.index(rank))
+        ok = np.array_equal(got, m2[0].numpy()) and np.array_equal(be.vel[:hi - lo], v2[0].numpy()[lo:hi])
+        ok = ok and grp.master_checksum_agrees()
+    with open(os.path.join(tmp, f"ok{rank}"), "w") as f:
+        f.write("1" if ok else "0")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_rank_leaves_between_rounds_velocity_survives():
+    """Three workers do a round, worker 1 leaves, workers 0 and 2 regroup and do another round: master and velocity
+    equal the restated Shepherd's, which keeps the Nesterov velocities across membership changes
+    (src/algorithms/diloco.zig:418-444, src/optimizers/nesterov.zig:70-98)."""
+    with tempfile.TemporaryDirectory() as tmp:
+        port = 29500 + (os.getpid() % 2000) + 7
+        mp.spawn(_elastic_worker, args=(3, tmp, port), nprocs=3, join=True)
+        for r in range(3):
+            assert open(os.path.join(tmp, f"ok{r}")).read() == "1"
+
+
+def test_reshard_velocity_round_trips_and_lost_shard():
+    from pcp_b200.diloco import reshard_velocity
+    full = np.arange(P, dtype=np.float32) + 1
+    old = []
+    for r in range(3):
+        lo, hi = shard_range(P, 3, r)
+        sh = np.zeros(shard_len(P, 3), np.float32); sh[:hi - lo] = full[lo:hi]
+        old.append(sh)
+    for new_world in (1, 2, 4):
+        got = np.concatenate([reshard_velocity(old, P, new_world, r)[: shard_range(P, new_world, r)[1] - shard_range(P, new_world, r)[0]]
+                              for r in range(new_world)])
+        assert np.array_equal(got, full)
+    old[1] = None                                                 # a rank that died without handing its shard over
+    got = np.concatenate([reshard_velocity(old, P, 2, r)[: shard_range(P, 2, r)[1] - shard_range(P, 2, r)[0]] for r in range(2)])
+    lo, hi = shard_range(P, 3, 1)
+    want = full.copy(); want[lo:hi] = 0
+    assert np.array_equal(got, want)
