@@ -412,9 +412,14 @@ def run_rollout(args):
     if dist:
         dist.barrier()
     sampler.start()
-    r = time_rollout(local, K, W, peaks)
+    c = dict(ROLLOUT)
+    if args.rollout_layers:                               # profiling sizes: fewer layers / tokens of the same kernels
+        c["n_layer"] = args.rollout_layers
+    if args.rollout_new:
+        c["new_tokens"] = args.rollout_new
+    r = time_rollout(local, K, W, peaks, c)
     clocks = sampler.stop()
-    n_new = ROLLOUT["batch"] * ROLLOUT["new_tokens"]
+    n_new = c["batch"] * c["new_tokens"]
     ms = r["prefill_ms"] + r["decode_ms"]
     e2e = r["e2e"]
     if dist:                                              # replicas only: no exchange between ranks; slowest rank sets the time
@@ -426,7 +431,7 @@ def run_rollout(args):
         return 0
     line = {"metric": "rollout_tokens_per_s", "value": world * n_new / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic", "config": {"workload": ROLLOUT_DESCR, "model": ROLLOUT, "parallelism": f"{world} independent replicas",
+            "data": "synthetic", "config": {"workload": ROLLOUT_DESCR, "model": c, "parallelism": f"{world} independent replicas",
                                             "l2": "inputs larger than L2: every decode step streams 15 GB of weights"},
             "roofline": dict(r["roofline"], peak_source=f"{peak_src} copy bandwidth"),
             "e2e": {"value": world * e2e, "unit": "tokens/s", "h2d_bytes_per_step": r["h2d_bytes"], "d2h_bytes_per_step": r["d2h_bytes"],
@@ -674,6 +679,8 @@ def main():
     ap.add_argument("--workload", default="d20", choices=sorted(WORKLOADS) + ["qwen3_rollout"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true")
+    ap.add_argument("--rollout-layers", type=int, default=0, help="qwen3_rollout: layers (default: the configuration's 36)")
+    ap.add_argument("--rollout-new", type=int, default=0, help="qwen3_rollout: new tokens per sequence (default 256)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

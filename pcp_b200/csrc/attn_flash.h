@@ -12,6 +12,8 @@ struct FlashArgs {
   float* lrow;          // [B*H*T] row sum of exp(s - max)
   int B, T, H, Hkv, hd;
   float scale;          // 1/sqrt(hd) rounded to bf16
+  int no_guard;         // forward only: 1 = plain softmax, p = e / l (generation graphs are not sanitised);
+                        // 0 = the training graphs' p = e / (l + 1e-4)
   // backward
   const void* dout;     // [B*T, d]
   void* dqkn;           // [B*T, d + dkv]   gradient wrt qkn (q and k parts written)

@@ -58,6 +58,7 @@ enum { MODE_FWD = 0, MODE_DQ = 1, MODE_DKV = 2 };
 struct AtcParams {
   int B, T, H, Hkv;
   float scale;
+  float fwd_guard;                             // added to the softmax denominator in the forward (1e-4, or 0)
   int d, dkv;                                  // model width, kv width
   const bf16* qkn; const bf16* dout;           // row-side tiles that the element-wise warps load themselves
   bf16* o; float* mrow; float* lrow; const float* drow;
@@ -483,7 +484,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
 #pragma unroll
         for (int c = 0; c < NCG; ++c) l += stat[(c * 128 + row) * 2 + 1] * ex2((stat[(c * 128 + row) * 2] - mn) * LOG2E);
         m_run = mn; l_run = l;
-        inv1 = 1.f / (l_run + PCPB_GUARD);
+        inv1 = 1.f / (l_run + p.fwd_guard);
       }
     }
     const int g0 = (MODE == MODE_FWD) ? n_it : 0;            // a multiple of NBUF: the buffer of sub-tile `it` is it % NBUF
@@ -677,52 +678,61 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
 __global__ void __launch_bounds__(256) k_attn_tc_prep(const bf16* __restrict__ o, const bf16* __restrict__ dout,
                                                       const float* __restrict__ lrow, float* __restrict__ drow, int B, int T, int H,
                                                       const bf16* __restrict__ qkv, int Hkv) {
-  const long long gt = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long gw = gt >> 3;                       // row index over (b, h, i); B*H*T is a multiple of 4: whole warps
+  __shared__ float sred[3][8];
   const int sub = threadIdx.x & 7;
-  if (gw >= (long long)B * H * T) return;
-  const int i = (int)(gw % T), bh = (int)(gw / T), b = bh / H, h = bh % H;
-  const size_t off = ((size_t)b * T + i) * ((size_t)H * HD) + (size_t)h * HD + sub * 16;
-  const uint4 a0 = *reinterpret_cast<const uint4*>(o + off), a1 = *reinterpret_cast<const uint4*>(o + off + 8);
-  const uint4 c0 = *reinterpret_cast<const uint4*>(dout + off), c1 = *reinterpret_cast<const uint4*>(dout + off + 8);
-  const uint32_t x[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-  const uint32_t y[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-  float acc = 0.f;
+  const long long rows = (long long)B * H * T;
+  // statistics for the bound on the adjoints that stay on the chip in the backward kernels (dP, dS): the largest
+  // squared norm of a dO row and of a V row, the largest |D|; gathered per thread over its rows, then per block
+  float m_do = 0.f, m_v = 0.f, m_d = 0.f;
+  for (long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3; gw < rows; gw += ((long long)gridDim.x * blockDim.x) >> 3) {
+    const int i = (int)(gw % T), bh = (int)(gw / T), b = bh / H, h = bh % H;
+    const size_t off = ((size_t)b * T + i) * ((size_t)H * HD) + (size_t)h * HD + sub * 16;
+    const uint4 a0 = *reinterpret_cast<const uint4*>(o + off), a1 = *reinterpret_cast<const uint4*>(o + off + 8);
+    const uint4 c0 = *reinterpret_cast<const uint4*>(dout + off), c1 = *reinterpret_cast<const uint4*>(dout + off + 8);
+    const uint32_t x[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const uint32_t y[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    float acc = 0.f, n_do = 0.f, n_v = 0.f;
 #pragma unroll
-  for (int k = 0; k < 8; ++k) acc += bf_lo(x[k]) * bf_lo(y[k]) + bf_hi(x[k]) * bf_hi(y[k]);
-  // squared norms of the dO row and (for the kv heads) of the V row: the bound on the on-chip adjoints dP, dS
-  float n_do = 0.f, n_v = 0.f;
+    for (int k = 0; k < 8; ++k) {
+      acc += bf_lo(x[k]) * bf_lo(y[k]) + bf_hi(x[k]) * bf_hi(y[k]);
+      n_do += bf_lo(y[k]) * bf_lo(y[k]) + bf_hi(y[k]) * bf_hi(y[k]);
+    }
+    if (h < Hkv) {
+      const size_t voff = ((size_t)b * T + i) * ((size_t)(H + 2 * Hkv) * HD) + (size_t)(H + Hkv + h) * HD + sub * 16;
+      const uint4 v0 = *reinterpret_cast<const uint4*>(qkv + voff), v1 = *reinterpret_cast<const uint4*>(qkv + voff + 8);
+      const uint32_t z[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 #pragma unroll
-  for (int k = 0; k < 8; ++k) n_do += bf_lo(y[k]) * bf_lo(y[k]) + bf_hi(y[k]) * bf_hi(y[k]);
-  if (h < Hkv) {
-    const size_t voff = ((size_t)b * T + i) * ((size_t)(H + 2 * Hkv) * HD) + (size_t)(H + Hkv + h) * HD + sub * 16;
-    const uint4 v0 = *reinterpret_cast<const uint4*>(qkv + voff), v1 = *reinterpret_cast<const uint4*>(qkv + voff + 8);
-    const uint32_t z[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+      for (int k = 0; k < 8; ++k) n_v += bf_lo(z[k]) * bf_lo(z[k]) + bf_hi(z[k]) * bf_hi(z[k]);
+    }
 #pragma unroll
-    for (int k = 0; k < 8; ++k) n_v += bf_lo(z[k]) * bf_lo(z[k]) + bf_hi(z[k]) * bf_hi(z[k]);
-  }
-#pragma unroll
-  for (int s = 1; s <= 4; s <<= 1) {
-    acc += __shfl_xor_sync(0xffffffffu, acc, s);
-    n_do += __shfl_xor_sync(0xffffffffu, n_do, s);
-    n_v += __shfl_xor_sync(0xffffffffu, n_v, s);
-  }
-  float D = 0.f;
-  if (sub == 0) {
+    for (int s = 1; s <= 4; s <<= 1) {
+      acc += __shfl_xor_sync(0xffffffffu, acc, s);
+      n_do += __shfl_xor_sync(0xffffffffu, n_do, s);
+      n_v += __shfl_xor_sync(0xffffffffu, n_v, s);
+    }
     const float l = lrow[gw];
-    D = acc * (l + PCPB_GUARD) / (l + 2.f * PCPB_GUARD);
-    drow[gw] = D;
+    const float D = acc * (l + PCPB_GUARD) / (l + 2.f * PCPB_GUARD);
+    if (sub == 0) drow[gw] = D;
+    // NaN must not be lost: a maximum that ignores NaN would hide it
+    m_do = (n_do > m_do || n_do != n_do) ? n_do : m_do;
+    m_v = (n_v > m_v || n_v != n_v) ? n_v : m_v;
+    m_d = (fabsf(D) > m_d || D != D) ? fabsf(D) : m_d;
   }
-  // largest values of the warp's four rows, then one conditional atomic per statistic
-  D = fabsf(D);
+  auto nmax = [](float a, float b) { return (b > a || b != b) ? b : a; };
 #pragma unroll
-  for (int s = 8; s <= 16; s <<= 1) {
-    n_do = fmaxf(n_do, __shfl_xor_sync(0xffffffffu, n_do, s));
-    n_v = fmaxf(n_v, __shfl_xor_sync(0xffffffffu, n_v, s));
-    const float od = __shfl_xor_sync(0xffffffffu, D, s);
-    D = (od > D || od != od) ? od : D;
+  for (int s = 1; s <= 16; s <<= 1) {
+    m_do = nmax(m_do, __shfl_xor_sync(0xffffffffu, m_do, s));
+    m_v = nmax(m_v, __shfl_xor_sync(0xffffffffu, m_v, s));
+    m_d = nmax(m_d, __shfl_xor_sync(0xffffffffu, m_d, s));
   }
-  if ((threadIdx.x & 31) == 0) { attn_bound_note(0, n_do); attn_bound_note(1, D); attn_bound_note(2, n_v); }
+  const int warp = threadIdx.x >> 5;
+  if ((threadIdx.x & 31) == 0) { sred[0][warp] = m_do; sred[1][warp] = m_d; sred[2][warp] = m_v; }
+  __syncthreads();
+  if (threadIdx.x < 3) {
+    float v = sred[threadIdx.x][0];
+    for (int w = 1; w < 8; ++w) v = nmax(v, sred[threadIdx.x][w]);
+    attn_bound_note((int)threadIdx.x, v);
+  }
 }
 
 template <int MODE>
@@ -747,7 +757,7 @@ cudaError_t launch_mode(cudaStream_t st, const CUtensorMap& a, const CUtensorMap
 bool fill(const FlashArgs& a, int* err, AtcParams* p, CUtensorMap* mq, CUtensorMap* mv, CUtensorMap* md, bool need_do) {
   const int d = a.H * HD, dkv = a.Hkv * HD;
   const uint64_t M = (uint64_t)a.B * a.T;
-  p->B = a.B; p->T = a.T; p->H = a.H; p->Hkv = a.Hkv; p->scale = a.scale; p->d = d; p->dkv = dkv;
+  p->B = a.B; p->T = a.T; p->H = a.H; p->Hkv = a.Hkv; p->scale = a.scale; p->fwd_guard = a.no_guard ? 0.f : PCPB_GUARD; p->d = d; p->dkv = dkv;
   p->qkn = (const bf16*)a.qkn; p->dout = (const bf16*)a.dout;
   p->o = (bf16*)a.o; p->mrow = a.mrow; p->lrow = a.lrow; p->drow = a.drow; p->dqkn = (bf16*)a.dqkn; p->dqkv = (bf16*)a.dqkv;
   p->err = err; p->n_items = 1; p->bh_count = 1;
@@ -791,8 +801,13 @@ cudaError_t launch_attn_tc_bwd(cudaStream_t st, const FlashArgs& a, int* err_wor
   CUtensorMap mq, mv, md;
   if (!err_word || !fill(a, err_word, &p, &mq, &mv, &md, true)) return cudaErrorInvalidValue;
   const long long rows = (long long)a.B * a.H * a.T;
-  k_attn_tc_prep<<<(unsigned)((rows * 8 + 255) / 256), 256, 0, st>>>((const bf16*)a.o, (const bf16*)a.dout, a.lrow, a.drow, a.B,
-                                                                     a.T, a.H, (const bf16*)a.qkv, a.Hkv);
+  {
+    // a few rows per thread: the block-level statistics then cost three atomics per block
+    const long long blocks = (rows * 8 + 255) / 256;
+    const unsigned grid = (unsigned)(blocks < 148 * 16 ? blocks : 148 * 16);
+    k_attn_tc_prep<<<grid, 256, 0, st>>>((const bf16*)a.o, (const bf16*)a.dout, a.lrow, a.drow, a.B,
+                                         a.T, a.H, (const bf16*)a.qkv, a.Hkv);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   // persistent backward kernels: one CTA per SM walks the work items, long row tiles first

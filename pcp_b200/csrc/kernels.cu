@@ -244,16 +244,18 @@ __global__ void __launch_bounds__(256) k_rmsnorm_bwd_vec(const T* __restrict__ x
   // the largest |dy| and |x| of the row bound them all, so the guard / clamp code only runs for a row whose bound fails
   // (then it is exact); a row inside the bound is untouched by it, as in the reference.
   float acc = 0.f;
-  uint32_t mg = 0u, ma = 0u;
+  uint32_t mg = 0u;
   for (int v = lane; v < nv; v += 32) {
     float a[8], g[8];
     ld8<T>(xr + v * 8, a);
     ld8<T>(dyr + v * 8, g);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { acc += rnd<T>(g[i] * a[i]); adj_track(mg, g[i]); adj_track(ma, a[i]); }
+    for (int i = 0; i < 8; ++i) { acc += rnd<T>(g[i] * a[i]); adj_track(mg, g[i]); }
   }
-  mg = __reduce_max_sync(0xffffffffu, mg); ma = __reduce_max_sync(0xffffffffu, ma);
-  const float gmax = __uint_as_float(mg), amax = __uint_as_float(ma);
+  mg = __reduce_max_sync(0xffffffffu, mg);
+  const float t = tsave[m];
+  // |x_j| <= sqrt(sum x^2) = sqrt((t - 1e-5) (d + 1e-4)), from the statistic the forward saved (NaN if x had one)
+  const float gmax = __uint_as_float(mg), amax = sqrtf(fmaxf(t - 1e-5f, 0.f) * ((float)d + PCPB_GUARD));
   if (!(gmax * amax <= PCPB_ADJ_CLIP)) {                         // some product may be beyond the clamp (or not finite)
     acc = 0.f;
     for (int v = lane; v < nv; v += 32) {
@@ -265,7 +267,6 @@ __global__ void __launch_bounds__(256) k_rmsnorm_bwd_vec(const T* __restrict__ x
     }
   }
   acc = warp_sum(acc);
-  const float t = tsave[m];
   const float dr = adj_edge<T>(acc);
   const float rp = rsqrtf(t + PCPB_GUARD);
   const float ds = adj_edge<float>(adj_edge<float>((dr * -0.5f) * ((rp * rp) * rp)) / (((float)d + PCPB_GUARD) + PCPB_GUARD));
@@ -571,7 +572,7 @@ __global__ void __launch_bounds__(256) k_rope_qknorm_fwd_bf16x2(const bf16* __re
   *reinterpret_cast<uint4*>(dst + half) = make_uint4(bmul2(y2[0], r2), bmul2(y2[1], r2), bmul2(y2[2], r2), bmul2(y2[3], r2));
 }
 
-__global__ void __launch_bounds__(256) k_rope_qknorm_bwd_bf16x2(const bf16* __restrict__ qkv, const bf16* __restrict__ dqkn,
+__global__ void __launch_bounds__(256, 4) k_rope_qknorm_bwd_bf16x2(const bf16* __restrict__ qkv, const bf16* __restrict__ dqkn,
                                                                 const float* __restrict__ tq, const uint16_t* __restrict__ cosT,
                                                                 const uint16_t* __restrict__ sinT, int M, int Tlen, int H, int Hkv,
                                                                 int hd, bf16* __restrict__ dqkv) {
@@ -597,7 +598,7 @@ __global__ void __launch_bounds__(256) k_rope_qknorm_bwd_bf16x2(const bf16* __re
   // |d| and |y| of the head row bound all the element-wise ones; the guard / clamp code runs only for a head row whose
   // bound fails (and is exact there).
   float acc = 0.f;
-  uint32_t md = 0u, my = 0u;
+  uint32_t md = 0u;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     y1[i] = badd2(bmul2(x1[i], c[i]), bmul2(x2[i], sn[i]));
@@ -605,15 +606,14 @@ __global__ void __launch_bounds__(256) k_rope_qknorm_bwd_bf16x2(const bf16* __re
     const uint32_t p1 = bmul2(d1[i], y1[i]), p2 = bmul2(d2[i], y2[i]);
     acc += bf_lo(p1) + bf_lo(p2);
     acc += bf_hi(p1) + bf_hi(p2);
-    adj_track2(md, d1[i]); adj_track2(md, d2[i]); adj_track2(my, y1[i]); adj_track2(my, y2[i]);
+    adj_track2(md, d1[i]); adj_track2(md, d2[i]);
   }
-  // largest |d|, |y| over the head row (the tph lanes of this group); NaN is kept by the packed maximum
-  for (int o = tph >> 1; o > 0; o >>= 1) {
-    adj_track2(md, __shfl_xor_sync(0xffffffffu, md, o));
-    adj_track2(my, __shfl_xor_sync(0xffffffffu, my, o));
-  }
-  const float dmax = fmaxf(bf_lo(md), bf_hi(md)), ymax = fmaxf(bf_lo(my), bf_hi(my));
-  const bool nan_in = (bf_lo(md) != bf_lo(md)) || (bf_hi(md) != bf_hi(md)) || (bf_lo(my) != bf_lo(my)) || (bf_hi(my) != bf_hi(my));
+  // largest |d| over the head row (the tph lanes of this group; NaN is kept by the packed maximum); |y_i| is bounded by
+  // sqrt(sum y^2) = sqrt((t - 1e-5) (hd + 1e-4)) from the statistic the forward saved (NaN if y had one)
+  for (int o = tph >> 1; o > 0; o >>= 1) adj_track2(md, __shfl_xor_sync(0xffffffffu, md, o));
+  const float t = tq[(size_t)m * heads + h];
+  const float dmax = fmaxf(bf_lo(md), bf_hi(md)), ymax = sqrtf(fmaxf(t - 1e-5f, 0.f) * ((float)hd + PCPB_GUARD));
+  const bool nan_in = (bf_lo(md) != bf_lo(md)) || (bf_hi(md) != bf_hi(md)) || (t != t);
   if (nan_in || !(dmax * ymax <= PCPB_ADJ_CLIP)) {
     acc = 0.f;
 #pragma unroll
@@ -624,7 +624,6 @@ __global__ void __launch_bounds__(256) k_rope_qknorm_bwd_bf16x2(const bf16* __re
     }
   }
   acc = group_sum(acc, tph);
-  const float t = tq[(size_t)m * heads + h];
   const float dr = adj_edge<bf16>(acc);
   const float rp = rsqrtf(t + PCPB_GUARD);
   const float ds = adj_edge<float>(adj_edge<float>((dr * -0.5f) * ((rp * rp) * rp)) / (((float)hd + PCPB_GUARD) + PCPB_GUARD));
@@ -1090,7 +1089,6 @@ __global__ void __launch_bounds__(512) k_softcap_ce_vec(T* __restrict__ logits, 
   if (!write_grad) return;
   __syncthreads();                                  // the target logit was read above before anyone overwrites it
   const float dtot = valid ? adj_edge<float>(seed / (*count + 2.f * PCPB_GUARD)) : 0.f;     // the one edge that can grow
-  uint32_t mxa = 0u;
   const float iden = 1.f / (se + 2.f * PCPB_GUARD);
   const float dzscale = capped ? cap / (capg + PCPB_GUARD) : 1.f;
   for (int v = threadIdx.x; v < nv; v += blockDim.x) {
@@ -1104,13 +1102,14 @@ __global__ void __launch_bounds__(512) k_softcap_ce_vec(T* __restrict__ logits, 
       if ((long long)(v * 8 + i) == t) dc -= 1.f;
       if (c == mx) dc += (2.f * PCPB_GUARD) * iden;
       o[i] = dc * dtot * dzscale * (1.f - th * th);
-      adj_track(mxa, o[i]);
     }
     st8<T>(z + v * 8, o);
   }
-  // every value above is bounded by |dtot| <= 100 unless a logit was not finite; only then the row is passed through
-  // the guard / clamp of the output edge (non-finite -> 0)
-  if (__syncthreads_or(adj_over(mxa))) {
+  // every value above is bounded by |dtot| <= 100 unless a logit was not finite, and a logit that is not finite makes
+  // the row's sum of exponentials not finite; only then the row is passed through the guard / clamp of the output
+  // edge (non-finite -> 0)
+  if (!(fabsf(se) < INFINITY) || !(fabsf(mx) < INFINITY)) {
+    __syncthreads();
     for (int j = threadIdx.x; j < V; j += blockDim.x) z[j] = from_f<T>(adj_edge<T>(to_f(z[j])));
   }
 }
@@ -1332,6 +1331,39 @@ __global__ void __launch_bounds__(256) k_nesterov_shard(OuterArgs a) {
       if (w < a.nouts) a.outs[w][i] = th;
   }
 }
+// The same arithmetic on four elements per thread with 16-byte accesses (local and peer memory alike): used when every
+// pointer is 16-byte aligned, which the shard layout guarantees (shard offsets are multiples of 256 elements).
+__global__ void __launch_bounds__(256) k_nesterov_shard_v4(OuterArgs a, long long n4) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const float div = (float)a.ncontrib;
+  for (; i < n4; i += stride) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+      if (w < a.ncontrib) {
+        const float4 d = reinterpret_cast<const float4*>(a.deltas[w])[i];
+        acc[0] = __fadd_rn(acc[0], d.x); acc[1] = __fadd_rn(acc[1], d.y); acc[2] = __fadd_rn(acc[2], d.z); acc[3] = __fadd_rn(acc[3], d.w);
+      }
+    const float4 v4 = reinterpret_cast<const float4*>(a.vel)[i], m4 = reinterpret_cast<const float4*>(a.master)[i];
+    const float vel[4] = {v4.x, v4.y, v4.z, v4.w}, mas[4] = {m4.x, m4.y, m4.z, m4.w};
+    float vn[4], th[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float g = __fdiv_rn(acc[k], div);
+      if (!a.keep_nonfinite && !((g - g) == 0.f)) g = 0.f;
+      vn[k] = __fadd_rn(__fmul_rn(a.mu, vel[k]), g);
+      th[k] = __fsub_rn(mas[k], __fmul_rn(a.lr, __fadd_rn(g, __fmul_rn(a.mu, vn[k]))));
+      if (a.trunc) th[k] = trunc_bf16(th[k]);
+    }
+    reinterpret_cast<float4*>(a.vel)[i] = make_float4(vn[0], vn[1], vn[2], vn[3]);
+    const float4 out = make_float4(th[0], th[1], th[2], th[3]);
+    reinterpret_cast<float4*>(a.master)[i] = out;
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+      if (w < a.nouts) reinterpret_cast<float4*>(a.outs[w])[i] = out;
+  }
+}
 // Streaming DiLoCo worker side (src/nodes/workers/worker.zig:2433-2437 and :2583-2600), f32, no FMA contraction.
 __global__ void k_stream_delta(float* __restrict__ snap, const float* __restrict__ theta, float* __restrict__ d, size_t n) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -1364,6 +1396,22 @@ cudaError_t launch_stream_merge(cudaStream_t st, float* theta, const float* glob
 
 cudaError_t launch_nesterov_shard(cudaStream_t st, const OuterArgs& a) {
   if (a.n == 0) return cudaSuccess;
+  uintptr_t all = (uintptr_t)a.vel | (uintptr_t)a.master;
+  for (int w = 0; w < a.ncontrib; ++w) all |= (uintptr_t)a.deltas[w];
+  for (int w = 0; w < a.nouts; ++w) all |= (uintptr_t)a.outs[w];
+  const long long n4 = ((all & 15) == 0) ? a.n / 4 : 0;
+  if (n4 > 0) {
+    k_nesterov_shard_v4<<<min(cdiv((size_t)n4, 256), 148u * 8), 256, 0, st>>>(a, n4);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess || n4 * 4 == a.n) return e;
+    OuterArgs t = a;                                       // the last one to three elements
+    const long long done = n4 * 4;
+    for (int w = 0; w < t.ncontrib; ++w) t.deltas[w] += done;
+    for (int w = 0; w < t.nouts; ++w) t.outs[w] += done;
+    t.vel += done; t.master += done; t.n = a.n - done;
+    k_nesterov_shard<<<1, 32, 0, st>>>(t);
+    return cudaGetLastError();
+  }
   k_nesterov_shard<<<min(cdiv((size_t)a.n, 256), 148u * 8), 256, 0, st>>>(a);
   return cudaGetLastError();
 }

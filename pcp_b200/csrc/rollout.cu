@@ -33,10 +33,14 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <stdlib.h>
+
 #include <string>
 #include <vector>
 
 #include "../../include/pcp_b200.h"
+#include "attn_flash.h"
+#include "attn_tc.h"
 #include "common.cuh"
 #include "gemm_tc.h"
 #include "kernels.h"
@@ -49,6 +53,12 @@ constexpr int ROWS = 16;            // rows of the decode-step operand (sequence
 constexpr int PER_LAYER = 11;       // q k v o q_norm k_norm gate up down input_ln post_ln
 
 enum { GV_STORE = 0, GV_RESID = 1, GV_SWIGLU = 2 };
+// Warps per GEMV CTA (each takes K / GV_WARPS of the contraction).  Eight warps at <= 64 registers: four resident CTAs
+// per SM, 592 slots, so the 512-CTA launches of a layer (N = 4096) run as one wave (at 70 registers ncu showed 444
+// slots and a 15 %-full second wave).  Measured alternatives: 4-warp CTAs (8 per SM) were slower for the N = 4096 and
+// the SwiGLU launches (30 against 19 us, 67 against 52 us); a cluster of 8 CTAs splitting K with X staged in shared
+// memory and a distributed-shared-memory reduction was slower still.
+constexpr int GV_WARPS = 8;
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
@@ -62,42 +72,69 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {      // weights: rea
   return v;
 }
 __device__ __forceinline__ float silu_bf16(float g) { return bf16_round(g / (1.f + expf(-g))); }
+// Programmatic dependent launch: the kernels of a decode step are launched so that the next one may start while the
+// previous one drains.  A kernel first lets its own dependents go, does whatever does not depend on its predecessor
+// (the GEMV: the first pieces of its weight rows, which nothing in a decode step writes), and only then waits for the
+// predecessor's results.  Both instructions do nothing in a kernel launched the ordinary way (the prefill).
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-// C[16, N] (+ epilogue) = X[16, K] * W[N, K]^T.  grid = N / 8, block = 256 (8 warps, each a K / 8 slice).
-// K % 256 == 0 (a warp's slice is a multiple of 32), N % 8 == 0.  X rows beyond the batch are zero.
+// C[16, N] (+ epilogue) = X[16, K] * W[N, K]^T.  grid = N / 8, block = GV_WARPS warps, each K / GV_WARPS of the contraction.
+// K % 512 == 0 (a warp's share is a multiple of 64), N % 8 == 0.  X rows beyond the batch are zero.
+// A lane reads 32 consecutive bytes (16 k values) of its weight row per step, so the four lanes of a row cover a whole
+// 128-byte line; those 16 values serve four k16 MMA steps, and X is read with the same permutation of k.
+// Which k values a warp takes does not matter for the result's definition (the partial sums are added in warp order);
+// by default the warps interleave: in step i warp w reads the 64 k values (128 bytes per row) at (GV_WARPS i + w) * 64,
+// so that the CTA as a whole reads 512 contiguous bytes of each of its 8 weight rows at a time.
 template <int EPI>
-__global__ void __launch_bounds__(256) k_gemv16(const bf16* __restrict__ X, const bf16* __restrict__ W, const bf16* __restrict__ W2,
-                                                int N, int K, bf16* __restrict__ C, long long ldc, const bf16* __restrict__ R) {
-  __shared__ float red[8][ROWS * 8 * (EPI == GV_SWIGLU ? 2 : 1)];
+__global__ void __launch_bounds__(GV_WARPS * 32, 4) k_gemv16(const bf16* __restrict__ X, const bf16* __restrict__ W, const bf16* __restrict__ W2,
+                                                int N, int K, bf16* __restrict__ C, long long ldc, const bf16* __restrict__ R,
+                                                int kmap_slices) {
+  __shared__ float red[GV_WARPS][ROWS * 8 * (EPI == GV_SWIGLU ? 2 : 1)];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
   const int n0 = blockIdx.x * 8;
-  const int kslice = K >> 3, k0 = warp * kslice;
-  const bf16* wrow = W + (size_t)(n0 + g) * K + k0 + 8 * q;
-  const bf16* w2row = (EPI == GV_SWIGLU) ? W2 + (size_t)(n0 + g) * K + k0 + 8 * q : nullptr;
-  const bf16* xlo = X + (size_t)g * K + k0 + 8 * q;
-  const bf16* xhi = X + (size_t)(g + 8) * K + k0 + 8 * q;
+  const int kslice = K / GV_WARPS;
+  // element offset of this warp's step at position kb of its slice: contiguous slice, or interleaved 64-element pieces
+  const int k0 = kmap_slices ? warp * kslice : warp * 64;
+  const int kmul = kmap_slices ? 1 : GV_WARPS;
+  const bf16* wrow = W + (size_t)(n0 + g) * K + k0 + 16 * q;
+  const bf16* w2row = (EPI == GV_SWIGLU) ? W2 + (size_t)(n0 + g) * K + k0 + 16 * q : nullptr;
+  const bf16* xlo = X + (size_t)g * K + k0 + 16 * q;
+  const bf16* xhi = X + (size_t)(g + 8) * K + k0 + 16 * q;
   float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
-  constexpr int U = (EPI == GV_SWIGLU) ? 4 : 8;                 // 16-byte weight loads in flight per lane
-  for (int kb = 0; kb < kslice; kb += 32 * U) {
-    uint4 wv[U], w2v[U];
+  constexpr int U = (EPI == GV_SWIGLU) ? 2 : 4;                 // 32-byte weight pieces in flight per lane and panel
+  uint4 wv[U][2], w2v[U][2];
+  auto load_w = [&](int kb) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const bool in = kb + 32 * u < kslice;
-      wv[u] = in ? ld_stream(wrow + kb + 32 * u) : make_uint4(0, 0, 0, 0);
-      if (EPI == GV_SWIGLU) w2v[u] = in ? ld_stream(w2row + kb + 32 * u) : make_uint4(0, 0, 0, 0);
+      const bool in = kb + 64 * u < kslice;
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        wv[u][hlf] = in ? ld_stream(wrow + (kb + 64 * u) * kmul + 8 * hlf) : make_uint4(0, 0, 0, 0);
+        if (EPI == GV_SWIGLU) w2v[u][hlf] = in ? ld_stream(w2row + (kb + 64 * u) * kmul + 8 * hlf) : make_uint4(0, 0, 0, 0);
+      }
     }
+  };
+  pdl_launch_dependents();
+  load_w(0);                                                    // weights do not depend on the previous kernel
+  pdl_wait();                                                   // X (and R) do
+  for (int kb = 0; kb < kslice; kb += 64 * U) {
+    if (kb > 0) load_w(kb);
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      if (kb + 32 * u >= kslice) break;
-      // the lane's 8 consecutive k values serve two k16 steps: elements {0,1,2,3} and {4,5,6,7}; the operand X is
-      // read with the same permutation of k, so the products line up
-      const uint4 a = *reinterpret_cast<const uint4*>(xlo + kb + 32 * u);
-      const uint4 b = *reinterpret_cast<const uint4*>(xhi + kb + 32 * u);
-      mma16816(acc, a.x, b.x, a.y, b.y, wv[u].x, wv[u].y);
-      mma16816(acc, a.z, b.z, a.w, b.w, wv[u].z, wv[u].w);
-      if (EPI == GV_SWIGLU) {
-        mma16816(acc2, a.x, b.x, a.y, b.y, w2v[u].x, w2v[u].y);
-        mma16816(acc2, a.z, b.z, a.w, b.w, w2v[u].z, w2v[u].w);
+      if (kb + 64 * u >= kslice) break;
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        // 8 consecutive k values serve two k16 steps: elements {0,1,2,3} and {4,5,6,7}; the operand X is read with
+        // the same permutation of k, so the products line up
+        const uint4 a = *reinterpret_cast<const uint4*>(xlo + (kb + 64 * u) * kmul + 8 * hlf);
+        const uint4 b = *reinterpret_cast<const uint4*>(xhi + (kb + 64 * u) * kmul + 8 * hlf);
+        mma16816(acc, a.x, b.x, a.y, b.y, wv[u][hlf].x, wv[u][hlf].y);
+        mma16816(acc, a.z, b.z, a.w, b.w, wv[u][hlf].z, wv[u][hlf].w);
+        if (EPI == GV_SWIGLU) {
+          mma16816(acc2, a.x, b.x, a.y, b.y, w2v[u][hlf].x, w2v[u][hlf].y);
+          mma16816(acc2, a.z, b.z, a.w, b.w, w2v[u][hlf].z, w2v[u][hlf].w);
+        }
       }
     }
   }
@@ -115,7 +152,7 @@ __global__ void __launch_bounds__(256) k_gemv16(const bf16* __restrict__ X, cons
     const int r = threadIdx.x >> 3, c = threadIdx.x & 7;
     float s = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) {                               // warp order: the sum does not depend on timing
+    for (int w = 0; w < GV_WARPS; ++w) {                        // warp order: the sum does not depend on timing
       s += red[w][threadIdx.x];
       if (EPI == GV_SWIGLU) s2 += red[w][ROWS * 8 + threadIdx.x];
     }
@@ -130,6 +167,8 @@ __global__ void __launch_bounds__(256) k_gemv16(const bf16* __restrict__ X, cons
 // rows of the embedding table -> h [M, d]; tokens outside the table are clamped like a gather's start indices
 __global__ void k_embed_rows(const bf16* __restrict__ emb, const long long* __restrict__ tok, int M, int d, int V,
                              bf16* __restrict__ h) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int m = blockIdx.x;
   if (m >= M) return;
   long long t = tok[m];
@@ -139,27 +178,55 @@ __global__ void k_embed_rows(const bf16* __restrict__ emb, const long long* __re
   for (int i = threadIdx.x; i < d / 8; i += blockDim.x) dst[i] = src[i];
 }
 
-// Qwen3RMSNorm: y = w * bf16(x * rsqrt(mean(x^2) + eps)), statistics in f32.  One block per row.  `gather` (optional)
-// selects the source row of output row m.
+// Qwen3RMSNorm: y = w * bf16(x * rsqrt(mean(x^2) + eps)), statistics in f32.  One block per row; a thread keeps its
+// 16-byte pieces of the row in registers between the statistics and the output (one read of the row).  `gather`
+// (optional) selects the source row of output row m.  d % 8 == 0, d <= 8 * 4 * blockDim.
 __global__ void __launch_bounds__(256) k_rmsnorm_w(const bf16* __restrict__ x, const bf16* __restrict__ w, const int* __restrict__ gather,
                                                    int M, int d, float eps, bf16* __restrict__ y) {
   __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int m = blockIdx.x;
   const bf16* xr = x + (size_t)(gather ? gather[m] : m) * d;
+  const int nv = d >> 3;
+  constexpr int MAXV = 4;
+  float f[MAXV][8];
   float ss = 0.f;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) { const float v = to_f(xr[i]); ss += v * v; }
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k) {
+    const int v = threadIdx.x + k * blockDim.x;
+    if (v < nv) {
+      ld8<bf16>(xr + v * 8, f[k]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += f[k][i] * f[k][i];
+    }
+  }
   ss = block_sum(ss, red);
   const float r = rsqrtf(ss / (float)d + eps);
-  for (int i = threadIdx.x; i < d; i += blockDim.x)
-    y[(size_t)m * d + i] = from_f<bf16>(to_f(w[i]) * bf16_round(to_f(xr[i]) * r));
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k) {
+    const int v = threadIdx.x + k * blockDim.x;
+    if (v < nv) {
+      float wf[8], o[8];
+      ld8<bf16>(w + v * 8, wf);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = wf[i] * bf16_round(f[k][i] * r);
+      st8<bf16>(y + (size_t)m * d + v * 8, o);
+    }
+  }
 }
 
-// act = bf16(silu(gate)) * up on [M, 2f] -> [M, f] (prefill; the decode step has this in the GEMV epilogue)
+// act = bf16(silu(gate)) * up on [M, 2f] -> [M, f] (prefill; the decode step has this in the GEMV epilogue); f % 8 == 0
 __global__ void k_swiglu(const bf16* __restrict__ gu, int M, int f, bf16* __restrict__ act) {
-  const size_t n = (size_t)M * f;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    const size_t m = i / f, c = i % f;
-    act[i] = from_f<bf16>(silu_bf16(to_f(gu[m * 2 * f + c])) * to_f(gu[m * 2 * f + f + c]));
+  const size_t nv = (size_t)M * (f >> 3), fv = (size_t)(f >> 3);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t m = i / fv, c = (i % fv) * 8;
+    float g[8], u[8], o[8];
+    ld8<bf16>(gu + m * 2 * f + c, g);
+    ld8<bf16>(gu + m * 2 * f + f + c, u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = silu_bf16(g[k]) * u[k];
+    st8<bf16>(act + m * (size_t)f + c, o);
   }
 }
 
@@ -174,7 +241,9 @@ __global__ void __launch_bounds__(256) k_qknorm_rope_cache(const bf16* __restric
                                                            const bf16* __restrict__ cosT, const bf16* __restrict__ sinT, RowMap map, int M, int H,
                                                            int Hkv, int hd, float eps, const int* __restrict__ block_table,
                                                            int max_pages, int page, bf16* __restrict__ kpages, bf16* __restrict__ vpages,
-                                                           bf16* __restrict__ qbuf) {
+                                                           bf16* __restrict__ qbuf, bf16* __restrict__ sqk, bf16* __restrict__ sqv, int Tseq) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int heads = H + 2 * Hkv;
   const long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -187,9 +256,17 @@ __global__ void __launch_bounds__(256) k_qknorm_rope_cache(const bf16* __restric
   float v[4];
   for (int i = 0; i < per; ++i) v[i] = to_f(src[i]);
   const int pg = block_table[sq * max_pages + pos / page], off = pos % page;
+  // sqk / sqv (prefill on the tensor-core attention kernel): q of row m in row m, k and v of row m in row m + 1 of the
+  // same sequence -- with a zero row at position 0 the ordinary causal kernel then sees, for the query at position p,
+  // the zero slot and the keys below p, which is what the exported step attends to
+  const bool stage_next = sqk && pos + 1 < Tseq;
   if (h >= H + Hkv) {                                           // value head: stored as projected
     bf16* dst = vpages + (((size_t)pg * Hkv + (h - H - Hkv)) * page + off) * hd + lane * per;
     for (int i = 0; i < per; ++i) dst[i] = from_f<bf16>(v[i]);
+    if (stage_next) {
+      bf16* d2 = sqv + (size_t)(m + 1) * (H + 2 * Hkv) * hd + (size_t)h * hd + lane * per;
+      for (int i = 0; i < per; ++i) d2[i] = from_f<bf16>(v[i]);
+    }
     return;
   }
   const bf16* wn = (h < H) ? qn : kn;
@@ -211,28 +288,37 @@ __global__ void __launch_bounds__(256) k_qknorm_rope_cache(const bf16* __restric
   }
   if (h < H) {
     const float sc = sqrtf((float)hd);
-    bf16* dst = qbuf + (size_t)m * H * hd + (size_t)h * hd + lane * per;
+    bf16* dst = sqk ? sqk + (size_t)m * (H + Hkv) * hd + (size_t)h * hd + lane * per
+                    : qbuf + (size_t)m * H * hd + (size_t)h * hd + lane * per;
     for (int i = 0; i < per; ++i) dst[i] = from_f<bf16>(o[i] / sc);
   } else {
     bf16* dst = kpages + (((size_t)pg * Hkv + (h - H)) * page + off) * hd + lane * per;
     for (int i = 0; i < per; ++i) dst[i] = from_f<bf16>(o[i]);
+    if (stage_next) {
+      bf16* d2 = sqk + (size_t)(m + 1) * (H + Hkv) * hd + (size_t)h * hd + lane * per;
+      for (int i = 0; i < per; ++i) d2[i] = from_f<bf16>(o[i]);
+    }
   }
 }
 
 // Attention of one token row against the cache below its position, for the G query heads of one kv head.
-// grid = (M, Hkv), block = 256.  Dynamic shared memory: q [G][hd] f32, p [G][npos_max] f32, partial out [8][G][hd] f32.
-template <int HD, int G>
-__global__ void __launch_bounds__(256) k_attn_rows(const bf16* __restrict__ qbuf, RowMap map, int H, int Hkv, const int* __restrict__ block_table,
+// grid = (M, Hkv), block = ATT_THREADS.  Dynamic shared memory: q [G][hd] f32, p [G][npos_max] f32, partial out [warps][G][hd] f32.
+// ATT_THREADS: 1024 for the decode step (few CTAs, hundreds of keys each: the keys of both passes are spread over 32
+// warps), 256 for prefill rows (thousands of CTAs with few keys each).
+template <int HD, int G, int ATT_THREADS>
+__global__ void __launch_bounds__(ATT_THREADS) k_attn_rows(const bf16* __restrict__ qbuf, RowMap map, int H, int Hkv, const int* __restrict__ block_table,
                                                    int max_pages, int page, const bf16* __restrict__ kpages, const bf16* __restrict__ vpages,
                                                    int npos_max, bf16* __restrict__ out) {
   extern __shared__ float sm[];
-  __shared__ float red[32];
+  constexpr int ATT_WARPS = ATT_THREADS / 32;
+  pdl_launch_dependents();
+  pdl_wait();
   const int m = blockIdx.x, kvh = blockIdx.y;
   const int sq = map.seq[m], pos = map.pos[m];
   if (sq < 0) return;
   float* qs = sm;                          // [G][HD]
   float* ps = qs + G * HD;                 // [G][npos_max]
-  float* po = ps + (size_t)G * npos_max;   // [8][G][HD]
+  float* po = ps + (size_t)G * npos_max;   // [ATT_WARPS][G][HD]
   for (int i = threadIdx.x; i < G * HD; i += blockDim.x)
     qs[i] = to_f(qbuf[(size_t)m * H * HD + (size_t)(kvh * G) * HD + i]);
   __syncthreads();
@@ -259,19 +345,50 @@ __global__ void __launch_bounds__(256) k_attn_rows(const bf16* __restrict__ qbuf
   }
   __syncthreads();
   // softmax in f32 over the keys below pos and the zero slot at pos (score 0, value 0); later slots carry -1e4 on a
-  // zero score and underflow to weight 0
-  for (int g = 0; g < G; ++g) {
-    float* pg = ps + (size_t)g * npos_max;
-    float mx = 0.f;                                              // the zero slot
-    for (int j = threadIdx.x; j < pos; j += blockDim.x) mx = fmaxf(mx, pg[j]);
-    mx = block_max(mx, red);
-    float se = 0.f;
-    for (int j = threadIdx.x; j < pos; j += blockDim.x) { const float e = expf(pg[j] - mx); pg[j] = e; se += e; }
-    se = block_sum(se, red) + expf(0.f - mx);
-    for (int j = threadIdx.x; j < pos; j += blockDim.x) pg[j] = bf16_round(pg[j] / se);
+  // zero score and underflow to weight 0.  All G heads are reduced together: two block-wide exchanges in all.
+  {
+    const int warp_ = threadIdx.x >> 5, lane_ = threadIdx.x & 31;
+    float mx[G], se[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      mx[g] = 0.f;                                               // the zero slot
+      const float* pg = ps + (size_t)g * npos_max;
+      for (int j = threadIdx.x; j < pos; j += blockDim.x) mx[g] = fmaxf(mx[g], pg[j]);
+      mx[g] = warp_max(mx[g]);
+      if (lane_ == 0) po[warp_ * G + g] = mx[g];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float m = 0.f;
+      for (int w = 0; w < ATT_WARPS; ++w) m = fmaxf(m, po[w * G + g]);
+      mx[g] = m;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float* pg = ps + (size_t)g * npos_max;
+      float sum = 0.f;
+      for (int j = threadIdx.x; j < pos; j += blockDim.x) { const float e = expf(pg[j] - mx[g]); pg[j] = e; sum += e; }
+      sum = warp_sum(sum);
+      if (lane_ == 0) po[warp_ * G + g] = sum;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float sum = 0.f;
+      for (int w = 0; w < ATT_WARPS; ++w) sum += po[w * G + g];     // warp order: the same sum in every thread
+      se[g] = sum + expf(0.f - mx[g]);
+    }
+    // a thread normalises the entries it wrote itself: no barrier needed in between
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float* pg = ps + (size_t)g * npos_max;
+      for (int j = threadIdx.x; j < pos; j += blockDim.x) pg[j] = bf16_round(pg[j] / se[g]);
+    }
   }
   __syncthreads();
-  // pass 2: P V.  The keys are split over the 8 warps; a lane owns HD / 32 consecutive output elements of every head.
+  // pass 2: P V.  The keys are split over the warps; a lane owns HD / 32 consecutive output elements of every head.
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int PER = HD / 32;
   float acc[G][PER];
@@ -279,12 +396,17 @@ __global__ void __launch_bounds__(256) k_attn_rows(const bf16* __restrict__ qbuf
   for (int g = 0; g < G; ++g)
 #pragma unroll
     for (int e = 0; e < PER; ++e) acc[g][e] = 0.f;
-#pragma unroll 4
-  for (int j = warp; j < pos; j += 8) {
+#pragma unroll 8
+  for (int j = warp; j < pos; j += ATT_WARPS) {
     const bf16* vr = vpages + (((size_t)bt[j / page] * Hkv + kvh) * page + (j % page)) * HD + lane * PER;
     float vf[PER];
-#pragma unroll
-    for (int e = 0; e < PER; ++e) vf[e] = to_f(vr[e]);
+    if (PER == 4) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(vr);          // one 8-byte load per lane: a 256-byte row per warp
+      vf[0] = bf_lo(raw.x); vf[1] = bf_hi(raw.x); vf[2 % PER] = bf_lo(raw.y); vf[3 % PER] = bf_hi(raw.y);
+    } else {
+      const uint32_t raw = *reinterpret_cast<const uint32_t*>(vr);
+      vf[0] = bf_lo(raw); vf[1] = bf_hi(raw);
+    }
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       const float p = ps[(size_t)g * npos_max + j];
@@ -299,53 +421,76 @@ __global__ void __launch_bounds__(256) k_attn_rows(const bf16* __restrict__ qbuf
   __syncthreads();
   for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
     float s = 0.f;
-    for (int w = 0; w < 8; ++w) s += po[(size_t)w * G * HD + i];
+    for (int w = 0; w < ATT_WARPS; ++w) s += po[(size_t)w * G * HD + i];
     out[(size_t)m * H * HD + (size_t)(kvh * G) * HD + i] = from_f<bf16>(s);
   }
 }
 
-// Sampler.argmax (src/core/math.zig:61-73): the first maximum wins, NaN never wins.  One block per row of logits; the
-// winner becomes the row's next input token, is recorded at out[row][step] and the row's position advances.
-__global__ void __launch_bounds__(1024) k_argmax_advance(const bf16* __restrict__ logits, int V, long long ldl, long long* __restrict__ cur_tok,
-                                                         int* __restrict__ cur_pos, long long* __restrict__ out, int max_new,
-                                                         const int* __restrict__ step, int advance) {
-  __shared__ float bv[32];
-  __shared__ int bi[32];
-  const int row = blockIdx.x;
+// Sampler.argmax (src/core/math.zig:61-73): the first maximum wins, NaN never wins.  Two stages: ARG_CHUNKS blocks per
+// row each find the first maximum of a slice of the row (16-byte loads), then one warp per row picks the first maximum
+// among the slices; the winner becomes the row's next input token, is recorded at out[row][step] and the row's position
+// advances.
+constexpr int ARG_CHUNKS = 32;
+__device__ __forceinline__ bool arg_better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+__global__ void __launch_bounds__(256) k_argmax_part(const bf16* __restrict__ logits, int V, long long ldl, float* __restrict__ pval,
+                                                     int* __restrict__ pidx) {
+  __shared__ float bv[8];
+  __shared__ int bi[8];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.y, chunk = blockIdx.x;
   const bf16* z = logits + (size_t)row * ldl;
+  const int nv = V >> 3, per = (nv + ARG_CHUNKS - 1) / ARG_CHUNKS;
+  const int v0 = chunk * per, v1 = min(nv, v0 + per);
   float best = -INFINITY;
   int at = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = to_f(z[i]);
-    if (v > best) { best = v; at = i; }                         // strided scan keeps the lowest index per thread
+  for (int v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+    float f[8];
+    ld8<bf16>(z + v * 8, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (f[i] > best) { best = f[i]; at = v * 8 + i; }          // ascending scan: the lowest index of the maximum
   }
-  auto better = [](float v, int i, float bvv, int bii) { return v > bvv || (v == bvv && i < bii); };
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);
     const int oi = __shfl_xor_sync(0xffffffffu, at, o);
-    if (better(ov, oi, best, at)) { best = ov; at = oi; }
+    if (arg_better(ov, oi, best, at)) { best = ov; at = oi; }
   }
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   if (lane == 0) { bv[w] = best; bi[w] = at; }
   __syncthreads();
-  if (w == 0) {
-    best = lane < (int)(blockDim.x >> 5) ? bv[lane] : -INFINITY;
-    at = lane < (int)(blockDim.x >> 5) ? bi[lane] : 0x7fffffff;
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, at, o);
-      if (better(ov, oi, best, at)) { best = ov; at = oi; }
-    }
-    if (lane == 0) {
-      const long long tok = (at == 0x7fffffff) ? 0 : at;       // all -inf / NaN: index 0, as the reference's scan
-      const int s = *step;
-      if (s < max_new) out[(size_t)row * max_new + s] = tok;
-      cur_tok[row] = tok;
-      if (advance) cur_pos[row] += 1;
-    }
+  if (threadIdx.x == 0) {
+    for (int k = 1; k < 8; ++k)
+      if (arg_better(bv[k], bi[k], best, at)) { best = bv[k]; at = bi[k]; }
+    pval[row * ARG_CHUNKS + chunk] = best; pidx[row * ARG_CHUNKS + chunk] = at;
   }
 }
-__global__ void k_bump(int* step) { *step += 1; }
+__global__ void __launch_bounds__(32) k_argmax_advance(const float* __restrict__ pval, const int* __restrict__ pidx, long long* __restrict__ cur_tok,
+                                                       int* __restrict__ cur_pos, long long* __restrict__ out, int max_new,
+                                                       const int* __restrict__ step, int advance) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x, lane = threadIdx.x;
+  float best = lane < ARG_CHUNKS ? pval[row * ARG_CHUNKS + lane] : -INFINITY;
+  int at = lane < ARG_CHUNKS ? pidx[row * ARG_CHUNKS + lane] : 0x7fffffff;
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, at, o);
+    if (arg_better(ov, oi, best, at)) { best = ov; at = oi; }
+  }
+  if (lane == 0) {
+    const long long tok = (at == 0x7fffffff) ? 0 : at;         // all -inf / NaN: index 0, as the reference's scan
+    const int s = *step;
+    if (s < max_new) out[(size_t)row * max_new + s] = tok;
+    cur_tok[row] = tok;
+    if (advance) cur_pos[row] += 1;
+  }
+}
+__global__ void k_bump(int* step) {
+  pdl_launch_dependents();
+  pdl_wait();
+  *step += 1;
+}
 
 // N(0, std) bf16 weights from a counter-based generator: for benchmark set-up only (the reference loads a weight
 // blob; generating 8 x 10^9 values on the host would take minutes).
@@ -384,13 +529,20 @@ struct pcpb_rollout {
   bf16 *h = nullptr, *h2 = nullptr, *x = nullptr, *qkv = nullptr, *q = nullptr, *att = nullptr, *gu = nullptr, *act = nullptr;
   bf16 *dh = nullptr, *dh2 = nullptr, *dx = nullptr, *dqkv = nullptr, *dq = nullptr, *datt = nullptr, *dact = nullptr, *logits = nullptr;
   bf16 *kpages = nullptr, *vpages = nullptr, *cosT = nullptr, *sinT = nullptr;
+  bf16 *sqk = nullptr, *sqv = nullptr;   // prefill staging for the tensor-core attention: [rows, hq + hk] (q | shifted k), [rows, hq + 2 hk] (v part: shifted v)
+  float *att_m = nullptr, *att_l = nullptr;
   int *block_table = nullptr, *row_seq = nullptr, *row_pos = nullptr, *last_row = nullptr, *drow_seq = nullptr, *cur_pos = nullptr,
       *step = nullptr, *tc_err = nullptr;
   long long *row_tok = nullptr, *cur_tok = nullptr, *out_tok = nullptr;
+  float* arg_val = nullptr;          // [16][ARG_CHUNKS] first maxima of the logit slices
+  int* arg_idx = nullptr;
   int out_cap = 0;
   cudaGraphExec_t graph = nullptr;
   int graph_batch = 0, graph_maxnew = 0;
   long long graph_launches = 0;      // kernels in one replay of the decode-step graph
+  int kmap_slices = 0;               // 0: the warps of a CTA interleave 128-byte pieces of the rows (default)
+  bool no_tc_prefill = false;             // PCPB_ROLLOUT_PREFILL=rows: the row kernel also for aligned prompts
+  bool use_pdl = true, pdl_now = false;   // programmatic dependent launch inside the decode step (PCPB_ROLLOUT_PDL=0: off)
   cudaEvent_t e0 = nullptr, e1 = nullptr, e2 = nullptr;
   long long launches = 0;
 };
@@ -433,6 +585,20 @@ struct Guard {
   ~Guard() { if (prev >= 0) cudaSetDevice(prev); }
 };
 
+// Kernel launch on the engine's stream.  While a decode step is being enqueued (r->pdl_now) the launch carries the
+// programmatic-serialisation attribute, so that the kernel may start while its predecessor drains; the kernels wait
+// for their predecessor themselves (pdl_wait) before they touch anything it produces.
+template <typename... KA, typename... A>
+cudaError_t klaunch(pcpb_rollout* r, void (*kern)(KA...), dim3 grid, dim3 block, size_t smem, A... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = r->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = r->pdl_now ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KA>(args)...);
+}
+
 std::vector<std::vector<long long>> param_shapes(const pcpb_rollout_cfg& c) {
   const long long d = c.d_model, hq = (long long)c.n_head * c.head_dim, hk = (long long)c.n_kv_head * c.head_dim, f = c.d_ff;
   std::vector<std::vector<long long>> s;
@@ -461,24 +627,32 @@ int big_gemm(pcpb_rollout* r, const bf16* A, const bf16* Wt, bf16* C, int M, int
 
 int gemv(pcpb_rollout* r, int epi, const bf16* X, const bf16* Wt, const bf16* W2, int N, int K, bf16* C, long long ldc, const bf16* R) {
   r->launches += 1;
-  if (epi == GV_STORE) k_gemv16<GV_STORE><<<N / 8, 256, 0, r->stream>>>(X, Wt, nullptr, N, K, C, ldc, nullptr);
-  else if (epi == GV_RESID) k_gemv16<GV_RESID><<<N / 8, 256, 0, r->stream>>>(X, Wt, nullptr, N, K, C, ldc, R);
-  else k_gemv16<GV_SWIGLU><<<N / 8, 256, 0, r->stream>>>(X, Wt, W2, N, K, C, ldc, nullptr);
-  RCK(r, cudaGetLastError());
+  const bf16* none = nullptr;
+  if (epi == GV_STORE) RCK(r, klaunch(r, k_gemv16<GV_STORE>, dim3(N / 8), dim3(GV_WARPS * 32), 0, X, Wt, none, N, K, C, ldc, none, r->kmap_slices));
+  else if (epi == GV_RESID) RCK(r, klaunch(r, k_gemv16<GV_RESID>, dim3(N / 8), dim3(GV_WARPS * 32), 0, X, Wt, none, N, K, C, ldc, R, r->kmap_slices));
+  else RCK(r, klaunch(r, k_gemv16<GV_SWIGLU>, dim3(N / 8), dim3(GV_WARPS * 32), 0, X, Wt, W2, N, K, C, ldc, none, r->kmap_slices));
   return PCPB_OK;
 }
 
-size_t attn_smem(const pcpb_rollout_cfg& c) {
+size_t attn_smem(const pcpb_rollout_cfg& c, int threads = 1024) {
   const int G = c.n_head / c.n_kv_head;
-  return ((size_t)G * c.head_dim + (size_t)G * c.max_seq + (size_t)8 * G * c.head_dim) * sizeof(float);
+  return ((size_t)G * c.head_dim + (size_t)G * c.max_seq + (size_t)(threads / 32) * G * c.head_dim) * sizeof(float);
 }
 
 template <int HD, int G>
 void attn_launch(pcpb_rollout* r, const bf16* q, RowMap map, int M, const bf16* kp, const bf16* vp, bf16* out, bool set_attr) {
   const pcpb_rollout_cfg& c = r->cfg;
-  if (set_attr) { cudaFuncSetAttribute(k_attn_rows<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem(c)); return; }
-  k_attn_rows<HD, G><<<dim3(M, c.n_kv_head), 256, attn_smem(c), r->stream>>>(q, map, c.n_head, c.n_kv_head, r->block_table, r->max_pages,
-                                                                            c.page_tokens, kp, vp, c.max_seq, out);
+  if (set_attr) {
+    cudaFuncSetAttribute(k_attn_rows<HD, G, 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem(c, 1024));
+    cudaFuncSetAttribute(k_attn_rows<HD, G, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem(c, 256));
+    return;
+  }
+  if (M <= ROWS)
+    klaunch(r, k_attn_rows<HD, G, 1024>, dim3(M, c.n_kv_head), dim3(1024), attn_smem(c, 1024), q, map, c.n_head, c.n_kv_head,
+            (const int*)r->block_table, r->max_pages, c.page_tokens, kp, vp, c.max_seq, out);
+  else
+    klaunch(r, k_attn_rows<HD, G, 256>, dim3(M, c.n_kv_head), dim3(256), attn_smem(c, 256), q, map, c.n_head, c.n_kv_head,
+            (const int*)r->block_table, r->max_pages, c.page_tokens, kp, vp, c.max_seq, out);
 }
 template <int HD>
 void attn_dispatch(pcpb_rollout* r, const bf16* q, RowMap map, int M, const bf16* kp, const bf16* vp, bf16* out, bool set_attr) {
@@ -501,8 +675,19 @@ int attention(pcpb_rollout* r, const bf16* q, const int* rs, const int* rp, int 
 }
 
 // One pass over the layers for M token rows.  decode: the 16-row buffers and the GEMV kernels; else prefill.
-int layers(pcpb_rollout* r, bool decode, int M, const int* rs, const int* rp) {
+// tc_T > 0 (prefill only): every sequence has tc_T prompt rows, a multiple of 128, and head_dim is 128: the attention runs
+// on the tcgen05 kernel over staged q / shifted k, v buffers instead of the row kernel.
+int layers(pcpb_rollout* r, bool decode, int M, const int* rs, const int* rp, int tc_T = 0) {
   const pcpb_rollout_cfg& c = r->cfg;
+  const bool tc_attn = !decode && tc_T > 0;
+  if (tc_attn) {
+    // position 0 of every sequence: the zero slot (k and v parts of the first row of each sequence)
+    const size_t wk = (size_t)(c.n_head + c.n_kv_head) * c.head_dim, wv = (size_t)(c.n_head + 2 * c.n_kv_head) * c.head_dim;
+    RCK(r, cudaMemset2DAsync(r->sqk + (size_t)c.n_head * c.head_dim, (size_t)tc_T * wk * 2, 0, (size_t)c.n_kv_head * c.head_dim * 2,
+                             (size_t)(M / tc_T), r->stream));
+    RCK(r, cudaMemset2DAsync(r->sqv + (size_t)(c.n_head + c.n_kv_head) * c.head_dim, (size_t)tc_T * wv * 2, 0,
+                             (size_t)c.n_kv_head * c.head_dim * 2, (size_t)(M / tc_T), r->stream));
+  }
   const int d = c.d_model, f = c.d_ff, hq = r->hq, hk = r->hk, nqkv = hq + 2 * hk;
   cudaStream_t st = r->stream;
   bf16 *h = decode ? r->dh : r->h, *h2 = decode ? r->dh2 : r->h2, *x = decode ? r->dx : r->x, *qkv = decode ? r->dqkv : r->qkv;
@@ -513,22 +698,29 @@ int layers(pcpb_rollout* r, bool decode, int M, const int* rs, const int* rp) {
     const int p0 = 1 + PER_LAYER * l;
     int rc;
     r->launches += 1;
-    k_rmsnorm_w<<<M, 256, 0, st>>>(h, W(r, p0 + 9), nullptr, M, d, c.rms_eps, x);
+    RCK(r, klaunch(r, k_rmsnorm_w, dim3(M), dim3(256), 0, (const bf16*)h, W(r, p0 + 9), (const int*)nullptr, M, d, c.rms_eps, x));
     if (decode) { if ((rc = gemv(r, GV_STORE, x, W(r, p0), nullptr, nqkv, d, qkv, nqkv, nullptr))) return rc; }
     else if ((rc = big_gemm(r, x, W(r, p0), qkv, Mp, nqkv, d, EPI_STORE, nullptr))) return rc;
     const long long warps = (long long)M * (c.n_head + 2 * c.n_kv_head);
     const size_t layer_pages = (size_t)l * r->n_pages * c.n_kv_head * c.page_tokens * c.head_dim;
     bf16 *kp = r->kpages + layer_pages, *vp = r->vpages + layer_pages;
     r->launches += 1;
-    k_qknorm_rope_cache<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(
-        qkv, W(r, p0 + 4), W(r, p0 + 5), r->cosT, r->sinT, map, M, c.n_head, c.n_kv_head, c.head_dim, c.rms_eps, r->block_table,
-        r->max_pages, c.page_tokens, kp, vp, q);
+    RCK(r, klaunch(r, k_qknorm_rope_cache, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256), 0, (const bf16*)qkv, W(r, p0 + 4),
+                   W(r, p0 + 5), (const bf16*)r->cosT, (const bf16*)r->sinT, map, M, c.n_head, c.n_kv_head, c.head_dim, c.rms_eps,
+                   (const int*)r->block_table, r->max_pages, c.page_tokens, kp, vp, q, tc_attn ? r->sqk : (bf16*)nullptr,
+                   tc_attn ? r->sqv : (bf16*)nullptr, tc_T));
     // the row's own key / value are in the cache now, but its attention reads only the slots below its position
-    if ((rc = attention(r, q, rs, rp, M, kp, vp, att))) return rc;
+    if (tc_attn) {
+      FlashArgs fa{};
+      fa.qkn = r->sqk; fa.qkv = r->sqv; fa.o = att; fa.mrow = r->att_m; fa.lrow = r->att_l;
+      fa.B = M / tc_T; fa.T = tc_T; fa.H = c.n_head; fa.Hkv = c.n_kv_head; fa.hd = c.head_dim; fa.scale = 1.f; fa.no_guard = 1;
+      r->launches += 1;
+      RCK(r, launch_attn_tc_fwd(st, fa, r->tc_err));
+    } else if ((rc = attention(r, q, rs, rp, M, kp, vp, att))) return rc;
     if (decode) { if ((rc = gemv(r, GV_RESID, att, W(r, p0 + 3), nullptr, d, hq, h2, d, h))) return rc; }
     else if ((rc = big_gemm(r, att, W(r, p0 + 3), h2, Mp, d, hq, EPI_RESID, h))) return rc;
     r->launches += 1;
-    k_rmsnorm_w<<<M, 256, 0, st>>>(h2, W(r, p0 + 10), nullptr, M, d, c.rms_eps, x);
+    RCK(r, klaunch(r, k_rmsnorm_w, dim3(M), dim3(256), 0, (const bf16*)h2, W(r, p0 + 10), (const int*)nullptr, M, d, c.rms_eps, x));
     if (decode) {
       if ((rc = gemv(r, GV_SWIGLU, x, W(r, p0 + 6), W(r, p0 + 7), f, d, act, f, nullptr))) return rc;
       if ((rc = gemv(r, GV_RESID, act, W(r, p0 + 8), nullptr, d, f, h, d, h2))) return rc;
@@ -546,12 +738,14 @@ int layers(pcpb_rollout* r, bool decode, int M, const int* rs, const int* rp) {
 // final norm of the given rows (gathered), LM head, argmax -> next tokens
 int head_and_sample(pcpb_rollout* r, const bf16* hsrc, const int* gather, int B, int max_new, int advance) {
   const pcpb_rollout_cfg& c = r->cfg;
-  r->launches += 3;
-  k_rmsnorm_w<<<B, 256, 0, r->stream>>>(hsrc, W(r, (int)r->nweights - 2), gather, B, c.d_model, c.rms_eps, r->dx);
+  r->launches += 4;
+  RCK(r, klaunch(r, k_rmsnorm_w, dim3(B), dim3(256), 0, hsrc, W(r, (int)r->nweights - 2), gather, B, c.d_model, c.rms_eps, r->dx));
   int rc = gemv(r, GV_STORE, r->dx, W(r, (int)r->nweights - 1), nullptr, c.vocab, c.d_model, r->logits, c.vocab, nullptr);
   if (rc) return rc;
-  k_argmax_advance<<<B, 1024, 0, r->stream>>>(r->logits, c.vocab, c.vocab, r->cur_tok, r->cur_pos, r->out_tok, max_new, r->step, advance);
-  k_bump<<<1, 1, 0, r->stream>>>(r->step);
+  RCK(r, klaunch(r, k_argmax_part, dim3(ARG_CHUNKS, B), dim3(256), 0, (const bf16*)r->logits, c.vocab, (long long)c.vocab, r->arg_val, r->arg_idx));
+  RCK(r, klaunch(r, k_argmax_advance, dim3(B), dim3(32), 0, (const float*)r->arg_val, (const int*)r->arg_idx, r->cur_tok, r->cur_pos, r->out_tok,
+                 max_new, (const int*)r->step, advance));
+  RCK(r, klaunch(r, k_bump, dim3(1), dim3(1), 0, r->step));
   RCK(r, cudaGetLastError());
   return PCPB_OK;
 }
@@ -559,10 +753,14 @@ int head_and_sample(pcpb_rollout* r, const bf16* hsrc, const int* gather, int B,
 int decode_step_enqueue(pcpb_rollout* r, int B, int max_new) {
   const pcpb_rollout_cfg& c = r->cfg;
   r->launches += 1;
-  k_embed_rows<<<B, 128, 0, r->stream>>>(W(r, 0), r->cur_tok, B, c.d_model, c.vocab, r->dh);
-  int rc = layers(r, true, B, r->drow_seq, r->cur_pos);
-  if (rc) return rc;
-  return head_and_sample(r, r->dh, nullptr, B, max_new, 1);
+  r->pdl_now = r->use_pdl;
+  cudaError_t e = klaunch(r, k_embed_rows, dim3(B), dim3(128), 0, W(r, 0), (const long long*)r->cur_tok, B, c.d_model, c.vocab, r->dh);
+  int rc = PCPB_OK;
+  if (e != cudaSuccess) rc = rfail(r, PCPB_E_CUDA, std::string("decode step launch failed: ") + cudaGetErrorString(e));
+  if (!rc) rc = layers(r, true, B, r->drow_seq, r->cur_pos);
+  if (!rc) rc = head_and_sample(r, r->dh, nullptr, B, max_new, 1);
+  r->pdl_now = false;
+  return rc;
 }
 
 }  // namespace
@@ -608,10 +806,11 @@ int pcpb_rollout_create(int device, const pcpb_rollout_cfg* cfg, pcpb_rollout** 
   }
   if (c.max_batch > ROWS) return rfail(r, PCPB_E_TOO_LARGE, "at most 16 sequences per step");
   r->hq = c.n_head * c.head_dim; r->hk = c.n_kv_head * c.head_dim;
-  // the decode GEMV splits K over 8 warps in pieces of 32 and N in pieces of 8
-  if (c.d_model % 256 || c.d_ff % 256 || r->hq % 256 || c.vocab % 8 || r->hk % 8)
-    return rfail(r, PCPB_E_INVALID, "d_model, d_ff and n_head*head_dim must be multiples of 256, vocab of 8");
+  // the decode GEMV splits K over 8 warps in pieces of 64 and N in pieces of 8
+  if (c.d_model % 512 || c.d_ff % 512 || r->hq % 512 || c.vocab % 8 || r->hk % 8)
+    return rfail(r, PCPB_E_INVALID, "d_model, d_ff and n_head*head_dim must be multiples of 512, vocab of 8");
   if (c.max_prompt > c.max_seq) return rfail(r, PCPB_E_INVALID, "max_prompt exceeds max_seq");
+  if (c.d_model > 8 * 4 * 256) return rfail(r, PCPB_E_TOO_LARGE, "d_model beyond 8192 is not supported by the norm kernel");
   Guard g(device);
   RCK(r, cudaSetDevice(device));
   cudaDeviceProp prop;
@@ -636,7 +835,11 @@ int pcpb_rollout_create(int device, const pcpb_rollout_cfg* cfg, pcpb_rollout** 
   r->n_pages = r->max_pages * c.max_batch;
   const size_t d = c.d_model, f = c.d_ff, nqkv = r->hq + 2 * r->hk, MR = r->max_rows;
   RA(r, r->h, MR * d * 2); RA(r, r->h2, MR * d * 2); RA(r, r->x, MR * d * 2); RA(r, r->qkv, MR * nqkv * 2);
-  RA(r, r->q, MR * r->hq * 2); RA(r, r->att, MR * r->hq * 2); RA(r, r->gu, MR * 2 * f * 2); RA(r, r->act, MR * f * 2);
+  RA(r, r->q, MR * r->hq * 2); RA(r, r->att, MR * r->hq * 2);
+  if (c.head_dim == 128) {
+    RA(r, r->sqk, MR * (size_t)(r->hq + r->hk) * 2); RA(r, r->sqv, MR * nqkv * 2);
+    RA(r, r->att_m, MR * (size_t)c.n_head * 4); RA(r, r->att_l, MR * (size_t)c.n_head * 4);
+  } RA(r, r->gu, MR * 2 * f * 2); RA(r, r->act, MR * f * 2);
   RA(r, r->dh, ROWS * d * 2); RA(r, r->dh2, ROWS * d * 2); RA(r, r->dx, ROWS * d * 2); RA(r, r->dqkv, ROWS * nqkv * 2);
   RA(r, r->dq, ROWS * (size_t)r->hq * 2); RA(r, r->datt, ROWS * (size_t)r->hq * 2); RA(r, r->dact, ROWS * f * 2);
   RA(r, r->logits, ROWS * (size_t)c.vocab * 2);
@@ -647,6 +850,7 @@ int pcpb_rollout_create(int device, const pcpb_rollout_cfg* cfg, pcpb_rollout** 
   RA(r, r->row_seq, MR * 4); RA(r, r->row_pos, MR * 4); RA(r, r->row_tok, MR * 8); RA(r, r->last_row, ROWS * 4);
   RA(r, r->drow_seq, ROWS * 4); RA(r, r->cur_pos, ROWS * 4); RA(r, r->cur_tok, ROWS * 8); RA(r, r->step, 4); RA(r, r->tc_err, 4);
   RCK(r, cudaMemset(r->tc_err, 0, 4));
+  RA(r, r->arg_val, ROWS * ARG_CHUNKS * 4); RA(r, r->arg_idx, ROWS * ARG_CHUNKS * 4);
   // rows beyond the batch stay zero in the 16-row operands of the decode GEMV
   RCK(r, cudaMemset(r->dh, 0, ROWS * d * 2)); RCK(r, cudaMemset(r->dh2, 0, ROWS * d * 2)); RCK(r, cudaMemset(r->dx, 0, ROWS * d * 2));
   RCK(r, cudaMemset(r->dq, 0, ROWS * (size_t)r->hq * 2)); RCK(r, cudaMemset(r->datt, 0, ROWS * (size_t)r->hq * 2));
@@ -668,6 +872,14 @@ int pcpb_rollout_create(int device, const pcpb_rollout_cfg* cfg, pcpb_rollout** 
     RCK(r, cudaMemcpy(r->sinT, stb.data(), stb.size() * 2, cudaMemcpyHostToDevice));
   }
   { int rc = attention(r, nullptr, nullptr, nullptr, 0, nullptr, nullptr, nullptr, true); if (rc) return rc; }
+  {
+    const char* e = getenv("PCPB_ROLLOUT_KMAP");          // "slices": every warp one contiguous K / 8 slice (for comparisons)
+    r->kmap_slices = (e && !strcmp(e, "slices")) ? 1 : 0;
+    e = getenv("PCPB_ROLLOUT_PREFILL");
+    r->no_tc_prefill = e && !strcmp(e, "rows");
+    e = getenv("PCPB_ROLLOUT_PDL");
+    r->use_pdl = !(e && e[0] == '0');
+  }
   return PCPB_OK;
 }
 
@@ -771,7 +983,18 @@ int pcpb_rollout_generate(pcpb_rollout* r, const int64_t* prompts, const int* pr
   if (Mp > M) RCK(r, cudaMemsetAsync(r->h + (size_t)M * c.d_model, 0, (size_t)(Mp - M) * c.d_model * 2, st));
   r->launches += 1;
   k_embed_rows<<<M, 128, 0, st>>>(W(r, 0), r->row_tok, M, c.d_model, c.vocab, r->h);
-  int rc = layers(r, false, M, r->row_seq, r->row_pos);
+  // equal prompt lengths that are a multiple of 128 (and head_dim 128): prefill attention on the tensor-core kernel
+  int tc_T = 0;
+  {
+    bool same = r->sqk != nullptr && lens[0] % 128 == 0 && !r->no_tc_prefill;
+    for (int b = 1; b < batch && same; ++b) same = lens[b] == lens[0];
+    if (same) {
+      FlashArgs fa{};
+      fa.qkn = r->sqk; fa.qkv = r->sqv; fa.o = r->att; fa.B = batch; fa.T = lens[0]; fa.H = c.n_head; fa.Hkv = c.n_kv_head; fa.hd = c.head_dim;
+      if (attn_tc_supported(fa)) tc_T = lens[0];
+    }
+  }
+  int rc = layers(r, false, M, r->row_seq, r->row_pos, tc_T);
   if (rc) return rc;
   if ((rc = head_and_sample(r, r->h, r->last_row, batch, max_new_tokens, 0))) return rc;
   RCK(r, cudaEventRecord(r->e1, st));

@@ -1,5 +1,6 @@
 """Disk formats of the reference's Shepherd, so that a run on this backend can be resumed by (or resume from) a PCP
-Shepherd: the model checkpoint `checkpoint_<step>.bin` (src/algorithms/diloco.zig:590-628) and the recovery file
+Shepherd (Backend.save_checkpoint / load_checkpoint for the parameters, Backend.load_recovery for parameters plus the
+Nesterov velocities of this rank's shard): the model checkpoint `checkpoint_<step>.bin` (src/algorithms/diloco.zig:590-628) and the recovery file
 `recovery/shepherd_state.bin` (diloco.zig:1063-1107, read back at :1110-1180).  Little-endian throughout.
 
     PCPCHECK file:  "PCPCHECK"  u32 version (= 1)  u32 n_tensors

@@ -17,9 +17,9 @@ from pcp_b200.backend import Rollout
 pytestmark = pytest.mark.gpu
 
 # Qwen3 geometry in small: head_dim 128, 4 query heads on 2 kv heads (GQA), weighted norms, SwiGLU
-SMALL = QwenConfig(vocab=1024, d_model=512, n_layer=2, n_head=4, n_kv_head=2, head_dim=128, d_ff=768, max_seq=64, dtype="bf16")
-# head_dim 64, one kv head for four query heads, odd vocabulary size (a multiple of 8 only)
-HD64 = QwenConfig(vocab=1000, d_model=256, n_layer=1, n_head=4, n_kv_head=1, head_dim=64, d_ff=512, max_seq=48, dtype="bf16")
+SMALL = QwenConfig(vocab=1024, d_model=512, n_layer=2, n_head=4, n_kv_head=2, head_dim=128, d_ff=1024, max_seq=64, dtype="bf16")
+# head_dim 64, two kv heads for eight query heads, odd vocabulary size (a multiple of 8 only)
+HD64 = QwenConfig(vocab=1000, d_model=512, n_layer=1, n_head=8, n_kv_head=2, head_dim=64, d_ff=512, max_seq=48, dtype="bf16")
 
 
 def _engine(cfg, max_batch=16, page_tokens=4):
@@ -112,6 +112,37 @@ def test_rollout_stops_at_eos_and_pages_are_reused():
             assert got[1][:n1] == full[1][:n1] and len(got[1]) == 8 and reasons[1] == "length"
 
 
+def test_prefill_on_the_tensor_core_attention_kernel(monkeypatch):
+    """Prompts of one length that is a multiple of 128 (head_dim 128) are prefilled with the tcgen05 attention kernel
+    over a staged copy of q and of k, v shifted by one position behind a zero row -- which gives the ordinary causal
+    kernel exactly the slots the exported step attends to.  Checked against the oracle and against the row kernel."""
+    cfg = QwenConfig(vocab=1024, d_model=512, n_layer=2, n_head=4, n_kv_head=2, head_dim=128, d_ff=1024, max_seq=160, dtype="bf16")
+    params = seeded_params(cfg, seed=5, std=0.05, head_std=1.0)
+    rng = np.random.default_rng(2)
+    prompts = [rng.integers(0, cfg.vocab, size=128).tolist() for _ in range(3)]
+    new = 4
+    recs = [[] for _ in prompts]
+    want = [generate(cfg, params, p, new, record_logits=r)[0] for p, r in zip(prompts, recs)]
+    out = {}
+    for mode in ("", "rows"):
+        monkeypatch.setenv("PCPB_ROLLOUT_PREFILL", mode)
+        with _engine(cfg, max_batch=4, page_tokens=16) as eng:
+            eng.ensure_device_weights(_blob_bf16(params))
+            toks, _, _ = eng.generate_rollout(prompts, 1)                # the prefill's own logits
+            first = [eng.read_logits(b) for b in range(len(prompts))]
+            full, _, _ = eng.generate_rollout(prompts, new)
+            out[mode] = (toks, first, full)
+    for mode, (toks, first, full) in out.items():
+        for b in range(len(prompts)):
+            ref = recs[b][0].numpy()
+            assert np.abs(first[b] - ref).max() <= 2e-2 * np.abs(ref).max(), (mode, b)
+            n = _clear_prefix(recs[b])
+            assert full[b][:n] == want[b][:n], (mode, b, n)
+    # the two prefill paths differ only by rounding noise
+    for b in range(len(prompts)):
+        assert np.abs(out[""][1][b] - out["rows"][1][b]).max() <= 1e-2 * np.abs(out["rows"][1][b]).max()
+
+
 def test_rollout_argument_errors():
     cfg = HD64
     with _engine(cfg, max_batch=2) as eng:
@@ -131,4 +162,4 @@ def test_rollout_argument_errors():
         toks, _, _ = eng.generate_rollout([[1, 2, 3]], 4)
         assert len(toks[0]) == 4 and all(0 <= t < cfg.vocab for t in toks[0])
     with pytest.raises(BackendError):
-        Rollout(0, 1000, 200, 1, 4, 1, 64, 512, 48)           # d_model not a multiple of 256
+        Rollout(0, 1000, 200, 1, 4, 1, 64, 512, 48)           # d_model not a multiple of 512
