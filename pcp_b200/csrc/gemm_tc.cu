@@ -192,7 +192,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, int c
 
 // Output tile of a work item.  Tiles are numbered so that tiles running at the same time share operands in L2: when
 // there are many column tiles (the LM head: every row tile would otherwise stream the whole weight matrix through
-// L2), groups of 8 row tiles walk the columns together; otherwise columns vary fastest.
+// L2), groups of row tiles walk the columns together; otherwise columns vary fastest.
 __device__ __forceinline__ void tile_coords(const TcParams& p, int tile, int* tm, int* tn) {
   if (p.group_m <= 1) { *tm = tile / p.tiles_n; *tn = tile % p.tiles_n; return; }
   const int per_group = p.group_m * p.tiles_n;
@@ -714,7 +714,15 @@ cudaError_t launch_gemm_tc(cudaStream_t st, const GemmArgs& g) {
   TcParams p;
   p.M = g.M; p.N = g.N; p.K = g.K;
   p.tiles_m = g.M / (pl.pair ? 256 : BM); p.tiles_n = g.N / pl.bn; p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
-  p.group_m = (p.tiles_n >= 32 && p.splits == 1) ? 8 : 1;
+  {
+    // Row tiles that walk the columns together (LM-head forward).  Every group streams the whole weight matrix, which
+    // does not stay in L2 next to the output stream, so DRAM reads are about (row tiles / group) x |W|; the group's rows
+    // of A must stay in L2 (group x 0.65 MB at K = 1280).  Measured at 32768 x 65536 x 1280 (128 row tiles): 8 -> 4.8 GB
+    // read, 3.85 ms; 32 -> 1.5 GB, 3.62 ms; 64 -> 2.9 GB, 3.73 ms.  PCPB_GEMM_GROUP_M overrides it for such comparisons.
+    static int group_env = -1;
+    if (group_env < 0) { const char* e = getenv("PCPB_GEMM_GROUP_M"); group_env = e ? atoi(e) : 0; }
+    p.group_m = (p.tiles_n >= 32 && p.splits == 1) ? (group_env > 0 ? group_env : 32) : 1;
+  }
   {
     // 256-bit epilogue accesses need every row segment to start on a 32-byte boundary (16 bf16 / 8 f32 elements)
     const uintptr_t all = (uintptr_t)g.C | (uintptr_t)g.R | (uintptr_t)g.C2 | (uintptr_t)g.scratch;

@@ -35,6 +35,7 @@
 
 #include <stdlib.h>
 
+#include <algorithm>
 #include <string>
 #include <vector>
 
@@ -83,9 +84,10 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 // K % 512 == 0 (a warp's share is a multiple of 64), N % 8 == 0.  X rows beyond the batch are zero.
 // A lane reads 32 consecutive bytes (16 k values) of its weight row per step, so the four lanes of a row cover a whole
 // 128-byte line; those 16 values serve four k16 MMA steps, and X is read with the same permutation of k.
-// Which k values a warp takes does not matter for the result's definition (the partial sums are added in warp order);
-// by default the warps interleave: in step i warp w reads the 64 k values (128 bytes per row) at (GV_WARPS i + w) * 64,
-// so that the CTA as a whole reads 512 contiguous bytes of each of its 8 weight rows at a time.
+// Which k values a warp takes does not matter for the result's definition (the partial sums are added in warp order):
+// by default warp w takes the contiguous slice [w K / 8, (w + 1) K / 8); with kmap_slices == 0 the warps interleave (in
+// step i warp w reads the 64 k values at (GV_WARPS i + w) * 64, so that the CTA reads 512 contiguous bytes of each of its
+// 8 weight rows at a time), which measured 1 - 2 % slower per decode step.
 template <int EPI>
 __global__ void __launch_bounds__(GV_WARPS * 32, 4) k_gemv16(const bf16* __restrict__ X, const bf16* __restrict__ W, const bf16* __restrict__ W2,
                                                 int N, int K, bf16* __restrict__ C, long long ldc, const bf16* __restrict__ R,
@@ -161,6 +163,143 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 4) k_gemv16(const bf16* __restr
     if (EPI == GV_RESID) v = bf16_round(to_f(R[o]) + v);
     if (EPI == GV_SWIGLU) v = bf16_round(silu_bf16(v) * bf16_round(s2));
     C[o] = from_f<bf16>(v);
+  }
+}
+
+// Wide form of the same product: a CTA of 8 warps owns 64 output columns (warp w the 8 columns n0 + 8 w ..) and the k
+// range [blockIdx.y kc, (blockIdx.y + 1) kc); the operand X of that range is staged in shared memory once per CTA (in
+// pieces of GW_KC columns) and shared by the 8 warps.  In the 8-column form every CTA fetches all of X: two bytes of X
+// from L2 for every weight byte from HBM (ncu: 273 MB into the SMs for 101 MB of DRAM reads), and the X loads sit
+// between the arrival of a batch of weights and the issue of the next.  Here X costs a quarter of a byte per weight
+// byte and comes out of shared memory.
+// The contraction is split over gridDim.y CTAs so that small matrices still fill the GPU.  Partial sums go to `part`
+// ([gridDim.y][16][N] f32, a second panel behind it for SwiGLU); the CTA that finds the column block's counter at
+// gridDim.y - 1 adds the partials in split order (the result does not depend on which CTA that is), applies the epilogue
+// and puts the counter back to 0.  No CTA waits for another.
+constexpr int GW_KC = 1024;                                     // columns of X staged at a time
+constexpr int GW_LD = GW_KC + 8;                                // shared-memory row stride (elements): conflict-free 16-byte reads
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+template <int EPI>
+__global__ void __launch_bounds__(256, 4) k_gemv16w(const bf16* __restrict__ X, const bf16* __restrict__ W, const bf16* __restrict__ W2,
+                                                    int N, int K, int kc, bf16* __restrict__ C, long long ldc, const bf16* __restrict__ R,
+                                                    float* __restrict__ part, int* __restrict__ counters) {
+  extern __shared__ __align__(16) uint8_t gw_smem[];
+  bf16* xs = reinterpret_cast<bf16*>(gw_smem);                  // [16][GW_LD]
+  __shared__ int s_last;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+  const int n0 = blockIdx.x * 64 + warp * 8;
+  const bool active = n0 < N;                                   // N % 8 == 0: a warp's 8 columns are all in or all out
+  const int kbeg = blockIdx.y * kc;
+  const int nsteps = kc / 64;
+  const bf16* wrow = W + (size_t)(active ? n0 + g : 0) * K + kbeg + 16 * q;
+  const bf16* w2row = (EPI == GV_SWIGLU) ? W2 + (size_t)(active ? n0 + g : 0) * K + kbeg + 16 * q : nullptr;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
+  constexpr int U = (EPI == GV_SWIGLU) ? 2 : 4;                 // 32-byte weight pieces in flight per lane and panel
+  uint4 wv[U][2], w2v[U][2];
+  auto load_w = [&](int s) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const bool in = active && s + u < nsteps;
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        wv[u][hlf] = in ? ld_stream(wrow + (s + u) * 64 + 8 * hlf) : make_uint4(0, 0, 0, 0);
+        if (EPI == GV_SWIGLU) w2v[u][hlf] = in ? ld_stream(w2row + (s + u) * 64 + 8 * hlf) : make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  pdl_launch_dependents();
+  load_w(0);                                                    // weights do not depend on the previous kernel
+  pdl_wait();                                                   // X (and R, part, counters) do
+  for (int s = 0; s < nsteps; s += U) {
+    if (s > 0) load_w(s);
+    if ((s * 64) % GW_KC == 0) {                                // next piece of X (GW_KC is a multiple of 64 U)
+      if (s > 0) __syncthreads();                               // every warp is done with the previous piece
+      const int len = min(GW_KC, kc - s * 64);
+      const bf16* src = X + kbeg + s * 64;
+      for (int i = threadIdx.x; i < ROWS * (len / 8); i += blockDim.x) {
+        const int row = i / (len / 8), c8 = i % (len / 8);
+        cp_async16(xs + row * GW_LD + c8 * 8, src + (size_t)row * K + c8 * 8);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      __syncthreads();
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (s + u >= nsteps) break;
+      const int xc = ((s + u) * 64) % GW_KC + 16 * q;
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        // 8 consecutive k values serve two k16 steps: elements {0,1,2,3} and {4,5,6,7}; the operand X is read with
+        // the same permutation of k, so the products line up
+        const uint4 a = *reinterpret_cast<const uint4*>(xs + g * GW_LD + xc + 8 * hlf);
+        const uint4 b = *reinterpret_cast<const uint4*>(xs + (g + 8) * GW_LD + xc + 8 * hlf);
+        mma16816(acc, a.x, b.x, a.y, b.y, wv[u][hlf].x, wv[u][hlf].y);
+        mma16816(acc, a.z, b.z, a.w, b.w, wv[u][hlf].z, wv[u][hlf].w);
+        if (EPI == GV_SWIGLU) {
+          mma16816(acc2, a.x, b.x, a.y, b.y, w2v[u][hlf].x, w2v[u][hlf].y);
+          mma16816(acc2, a.z, b.z, a.w, b.w, w2v[u][hlf].z, w2v[u][hlf].w);
+        }
+      }
+    }
+  }
+  // accumulator layout: acc[0], acc[1] = (row g, cols 2q, 2q+1); acc[2], acc[3] = (row g + 8, same cols)
+  const int splits = gridDim.y;
+  const int col = n0 + 2 * q;
+  if (splits > 1) {
+    if (active) {
+      float* mine = part + (size_t)blockIdx.y * ROWS * N;
+      *reinterpret_cast<float2*>(mine + (size_t)g * N + col) = make_float2(acc[0], acc[1]);
+      *reinterpret_cast<float2*>(mine + (size_t)(g + 8) * N + col) = make_float2(acc[2], acc[3]);
+      if (EPI == GV_SWIGLU) {
+        float* m2 = mine + (size_t)splits * ROWS * N;
+        *reinterpret_cast<float2*>(m2 + (size_t)g * N + col) = make_float2(acc2[0], acc2[1]);
+        *reinterpret_cast<float2*>(m2 + (size_t)(g + 8) * N + col) = make_float2(acc2[2], acc2[3]);
+      }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int seen = atomicAdd(counters + blockIdx.x, 1);
+      s_last = (seen == splits - 1);
+      if (s_last) counters[blockIdx.x] = 0;                     // ready for the next launch (launches are serialised)
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (active) {
+      acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+      acc2[0] = acc2[1] = acc2[2] = acc2[3] = 0.f;
+      for (int sp = 0; sp < splits; ++sp) {                     // split order: the sum does not depend on timing
+        const float* src = part + (size_t)sp * ROWS * N;
+        const float2 lo = __ldcg(reinterpret_cast<const float2*>(src + (size_t)g * N + col));
+        const float2 hi = __ldcg(reinterpret_cast<const float2*>(src + (size_t)(g + 8) * N + col));
+        acc[0] += lo.x; acc[1] += lo.y; acc[2] += hi.x; acc[3] += hi.y;
+        if (EPI == GV_SWIGLU) {
+          const float* s2 = src + (size_t)splits * ROWS * N;
+          const float2 lo2 = __ldcg(reinterpret_cast<const float2*>(s2 + (size_t)g * N + col));
+          const float2 hi2 = __ldcg(reinterpret_cast<const float2*>(s2 + (size_t)(g + 8) * N + col));
+          acc2[0] += lo2.x; acc2[1] += lo2.y; acc2[2] += hi2.x; acc2[3] += hi2.y;
+        }
+      }
+    }
+  }
+  if (!active) return;
+#pragma unroll
+  for (int hlf = 0; hlf < 2; ++hlf) {
+    const size_t o = (size_t)(g + 8 * hlf) * ldc + col;
+    float v0 = bf16_round(acc[2 * hlf]), v1 = bf16_round(acc[2 * hlf + 1]);
+    if (EPI == GV_RESID) {
+      const __nv_bfloat162 rr = *reinterpret_cast<const __nv_bfloat162*>(R + o);
+      v0 = bf16_round(__bfloat162float(rr.x) + v0); v1 = bf16_round(__bfloat162float(rr.y) + v1);
+    }
+    if (EPI == GV_SWIGLU) {
+      v0 = bf16_round(silu_bf16(v0) * bf16_round(acc2[2 * hlf]));
+      v1 = bf16_round(silu_bf16(v1) * bf16_round(acc2[2 * hlf + 1]));
+    }
+    *reinterpret_cast<__nv_bfloat162*>(C + o) = __floats2bfloat162_rn(v0, v1);
   }
 }
 
@@ -540,7 +679,10 @@ struct pcpb_rollout {
   cudaGraphExec_t graph = nullptr;
   int graph_batch = 0, graph_maxnew = 0;
   long long graph_launches = 0;      // kernels in one replay of the decode-step graph
-  int kmap_slices = 0;               // 0: the warps of a CTA interleave 128-byte pieces of the rows (default)
+  float* gv_part = nullptr;          // split-K partial sums of the wide decode GEMV
+  int* gv_cnt = nullptr;             // one arrival counter per 64-column block (back at 0 after every launch)
+  int gv_wide = 1, gv_min_ctas = 512;     // PCPB_ROLLOUT_GEMV=narrow: the 8-column kernel; PCPB_ROLLOUT_GEMV_CTAS: split target
+  int kmap_slices = 1;               // 1: every warp one contiguous K / 8 slice (default); 0: interleaved 128-byte pieces
   bool no_tc_prefill = false;             // PCPB_ROLLOUT_PREFILL=rows: the row kernel also for aligned prompts
   bool use_pdl = true, pdl_now = false;   // programmatic dependent launch inside the decode step (PCPB_ROLLOUT_PDL=0: off)
   cudaEvent_t e0 = nullptr, e1 = nullptr, e2 = nullptr;
@@ -625,9 +767,36 @@ int big_gemm(pcpb_rollout* r, const bf16* A, const bf16* Wt, bf16* C, int M, int
   return PCPB_OK;
 }
 
+// Split of the contraction for the wide GEMV: the smallest number of k ranges (each a multiple of 64) with which the
+// launch has at least min_ctas CTAs and no CTA streams more than 256 KB of weights.
+int gv_splits(int N, int K, bool swiglu, int min_ctas) {
+  const int blocks = (N + 63) / 64, steps = K / 64;
+  int best = 1;
+  for (int sp = 1; sp <= steps && sp <= 32; ++sp) {
+    if (steps % sp) continue;
+    best = sp;
+    const size_t bytes = (size_t)64 * (K / sp) * 2 * (swiglu ? 2 : 1);
+    if (blocks * sp >= min_ctas && bytes <= 256 * 1024) break;
+  }
+  return best;
+}
+size_t gv_part_elems(int N, int K, bool swiglu, int min_ctas) {
+  const int sp = gv_splits(N, K, swiglu, min_ctas);
+  return sp > 1 ? (size_t)sp * ROWS * N * (swiglu ? 2 : 1) : 0;
+}
+
 int gemv(pcpb_rollout* r, int epi, const bf16* X, const bf16* Wt, const bf16* W2, int N, int K, bf16* C, long long ldc, const bf16* R) {
   r->launches += 1;
   const bf16* none = nullptr;
+  if (r->gv_wide) {
+    const int sp = gv_splits(N, K, epi == GV_SWIGLU, r->gv_min_ctas), kc = K / sp;
+    const dim3 grid((N + 63) / 64, sp), block(256);
+    const size_t smem = (size_t)ROWS * GW_LD * 2;
+    if (epi == GV_STORE) RCK(r, klaunch(r, k_gemv16w<GV_STORE>, grid, block, smem, X, Wt, none, N, K, kc, C, ldc, none, r->gv_part, r->gv_cnt));
+    else if (epi == GV_RESID) RCK(r, klaunch(r, k_gemv16w<GV_RESID>, grid, block, smem, X, Wt, none, N, K, kc, C, ldc, R, r->gv_part, r->gv_cnt));
+    else RCK(r, klaunch(r, k_gemv16w<GV_SWIGLU>, grid, block, smem, X, Wt, W2, N, K, kc, C, ldc, none, r->gv_part, r->gv_cnt));
+    return PCPB_OK;
+  }
   if (epi == GV_STORE) RCK(r, klaunch(r, k_gemv16<GV_STORE>, dim3(N / 8), dim3(GV_WARPS * 32), 0, X, Wt, none, N, K, C, ldc, none, r->kmap_slices));
   else if (epi == GV_RESID) RCK(r, klaunch(r, k_gemv16<GV_RESID>, dim3(N / 8), dim3(GV_WARPS * 32), 0, X, Wt, none, N, K, C, ldc, R, r->kmap_slices));
   else RCK(r, klaunch(r, k_gemv16<GV_SWIGLU>, dim3(N / 8), dim3(GV_WARPS * 32), 0, X, Wt, W2, N, K, C, ldc, none, r->kmap_slices));
@@ -851,6 +1020,22 @@ int pcpb_rollout_create(int device, const pcpb_rollout_cfg* cfg, pcpb_rollout** 
   RA(r, r->drow_seq, ROWS * 4); RA(r, r->cur_pos, ROWS * 4); RA(r, r->cur_tok, ROWS * 8); RA(r, r->step, 4); RA(r, r->tc_err, 4);
   RCK(r, cudaMemset(r->tc_err, 0, 4));
   RA(r, r->arg_val, ROWS * ARG_CHUNKS * 4); RA(r, r->arg_idx, ROWS * ARG_CHUNKS * 4);
+  {
+    const char* e = getenv("PCPB_ROLLOUT_GEMV");
+    r->gv_wide = !(e && !strcmp(e, "narrow"));
+    e = getenv("PCPB_ROLLOUT_GEMV_CTAS");
+    if (e && atoi(e) > 0) r->gv_min_ctas = atoi(e);
+    const int mc = r->gv_min_ctas, nqkv = r->hq + 2 * r->hk;
+    size_t pe = gv_part_elems(nqkv, (int)d, false, mc);
+    pe = std::max(pe, gv_part_elems((int)d, r->hq, false, mc));
+    pe = std::max(pe, gv_part_elems(c.d_ff, (int)d, true, mc));
+    pe = std::max(pe, gv_part_elems((int)d, c.d_ff, false, mc));
+    pe = std::max(pe, gv_part_elems(c.vocab, (int)d, false, mc));
+    RA(r, r->gv_part, pe * 4);
+    const size_t nb = (size_t)(std::max(std::max(nqkv, c.d_ff), c.vocab) + 63) / 64;
+    RA(r, r->gv_cnt, nb * 4);
+    RCK(r, cudaMemset(r->gv_cnt, 0, nb * 4));
+  }
   // rows beyond the batch stay zero in the 16-row operands of the decode GEMV
   RCK(r, cudaMemset(r->dh, 0, ROWS * d * 2)); RCK(r, cudaMemset(r->dh2, 0, ROWS * d * 2)); RCK(r, cudaMemset(r->dx, 0, ROWS * d * 2));
   RCK(r, cudaMemset(r->dq, 0, ROWS * (size_t)r->hq * 2)); RCK(r, cudaMemset(r->datt, 0, ROWS * (size_t)r->hq * 2));
@@ -873,8 +1058,8 @@ int pcpb_rollout_create(int device, const pcpb_rollout_cfg* cfg, pcpb_rollout** 
   }
   { int rc = attention(r, nullptr, nullptr, nullptr, 0, nullptr, nullptr, nullptr, true); if (rc) return rc; }
   {
-    const char* e = getenv("PCPB_ROLLOUT_KMAP");          // "slices": every warp one contiguous K / 8 slice (for comparisons)
-    r->kmap_slices = (e && !strcmp(e, "slices")) ? 1 : 0;
+    const char* e = getenv("PCPB_ROLLOUT_KMAP");          // "interleave": 128-byte pieces of a row go round the warps (for comparisons)
+    r->kmap_slices = (e && !strcmp(e, "interleave")) ? 0 : 1;
     e = getenv("PCPB_ROLLOUT_PREFILL");
     r->no_tc_prefill = e && !strcmp(e, "rows");
     e = getenv("PCPB_ROLLOUT_PDL");
