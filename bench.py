@@ -393,7 +393,7 @@ def time_rollout(device, steps, warmup, peaks, c=None):
     achieved = weight_bytes / (step_ms / 1e3) / 1e9
     return {"value": steps * n_new / ((pre + dec) / 1e3), "e2e": steps * n_new / wall, "prefill_ms": pre / steps, "decode_ms": dec / steps,
             "decode_step_ms": step_ms, "launches": int(launches), "weight_bytes_per_decode_step": weight_bytes,
-            "roofline": {"kernel": "k_gemv16 (decode-step weight streaming: every weight byte read once per step for 16 rows)",
+            "roofline": {"kernel": "k_gemv16w (decode-step weight streaming: every weight byte read once per step for 16 rows)",
                          "bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm, "traffic": None,
                          "how": "algorithmic bytes = bf16 weights of all layers + LM head per decode step, over the mean device time "
                                 "of a decode step (CUDA events around the decode loop); the step also reads the KV cache and runs the "

@@ -192,7 +192,8 @@ __global__ void __launch_bounds__(256, 4) k_gemv16w(const bf16* __restrict__ X, 
   const int n0 = blockIdx.x * 64 + warp * 8;
   const bool active = n0 < N;                                   // N % 8 == 0: a warp's 8 columns are all in or all out
   const int kbeg = blockIdx.y * kc;
-  const int nsteps = kc / 64;
+  const int klen = min(kc, K - kbeg);                           // the last k range may be shorter
+  const int nsteps = klen / 64;
   const bf16* wrow = W + (size_t)(active ? n0 + g : 0) * K + kbeg + 16 * q;
   const bf16* w2row = (EPI == GV_SWIGLU) ? W2 + (size_t)(active ? n0 + g : 0) * K + kbeg + 16 * q : nullptr;
   float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
@@ -216,7 +217,7 @@ __global__ void __launch_bounds__(256, 4) k_gemv16w(const bf16* __restrict__ X, 
     if (s > 0) load_w(s);
     if ((s * 64) % GW_KC == 0) {                                // next piece of X (GW_KC is a multiple of 64 U)
       if (s > 0) __syncthreads();                               // every warp is done with the previous piece
-      const int len = min(GW_KC, kc - s * 64);
+      const int len = min(GW_KC, klen - s * 64);
       const bf16* src = X + kbeg + s * 64;
       for (int i = threadIdx.x; i < ROWS * (len / 8); i += blockDim.x) {
         const int row = i / (len / 8), c8 = i % (len / 8);
@@ -681,7 +682,7 @@ struct pcpb_rollout {
   long long graph_launches = 0;      // kernels in one replay of the decode-step graph
   float* gv_part = nullptr;          // split-K partial sums of the wide decode GEMV
   int* gv_cnt = nullptr;             // one arrival counter per 64-column block (back at 0 after every launch)
-  int gv_wide = 1, gv_min_ctas = 512;     // PCPB_ROLLOUT_GEMV=narrow: the 8-column kernel; PCPB_ROLLOUT_GEMV_CTAS: split target
+  int gv_wide = 1, gv_slots = 592;        // PCPB_ROLLOUT_GEMV=narrow: the 8-column kernel; gv_slots: resident CTAs (4 per SM)
   int kmap_slices = 1;               // 1: every warp one contiguous K / 8 slice (default); 0: interleaved 128-byte pieces
   bool no_tc_prefill = false;             // PCPB_ROLLOUT_PREFILL=rows: the row kernel also for aligned prompts
   bool use_pdl = true, pdl_now = false;   // programmatic dependent launch inside the decode step (PCPB_ROLLOUT_PDL=0: off)
@@ -767,30 +768,31 @@ int big_gemm(pcpb_rollout* r, const bf16* A, const bf16* Wt, bf16* C, int M, int
   return PCPB_OK;
 }
 
-// Split of the contraction for the wide GEMV: the smallest number of k ranges (each a multiple of 64) with which the
-// launch has at least min_ctas CTAs and no CTA streams more than 256 KB of weights.
-int gv_splits(int N, int K, bool swiglu, int min_ctas) {
+// Split of the contraction for the wide GEMV into k ranges of `kc` columns (a multiple of 64; the last range may be
+// shorter).  Matrices with fewer column blocks than CTA slots (4 per SM): as many ranges as keep the launch within one
+// wave of resident CTAs, so that no second, mostly empty wave follows (768 CTAs on 592 slots ran as two).  Larger
+// matrices (the LM head): ranges of at most 256 KB of weights per CTA, many waves.
+struct GvPlan { int splits, kc; };
+GvPlan gv_plan(int N, int K, bool swiglu, int slots) {
   const int blocks = (N + 63) / 64, steps = K / 64;
-  int best = 1;
-  for (int sp = 1; sp <= steps && sp <= 32; ++sp) {
-    if (steps % sp) continue;
-    best = sp;
-    const size_t bytes = (size_t)64 * (K / sp) * 2 * (swiglu ? 2 : 1);
-    if (blocks * sp >= min_ctas && bytes <= 256 * 1024) break;
-  }
-  return best;
+  int sp;
+  if (blocks <= slots) sp = std::max(1, std::min(steps, slots / blocks));
+  else sp = std::max(1, (int)(((size_t)64 * K * 2 * (swiglu ? 2 : 1) + 256 * 1024 - 1) / (256 * 1024)));
+  const int kc_steps = (steps + sp - 1) / sp;
+  return GvPlan{(steps + kc_steps - 1) / kc_steps, kc_steps * 64};
 }
-size_t gv_part_elems(int N, int K, bool swiglu, int min_ctas) {
-  const int sp = gv_splits(N, K, swiglu, min_ctas);
-  return sp > 1 ? (size_t)sp * ROWS * N * (swiglu ? 2 : 1) : 0;
+size_t gv_part_elems(int N, int K, bool swiglu, int slots) {
+  const GvPlan pl = gv_plan(N, K, swiglu, slots);
+  return pl.splits > 1 ? (size_t)pl.splits * ROWS * N * (swiglu ? 2 : 1) : 0;
 }
 
 int gemv(pcpb_rollout* r, int epi, const bf16* X, const bf16* Wt, const bf16* W2, int N, int K, bf16* C, long long ldc, const bf16* R) {
   r->launches += 1;
   const bf16* none = nullptr;
   if (r->gv_wide) {
-    const int sp = gv_splits(N, K, epi == GV_SWIGLU, r->gv_min_ctas), kc = K / sp;
-    const dim3 grid((N + 63) / 64, sp), block(256);
+    const GvPlan pl = gv_plan(N, K, epi == GV_SWIGLU, r->gv_slots);
+    const int kc = pl.kc;
+    const dim3 grid((N + 63) / 64, pl.splits), block(256);
     const size_t smem = (size_t)ROWS * GW_LD * 2;
     if (epi == GV_STORE) RCK(r, klaunch(r, k_gemv16w<GV_STORE>, grid, block, smem, X, Wt, none, N, K, kc, C, ldc, none, r->gv_part, r->gv_cnt));
     else if (epi == GV_RESID) RCK(r, klaunch(r, k_gemv16w<GV_RESID>, grid, block, smem, X, Wt, none, N, K, kc, C, ldc, R, r->gv_part, r->gv_cnt));
@@ -1023,9 +1025,14 @@ int pcpb_rollout_create(int device, const pcpb_rollout_cfg* cfg, pcpb_rollout** 
   {
     const char* e = getenv("PCPB_ROLLOUT_GEMV");
     r->gv_wide = !(e && !strcmp(e, "narrow"));
-    e = getenv("PCPB_ROLLOUT_GEMV_CTAS");
-    if (e && atoi(e) > 0) r->gv_min_ctas = atoi(e);
-    const int mc = r->gv_min_ctas, nqkv = r->hq + 2 * r->hk;
+    {
+      int sms = 148;
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, r->device);
+      r->gv_slots = 4 * (sms > 0 ? sms : 148);
+    }
+    e = getenv("PCPB_ROLLOUT_GEMV_CTAS");                  // for comparisons
+    if (e && atoi(e) > 0) r->gv_slots = atoi(e);
+    const int mc = r->gv_slots, nqkv = r->hq + 2 * r->hk;
     size_t pe = gv_part_elems(nqkv, (int)d, false, mc);
     pe = std::max(pe, gv_part_elems((int)d, r->hq, false, mc));
     pe = std::max(pe, gv_part_elems(c.d_ff, (int)d, true, mc));
