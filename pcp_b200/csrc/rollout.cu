@@ -566,195 +566,6 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_rows(const bf16* __restric
   }
 }
 
-// Decode-step attention in two kernels, the keys of a row spread over many CTAs (with one CTA per (row, kv head) the
-// step had 128 CTAs, each a chain of dependent loads as long as the context).  Same arithmetic as k_attn_rows.
-//   k_attn_dscores  grid (rows, Hkv, ceil(kcap / 32)), 128 threads: four threads per key, each a quarter of the head
-//                   dimension with all its 16-byte loads requested together; G dot products per key, the quarters added
-//                   by shuffles; the bf16-rounded scores go to S [row][head][position] (f32).
-//   k_attn_dpv      grid (rows, Hkv, ceil(kcap / 64)), 256 threads: every CTA reads the row's scores (G x pos floats, out
-//                   of L2), computes the row maxima and sums itself (every CTA the same numbers in the same order), turns
-//                   its own 64 keys into bf16 probabilities and multiplies them with its 64 value rows (8 per warp, all
-//                   requested together).  Partial outputs go to `part`; the CTA that finds the arrival counter of the
-//                   (row, kv head) complete adds them in chunk order and writes the bf16 output.  No CTA waits for another.
-// kcap: upper bound of the positions in this generate call (grid size of the captured graph); CTAs beyond the row's
-// position return at once.
-constexpr int DS_KEYS = 32, DP_KEYS = 64;
-template <int HD, int G>
-__global__ void __launch_bounds__(128) k_attn_dscores(const bf16* __restrict__ qbuf, RowMap map, int H, int Hkv, const int* __restrict__ block_table,
-                                                      int max_pages, int page, const bf16* __restrict__ kpages, int ldS, float* __restrict__ S) {
-  constexpr int QW = HD / 4;                     // elements per quarter
-  constexpr int QS = G * QW + 4;                 // words per quarter in shared memory: the four quarters fall on different banks
-  constexpr int NQ = HD / 32;                    // 16-byte loads per thread
-  __shared__ __align__(16) float qs[4 * QS];
-  pdl_launch_dependents();
-  pdl_wait();
-  const int m = blockIdx.x, kvh = blockIdx.y;
-  const int sq = map.seq[m], pos = map.pos[m];
-  const int j0 = blockIdx.z * DS_KEYS;
-  if (sq < 0 || j0 >= pos) return;
-  const int qd = threadIdx.x & 3, j = j0 + (threadIdx.x >> 2);
-  const bool in = j < pos;
-  const int jj = in ? j : j0;
-  const int pg = block_table[sq * max_pages + jj / page];
-  for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
-    const int g = i / HD, e = i % HD;
-    qs[(e / QW) * QS + g * QW + (e % QW)] = to_f(qbuf[(size_t)m * H * HD + (size_t)(kvh * G) * HD + i]);
-  }
-  const bf16* kr = kpages + (((size_t)pg * Hkv + kvh) * page + (jj % page)) * HD + qd * QW;
-  uint4 kraw[NQ];
-#pragma unroll
-  for (int c = 0; c < NQ; ++c) kraw[c] = *reinterpret_cast<const uint4*>(kr + c * 8);
-  __syncthreads();
-  float d[G];
-#pragma unroll
-  for (int g = 0; g < G; ++g) d[g] = 0.f;
-#pragma unroll
-  for (int c = 0; c < NQ; ++c) {
-    const float kf[8] = {bf_lo(kraw[c].x), bf_hi(kraw[c].x), bf_lo(kraw[c].y), bf_hi(kraw[c].y),
-                         bf_lo(kraw[c].z), bf_hi(kraw[c].z), bf_lo(kraw[c].w), bf_hi(kraw[c].w)};
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const float4 qa = *reinterpret_cast<const float4*>(qs + qd * QS + g * QW + c * 8);
-      const float4 qb = *reinterpret_cast<const float4*>(qs + qd * QS + g * QW + c * 8 + 4);
-      d[g] = fmaf(qa.x, kf[0], d[g]); d[g] = fmaf(qa.y, kf[1], d[g]); d[g] = fmaf(qa.z, kf[2], d[g]); d[g] = fmaf(qa.w, kf[3], d[g]);
-      d[g] = fmaf(qb.x, kf[4], d[g]); d[g] = fmaf(qb.y, kf[5], d[g]); d[g] = fmaf(qb.z, kf[6], d[g]); d[g] = fmaf(qb.w, kf[7], d[g]);
-    }
-  }
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    d[g] += __shfl_xor_sync(0xffffffffu, d[g], 1);
-    d[g] += __shfl_xor_sync(0xffffffffu, d[g], 2);
-    if (in && qd == 0) S[((size_t)m * H + kvh * G + g) * ldS + j] = bf16_round(d[g]);   // the product of the matmul is a bf16 value
-  }
-}
-
-template <int HD, int G>
-__global__ void __launch_bounds__(256) k_attn_dpv(const float* __restrict__ S, int ldS, RowMap map, int H, int Hkv, const int* __restrict__ block_table,
-                                                  int max_pages, int page, const bf16* __restrict__ vpages, float* __restrict__ part, int part_chunks,
-                                                  int* __restrict__ counters, bf16* __restrict__ out) {
-  extern __shared__ float sm[];                  // the row's scores, [G][ldS]
-  constexpr int NW = 8, PER = HD / 32, KPW = DP_KEYS / NW;
-  __shared__ float red[NW * G];
-  __shared__ float pc[G * DP_KEYS];              // probabilities of this CTA's keys
-  __shared__ int pgs[DP_KEYS];
-  __shared__ float po[NW * G * HD];
-  __shared__ int s_last;
-  pdl_launch_dependents();
-  pdl_wait();
-  const int m = blockIdx.x, kvh = blockIdx.y, chunk = blockIdx.z;
-  const int sq = map.seq[m], pos = map.pos[m];
-  const int j0 = chunk * DP_KEYS;
-  if (sq < 0) return;
-  if (pos == 0) {                                // only the zero slot: the output is zero
-    if (chunk == 0) for (int i = threadIdx.x; i < G * HD; i += blockDim.x) out[(size_t)m * H * HD + (size_t)(kvh * G) * HD + i] = from_f<bf16>(0.f);
-    return;
-  }
-  if (j0 >= pos) return;
-  const int n = min(DP_KEYS, pos - j0), nchunks = (pos + DP_KEYS - 1) / DP_KEYS;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x < DP_KEYS) pgs[threadIdx.x] = block_table[sq * max_pages + (j0 + min((int)threadIdx.x, n - 1)) / page];
-  for (int g = 0; g < G; ++g)
-    for (int j = threadIdx.x; j < pos; j += blockDim.x) sm[g * ldS + j] = S[((size_t)m * H + kvh * G + g) * ldS + j];
-  __syncthreads();
-  // value rows of this warp's keys, all requested before anything is computed
-  uint2 raw[KPW];
-#pragma unroll
-  for (int u = 0; u < KPW; ++u) {
-    const int jl = warp * KPW + u;
-    const int j = j0 + min(jl, n - 1);
-    const bf16* vr = vpages + (((size_t)pgs[min(jl, n - 1)] * Hkv + kvh) * page + (j % page)) * HD + lane * PER;
-    if (PER == 4) raw[u] = *reinterpret_cast<const uint2*>(vr);
-    else raw[u] = make_uint2(*reinterpret_cast<const uint32_t*>(vr), 0u);
-  }
-  // softmax statistics in f32 over all keys below pos and the zero slot at pos (score 0, value 0)
-  float mx[G], se[G];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    float v = 0.f;
-    for (int j = threadIdx.x; j < pos; j += blockDim.x) v = fmaxf(v, sm[g * ldS + j]);
-    v = warp_max(v);
-    if (lane == 0) red[warp * G + g] = v;
-  }
-  __syncthreads();
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    float v = 0.f;
-    for (int w = 0; w < NW; ++w) v = fmaxf(v, red[w * G + g]);
-    mx[g] = v;
-  }
-  __syncthreads();
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    float sum = 0.f;
-    for (int j = threadIdx.x; j < pos; j += blockDim.x) sum += expf(sm[g * ldS + j] - mx[g]);
-    sum = warp_sum(sum);
-    if (lane == 0) red[warp * G + g] = sum;
-  }
-  __syncthreads();
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    float sum = 0.f;
-    for (int w = 0; w < NW; ++w) sum += red[w * G + g];          // warp order: the same sum in every thread and CTA
-    se[g] = sum + expf(0.f - mx[g]);
-  }
-  for (int i = threadIdx.x; i < G * DP_KEYS; i += blockDim.x) {
-    const int g = i / DP_KEYS, jl = i % DP_KEYS;
-    float pv = 0.f;
-#pragma unroll
-    for (int gg = 0; gg < G; ++gg)
-      if (gg == g && jl < n) pv = bf16_round(expf(sm[gg * ldS + j0 + jl] - mx[gg]) / se[gg]);
-    pc[i] = pv;
-  }
-  __syncthreads();
-  float acc[G][PER];
-#pragma unroll
-  for (int g = 0; g < G; ++g)
-#pragma unroll
-    for (int e = 0; e < PER; ++e) acc[g][e] = 0.f;
-#pragma unroll
-  for (int u = 0; u < KPW; ++u) {
-    const int jl = warp * KPW + u;                 // keys beyond n carry probability 0
-    float vf[PER];
-    vf[0] = bf_lo(raw[u].x); vf[1] = bf_hi(raw[u].x);
-    if (PER == 4) { vf[2 % PER] = bf_lo(raw[u].y); vf[3 % PER] = bf_hi(raw[u].y); }
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const float p = pc[g * DP_KEYS + jl];
-#pragma unroll
-      for (int e = 0; e < PER; ++e) acc[g][e] = fmaf(p, vf[e], acc[g][e]);
-    }
-  }
-#pragma unroll
-  for (int g = 0; g < G; ++g)
-#pragma unroll
-    for (int e = 0; e < PER; ++e) po[((size_t)warp * G + g) * HD + lane * PER + e] = acc[g][e];
-  __syncthreads();
-  const size_t slot = (size_t)m * Hkv + kvh;
-  float* mine = part + (slot * part_chunks + chunk) * (G * HD);
-  for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
-    float v = 0.f;
-    for (int w = 0; w < NW; ++w) v += po[(size_t)w * G * HD + i];
-    if (nchunks == 1) out[(size_t)m * H * HD + (size_t)(kvh * G) * HD + i] = from_f<bf16>(v);
-    else mine[i] = v;
-  }
-  if (nchunks == 1) return;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const int seen = atomicAdd(counters + slot, 1);
-    s_last = (seen == nchunks - 1);
-    if (s_last) counters[slot] = 0;                // ready for the next launch (launches are serialised)
-  }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
-    float v = 0.f;
-    for (int ch = 0; ch < nchunks; ++ch) v += __ldcg(part + (slot * part_chunks + ch) * (G * HD) + i);   // chunk order
-    out[(size_t)m * H * HD + (size_t)(kvh * G) * HD + i] = from_f<bf16>(v);
-  }
-}
-
 // Sampler.argmax (src/core/math.zig:61-73): the first maximum wins, NaN never wins.  Two stages: ARG_CHUNKS blocks per
 // row each find the first maximum of a slice of the row (16-byte loads), then one warp per row picks the first maximum
 // among the slices; the winner becomes the row's next input token, is recorded at out[row][step] and the row's position
@@ -871,10 +682,6 @@ struct pcpb_rollout {
   long long graph_launches = 0;      // kernels in one replay of the decode-step graph
   float* gv_part = nullptr;          // split-K partial sums of the wide decode GEMV
   int* gv_cnt = nullptr;             // one arrival counter per 64-column block (back at 0 after every launch)
-  float *att_S = nullptr, *att_part = nullptr;   // decode attention: scores [16][H][max_seq], partial outputs per 64-key chunk
-  int* att_cnt = nullptr;            // arrival counter per (row, kv head), back at 0 after every launch
-  int attn_split = 1, attn_kcap = 0;     // PCPB_ROLLOUT_ATTN=rows: one CTA per (row, kv head) in the decode step too
-  int graph_kcap = 0;
   int gv_wide = 1, gv_slots = 592;        // PCPB_ROLLOUT_GEMV=narrow: the 8-column kernel; gv_slots: resident CTAs (4 per SM)
   int kmap_slices = 1;               // 1: every warp one contiguous K / 8 slice (default); 0: interleaved 128-byte pieces
   bool no_tc_prefill = false;             // PCPB_ROLLOUT_PREFILL=rows: the row kernel also for aligned prompts
@@ -1009,18 +816,9 @@ void attn_launch(pcpb_rollout* r, const bf16* q, RowMap map, int M, const bf16* 
   if (set_attr) {
     cudaFuncSetAttribute(k_attn_rows<HD, G, 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem(c, 1024));
     cudaFuncSetAttribute(k_attn_rows<HD, G, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem(c, 256));
-    cudaFuncSetAttribute(k_attn_dpv<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((size_t)G * c.max_seq * sizeof(float)));
     return;
   }
-  if (M <= ROWS && r->attn_split && r->attn_kcap > 0) {
-    const int kcap = std::min(r->attn_kcap, c.max_seq);
-    klaunch(r, k_attn_dscores<HD, G>, dim3(M, c.n_kv_head, (kcap + DS_KEYS - 1) / DS_KEYS), dim3(128), 0, q, map, c.n_head, c.n_kv_head,
-            (const int*)r->block_table, r->max_pages, c.page_tokens, kp, c.max_seq, r->att_S);
-    r->launches += 1;
-    klaunch(r, k_attn_dpv<HD, G>, dim3(M, c.n_kv_head, (kcap + DP_KEYS - 1) / DP_KEYS), dim3(256), (size_t)G * c.max_seq * sizeof(float),
-            (const float*)r->att_S, c.max_seq, map, c.n_head, c.n_kv_head, (const int*)r->block_table, r->max_pages, c.page_tokens, vp,
-            r->att_part, (c.max_seq + DP_KEYS - 1) / DP_KEYS, r->att_cnt, out);
-  } else if (M <= ROWS)
+  if (M <= ROWS)
     klaunch(r, k_attn_rows<HD, G, 1024>, dim3(M, c.n_kv_head), dim3(1024), attn_smem(c, 1024), q, map, c.n_head, c.n_kv_head,
             (const int*)r->block_table, r->max_pages, c.page_tokens, kp, vp, c.max_seq, out);
   else
@@ -1225,13 +1023,7 @@ int pcpb_rollout_create(int device, const pcpb_rollout_cfg* cfg, pcpb_rollout** 
   RCK(r, cudaMemset(r->tc_err, 0, 4));
   RA(r, r->arg_val, ROWS * ARG_CHUNKS * 4); RA(r, r->arg_idx, ROWS * ARG_CHUNKS * 4);
   {
-    const char* e = getenv("PCPB_ROLLOUT_ATTN");
-    r->attn_split = !(e && !strcmp(e, "rows"));
-    RA(r, r->att_S, (size_t)ROWS * c.n_head * c.max_seq * 4);
-    RA(r, r->att_part, (size_t)ROWS * c.n_kv_head * ((c.max_seq + DP_KEYS - 1) / DP_KEYS) * (c.n_head / c.n_kv_head) * c.head_dim * 4);
-    RA(r, r->att_cnt, (size_t)ROWS * c.n_kv_head * 4);
-    RCK(r, cudaMemset(r->att_cnt, 0, (size_t)ROWS * c.n_kv_head * 4));
-    e = getenv("PCPB_ROLLOUT_GEMV");
+    const char* e = getenv("PCPB_ROLLOUT_GEMV");
     r->gv_wide = !(e && !strcmp(e, "narrow"));
     {
       int sms = 148;
@@ -1355,10 +1147,6 @@ int pcpb_rollout_generate(pcpb_rollout* r, const int64_t* prompts, const int* pr
   }
   const int M = (int)rs.size();
   if (M > r->max_rows) return rfail(r, PCPB_E_TOO_LARGE, "more prompt tokens than max_batch * max_prompt");
-  int kcap = 0;                                                // upper bound of the positions a row of this call sees
-  for (int b = 0; b < batch; ++b) kcap = std::max(kcap, lens[b] + max_new_tokens);
-  kcap = (kcap + DP_KEYS - 1) / DP_KEYS * DP_KEYS;
-  r->attn_kcap = kcap;                                         // grid size of the split decode attention
   // pages: handed out round-robin over the sequences, so that no sequence's pages are contiguous
   std::vector<int> bt((size_t)c.max_batch * r->max_pages, 0);
   {
@@ -1404,8 +1192,7 @@ int pcpb_rollout_generate(pcpb_rollout* r, const int64_t* prompts, const int* pr
   RCK(r, cudaEventRecord(r->e1, st));
   // ---- decode: one graph launch per step ----
   if (max_new_tokens > 1) {
-    if (!r->graph || r->graph_batch != batch || r->graph_maxnew != max_new_tokens || r->graph_kcap != kcap) {
-
+    if (!r->graph || r->graph_batch != batch || r->graph_maxnew != max_new_tokens) {
       if (r->graph) { cudaGraphExecDestroy(r->graph); r->graph = nullptr; }
       cudaGraph_t gr = nullptr;
       RCK(r, cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
@@ -1419,7 +1206,7 @@ int pcpb_rollout_generate(pcpb_rollout* r, const int64_t* prompts, const int* pr
       ce = cudaGraphInstantiate(&r->graph, gr, 0);
       cudaGraphDestroy(gr);
       RCK(r, ce);
-      r->graph_batch = batch; r->graph_maxnew = max_new_tokens; r->graph_kcap = kcap;
+      r->graph_batch = batch; r->graph_maxnew = max_new_tokens;
     }
     for (int s = 1; s < max_new_tokens; ++s) RCK(r, cudaGraphLaunch(r->graph, st));
     r->launches += r->graph_launches * (max_new_tokens - 1);
