@@ -621,11 +621,11 @@ Plan plan_for(const GemmArgs& g) {
   if (((uintptr_t)g.A | (uintptr_t)g.B | (uintptr_t)g.C) & 15) return pl;
   if (g.R && ((uintptr_t)g.R & 15)) return pl;
   if (g.C2 && ((uintptr_t)g.C2 & 15)) return pl;
-  if (g.epi < EPI_STORE || g.epi > EPI_DGELU) return pl;
+  if (g.epi < EPI_STORE || g.epi > EPI_RAWF32) return pl;
   pl.bn = (g.N % 256 == 0) ? 256 : 128;
   pl.pair = pair_enabled() && g.M % 256 == 0 && g.N % 256 == 0 && g.K <= pair_max_k();
   const int tiles = (g.M / (pl.pair ? 256 : BM)) * (g.N / pl.bn), kblocks = g.K / BK;
-  pl.splits = (g.epi == EPI_WGRAD) ? pick_splits(tiles, kblocks, pl.pair ? 74 : 148) : 1;
+  pl.splits = (g.epi == EPI_WGRAD || g.epi == EPI_RAWF32) ? pick_splits(tiles, kblocks, pl.pair ? 74 : 148) : 1;
   // the f32 slabs must fit the caller's scratch
   while (pl.splits > 1 && (size_t)pl.splits * g.M * g.N * sizeof(float) > g.scratch_bytes) --pl.splits;
   pl.kb_per_split = (kblocks + pl.splits - 1) / pl.splits;
@@ -730,6 +730,7 @@ cudaError_t launch_gemm_tc(cudaStream_t st, const GemmArgs& g) {
   }
   p.epi = g.epi; p.C = g.C; p.ldc = g.ldc; p.R = g.R; p.C2 = g.C2; p.clip = g.clip; p.adj = g.adj; p.slab = nullptr; p.err = err;
   if (pl.splits > 1) p.slab = (float*)g.scratch;
+  else if (g.epi == EPI_RAWF32) { p.epi = -1; p.slab = (float*)g.C; }     // the accumulators as they are, like a split-K slab
   const int items = p.tiles_m * p.tiles_n * p.splits;
   const int grid = items < g_sm_count ? items : g_sm_count;
   if (pl.pair) {

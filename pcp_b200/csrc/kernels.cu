@@ -822,6 +822,58 @@ __global__ void __launch_bounds__(256) k_gemm_generic(GemmArgs g) {
   }
 }
 
+// ---- f32 operands as sums of three bf16 values, packed for one bf16 GEMM over 6 K (see kernels.h) ----
+template <bool ROWFAST>
+__global__ void __launch_bounds__(256) k_split3_pack(const float* __restrict__ src, long long s_row, long long s_k, int rows, int K,
+                                                     int bpat, __nv_bfloat16* __restrict__ dst) {
+  __shared__ float tile[32][33];                                // [row][k]
+  const int r0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
+  for (int i = threadIdx.y; i < 32; i += 8) {
+    if (ROWFAST) {                                              // rows are contiguous in memory: read along the rows
+      const int r = r0 + threadIdx.x, k = k0 + i;
+      tile[threadIdx.x][i] = (r < rows && k < K) ? src[(size_t)r * s_row + (size_t)k * s_k] : 0.f;
+    } else {
+      const int r = r0 + i, k = k0 + threadIdx.x;
+      tile[i][threadIdx.x] = (r < rows && k < K) ? src[(size_t)r * s_row + (size_t)k * s_k] : 0.f;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += 8) {
+    const int r = r0 + i, k = k0 + threadIdx.x;
+    if (r >= rows || k >= K) continue;
+    const float x = tile[i][threadIdx.x];
+    const __nv_bfloat16 p1 = __float2bfloat16_rn(x);
+    const float r1 = x - __bfloat162float(p1);
+    const __nv_bfloat16 p2 = __float2bfloat16_rn(r1);
+    const float r2 = r1 - __bfloat162float(p2);
+    const __nv_bfloat16 p3 = __float2bfloat16_rn(r2);
+    __nv_bfloat16* d = dst + (size_t)r * 6 * K + k;
+    if (bpat == 0) { d[0] = p1; d[K] = p1; d[2 * (size_t)K] = p2; d[3 * (size_t)K] = p1; d[4 * (size_t)K] = p2; d[5 * (size_t)K] = p3; }
+    else           { d[0] = p1; d[K] = p2; d[2 * (size_t)K] = p1; d[3 * (size_t)K] = p3; d[4 * (size_t)K] = p2; d[5 * (size_t)K] = p1; }
+  }
+}
+cudaError_t launch_split3_pack(cudaStream_t st, const float* src, long long s_row, long long s_k, int rows, int K, int b_pattern,
+                               void* dst_bf16) {
+  if (rows == 0 || K == 0) return cudaSuccess;
+  const dim3 grid(cdiv(K, 32), cdiv(rows, 32)), block(32, 8);
+  if (s_row == 1 && s_k != 1) k_split3_pack<true><<<grid, block, 0, st>>>(src, s_row, s_k, rows, K, b_pattern, (__nv_bfloat16*)dst_bf16);
+  else k_split3_pack<false><<<grid, block, 0, st>>>(src, s_row, s_k, rows, K, b_pattern, (__nv_bfloat16*)dst_bf16);
+  return cudaGetLastError();
+}
+__global__ void __launch_bounds__(256) k_gemm_epilogue_f32(GemmArgs g, const float* __restrict__ acc) {
+  const size_t mn = (size_t)g.M * g.N;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < mn; i += (size_t)gridDim.x * blockDim.x)
+    gemm_epilogue<float>(g, (int)(i / g.N), (int)(i % g.N), acc[i]);
+}
+cudaError_t launch_gemm_epilogue_f32(cudaStream_t st, const GemmArgs& g, const float* acc) {
+  if (g.M == 0 || g.N == 0) return cudaSuccess;
+  const size_t mn = (size_t)g.M * g.N;
+  unsigned blocks = (unsigned)((mn + 255) / 256);
+  if (blocks > 148u * 16) blocks = 148u * 16;
+  k_gemm_epilogue_f32<<<blocks, 256, 0, st>>>(g, acc);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_gemm_generic(cudaStream_t st, int dt, const GemmArgs& g) {
   if (g.M == 0 || g.N == 0) return cudaSuccess;
   dim3 grid(cdiv(g.N, 64), cdiv(g.M, 64));

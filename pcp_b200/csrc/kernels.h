@@ -21,6 +21,7 @@ enum GemmEpilogue : int {
   EPI_BIAS = 7,     // C = T(acc + bias[n])               (lm_head with bias; bias of model dtype in R, length N)
   EPI_GELU = 8,     // C = T(acc); C2 = gelu_tanh(C), every op of the activation rounded to T (two outputs)
   EPI_DGELU = 9,    // C = T(T(acc) * gelu_tanh'(U))      (backward of the tanh GELU, U in R)
+  EPI_RAWF32 = 10,  // tensor-core kernels only: Cf32 = acc, nothing else (the f32 models' split-operand path)
 };
 struct GemmArgs {
   const void* A; long long sam, sak;
@@ -38,6 +39,17 @@ struct GemmArgs {
   void* scratch = nullptr; size_t scratch_bytes = 0; int* err_word = nullptr;
 };
 cudaError_t launch_gemm_generic(cudaStream_t st, int dt, const GemmArgs& g);
+// f32 models on the bf16 tensor cores.  An f32 value is the sum of three bf16 values to 24 bits (x1 = bf16(x),
+// x2 = bf16(x - x1), x3 = bf16(x - x1 - x2)); a product a*b is then a1 b1 + a1 b2 + a2 b1 + a1 b3 + a2 b2 + a3 b1 up to
+// 2^-24 relative, every bf16 product exact in the f32 accumulator.  launch_split3_pack writes the operand src(row, k) =
+// src[row * s_row + k * s_k] as bf16 [rows, 6 K], the six K-long segments being (x1 x1 x2 x1 x2 x3) for the A operand
+// (b_pattern 0) and (x1 x2 x1 x3 x2 x1) for the B operand (b_pattern 1), so that ONE bf16 GEMM over 6 K sums the six
+// products.  launch_gemm_epilogue_f32 then applies g's epilogue (the generic kernel's, element by element) to the f32
+// result acc [M, N].  Non-finite inputs do not survive the split (Inf - Inf): the caller keeps such cases on the
+// generic kernel only in so far as its shapes are small; a non-finite operand gives NaN here.
+cudaError_t launch_split3_pack(cudaStream_t st, const float* src, long long s_row, long long s_k, int rows, int K, int b_pattern,
+                               void* dst_bf16);
+cudaError_t launch_gemm_epilogue_f32(cudaStream_t st, const GemmArgs& g, const float* acc);
 
 // ---- elementwise / normalisation -------------------------------------------------------------
 cudaError_t launch_convert_f32(cudaStream_t st, int dt, const float* in, void* out, size_t n);

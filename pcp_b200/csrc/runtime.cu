@@ -173,6 +173,19 @@ int build_workspace(pcpb_backend* b) {
     for (auto& s : shapes) { size_t x = gemm_tc_scratch_wanted(s[0], s[1], Mi); if (x > want) want = x; }
     if (want) { WS(b, w.tc_scratch, want); w.tc_scratch_bytes = want; }
   }
+  // f32 models: buffers of the split-operand tensor-core path (gemm()), sized for the widest layer GEMM of the model;
+  // PCPB_F32_TC=0 keeps f32 models on the SIMT kernel
+  {
+    const char* e = getenv("PCPB_F32_TC");
+    const long long wide = std::max<long long>(std::max<long long>(F, d + 2 * dkv), d);
+    const size_t ab = (size_t)M * wide * 12, cc = (size_t)M * wide * 4;
+    if (c.dtype == DT_F32 && !(e && e[0] == '0') && M % 128 == 0 && d % 128 == 0 && 2 * ab + cc <= ((size_t)24 << 30)) {
+      WS(b, w.pk_a, ab); WS(b, w.pk_b, ab); WS(b, w.pk_c, cc);
+      w.pk_ab_bytes = ab; w.pk_c_bytes = cc;
+      const size_t want = (size_t)64 << 20;                     // split-K slabs of the narrow (weight-gradient) products
+      WS(b, w.tc_scratch, want); w.tc_scratch_bytes = want;
+    }
+  }
   WS(b, w.tc_err, sizeof(int));
   CK(b, cudaMemset(w.tc_err, 0, sizeof(int)));
   w.ready = true;
@@ -228,6 +241,23 @@ int gemm(pcpb_backend* b, GemmArgs g) {
     }
     KL(b, gemm_tc_launches(g), launch_gemm_tc(b->stream, g));
     return PCPB_OK;
+  }
+  // f32 model, shapes of the tensor-core kernel: operands as sums of three bf16 pieces, one bf16 GEMM over 6 K with the
+  // exact products accumulated in f32, then the generic kernel's epilogue on the f32 result (kernels.h)
+  if (!b->force_generic && b->cfg.dtype == DT_F32 && b->ws.pk_a && g.M % 128 == 0 && g.N % 128 == 0 && g.K % 64 == 0 &&
+      (size_t)g.M * g.K * 12 <= b->ws.pk_ab_bytes && (size_t)g.N * g.K * 12 <= b->ws.pk_ab_bytes &&
+      (size_t)g.M * g.N * 4 <= b->ws.pk_c_bytes) {
+    GemmArgs t;
+    t.A = b->ws.pk_a; t.sam = 6LL * g.K; t.sak = 1; t.B = b->ws.pk_b; t.sbk = 1; t.sbn = 6LL * g.K;
+    t.C = b->ws.pk_c; t.ldc = g.N; t.R = nullptr; t.C2 = nullptr; t.M = g.M; t.N = g.N; t.K = 6 * g.K; t.epi = EPI_RAWF32; t.clip = 0.f;
+    t.scratch = b->ws.tc_scratch; t.scratch_bytes = b->ws.tc_scratch_bytes; t.err_word = b->ws.tc_err;
+    if (gemm_tc_supported(t)) {
+      KL(b, 1, launch_split3_pack(b->stream, (const float*)g.A, g.sam, g.sak, g.M, g.K, 0, b->ws.pk_a));
+      KL(b, 1, launch_split3_pack(b->stream, (const float*)g.B, g.sbn, g.sbk, g.N, g.K, 1, b->ws.pk_b));
+      KL(b, gemm_tc_launches(t), launch_gemm_tc(b->stream, t));
+      KL(b, 1, launch_gemm_epilogue_f32(b->stream, g, b->ws.pk_c));
+      return PCPB_OK;
+    }
   }
   KL(b, 1, launch_gemm_generic(b->stream, b->cfg.dtype, g));
   return PCPB_OK;

@@ -148,3 +148,78 @@ def test_tc_gemm_split_k(be):
     np.testing.assert_allclose(out, want, rtol=2 ** -6, atol=0.5)
     out_b, _, _ = _run(be, "tn", M, N, K, epi=4, path=2, seed=11)
     np.testing.assert_array_equal(out, out_b)        # deterministic: no atomics in the reduction
+
+
+# ---- f32 models on the tensor cores: operands split into three bf16 pieces, six products in one bf16 GEMM --------------
+F32_TC_MODEL = dict(vocab=512, d_model=256, n_layer=1, n_head=2, n_kv_head=2, seq_len=128, batch=2, dtype="f32")
+
+
+@pytest.fixture(scope="module")
+def be32():
+    b = Backend(0)
+    b.load_session(nanochat_forward_mlir(NanochatConfig(**F32_TC_MODEL)))
+    yield b
+    b.close()
+
+
+def _run32(be, layout, M, N, K, epi, path, seed=0, scale=1.0):
+    rng = np.random.default_rng(seed)
+    a = (rng.standard_normal((M, K)) * scale).astype(np.float32)
+    bm = rng.standard_normal((K, N)).astype(np.float32)
+    if layout == "nt":
+        ah, bh, sa, sb = a, bm.T.copy(), (K, 1), (1, K)
+    elif layout == "nn":
+        ah, bh, sa, sb = a, bm, (K, 1), (N, 1)
+    else:
+        ah, bh, sa, sb = a.T.copy(), bm, (1, M), (N, 1)
+    ref = a.astype(np.float64) @ bm.astype(np.float64)
+    A = be.move_to_device(ah, ah.shape, F32)
+    B = be.move_to_device(bh, bh.shape, F32)
+    R = None
+    rv = None
+    if epi == 1:
+        rv = rng.standard_normal((M, N)).astype(np.float32)
+        R = be.move_to_device(rv, (M, N), F32)
+    if epi == 7:
+        rv = rng.standard_normal((N,)).astype(np.float32)
+        R = be.move_to_device(rv, (N,), F32)
+    Cb = be.allocate_zeros_device((M, N), F32)
+    be.op_gemm(A, sa[0], sa[1], B, sb[0], sb[1], Cb, N, M, N, K, epilogue=epi, R=R, path=path)
+    out = be.read_to_host(Cb, F32, (M, N)).astype(np.float64)
+    for x in (A, B, Cb, R):
+        if x is not None:
+            x.release()
+    if epi == 1:
+        ref = ref + rv
+    elif epi == 7:
+        ref = ref + rv[None, :]
+    elif epi == 4:
+        ref = np.clip(ref, -100, 100)
+    return out, ref
+
+
+@pytest.mark.parametrize("layout", LAYOUTS)
+@pytest.mark.parametrize("shape", [(256, 256, 512), (128, 128, 64), (256, 1024, 256), (128, 128, 2048)])
+def test_f32_split_gemm_is_f32_accurate(be32, layout, shape):
+    """path 0 = what the f32 models' GEMMs take: for these shapes the split-operand tensor-core path.  The result has to
+    be as close to the float64 product as an f32 FMA chain is (the SIMT kernel, path 1), far inside the 1e-4 of the f32
+    parity tests; a single bf16 product would be off by 1e-2."""
+    M, N, K = shape
+    n0 = be32.launch_count
+    out, ref = _run32(be32, layout, M, N, K, 0, path=0)
+    assert be32.launch_count - n0 >= 4                       # two packs, the GEMM (+ its split-K reduction), the epilogue
+    n0 = be32.launch_count
+    gen, _ = _run32(be32, layout, M, N, K, 0, path=1)
+    assert be32.launch_count - n0 == 1
+    scale = np.sqrt(K)
+    assert np.abs(gen - ref).max() <= 4e-6 * scale
+    assert np.abs(out - ref).max() <= 4e-6 * scale
+    assert np.abs(out - gen).max() <= 4e-6 * scale
+
+
+@pytest.mark.parametrize("epi", [1, 4, 7])
+def test_f32_split_gemm_epilogues(be32, epi):
+    out, ref = _run32(be32, "nt", 256, 256, 256, epi, path=0, seed=3, scale=8.0 if epi == 4 else 1.0)
+    assert np.abs(out - ref).max() <= 1e-4 if epi == 4 else np.abs(out - ref).max() <= 7e-5
+    if epi == 4:
+        assert (np.abs(out) <= 100).all() and (np.abs(out) == 100).any()           # the clamp was active
