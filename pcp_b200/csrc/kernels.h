@@ -93,6 +93,11 @@ struct AttnArgs {
   float* dkv_acc;       // [M, 2*dkv] f32 scratch: dk then dv, zeroed by the launcher
 };
 cudaError_t launch_attn_fwd_generic(cudaStream_t st, int dt, const AttnArgs& a);
+// f32 models with 64-wide heads and T a multiple of 64: tiled SIMT kernels, backward without atomics (attn_f32.cu).
+// drow: f32 scratch of at least B * H * T elements (the callers pass dkv_acc, which these kernels do not need).
+bool attn_f32_supported(int dt, const AttnArgs& a);
+cudaError_t launch_attn_f32_fwd(cudaStream_t st, const AttnArgs& a);
+cudaError_t launch_attn_f32_bwd(cudaStream_t st, const AttnArgs& a, float* drow);     // 3 kernels
 cudaError_t launch_attn_bwd_generic(cudaStream_t st, int dt, const AttnArgs& a);
 
 // ---- nanoGPT family ---------------------------------------------------------------------------------
@@ -128,6 +133,7 @@ cudaError_t adj_status_fetch_kernels_gpt(cudaStream_t st, int* out, bool clear);
 cudaError_t adj_status_fetch_gemm_tc(cudaStream_t st, int* out, bool clear);
 cudaError_t adj_status_fetch_attn_tc(cudaStream_t st, int* out, bool clear);
 cudaError_t adj_status_fetch_attn_flash(cudaStream_t st, int* out, bool clear);
+cudaError_t adj_status_fetch_attn_f32(cudaStream_t st, int* out, bool clear);
 cudaError_t launch_loss_finalize(cudaStream_t st, const float* rowloss, int M, const float* count, float* loss);
 
 // ---- optimiser -----------------------------------------------------------------------------------

@@ -320,7 +320,8 @@ int forward_backward(pcpb_backend* b, const void* wts, const long long* ids, con
       AttnArgs at{};
       at.qkn = a.qkn; at.qkv = a.qkv; at.o = a.o; at.mrow = a.mrow; at.lrow = a.lrow;
       at.B = (int)c.B; at.T = Tn; at.H = H; at.Hkv = Hkv; at.hd = hd; at.scale = scale;
-      KL(b, 1, launch_attn_fwd_generic(st, dt, at));
+      if (!b->force_generic && attn_f32_supported(dt, at)) KL(b, 1, launch_attn_f32_fwd(st, at));
+      else KL(b, 1, launch_attn_fwd_generic(st, dt, at));
     }
     G(b, a.o, d, 1, W(pq + 3), 1, d, a.xmid, d, M, d, d, EPI_RESID, w.xs[l]);
     KL(b, 1, launch_rmsnorm_fwd(st, dt, a.xmid, M, d, a.h2, a.t2));
@@ -367,7 +368,8 @@ int forward_backward(pcpb_backend* b, const void* wts, const long long* ids, con
       at.qkn = a.qkn; at.qkv = a.qkv; at.o = a.o; at.mrow = a.mrow; at.lrow = a.lrow;
       at.B = (int)c.B; at.T = Tn; at.H = H; at.Hkv = Hkv; at.hd = hd; at.scale = scale;
       at.dout = w.dout; at.dqkn = w.dqkn; at.dqkv = w.dqkv; at.dkv_acc = w.dkv_acc;
-      KL(b, 3, launch_attn_bwd_generic(st, dt, at));
+      if (!b->force_generic && attn_f32_supported(dt, at)) KL(b, 3, launch_attn_f32_bwd(st, at, w.dkv_acc));
+      else KL(b, 3, launch_attn_bwd_generic(st, dt, at));
     }
     KL(b, 1, launch_rope_qknorm_bwd(st, dt, a.qkv, w.dqkn, a.tq, w.d_cos, w.d_sin, M, Tn, H, Hkv, hd, w.dqkv));
     G(b, w.dqkv, 1, wq, a.h1, d, 1, GR(pq), d, wq, d, M, EPI_WGRAD);                // d c_q,c_k,c_v (contiguous)
@@ -395,7 +397,8 @@ int attention_fwd(pcpb_backend* b, LayerActs& a, float scale) {
   AttnArgs at{};
   at.qkn = a.qkn; at.qkv = a.qkv; at.o = a.o; at.mrow = a.mrow; at.lrow = a.lrow;
   at.B = fa.B; at.T = fa.T; at.H = fa.H; at.Hkv = fa.Hkv; at.hd = fa.hd; at.scale = scale;
-  KL(b, 1, launch_attn_fwd_generic(b->stream, dt, at));
+  if (!b->force_generic && attn_f32_supported(dt, at)) KL(b, 1, launch_attn_f32_fwd(b->stream, at));
+  else KL(b, 1, launch_attn_fwd_generic(b->stream, dt, at));
   return PCPB_OK;
 }
 int attention_bwd(pcpb_backend* b, LayerActs& a, float scale) {
@@ -414,7 +417,8 @@ int attention_bwd(pcpb_backend* b, LayerActs& a, float scale) {
   at.qkn = a.qkn; at.qkv = a.qkv; at.o = a.o; at.mrow = a.mrow; at.lrow = a.lrow;
   at.B = fa.B; at.T = fa.T; at.H = fa.H; at.Hkv = fa.Hkv; at.hd = fa.hd; at.scale = scale;
   at.dout = w.dout; at.dqkn = w.dqkn; at.dqkv = w.dqkv; at.dkv_acc = w.dkv_acc;
-  KL(b, 3, launch_attn_bwd_generic(b->stream, dt, at));
+  if (!b->force_generic && attn_f32_supported(dt, at)) KL(b, 3, launch_attn_f32_bwd(b->stream, at, w.dkv_acc));
+  else KL(b, 3, launch_attn_bwd_generic(b->stream, dt, at));
   return PCPB_OK;
 }
 
@@ -717,7 +721,8 @@ int pcpb_adjoint_status(pcpb_backend* b, int* flags, int clear) {
   DeviceGuard g(b->device);
   int total = 0, one = 0;
   cudaError_t (*fetch[])(cudaStream_t, int*, bool) = {adj_status_fetch_kernels, adj_status_fetch_kernels_gpt, adj_status_fetch_gemm_tc,
-                                                      adj_status_fetch_attn_tc, adj_status_fetch_attn_flash};
+                                                      adj_status_fetch_attn_tc, adj_status_fetch_attn_flash,
+                                                      adj_status_fetch_attn_f32};
   for (auto f : fetch) {
     one = 0;
     CK(b, f(b->stream, &one, clear != 0));

@@ -23,6 +23,9 @@ HD64_GQA_BF16 = dict(vocab=512, d_model=256, n_layer=2, n_head=4, n_kv_head=2, s
 # scatter under Zipf tokens.  The oracle needs about two minutes and 25 GB of host memory for it.
 D20_SHAPES_BF16 = dict(vocab=65536, d_model=1280, n_layer=2, n_head=10, n_kv_head=10, seq_len=2048, batch=1, dtype="bf16")
 HD128_F32 = dict(vocab=512, d_model=256, n_layer=1, n_head=2, n_kv_head=1, seq_len=64, batch=2, dtype="f32")
+# f32 with 64-wide heads, T a multiple of 64 and GEMM dimensions that are multiples of 128: the tiled f32 attention
+# kernels (two query tiles per head, grouped-query heads) and the split-operand tensor-core GEMM path
+HD64_F32 = dict(vocab=512, d_model=256, n_layer=2, n_head=4, n_kv_head=2, seq_len=128, batch=2, dtype="f32")
 
 
 GPT_SMALL_F32 = dict(vocab=65, d_model=64, n_layer=2, n_head=4, seq_len=32, batch=8, dtype="f32")
@@ -34,6 +37,9 @@ GPT_GELU_F32 = dict(GPT_SMALL_F32, activation="gelu")
 GPT_GELU_BF16 = dict(vocab=256, d_model=256, n_layer=2, n_head=4, seq_len=128, batch=4, dtype="bf16", activation="gelu")
 # d_model a multiple of 256: the vectorised LayerNorm backward, f32
 GPT_D256_F32 = dict(vocab=97, d_model=256, n_layer=1, n_head=4, seq_len=32, batch=4, dtype="f32")
+# nanoGPT-small's kernel shapes in small (BASELINE config 1: fp32, 64-wide heads): tiled f32 attention over three query
+# tiles, split-operand tensor-core GEMMs, GELU
+GPT_HD64_F32 = dict(vocab=65, d_model=128, n_layer=2, n_head=2, seq_len=192, batch=2, dtype="f32", activation="gelu")
 
 
 def make_model(cfgd):
