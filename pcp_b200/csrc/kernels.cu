@@ -848,8 +848,9 @@ __global__ void __launch_bounds__(256) k_split3_pack(const float* __restrict__ s
     const float r2 = r1 - __bfloat162float(p2);
     const __nv_bfloat16 p3 = __float2bfloat16_rn(r2);
     __nv_bfloat16* d = dst + (size_t)r * 6 * K + k;
-    if (bpat == 0) { d[0] = p1; d[K] = p1; d[2 * (size_t)K] = p2; d[3 * (size_t)K] = p1; d[4 * (size_t)K] = p2; d[5 * (size_t)K] = p3; }
-    else           { d[0] = p1; d[K] = p2; d[2 * (size_t)K] = p1; d[3 * (size_t)K] = p3; d[4 * (size_t)K] = p2; d[5 * (size_t)K] = p1; }
+    // smallest products first, a1 b1 last (see kernels.h)
+    if (bpat == 0) { d[0] = p3; d[K] = p2; d[2 * (size_t)K] = p1; d[3 * (size_t)K] = p2; d[4 * (size_t)K] = p1; d[5 * (size_t)K] = p1; }
+    else           { d[0] = p1; d[K] = p2; d[2 * (size_t)K] = p3; d[3 * (size_t)K] = p1; d[4 * (size_t)K] = p2; d[5 * (size_t)K] = p1; }
   }
 }
 cudaError_t launch_split3_pack(cudaStream_t st, const float* src, long long s_row, long long s_k, int rows, int K, int b_pattern,
