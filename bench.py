@@ -656,6 +656,19 @@ def run_ours(args):
                            "decode_step_ms": r["decode_step_ms"], "gpu_launches": r["launches"], "roofline": r["roofline"]})
         except Exception as e:
             others.append({"workload": "qwen3_rollout", "error": str(e)})
+        if not args.no_cpu_baseline:
+            # BASELINE config 1 fits the host whole: two seeded inner steps of it on the CPU oracle and on the GPU (its f32
+            # GEMMs run on the tensor cores through the three-piece split, its attention on the tiled f32 kernels)
+            for o in others:
+                if o.get("workload") == "c1" and "error" not in o:
+                    try:
+                        c1 = WORKLOADS["c1"]
+                        rc = cpu_oracle_run(c1, "c1", steps=2, seq=c1["seq_len"], batch=c1["batch"])
+                        o["parity"] = parity_object(gpu_losses_on_sample(c1, "c1", 2, c1["seq_len"], c1["batch"], local),
+                                                    rc["losses"], "f32")
+                        o["cpu_oracle_tokens_per_s_same_config"] = rc["tokens_per_s"]
+                    except Exception as e:
+                        o["parity"] = {"error": str(e)}
         line["other_configs"] = others
     if world == 1 and not args.no_cpu_baseline:
         try:
