@@ -1,4 +1,4 @@
-// Causal attention for bf16 models with head_dim 128 or 64, tiled so that the [T,T] score matrix never leaves
+// Causal attention for bf16 models with head_dim 128, 64, 32 or 16, tiled so that the [T,T] score matrix never leaves
 // the SM (forward) and is recomputed per tile (backward).  Tensor-core path: mma.sync m16n8k16 bf16 with
 // ldmatrix-fed fragments; shared-memory tiles are filled with cp.async and XOR-swizzled per 16-byte chunk.
 //
@@ -24,17 +24,23 @@ namespace pcpb {
 
 namespace {
 
-// Every kernel and tile helper below is a template over the head dim HD (128 or 64): a tile row is HD bf16 =
-// HD/8 chunks of 16 bytes, the contraction over the head dim takes HD/16 mma k-steps and an output row has HD/8
-// n-tiles of 8 columns.
+// Every kernel and tile helper below is a template over the head dim HD (128, 64, 32 or 16 — the shipped nanochat
+// graphs have 32-wide heads): a tile row is HD bf16 = HD/8 chunks of 16 bytes, the contraction over the head dim takes
+// HD/16 mma k-steps and an output row has HD/8 n-tiles of 8 columns.
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-// address of 16-byte chunk `chunk` (0..HD/8-1) of row `row` in a [rows][HD] bf16 tile
+// address of 16-byte chunk `chunk` (0..HD/8-1) of row `row` in a [rows][HD] bf16 tile.  The chunk index is XORed with
+// a function of the row such that the 8 rows an ldmatrix phase reads (same chunk, consecutive rows) fall on the 8
+// different 16-byte slots of a 128-byte bank line: rows of 128 bytes or more use the row's low three bits; shorter rows
+// share a line (2 rows of 64 bytes, 4 of 32), which already separates them, and use the remaining row bits.
 template <int HD>
 __device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk) {
-  return base + (uint32_t)row * (HD * 2) + (uint32_t)((chunk ^ (row & 7)) << 4);
+  constexpr int CPR = HD / 8;                                  // chunks per row
+  constexpr int RPL = CPR >= 8 ? 1 : 8 / CPR;                  // rows per 128-byte line
+  constexpr int MASK = (CPR >= 8 ? 8 : CPR) - 1;
+  return base + (uint32_t)row * (HD * 2) + (uint32_t)((chunk ^ ((row / RPL) & MASK)) << 4);
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -61,10 +67,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int HD, int ROWS, int THREADS>
 __device__ __forceinline__ void load_tile(uint32_t sbase, const bf16* __restrict__ g, long long pitch) {
   constexpr int CPR = HD / 8;                                  // 16-byte chunks per row
-  static_assert((ROWS * CPR) % THREADS == 0, "tile does not divide over the threads");
 #pragma unroll
-  for (int i = 0; i < ROWS * CPR / THREADS; ++i) {
+  for (int i = 0; i < (ROWS * CPR + THREADS - 1) / THREADS; ++i) {
     const int idx = threadIdx.x + i * THREADS;
+    if ((ROWS * CPR) % THREADS != 0 && idx >= ROWS * CPR) break;
     const int row = idx / CPR, chunk = idx % CPR;
     cp_async16(tile_addr<HD>(sbase, row, chunk), g + (long long)row * pitch + chunk * 8);
   }
@@ -255,7 +261,7 @@ __global__ void k_flash_prep(FlashArgs a) {
       const uint2 z = *reinterpret_cast<const uint2*>(vp + lane * 4);
       n_v = bf_lo(z.x) * bf_lo(z.x) + bf_hi(z.x) * bf_hi(z.x) + bf_lo(z.y) * bf_lo(z.y) + bf_hi(z.y) * bf_hi(z.y);
     }
-  } else {
+  } else if (HD == 64) {
     const uint32_t x = *reinterpret_cast<const uint32_t*>(op + lane * 2), y = *reinterpret_cast<const uint32_t*>(dp + lane * 2);
     acc = bf_lo(x) * bf_lo(y) + bf_hi(x) * bf_hi(y);
     n_do = bf_lo(y) * bf_lo(y) + bf_hi(y) * bf_hi(y);
@@ -263,6 +269,11 @@ __global__ void k_flash_prep(FlashArgs a) {
       const uint32_t z = *reinterpret_cast<const uint32_t*>(vp + lane * 2);
       n_v = bf_lo(z) * bf_lo(z) + bf_hi(z) * bf_hi(z);
     }
+  } else if (lane < HD) {                                      // 32 or 16: one element per lane
+    const float x = to_f(op[lane]), y = to_f(dp[lane]);
+    acc = x * y;
+    n_do = y * y;
+    if (h < a.Hkv) { const float z = to_f(vp[lane]); n_v = z * z; }
   }
   acc = warp_sum(acc); n_do = warp_sum(n_do); n_v = warp_sum(n_v);
   if (lane == 0) {
@@ -565,16 +576,26 @@ template <int HD> cudaError_t flash_bwd(cudaStream_t st, const FlashArgs& a) {
 }  // namespace
 
 bool flash_supported(const FlashArgs& a) {
-  return (a.hd == 128 || a.hd == 64) && a.T % 128 == 0 && a.T >= 128 && a.H % a.Hkv == 0 && a.B > 0 &&
+  return (a.hd == 128 || a.hd == 64 || a.hd == 32 || a.hd == 16) && a.T % 128 == 0 && a.T >= 128 && a.H % a.Hkv == 0 && a.B > 0 &&
          ((a.H * a.hd) % 8 == 0) && (long long)a.B * a.H <= 65535 && (long long)a.B * a.Hkv <= 65535;
 }
 
 cudaError_t launch_flash_fwd(cudaStream_t st, const FlashArgs& a) {
-  return a.hd == 128 ? flash_fwd<128>(st, a) : flash_fwd<64>(st, a);
+  switch (a.hd) {
+    case 128: return flash_fwd<128>(st, a);
+    case 64: return flash_fwd<64>(st, a);
+    case 32: return flash_fwd<32>(st, a);
+    default: return flash_fwd<16>(st, a);
+  }
 }
 
 cudaError_t launch_flash_bwd(cudaStream_t st, const FlashArgs& a) {
-  return a.hd == 128 ? flash_bwd<128>(st, a) : flash_bwd<64>(st, a);
+  switch (a.hd) {
+    case 128: return flash_bwd<128>(st, a);
+    case 64: return flash_bwd<64>(st, a);
+    case 32: return flash_bwd<32>(st, a);
+    default: return flash_bwd<16>(st, a);
+  }
 }
 
 cudaError_t adj_status_fetch_attn_flash(cudaStream_t st, int* out, bool clear) { return adj_status_fetch_tu(st, out, clear); }

@@ -1,4 +1,4 @@
-// Tiled causal attention (bf16, head_dim 128 or 64), forward and backward.
+// Tiled causal attention (bf16, head_dim 128, 64, 32 or 16), forward and backward.
 #pragma once
 #include <cuda_runtime.h>
 

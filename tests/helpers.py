@@ -17,6 +17,10 @@ HD128_GQA_BF16 = dict(vocab=512, d_model=512, n_layer=1, n_head=4, n_kv_head=2, 
 HD128_MANY_BF16 = dict(vocab=512, d_model=256, n_layer=1, n_head=2, n_kv_head=2, seq_len=256, batch=40, dtype="bf16")
 # head dim 64 (what the nanoGPT configurations of the baseline use): the mma.sync tiled attention kernels, GQA
 HD64_GQA_BF16 = dict(vocab=512, d_model=256, n_layer=2, n_head=4, n_kv_head=2, seq_len=256, batch=2, dtype="bf16")
+# 32-wide heads, 8 query / 4 kv heads: the head layout of the shipped models/nanochat_d8_b*_t2048_bf16.mlir graphs; and
+# 16-wide heads (the shipped f32 test graphs' layout, here in bf16)
+HD32_GQA_BF16 = dict(vocab=512, d_model=256, n_layer=2, n_head=8, n_kv_head=4, seq_len=256, batch=2, dtype="bf16")
+HD16_BF16 = dict(vocab=512, d_model=64, n_layer=1, n_head=4, n_kv_head=4, seq_len=128, batch=2, dtype="bf16")
 # The kernel shapes of BASELINE config 3 (nanochat d20: d_model 1280, 10 heads x 128, T = 2048, vocabulary 65536) at two
 # layers and batch 1: the two-CTA GEMM at K = 1280 / 5120 and N = 65536 with grouped tile order and split-K, the
 # tcgen05 attention with 16 row tiles per head, the loss kernel over 65536-wide rows, the vector-reduction embedding

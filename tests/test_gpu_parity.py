@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import (D20_SHAPES_BF16, GPT_D256_F32, GPT_HD64_F32, HD64_F32, GPT_GELU_BF16, GPT_GELU_F32, GPT_ODD_F32, GPT_SMALL_BF16, GPT_SMALL_F32, GQA_F32, HD128_BF16, HD128_F32, HD128_GQA_BF16, HD128_MANY_BF16, HD64_GQA_BF16, make_model, SMALL_BF16, SMALL_F32, bf16_bits_to_f32, f32_to_bf16_trunc_bits,
+from helpers import (D20_SHAPES_BF16, GPT_D256_F32, GPT_HD64_F32, HD64_F32, GPT_GELU_BF16, GPT_GELU_F32, GPT_ODD_F32, GPT_SMALL_BF16, GPT_SMALL_F32, GQA_F32, HD128_BF16, HD128_F32, HD128_GQA_BF16, HD128_MANY_BF16, HD16_BF16, HD32_GQA_BF16, HD64_GQA_BF16, make_model, SMALL_BF16, SMALL_F32, bf16_bits_to_f32, f32_to_bf16_trunc_bits,
                      flat, rel_err, seeded_params, split, tokens_for)
 from oracle.loader import FifoU16
 from oracle.optim import AdamConf, NesterovConf, adamw_update
@@ -90,10 +90,11 @@ def test_d20_kernel_shapes_match_oracle():
     print(f"d20 shapes: loss {loss:.6f} vs {loss_ref:.6f}; worst max-rel {worst:.3e}, worst rel-L2 {worst_l2:.3e}")
 
 
-@pytest.mark.parametrize("cfgd", [HD128_BF16, HD128_GQA_BF16, HD128_MANY_BF16, HD64_GQA_BF16])
+@pytest.mark.parametrize("cfgd", [HD128_BF16, HD128_GQA_BF16, HD128_MANY_BF16, HD64_GQA_BF16, HD32_GQA_BF16, HD16_BF16])
 def test_attention_paths_agree(cfgd, monkeypatch):
     """The three attention implementations (tcgen05 / tensor memory, mma.sync, generic) against the oracle and against
-    each other on head_dim-128 bf16 models, GQA included; at head dim 64 the default is the mma.sync kernel."""
+    each other on head_dim-128 bf16 models, GQA included; at head dims 64, 32 and 16 the default is the mma.sync kernel
+    (32: the head width of the shipped nanochat d4 / d8 graphs)."""
     cfg = NanochatConfig(**cfgd)
     text = nanochat_forward_mlir(cfg)
     params = seeded_params(cfg, seed=3, std=0.05)
