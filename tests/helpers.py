@@ -30,6 +30,9 @@ HD128_F32 = dict(vocab=512, d_model=256, n_layer=1, n_head=2, n_kv_head=1, seq_l
 # f32 with 64-wide heads, T a multiple of 64 and GEMM dimensions that are multiples of 128: the tiled f32 attention
 # kernels (two query tiles per head, grouped-query heads) and the split-operand tensor-core GEMM path
 HD64_F32 = dict(vocab=512, d_model=256, n_layer=2, n_head=4, n_kv_head=2, seq_len=128, batch=2, dtype="f32")
+# the other head widths of the tiled f32 attention: 32 (grouped-query) and 16 (the shipped f32 nanochat graphs' widths)
+HD32_F32 = dict(vocab=512, d_model=128, n_layer=1, n_head=4, n_kv_head=2, seq_len=128, batch=2, dtype="f32")
+HD16_F32 = dict(vocab=256, d_model=64, n_layer=1, n_head=4, n_kv_head=4, seq_len=64, batch=2, dtype="f32")
 
 
 GPT_SMALL_F32 = dict(vocab=65, d_model=64, n_layer=2, n_head=4, seq_len=32, batch=8, dtype="f32")
@@ -43,6 +46,8 @@ GPT_GELU_BF16 = dict(vocab=256, d_model=256, n_layer=2, n_head=4, seq_len=128, b
 GPT_D256_F32 = dict(vocab=97, d_model=256, n_layer=1, n_head=4, seq_len=32, batch=4, dtype="f32")
 # nanoGPT-small's kernel shapes in small (BASELINE config 1: fp32, 64-wide heads): tiled f32 attention over three query
 # tiles, split-operand tensor-core GEMMs, GELU
+# the shipped models/nanogpt_medium.mlir layout in small: f32, 8 heads x 32
+GPT_HD32_F32 = dict(vocab=256, d_model=256, n_layer=1, n_head=8, seq_len=128, batch=2, dtype="f32")
 GPT_HD64_F32 = dict(vocab=65, d_model=128, n_layer=2, n_head=2, seq_len=192, batch=2, dtype="f32", activation="gelu")
 
 

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import (D20_SHAPES_BF16, GPT_D256_F32, GPT_HD64_F32, HD64_F32, GPT_GELU_BF16, GPT_GELU_F32, GPT_ODD_F32, GPT_SMALL_BF16, GPT_SMALL_F32, GQA_F32, HD128_BF16, HD128_F32, HD128_GQA_BF16, HD128_MANY_BF16, HD16_BF16, HD32_GQA_BF16, HD64_GQA_BF16, make_model, SMALL_BF16, SMALL_F32, bf16_bits_to_f32, f32_to_bf16_trunc_bits,
+from helpers import (D20_SHAPES_BF16, GPT_D256_F32, GPT_HD32_F32, GPT_HD64_F32, HD16_F32, HD32_F32, HD64_F32, GPT_GELU_BF16, GPT_GELU_F32, GPT_ODD_F32, GPT_SMALL_BF16, GPT_SMALL_F32, GQA_F32, HD128_BF16, HD128_F32, HD128_GQA_BF16, HD128_MANY_BF16, HD16_BF16, HD32_GQA_BF16, HD64_GQA_BF16, make_model, SMALL_BF16, SMALL_F32, bf16_bits_to_f32, f32_to_bf16_trunc_bits,
                      flat, rel_err, seeded_params, split, tokens_for)
 from oracle.loader import FifoU16
 from oracle.optim import AdamConf, NesterovConf, adamw_update
@@ -36,7 +36,8 @@ def _grads_via_abi(be, cfg, params, x, y):
 @pytest.mark.parametrize("cfgd,tol", [(SMALL_F32, 1e-4), (GQA_F32, 1e-4), (HD128_F32, 1e-4), (SMALL_BF16, 2e-2),
                                       (HD128_BF16, 2e-2), (GPT_SMALL_F32, 1e-4), (GPT_ODD_F32, 1e-4),
                                       (GPT_SMALL_BF16, 2e-2), (GPT_GELU_F32, 1e-4), (GPT_GELU_BF16, 2e-2), (GPT_D256_F32, 1e-4),
-                                      (HD64_F32, 1e-4), (GPT_HD64_F32, 1e-4)])
+                                      (HD64_F32, 1e-4), (GPT_HD64_F32, 1e-4), (HD32_F32, 1e-4), (HD16_F32, 1e-4),
+                                      (GPT_HD32_F32, 1e-4)])
 def test_compute_gradients_matches_oracle(cfgd, tol):
     cfg, text = make_model(cfgd)
     mod = TrainingModule(text)

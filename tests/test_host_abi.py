@@ -105,3 +105,18 @@ def test_recogniser_refuses_same_signature_other_body(lib_built):
         with pytest.raises(BackendError) as ei:
             inspect_artifact(text)
         assert ei.value.code == bk.E_ARTIFACT, what
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "models")), reason="reference tree not present")
+def test_every_shipped_reference_graph_is_recognised(lib_built):
+    """All forward graphs under the reference's models/ load: both families, f32 and bf16, head widths 16 / 32 / 128."""
+    import glob
+    files = sorted(glob.glob(os.path.join(REF, "models", "*.mlir")))
+    assert len(files) >= 17
+    widths = set()
+    for fn in files:
+        f = inspect_artifact(open(fn).read())
+        assert f["n_head"] * f["head_dim"] == f["d_model"] and f["n_head"] % f["n_kv_head"] == 0, fn
+        assert f["total_params"] > 0 and f["dtype"] in (bk.F32, bk.BF16), fn
+        widths.add(f["head_dim"])
+    assert widths == {16, 32, 128}
