@@ -54,6 +54,7 @@ WORKLOADS = {
     "d20l2b2": dict(vocab=65536, d_model=1280, n_layer=2, n_head=10, n_kv_head=10, seq_len=2048, batch=2, dtype="bf16"),
     "d20l2b4": dict(vocab=65536, d_model=1280, n_layer=2, n_head=10, n_kv_head=10, seq_len=2048, batch=4, dtype="bf16"),
     "d8ship": dict(vocab=65536, d_model=256, n_layer=8, n_head=8, n_kv_head=4, seq_len=2048, batch=8, dtype="bf16"),
+    "d12ship": dict(vocab=65536, d_model=768, n_layer=12, n_head=6, n_kv_head=6, seq_len=2048, batch=6, dtype="f32"),
     "d20l2b16": dict(vocab=65536, d_model=1280, n_layer=2, n_head=10, n_kv_head=10, seq_len=2048, batch=16, dtype="bf16"),
 }
 DESCR = {
@@ -68,6 +69,7 @@ DESCR = {
     "d20l2b2": "two d20 layers + the d20 LM head, B=2, T=2048 (GEMM DRAM-traffic profiling size)",
     "d20l2b4": "two d20 layers + the d20 LM head, B=4, T=2048 (GEMM DRAM-traffic profiling size)",
     "d8ship": "the shipped models/nanochat_d8_b8_t2048_bf16.mlir shape: d=256, 8 query / 4 kv heads x 32, 8 layers, B=8, T=2048",
+    "d12ship": "the shipped models/nanochat_d12_b6_t2048.mlir shape: fp32, d=768, 6 heads x 128, 12 layers, B=6, T=2048",
     "d20l2b16": "two d20 layers + the d20 LM head, B=16, T=2048 (LM-head DRAM-traffic profiling size: 128 row tiles)",
 }
 # BASELINE.json configs[4]: Qwen3-8B-shaped bf16 rollout generation, one replica per GPU

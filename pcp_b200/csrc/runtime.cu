@@ -177,7 +177,9 @@ int build_workspace(pcpb_backend* b) {
   // PCPB_F32_TC=0 keeps f32 models on the SIMT kernel
   {
     const char* e = getenv("PCPB_F32_TC");
-    const long long wide = std::max<long long>(std::max<long long>(F, d + 2 * dkv), d);
+    long long wide = std::max<long long>(std::max<long long>(F, d + 2 * dkv), d);
+    // the LM head too when its width is a tile multiple and the buffers stay within 24 GB
+    if (c.V % 128 == 0 && (size_t)M * std::max<long long>(wide, c.V) * 28 <= ((size_t)24 << 30)) wide = std::max<long long>(wide, c.V);
     const size_t ab = (size_t)M * wide * 12, cc = (size_t)M * wide * 4;
     if (c.dtype == DT_F32 && !(e && e[0] == '0') && M % 128 == 0 && d % 128 == 0 && 2 * ab + cc <= ((size_t)24 << 30)) {
       WS(b, w.pk_a, ab); WS(b, w.pk_b, ab); WS(b, w.pk_c, cc);
