@@ -1,4 +1,4 @@
-// Causal attention (bf16, head_dim 128) on the 5th-generation tensor cores: tcgen05.mma with the score /
+// Causal attention (bf16, head_dim 128 or 64) on the 5th-generation tensor cores: tcgen05.mma with the score /
 // gradient tiles and the output accumulators in tensor memory, operand tiles brought in by TMA.
 //
 // One CTA owns 128 "row-side" positions of one (batch, head) and streams 64-position "column-side" sub-tiles:
@@ -23,7 +23,9 @@
 // The element-wise arithmetic works on bf16 pairs: one cvt.rn.bf16x2 and one mul.bf16x2 reproduce the two roundings
 // of a score, one more pair of them the rounding of dS.
 //
-// A streamed [64 x 128] sub-tile serves two roles with the same bytes: "K-major" B operand of the score product
+// Tiles are stored as HD / 64 halves of 64 columns (one 128-byte swizzle atom per row), so the 64-wide heads of the
+// nanoGPT configurations are the one-half case of the same code: HD / 16 k-steps per score product, N = HD output
+// columns.  A streamed [64 x HD] sub-tile serves two roles with the same bytes: "K-major" B operand of the score product
 // (contraction over head_dim) and "MN-major" B operand of the output product (contraction over its 64 rows).
 //
 // Numerics are those of attn_flash.cu / the generic kernels (scores rounded twice to bf16, guard terms 1e-4 / 2e-4,
@@ -38,16 +40,12 @@ namespace pcpb {
 
 namespace {
 
-constexpr int HD = 128;
 #ifndef PCPB_ATC_NST_FWD
 #define PCPB_ATC_NST_FWD 2
 #endif
 #ifndef PCPB_ATC_NST_DQ
 #define PCPB_ATC_NST_DQ 4
 #endif
-constexpr int SUB_BYTES = 64 * HD * 2;         // one streamed sub-tile: 16 KB
-constexpr int STAGE_BYTES = 2 * SUB_BYTES;     // (C1, C2)
-constexpr int TILE_BYTES = 128 * HD * 2;       // one resident tile: 32 KB
 constexpr float LOG2E = 1.4426950408889634f;
 // Element-wise warps per CTA: 16 (two groups of 8) in the backward kernels, which fill the SM alone; 8 (two groups of 4)
 // in the forward kernel, which needs half of the tensor memory and half of the shared memory and runs two CTAs per SM
@@ -67,7 +65,10 @@ struct AtcParams {
   int n_items, bh_count;                       // backward kernels: work items (row tile x batch-head), batch-heads
 };
 
-template <int MODE> struct AtcCfg {
+template <int MODE, int HD> struct AtcCfg {
+  static constexpr int SUB_BYTES = 64 * HD * 2;                // one streamed sub-tile: 16 KB at HD = 128
+  static constexpr int STAGE_BYTES = 2 * SUB_BYTES;            // (C1, C2)
+  static constexpr int TILE_BYTES = 128 * HD * 2;              // one resident tile: 32 KB at HD = 128
   static constexpr int N_EW = (MODE == MODE_FWD) ? 8 : 16;
   // score buffers in tensor memory = sub-tiles in flight = element-wise groups (one group per buffer)
   static constexpr int NBUF = 2;
@@ -143,11 +144,35 @@ __device__ __forceinline__ void store_out_cols(uint32_t taddr, bf16* dst) {
   }
 }
 
-template <int MODE>
-__global__ void __launch_bounds__(AtcCfg<MODE>::THREADS, AtcCfg<MODE>::CTAS_PER_SM)
+// 16 columns (64-wide heads, four warps per lane quarter)
+template <bool ADJ>
+__device__ __forceinline__ void store_out_cols16(uint32_t taddr, bf16* dst) {
+  uint32_t r[16];
+  tmem_ld16_issue(taddr, r);
+  tmem_ld_wait16(r);
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    uint4 v;
+    v.x = pack2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+    v.y = pack2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+    v.z = pack2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+    v.w = pack2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+    if (ADJ) {
+      uint32_t mx2 = 0u;
+      adj_track2(mx2, v.x); adj_track2(mx2, v.y); adj_track2(mx2, v.z); adj_track2(mx2, v.w);
+      if (adj_over2(mx2)) { v.x = adj_edge2(v.x); v.y = adj_edge2(v.y); v.z = adj_edge2(v.z); v.w = adj_edge2(v.w); }
+    }
+    *reinterpret_cast<uint4*>(dst + 8 * j) = v;
+  }
+}
+
+template <int MODE, int HD>
+__global__ void __launch_bounds__(AtcCfg<MODE, HD>::THREADS, AtcCfg<MODE, HD>::CTAS_PER_SM)
 k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CUtensorMap tm_qkv,
           const __grid_constant__ CUtensorMap tm_do, const AtcParams p) {
-  using Cfg = AtcCfg<MODE>;
+  using Cfg = AtcCfg<MODE, HD>;
+  constexpr int SUB_BYTES = Cfg::SUB_BYTES, STAGE_BYTES = Cfg::STAGE_BYTES, TILE_BYTES = Cfg::TILE_BYTES;
+  constexpr bool TWO_HALVES = (HD == 128);                     // a tile row is one or two 64-column halves
   constexpr int NST = Cfg::NST, N_EW = Cfg::N_EW, NCG = Cfg::NCG, PASSES = Cfg::PASSES, NBUF = Cfg::NBUF, LPR = Cfg::LPR;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -244,7 +269,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
     // All 32 lanes run the loop (warp-uniform control flow and addresses); one elected lane issues.
     auto load_tile128 = [&](uint32_t dst, const CUtensorMap* m, int x, int y) {
       tma_load_2d_elect(dst, m, res_bar, x, y);              tma_load_2d_elect(dst + 8192, m, res_bar, x, y + 64);
-      tma_load_2d_elect(dst + 16384, m, res_bar, x + 64, y); tma_load_2d_elect(dst + 24576, m, res_bar, x + 64, y + 64);
+      if (TWO_HALVES) { tma_load_2d_elect(dst + 16384, m, res_bar, x + 64, y); tma_load_2d_elect(dst + 24576, m, res_bar, x + 64, y + 64); }
     };
     bool ok = true;
     int gb = 0, ge = 0, g = 0, k = 0;                        // ring positions run on gb + g (forward V ring: ge + it) across items
@@ -274,25 +299,35 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
           // K of key sub-tile g % n_it (both sweeps); V of sub-tile it = g - n_it (second sweep) through its own barriers
           const int y = row_base + (g % n_it) * 64;
           mbar_expect_tx_elect(full_bar(s), SUB_BYTES);
-          tma_load_2d_elect(c1, &tm_qkn, full_bar(s), xk, y); tma_load_2d_elect(c1 + 8192, &tm_qkn, full_bar(s), xk + 64, y);
+          tma_load_2d_elect(c1, &tm_qkn, full_bar(s), xk, y);
+          if (TWO_HALVES) tma_load_2d_elect(c1 + 8192, &tm_qkn, full_bar(s), xk + 64, y);
           if (g >= n_it) {
             const int it = g - n_it, sv = (ge + it) % NST;
             ok = __all_sync(0xffffffffu, twait(11, vempty_bar(sv), (((uint32_t)(ge + it) / NST) & 1u) ^ 1u, p.err, tacc[0]));
             if (!ok) { ++g; break; }
             const uint32_t cv = sRing + sv * STAGE_BYTES + SUB_BYTES;
             mbar_expect_tx_elect(vfull_bar(sv), SUB_BYTES);
-            tma_load_2d_elect(cv, &tm_qkv, vfull_bar(sv), xv, y); tma_load_2d_elect(cv + 8192, &tm_qkv, vfull_bar(sv), xv + 64, y);
+            tma_load_2d_elect(cv, &tm_qkv, vfull_bar(sv), xv, y);
+            if (TWO_HALVES) tma_load_2d_elect(cv + 8192, &tm_qkv, vfull_bar(sv), xv + 64, y);
           }
         } else if (MODE == MODE_DKV) {
           mbar_expect_tx_elect(full_bar(s), STAGE_BYTES);
           const int hh = h + g / n_q, y = row_base + r0 + (g % n_q) * 64;
-          tma_load_2d_elect(c1, &tm_qkn, full_bar(s), hh * HD, y); tma_load_2d_elect(c1 + 8192, &tm_qkn, full_bar(s), hh * HD + 64, y);
-          tma_load_2d_elect(c2, &tm_do, full_bar(s), hh * HD, y);  tma_load_2d_elect(c2 + 8192, &tm_do, full_bar(s), hh * HD + 64, y);
+          tma_load_2d_elect(c1, &tm_qkn, full_bar(s), hh * HD, y);
+          tma_load_2d_elect(c2, &tm_do, full_bar(s), hh * HD, y);
+          if (TWO_HALVES) {
+            tma_load_2d_elect(c1 + 8192, &tm_qkn, full_bar(s), hh * HD + 64, y);
+            tma_load_2d_elect(c2 + 8192, &tm_do, full_bar(s), hh * HD + 64, y);
+          }
         } else {
           mbar_expect_tx_elect(full_bar(s), STAGE_BYTES);
           const int y = row_base + g * 64;
-          tma_load_2d_elect(c1, &tm_qkn, full_bar(s), xk, y); tma_load_2d_elect(c1 + 8192, &tm_qkn, full_bar(s), xk + 64, y);
-          tma_load_2d_elect(c2, &tm_qkv, full_bar(s), xv, y); tma_load_2d_elect(c2 + 8192, &tm_qkv, full_bar(s), xv + 64, y);
+          tma_load_2d_elect(c1, &tm_qkn, full_bar(s), xk, y);
+          tma_load_2d_elect(c2, &tm_qkv, full_bar(s), xv, y);
+          if (TWO_HALVES) {
+            tma_load_2d_elect(c1 + 8192, &tm_qkn, full_bar(s), xk + 64, y);
+            tma_load_2d_elect(c2 + 8192, &tm_qkv, full_bar(s), xv + 64, y);
+          }
         }
       }
       if (!ok) break;
@@ -318,9 +353,9 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
     // All 32 lanes run the loops and the waits; one elected lane issues the MMAs and the commits.
-    // score products: M=128, N=64, A and B K-major; output products: M=128, N=128, A K-major, B MN-major
+    // score products: M=128, N=64, A and B K-major; output products: M=128, N=HD, A K-major, B MN-major
     constexpr uint32_t ID_T = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-    constexpr uint32_t ID_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    constexpr uint32_t ID_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     bool ok = true;
     int gb = 0, ge = 0;                                      // score products / result tiles of the items done so far (even)
     // g: position in the item (selects nothing here but the last-tile test); gb + g: ring / buffer position
@@ -333,7 +368,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
       const uint32_t c1 = sRing + s * STAGE_BYTES, c2 = c1 + SUB_BYTES;
       // The two independent products of the backward kernels are issued alternately.
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
+      for (int ks = 0; ks < HD / 16; ++ks) {
         const uint32_t ao = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
         const uint32_t bo = (uint32_t)(ks >> 2) * 8192u + (uint32_t)(ks & 3) * 32u;
         // first resident tile (Q or K) against the first streamed one; second (dO or V) against the second
@@ -624,19 +659,30 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
     if (ok) {
       tc_fence_after();
       const long long grow = (long long)row_base + my;
-      // 128 output columns over the NCG warps of a lane quarter: 32 each (4 warps) or 64 each for the first two
-      constexpr int PARTS = (NCG == 4) ? 1 : 2;
+      // HD output columns over the NCG warps of a lane quarter: HD / NCG each, in pieces of 32 (or one of 16)
+      constexpr int CW = HD / NCG;
+      if (CW >= 32) {
 #pragma unroll
-      for (int part = 0; part < PARTS; ++part) {
-        const int oc = (cg * PARTS + part) * 32;
-        if (oc >= 128) break;
-        if (MODE == MODE_FWD) {
-          store_out_cols<false>(out1 + lane_off + oc, p.o + grow * p.d + xq + oc);
-        } else if (MODE == MODE_DQ) {
-          store_out_cols<true>(out1 + lane_off + oc, p.dqkn + grow * (p.d + p.dkv) + xq + oc);
+        for (int part = 0; part < CW / 32; ++part) {
+          const int oc = cg * CW + part * 32;
+          if (MODE == MODE_FWD) {
+            store_out_cols<false>(out1 + lane_off + oc, p.o + grow * p.d + xq + oc);
+          } else if (MODE == MODE_DQ) {
+            store_out_cols<true>(out1 + lane_off + oc, p.dqkn + grow * (p.d + p.dkv) + xq + oc);
+          } else {
+            store_out_cols<true>(out1 + lane_off + oc, p.dqkv + grow * (p.d + 2 * p.dkv) + xv + oc);
+            store_out_cols<true>(out2 + lane_off + oc, p.dqkn + grow * (p.d + p.dkv) + xk + oc);
+          }
+        }
+      } else {
+        const int oc = cg * CW;
+        if (MODE == MODE_DQ) {
+          store_out_cols16<true>(out1 + lane_off + oc, p.dqkn + grow * (p.d + p.dkv) + xq + oc);
+        } else if (MODE == MODE_DKV) {
+          store_out_cols16<true>(out1 + lane_off + oc, p.dqkv + grow * (p.d + 2 * p.dkv) + xv + oc);
+          store_out_cols16<true>(out2 + lane_off + oc, p.dqkn + grow * (p.d + p.dkv) + xk + oc);
         } else {
-          store_out_cols<true>(out1 + lane_off + oc, p.dqkv + grow * (p.d + 2 * p.dkv) + xv + oc);
-          store_out_cols<true>(out2 + lane_off + oc, p.dqkn + grow * (p.d + p.dkv) + xk + oc);
+          store_out_cols16<false>(out1 + lane_off + oc, p.o + grow * p.d + xq + oc);
         }
       }
       if (MODE == MODE_FWD && cg == 0) {
@@ -673,18 +719,20 @@ k_attn_tc(const __grid_constant__ CUtensorMap tm_qkn, const __grid_constant__ CU
   }
 }
 
-// D[b,h,i] = rowsum(do * o) * (l + 1e-4) / (l + 2e-4).  Eight lanes per row, 16 elements (two 16-byte loads of each
-// tensor) per lane: four rows per warp, 64 bytes in flight per thread.
+// D[b,h,i] = rowsum(do * o) * (l + 1e-4) / (l + 2e-4).  HD / 16 lanes per row, 16 elements (two 16-byte loads of each
+// tensor) per lane: four (eight) rows per warp, 64 bytes in flight per thread.
+template <int HD>
 __global__ void __launch_bounds__(256) k_attn_tc_prep(const bf16* __restrict__ o, const bf16* __restrict__ dout,
                                                       const float* __restrict__ lrow, float* __restrict__ drow, int B, int T, int H,
                                                       const bf16* __restrict__ qkv, int Hkv) {
   __shared__ float sred[3][8];
-  const int sub = threadIdx.x & 7;
+  constexpr int LPROW = HD / 16, SHIFT = (HD == 128) ? 3 : 2;  // lanes per row
+  const int sub = threadIdx.x & (LPROW - 1);
   const long long rows = (long long)B * H * T;
   // statistics for the bound on the adjoints that stay on the chip in the backward kernels (dP, dS): the largest
   // squared norm of a dO row and of a V row, the largest |D|; gathered per thread over its rows, then per block
   float m_do = 0.f, m_v = 0.f, m_d = 0.f;
-  for (long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3; gw < rows; gw += ((long long)gridDim.x * blockDim.x) >> 3) {
+  for (long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> SHIFT; gw < rows; gw += ((long long)gridDim.x * blockDim.x) >> SHIFT) {
     const int i = (int)(gw % T), bh = (int)(gw / T), b = bh / H, h = bh % H;
     const size_t off = ((size_t)b * T + i) * ((size_t)H * HD) + (size_t)h * HD + sub * 16;
     const uint4 a0 = *reinterpret_cast<const uint4*>(o + off), a1 = *reinterpret_cast<const uint4*>(o + off + 8);
@@ -705,7 +753,7 @@ __global__ void __launch_bounds__(256) k_attn_tc_prep(const bf16* __restrict__ o
       for (int k = 0; k < 8; ++k) n_v += bf_lo(z[k]) * bf_lo(z[k]) + bf_hi(z[k]) * bf_hi(z[k]);
     }
 #pragma unroll
-    for (int s = 1; s <= 4; s <<= 1) {
+    for (int s = 1; s < LPROW; s <<= 1) {
       acc += __shfl_xor_sync(0xffffffffu, acc, s);
       n_do += __shfl_xor_sync(0xffffffffu, n_do, s);
       n_v += __shfl_xor_sync(0xffffffffu, n_v, s);
@@ -735,27 +783,27 @@ __global__ void __launch_bounds__(256) k_attn_tc_prep(const bf16* __restrict__ o
   }
 }
 
-template <int MODE>
+template <int MODE, int HD>
 cudaError_t launch_mode(cudaStream_t st, const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const AtcParams& p,
                         dim3 grid) {
-  auto kern = k_attn_tc<MODE>;
+  auto kern = k_attn_tc<MODE, HD>;
   static bool attr[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !attr[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AtcCfg<MODE>::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AtcCfg<MODE, HD>::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     // all of the SM's L1 / shared-memory array as shared memory: the forward kernel needs it to fit two CTAs per SM
     e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) attr[dev] = true;
   }
-  kern<<<grid, AtcCfg<MODE>::THREADS, AtcCfg<MODE>::SMEM_BYTES, st>>>(a, b, c, p);
+  kern<<<grid, AtcCfg<MODE, HD>::THREADS, AtcCfg<MODE, HD>::SMEM_BYTES, st>>>(a, b, c, p);
   return cudaGetLastError();
 }
 
 bool fill(const FlashArgs& a, int* err, AtcParams* p, CUtensorMap* mq, CUtensorMap* mv, CUtensorMap* md, bool need_do) {
-  const int d = a.H * HD, dkv = a.Hkv * HD;
+  const int d = a.H * a.hd, dkv = a.Hkv * a.hd;
   const uint64_t M = (uint64_t)a.B * a.T;
   p->B = a.B; p->T = a.T; p->H = a.H; p->Hkv = a.Hkv; p->scale = a.scale; p->fwd_guard = a.no_guard ? 0.f : PCPB_GUARD; p->d = d; p->dkv = dkv;
   p->qkn = (const bf16*)a.qkn; p->dout = (const bf16*)a.dout;
@@ -779,7 +827,7 @@ extern "C" int pcpb_debug_atc_timing(unsigned long long* out96, int reset) {
 #endif
 
 bool attn_tc_supported(const FlashArgs& a) {
-  return a.hd == HD && a.T % 128 == 0 && a.T >= 128 && a.H % a.Hkv == 0 && a.B > 0 && (long long)a.B * a.H <= 65535 &&
+  return (a.hd == 128 || a.hd == 64) && a.T % 128 == 0 && a.T >= 128 && a.H % a.Hkv == 0 && a.B > 0 && (long long)a.B * a.H <= 65535 &&
          ((((uintptr_t)a.qkn) | ((uintptr_t)a.qkv) | ((uintptr_t)a.o)) & 15) == 0 && encode_fn() != nullptr;
 }
 
@@ -792,8 +840,9 @@ cudaError_t launch_attn_tc_fwd(cudaStream_t st, const FlashArgs& a, int* err_wor
   cudaGetDevice(&dev);
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
   p.bh_count = a.B * a.H; p.n_items = (a.T / 128) * p.bh_count;
-  const int slots = sms * AtcCfg<MODE_FWD>::CTAS_PER_SM;
-  return launch_mode<MODE_FWD>(st, mq, mv, md, p, dim3(p.n_items < slots ? p.n_items : slots));
+  const int slots = sms * AtcCfg<MODE_FWD, 128>::CTAS_PER_SM;
+  const dim3 grid(p.n_items < slots ? p.n_items : slots);
+  return a.hd == 128 ? launch_mode<MODE_FWD, 128>(st, mq, mv, md, p, grid) : launch_mode<MODE_FWD, 64>(st, mq, mv, md, p, grid);
 }
 
 cudaError_t launch_attn_tc_bwd(cudaStream_t st, const FlashArgs& a, int* err_word) {
@@ -803,10 +852,12 @@ cudaError_t launch_attn_tc_bwd(cudaStream_t st, const FlashArgs& a, int* err_wor
   const long long rows = (long long)a.B * a.H * a.T;
   {
     // a few rows per thread: the block-level statistics then cost three atomics per block
-    const long long blocks = (rows * 8 + 255) / 256;
+    const long long blocks = (rows * (a.hd / 16) + 255) / 256;
     const unsigned grid = (unsigned)(blocks < 148 * 16 ? blocks : 148 * 16);
-    k_attn_tc_prep<<<grid, 256, 0, st>>>((const bf16*)a.o, (const bf16*)a.dout, a.lrow, a.drow, a.B,
-                                         a.T, a.H, (const bf16*)a.qkv, a.Hkv);
+    if (a.hd == 128)
+      k_attn_tc_prep<128><<<grid, 256, 0, st>>>((const bf16*)a.o, (const bf16*)a.dout, a.lrow, a.drow, a.B, a.T, a.H, (const bf16*)a.qkv, a.Hkv);
+    else
+      k_attn_tc_prep<64><<<grid, 256, 0, st>>>((const bf16*)a.o, (const bf16*)a.dout, a.lrow, a.drow, a.B, a.T, a.H, (const bf16*)a.qkv, a.Hkv);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
@@ -815,10 +866,12 @@ cudaError_t launch_attn_tc_bwd(cudaStream_t st, const FlashArgs& a, int* err_wor
   cudaGetDevice(&dev);
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
   p.bh_count = a.B * a.Hkv; p.n_items = (a.T / 128) * p.bh_count;
-  e = launch_mode<MODE_DKV>(st, mq, mv, md, p, dim3(p.n_items < sms ? p.n_items : sms));
+  const dim3 g1(p.n_items < sms ? p.n_items : sms);
+  e = a.hd == 128 ? launch_mode<MODE_DKV, 128>(st, mq, mv, md, p, g1) : launch_mode<MODE_DKV, 64>(st, mq, mv, md, p, g1);
   if (e != cudaSuccess) return e;
   p.bh_count = a.B * a.H; p.n_items = (a.T / 128) * p.bh_count;
-  return launch_mode<MODE_DQ>(st, mq, mv, md, p, dim3(p.n_items < sms ? p.n_items : sms));
+  const dim3 g2(p.n_items < sms ? p.n_items : sms);
+  return a.hd == 128 ? launch_mode<MODE_DQ, 128>(st, mq, mv, md, p, g2) : launch_mode<MODE_DQ, 64>(st, mq, mv, md, p, g2);
 }
 
 cudaError_t adj_status_fetch_attn_tc(cudaStream_t st, int* out, bool clear) { return adj_status_fetch_tu(st, out, clear); }
