@@ -177,7 +177,8 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 4) k_gemv16(const bf16* __restr
 // gridDim.y - 1 adds the partials in split order (the result does not depend on which CTA that is), applies the epilogue
 // and puts the counter back to 0.  No CTA waits for another.
 constexpr int GW_KC = 1024;                                     // columns of X staged at a time
-constexpr int GW_LD = GW_KC + 8;                                // shared-memory row stride (elements): conflict-free 16-byte reads
+constexpr int GW_LD = GW_KC + 32;                               // shared-memory row stride (elements): rows 64 bytes apart modulo a bank line, so
+                                                                // that the 16-byte reads of two rows (8 lanes) miss each other
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
 }
@@ -194,8 +195,13 @@ __global__ void __launch_bounds__(256, 4) k_gemv16w(const bf16* __restrict__ X, 
   const int kbeg = blockIdx.y * kc;
   const int klen = min(kc, K - kbeg);                           // the last k range may be shorter
   const int nsteps = klen / 64;
-  const bf16* wrow = W + (size_t)(active ? n0 + g : 0) * K + kbeg + 16 * q;
-  const bf16* w2row = (EPI == GV_SWIGLU) ? W2 + (size_t)(active ? n0 + g : 0) * K + kbeg + 16 * q : nullptr;
+  // Per 64-column step a lane reads two 16-byte pieces of its weight row: columns [8 q, 8 q + 8) and [32 + 8 q, 40 + 8 q).
+  // The four lanes of a row then cover 64 contiguous bytes, two whole 32-byte sectors, with each load instruction.
+  // (With 32 contiguous bytes per lane, one half per instruction, every sector crossed from L2 to the SM twice: ncu
+  // showed 241 MB into the SMs for the 101 MB matrix.)  Which k values a lane takes does not matter as long as X is read
+  // with the same assignment.
+  const bf16* wrow = W + (size_t)(active ? n0 + g : 0) * K + kbeg + 8 * q;
+  const bf16* w2row = (EPI == GV_SWIGLU) ? W2 + (size_t)(active ? n0 + g : 0) * K + kbeg + 8 * q : nullptr;
   float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
   constexpr int U = (EPI == GV_SWIGLU) ? 2 : 4;                 // 32-byte weight pieces in flight per lane and panel
   uint4 wv[U][2], w2v[U][2];
@@ -205,8 +211,8 @@ __global__ void __launch_bounds__(256, 4) k_gemv16w(const bf16* __restrict__ X, 
       const bool in = active && s + u < nsteps;
 #pragma unroll
       for (int hlf = 0; hlf < 2; ++hlf) {
-        wv[u][hlf] = in ? ld_stream(wrow + (s + u) * 64 + 8 * hlf) : make_uint4(0, 0, 0, 0);
-        if (EPI == GV_SWIGLU) w2v[u][hlf] = in ? ld_stream(w2row + (s + u) * 64 + 8 * hlf) : make_uint4(0, 0, 0, 0);
+        wv[u][hlf] = in ? ld_stream(wrow + (s + u) * 64 + 32 * hlf) : make_uint4(0, 0, 0, 0);
+        if (EPI == GV_SWIGLU) w2v[u][hlf] = in ? ld_stream(w2row + (s + u) * 64 + 32 * hlf) : make_uint4(0, 0, 0, 0);
       }
     }
   };
@@ -230,13 +236,13 @@ __global__ void __launch_bounds__(256, 4) k_gemv16w(const bf16* __restrict__ X, 
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       if (s + u >= nsteps) break;
-      const int xc = ((s + u) * 64) % GW_KC + 16 * q;
+      const int xc = ((s + u) * 64) % GW_KC + 8 * q;
 #pragma unroll
       for (int hlf = 0; hlf < 2; ++hlf) {
         // 8 consecutive k values serve two k16 steps: elements {0,1,2,3} and {4,5,6,7}; the operand X is read with
         // the same permutation of k, so the products line up
-        const uint4 a = *reinterpret_cast<const uint4*>(xs + g * GW_LD + xc + 8 * hlf);
-        const uint4 b = *reinterpret_cast<const uint4*>(xs + (g + 8) * GW_LD + xc + 8 * hlf);
+        const uint4 a = *reinterpret_cast<const uint4*>(xs + g * GW_LD + xc + 32 * hlf);
+        const uint4 b = *reinterpret_cast<const uint4*>(xs + (g + 8) * GW_LD + xc + 32 * hlf);
         mma16816(acc, a.x, b.x, a.y, b.y, wv[u][hlf].x, wv[u][hlf].y);
         mma16816(acc, a.z, b.z, a.w, b.w, wv[u][hlf].z, wv[u][hlf].w);
         if (EPI == GV_SWIGLU) {
