@@ -661,7 +661,7 @@ def run_ours(args):
         except Exception as e:
             others.append({"workload": "qwen3_rollout", "error": str(e)})
         if not args.no_cpu_baseline:
-            # BASELINE config 1 fits the host whole: two seeded inner steps of it on the CPU oracle and on the GPU (its f32
+            # the nanoGPT-small fp32 configuration fits the host whole: two seeded inner steps of it on the CPU oracle and on the GPU (its f32
             # GEMMs run on the tensor cores through the three-piece split, its attention on the tiled f32 kernels)
             for o in others:
                 if o.get("workload") == "c1" and "error" not in o:

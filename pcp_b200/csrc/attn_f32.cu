@@ -1,5 +1,5 @@
-// Causal attention for f32 models with 16-, 32-, 64- or 128-wide heads (64: nanoGPT-small, BASELINE config 1; the
-// others: the shipped f32 graphs), forward and backward, tiled for the SIMT pipes: the f32 models must stay f32-exact, so the score / probability / gradient tiles are f32 FMAs —
+// Causal attention for f32 models with 16-, 32-, 64- or 128-wide heads (64: the nanoGPT-small fp32 configuration;
+// the others: the shipped f32 graphs), forward and backward, tiled for the SIMT pipes: the f32 models must stay f32-exact, so the score / probability / gradient tiles are f32 FMAs —
 // 64 x 64 score tiles, 256 threads, a 4 x 4 register block per thread (4 x HD/16 for the head-dim-wide outputs), operands
 // in shared memory in a k-major layout read with 16-byte loads.  It replaces the one-block-per-query-row kernels of kernels.cu (k_attn_*_generic) for these
 // shapes: those take 60 ms of the 135 ms nanoGPT-small step (one scalar dot product per thread and key, atomics in the

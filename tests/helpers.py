@@ -44,7 +44,7 @@ GPT_GELU_F32 = dict(GPT_SMALL_F32, activation="gelu")
 GPT_GELU_BF16 = dict(vocab=256, d_model=256, n_layer=2, n_head=4, seq_len=128, batch=4, dtype="bf16", activation="gelu")
 # d_model a multiple of 256: the vectorised LayerNorm backward, f32
 GPT_D256_F32 = dict(vocab=97, d_model=256, n_layer=1, n_head=4, seq_len=32, batch=4, dtype="f32")
-# nanoGPT-small's kernel shapes in small (BASELINE config 1: fp32, 64-wide heads): tiled f32 attention over three query
+# nanoGPT-small's kernel shapes in small (the fp32 benchmark configuration: 64-wide heads): tiled f32 attention over three query
 # tiles, split-operand tensor-core GEMMs, GELU
 # the shipped models/nanogpt_medium.mlir layout in small: f32, 8 heads x 32
 GPT_HD32_F32 = dict(vocab=256, d_model=256, n_layer=1, n_head=8, seq_len=128, batch=2, dtype="f32")
