@@ -1,9 +1,9 @@
-// Causal attention for f32 models with 16-, 32-, 64- or 128-wide heads (64: the nanoGPT-small fp32 configuration;
-// the others: the shipped f32 graphs), forward and backward, tiled for the SIMT pipes: the f32 models must stay f32-exact, so the score / probability / gradient tiles are f32 FMAs —
-// 64 x 64 score tiles, 256 threads, a 4 x 4 register block per thread (4 x HD/16 for the head-dim-wide outputs), operands
-// in shared memory in a k-major layout read with 16-byte loads.  It replaces the one-block-per-query-row kernels of kernels.cu (k_attn_*_generic) for these
-// shapes: those take 60 ms of the 135 ms nanoGPT-small step (one scalar dot product per thread and key, atomics in the
-// backward).
+// Causal attention for f32 models with 16-, 32-, 64- or 128-wide heads (64: the nanoGPT-small fp32 configuration; the
+// others: the shipped f32 graphs), forward and backward, tiled for the SIMT pipes.  The f32 models must stay f32-exact,
+// so the score / probability / gradient tiles are f32 FMAs: 64 x 64 score tiles, 256 threads, a 4 x 4 register block per
+// thread (4 x HD/16 for the head-dim-wide outputs), operands in shared memory in a k-major layout read with 16-byte
+// loads.  They replace the one-block-per-query-row kernels of kernels.cu (k_attn_*_generic) for these shapes: those took
+// 60 ms of the 135 ms nanoGPT-small step (one scalar dot product per thread and key, atomics in the backward).
 //   forward   one CTA per (64 queries, batch, head): S = Q K^T per key tile, running row max / sum, O += P V,
 //             O / (l + 1e-4) at the end.  f32 has no rounding between the ops of the graph, so normalising after the
 //             sum is the graph's P = e / (l + 1e-4), O = P V up to the order of the f32 additions.
