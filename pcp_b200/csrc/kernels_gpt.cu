@@ -174,13 +174,17 @@ cudaError_t launch_layernorm_fwd(cudaStream_t st, int dt, const void* x, const v
 // dgamma / dbeta over the rows it handled in its own shared-memory slice (a lane owns columns lane + 32 k); the
 // 8 slices are combined and written as one partial per block.
 constexpr int LN_ROWS = 64;
+// The generic kernel (widths that are not a multiple of 256, e.g. 384) has no loads in flight beyond the row a warp works
+// on, so it wants many resident warps instead: 16 rows per block (two per warp), 1024 blocks at 16384 rows.  With 64 rows
+// per block it took 148 us per launch at [16384, 384] f32 (100 MB of traffic: 15 us at the copy bandwidth).
+constexpr int LN_ROWS_GENERIC = 16;
 
 template <typename T>
 __global__ void __launch_bounds__(256) k_layernorm_bwd(const T* __restrict__ x, const T* __restrict__ gamma,
                                                        const float* __restrict__ mean_in, const float* __restrict__ t_in,
                                                        const double* __restrict__ mean64_in, const T* __restrict__ dy,
                                                        const T* __restrict__ dres, int M, int d, T* __restrict__ dx,
-                                                       float* __restrict__ partial) {
+                                                       float* __restrict__ partial, int rows_per_block) {
   extern __shared__ float sm[];                  // [8 warps][2][d]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nc = (d + 31) / 32;
@@ -189,8 +193,8 @@ __global__ void __launch_bounds__(256) k_layernorm_bwd(const T* __restrict__ x, 
   for (int j = lane; j < d; j += 32) { dgw[j] = 0.f; dbw[j] = 0.f; }
   const double dd2 = ((double)d + 1e-4) + 1e-4;
   const float df2 = ((float)d + PCPB_GUARD) + PCPB_GUARD;
-  for (int rr = warp; rr < LN_ROWS; rr += 8) {
-    const int m = blockIdx.x * LN_ROWS + rr;
+  for (int rr = warp; rr < rows_per_block; rr += 8) {
+    const int m = blockIdx.x * rows_per_block + rr;
     if (m >= M) break;
     const T* xr = x + (size_t)m * d; const T* dyr = dy + (size_t)m * d;
     const float mean = mean_in[m], t = t_in[m], r = rsqrtf(t);
@@ -443,14 +447,14 @@ __global__ void __launch_bounds__(256) k_ln_param_grads(const float* __restrict_
     (i / d == 0 ? dgamma : dbeta)[i % d] = v;
   }
 }
-size_t layernorm_bwd_scratch_floats(int M, int d) { return (size_t)((M + LN_ROWS - 1) / LN_ROWS) * 2 * d; }
+size_t layernorm_bwd_scratch_floats(int M, int d) { return (size_t)((M + LN_ROWS_GENERIC - 1) / LN_ROWS_GENERIC) * 2 * d; }
 
 cudaError_t launch_layernorm_bwd(cudaStream_t st, int dt, const void* x, const void* gamma, const float* mean,
                                  const float* tsave, const double* mean64, const void* dy, const void* dres, int M, int d,
                                  void* dx, float* partial, float* dgamma, float* dbeta) {
   if (M == 0) return cudaSuccess;
   if ((size_t)8 * 2 * d * sizeof(float) > 200 * 1024) return cudaErrorInvalidValue;
-  const int nblk = (M + LN_ROWS - 1) / LN_ROWS;
+  int nblk = (M + LN_ROWS - 1) / LN_ROWS;
   const size_t smem = (size_t)8 * 2 * d * sizeof(float);
   if (smem > 48 * 1024) {
     cudaError_t e = (dt == DT_F32)
@@ -486,9 +490,11 @@ cudaError_t launch_layernorm_bwd(cudaStream_t st, int dt, const void* x, const v
 #undef PCPB_LN_BF16
   PCPB_LN_VEC(1) PCPB_LN_VEC(2) PCPB_LN_VEC(3) PCPB_LN_VEC(4)
 #undef PCPB_LN_VEC
-  if (!done)
+  if (!done) {
+    nblk = (M + LN_ROWS_GENERIC - 1) / LN_ROWS_GENERIC;
     DISPATCH_DT(dt, (k_layernorm_bwd<T><<<nblk, 256, smem, st>>>((const T*)x, (const T*)gamma, mean, tsave, mean64,
-                                                                 (const T*)dy, (const T*)dres, M, d, (T*)dx, partial)));
+                                                                 (const T*)dy, (const T*)dres, M, d, (T*)dx, partial, LN_ROWS_GENERIC)));
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   DISPATCH_DT(dt, (k_ln_param_grads<T><<<cdiv(2 * d, 32), 256, 0, st>>>(partial, nblk, d, dgamma, dbeta, 100.f)));
