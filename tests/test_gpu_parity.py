@@ -316,6 +316,15 @@ def test_diloco_nanogpt_small_f32_baseline_config():
                 adam=dict(beta1=0.9, beta2=0.95, weight_decay=0.1))
 
 
+def test_diloco_f32_tensor_core_gemms_and_tiled_attention():
+    """The fp32 protocol (2 workers, H=10, two outer rounds, per-step loss and parameters within 1e-4) on a nanoGPT shape
+    whose GEMMs take the split-operand tensor-core path and whose attention runs on the tiled f32 kernels (64-wide
+    heads, three query tiles), and on a grouped-query nanochat shape with 64-wide heads."""
+    _run_diloco(GPT_HD64_F32, workers=2, tau=10, rounds=2, lr=3e-4, tol_loss=1e-4, tol_param=1e-4,
+                adam=dict(beta1=0.9, beta2=0.95, weight_decay=0.1))
+    _run_diloco(HD64_F32, workers=2, tau=10, rounds=2, lr=3e-4, tol_loss=1e-4, tol_param=1e-4)
+
+
 def test_diloco_bf16_3_workers():
     _run_diloco(SMALL_BF16, workers=3, tau=4, rounds=2, lr=1e-3, tol_loss=2e-2, tol_param=2e-2, zipf=True)
 
