@@ -162,7 +162,7 @@ __global__ void k_rmsnorm_bwd(const T* __restrict__ x, const float* __restrict__
 template <typename T>
 __global__ void k_embed_norm_bwd(const T* __restrict__ wte, const long long* __restrict__ idx, int d, int V,
                                  const T* __restrict__ dy, const float* __restrict__ tsave,
-                                 float* __restrict__ dwte) {
+                                 float* __restrict__ dwte, T* __restrict__ rows) {
   __shared__ float red[32];
   const size_t m = blockIdx.x;
   long long row = idx[m];
@@ -174,7 +174,8 @@ __global__ void k_embed_norm_bwd(const T* __restrict__ wte, const long long* __r
   for (int j = threadIdx.x; j < d; j += blockDim.x) {
     const float xv = to_f(xr[j]);
     const float g = rnd<T>(adj_edge<T>(to_f(dyr[j]) * r) + adj_edge<T>(ds * (2.f * xv)));
-    atomicAdd(dwte + (size_t)row * d + j, g);
+    if (rows) rows[m * d + j] = from_f<T>(g);                    // summed per token by launch_embed_scatter_sorted
+    else atomicAdd(dwte + (size_t)row * d + j, g);
   }
 }
 
@@ -346,7 +347,21 @@ cudaError_t launch_embed_norm_bwd(cudaStream_t st, int dt, const void* wte, cons
     return cudaGetLastError();
   }
   DISPATCH_DT(dt, (k_embed_norm_bwd<T><<<M, norm_threads(d), 0, st>>>((const T*)wte, idx, d, V, (const T*)dy,
-                                                                       tsave, dwte)));
+                                                                       tsave, dwte, (T*)nullptr)));
+  return cudaGetLastError();
+}
+cudaError_t launch_embed_norm_bwd_rows(cudaStream_t st, int dt, const void* wte, const long long* idx, int M, int d, int V,
+                                       const void* dy, const float* tsave, void* rows) {
+  if (M == 0) return cudaSuccess;
+  if (vec_ok(d, wte, dy, rows)) {
+    // the embedding form of the RMSNorm backward with the row written instead of scattered (same values: the sum of the
+    // two rounded terms, rounded to the model dtype by the store)
+    DISPATCH_DT(dt, (k_rmsnorm_bwd_vec<T><<<cdiv(M, 8), 256, 0, st>>>(nullptr, (const T*)wte, idx, tsave, (const T*)dy,
+                                                                    nullptr, M, d, V, (T*)rows, nullptr)));
+    return cudaGetLastError();
+  }
+  DISPATCH_DT(dt, (k_embed_norm_bwd<T><<<M, norm_threads(d), 0, st>>>((const T*)wte, idx, d, V, (const T*)dy, tsave,
+                                                                       (float*)nullptr, (T*)rows)));
   return cudaGetLastError();
 }
 

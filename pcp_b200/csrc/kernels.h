@@ -64,6 +64,16 @@ cudaError_t launch_window_batch(cudaStream_t st, const void* tokens, int token_b
                                 int batch, long long block, long long* inputs, long long* targets);
 cudaError_t launch_embed_norm_fwd(cudaStream_t st, int dt, const void* wte, const long long* idx, int M, int d,
                                   int V, void* x, float* tsave);
+// Embedding gradient without atomics: dwte[token] = sum of the rows of `rows` ([M, d], model dtype) whose token it is,
+// added in ascending position order, so the result does not depend on timing (the reference's scatter has no such
+// freedom either).  Tokens are sorted by a stable radix sort of (token, position); one block per distinct token walks its
+// positions.  dwte must be zero where a token does not occur (the caller clears it).  scratch: embed_scatter_scratch_bytes.
+size_t embed_scatter_scratch_bytes(int M, int d);
+cudaError_t launch_embed_scatter_sorted(cudaStream_t st, int dt, const long long* idx, int M, int d, int V, const void* rows,
+                                        void* scratch, size_t scratch_bytes, float* dwte);
+// rows != nullptr: write the per-position gradient rows there instead of adding them into dwte
+cudaError_t launch_embed_norm_bwd_rows(cudaStream_t st, int dt, const void* wte, const long long* idx, int M, int d, int V,
+                                       const void* dy, const float* tsave, void* rows);
 cudaError_t launch_embed_norm_bwd(cudaStream_t st, int dt, const void* wte, const long long* idx, int M, int d,
                                   int V, const void* dy, const float* tsave, float* dwte);
 cudaError_t launch_rmsnorm_fwd(cudaStream_t st, int dt, const void* x, int M, int d, void* y, float* tsave);
@@ -96,7 +106,8 @@ struct AttnArgs {
   float* dkv_acc;       // [M, 2*dkv] f32 scratch: dk then dv, zeroed by the launcher
 };
 cudaError_t launch_attn_fwd_generic(cudaStream_t st, int dt, const AttnArgs& a);
-// f32 models with 64-wide heads and T a multiple of 64: tiled SIMT kernels, backward without atomics (attn_f32.cu).
+// f32 models with 16-, 32-, 64- or 128-wide heads and T a multiple of 64: tiled SIMT kernels, backward without atomics
+// (attn_f32.cu).
 // drow: f32 scratch of at least B * H * T elements (the callers pass dkv_acc, which these kernels do not need).
 bool attn_f32_supported(int dt, const AttnArgs& a);
 cudaError_t launch_attn_f32_fwd(cudaStream_t st, const AttnArgs& a);

@@ -56,9 +56,11 @@ __global__ void k_embed_pos_bwd(const long long* __restrict__ idx, int B, int Tl
       const size_t m = (size_t)b * Tlen + t;
       const float g = to_f(dx[m * d + j]);
       acc += g;
-      long long row = idx[m];
-      row = row < 0 ? 0 : (row >= V ? V - 1 : row);
-      atomicAdd(dwte + (size_t)row * d + j, g);
+      if (dwte) {                                             // else: summed per token by launch_embed_scatter_sorted
+        long long row = idx[m];
+        row = row < 0 ? 0 : (row >= V ? V - 1 : row);
+        atomicAdd(dwte + (size_t)row * d + j, g);
+      }
     }
     dwpe[i] = acc;
   }

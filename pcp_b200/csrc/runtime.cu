@@ -188,6 +188,14 @@ int build_workspace(pcpb_backend* b) {
       WS(b, w.tc_scratch, want); w.tc_scratch_bytes = want;
     }
   }
+  // the embedding gradient is a sort + segmented sum (no float atomics); PCPB_EMBED_ATOMIC=1 keeps the atomic scatter
+  {
+    const char* e = getenv("PCPB_EMBED_ATOMIC");
+    if (!(e && e[0] == '1')) {
+      w.emb_scratch_bytes = embed_scatter_scratch_bytes((int)M, (int)d);
+      WS(b, w.emb_scratch, w.emb_scratch_bytes);
+    }
+  }
   WS(b, w.tc_err, sizeof(int));
   CK(b, cudaMemset(w.tc_err, 0, sizeof(int)));
   w.ready = true;
@@ -379,7 +387,13 @@ int forward_backward(pcpb_backend* b, const void* wts, const long long* ids, con
     KL(b, 1, launch_rmsnorm_bwd(st, dt, w.xs[l], a.t1, w.dh, w.dx, M, d, w.dx));
   }
   CK(b, cudaMemsetAsync(GR(0), 0, (size_t)c.params[0].numel * 4, st));
-  KL(b, 1, launch_embed_norm_bwd(st, dt, W(0), ids, M, d, V, w.dx, w.t0, GR(0)));
+  if (w.emb_scratch) {
+    // per-position gradient rows into dh (free by now), then summed per token in position order
+    KL(b, 1, launch_embed_norm_bwd_rows(st, dt, W(0), ids, M, d, V, w.dx, w.t0, w.dh));
+    KL(b, 4, launch_embed_scatter_sorted(st, dt, ids, M, d, V, w.dh, w.emb_scratch, w.emb_scratch_bytes, GR(0)));
+  } else {
+    KL(b, 1, launch_embed_norm_bwd(st, dt, W(0), ids, M, d, V, w.dx, w.t0, GR(0)));
+  }
   KL(b, 1, launch_round_guard_f32(st, dt, GR(0), (size_t)c.params[0].numel, 100.f));
   return PCPB_OK;
 }
@@ -490,7 +504,12 @@ int forward_backward_gpt(pcpb_backend* b, const void* wts, const long long* ids,
                                   GR(p0), GR(p0 + 1)));
   }
   CK(b, cudaMemsetAsync(GR(0), 0, (size_t)c.params[0].numel * 4, st));
-  KL(b, 1, launch_embed_pos_bwd(st, dt, ids, Bn, Tn, d, V, w.dx, GR(0), GR(1)));
+  if (w.emb_scratch) {
+    KL(b, 1, launch_embed_pos_bwd(st, dt, ids, Bn, Tn, d, V, w.dx, nullptr, GR(1)));        // position-embedding gradient only
+    KL(b, 4, launch_embed_scatter_sorted(st, dt, ids, M, d, V, w.dx, w.emb_scratch, w.emb_scratch_bytes, GR(0)));
+  } else {
+    KL(b, 1, launch_embed_pos_bwd(st, dt, ids, Bn, Tn, d, V, w.dx, GR(0), GR(1)));
+  }
   KL(b, 1, launch_round_guard_f32(st, dt, GR(0), (size_t)(c.params[0].numel + c.params[1].numel), 100.f));
   return PCPB_OK;
 }

@@ -55,6 +55,7 @@ struct Workspace {
   void* tc_scratch = nullptr; size_t tc_scratch_bytes = 0; int* tc_err = nullptr;
   // f32 models on the tensor cores: operands split into three bf16 pieces and packed [rows, 6 K] (launch_split3_pack),
   // the f32 result before its epilogue
+  void* emb_scratch = nullptr; size_t emb_scratch_bytes = 0;   // sorted embedding-gradient scatter (keys, positions, partials)
   void *pk_a = nullptr, *pk_b = nullptr; float* pk_c = nullptr;
   size_t pk_ab_bytes = 0, pk_c_bytes = 0;
   float* loss_record = nullptr;    // device, one per inner step of a round

@@ -26,6 +26,19 @@ def _adam(be, conf):
     be.set_adam(conf.learning_rate, conf.beta1, conf.beta2, conf.epsilon, conf.weight_decay, conf.max_grad_norm)
 
 
+def _grads(be, cfg, params, x, y):
+    """compute_gradients through the C ABI -> (list of f32 gradient arrays, loss)."""
+    bufs = [be.move_to_device(p.numpy(), p.shape, F32) for p in params]
+    bx = be.move_to_device(x, x.shape, I64)
+    by = be.move_to_device(y, y.shape, I64)
+    outs = be.execute_with_device_buffers(None, "compute_gradients", bufs + [bx, by])
+    grads = [be.read_to_host(o, F32, p.shape) for o, p in zip(outs[:-1], params)]
+    loss = float(be.read_to_host(outs[-1], F32, ())[()])
+    for b in bufs + [bx, by] + outs:
+        b.release()
+    return grads, loss
+
+
 def _close(got, want, tol=1e-4):
     diff = np.abs(got.astype(np.float64) - want.astype(np.float64))
     bad = diff > tol + tol * np.abs(want)
@@ -450,3 +463,39 @@ def test_adjoint_status_reports_clamping(cfgd):
                 b.release()
         for b in bufs:
             b.release()
+
+
+@pytest.mark.parametrize("cfgd", [dict(vocab=512, d_model=256, n_layer=1, n_head=4, n_kv_head=2, seq_len=192, batch=2, dtype="f32"),
+                                  dict(vocab=65, d_model=128, n_layer=1, n_head=2, seq_len=192, batch=2, dtype="f32", activation="gelu"),
+                                  dict(vocab=512, d_model=256, n_layer=1, n_head=2, n_kv_head=2, seq_len=256, batch=1, dtype="bf16")])
+def test_gradients_are_bit_identical_from_run_to_run(cfgd):
+    """The embedding gradient is a sort + segmented sum in position order and the f32 attention backward has no atomics,
+    so repeated evaluations of the same step give the same bits.  The token stream has one token on two thirds of the
+    positions (runs of equal keys that cross several 128-entry chunks of the sorted order), a few tokens once, and the
+    largest token id; the gradient of the frequent row is also checked against the oracle."""
+    cfg, text = make_model(cfgd)
+    rng = np.random.default_rng(5)
+    n = cfg.batch * cfg.seq_len
+    ids = rng.integers(0, cfg.vocab, size=n)
+    ids[rng.random(n) < 0.66] = 7
+    ids[3] = cfg.vocab - 1
+    x = ids.reshape(cfg.batch, cfg.seq_len).astype(np.int64)
+    y = np.roll(ids, -1).reshape(cfg.batch, cfg.seq_len).astype(np.int64)
+    params = seeded_params(cfg, seed=2, std=0.05)
+    runs = []
+    with Backend(0) as be:
+        be.load_session(text)
+        for _ in range(3):
+            runs.append(_grads(be, cfg, params, x, y))
+    for g, loss in runs[1:]:
+        assert loss == runs[0][1]
+        for a, b in zip(g, runs[0][0]):
+            assert np.array_equal(a, b)
+    g_ref, _ = TrainingModule(text).compute_gradients(params, torch.from_numpy(x), torch.from_numpy(y))
+    tol = 1e-4 if cfg.dtype == "f32" else 4e-2
+    got, want = runs[0][0][0], g_ref[0].numpy()
+    assert np.abs(got - want).max() <= tol * np.abs(want).max()
+    assert np.abs(got[7] - want[7]).max() <= tol * np.abs(want).max()
+    absent = sorted(set(range(cfg.vocab)) - set(ids.tolist()))
+    if absent:
+        assert not got[absent].any()                                       # rows of tokens that do not occur stay zero
