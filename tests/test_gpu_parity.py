@@ -224,8 +224,8 @@ def _close(got, want, tol, dtype):
     (test/nanochat/test_pcp_training_step_parity.py:38), for all but at most one element in 10^4, which must still be
     within 10 * tol; plus the same tol on the relative L2 error of the whole vector.  The allowance is for elements
     whose gradient is of the size of Adam's epsilon (1e-8): their update lr * g / (|g| + eps) amplifies last-bit
-    differences of g (embedding and generic-attention gradients are accumulated with float atomics, so these differ
-    from run to run) into a fraction of a step; one such element of 109377 shows up in about one run in ten.
+    differences of g (the device adds in another order than the oracle; shapes on the generic attention kernel also add
+    with float atomics) into a fraction of a step; one such element of 109377 shows up in about one run in ten.
     bf16: relative L2 error of the whole parameter vector — the same amplification acts on bf16 rounding noise, so
     an element-wise bound is not meaningful there (the reference states its bf16 tolerance on the loss curve)."""
     err = np.linalg.norm(got.astype(np.float64) - want.astype(np.float64)) / np.linalg.norm(want.astype(np.float64))
