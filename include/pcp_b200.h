@@ -58,8 +58,19 @@ int pcpb_load_artifact(pcpb_backend* b, const void* bytes, size_t n);
 
 /* ModelInspector.inspect without a device (src/mlir/model_introspection.zig:251-312): parses the artefact and
  * writes vocab, d_model, layers, heads, kv_heads, head_dim, mlp width, batch, block, model dtype, number of
- * parameter tensors, total parameter count into facts[12].  err (may be NULL) receives the reason on failure. */
+ * parameter tensors, total parameter count into facts[12].  err (may be NULL) receives the reason on failure.
+ * For a graph of neither fused family (run op by op by the general front end) d_model, layers, heads, kv_heads,
+ * head_dim and mlp width are 0, and vocab is the first parameter's row count. */
 int pcpb_inspect_artifact(const void* bytes, size_t n, int64_t* facts, char* err, size_t err_cap);
+
+/* The general front end's view of a forward graph, for graphs outside the two fused families: what the reference's
+ * AD engine does when it emits the gradient function next to the forward function (src/autodiff/engine.zig:196-348,
+ * rules src/autodiff/vjp_rules.zig, adjoint edges engine.zig:604-702), after the stability patches of
+ * src/compiler/sanitizer.zig:8-244.  Writes the tensor program (one line per value and per op; forward ops first, then,
+ * if with_gradients, the gradient ops for every argument but the last two) as text into *text_out (release with
+ * pcpb_free).  Needs no device.  A graph pcpb_inspect_artifact reports with d_model = 0 is run from this program
+ * (one kernel per op); PCPB_FRONTEND=graph in the environment sends every graph that way, PCPB_FRONTEND=fused none. */
+int pcpb_graph_describe(const void* bytes, size_t n, int with_gradients, char** text_out, char* err, size_t err_cap);
 
 /* Model facts recovered from the artefact (src/mlir/model_introspection.zig:251-312: parameters are all
  * @main arguments except the last two).  shape_out receives up to 8 dims. */

@@ -35,7 +35,7 @@ LIB_PATH = os.environ.get("PCPB_LIBRARY") or os.path.join(os.path.dirname(os.pat
 
 EXPORTS = [
     "pcpb_create", "pcpb_destroy", "pcpb_backend_type", "pcpb_last_error", "pcpb_free", "pcpb_load_artifact",
-    "pcpb_inspect_artifact", "pcpb_num_params", "pcpb_param_shape", "pcpb_model_info", "pcpb_buffer_from_host", "pcpb_buffer_zeros",
+    "pcpb_inspect_artifact", "pcpb_graph_describe", "pcpb_num_params", "pcpb_param_shape", "pcpb_model_info", "pcpb_buffer_from_host", "pcpb_buffer_zeros",
     "pcpb_buffer_retain", "pcpb_buffer_release", "pcpb_buffer_nbytes", "pcpb_execute", "pcpb_read_to_host",
     "pcpb_execute_host", "pcpb_op_gemm", "pcpb_fifo_get_batch", "pcpb_set_adam", "pcpb_worker_begin_round", "pcpb_worker_set_tokens", "pcpb_worker_step",
     "pcpb_worker_end_round", "pcpb_inner_loop", "pcpb_worker_read_state", "pcpb_synchronize", "pcpb_outer_export",
@@ -110,6 +110,7 @@ def load_library(path: str | None = None):
     lib.pcpb_free.argtypes = [vp]; lib.pcpb_free.restype = None
     lib.pcpb_load_artifact.argtypes = [vp, vp, sz]
     lib.pcpb_inspect_artifact.argtypes = [vp, sz, C.POINTER(C.c_int64), C.c_char_p, sz]
+    lib.pcpb_graph_describe.argtypes = [vp, sz, i, C.POINTER(vp), C.c_char_p, sz]
     lib.pcpb_num_params.argtypes = [vp]
     lib.pcpb_param_shape.argtypes = [vp, i, C.POINTER(C.c_int64), C.POINTER(i)]
     lib.pcpb_model_info.argtypes = [vp, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64),
@@ -264,7 +265,24 @@ def inspect_artifact(artifact) -> dict:
         raise BackendError(rc, err.value.decode())
     keys = ["vocab", "d_model", "n_layer", "n_head", "n_kv_head", "head_dim", "d_ff", "batch", "block", "dtype",
             "num_tensors", "total_params"]
-    return dict(zip(keys, [int(x) for x in facts]))
+    out = dict(zip(keys, [int(x) for x in facts]))
+    out["family"] = "graph" if out["d_model"] == 0 else "fused"      # graph: run op by op by the general front end
+    return out
+
+
+def graph_describe(artifact, with_gradients: bool = True) -> str:
+    """The general front end's tensor program of a forward graph as text (see include/pcp_b200.h); no GPU needed."""
+    lib = load_library()
+    raw = artifact.encode() if isinstance(artifact, str) else artifact
+    text = C.c_void_p()
+    err = C.create_string_buffer(512)
+    rc = lib.pcpb_graph_describe(raw, len(raw), 1 if with_gradients else 0, C.byref(text), err, 512)
+    if rc:
+        raise BackendError(rc, err.value.decode())
+    try:
+        return C.string_at(text).decode()
+    finally:
+        lib.pcpb_free(text)
 
 
 NOALLOC_MAX_ELEMS = 1 << 26

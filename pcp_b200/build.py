@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libpcp_b200.so")
-SOURCES = ["kernels.cu", "kernels_gpt.cu", "gemm_tc.cu", "attn_flash.cu", "attn_tc.cu", "attn_f32.cu", "embed_scatter.cu", "runtime.cu", "rollout.cu", "noalloc.cu", "model.cpp", "host_data.cpp"]
+SOURCES = ["kernels.cu", "kernels_gpt.cu", "gemm_tc.cu", "attn_flash.cu", "attn_tc.cu", "attn_f32.cu", "embed_scatter.cu", "runtime.cu", "graph_exec.cu", "rollout.cu", "noalloc.cu", "model.cpp", "graph.cpp", "host_data.cpp"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

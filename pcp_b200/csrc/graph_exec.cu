@@ -1,0 +1,893 @@
+// Executor of the general StableHLO front end: planning (host) and the per-op kernels.  See graph_exec.h / graph.h.
+//
+// Element semantics follow the StableHLO specification as the reference's runtime implements it for these graphs:
+// bf16 ops compute in f32 and round once to bf16, f64 stays f64, integer division truncates, reductions of f32 / bf16
+// accumulate in f32.  Every kernel is a grid-stride loop over the elements of its result; index arithmetic for the
+// strided ops (transpose, broadcast, slice, concatenate, reduce) is a mixed-radix walk over at most 8 dimensions.
+#include "graph_exec.h"
+
+#include <math.h>
+#include <string.h>
+
+#include <map>
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace pcpb {
+
+namespace {
+
+constexpr int MAX_RANK = 8;
+constexpr int TPB = 256;
+
+// ------------------------------------------------------------------------------------------------
+// element types
+// ------------------------------------------------------------------------------------------------
+template <typename T> struct TT;
+template <> struct TT<float> { typedef float C; static constexpr bool is_fp = true; };
+template <> struct TT<bf16> { typedef float C; static constexpr bool is_fp = true; };
+template <> struct TT<double> { typedef double C; static constexpr bool is_fp = true; };
+template <> struct TT<long long> { typedef long long C; static constexpr bool is_fp = false; };
+template <> struct TT<int> { typedef long long C; static constexpr bool is_fp = false; };
+template <> struct TT<uint8_t> { typedef long long C; static constexpr bool is_fp = false; };      // i1
+
+template <typename T> __device__ __forceinline__ typename TT<T>::C ld(const T* p, long long i) { return (typename TT<T>::C)p[i]; }
+template <> __device__ __forceinline__ float ld<bf16>(const bf16* p, long long i) { return __bfloat162float(p[i]); }
+
+template <typename T, typename C> __device__ __forceinline__ T narrow(C c) {
+  if constexpr (std::is_same<T, bf16>::value) return __float2bfloat16_rn((float)c);
+  else if constexpr (std::is_same<T, uint8_t>::value) return (uint8_t)(c != 0);
+  else return (T)c;
+}
+
+// ------------------------------------------------------------------------------------------------
+// kernels
+// ------------------------------------------------------------------------------------------------
+#define GRID_STRIDE(i, n) for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (n); i += (long long)gridDim.x * blockDim.x)
+
+template <typename T> __global__ void k_fill(T* out, long long n, double f, long long iv) {
+  T v;
+  if constexpr (TT<T>::is_fp) {
+    if constexpr (std::is_same<T, double>::value) v = f; else v = narrow<T, float>((float)f);
+  } else v = narrow<T, long long>(iv);
+  GRID_STRIDE(i, n) out[i] = v;
+}
+
+template <typename T> __global__ void k_iota(T* out, long long n, long long inner, long long extent) {
+  GRID_STRIDE(i, n) out[i] = narrow<T, long long>((i / inner) % extent);
+}
+
+template <typename C> __device__ __forceinline__ C unary_fp(int sub, C x) {
+  switch (sub) {
+    case U_RSQRT: return C(1) / sqrt(x);
+    case U_SQRT: return sqrt(x);
+    case U_EXP: return exp(x);
+    case U_LOG: return log(x);
+    case U_TANH: return tanh(x);
+    case U_LOGISTIC: return C(1) / (C(1) + exp(-x));
+    case U_NEG: return -x;
+    case U_CEIL: return ceil(x);
+    case U_FLOOR: return floor(x);
+    case U_SIN: return sin(x);
+    case U_COS: return cos(x);
+    default: return fabs(x);
+  }
+}
+
+template <typename T> __global__ void k_unary(int sub, const T* in, T* out, long long n) {
+  typedef typename TT<T>::C C;
+  GRID_STRIDE(i, n) {
+    const C x = ld(in, i);
+    if constexpr (TT<T>::is_fp) out[i] = narrow<T, C>(unary_fp<C>(sub, x));
+    else out[i] = narrow<T, C>(sub == U_NEG ? -x : (sub == U_ABS ? (x < 0 ? -x : x) : x));
+  }
+}
+
+template <typename C> __device__ __forceinline__ C pow_fp(C x, C e) {
+  // the cases the exporters produce, exact like the CPU library's fast paths; pow() otherwise
+  if (e == C(2)) return x * x;
+  if (e == C(3)) return (x * x) * x;
+  if (e == C(1)) return x;
+  if (e == C(0.5)) return sqrt(x);
+  return pow(x, e);
+}
+
+template <typename T> __global__ void k_binary(int sub, const T* a, const T* b, T* out, long long n) {
+  typedef typename TT<T>::C C;
+  GRID_STRIDE(i, n) {
+    const C x = ld(a, i), y = ld(b, i);
+    C r;
+    if constexpr (TT<T>::is_fp) {
+      switch (sub) {
+        case B_ADD: r = x + y; break;
+        case B_SUB: r = x - y; break;
+        case B_MUL: r = x * y; break;
+        case B_DIV: r = x / y; break;
+        case B_POW: r = pow_fp<C>(x, y); break;
+        case B_MAX: r = (x != x || y != y) ? (x + y) : (x > y ? x : y); break;       // NaN propagates
+        default: r = (x != x || y != y) ? (x + y) : (x < y ? x : y); break;
+      }
+    } else {
+      switch (sub) {
+        case B_ADD: r = x + y; break;
+        case B_SUB: r = x - y; break;
+        case B_MUL: r = x * y; break;
+        case B_DIV: r = y == 0 ? 0 : x / y; break;
+        case B_MAX: r = x > y ? x : y; break;
+        case B_MIN: r = x < y ? x : y; break;
+        case B_AND: r = x & y; break;
+        case B_OR: r = x | y; break;
+        default: r = 0; break;
+      }
+    }
+    out[i] = narrow<T, C>(r);
+  }
+}
+
+template <typename T> __global__ void k_compare(int dir, const T* a, const T* b, uint8_t* out, long long n) {
+  typedef typename TT<T>::C C;
+  GRID_STRIDE(i, n) {
+    const C x = ld(a, i), y = ld(b, i);
+    bool r;
+    switch (dir) {
+      case C_EQ: r = x == y; break;
+      case C_NE: r = x != y; break;
+      case C_GE: r = x >= y; break;
+      case C_GT: r = x > y; break;
+      case C_LE: r = x <= y; break;
+      default: r = x < y; break;
+    }
+    out[i] = r;
+  }
+}
+
+template <typename U> __global__ void k_select(const uint8_t* pred, const U* a, const U* b, U* out, long long n) {
+  GRID_STRIDE(i, n) out[i] = pred[i] ? a[i] : b[i];
+}
+
+template <typename TI, typename TO> __global__ void k_convert(const TI* in, TO* out, long long n) {
+  typedef typename TT<TI>::C CI;
+  GRID_STRIDE(i, n) {
+    const CI x = ld(in, i);
+    if constexpr (TT<TI>::is_fp && !TT<TO>::is_fp) {
+      if constexpr (std::is_same<TO, uint8_t>::value) out[i] = (uint8_t)(x != CI(0));
+      else out[i] = (TO)(long long)trunc(x);
+    } else if constexpr (std::is_same<TO, bf16>::value) out[i] = __float2bfloat16_rn((float)x);     // via f32, like the CPU library
+    else out[i] = narrow<TO, CI>(x);
+  }
+}
+
+// adjoint edge (src/autodiff/engine.zig:622-682): (g - g) == 0 ? g : 0, then clamp in f32 and back to the element type
+template <typename T> __global__ void k_guard_clamp(const T* in, T* out, long long n, int clamp, float lo, float hi) {
+  typedef typename TT<T>::C C;
+  GRID_STRIDE(i, n) {
+    C g = ld(in, i);
+    if (!((g - g) == C(0))) g = C(0);
+    if (clamp) g = (C)fminf(fmaxf((float)g, lo), hi);
+    out[i] = narrow<T, C>(g);
+  }
+}
+
+struct NdDesc {            // walk over `rank` dimensions of extents dim[], the other side's strides in stride[]
+  int rank;
+  long long dim[MAX_RANK], stride[MAX_RANK], offset;
+};
+
+// out[i] = in[offset + sum coord_k * stride_k]: transpose, broadcast_in_dim, slice
+template <typename U> __global__ void k_gather_nd(const U* in, U* out, long long n, NdDesc d) {
+  GRID_STRIDE(i, n) {
+    long long rem = i, src = d.offset;
+    for (int k = d.rank - 1; k >= 0; --k) { src += (rem % d.dim[k]) * d.stride[k]; rem /= d.dim[k]; }
+    out[i] = in[src];
+  }
+}
+
+// out[offset + sum coord_k * stride_k] = in[i]: concatenate (one launch per operand), pad
+template <typename U> __global__ void k_scatter_nd(const U* in, U* out, long long n, NdDesc d) {
+  GRID_STRIDE(i, n) {
+    long long rem = i, dst = d.offset;
+    for (int k = d.rank - 1; k >= 0; --k) { dst += (rem % d.dim[k]) * d.stride[k]; rem /= d.dim[k]; }
+    out[dst] = in[i];
+  }
+}
+
+struct RedDesc {
+  int krank, rrank;
+  long long kdim[MAX_RANK], kstr[MAX_RANK], rdim[MAX_RANK], rstr[MAX_RANK];
+  long long n_out, n_red;
+};
+
+// GROUP threads per result element (1 or 32); f32 / bf16 accumulate in f32, f64 in f64, integers in i64; the result is
+// rounded to the element type and then combined with the init value, as "reduce then op with init" evaluates
+template <typename T, int KIND, int GROUP> __global__ void k_reduce(const T* in, const T* init, T* out, RedDesc d) {
+  typedef typename TT<T>::C C;
+  const long long gid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long o = gid / GROUP;
+  const int lane = (int)(gid % GROUP);
+  if (o >= d.n_out) return;                                  // GROUP == 32: a whole warp leaves together
+  long long base = 0, rem = o;
+  for (int k = d.krank - 1; k >= 0; --k) { base += (rem % d.kdim[k]) * d.kstr[k]; rem /= d.kdim[k]; }
+  C acc;
+  if constexpr (KIND == R_ADD) acc = C(0);
+  else if constexpr (TT<T>::is_fp) acc = (C)(-INFINITY);
+  else acc = (C)(-0x7FFFFFFFFFFFFFFFLL - 1);
+  for (long long r = lane; r < d.n_red; r += GROUP) {
+    long long off = base, q = r;
+    for (int k = d.rrank - 1; k >= 0; --k) { off += (q % d.rdim[k]) * d.rstr[k]; q /= d.rdim[k]; }
+    const C x = ld(in, off);
+    if constexpr (KIND == R_ADD) acc += x; else acc = (x > acc || x != x) ? x : acc;
+  }
+  if constexpr (GROUP == 32) {
+    for (int s = 16; s > 0; s >>= 1) {
+      const C y = __shfl_xor_sync(0xffffffffu, acc, s);
+      if constexpr (KIND == R_ADD) acc += y; else acc = (y > acc || y != y) ? y : acc;
+    }
+  }
+  if (lane == 0) {
+    const T rounded = narrow<T, C>(acc);
+    const C a = ld(&rounded, 0), b = ld(init, 0);
+    out[o] = narrow<T, C>(KIND == R_ADD ? a + b : ((b > a || b != b) ? b : a));
+  }
+}
+
+struct DotDesc { long long ab, am, ak, bb, bk, bn; int M, N, K; };
+
+// C[b, m, n] = sum_k A[b, m, k] B[b, k, n] over strided operands; 64 x 64 tile per block, 4 x 4 per thread, k in order
+template <typename T> __global__ void __launch_bounds__(256) k_dot(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ Cm, DotDesc s) {
+  typedef typename TT<T>::C C;
+  __shared__ C As[16][65], Bs[16][65];
+  const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  const long long bz = blockIdx.z;
+  const T* Ab = A + bz * s.ab;
+  const T* Bb = B + bz * s.bb;
+  C acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = C(0);
+  for (int k0 = 0; k0 < s.K; k0 += 16) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int e = tid + i * 256;
+      int mm, kk;
+      if (s.ak == 1) { kk = e % 16; mm = e / 16; } else { mm = e % 64; kk = e / 64; }
+      const int gm = m0 + mm, gk = k0 + kk;
+      As[kk][mm] = (gm < s.M && gk < s.K) ? ld(Ab, gm * s.am + gk * s.ak) : C(0);
+      int nn, k2;
+      if (s.bn == 1) { nn = e % 64; k2 = e / 64; } else { k2 = e % 16; nn = e / 16; }
+      const int gn = n0 + nn, gk2 = k0 + k2;
+      Bs[k2][nn] = (gn < s.N && gk2 < s.K) ? ld(Bb, gk2 * s.bk + gn * s.bn) : C(0);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      C a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { a[i] = As[kk][ty * 4 + i]; b[i] = Bs[kk][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] += a[i] * b[j];
+    }
+    __syncthreads();
+  }
+  T* Cb = Cm + bz * (long long)s.M * s.N;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int gm = m0 + ty * 4 + i;
+    if (gm >= s.M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn < s.N) Cb[(long long)gm * s.N + gn] = narrow<T, C>(acc[i][j]);
+    }
+  }
+}
+
+template <typename U> __global__ void k_gather_rows(const U* x, const long long* idx, U* out, long long n, long long rowlen, long long R) {
+  GRID_STRIDE(i, n) {
+    long long r = idx[i / rowlen];
+    r = r < 0 ? 0 : (r > R - 1 ? R - 1 : r);
+    out[i] = x[r * rowlen + i % rowlen];
+  }
+}
+
+template <typename U> __global__ void k_gather2(const U* x, const long long* idx, U* out, long long n, long long R, long long Cn) {
+  GRID_STRIDE(i, n) {
+    long long r = idx[2 * i], c = idx[2 * i + 1];
+    r = r < 0 ? 0 : (r > R - 1 ? R - 1 : r);
+    c = c < 0 ? 0 : (c > Cn - 1 ? Cn - 1 : c);
+    out[i] = x[r * Cn + c];
+  }
+}
+
+template <typename T> __device__ __forceinline__ void atomic_add_t(T* p, T v) { atomicAdd(p, v); }
+
+// scatter-add of the gradient rows (the result was zeroed before): sums arrive in any order
+template <typename T> __global__ void k_scatter_rows(const T* g, const long long* idx, T* out, long long n, long long rowlen, long long R) {
+  GRID_STRIDE(i, n) {
+    long long r = idx[i / rowlen];
+    r = r < 0 ? 0 : (r > R - 1 ? R - 1 : r);
+    atomic_add_t(out + r * rowlen + i % rowlen, g[i]);
+  }
+}
+
+template <typename T> __global__ void k_scatter2(const T* g, const long long* idx, T* out, long long n, long long R, long long Cn) {
+  GRID_STRIDE(i, n) {
+    const long long r = idx[2 * i], c = idx[2 * i + 1];
+    if (r < 0 || r >= R || c < 0 || c >= Cn) continue;
+    atomic_add_t(out + r * Cn + c, g[i]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// launch helpers
+// ------------------------------------------------------------------------------------------------
+int blocks_for(long long n) {
+  long long b = (n + TPB - 1) / TPB;
+  if (b < 1) b = 1;
+  if (b > 148 * 32) b = 148 * 32;
+  return (int)b;
+}
+
+std::vector<long long> row_major_strides(const std::vector<int64_t>& shape) {
+  std::vector<long long> s(shape.size(), 1);
+  for (int i = (int)shape.size() - 2; i >= 0; --i) s[i] = s[i + 1] * shape[i + 1];
+  return s;
+}
+
+#define BY_SIZE(es, ...)                                   \
+  switch (es) {                                             \
+    case 1: { typedef uint8_t U; __VA_ARGS__; break; }             \
+    case 2: { typedef uint16_t U; __VA_ARGS__; break; }            \
+    case 4: { typedef uint32_t U; __VA_ARGS__; break; }            \
+    default: { typedef unsigned long long U; __VA_ARGS__; break; } \
+  }
+
+#define BY_TYPE(dt, ...)                                   \
+  switch (dt) {                                             \
+    case DT_F32: { typedef float T; __VA_ARGS__; break; }          \
+    case DT_BF16: { typedef bf16 T; __VA_ARGS__; break; }          \
+    case DT_F64: { typedef double T; __VA_ARGS__; break; }         \
+    case DT_I64: { typedef long long T; __VA_ARGS__; break; }      \
+    case DT_I32: { typedef int T; __VA_ARGS__; break; }            \
+    default: { typedef uint8_t T; __VA_ARGS__; break; }            \
+  }
+
+#define BY_FLOAT(dt, ...)                                  \
+  switch (dt) {                                             \
+    case DT_F32: { typedef float T; __VA_ARGS__; break; }          \
+    case DT_BF16: { typedef bf16 T; __VA_ARGS__; break; }          \
+    default: { typedef double T; __VA_ARGS__; break; }             \
+  }
+
+bool is_fp(int dt) { return dt == DT_F32 || dt == DT_BF16 || dt == DT_F64; }
+bool known(int dt) { return is_fp(dt) || dt == DT_I64 || dt == DT_I32 || dt == DT_BOOL; }
+
+template <typename TI> void convert_from(cudaStream_t st, const void* in, void* out, int dto, long long n) {
+  const int nb = blocks_for(n);
+  switch (dto) {
+    case DT_F32: k_convert<TI, float><<<nb, TPB, 0, st>>>((const TI*)in, (float*)out, n); break;
+    case DT_BF16: k_convert<TI, bf16><<<nb, TPB, 0, st>>>((const TI*)in, (bf16*)out, n); break;
+    case DT_F64: k_convert<TI, double><<<nb, TPB, 0, st>>>((const TI*)in, (double*)out, n); break;
+    case DT_I64: k_convert<TI, long long><<<nb, TPB, 0, st>>>((const TI*)in, (long long*)out, n); break;
+    case DT_I32: k_convert<TI, int><<<nb, TPB, 0, st>>>((const TI*)in, (int*)out, n); break;
+    default: k_convert<TI, uint8_t><<<nb, TPB, 0, st>>>((const TI*)in, (uint8_t*)out, n); break;
+  }
+}
+
+void convert(cudaStream_t st, const void* in, int dti, void* out, int dto, long long n) {
+  BY_TYPE(dti, convert_from<T>(st, in, out, dto, n));
+}
+
+// a group of dimensions (in the given order) of a row-major tensor as ONE strided dimension; false if they do not
+// lie in memory like one
+bool collapse(const std::vector<int64_t>& shape, const std::vector<long long>& strides, const std::vector<int64_t>& dims,
+              long long* size, long long* stride) {
+  long long n = 1, st = 1;
+  bool have = false;
+  for (int i = (int)dims.size() - 1; i >= 0; --i) {
+    const int64_t d = dims[i];
+    if (shape[d] == 1) continue;
+    if (!have) { st = strides[d]; n = shape[d]; have = true; continue; }
+    if (strides[d] != st * n) return false;
+    n *= shape[d];
+  }
+  *size = n; *stride = have ? st : 1;
+  return true;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------------
+// plan
+// ------------------------------------------------------------------------------------------------
+struct GraphExec {
+  Graph g;
+  int n_params = 0;
+  std::vector<int64_t> param_offsets;
+  std::vector<int> root;                 // value -> the value whose storage it shares
+  std::vector<char> where;               // per root: 0 external (argument), 1 constant arena, 2 step arena
+  std::vector<long long> off;            // per root: byte offset in its arena
+  std::vector<char> need_fwd, need_all;  // per op
+  std::vector<char> is_const_op;
+  char *const_arena = nullptr, *arena = nullptr;
+  size_t const_bytes = 0, arena_bytes = 0;
+  std::vector<const void*> ext;          // per value: pointer of an external value (set per run)
+};
+
+namespace {
+
+enum { W_EXT = 0, W_CONST = 1, W_STEP = 2 };
+
+size_t round256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+struct FreeList {
+  std::map<size_t, size_t> free_;        // offset -> size
+  size_t end = 0;
+  size_t alloc(size_t n) {
+    // best fit
+    auto best = free_.end();
+    for (auto it = free_.begin(); it != free_.end(); ++it)
+      if (it->second >= n && (best == free_.end() || it->second < best->second)) best = it;
+    if (best != free_.end()) {
+      const size_t o = best->first, sz = best->second;
+      free_.erase(best);
+      if (sz > n) free_[o + n] = sz - n;
+      return o;
+    }
+    // grow; a free block touching the end is extended
+    if (!free_.empty()) {
+      auto last = std::prev(free_.end());
+      if (last->first + last->second == end) {
+        const size_t o = last->first;
+        free_.erase(last);
+        end = o + n;
+        return o;
+      }
+    }
+    const size_t o = end;
+    end += n;
+    return o;
+  }
+  void release(size_t o, size_t n) {
+    auto it = free_.emplace(o, n).first;
+    auto nx = std::next(it);
+    if (nx != free_.end() && it->first + it->second == nx->first) { it->second += nx->second; free_.erase(nx); }
+    if (it != free_.begin()) {
+      auto pv = std::prev(it);
+      if (pv->first + pv->second == it->first) { pv->second += it->second; free_.erase(it); }
+    }
+  }
+};
+
+void* ptr_of(const GraphExec& e, int v) {
+  const int r = e.root[v];
+  if (e.where[r] == W_EXT) return const_cast<void*>(e.ext[r]);
+  return (e.where[r] == W_CONST ? e.const_arena : e.arena) + e.off[r];
+}
+
+#define LAUNCH_CHECK() do { cudaError_t le__ = cudaGetLastError(); if (le__ != cudaSuccess) return std::string("kernel launch failed: ") + cudaGetErrorString(le__); } while (0)
+
+// Runs one op (dry = true: only checks that it is supported).
+std::string run_op(GraphExec& e, const GOp& op, cudaStream_t st, bool dry, const std::function<int(int, const GemmArgs&)>* dot2d,
+                   long long* launches) {
+  const Graph& g = e.g;
+  const GValue& o = g.vals[op.out];
+  const long long n = o.numel;
+  if (!known(o.dt)) return "unsupported element type";
+  if (o.shape.size() > MAX_RANK) return "rank above 8";
+  for (int i : op.in) if (!known(g.vals[i].dt) || g.vals[i].shape.size() > MAX_RANK) return "unsupported operand type";
+  void* out = dry ? nullptr : ptr_of(e, op.out);
+  auto in = [&](int k) -> const void* { return dry ? nullptr : ptr_of(e, op.in[k]); };
+  auto count = [&](int k) { if (launches) *launches += k; };
+  const int nb = blocks_for(n);
+  const size_t es = dtype_size(o.dt);
+  switch (op.kind) {
+    case G_CONST_SPLAT:
+    case G_SEED:
+      if (dry) return "";
+      BY_TYPE(o.dt, k_fill<T><<<nb, TPB, 0, st>>>((T*)out, n, op.fval, op.ival));
+      count(1);
+      break;
+    case G_CONST_DATA:
+      if ((long long)op.data.size() != n * (long long)es) return "constant payload of the wrong size";
+      if (dry) return "";
+      if (cudaMemcpyAsync(out, op.data.data(), op.data.size(), cudaMemcpyHostToDevice, st) != cudaSuccess) return "constant upload failed";
+      break;
+    case G_IOTA: {
+      if (!(o.dt == DT_I64 || o.dt == DT_I32)) return "iota of this element type";
+      if (op.a.size() != 1 || op.a[0] < 0 || op.a[0] >= (int64_t)o.shape.size()) return "iota: bad dimension";
+      if (dry) return "";
+      long long inner = 1;
+      for (size_t i = op.a[0] + 1; i < o.shape.size(); ++i) inner *= o.shape[i];
+      if (o.dt == DT_I64) k_iota<long long><<<nb, TPB, 0, st>>>((long long*)out, n, inner, o.shape[op.a[0]]);
+      else k_iota<int><<<nb, TPB, 0, st>>>((int*)out, n, inner, o.shape[op.a[0]]);
+      count(1);
+      break;
+    }
+    case G_UNARY:
+      if (!is_fp(o.dt) && !(op.sub == U_NEG || op.sub == U_ABS)) return "unary op on an integer type";
+      if (o.dt == DT_BOOL) return "unary op on i1";
+      if (dry) return "";
+      BY_TYPE(o.dt, k_unary<T><<<nb, TPB, 0, st>>>(op.sub, (const T*)in(0), (T*)out, n));
+      count(1);
+      break;
+    case G_BINARY:
+      if (is_fp(o.dt) && (op.sub == B_AND || op.sub == B_OR)) return "logical op on a float type";
+      if (!is_fp(o.dt) && op.sub == B_POW) return "power on an integer type";
+      if (dry) return "";
+      BY_TYPE(o.dt, k_binary<T><<<nb, TPB, 0, st>>>(op.sub, (const T*)in(0), (const T*)in(1), (T*)out, n));
+      count(1);
+      break;
+    case G_COMPARE: {
+      const int dt = g.vals[op.in[0]].dt;
+      if (dt != g.vals[op.in[1]].dt || o.dt != DT_BOOL) return "compare: operand types";
+      if (dry) return "";
+      BY_TYPE(dt, k_compare<T><<<nb, TPB, 0, st>>>(op.sub, (const T*)in(0), (const T*)in(1), (uint8_t*)out, n));
+      count(1);
+      break;
+    }
+    case G_SELECT:
+      if (g.vals[op.in[0]].dt != DT_BOOL || g.vals[op.in[0]].numel != n) return "select: the predicate must be i1 of the result's shape";
+      if (dry) return "";
+      BY_SIZE(es, k_select<U><<<nb, TPB, 0, st>>>((const uint8_t*)in(0), (const U*)in(1), (const U*)in(2), (U*)out, n));
+      count(1);
+      break;
+    case G_CONVERT:
+      if (dry) return "";
+      if (g.vals[op.in[0]].dt == o.dt) break;                 // shares its operand's storage
+      convert(st, in(0), g.vals[op.in[0]].dt, out, o.dt, n);
+      count(1);
+      break;
+    case G_RESHAPE:
+      break;                                                   // shares its operand's storage
+    case G_GUARD_CLAMP:
+      if (!is_fp(o.dt)) return "adjoint of an integer type";
+      if (dry) return "";
+      BY_FLOAT(o.dt, k_guard_clamp<T><<<nb, TPB, 0, st>>>((const T*)in(0), (T*)out, n, op.sub, op.lo, op.hi));
+      count(1);
+      break;
+    case G_TRANSPOSE:
+    case G_BCAST:
+    case G_SLICE: {
+      const GValue& x = g.vals[op.in[0]];
+      const std::vector<long long> xs = row_major_strides(x.shape);
+      NdDesc d;
+      d.rank = (int)o.shape.size(); d.offset = 0;
+      for (int k = 0; k < d.rank; ++k) { d.dim[k] = o.shape[k]; d.stride[k] = 0; }
+      if (op.kind == G_TRANSPOSE) {
+        if (op.a.size() != o.shape.size()) return "transpose: rank mismatch";
+        for (int k = 0; k < d.rank; ++k) {
+          if (op.a[k] < 0 || op.a[k] >= d.rank || x.shape[op.a[k]] != o.shape[k]) return "transpose: bad permutation";
+          d.stride[k] = xs[op.a[k]];
+        }
+      } else if (op.kind == G_BCAST) {
+        if (op.a.size() != x.shape.size()) return "broadcast_in_dim: rank mismatch";
+        for (size_t s = 0; s < op.a.size(); ++s) {
+          const int64_t dst = op.a[s];
+          if (dst < 0 || dst >= d.rank || (x.shape[s] != 1 && x.shape[s] != o.shape[dst])) return "broadcast_in_dim: bad dims";
+          d.stride[dst] = (x.shape[s] == 1) ? 0 : xs[s];
+        }
+      } else {
+        if (op.a.size() != x.shape.size() || x.shape.size() != o.shape.size()) return "slice: rank mismatch";
+        for (int k = 0; k < d.rank; ++k) {
+          if (op.c[k] < 1 || op.a[k] < 0 || op.b[k] > x.shape[k] || (op.b[k] - op.a[k] + op.c[k] - 1) / op.c[k] != o.shape[k]) return "slice: bad range";
+          d.stride[k] = xs[k] * op.c[k];
+          d.offset += op.a[k] * xs[k];
+        }
+      }
+      if (dry) return "";
+      BY_SIZE(es, k_gather_nd<U><<<nb, TPB, 0, st>>>((const U*)in(0), (U*)out, n, d));
+      count(1);
+      break;
+    }
+    case G_PAD: {
+      const GValue& x = g.vals[op.in[0]];
+      const std::vector<long long> os = row_major_strides(o.shape);
+      if (op.a.size() != o.shape.size() || x.shape.size() != o.shape.size()) return "pad: rank mismatch";
+      NdDesc d;
+      d.rank = (int)x.shape.size(); d.offset = 0;
+      for (int k = 0; k < d.rank; ++k) {
+        if ((op.b[k] - op.a[k] + op.c[k] - 1) / op.c[k] != x.shape[k] || op.b[k] > o.shape[k]) return "pad: bad range";
+        d.dim[k] = x.shape[k]; d.stride[k] = os[k] * op.c[k]; d.offset += op.a[k] * os[k];
+      }
+      if (dry) return "";
+      if (cudaMemsetAsync(out, 0, (size_t)n * es, st) != cudaSuccess) return "memset failed";
+      BY_SIZE(es, k_scatter_nd<U><<<blocks_for(x.numel), TPB, 0, st>>>((const U*)in(0), (U*)out, x.numel, d));
+      count(1);
+      break;
+    }
+    case G_CONCAT: {
+      const std::vector<long long> os = row_major_strides(o.shape);
+      const int64_t dim = op.a[0];
+      if (dim < 0 || dim >= (int64_t)o.shape.size()) return "concatenate: bad dimension";
+      long long at = 0;
+      for (size_t i = 0; i < op.in.size(); ++i) {
+        const GValue& x = g.vals[op.in[i]];
+        if (x.shape.size() != o.shape.size() || x.dt != o.dt) return "concatenate: operand types";
+        NdDesc d;
+        d.rank = (int)x.shape.size(); d.offset = at * os[dim];
+        for (int k = 0; k < d.rank; ++k) {
+          if (k != dim && x.shape[k] != o.shape[k]) return "concatenate: operand shapes";
+          d.dim[k] = x.shape[k]; d.stride[k] = os[k];
+        }
+        at += x.shape[dim];
+        if (dry) continue;
+        BY_SIZE(es, k_scatter_nd<U><<<blocks_for(x.numel), TPB, 0, st>>>((const U*)in((int)i), (U*)out, x.numel, d));
+        count(1);
+      }
+      if (at != o.shape[dim]) return "concatenate: sizes do not add up";
+      break;
+    }
+    case G_REDUCE: {
+      const GValue& x = g.vals[op.in[0]];
+      if (x.dt != o.dt || g.vals[op.in[1]].dt != o.dt || g.vals[op.in[1]].numel != 1) return "reduce: operand types";
+      if (o.dt == DT_BOOL) return "reduce over i1";
+      const std::vector<long long> xs = row_major_strides(x.shape);
+      RedDesc d;
+      d.krank = d.rrank = 0; d.n_out = 1; d.n_red = 1;
+      for (size_t i = 0; i < x.shape.size(); ++i) {
+        bool red = false;
+        for (int64_t r : op.a) red |= (r == (int64_t)i);
+        if (red) { d.rdim[d.rrank] = x.shape[i]; d.rstr[d.rrank++] = xs[i]; d.n_red *= x.shape[i]; }
+        else { d.kdim[d.krank] = x.shape[i]; d.kstr[d.krank++] = xs[i]; d.n_out *= x.shape[i]; }
+      }
+      if (d.n_out != n) return "reduce: result shape mismatch";
+      if (dry) return "";
+      const bool wide = d.n_red >= 64;
+      const long long threads = d.n_out * (wide ? 32 : 1);
+      const int blocks = (int)((threads + TPB - 1) / TPB);
+#define RED(T)                                                                                                        \
+  do {                                                                                                                \
+    if (op.sub == R_ADD) { if (wide) k_reduce<T, R_ADD, 32><<<blocks, TPB, 0, st>>>((const T*)in(0), (const T*)in(1), (T*)out, d); \
+                           else k_reduce<T, R_ADD, 1><<<blocks, TPB, 0, st>>>((const T*)in(0), (const T*)in(1), (T*)out, d); }     \
+    else { if (wide) k_reduce<T, R_MAX, 32><<<blocks, TPB, 0, st>>>((const T*)in(0), (const T*)in(1), (T*)out, d);              \
+           else k_reduce<T, R_MAX, 1><<<blocks, TPB, 0, st>>>((const T*)in(0), (const T*)in(1), (T*)out, d); }                  \
+  } while (0)
+      switch (o.dt) {
+        case DT_F32: RED(float); break;
+        case DT_BF16: RED(bf16); break;
+        case DT_F64: RED(double); break;
+        case DT_I64: RED(long long); break;
+        default: RED(int); break;
+      }
+#undef RED
+      count(1);
+      break;
+    }
+    case G_DOT: {
+      const GValue &x = g.vals[op.in[0]], &y = g.vals[op.in[1]];
+      if (!is_fp(o.dt) || x.dt != o.dt || y.dt != o.dt) return "dot_general: operand types";
+      const std::vector<long long> xs = row_major_strides(x.shape), ys = row_major_strides(y.shape);
+      auto inl = [](const std::vector<int64_t>& v, int64_t i) { for (int64_t q : v) if (q == i) return true; return false; };
+      std::vector<int64_t> xf, yf;
+      for (size_t i = 0; i < x.shape.size(); ++i) if (!inl(op.a, i) && !inl(op.c, i)) xf.push_back((int64_t)i);
+      for (size_t i = 0; i < y.shape.size(); ++i) if (!inl(op.b, i) && !inl(op.d, i)) yf.push_back((int64_t)i);
+      long long nbx, nby, M, N, K, K2;
+      DotDesc d;
+      if (!collapse(x.shape, xs, op.a, &nbx, &d.ab) || !collapse(y.shape, ys, op.b, &nby, &d.bb) ||
+          !collapse(x.shape, xs, xf, &M, &d.am) || !collapse(y.shape, ys, yf, &N, &d.bn) ||
+          !collapse(x.shape, xs, op.c, &K, &d.ak) || !collapse(y.shape, ys, op.d, &K2, &d.bk))
+        return "dot_general: the dimension groups of an operand do not lie in memory like one dimension each";
+      if (nbx != nby || K != K2 || nbx * M * N != n) return "dot_general: shape mismatch";
+      if (M > 0x7FFFFFFF || N > 0x7FFFFFFF || K > 0x7FFFFFFF || nbx > 65535 || (M + 63) / 64 > 65535) return "dot_general: too large for the general kernel";
+      d.M = (int)M; d.N = (int)N; d.K = (int)K;
+      if (dry) return "";
+      if (nbx == 1 && dot2d && *dot2d && (o.dt == DT_F32 || o.dt == DT_BF16)) {
+        GemmArgs ga;
+        ga.A = in(0); ga.sam = d.am; ga.sak = d.ak; ga.B = in(1); ga.sbk = d.bk; ga.sbn = d.bn; ga.C = out; ga.ldc = N;
+        ga.R = nullptr; ga.C2 = nullptr; ga.M = d.M; ga.N = d.N; ga.K = d.K; ga.epi = EPI_STORE; ga.clip = 0.f;
+        const int hr = (*dot2d)(o.dt, ga);
+        if (hr == 0) break;
+        if (hr != 1) return "dot_general: the GEMM dispatch failed";
+      }
+      const dim3 grid((unsigned)((N + 63) / 64), (unsigned)((M + 63) / 64), (unsigned)nbx);
+      BY_FLOAT(o.dt, k_dot<T><<<grid, 256, 0, st>>>((const T*)in(0), (const T*)in(1), (T*)out, d));
+      count(1);
+      break;
+    }
+    case G_GATHER_ROWS: {
+      const GValue& x = g.vals[op.in[0]];
+      if (g.vals[op.in[1]].dt != DT_I64 || x.shape.empty() || x.dt != o.dt) return "gather: operand types";
+      const long long rowlen = x.numel / x.shape[0];
+      if (g.vals[op.in[1]].numel * rowlen != n) return "gather: shape mismatch";
+      if (dry) return "";
+      BY_SIZE(es, k_gather_rows<U><<<nb, TPB, 0, st>>>((const U*)in(0), (const long long*)in(1), (U*)out, n, rowlen, x.shape[0]));
+      count(1);
+      break;
+    }
+    case G_GATHER2: {
+      const GValue& x = g.vals[op.in[0]];
+      if (g.vals[op.in[1]].dt != DT_I64 || x.shape.size() != 2 || x.dt != o.dt || g.vals[op.in[1]].numel != 2 * n) return "gather: operand types";
+      if (dry) return "";
+      BY_SIZE(es, k_gather2<U><<<nb, TPB, 0, st>>>((const U*)in(0), (const long long*)in(1), (U*)out, n, x.shape[0], x.shape[1]));
+      count(1);
+      break;
+    }
+    case G_SCATTER_ROWS:
+    case G_SCATTER2: {
+      const GValue& gr = g.vals[op.in[0]];
+      if (!is_fp(o.dt) || gr.dt != o.dt || g.vals[op.in[1]].dt != DT_I64 || o.shape.empty()) return "scatter: operand types";
+      const long long rowlen = n / o.shape[0];
+      if (op.kind == G_SCATTER_ROWS ? (g.vals[op.in[1]].numel * rowlen != gr.numel) : (o.shape.size() != 2 || g.vals[op.in[1]].numel != 2 * gr.numel))
+        return "scatter: shape mismatch";
+      if (dry) return "";
+      if (cudaMemsetAsync(out, 0, (size_t)n * es, st) != cudaSuccess) return "memset failed";
+      const int gb = blocks_for(gr.numel);
+      if (op.kind == G_SCATTER_ROWS) {
+        BY_FLOAT(o.dt, k_scatter_rows<T><<<gb, TPB, 0, st>>>((const T*)in(0), (const long long*)in(1), (T*)out, gr.numel, rowlen, o.shape[0]));
+      } else {
+        BY_FLOAT(o.dt, k_scatter2<T><<<gb, TPB, 0, st>>>((const T*)in(0), (const long long*)in(1), (T*)out, gr.numel, o.shape[0], o.shape[1]));
+      }
+      count(1);
+      break;
+    }
+    default:
+      return "unknown op kind";
+  }
+  if (!dry) LAUNCH_CHECK();
+  return "";
+}
+
+}  // namespace
+
+std::string graph_exec_create(const Graph& g, int n_params, const std::vector<int64_t>& param_offsets, cudaStream_t st,
+                              GraphExec** out) {
+  *out = nullptr;
+  GraphExec* e = new GraphExec();
+  e->g = g;
+  e->n_params = n_params;
+  e->param_offsets = param_offsets;
+  const int nv = (int)g.vals.size(), nops = (int)g.ops.size();
+  auto failed = [&](const std::string& why) { graph_exec_destroy(e); return why; };
+  // storage sharing: reshape and same-type convert are views of their operand
+  e->root.resize(nv);
+  for (int v = 0; v < nv; ++v) e->root[v] = v;
+  for (int i = 0; i < nops; ++i) {
+    const GOp& op = g.ops[i];
+    if (op.kind == G_RESHAPE || (op.kind == G_CONVERT && g.vals[op.in[0]].dt == g.vals[op.out].dt)) e->root[op.out] = e->root[op.in[0]];
+  }
+  // constants: produced without reading an argument or the seed
+  std::vector<char> cval(nv, 0);
+  e->is_const_op.assign(nops, 0);
+  for (int i = 0; i < nops; ++i) {
+    const GOp& op = g.ops[i];
+    bool c = op.kind != G_SEED;
+    for (int x : op.in) c = c && cval[x];
+    e->is_const_op[i] = c;
+    cval[op.out] = c;
+  }
+  // needed ops: those the result (forward) or the result and the gradients (all) depend on
+  auto mark = [&](std::vector<char>& need, const std::vector<int>& outs, int upto) {
+    std::vector<char> nval(nv, 0);
+    for (int v : outs) if (v >= 0) nval[v] = 1;
+    need.assign(nops, 0);
+    for (int i = upto - 1; i >= 0; --i) {
+      const GOp& op = g.ops[i];
+      if (!nval[op.out]) continue;
+      need[i] = 1;
+      for (int x : op.in) nval[x] = 1;
+    }
+  };
+  std::vector<int> outs = {g.ret};
+  mark(e->need_fwd, outs, g.n_forward_ops);
+  for (int v : g.grad_of_arg) outs.push_back(v);
+  mark(e->need_all, outs, nops);
+  // every needed op must have a kernel
+  for (int i = 0; i < nops; ++i) {
+    if (!e->need_all[i]) continue;
+    const std::string why = run_op(*e, g.ops[i], st, true, nullptr, nullptr);
+    if (!why.empty()) {
+      const GValue& o = g.vals[g.ops[i].out];
+      return failed(why + (o.name.empty() ? std::string(" (in the gradient program)") : " (%" + o.name + ")"));
+    }
+  }
+  // placement
+  e->where.assign(nv, W_STEP);
+  e->off.assign(nv, 0);
+  for (int a : g.args) e->where[a] = W_EXT;
+  std::vector<long long> last(nv, -1);            // per root: index of the last needed step op that touches it
+  const long long FOREVER = (long long)nops + 1;
+  for (int i = 0; i < nops; ++i) {
+    if (!e->need_all[i]) continue;
+    const GOp& op = g.ops[i];
+    if (e->is_const_op[i]) { e->where[e->root[op.out]] = W_CONST; continue; }
+    last[e->root[op.out]] = std::max<long long>(last[e->root[op.out]], i);
+    for (int x : op.in) last[e->root[x]] = std::max<long long>(last[e->root[x]], i);
+  }
+  for (int v : outs) if (v >= 0) last[e->root[v]] = FOREVER;
+  size_t cbytes = 0;
+  FreeList fl;
+  std::vector<char> placed(nv, 0);
+  std::map<long long, std::vector<int>> dies;     // op index -> roots to release after it
+  for (int i = 0; i < nops; ++i) {
+    if (!e->need_all[i]) continue;
+    const GOp& op = g.ops[i];
+    const int r = e->root[op.out];
+    const size_t bytes = round256((size_t)g.vals[r].numel * dtype_size(g.vals[r].dt));
+    if (e->is_const_op[i]) {
+      if (r == op.out && !placed[r]) { e->off[r] = (long long)cbytes; cbytes += bytes; placed[r] = 1; }
+      continue;
+    }
+    if (e->where[r] == W_STEP && !placed[r]) {
+      e->off[r] = (long long)fl.alloc(bytes);
+      placed[r] = 1;
+      if (last[r] != FOREVER) dies[last[r]].push_back(r);
+    }
+    auto d = dies.find(i);
+    if (d != dies.end())
+      for (int dead : d->second) fl.release((size_t)e->off[dead], round256((size_t)g.vals[dead].numel * dtype_size(g.vals[dead].dt)));
+  }
+  e->const_bytes = cbytes;
+  e->arena_bytes = fl.end;
+  if (cudaMalloc(&e->const_arena, cbytes ? cbytes : 256) != cudaSuccess) { e->const_arena = nullptr; return failed("cudaMalloc of the constant arena failed"); }
+  if (cudaMalloc(&e->arena, e->arena_bytes ? e->arena_bytes : 256) != cudaSuccess) {
+    e->arena = nullptr;
+    char m[128];
+    snprintf(m, sizeof m, "cudaMalloc of the %zu-byte arena failed", e->arena_bytes);
+    return failed(m);
+  }
+  e->ext.assign(nv, nullptr);
+  // the constant part, once
+  for (int i = 0; i < nops; ++i) {
+    if (!e->need_all[i] || !e->is_const_op[i]) continue;
+    const std::string why = run_op(*e, g.ops[i], st, false, nullptr, nullptr);
+    if (!why.empty()) return failed(why);
+  }
+  if (cudaStreamSynchronize(st) != cudaSuccess) return failed("evaluating the constants of the graph failed");
+  *out = e;
+  return "";
+}
+
+void graph_exec_destroy(GraphExec* e) {
+  if (!e) return;
+  if (e->const_arena) cudaFree(e->const_arena);
+  if (e->arena) cudaFree(e->arena);
+  delete e;
+}
+
+size_t graph_exec_arena_bytes(const GraphExec* e) { return e ? e->arena_bytes + e->const_bytes : 0; }
+
+std::string graph_exec_run(GraphExec* e, cudaStream_t st, const GraphBind& bind,
+                           const std::function<int(int, const GemmArgs&)>& dot2d, long long* launches) {
+  const Graph& g = e->g;
+  const int n_args = (int)g.args.size();
+  if ((int)bind.data.size() != n_args - e->n_params) return "wrong number of data inputs";
+  for (int i = 0; i < n_args; ++i) {
+    const int v = g.args[i];
+    if (i < e->n_params) e->ext[v] = (const char*)bind.params + (size_t)e->param_offsets[i] * dtype_size(g.vals[v].dt);
+    else e->ext[v] = bind.data[i - e->n_params];
+  }
+  const int upto = bind.backward ? (int)g.ops.size() : g.n_forward_ops;
+  const std::vector<char>& need = bind.backward ? e->need_all : e->need_fwd;
+  for (int i = 0; i < upto; ++i) {
+    if (!need[i] || e->is_const_op[i]) continue;
+    GOp seed_op;
+    const GOp* op = &g.ops[i];
+    if (op->kind == G_SEED) { seed_op = *op; seed_op.fval = (double)bind.seed; seed_op.ival = (long long)bind.seed; op = &seed_op; }
+    const std::string why = run_op(*e, *op, st, false, &dot2d, launches);
+    if (!why.empty()) return why;
+  }
+  const GValue& r = g.vals[g.ret];
+  if (bind.loss_out) {
+    convert(st, ptr_of(*e, g.ret), r.dt, bind.loss_out, DT_F32, 1);
+    if (launches) *launches += 1;
+  }
+  if (bind.backward && bind.grads) {
+    for (int i = 0; i < e->n_params; ++i) {
+      const GValue& p = g.vals[g.args[i]];
+      float* dst = bind.grads + e->param_offsets[i];
+      const int gv = g.grad_of_arg[i];
+      if (gv < 0) { if (cudaMemsetAsync(dst, 0, (size_t)p.numel * 4, st) != cudaSuccess) return "memset failed"; continue; }
+      convert(st, ptr_of(*e, gv), g.vals[gv].dt, dst, DT_F32, p.numel);
+      if (launches) *launches += 1;
+    }
+  }
+  LAUNCH_CHECK();
+  return "";
+}
+
+}  // namespace pcpb

@@ -13,7 +13,9 @@ struct TensorInfo {
   int64_t offset = 0;      // element offset in the flat parameter buffer (argument order)
 };
 
-enum { FAMILY_NANOCHAT = 0, FAMILY_NANOGPT = 1 };
+// FAMILY_GRAPH: not one of the two recognised architectures; run op by op by the general front end (graph.h).  Only the
+// fields dtype, B, T, params, total_params (and V when the first parameter is a [V, d] table) are meaningful then.
+enum { FAMILY_NANOCHAT = 0, FAMILY_NANOGPT = 1, FAMILY_GRAPH = 2 };
 enum { ACT_NATIVE = 0, ACT_GELU_TANH = 1 };     // native: ReLU^2 (nanochat) / ReLU (nanoGPT)
 
 struct ModelConfig {

@@ -79,6 +79,7 @@ void free_workspace(pcpb_backend* b) {
   b->frag_pending.clear();
   for (void* p : b->ws.allocs) cudaFree(p);
   b->ws = Workspace();
+  if (b->gx) { graph_exec_destroy(b->gx); b->gx = nullptr; }
   if (b->tokens_stage) { cudaFree(b->tokens_stage); b->tokens_stage = nullptr; b->stage_cap = 0; }
   if (b->window_stage) { cudaFree(b->window_stage); b->window_stage = nullptr; b->window_stage_cap = 0; }
   if (b->starts_dev) { cudaFree(b->starts_dev); b->starts_dev = nullptr; }
@@ -109,6 +110,32 @@ int wsalloc(pcpb_backend* b, P** out, size_t bytes) {
 }
 #define WS(b, ptr, bytes) do { int r__ = wsalloc(b, &(ptr), (bytes)); if (r__) return r__; } while (0)
 
+// optimiser tables of the flat parameter layout
+int build_flat_tables(pcpb_backend* b) {
+  const ModelConfig& c = b->cfg;
+  Workspace& w = b->ws;
+  const size_t es = dtype_size(c.dtype);
+  const int nseg = (int)c.params.size();
+  std::vector<TensorSeg> segs(nseg);
+  std::vector<int> c2s;
+  for (int i = 0; i < nseg; ++i) {
+    const TensorInfo& t = c.params[i];
+    TensorSeg& s = segs[i];
+    s.p = w.theta + t.offset; s.g = w.grads + t.offset; s.m = w.mstate + t.offset; s.v = w.vstate + t.offset;
+    s.p_out = w.theta + t.offset; s.m_out = w.mstate + t.offset; s.v_out = w.vstate + t.offset;
+    s.shadow = (c.dtype == DT_F32) ? nullptr : (void*)((char*)w.shadow + (size_t)t.offset * es);
+    s.n = t.numel; s.first_chunk = (int)c2s.size();
+    s.num_chunks = (int)((t.numel + ADAM_CHUNK - 1) / ADAM_CHUNK);
+    for (int k = 0; k < s.num_chunks; ++k) c2s.push_back(i);
+  }
+  w.nchunks = (int)c2s.size();
+  WS(b, w.segs, sizeof(TensorSeg) * nseg); WS(b, w.chunk2seg, sizeof(int) * c2s.size());
+  WS(b, w.partial, 4 * c2s.size()); WS(b, w.normsq, 4 * (size_t)nseg); WS(b, w.heal_flags, 4 * (size_t)nseg * 2);
+  CK(b, cudaMemcpy(w.segs, segs.data(), sizeof(TensorSeg) * nseg, cudaMemcpyHostToDevice));
+  CK(b, cudaMemcpy(w.chunk2seg, c2s.data(), sizeof(int) * c2s.size(), cudaMemcpyHostToDevice));
+  return PCPB_OK;
+}
+
 int build_workspace(pcpb_backend* b) {
   const ModelConfig& c = b->cfg;
   Workspace& w = b->ws;
@@ -117,6 +144,20 @@ int build_workspace(pcpb_backend* b) {
   WS(b, w.theta, P * 4); WS(b, w.theta0, P * 4); WS(b, w.mstate, P * 4); WS(b, w.vstate, P * 4);
   WS(b, w.grads, P * 4); WS(b, w.delta, P * 4);
   if (c.dtype == DT_F32) w.shadow = w.theta; else WS(b, w.shadow, P * es);
+  if (c.family == FAMILY_GRAPH) {
+    // general front end: the values of the program live in the executor's own arena
+    WS(b, w.loss, 4); WS(b, w.count, 4); WS(b, w.ids, M * 8); WS(b, w.targets, M * 8);
+    int r = build_flat_tables(b);
+    if (r) return r;
+    WS(b, w.tc_err, sizeof(int));
+    CK(b, cudaMemset(w.tc_err, 0, sizeof(int)));
+    std::vector<int64_t> offs;
+    for (const TensorInfo& t : c.params) offs.push_back(t.offset);
+    const std::string why = graph_exec_create(b->graph, (int)c.params.size(), offs, b->stream, &b->gx);
+    if (!why.empty()) return fail(b, PCPB_E_ARTIFACT, "the general front end cannot run this graph: " + why);
+    w.ready = true;
+    return PCPB_OK;
+  }
   w.xs.resize(c.L + 1);
   for (auto& x : w.xs) WS(b, x, M * d * es);
   w.layers.resize(c.L);
@@ -146,25 +187,10 @@ int build_workspace(pcpb_backend* b) {
     CK(b, cudaMemcpy(w.d_cos, c.rope_cos.data(), c.rope_cos.size() * 2, cudaMemcpyHostToDevice));
     CK(b, cudaMemcpy(w.d_sin, c.rope_sin.data(), c.rope_sin.size() * 2, cudaMemcpyHostToDevice));
   }
-  // optimiser tables of the flat layout
-  const int nseg = (int)c.params.size();
-  std::vector<TensorSeg> segs(nseg);
-  std::vector<int> c2s;
-  for (int i = 0; i < nseg; ++i) {
-    const TensorInfo& t = c.params[i];
-    TensorSeg& s = segs[i];
-    s.p = w.theta + t.offset; s.g = w.grads + t.offset; s.m = w.mstate + t.offset; s.v = w.vstate + t.offset;
-    s.p_out = w.theta + t.offset; s.m_out = w.mstate + t.offset; s.v_out = w.vstate + t.offset;
-    s.shadow = (c.dtype == DT_F32) ? nullptr : (void*)((char*)w.shadow + (size_t)t.offset * es);
-    s.n = t.numel; s.first_chunk = (int)c2s.size();
-    s.num_chunks = (int)((t.numel + ADAM_CHUNK - 1) / ADAM_CHUNK);
-    for (int k = 0; k < s.num_chunks; ++k) c2s.push_back(i);
+  {
+    int r = build_flat_tables(b);
+    if (r) return r;
   }
-  w.nchunks = (int)c2s.size();
-  WS(b, w.segs, sizeof(TensorSeg) * nseg); WS(b, w.chunk2seg, sizeof(int) * c2s.size());
-  WS(b, w.partial, 4 * c2s.size()); WS(b, w.normsq, 4 * (size_t)nseg); WS(b, w.heal_flags, 4 * (size_t)nseg * 2);
-  CK(b, cudaMemcpy(w.segs, segs.data(), sizeof(TensorSeg) * nseg, cudaMemcpyHostToDevice));
-  CK(b, cudaMemcpy(w.chunk2seg, c2s.data(), sizeof(int) * c2s.size(), cudaMemcpyHostToDevice));
   // tensor-core GEMM scratch (split-K slabs of the weight-gradient GEMMs) and error word
   if (c.dtype == DT_BF16) {
     const int Mi = (int)M, di = (int)d, Fi = (int)F, wqi = (int)(d + 2 * dkv), Vi = (int)c.V;
@@ -290,11 +316,33 @@ GemmArgs mk(const void* A, long long sam, long long sak, const void* B, long lon
 int forward_backward_gpt(pcpb_backend* b, const void* wts, const long long* ids, const long long* targets, float* grads,
                          float* loss_out, bool backward, float seed);
 
+// Any other graph: the tensor program of the general front end, one kernel per op; un-batched bf16 products of
+// tensor-core shape go through the tcgen05 GEMM.
+int forward_backward_graph(pcpb_backend* b, const void* wts, const long long* ids, const long long* targets, float* grads,
+                           float* loss_out, bool backward, float seed) {
+  GraphBind bind;
+  bind.params = wts; bind.data = {ids, targets}; bind.seed = seed; bind.grads = grads; bind.loss_out = loss_out;
+  bind.backward = backward;
+  int hook_rc = PCPB_OK;
+  auto dot2d = [&](int dt, const GemmArgs& g0) -> int {
+    GemmArgs g = g0;
+    g.scratch = b->ws.tc_scratch; g.scratch_bytes = b->ws.tc_scratch_bytes; g.err_word = b->ws.tc_err;
+    if (b->force_generic || dt != DT_BF16 || !gemm_tc_supported(g)) return 1;
+    b->launches += gemm_tc_launches(g);
+    if (launch_gemm_tc(b->stream, g) != cudaSuccess) { hook_rc = PCPB_E_CUDA; return 2; }
+    return 0;
+  };
+  const std::string why = graph_exec_run(b->gx, b->stream, bind, dot2d, &b->launches);
+  if (!why.empty()) return fail(b, hook_rc ? hook_rc : PCPB_E_CUDA, "general front end: " + why);
+  return PCPB_OK;
+}
+
 // seed: d(loss), 1 for compute_gradients; model_forward_pass_grad passes the caller's value, which then flows through
 // every adjoint edge (and its clamp) like in the reference's gradient function
 int forward_backward(pcpb_backend* b, const void* wts, const long long* ids, const long long* targets, float* grads,
                      float* loss_out, bool backward, float seed = 1.f) {
   if (b->cfg.family == FAMILY_NANOGPT) return forward_backward_gpt(b, wts, ids, targets, grads, loss_out, backward, seed);
+  if (b->cfg.family == FAMILY_GRAPH) return forward_backward_graph(b, wts, ids, targets, grads, loss_out, backward, seed);
   const ModelConfig& c = b->cfg;
   Workspace& w = b->ws;
   cudaStream_t st = b->stream;
@@ -622,17 +670,61 @@ const char* pcpb_last_error(const pcpb_backend* b) { return b ? b->err.c_str() :
 void pcpb_free(void* p) { free(p); }
 long long pcpb_launch_count(const pcpb_backend* b) { return b ? b->launches : 0; }
 
+// Describes a graph the family recogniser refused as a FAMILY_GRAPH model: parameters = all @main arguments but the
+// last two (src/mlir/model_introspection.zig:251-312), which are the i64 [B, T] inputs; the result is the scalar loss.
+static std::string general_model(const void* bytes, size_t n, ModelConfig* c, Graph* graph) {
+  std::string why = graph_parse((const char*)bytes, n, true, graph);
+  if (!why.empty()) return why;
+  const int n_args = (int)graph->args.size();
+  if (n_args < 3) return "@main needs parameters and two data inputs";
+  const GValue &ids = graph->vals[graph->args[n_args - 2]], &tg = graph->vals[graph->args[n_args - 1]];
+  if (ids.dt != DT_I64 || tg.dt != DT_I64 || ids.shape != tg.shape || ids.shape.size() != 2) return "the last two arguments must be i64 [B, T]";
+  const GValue& ret = graph->vals[graph->ret];
+  if (ret.numel != 1 || !(ret.dt == DT_F32 || ret.dt == DT_BF16 || ret.dt == DT_F64)) return "@main must return a scalar loss";
+  *c = ModelConfig();
+  c->family = FAMILY_GRAPH;
+  c->dtype = graph->vals[graph->args[0]].dt;
+  if (c->dtype != DT_F32 && c->dtype != DT_BF16) return "parameters must be f32 or bf16";
+  c->B = ids.shape[0]; c->T = ids.shape[1];
+  int64_t off = 0;
+  for (int i = 0; i < n_args - 2; ++i) {
+    const GValue& v = graph->vals[graph->args[i]];
+    if (v.dt != c->dtype) return "parameters of different element types";
+    TensorInfo t;
+    t.shape = v.shape; t.numel = v.numel; t.offset = off;
+    off += v.numel;
+    c->params.push_back(t);
+  }
+  c->total_params = off;
+  if (c->params[0].shape.size() == 2) c->V = c->params[0].shape[0];      // the token table comes first in the exports
+  return graph_add_gradients(graph, n_args - 2, 1, -100.f, 100.f);
+}
+
+// The two fused families first; anything else (or everything, with PCPB_FRONTEND=graph) through the general front end.
+static std::string recognise(const void* bytes, size_t n, ModelConfig* c, Graph* graph) {
+  const char* e = getenv("PCPB_FRONTEND");
+  const bool force = e && strcmp(e, "graph") == 0;
+  std::string why = force ? std::string("general front end forced") : parse_artifact((const char*)bytes, n, c);
+  if (why.empty()) return "";
+  if (e && strcmp(e, "fused") == 0) return why;
+  const std::string why2 = general_model(bytes, n, c, graph);
+  if (why2.empty()) return "";
+  return force ? why2 : why + "; general front end: " + why2;
+}
+
 int pcpb_load_artifact(pcpb_backend* b, const void* bytes, size_t n) {
   if (!b || !bytes || n == 0) return fail(b, PCPB_E_INVALID, "null artefact");
   if (!b->stream) return fail(b, PCPB_E_CUDA, "backend has no device");
   if (b->loaded && b->art_ptr == bytes && b->art_len == n) return PCPB_OK;     // same (ptr, len): keep the session
   DeviceGuard g(b->device);
   ModelConfig c;
-  std::string why = parse_artifact((const char*)bytes, n, &c);
+  Graph graph;
+  std::string why = recognise(bytes, n, &c, &graph);
   if (!why.empty()) return fail(b, PCPB_E_ARTIFACT, "artefact not recognised: " + why);
   CK(b, cudaStreamSynchronize(b->stream));
   free_workspace(b);
   b->cfg = c;
+  b->graph = std::move(graph);
   b->loaded = false;
   int r = build_workspace(b);
   if (r) { free_workspace(b); return r; }
@@ -643,13 +735,36 @@ int pcpb_load_artifact(pcpb_backend* b, const void* bytes, size_t n) {
 int pcpb_inspect_artifact(const void* bytes, size_t n, int64_t* facts, char* err, size_t err_cap) {
   if (!bytes || !facts) return PCPB_E_INVALID;
   ModelConfig c;
-  std::string why = parse_artifact((const char*)bytes, n, &c);
+  Graph graph;
+  std::string why = recognise(bytes, n, &c, &graph);
   if (!why.empty()) {
     if (err && err_cap) snprintf(err, err_cap, "%s", why.c_str());
     return PCPB_E_ARTIFACT;
   }
   const int64_t f[12] = {c.V, c.d, c.L, c.H, c.Hkv, c.hd, c.F, c.B, c.T, c.dtype, (int64_t)c.params.size(), c.total_params};
   memcpy(facts, f, sizeof f);
+  if (err && err_cap) err[0] = 0;
+  return PCPB_OK;
+}
+
+int pcpb_graph_describe(const void* bytes, size_t n, int with_gradients, char** text_out, char* err, size_t err_cap) {
+  if (!bytes || !text_out) return PCPB_E_INVALID;
+  *text_out = nullptr;
+  Graph g;
+  std::string why = graph_parse((const char*)bytes, n, true, &g);
+  if (why.empty() && with_gradients) {
+    if (g.args.size() < 3) why = "@main needs parameters and two data inputs";
+    else why = graph_add_gradients(&g, (int)g.args.size() - 2, 1, -100.f, 100.f);
+  }
+  if (!why.empty()) {
+    if (err && err_cap) snprintf(err, err_cap, "%s", why.c_str());
+    return PCPB_E_ARTIFACT;
+  }
+  const std::string s = graph_dump(g);
+  char* out = (char*)malloc(s.size() + 1);
+  if (!out) return PCPB_E_INVALID;
+  memcpy(out, s.c_str(), s.size() + 1);
+  *text_out = out;
   if (err && err_cap) err[0] = 0;
   return PCPB_OK;
 }

@@ -6,6 +6,7 @@
 #include <string>
 #include <vector>
 
+#include "graph_exec.h"
 #include "kernels.h"
 #include "model.h"
 
@@ -82,6 +83,8 @@ struct pcpb_backend {
   size_t art_len = 0;
   bool loaded = false;
   pcpb::ModelConfig cfg;
+  pcpb::Graph graph;                         // FAMILY_GRAPH: the tensor program of the artefact (forward + gradients)
+  pcpb::GraphExec* gx = nullptr;             // ... and its planned executor
   pcpb::Workspace ws;
   pcpb::AdamHyper adam;
   long long launches = 0;

@@ -1,0 +1,105 @@
+"""General StableHLO front end, host side (no GPU): the tensor program the library derives from a forward graph —
+parser, stability patches, gradient rules, adjoint edges — evaluated with torch and compared with the oracle's
+interpretation of the same graph (oracle/stablehlo.py + oracle/autodiff.py).  Both apply the same rules to the same
+values in the same order, so the comparison is exact."""
+import os
+
+import pytest
+import torch
+
+import graph_program as gp
+import helpers
+from helpers import make_model, seeded_params
+from oracle.worker import TrainingModule
+from pcp_b200 import backend as bk
+from pcp_b200.backend import BackendError, graph_describe, inspect_artifact
+
+REF = os.environ.get("PCP_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"))
+
+
+def _batch(cfg, seed):
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.randint(0, cfg.vocab, (cfg.batch, cfg.seq_len), generator=g)
+    tg = torch.randint(0, cfg.vocab, (cfg.batch, cfg.seq_len), generator=g)
+    tg[0, :3] = -1 if hasattr(cfg, "n_kv_head") else -100          # ignored positions
+    return ids, tg
+
+
+def _compare(text, cfg, seed=1.0):
+    mod = TrainingModule(text)
+    params = seeded_params(cfg, 1)
+    ids, tg = _batch(cfg, 3)
+    prog = gp.parse(graph_describe(text))
+    model_params = mod._model_params(params)
+    loss, grads = gp.run(prog, model_params + [ids, tg], seed=seed)
+    want = mod.model_forward_pass_grad(model_params, ids, tg, seed)
+    want_loss = mod.forward(params, ids, tg)
+    assert float(loss) == float(want_loss)
+    for g, w in zip(grads, want):
+        g = g if g is not None else torch.zeros_like(w)
+        assert g.dtype == w.dtype and torch.equal(g, w)
+    return prog
+
+
+@pytest.mark.parametrize("name", ["SMALL_F32", "GPT_SMALL_F32", "GPT_SMALL_BF16", "GPT_GELU_F32"])
+def test_program_matches_oracle_exactly(lib_built, name):
+    cfg, text = make_model(getattr(helpers, name))
+    prog = _compare(text, cfg)
+    assert prog.forward_ops < len(prog.ops) and prog.seed >= 0 and all(g >= 0 for g in prog.grads[:-2])
+
+
+def test_clamp_of_the_adjoint_edges_is_in_the_program(lib_built):
+    """d(loss) = 500: the oracle's clamp to +-100 is active on the first edges; the program must clamp the same way."""
+    cfg, text = make_model(helpers.SMALL_F32)
+    _compare(text, cfg, seed=500.0)
+
+
+def test_graphs_outside_the_fused_families_take_the_general_path(lib_built):
+    cfg, text = make_model(helpers.SMALL_F32)
+    assert inspect_artifact(text)["family"] == "fused"
+    other = text.replace("stablehlo.tanh ", "stablehlo.logistic ", 1)         # another soft-cap: not nanochat any more
+    f = inspect_artifact(other)
+    assert f["family"] == "graph" and f["d_model"] == 0 and f["n_layer"] == 0
+    assert (f["batch"], f["block"], f["dtype"], f["vocab"]) == (cfg.batch, cfg.seq_len, bk.F32, cfg.vocab)
+    assert f["num_tensors"] == len(cfg.param_shapes()) and f["total_params"] == cfg.num_params()
+    _compare(other, cfg)
+
+
+def test_unsupported_graphs_are_refused_with_a_reason(lib_built):
+    cfg, text = make_model(helpers.SMALL_F32)
+    for bad, what in ((text.replace("stablehlo.tanh ", "stablehlo.erf_inv ", 1), "unsupported op"),
+                      (text.replace("func.func @main", "func.func @other"), "@main")):
+        with pytest.raises(BackendError) as ei:
+            graph_describe(bad)
+        assert ei.value.code == bk.E_ARTIFACT and what in str(ei.value)
+        with pytest.raises(BackendError):
+            inspect_artifact(bad)
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "models")), reason="reference tree not present")
+def test_every_shipped_reference_graph_has_a_program(lib_built):
+    import glob
+    files = sorted(glob.glob(os.path.join(REF, "models", "*.mlir")))
+    assert len(files) >= 17
+    for fn in files:
+        prog = gp.parse(graph_describe(open(fn).read()))
+        assert prog.forward_ops > 100 and all(g >= 0 for g in prog.grads[:-2]), fn
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "models")), reason="reference tree not present")
+def test_shipped_small_graph_program_matches_oracle(lib_built):
+    text = open(os.path.join(REF, "models", "nanochat_smoke_d1_128.mlir")).read()
+    mod = TrainingModule(text)
+    g = torch.Generator().manual_seed(5)
+    params = [torch.randn(s, generator=g) * 0.02 for s in mod.param_shapes]
+    B, T = mod.data_types[0].shape
+    V = mod.param_shapes[0][0]
+    ids = torch.randint(0, V, (B, T), generator=g)
+    tg = torch.randint(0, V, (B, T), generator=g)
+    prog = gp.parse(graph_describe(text))
+    mp = mod._model_params(params)
+    loss, grads = gp.run(prog, mp + [ids, tg])
+    want = mod.model_forward_pass_grad(mp, ids, tg, 1.0)
+    assert float(loss) == float(mod.forward(params, ids, tg))
+    for a, w in zip(grads, want):
+        assert torch.equal(a, w)

@@ -76,9 +76,11 @@ def test_d20_parameter_count():
     assert d8.num_params() == 92_274_688
 
 
-def test_recogniser_refuses_same_signature_other_body(lib_built):
+def test_recogniser_refuses_same_signature_other_body(lib_built, monkeypatch):
     """A graph with the nanochat parameter list but another body (no ReLU^2, a norm dropped, GELU-like ops, another
-    ignore index) must be refused, not trained with the built-in nanochat arithmetic."""
+    ignore index) must not be trained with the built-in nanochat arithmetic: the fused recogniser refuses it
+    (PCPB_FRONTEND=fused: no other path), and by default it goes to the general front end, op by op."""
+    monkeypatch.setenv("PCPB_FRONTEND", "fused")
     cfg = NanochatConfig(vocab=97, d_model=64, n_layer=2, n_head=4, n_kv_head=2, seq_len=16, batch=2, dtype="f32")
     good = nanochat_forward_mlir(cfg)
     inspect_artifact(good)
@@ -105,6 +107,14 @@ def test_recogniser_refuses_same_signature_other_body(lib_built):
         with pytest.raises(BackendError) as ei:
             inspect_artifact(text)
         assert ei.value.code == bk.E_ARTIFACT, what
+    monkeypatch.delenv("PCPB_FRONTEND")
+    for what, text in mutated.items():
+        if "abs" in what:               # abs with two operands is not StableHLO: refused by both
+            with pytest.raises(BackendError):
+                inspect_artifact(text)
+            continue
+        assert inspect_artifact(text)["family"] == "graph", what
+    assert inspect_artifact(good)["family"] == "fused"
 
 
 @pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "models")), reason="reference tree not present")
