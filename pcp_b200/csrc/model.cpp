@@ -144,6 +144,27 @@ std::string parse_artifact(const char* text, size_t n, ModelConfig* cfg) {
       else
         return "nanoGPT graph with an activation other than ReLU or tanh-GELU is not supported";
     }
+    // Body fingerprint, as for nanochat below: per layer two rsqrt (LayerNorms), one exponential (softmax), six
+    // dot_general, one select (causal mask) and, with ReLU, one maximum; the head adds one rsqrt, one exponential and
+    // one log (cross entropy), one negate, one dot_general and three selects.
+    {
+      auto count = [&](const char* op) {
+        size_t n = 0;
+        const std::string pat = std::string("= stablehlo.") + op + " ";
+        for (size_t q = 0; (q = src.find(pat, q)) != std::string::npos; ++q) ++n;
+        return (int64_t)n;
+      };
+      struct { const char* op; int64_t want; } expect[] = {
+          {"rsqrt", 2 * c.L + 1}, {"maximum", c.activation == ACT_NATIVE ? c.L : 0}, {"exponential", c.L + 1}, {"log", 1},
+          {"dot_general", 6 * c.L + 1}, {"select", c.L + 3}, {"negate", 1}, {"sqrt", 0}, {"sine", 0}, {"cosine", 0},
+          {"abs", 0}, {"minimum", 0}, {"clamp", 0}, {"convolution", 0}};
+      for (auto& e : expect) {
+        const int64_t got = count(e.op);
+        if (got != e.want)
+          return std::string("not a nanoGPT-family body: ") + std::to_string(got) + " stablehlo." + e.op +
+                 " ops where the family has " + std::to_string(e.want);
+      }
+    }
     if (src.find("dense<-100>") == std::string::npos) return "expected ignore_index -100 in the loss";
     c.ignore_index = -100;
     c.softcap = 0.f;
