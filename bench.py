@@ -653,6 +653,18 @@ def run_ours(args):
                 others.append(time_workload(name, st, 3, local, peaks))
             except Exception as e:
                 others.append({"workload": name, "error": str(e)})
+        # the general front end (any StableHLO graph: one kernel per op of the derived tensor program, replayed as a CUDA
+        # graph) on the nanoGPT-small fp32 configuration: what a graph outside the two fused families costs
+        try:
+            os.environ["PCPB_FRONTEND"] = "graph"
+            o = time_workload("c1", 4, 3, local, peaks)
+            o["workload"] = "c1_general_front_end"
+            o["descr"] = DESCR["c1"] + "; run op by op by the general StableHLO front end (PCPB_FRONTEND=graph)"
+            others.append(o)
+        except Exception as e:
+            others.append({"workload": "c1_general_front_end", "error": str(e)})
+        finally:
+            os.environ.pop("PCPB_FRONTEND", None)
         try:                                              # BASELINE configs[4]: rollout generation, two rollouts
             r = time_rollout(local, 2, 1, peaks)
             others.append({"workload": "qwen3_rollout", "descr": ROLLOUT_DESCR, "value": r["value"], "unit": "generated tokens/s",

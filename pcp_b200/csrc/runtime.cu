@@ -151,6 +151,28 @@ int build_workspace(pcpb_backend* b) {
     if (r) return r;
     WS(b, w.tc_err, sizeof(int));
     CK(b, cudaMemset(w.tc_err, 0, sizeof(int)));
+    // f32 graphs: buffers of the split-operand tensor-core path for the un-batched products of tensor-core shape
+    // (PCPB_F32_TC=0 keeps them on the general kernel)
+    {
+      const char* e = getenv("PCPB_F32_TC");
+      size_t ab = 0, cc = 0;
+      for (const GOp& op : b->graph.ops) {
+        if (op.kind != G_DOT || !op.a.empty()) continue;
+        const GValue &x = b->graph.vals[op.in[0]], &y = b->graph.vals[op.in[1]];
+        long long K = 1;
+        for (int64_t i : op.c) K *= x.shape[i];
+        const long long Mm = x.numel / K, Nn = y.numel / K;
+        if (Mm % 128 || Nn % 128 || K % 64) continue;
+        ab = std::max<size_t>(ab, (size_t)std::max<long long>(Mm, Nn) * (size_t)K * 12);
+        cc = std::max<size_t>(cc, (size_t)Mm * (size_t)Nn * 4);
+      }
+      if (c.dtype == DT_F32 && !(e && e[0] == '0') && ab && 2 * ab + cc <= ((size_t)24 << 30)) {
+        WS(b, w.pk_a, ab); WS(b, w.pk_b, ab); WS(b, w.pk_c, cc);
+        w.pk_ab_bytes = ab; w.pk_c_bytes = cc;
+        const size_t want = (size_t)64 << 20;
+        WS(b, w.tc_scratch, want); w.tc_scratch_bytes = want;
+      }
+    }
     std::vector<int64_t> offs;
     for (const TensorInfo& t : c.params) offs.push_back(t.offset);
     const std::string why = graph_exec_create(b->graph, (int)c.params.size(), offs, b->stream, &b->gx);
@@ -255,6 +277,29 @@ int drain_profile(pcpb_backend* b) {
 // ------------------------------------------------------------------------------------------------
 // GEMM dispatch: tensor-core kernel when the shape qualifies, generic kernel otherwise
 // ------------------------------------------------------------------------------------------------
+// f32 product of tensor-core shape: operands as sums of three bf16 pieces, one bf16 GEMM over 6 K with the exact
+// products accumulated in f32, then the generic kernel's epilogue on the f32 result (kernels.h).  *done = false when the
+// shape or the buffers do not allow it (nothing was launched then).
+int gemm_f32_split(pcpb_backend* b, const GemmArgs& g, bool* done) {
+  *done = false;
+  if (!b->force_generic && b->cfg.dtype == DT_F32 && b->ws.pk_a && g.M % 128 == 0 && g.N % 128 == 0 && g.K % 64 == 0 &&
+      (size_t)g.M * g.K * 12 <= b->ws.pk_ab_bytes && (size_t)g.N * g.K * 12 <= b->ws.pk_ab_bytes &&
+      (size_t)g.M * g.N * 4 <= b->ws.pk_c_bytes) {
+    GemmArgs t;
+    t.A = b->ws.pk_a; t.sam = 6LL * g.K; t.sak = 1; t.B = b->ws.pk_b; t.sbk = 1; t.sbn = 6LL * g.K;
+    t.C = b->ws.pk_c; t.ldc = g.N; t.R = nullptr; t.C2 = nullptr; t.M = g.M; t.N = g.N; t.K = 6 * g.K; t.epi = EPI_RAWF32; t.clip = 0.f;
+    t.scratch = b->ws.tc_scratch; t.scratch_bytes = b->ws.tc_scratch_bytes; t.err_word = b->ws.tc_err;
+    if (gemm_tc_supported(t)) {
+      KL(b, 1, launch_split3_pack(b->stream, (const float*)g.A, g.sam, g.sak, g.M, g.K, 0, b->ws.pk_a));
+      KL(b, 1, launch_split3_pack(b->stream, (const float*)g.B, g.sbn, g.sbk, g.N, g.K, 1, b->ws.pk_b));
+      KL(b, gemm_tc_launches(t), launch_gemm_tc(b->stream, t));
+      KL(b, 1, launch_gemm_epilogue_f32(b->stream, g, b->ws.pk_c));
+      *done = true;
+    }
+  }
+  return PCPB_OK;
+}
+
 int gemm(pcpb_backend* b, GemmArgs g) {
   g.scratch = b->ws.tc_scratch; g.scratch_bytes = b->ws.tc_scratch_bytes; g.err_word = b->ws.tc_err;
   if (!b->force_generic && b->cfg.dtype == DT_BF16 && gemm_tc_supported(g)) {
@@ -278,22 +323,10 @@ int gemm(pcpb_backend* b, GemmArgs g) {
     KL(b, gemm_tc_launches(g), launch_gemm_tc(b->stream, g));
     return PCPB_OK;
   }
-  // f32 model, shapes of the tensor-core kernel: operands as sums of three bf16 pieces, one bf16 GEMM over 6 K with the
-  // exact products accumulated in f32, then the generic kernel's epilogue on the f32 result (kernels.h)
-  if (!b->force_generic && b->cfg.dtype == DT_F32 && b->ws.pk_a && g.M % 128 == 0 && g.N % 128 == 0 && g.K % 64 == 0 &&
-      (size_t)g.M * g.K * 12 <= b->ws.pk_ab_bytes && (size_t)g.N * g.K * 12 <= b->ws.pk_ab_bytes &&
-      (size_t)g.M * g.N * 4 <= b->ws.pk_c_bytes) {
-    GemmArgs t;
-    t.A = b->ws.pk_a; t.sam = 6LL * g.K; t.sak = 1; t.B = b->ws.pk_b; t.sbk = 1; t.sbn = 6LL * g.K;
-    t.C = b->ws.pk_c; t.ldc = g.N; t.R = nullptr; t.C2 = nullptr; t.M = g.M; t.N = g.N; t.K = 6 * g.K; t.epi = EPI_RAWF32; t.clip = 0.f;
-    t.scratch = b->ws.tc_scratch; t.scratch_bytes = b->ws.tc_scratch_bytes; t.err_word = b->ws.tc_err;
-    if (gemm_tc_supported(t)) {
-      KL(b, 1, launch_split3_pack(b->stream, (const float*)g.A, g.sam, g.sak, g.M, g.K, 0, b->ws.pk_a));
-      KL(b, 1, launch_split3_pack(b->stream, (const float*)g.B, g.sbn, g.sbk, g.N, g.K, 1, b->ws.pk_b));
-      KL(b, gemm_tc_launches(t), launch_gemm_tc(b->stream, t));
-      KL(b, 1, launch_gemm_epilogue_f32(b->stream, g, b->ws.pk_c));
-      return PCPB_OK;
-    }
+  {
+    bool done = false;
+    int r = gemm_f32_split(b, g, &done);
+    if (r || done) return r;
   }
   KL(b, 1, launch_gemm_generic(b->stream, b->cfg.dtype, g));
   return PCPB_OK;
@@ -327,7 +360,13 @@ int forward_backward_graph(pcpb_backend* b, const void* wts, const long long* id
   auto dot2d = [&](int dt, const GemmArgs& g0) -> int {
     GemmArgs g = g0;
     g.scratch = b->ws.tc_scratch; g.scratch_bytes = b->ws.tc_scratch_bytes; g.err_word = b->ws.tc_err;
-    if (b->force_generic || dt != DT_BF16 || !gemm_tc_supported(g)) return 1;
+    if (b->force_generic) return 1;
+    if (dt == DT_F32 && b->cfg.dtype == DT_F32) {
+      bool done = false;
+      if ((hook_rc = gemm_f32_split(b, g, &done))) return 2;
+      return done ? 0 : 1;
+    }
+    if (dt != DT_BF16 || !gemm_tc_supported(g)) return 1;
     b->launches += gemm_tc_launches(g);
     if (launch_gemm_tc(b->stream, g) != cudaSuccess) { hook_rc = PCPB_E_CUDA; return 2; }
     return 0;
