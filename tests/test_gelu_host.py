@@ -59,15 +59,20 @@ def test_gelu_changes_the_loss():
     assert abs(float(lr) - float(lg)) > 1e-4
 
 
-def test_recogniser_accepts_gelu_and_refuses_other_activations(lib_built):
+def test_recogniser_accepts_gelu_and_refuses_other_activations(lib_built, monkeypatch):
     cfg, text = make_model(GPT_GELU_F32)
     f = inspect_artifact(text)
     assert (f["d_model"], f["n_layer"], f["d_ff"], f["total_params"]) == (cfg.d_model, cfg.n_layer, 4 * cfg.d_model, cfg.num_params())
-    # a different cubic coefficient is not the activation the kernels implement
-    with pytest.raises(BackendError) as ei:
-        inspect_artifact(text.replace("4.47149985e-02", "5.00000000e-02"))
-    assert ei.value.code == bk.E_ARTIFACT
-    # one tanh removed: the count no longer matches the layer count
-    with pytest.raises(BackendError) as ei:
-        inspect_artifact(text.replace("stablehlo.tanh", "stablehlo.negate", 1))
-    assert ei.value.code == bk.E_ARTIFACT
+    assert f["family"] == "fused"
+    # a different cubic coefficient is not the activation the fused kernels implement, nor is a graph with one tanh
+    # removed (the count no longer matches the layer count): the fused recogniser refuses both ...
+    others = (text.replace("4.47149985e-02", "5.00000000e-02"), text.replace("stablehlo.tanh", "stablehlo.negate", 1))
+    monkeypatch.setenv("PCPB_FRONTEND", "fused")
+    for other in others:
+        with pytest.raises(BackendError) as ei:
+            inspect_artifact(other)
+        assert ei.value.code == bk.E_ARTIFACT
+    # ... and without that restriction they run op by op on the general front end
+    monkeypatch.delenv("PCPB_FRONTEND")
+    for other in others:
+        assert inspect_artifact(other)["family"] == "graph"
