@@ -12,9 +12,12 @@
  * Shepherd holds before compiling, src/algorithms/diloco.zig:153), of the nanochat family (RMSNorm, RoPE,
  * QK-norm, ReLU^2, soft-capped loss) or the nanoGPT family (LayerNorm, learned positions, ReLU or tanh-GELU MLP,
  * biased head).  The backend recognises the model from the @main signature, the RoPE table resources, the
- * soft-cap constant and the activation's ops, refuses anything else with PCPB_E_ARTIFACT, and implements for it the functions the reference's graph builder emits
+ * soft-cap constant and the activation's ops, and implements for it the functions the reference's graph builder emits
  * (src/compiler/graph_builder.zig:56-278), including the sanitiser's and the autodiff engine's guard
- * terms (src/compiler/sanitizer.zig:8-111, src/autodiff/vjp_rules.zig).
+ * terms (src/compiler/sanitizer.zig:8-111, src/autodiff/vjp_rules.zig), with fused kernels.  Any other forward graph
+ * (parameters..., ids [B,T] i64, targets [B,T] i64) -> scalar loss over the StableHLO ops of the reference's exports
+ * runs through the general front end: the same functions, one kernel per op of the program pcpb_graph_describe shows.
+ * What neither path can run is refused with PCPB_E_ARTIFACT and a reason.
  */
 #ifndef PCP_B200_H
 #define PCP_B200_H
