@@ -200,6 +200,20 @@ template <typename U> __global__ void k_gather_nd(const U* in, U* out, long long
   }
 }
 
+// The same walk with 32-bit arithmetic, one warp per run of the innermost dimension: the mixed-radix decomposition is
+// done once per run instead of once per element (the divisions, not the loads, bound the element-wise form).
+template <typename U> __global__ void k_gather_rows_nd(const U* in, U* out, unsigned n_rows, unsigned inner, NdDesc d) {
+  const unsigned lane = threadIdx.x & 31, warps = (gridDim.x * blockDim.x) >> 5;
+  const long long s_in = d.stride[d.rank - 1];
+  for (unsigned row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < n_rows; row += warps) {
+    unsigned rem = row;
+    long long src = d.offset;
+    for (int k = d.rank - 2; k >= 0; --k) { const unsigned dk = (unsigned)d.dim[k]; src += (long long)(rem % dk) * d.stride[k]; rem /= dk; }
+    U* o = out + (size_t)row * inner;
+    for (unsigned c = lane; c < inner; c += 32) o[c] = in[src + (long long)c * s_in];
+  }
+}
+
 // out[offset + sum coord_k * stride_k] = in[i]: concatenate (one launch per operand), pad
 template <typename U> __global__ void k_scatter_nd(const U* in, U* out, long long n, NdDesc d) {
   GRID_STRIDE(i, n) {
@@ -392,6 +406,19 @@ int blocks_for(long long n) {
   if (b < 1) b = 1;
   if (b > 148 * 32) b = 148 * 32;
   return (int)b;
+}
+
+// merges neighbouring dimensions of a gather walk that the source also holds like one dimension, drops extents of 1
+void collapse_walk(NdDesc* d) {
+  NdDesc r;
+  r.rank = 0; r.offset = d->offset;
+  for (int k = 0; k < d->rank; ++k) {
+    if (d->dim[k] == 1) continue;
+    if (r.rank > 0 && r.stride[r.rank - 1] == d->stride[k] * d->dim[k]) { r.dim[r.rank - 1] *= d->dim[k]; r.stride[r.rank - 1] = d->stride[k]; continue; }
+    r.dim[r.rank] = d->dim[k]; r.stride[r.rank] = d->stride[k]; r.rank += 1;
+  }
+  if (r.rank == 0) { r.rank = 1; r.dim[0] = 1; r.stride[0] = 0; }
+  *d = r;
 }
 
 std::vector<long long> row_major_strides(const std::vector<int64_t>& shape) {
@@ -670,7 +697,15 @@ std::string run_op(GraphExec& e, const GOp& op, cudaStream_t st, bool dry, const
         }
       }
       if (dry) return "";
-      BY_SIZE(es, k_gather_nd<U><<<nb, TPB, 0, st>>>((const U*)in(0), (U*)out, n, d));
+      collapse_walk(&d);
+      const long long inner = d.dim[d.rank - 1];
+      if (inner >= 32 && n < 0x7FFFFFFFLL) {
+        const unsigned n_rows = (unsigned)(n / inner);
+        const int rb = (int)std::min<long long>(((long long)n_rows * 32 + TPB - 1) / TPB, 148 * 32);
+        BY_SIZE(es, k_gather_rows_nd<U><<<rb, TPB, 0, st>>>((const U*)in(0), (U*)out, n_rows, (unsigned)inner, d));
+      } else {
+        BY_SIZE(es, k_gather_nd<U><<<nb, TPB, 0, st>>>((const U*)in(0), (U*)out, n, d));
+      }
       count(1);
       break;
     }
@@ -888,6 +923,37 @@ std::string graph_exec_create(const Graph& g, int n_params, const std::vector<in
   // runs inside the producing kernel (PCPB_GRAPH_FUSE=0 keeps them apart)
   e->skip.assign(nops, 0);
   e->post_of.assign(nops, -1);
+  // A guard + clamp of a value that is known to be finite and inside the bounds already is the identity and shares its
+  // operand's storage: the operand is itself a guarded value, or pure data movement (reshape, transpose, slice,
+  // broadcast, pad, concatenate, gather, select) of guarded values and in-range constants.  The AD rules produce many:
+  // add, reshape, transpose, slice, broadcast and select hand an already guarded adjoint on.
+  {
+    const char* fe = getenv("PCPB_GRAPH_FUSE");
+    const GOp* first = nullptr;
+    for (int i = g.n_forward_ops; i < nops && !first; ++i) if (g.ops[i].kind == G_GUARD_CLAMP) first = &g.ops[i];
+    std::vector<char> guarded(nv, 0);
+    for (int i = 0; i < nops && first && !(fe && fe[0] == '0'); ++i) {
+      const GOp& op = g.ops[i];
+      auto in_ok = [&](size_t k) { return k < op.in.size() && guarded[op.in[k]]; };
+      bool ok = false;
+      switch (op.kind) {
+        case G_GUARD_CLAMP:
+          if (op.sub == first->sub && op.lo == first->lo && op.hi == first->hi) {
+            if (in_ok(0) && e->need_all[i] && !e->is_const_op[i]) e->skip[i] = 1;
+            ok = true;
+          }
+          break;
+        case G_CONST_SPLAT: ok = is_fp(g.vals[op.out].dt) && std::isfinite(op.fval) && (!first->sub || (op.fval >= first->lo && op.fval <= first->hi)); break;
+        case G_RESHAPE: case G_TRANSPOSE: case G_SLICE: case G_BCAST: case G_PAD: case G_GATHER_ROWS: case G_GATHER2: ok = in_ok(0); break;
+        case G_CONVERT: ok = in_ok(0) && g.vals[op.in[0]].dt == g.vals[op.out].dt; break;
+        case G_SELECT: ok = in_ok(1) && in_ok(2); break;
+        case G_CONCAT: ok = true; for (size_t k = 0; k < op.in.size(); ++k) ok = ok && in_ok(k); break;
+        case G_UNARY: ok = op.sub == U_NEG && in_ok(0) && (!first->sub || first->lo == -first->hi); break;
+        default: break;
+      }
+      guarded[op.out] = ok;
+    }
+  }
   {
     const char* fe = getenv("PCPB_GRAPH_FUSE");
     std::vector<int> readers(nv, 0);
@@ -896,7 +962,7 @@ std::string graph_exec_create(const Graph& g, int n_params, const std::vector<in
     for (int v : outs) if (v >= 0) readers[v] += 1;
     for (int i = g.n_forward_ops; i < nops && !(fe && fe[0] == '0'); ++i) {
       const GOp& op = g.ops[i];
-      if (!e->need_all[i] || op.kind != G_GUARD_CLAMP || e->is_const_op[i]) continue;
+      if (!e->need_all[i] || op.kind != G_GUARD_CLAMP || e->is_const_op[i] || e->skip[i]) continue;
       const int v = op.in[0], j = g.vals[v].op;
       if (j < g.n_forward_ops || !e->need_all[j] || e->is_const_op[j] || readers[v] != 1 || e->post_of[j] >= 0) continue;
       if (!(g.ops[j].kind == G_UNARY || g.ops[j].kind == G_BINARY) || !is_fp(g.vals[v].dt)) continue;
