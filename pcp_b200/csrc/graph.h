@@ -79,7 +79,7 @@ struct Graph {
 std::string graph_parse(const char* text, size_t n, bool sanitize, Graph* g);
 // Appends the gradient program for the first n_params arguments (float tensors).  clamp = 0 leaves the clamp out.
 std::string graph_add_gradients(Graph* g, int n_params, int clamp, float lo, float hi);
-// One line per value and op (the format tests/test_graph_frontend.py reads).
+// One line per value and op (the format tests/graph_program.py reads).
 std::string graph_dump(const Graph& g);
 
 }  // namespace pcpb

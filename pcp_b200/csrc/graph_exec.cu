@@ -110,10 +110,27 @@ template <typename C> __device__ __forceinline__ C pow_fp(C x, C e) {
   return pow(x, e);
 }
 
-template <typename T> __global__ void k_binary(int sub, const T* a, const T* b, T* out, long long n, Post post) {
+// How a binary op reads an operand: the tensor itself, a broadcast that was not materialised (one value per run of
+// `inner` elements, one value per position inside such a run, or one value for all), or a splat constant.
+enum : int { O_DIRECT = 0, O_PER_RUN, O_IN_RUN, O_SCALAR, O_IMM };
+struct Opnd { int mode; unsigned inner; double imm; long long iimm; };
+
+template <typename T> __device__ __forceinline__ typename TT<T>::C ldo(const T* p, long long i, const Opnd& o) {
+  typedef typename TT<T>::C C;
+  switch (o.mode) {
+    case O_DIRECT: return ld(p, i);
+    case O_PER_RUN: return ld(p, (long long)((unsigned)i / o.inner));
+    case O_IN_RUN: return ld(p, (long long)((unsigned)i % o.inner));
+    case O_SCALAR: return ld(p, 0);
+    default:
+      if constexpr (TT<T>::is_fp) return (C)o.imm; else return (C)o.iimm;
+  }
+}
+
+template <typename T> __global__ void k_binary(int sub, const T* a, const T* b, T* out, long long n, Post post, Opnd oa, Opnd ob) {
   typedef typename TT<T>::C C;
   GRID_STRIDE(i, n) {
-    const C x = ld(a, i), y = ld(b, i);
+    const C x = ldo(a, i, oa), y = ldo(b, i, ob);
     C r;
     if constexpr (TT<T>::is_fp) {
       switch (sub) {
@@ -502,6 +519,9 @@ struct GraphExec {
   std::vector<long long> off;            // per root: byte offset in its arena
   std::vector<char> need_fwd, need_all;  // per op
   std::vector<char> is_const_op;
+  struct OperandSrc { int mode = 0; unsigned inner = 1; int src = -1; double imm = 0.0; long long iimm = 0; };
+  std::vector<OperandSrc> opnd;          // per op, two entries: how a binary op reads its operands (O_* modes)
+  std::vector<char> absorbed;            // per op: a broadcast_in_dim that its only reader takes as a strided operand
   std::vector<char> skip;                // per op: a guard + clamp that runs inside its producer
   std::vector<int> post_of;              // per op: the guard + clamp op fused into it, -1 if none
   char *const_arena = nullptr, *arena = nullptr;
@@ -588,7 +608,7 @@ bool cols_form(const GValue& x, const std::vector<int64_t>& dims, long long* n_r
 int cols_chunks(long long n_red) { const long long c = (n_red + 255) / 256; return (int)(c < 1 ? 1 : (c > 64 ? 64 : c)); }
 
 std::string run_op(GraphExec& e, const GOp& op, cudaStream_t st, bool dry, const std::function<int(int, const GemmArgs&)>* dot2d,
-                   long long* launches, const GOp* fused_clamp = nullptr) {
+                   long long* launches, const GOp* fused_clamp = nullptr, const GraphExec::OperandSrc* osrc = nullptr) {
   Post post = {0, 0, 0.f, 0.f};
   if (fused_clamp) { post.on = 1; post.clamp = fused_clamp->sub; post.lo = fused_clamp->lo; post.hi = fused_clamp->hi; }
   const Graph& g = e.g;
@@ -636,7 +656,19 @@ std::string run_op(GraphExec& e, const GOp& op, cudaStream_t st, bool dry, const
       if (is_fp(o.dt) && (op.sub == B_AND || op.sub == B_OR)) return "logical op on a float type";
       if (!is_fp(o.dt) && op.sub == B_POW) return "power on an integer type";
       if (dry) return "";
-      BY_TYPE(o.dt, k_binary<T><<<nb, TPB, 0, st>>>(op.sub, (const T*)in(0), (const T*)in(1), (T*)out, n, post));
+      {
+        Opnd od[2];
+        const void* ptr[2];
+        for (int k = 0; k < 2; ++k) {
+          od[k].mode = O_DIRECT; od[k].inner = 1; od[k].imm = 0.0; od[k].iimm = 0;
+          ptr[k] = nullptr;
+          if (osrc && osrc[k].mode != O_DIRECT) {
+            od[k].mode = osrc[k].mode; od[k].inner = osrc[k].inner; od[k].imm = osrc[k].imm; od[k].iimm = osrc[k].iimm;
+            if (osrc[k].mode != O_IMM) ptr[k] = ptr_of(e, osrc[k].src);
+          } else ptr[k] = in(k);
+        }
+        BY_TYPE(o.dt, k_binary<T><<<nb, TPB, 0, st>>>(op.sub, (const T*)ptr[0], (const T*)ptr[1], (T*)out, n, post, od[0], od[1]));
+      }
       count(1);
       break;
     case G_COMPARE: {
@@ -977,6 +1009,82 @@ std::string graph_exec_create(const Graph& g, int n_params, const std::vector<in
     const GOp& op = g.ops[i];
     if (op.kind == G_RESHAPE || (op.kind == G_CONVERT && g.vals[op.in[0]].dt == g.vals[op.out].dt) || e->skip[i]) e->root[op.out] = e->root[op.in[0]];
   }
+  // Operands of binary ops that need no tensor of their own: a broadcast_in_dim read by this op alone, of the forms
+  // [rows, 1] -> [rows, inner], [inner] -> [rows, inner] or scalar -> anything, is read from its source with the index
+  // arithmetic done in the kernel, and a constant that is a splat (through broadcasts and reshapes) is an immediate.
+  // PCPB_GRAPH_FUSE=0 keeps every operand a tensor.
+  e->opnd.assign(2 * (size_t)nops, GraphExec::OperandSrc());
+  e->absorbed.assign(nops, 0);
+  {
+    const char* fe = getenv("PCPB_GRAPH_FUSE");
+    const bool on = !(fe && fe[0] == '0');
+    auto is_view = [&](int i) {
+      const GOp& op = g.ops[i];
+      return op.kind == G_RESHAPE || (op.kind == G_CONVERT && g.vals[op.in[0]].dt == g.vals[op.out].dt) || e->skip[i];
+    };
+    std::vector<std::vector<std::pair<int, int>>> kreaders(nv);
+    std::vector<char> is_out(nv, 0);
+    for (int i = 0; i < nops; ++i)
+      if (e->need_all[i] && !is_view(i))
+        for (size_t k = 0; k < g.ops[i].in.size(); ++k) kreaders[e->root[g.ops[i].in[k]]].push_back({i, (int)k});
+    for (int v : outs) if (v >= 0) is_out[e->root[v]] = 1;
+    for (int j = 0; j < nops && on; ++j) {
+      const GOp& op = g.ops[j];
+      if (!e->need_all[j] || e->is_const_op[j] || op.kind != G_BCAST || e->root[op.out] != op.out || is_out[op.out]) continue;
+      const auto& rd = kreaders[op.out];
+      if (rd.size() != 1) continue;
+      const int i = rd[0].first, k = rd[0].second;
+      const GValue &x = g.vals[op.in[0]], &o = g.vals[op.out];
+      if (g.ops[i].kind != G_BINARY || e->is_const_op[i] || o.numel >= 0x7FFFFFFFLL || op.a.size() != x.shape.size()) continue;
+      const std::vector<long long> xs = row_major_strides(x.shape);
+      NdDesc d;
+      d.rank = (int)o.shape.size(); d.offset = 0;
+      bool ok = d.rank <= MAX_RANK;
+      for (int q = 0; q < d.rank && ok; ++q) { d.dim[q] = o.shape[q]; d.stride[q] = 0; }
+      for (size_t q = 0; q < op.a.size() && ok; ++q) {
+        const int64_t dst = op.a[q];
+        if (dst < 0 || dst >= d.rank || (x.shape[q] != 1 && x.shape[q] != o.shape[dst])) { ok = false; break; }
+        d.stride[dst] = (x.shape[q] == 1) ? 0 : xs[q];
+      }
+      if (!ok) continue;
+      collapse_walk(&d);
+      GraphExec::OperandSrc os;
+      os.src = op.in[0];
+      if (d.rank == 1 && d.stride[0] == 0) os.mode = O_SCALAR;
+      else if (d.rank == 2 && d.stride[0] == 1 && d.stride[1] == 0) { os.mode = O_PER_RUN; os.inner = (unsigned)d.dim[1]; }
+      else if (d.rank == 2 && d.stride[0] == 0 && d.stride[1] == 1) { os.mode = O_IN_RUN; os.inner = (unsigned)d.dim[1]; }
+      else continue;
+      e->opnd[2 * (size_t)i + k] = os;
+      e->absorbed[j] = 1;
+    }
+    // splat constants as immediates
+    auto splat_of = [&](int v, double* f, long long* iv) {
+      for (int hops = 0; hops < 8; ++hops) {
+        const int pi = g.vals[v].op;
+        if (pi < 0 || !e->is_const_op[pi]) return false;
+        const GOp& po = g.ops[pi];
+        if (po.kind == G_CONST_SPLAT) {
+          const int dt = g.vals[po.out].dt;
+          *f = dt == DT_F64 ? po.fval : (double)(dt == DT_BF16 ? __bfloat162float(__float2bfloat16_rn((float)po.fval)) : (float)po.fval);
+          *iv = dt == DT_BOOL ? (po.ival != 0) : (dt == DT_I32 ? (long long)(int)po.ival : po.ival);
+          return true;
+        }
+        if (po.kind == G_BCAST || po.kind == G_RESHAPE) { v = po.in[0]; continue; }
+        return false;
+      }
+      return false;
+    };
+    for (int i = 0; i < nops && on; ++i) {
+      const GOp& op = g.ops[i];
+      if (!e->need_all[i] || e->is_const_op[i] || op.kind != G_BINARY) continue;
+      for (int k = 0; k < 2; ++k) {
+        GraphExec::OperandSrc& os = e->opnd[2 * (size_t)i + k];
+        if (os.mode != O_DIRECT) continue;
+        double f; long long iv;
+        if (g.vals[op.in[k]].dt == g.vals[op.out].dt && splat_of(op.in[k], &f, &iv)) { os.mode = O_IMM; os.imm = f; os.iimm = iv; }
+      }
+    }
+  }
   // every needed op must have a kernel
   for (int i = 0; i < nops; ++i) {
     if (!e->need_all[i]) continue;
@@ -996,8 +1104,17 @@ std::string graph_exec_create(const Graph& g, int n_params, const std::vector<in
     if (!e->need_all[i]) continue;
     const GOp& op = g.ops[i];
     if (e->is_const_op[i]) { e->where[e->root[op.out]] = W_CONST; continue; }
+    if (e->absorbed[i]) continue;                        // never materialised: its reader takes the source
     last[e->root[op.out]] = std::max<long long>(last[e->root[op.out]], i);
-    for (int x : op.in) last[e->root[x]] = std::max<long long>(last[e->root[x]], i);
+    for (size_t k = 0; k < op.in.size(); ++k) {
+      int x = op.in[k];
+      if (op.kind == G_BINARY && k < 2) {
+        const GraphExec::OperandSrc& os = e->opnd[2 * (size_t)i + k];
+        if (os.mode == O_IMM) continue;
+        if (os.mode != O_DIRECT) x = os.src;
+      }
+      last[e->root[x]] = std::max<long long>(last[e->root[x]], i);
+    }
   }
   for (int v : outs) if (v >= 0) last[e->root[v]] = FOREVER;
   size_t cbytes = 0;
@@ -1005,7 +1122,7 @@ std::string graph_exec_create(const Graph& g, int n_params, const std::vector<in
   std::vector<char> placed(nv, 0);
   std::map<long long, std::vector<int>> dies;     // op index -> roots to release after it
   for (int i = 0; i < nops; ++i) {
-    if (!e->need_all[i]) continue;
+    if (!e->need_all[i] || e->absorbed[i]) continue;
     const GOp& op = g.ops[i];
     const int r = e->root[op.out];
     const size_t bytes = round256((size_t)g.vals[r].numel * dtype_size(g.vals[r].dt));
@@ -1076,11 +1193,12 @@ std::string enqueue_run(GraphExec* e, cudaStream_t st, const GraphBind& bind, co
   const int upto = bind.backward ? (int)g.ops.size() : g.n_forward_ops;
   const std::vector<char>& need = bind.backward ? e->need_all : e->need_fwd;
   for (int i = 0; i < upto; ++i) {
-    if (!need[i] || e->is_const_op[i] || e->skip[i]) continue;
+    if (!need[i] || e->is_const_op[i] || e->skip[i] || e->absorbed[i]) continue;
     GOp seed_op;
     const GOp* op = &g.ops[i];
     if (op->kind == G_SEED) { seed_op = *op; seed_op.fval = (double)bind.seed; seed_op.ival = (long long)bind.seed; op = &seed_op; }
-    const std::string why = run_op(*e, *op, st, false, &dot2d, launches, e->post_of[i] >= 0 ? &g.ops[e->post_of[i]] : nullptr);
+    const std::string why = run_op(*e, *op, st, false, &dot2d, launches, e->post_of[i] >= 0 ? &g.ops[e->post_of[i]] : nullptr,
+                                   &e->opnd[2 * (size_t)i]);
     if (!why.empty()) return why;
   }
   const GValue& r = g.vals[g.ret];
