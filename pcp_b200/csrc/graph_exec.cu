@@ -1149,6 +1149,15 @@ std::string graph_exec_create(const Graph& g, int n_params, const std::vector<in
     return failed(m);
   }
   e->ext.assign(nv, nullptr);
+  // PCPB_POISON=1 (as for the workspace of the fused families): NaN patterns in the arenas, so that an op reading a
+  // value nothing wrote shows up in the parity tests
+  {
+    const char* pe = getenv("PCPB_POISON");
+    if (pe && pe[0] == '1') {
+      cudaMemset(e->arena, 0xFF, e->arena_bytes ? e->arena_bytes : 256);
+      cudaMemset(e->const_arena, 0xFF, cbytes ? cbytes : 256);
+    }
+  }
   // scratch of the column reductions: [chunks][n_out] partials of the widest one
   {
     size_t want = 0;
