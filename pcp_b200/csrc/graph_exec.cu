@@ -527,6 +527,8 @@ struct GraphExec {
   char *const_arena = nullptr, *arena = nullptr;
   char* red_scratch = nullptr;           // per-chunk partials of the column reductions
   size_t red_scratch_bytes = 0;
+  char* scat_scratch = nullptr;          // sort buffers (and an f32 result for bf16) of the ordered row scatter
+  size_t scat_scratch_bytes = 0;
   size_t const_bytes = 0, arena_bytes = 0;
   std::vector<const void*> ext;          // per value: pointer of an external value (set per run)
   // CUDA graphs of whole runs, keyed by the bindings (pointers, seed, direction); a binding seen for the second time is
@@ -897,6 +899,22 @@ std::string run_op(GraphExec& e, const GOp& op, cudaStream_t st, bool dry, const
       if (op.kind == G_SCATTER_ROWS ? (g.vals[op.in[1]].numel * rowlen != gr.numel) : (o.shape.size() != 2 || g.vals[op.in[1]].numel != 2 * gr.numel))
         return "scatter: shape mismatch";
       if (dry) return "";
+      if (op.kind == G_SCATTER_ROWS && e.scat_scratch && (o.dt == DT_F32 || o.dt == DT_BF16)) {
+        // the embedding-gradient form: rows sorted by index (stable), summed in position order in f32 — no float
+        // atomics, the same bits every run (embed_scatter.cu); indices are clamped like the gather's
+        const int M = (int)g.vals[op.in[1]].numel, d = (int)rowlen, V = (int)o.shape[0];
+        const size_t sorted_bytes = embed_scatter_scratch_bytes(M, d);
+        const size_t tmp_bytes = o.dt == DT_BF16 ? (size_t)n * 4 : 0;
+        if (sorted_bytes + tmp_bytes <= e.scat_scratch_bytes) {
+          float* acc = o.dt == DT_F32 ? (float*)out : (float*)(e.scat_scratch + sorted_bytes);
+          if (cudaMemsetAsync(acc, 0, (size_t)n * 4, st) != cudaSuccess) return "memset failed";
+          if (launch_embed_scatter_sorted(st, o.dt, (const long long*)in(1), M, d, V, in(0), e.scat_scratch, sorted_bytes, acc) != cudaSuccess)
+            return "the ordered row scatter failed";
+          count(6);
+          if (o.dt == DT_BF16) { convert(st, acc, DT_F32, out, DT_BF16, n); count(1); }
+          break;
+        }
+      }
       if (cudaMemsetAsync(out, 0, (size_t)n * es, st) != cudaSuccess) return "memset failed";
       const int gb = blocks_for(gr.numel);
       if (op.kind == G_SCATTER_ROWS) {
@@ -1171,6 +1189,24 @@ std::string graph_exec_create(const Graph& g, int n_params, const std::vector<in
       e->red_scratch_bytes = want;
     }
   }
+  // scratch of the ordered row scatter (PCPB_EMBED_ATOMIC=1: float atomics instead, as for the fused families)
+  {
+    const char* ae = getenv("PCPB_EMBED_ATOMIC");
+    size_t want = 0;
+    for (int i = 0; i < nops && !(ae && ae[0] == '1'); ++i) {
+      const GOp& op = g.ops[i];
+      if (!e->need_all[i] || op.kind != G_SCATTER_ROWS) continue;
+      const GValue& o = g.vals[op.out];
+      const long long M = g.vals[op.in[1]].numel, V = o.shape.empty() ? 0 : o.shape[0];
+      if (!(o.dt == DT_F32 || o.dt == DT_BF16) || V <= 0 || M <= 0 || M >= 0x7FFFFFFFLL || V >= 0x7FFFFFFFLL || o.numel / V >= 0x7FFFFFFFLL) continue;
+      const size_t need = round256(embed_scatter_scratch_bytes((int)M, (int)(o.numel / V))) + (o.dt == DT_BF16 ? (size_t)o.numel * 4 : 0);
+      want = std::max(want, need);
+    }
+    if (want) {
+      if (cudaMalloc(&e->scat_scratch, want) != cudaSuccess) { e->scat_scratch = nullptr; return failed("cudaMalloc of the scatter scratch failed"); }
+      e->scat_scratch_bytes = want;
+    }
+  }
   // the constant part, once
   for (int i = 0; i < nops; ++i) {
     if (!e->need_all[i] || !e->is_const_op[i]) continue;
@@ -1188,6 +1224,7 @@ void graph_exec_destroy(GraphExec* e) {
   if (e->const_arena) cudaFree(e->const_arena);
   if (e->arena) cudaFree(e->arena);
   if (e->red_scratch) cudaFree(e->red_scratch);
+  if (e->scat_scratch) cudaFree(e->scat_scratch);
   delete e;
 }
 
