@@ -222,7 +222,9 @@ int pcpb_worker_set_sampling(pcpb_backend* b, int mode, uint64_t seed);
  *                              reference's clamped arithmetic at every edge listed above
  *   bit 1 (PCPB_ADJ_INTERNAL)  an adjoint inside the fused attention backward was beyond +-100: from there on the
  *                              gradients are those of the unclamped softmax backward, clamped where they leave the kernel
- * 0 means no guard or clamp of the reference was active: gradients are those of the reference's engine.  Blocks. */
+ * 0 means no guard or clamp of the reference was active: gradients are those of the reference's engine.  Blocks.
+ * A graph run by the general front end applies every guard and clamp as an op of its program, exactly where the engine
+ * does; nothing is approximated there and nothing is recorded: the flags stay 0 for it. */
 #define PCPB_ADJ_CLAMPED 1
 #define PCPB_ADJ_INTERNAL 2
 int pcpb_adjoint_status(pcpb_backend* b, int* flags, int clear);
