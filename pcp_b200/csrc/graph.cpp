@@ -6,6 +6,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <deque>
 #include <map>
 
@@ -404,8 +405,15 @@ std::string graph_parse(const char* text, size_t n, bool sanitize, Graph* g) {
     const std::vector<int64_t> oshape = tshapes.back();
     const int odt = tdts.back();
     std::string name, after;
+    if (head.empty()) return "op without a name: " + s.substr(0, 80);
+    for (const auto& sh : tshapes) {
+      int64_t nel = 1;
+      for (int64_t dsz : sh) { if (dsz < 0 || (dsz > 0 && nel > ((int64_t)1 << 40) / dsz)) return "tensor too large: " + s.substr(0, 80); nel *= dsz; }
+      if (sh.size() > 8) return "tensor rank above 8: " + s.substr(0, 80);
+    }
     if (head[0] == '"') {
       const size_t q = head.find('"', 1);
+      if (q == std::string::npos) return "cannot parse line: " + s.substr(0, 80);
       name = head.substr(1, q - 1);
       after = head.substr(q + 1);
     } else {
@@ -417,6 +425,7 @@ std::string graph_parse(const char* text, size_t n, bool sanitize, Graph* g) {
     GOp op;
     if (name == "stablehlo.constant" || name == "arith.constant") {
       const std::string v = trim(after);
+      if (v.empty()) return "constant without a value: %" + res;
       if (v.compare(0, 15, "dense_resource<") == 0) {
         const std::string key = v.substr(15, v.find('>') - 15);
         if (!resources.count(key)) return "constant refers to an unknown resource: " + key;
@@ -562,6 +571,78 @@ std::string graph_parse(const char* text, size_t n, bool sanitize, Graph* g) {
       } else return "gather: unsupported dimension numbers (%" + res + ")";
     } else {
       return "unsupported op " + name;
+    }
+    // attribute checks: everything that later code indexes with must be in range
+    {
+      auto in_range = [](const std::vector<int64_t>& v, int64_t n) { for (int64_t x : v) if (x < 0 || x >= n) return false; return true; };
+      auto distinct = [](std::vector<int64_t> v) { std::sort(v.begin(), v.end()); return std::adjacent_find(v.begin(), v.end()) == v.end(); };
+      const int64_t orank = (int64_t)oshape.size();
+      const int64_t irank = in.empty() ? 0 : (int64_t)bld.V(in[0]).shape.size();
+      switch (op.kind) {
+        case G_TRANSPOSE:
+          if (!in_range(op.a, irank) || !distinct(op.a) || orank != irank) return "transpose: not a permutation (%" + res + ")";
+          for (int64_t k = 0; k < orank; ++k) if (oshape[k] != bld.V(in[0]).shape[op.a[k]]) return "transpose: result shape mismatch (%" + res + ")";
+          break;
+        case G_BCAST:
+          if (!in_range(op.a, orank) || !distinct(op.a)) return "broadcast_in_dim: dims out of range (%" + res + ")";
+          for (size_t k = 0; k < op.a.size(); ++k) {
+            const int64_t sz = bld.V(in[0]).shape[k];
+            if (sz != 1 && sz != oshape[op.a[k]]) return "broadcast_in_dim: operand does not fit the result (%" + res + ")";
+          }
+          break;
+        case G_REDUCE: {
+          if (!in_range(op.a, irank) || !distinct(op.a)) return "reduce: dimensions out of range (%" + res + ")";
+          std::vector<int64_t> kept;
+          for (int64_t k = 0; k < irank; ++k) if (std::find(op.a.begin(), op.a.end(), k) == op.a.end()) kept.push_back(bld.V(in[0]).shape[k]);
+          if (kept != oshape || bld.V(in[1]).numel != 1) return "reduce: result shape mismatch (%" + res + ")";
+          break;
+        }
+        case G_CONCAT: {
+          if (!in_range(op.a, orank)) return "concatenate: dimension out of range (%" + res + ")";
+          int64_t total = 0;
+          for (int v : in) {
+            const GValue& x = bld.V(v);
+            if ((int64_t)x.shape.size() != orank || x.dt != odt) return "concatenate: operand types differ (%" + res + ")";
+            for (int64_t k = 0; k < orank; ++k) if (k != op.a[0] && x.shape[k] != oshape[k]) return "concatenate: operand shapes differ (%" + res + ")";
+            total += x.shape[op.a[0]];
+          }
+          if (total != oshape[op.a[0]]) return "concatenate: sizes do not add up (%" + res + ")";
+          break;
+        }
+        case G_IOTA:
+          if (!in_range(op.a, orank)) return "iota: dimension out of range (%" + res + ")";
+          break;
+        case G_SLICE:
+          if (orank != irank) return "slice: rank mismatch (%" + res + ")";
+          for (int64_t k = 0; k < irank; ++k)
+            if (op.c[k] < 1 || op.a[k] < 0 || op.b[k] < op.a[k] || op.b[k] > bld.V(in[0]).shape[k] ||
+                (op.b[k] - op.a[k] + op.c[k] - 1) / op.c[k] != oshape[k])
+              return "slice: bad range (%" + res + ")";
+          break;
+        case G_DOT: {
+          const int64_t rrank = (int64_t)bld.V(in[1]).shape.size();
+          std::vector<int64_t> l = op.a, r = op.b;
+          l.insert(l.end(), op.c.begin(), op.c.end());
+          r.insert(r.end(), op.d.begin(), op.d.end());
+          if (op.a.size() != op.b.size() || op.c.size() != op.d.size() || !in_range(l, irank) || !in_range(r, rrank) || !distinct(l) || !distinct(r))
+            return "dot_general: dimension numbers out of range (%" + res + ")";
+          for (size_t k = 0; k < op.a.size(); ++k)
+            if (bld.V(in[0]).shape[op.a[k]] != bld.V(in[1]).shape[op.b[k]]) return "dot_general: batch sizes differ (%" + res + ")";
+          break;
+        }
+        case G_SELECT:
+          if (bld.V(in[0]).dt != 6 /* i1 */ || bld.V(in[0]).shape != oshape || bld.V(in[1]).shape != oshape || bld.V(in[1]).dt != odt)
+            return "select: operand types (%" + res + ")";
+          break;
+        case G_COMPARE:
+          if (bld.V(in[0]).shape != bld.V(in[1]).shape || bld.V(in[0]).dt != bld.V(in[1]).dt || bld.V(in[0]).shape != oshape || odt != 6)
+            return "compare: operand types (%" + res + ")";
+          break;
+        case G_CONVERT:
+          if (bld.V(in[0]).shape != oshape) return "convert changes the shape (%" + res + ")";
+          break;
+        default: break;
+      }
     }
     if (op.kind == G_DOT) {
       const int v = bld.dot(in[0], in[1], op.a, op.b, op.c, op.d);

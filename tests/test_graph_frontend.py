@@ -103,3 +103,32 @@ def test_shipped_small_graph_program_matches_oracle(lib_built):
     assert float(loss) == float(mod.forward(params, ids, tg))
     for a, w in zip(grads, want):
         assert torch.equal(a, w)
+
+
+def test_malformed_attributes_are_refused_not_indexed_with(lib_built):
+    """Dimension numbers that do not fit their operands (a permutation with a repeated or out-of-range entry, broadcast /
+    reduce / concatenate / iota dimensions beyond the rank, a slice past the end, contracting dimensions that do not
+    exist) end with PCPB_E_ARTIFACT and a reason."""
+    import re
+    cfg, text = make_model(helpers.SMALL_F32)
+
+    def first(pattern, repl):
+        out, n = re.subn(pattern, repl, text, count=1)
+        assert n == 1, pattern
+        return out
+
+    bad = {
+        "transpose": first(r"(stablehlo\.transpose %\w+, dims = )\[1, 0\]", r"\1[1, 1]"),
+        "transpose range": first(r"(stablehlo\.transpose %\w+, dims = )\[0, 2, 1, 3\]", r"\1[0, 2, 1, 7]"),
+        "broadcast_in_dim": first(r"(stablehlo\.broadcast_in_dim %\w+, dims = )\[0, 1, 2\]", r"\1[0, 1, 5]"),
+        "reduce": first(r"(across dimensions = )\[2\]", r"\1[4]"),
+        "slice": first(r"\[0:(\d+), 0:(\d+), 0:(\d+), 0:8\]", r"[0:\1, 0:\2, 0:\3, 0:99]"),
+        "concatenate": first(r"(stablehlo\.concatenate %\w+, %\w+, dim = )3", r"\g<1>9"),
+        "dot_general": first(r"contracting_dims = \[1\] x \[0\]", "contracting_dims = [3] x [0]"),
+        "iota": first(r"stablehlo\.iota dim = 0", "stablehlo.iota dim = 6"),
+    }
+    for what, t in bad.items():
+        with pytest.raises(BackendError) as ei:
+            graph_describe(t)
+        assert ei.value.code == bk.E_ARTIFACT, what
+        assert what.split()[0] in str(ei.value), (what, str(ei.value))
