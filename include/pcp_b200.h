@@ -71,7 +71,9 @@ int pcpb_inspect_artifact(const void* bytes, size_t n, int64_t* facts, char* err
  * rules src/autodiff/vjp_rules.zig, adjoint edges engine.zig:604-702), after the stability patches of
  * src/compiler/sanitizer.zig:8-244.  Writes the tensor program (one line per value and per op; forward ops first, then,
  * if with_gradients, the gradient ops for every argument but the last two) as text into *text_out (release with
- * pcpb_free).  Needs no device.  A graph pcpb_inspect_artifact reports with d_model = 0 is run from this program
+ * pcpb_free).  with_gradients = 2 appends the executor's plan of that program: per value where it is stored (arena
+ * offset, the ops that define and release it), per op whether it runs, was folded into the constants, dropped or fused.
+ * Needs no device.  A graph pcpb_inspect_artifact reports with d_model = 0 is run from this program
  * (one kernel per op); PCPB_FRONTEND=graph in the environment sends every graph that way, PCPB_FRONTEND=fused none. */
 int pcpb_graph_describe(const void* bytes, size_t n, int with_gradients, char** text_out, char* err, size_t err_cap);
 

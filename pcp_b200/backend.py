@@ -270,13 +270,14 @@ def inspect_artifact(artifact) -> dict:
     return out
 
 
-def graph_describe(artifact, with_gradients: bool = True) -> str:
-    """The general front end's tensor program of a forward graph as text (see include/pcp_b200.h); no GPU needed."""
+def graph_describe(artifact, with_gradients: bool = True, with_plan: bool = False) -> str:
+    """The general front end's tensor program of a forward graph as text, with_plan: followed by the executor's plan
+    of it (see include/pcp_b200.h); no GPU needed."""
     lib = load_library()
     raw = artifact.encode() if isinstance(artifact, str) else artifact
     text = C.c_void_p()
     err = C.create_string_buffer(512)
-    rc = lib.pcpb_graph_describe(raw, len(raw), 1 if with_gradients else 0, C.byref(text), err, 512)
+    rc = lib.pcpb_graph_describe(raw, len(raw), 2 if with_plan else (1 if with_gradients else 0), C.byref(text), err, 512)
     if rc:
         raise BackendError(rc, err.value.decode())
     try:

@@ -531,6 +531,7 @@ struct GraphExec {
   size_t scat_scratch_bytes = 0;
   size_t const_bytes = 0, arena_bytes = 0;
   std::vector<const void*> ext;          // per value: pointer of an external value (set per run)
+  std::vector<long long> placed_at, freed_after;   // per root in the step arena: the op that defines it, the op after which its space is free (-1: never)
   // CUDA graphs of whole runs, keyed by the bindings (pointers, seed, direction); a binding seen for the second time is
   // captured, so one-off buffers never pay for an instantiation
   struct Captured { cudaGraphExec_t exec; long long launches; };
@@ -935,7 +936,7 @@ std::string run_op(GraphExec& e, const GOp& op, cudaStream_t st, bool dry, const
 }  // namespace
 
 std::string graph_exec_create(const Graph& g, int n_params, const std::vector<int64_t>& param_offsets, cudaStream_t st,
-                              GraphExec** out) {
+                              GraphExec** out, bool plan_only) {
   *out = nullptr;
   GraphExec* e = new GraphExec();
   e->g = g;
@@ -1137,6 +1138,8 @@ std::string graph_exec_create(const Graph& g, int n_params, const std::vector<in
   for (int v : outs) if (v >= 0) last[e->root[v]] = FOREVER;
   size_t cbytes = 0;
   FreeList fl;
+  e->placed_at.assign(nv, -1);
+  e->freed_after.assign(nv, -1);
   std::vector<char> placed(nv, 0);
   std::map<long long, std::vector<int>> dies;     // op index -> roots to release after it
   for (int i = 0; i < nops; ++i) {
@@ -1148,10 +1151,11 @@ std::string graph_exec_create(const Graph& g, int n_params, const std::vector<in
       if (r == op.out && !placed[r]) { e->off[r] = (long long)cbytes; cbytes += bytes; placed[r] = 1; }
       continue;
     }
-    if (e->where[r] == W_STEP && !placed[r]) {
+    if (e->where[r] == W_STEP && !placed[r] && !(g.vals[r].op >= 0 && e->absorbed[g.vals[r].op])) {   // an absorbed broadcast has no storage, nor have its views
       e->off[r] = (long long)fl.alloc(bytes);
       placed[r] = 1;
-      if (last[r] != FOREVER) dies[last[r]].push_back(r);
+      e->placed_at[r] = i;
+      if (last[r] != FOREVER) { dies[last[r]].push_back(r); e->freed_after[r] = last[r]; }
     }
     auto d = dies.find(i);
     if (d != dies.end())
@@ -1159,6 +1163,7 @@ std::string graph_exec_create(const Graph& g, int n_params, const std::vector<in
   }
   e->const_bytes = cbytes;
   e->arena_bytes = fl.end;
+  if (plan_only) { *out = e; return ""; }
   if (cudaMalloc(&e->const_arena, cbytes ? cbytes : 256) != cudaSuccess) { e->const_arena = nullptr; return failed("cudaMalloc of the constant arena failed"); }
   if (cudaMalloc(&e->arena, e->arena_bytes ? e->arena_bytes : 256) != cudaSuccess) {
     e->arena = nullptr;
@@ -1328,6 +1333,32 @@ std::string graph_exec_run(GraphExec* e, cudaStream_t st, const GraphBind& bind,
   }
   e->captured[key] = GraphExec::Captured{exec, n_launch};
   if (cudaGraphLaunch(exec, st) != cudaSuccess) return "launch of the captured program failed";
+  return "";
+}
+
+std::string graph_exec_plan_text(const Graph& g, int n_params, const std::vector<int64_t>& param_offsets, std::string* text) {
+  GraphExec* e = nullptr;
+  const std::string why = graph_exec_create(g, n_params, param_offsets, nullptr, &e, true);
+  if (!why.empty()) return why;
+  char buf[256];
+  std::string s;
+  snprintf(buf, sizeof buf, "plan arena=%zu const=%zu\n", e->arena_bytes, e->const_bytes);
+  s += buf;
+  for (size_t v = 0; v < g.vals.size(); ++v) {
+    snprintf(buf, sizeof buf, "pv %zu root=%d where=%d off=%lld bytes=%zu placed_at=%lld freed_after=%lld\n", v, e->root[v], (int)e->where[e->root[v]],
+             e->off[e->root[v]], round256((size_t)g.vals[e->root[v]].numel * dtype_size(g.vals[e->root[v]].dt)), e->placed_at[e->root[v]],
+             e->freed_after[e->root[v]]);
+    s += buf;
+  }
+  for (size_t i = 0; i < g.ops.size(); ++i) {
+    const GraphExec::OperandSrc &a = e->opnd[2 * i], &b = e->opnd[2 * i + 1];
+    snprintf(buf, sizeof buf, "po %zu need=%d fwd=%d const=%d skip=%d absorbed=%d post=%d oa=%d:%d ob=%d:%d\n", i, (int)e->need_all[i],
+             i < e->need_fwd.size() ? (int)e->need_fwd[i] : 0, (int)e->is_const_op[i], (int)e->skip[i], (int)e->absorbed[i], e->post_of[i], a.mode, a.src,
+             b.mode, b.src);
+    s += buf;
+  }
+  graph_exec_destroy(e);
+  *text = s;
   return "";
 }
 

@@ -25,8 +25,13 @@ struct GraphBind {
 
 // Plans the program (constant folding, dead-op elimination, liveness, arena offsets), checks that every op has a
 // kernel, allocates the arenas and evaluates the constant part once.  Returns "" or the reason.
+// plan_only: stop after the planning (no device is touched): for graph_exec_plan_text.
 std::string graph_exec_create(const Graph& g, int n_params, const std::vector<int64_t>& param_offsets, cudaStream_t st,
-                              GraphExec** out);
+                              GraphExec** out, bool plan_only = false);
+// The plan as text, without a device: one line per value (its storage: which value's buffer it shares, arena, offset,
+// bytes, the ops that define and release it) and per op (needed, constant, dropped guard, absorbed broadcast, fused
+// guard, operand modes).  The CPU tests check the plan's invariants from it.
+std::string graph_exec_plan_text(const Graph& g, int n_params, const std::vector<int64_t>& param_offsets, std::string* text);
 void graph_exec_destroy(GraphExec* e);
 size_t graph_exec_arena_bytes(const GraphExec* e);
 // dot2d(element type, product): hook for un-batched f32 / bf16 products (the caller's GEMM dispatch, tensor cores when

@@ -799,7 +799,20 @@ int pcpb_graph_describe(const void* bytes, size_t n, int with_gradients, char** 
     if (err && err_cap) snprintf(err, err_cap, "%s", why.c_str());
     return PCPB_E_ARTIFACT;
   }
-  const std::string s = graph_dump(g);
+  std::string s = graph_dump(g);
+  if (with_gradients == 2) {
+    // the executor's plan of the same program (constant folding, dropped and fused ops, arena layout), no device needed
+    std::vector<int64_t> offs;
+    int64_t off = 0;
+    for (size_t i = 0; i + 2 < g.args.size(); ++i) { offs.push_back(off); off += g.vals[g.args[i]].numel; }
+    std::string plan;
+    why = graph_exec_plan_text(g, (int)g.args.size() - 2, offs, &plan);
+    if (!why.empty()) {
+      if (err && err_cap) snprintf(err, err_cap, "%s", why.c_str());
+      return PCPB_E_ARTIFACT;
+    }
+    s += plan;
+  }
   char* out = (char*)malloc(s.size() + 1);
   if (!out) return PCPB_E_INVALID;
   memcpy(out, s.c_str(), s.size() + 1);

@@ -132,3 +132,83 @@ def test_malformed_attributes_are_refused_not_indexed_with(lib_built):
             graph_describe(t)
         assert ei.value.code == bk.E_ARTIFACT, what
         assert what.split()[0] in str(ei.value), (what, str(ei.value))
+
+
+def _plan(text):
+    t = graph_describe(text, with_plan=True)
+    prog = gp.parse(t)
+    head, pv, po = None, {}, {}
+    for ln in t.split("\n"):
+        f = ln.split(" ")
+        if f[0] == "plan":
+            head = dict(x.split("=") for x in f[1:])
+        elif f[0] == "pv":
+            pv[int(f[1])] = {k: int(v) for k, v in (x.split("=") for x in f[2:])}
+        elif f[0] == "po":
+            d = dict(x.split("=") for x in f[2:])
+            po[int(f[1])] = {k: (tuple(int(y) for y in v.split(":")) if ":" in v else int(v)) for k, v in d.items()}
+    return prog, {k: int(v) for k, v in head.items()}, pv, po
+
+
+@pytest.mark.parametrize("name", ["SMALL_F32", "GPT_SMALL_BF16", "GPT_HD64_F32"])
+def test_executor_plan_invariants(lib_built, name):
+    """The executor's plan of a program, checked without a device: every kernel reads values that exist when it runs
+    (defined earlier, not yet released), two values whose lifetimes overlap never share arena bytes, results are never
+    released, dropped guards and views share storage with their operand, an absorbed broadcast has no storage and its
+    one reader takes the source."""
+    cfg, text = make_model(getattr(helpers, name))
+    prog, head, pv, po = _plan(text)
+    INF = 10 ** 9
+    root = {v: d["root"] for v, d in pv.items()}
+    R = lambda v: pv[root[v]]
+    is_view = lambda i, op: op.kind == "reshape" or (op.kind == "convert" and prog.vals[op.ins[0]].dtype == prog.vals[op.out].dtype) or po[i]["skip"]
+    producer = {op.out: i for i, op in enumerate(prog.ops)}
+    kernels = 0
+    for i, op in enumerate(prog.ops):
+        f = po[i]
+        if not f["need"] or f["const"]:
+            continue
+        if f["skip"]:
+            assert op.kind == "guard_clamp" and root[op.out] == root[op.ins[0]]
+            continue
+        if f["absorbed"]:
+            assert op.kind == "bcast" and root[op.out] == op.out and pv[op.out]["placed_at"] == -1
+            readers = [(j, o) for j, o in enumerate(prog.ops) if po[j]["need"] and not is_view(j, o) and any(root[x] == op.out for x in o.ins)]
+            assert len(readers) == 1 and readers[0][1].kind == "binary"
+            j, o = readers[0]
+            k = [root[x] for x in o.ins].index(op.out)
+            assert po[j]["oa" if k == 0 else "ob"] == (po[j]["oa" if k == 0 else "ob"][0], op.ins[0]) and po[j]["oa" if k == 0 else "ob"][0] in (1, 2, 3)
+            continue
+        if is_view(i, op):
+            assert root[op.out] == root[op.ins[0]]
+            continue
+        kernels += 1
+        ins = list(op.ins)
+        if op.kind == "binary":
+            for k, key in enumerate(("oa", "ob")):
+                mode, src = f[key]
+                ins[k] = None if mode == 4 else (src if mode in (1, 2, 3) else ins[k])
+        for x in ins:
+            if x is None:
+                continue
+            r = R(x)
+            if r["where"] == 2:
+                assert 0 <= r["placed_at"] < i and (r["freed_after"] == -1 or r["freed_after"] >= i), (i, op.kind, x, r)
+            elif r["where"] == 1:
+                assert po[producer[root[x]]]["const"]
+            else:
+                assert root[x] in prog.args
+        ro = R(op.out)
+        assert ro["where"] == 2 and 0 <= ro["placed_at"] <= i and (ro["freed_after"] == -1 or ro["freed_after"] >= i), (i, op.kind, ro)
+        assert ro["off"] + ro["bytes"] <= head["arena"]
+    assert kernels > 100
+    for v in [prog.ret] + [g for g in prog.grads if g >= 0]:
+        assert R(v)["freed_after"] == -1
+    live = sorted((d["off"], d["off"] + d["bytes"], d["placed_at"], d["freed_after"] if d["freed_after"] >= 0 else INF, v)
+                  for v, d in pv.items() if root[v] == v and d["where"] == 2 and d["placed_at"] >= 0)
+    for a in range(len(live)):
+        for b in range(a + 1, len(live)):
+            if live[b][0] >= live[a][1]:
+                break                                        # sorted by offset: no later one overlaps a in memory
+            A, B = live[a], live[b]
+            assert A[3] < B[2] or B[3] < A[2], (A, B)        # lifetimes apart
