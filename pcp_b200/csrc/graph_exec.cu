@@ -159,10 +159,10 @@ template <typename T> __global__ void k_binary(int sub, const T* a, const T* b, 
   }
 }
 
-template <typename T> __global__ void k_compare(int dir, const T* a, const T* b, uint8_t* out, long long n) {
+template <typename T> __global__ void k_compare(int dir, const T* a, const T* b, uint8_t* out, long long n, Opnd oa, Opnd ob) {
   typedef typename TT<T>::C C;
   GRID_STRIDE(i, n) {
-    const C x = ld(a, i), y = ld(b, i);
+    const C x = ldo(a, i, oa), y = ldo(b, i, ob);
     bool r;
     switch (dir) {
       case C_EQ: r = x == y; break;
@@ -176,8 +176,9 @@ template <typename T> __global__ void k_compare(int dir, const T* a, const T* b,
   }
 }
 
-template <typename U> __global__ void k_select(const uint8_t* pred, const U* a, const U* b, U* out, long long n) {
-  GRID_STRIDE(i, n) out[i] = pred[i] ? a[i] : b[i];
+// a_imm / b_imm: that operand is a splat constant, given as the bits of one element
+template <typename U> __global__ void k_select(const uint8_t* pred, const U* a, const U* b, U* out, long long n, int a_imm, int b_imm, U av, U bv) {
+  GRID_STRIDE(i, n) out[i] = pred[i] ? (a_imm ? av : a[i]) : (b_imm ? bv : b[i]);
 }
 
 template <typename TI, typename TO> __global__ void k_convert(const TI* in, TO* out, long long n) {
@@ -595,6 +596,14 @@ void* ptr_of(const GraphExec& e, int v) {
 #define LAUNCH_CHECK() do { cudaError_t le__ = cudaGetLastError(); if (le__ != cudaSuccess) return std::string("kernel launch failed: ") + cudaGetErrorString(le__); } while (0)
 
 // Runs one op (dry = true: only checks that it is supported).
+// how operand k of op i is read (binary, compare: operands 0 and 1; select: its value operands 1 and 2), null for the rest
+const GraphExec::OperandSrc* operand_src(const GraphExec& e, int i, int k) {
+  const int kind = e.g.ops[i].kind;
+  if ((kind == G_BINARY || kind == G_COMPARE) && k < 2) return &e.opnd[2 * (size_t)i + k];
+  if (kind == G_SELECT && (k == 1 || k == 2)) return &e.opnd[2 * (size_t)i + k - 1];
+  return nullptr;
+}
+
 // the column-reduction form of a reduce: reduced dimensions all in front of the kept ones, enough rows to be worth it
 bool cols_form(const GValue& x, const std::vector<int64_t>& dims, long long* n_red, long long* n_out) {
   long long nr = 1, no = 1;
@@ -678,14 +687,41 @@ std::string run_op(GraphExec& e, const GOp& op, cudaStream_t st, bool dry, const
       const int dt = g.vals[op.in[0]].dt;
       if (dt != g.vals[op.in[1]].dt || o.dt != DT_BOOL) return "compare: operand types";
       if (dry) return "";
-      BY_TYPE(dt, k_compare<T><<<nb, TPB, 0, st>>>(op.sub, (const T*)in(0), (const T*)in(1), (uint8_t*)out, n));
+      {
+        Opnd od[2];
+        const void* ptr[2];
+        for (int k = 0; k < 2; ++k) {
+          od[k].mode = O_DIRECT; od[k].inner = 1; od[k].imm = 0.0; od[k].iimm = 0;
+          if (osrc && osrc[k].mode == O_IMM) { od[k].mode = O_IMM; od[k].imm = osrc[k].imm; od[k].iimm = osrc[k].iimm; ptr[k] = nullptr; }
+          else ptr[k] = in(k);
+        }
+        BY_TYPE(dt, k_compare<T><<<nb, TPB, 0, st>>>(op.sub, (const T*)ptr[0], (const T*)ptr[1], (uint8_t*)out, n, od[0], od[1]));
+      }
       count(1);
       break;
     }
     case G_SELECT:
       if (g.vals[op.in[0]].dt != DT_BOOL || g.vals[op.in[0]].numel != n) return "select: the predicate must be i1 of the result's shape";
       if (dry) return "";
-      BY_SIZE(es, k_select<U><<<nb, TPB, 0, st>>>((const uint8_t*)in(0), (const U*)in(1), (const U*)in(2), (U*)out, n));
+      {
+        unsigned long long bits[2] = {0, 0};
+        int imm[2] = {0, 0};
+        const void* ptr[2];
+        for (int k = 0; k < 2; ++k) {
+          if (osrc && osrc[k].mode == O_IMM) {
+            imm[k] = 1; ptr[k] = nullptr;
+            switch (o.dt) {
+              case DT_F32: { const float f = (float)osrc[k].imm; unsigned u; memcpy(&u, &f, 4); bits[k] = u; break; }
+              case DT_BF16: { const bf16 h = __float2bfloat16_rn((float)osrc[k].imm); unsigned short u; memcpy(&u, &h, 2); bits[k] = u; break; }
+              case DT_F64: { memcpy(&bits[k], &osrc[k].imm, 8); break; }
+              case DT_I32: bits[k] = (unsigned)(int)osrc[k].iimm; break;
+              case DT_BOOL: bits[k] = osrc[k].iimm != 0; break;
+              default: bits[k] = (unsigned long long)osrc[k].iimm; break;
+            }
+          } else ptr[k] = in(k + 1);
+        }
+        BY_SIZE(es, k_select<U><<<nb, TPB, 0, st>>>((const uint8_t*)in(0), (const U*)ptr[0], (const U*)ptr[1], (U*)out, n, imm[0], imm[1], (U)bits[0], (U)bits[1]));
+      }
       count(1);
       break;
     case G_CONVERT:
@@ -1095,12 +1131,28 @@ std::string graph_exec_create(const Graph& g, int n_params, const std::vector<in
     };
     for (int i = 0; i < nops && on; ++i) {
       const GOp& op = g.ops[i];
-      if (!e->need_all[i] || e->is_const_op[i] || op.kind != G_BINARY) continue;
+      if (!e->need_all[i] || e->is_const_op[i] || !(op.kind == G_BINARY || op.kind == G_COMPARE || op.kind == G_SELECT)) continue;
+      const int first = op.kind == G_SELECT ? 1 : 0;           // select: the two value operands
       for (int k = 0; k < 2; ++k) {
         GraphExec::OperandSrc& os = e->opnd[2 * (size_t)i + k];
         if (os.mode != O_DIRECT) continue;
         double f; long long iv;
-        if (g.vals[op.in[k]].dt == g.vals[op.out].dt && splat_of(op.in[k], &f, &iv)) { os.mode = O_IMM; os.imm = f; os.iimm = iv; }
+        if (splat_of(op.in[first + k], &f, &iv)) { os.mode = O_IMM; os.imm = f; os.iimm = iv; }
+      }
+    }
+    // constants that nothing reads as a tensor any more (every reader takes an immediate) are neither evaluated nor stored
+    std::vector<char> read(nv, 0);
+    for (int v : outs) if (v >= 0) read[v] = 1;
+    for (int i = nops - 1; i >= 0 && on; --i) {
+      const GOp& op = g.ops[i];
+      if (!e->need_all[i] || e->absorbed[i]) continue;
+      if (e->is_const_op[i] && !read[op.out]) { e->need_all[i] = 0; e->need_fwd[i] = 0; continue; }
+      for (size_t k = 0; k < op.in.size(); ++k) {
+        int x = op.in[k];
+        const GraphExec::OperandSrc* os = operand_src(*e, i, (int)k);
+        if (os && os->mode == O_IMM) continue;
+        if (os && os->mode != O_DIRECT) x = os->src;
+        read[x] = 1;
       }
     }
   }
@@ -1127,11 +1179,9 @@ std::string graph_exec_create(const Graph& g, int n_params, const std::vector<in
     last[e->root[op.out]] = std::max<long long>(last[e->root[op.out]], i);
     for (size_t k = 0; k < op.in.size(); ++k) {
       int x = op.in[k];
-      if (op.kind == G_BINARY && k < 2) {
-        const GraphExec::OperandSrc& os = e->opnd[2 * (size_t)i + k];
-        if (os.mode == O_IMM) continue;
-        if (os.mode != O_DIRECT) x = os.src;
-      }
+      const GraphExec::OperandSrc* os = operand_src(*e, i, (int)k);
+      if (os && os->mode == O_IMM) continue;
+      if (os && os->mode != O_DIRECT) x = os->src;
       last[e->root[x]] = std::max<long long>(last[e->root[x]], i);
     }
   }

@@ -184,10 +184,11 @@ def test_executor_plan_invariants(lib_built, name):
             continue
         kernels += 1
         ins = list(op.ins)
-        if op.kind == "binary":
+        if op.kind in ("binary", "compare", "select"):
+            first = 1 if op.kind == "select" else 0         # select: its two value operands
             for k, key in enumerate(("oa", "ob")):
                 mode, src = f[key]
-                ins[k] = None if mode == 4 else (src if mode in (1, 2, 3) else ins[k])
+                ins[first + k] = None if mode == 4 else (src if mode in (1, 2, 3) else ins[first + k])
         for x in ins:
             if x is None:
                 continue
@@ -195,7 +196,7 @@ def test_executor_plan_invariants(lib_built, name):
             if r["where"] == 2:
                 assert 0 <= r["placed_at"] < i and (r["freed_after"] == -1 or r["freed_after"] >= i), (i, op.kind, x, r)
             elif r["where"] == 1:
-                assert po[producer[root[x]]]["const"]
+                assert po[producer[root[x]]]["const"] and po[producer[root[x]]]["need"]      # a constant that is materialised
             else:
                 assert root[x] in prog.args
         ro = R(op.out)
