@@ -213,3 +213,21 @@ def test_executor_plan_invariants(lib_built, name):
                 break                                        # sorted by offset: no later one overlaps a in memory
             A, B = live[a], live[b]
             assert A[3] < B[2] or B[3] < A[2], (A, B)        # lifetimes apart
+
+
+def test_op_zoo_program_matches_oracle(lib_built):
+    """Ops and op forms outside the model exporters' repertoire (tests/graph_zoo.py)."""
+    from graph_zoo import ZOO_BATCH, ZOO_BLOCK, ZOO_MLIR, ZOO_PARAM_SHAPES, ZOO_VOCAB
+    f = inspect_artifact(ZOO_MLIR)
+    assert f["family"] == "graph" and (f["batch"], f["block"], f["num_tensors"], f["total_params"]) == (ZOO_BATCH, ZOO_BLOCK, 3, 90)
+    mod = TrainingModule(ZOO_MLIR)
+    g = torch.Generator().manual_seed(0)
+    params = [torch.randn(s, generator=g) * 0.5 for s in ZOO_PARAM_SHAPES]
+    ids = torch.randint(0, ZOO_VOCAB, (ZOO_BATCH, ZOO_BLOCK), generator=g)
+    tg = torch.randint(0, ZOO_VOCAB, (ZOO_BATCH, ZOO_BLOCK), generator=g)
+    prog = gp.parse(graph_describe(ZOO_MLIR))
+    loss, grads = gp.run(prog, params + [ids, tg])
+    want = mod.model_forward_pass_grad(params, ids, tg, 1.0)
+    assert float(loss) == float(mod.forward(params, ids, tg))
+    for a, w in zip(grads, want):
+        assert torch.equal(a, w) and float(w.abs().max()) > 0
