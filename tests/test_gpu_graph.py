@@ -109,20 +109,22 @@ def test_graph_of_neither_family_trains_like_the_oracle(name, tol):
     assert rel_err(after, after_ref) <= tol
 
 
-def test_op_zoo_on_the_gpu():
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_op_zoo_on_the_gpu(dtype):
     """The hand-written graph of tests/graph_zoo.py (sine, cosine, logistic, strided slices, three-way concatenate,
     rank-3 transpose, batched dot_general, reductions over middle and leading dimensions, broadcasts into non-adjacent
     dimensions, integer converts, compare + select, ops without a gradient rule) against the oracle."""
     from graph_zoo import ZOO_BATCH, ZOO_BLOCK, ZOO_MLIR, ZOO_PARAM_SHAPES, ZOO_VOCAB
-    mod = TrainingModule(ZOO_MLIR)
+    text = ZOO_MLIR.replace("f32", dtype)
+    mod = TrainingModule(text)
     g = torch.Generator().manual_seed(0)
     params = [torch.randn(s, generator=g) * 0.5 for s in ZOO_PARAM_SHAPES]
     x = torch.randint(0, ZOO_VOCAB, (ZOO_BATCH, ZOO_BLOCK), generator=g).numpy()
     y = torch.randint(0, ZOO_VOCAB, (ZOO_BATCH, ZOO_BLOCK), generator=g).numpy()
     g_ref, loss_ref = mod.compute_gradients(params, torch.from_numpy(x), torch.from_numpy(y))
     with Backend(0) as be:
-        be.load_session(ZOO_MLIR)
+        be.load_session(text)
         assert be.param_shapes() == [tuple(s) for s in ZOO_PARAM_SHAPES]
         got, loss = _grads_via_abi(be, None, params, x, y)
-    assert abs(loss - float(loss_ref)) <= 1e-5 * abs(float(loss_ref))
-    assert max(rel_err(a, b.numpy()) for a, b in zip(got, g_ref)) <= 1e-4
+    assert abs(loss - float(loss_ref)) <= (1e-5 if dtype == "f32" else 2e-2) * abs(float(loss_ref))
+    assert max(rel_err(a, b.numpy()) for a, b in zip(got, g_ref)) <= (1e-4 if dtype == "f32" else 4e-2)

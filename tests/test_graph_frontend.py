@@ -215,19 +215,22 @@ def test_executor_plan_invariants(lib_built, name):
             assert A[3] < B[2] or B[3] < A[2], (A, B)        # lifetimes apart
 
 
-def test_op_zoo_program_matches_oracle(lib_built):
-    """Ops and op forms outside the model exporters' repertoire (tests/graph_zoo.py)."""
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_op_zoo_program_matches_oracle(lib_built, dtype):
+    """Ops and op forms outside the model exporters' repertoire (tests/graph_zoo.py), in f32 and with every f32
+    replaced by bf16 (the -inf literal then takes the sanitiser's hex rewrite)."""
     from graph_zoo import ZOO_BATCH, ZOO_BLOCK, ZOO_MLIR, ZOO_PARAM_SHAPES, ZOO_VOCAB
-    f = inspect_artifact(ZOO_MLIR)
+    text = ZOO_MLIR.replace("f32", dtype)
+    f = inspect_artifact(text)
     assert f["family"] == "graph" and (f["batch"], f["block"], f["num_tensors"], f["total_params"]) == (ZOO_BATCH, ZOO_BLOCK, 3, 90)
-    mod = TrainingModule(ZOO_MLIR)
+    mod = TrainingModule(text)
     g = torch.Generator().manual_seed(0)
-    params = [torch.randn(s, generator=g) * 0.5 for s in ZOO_PARAM_SHAPES]
+    params = mod._model_params([torch.randn(s, generator=g) * 0.5 for s in ZOO_PARAM_SHAPES])
     ids = torch.randint(0, ZOO_VOCAB, (ZOO_BATCH, ZOO_BLOCK), generator=g)
     tg = torch.randint(0, ZOO_VOCAB, (ZOO_BATCH, ZOO_BLOCK), generator=g)
-    prog = gp.parse(graph_describe(ZOO_MLIR))
+    prog = gp.parse(graph_describe(text))
     loss, grads = gp.run(prog, params + [ids, tg])
     want = mod.model_forward_pass_grad(params, ids, tg, 1.0)
-    assert float(loss) == float(mod.forward(params, ids, tg))
+    assert float(loss) == float(mod.forward([p.to(torch.float32) for p in params], ids, tg))
     for a, w in zip(grads, want):
         assert torch.equal(a, w) and float(w.abs().max()) > 0
