@@ -595,7 +595,6 @@ void* ptr_of(const GraphExec& e, int v) {
 
 #define LAUNCH_CHECK() do { cudaError_t le__ = cudaGetLastError(); if (le__ != cudaSuccess) return std::string("kernel launch failed: ") + cudaGetErrorString(le__); } while (0)
 
-// Runs one op (dry = true: only checks that it is supported).
 // how operand k of op i is read (binary, compare: operands 0 and 1; select: its value operands 1 and 2), null for the rest
 const GraphExec::OperandSrc* operand_src(const GraphExec& e, int i, int k) {
   const int kind = e.g.ops[i].kind;
@@ -619,6 +618,8 @@ bool cols_form(const GValue& x, const std::vector<int64_t>& dims, long long* n_r
 }
 int cols_chunks(long long n_red) { const long long c = (n_red + 255) / 256; return (int)(c < 1 ? 1 : (c > 64 ? 64 : c)); }
 
+// Runs one op (dry = true: only checks that it is supported).  fused_clamp: the adjoint guard that runs inside this
+// element-wise op; osrc: the two operand sources of a binary / compare / select op (operand_src).
 std::string run_op(GraphExec& e, const GOp& op, cudaStream_t st, bool dry, const std::function<int(int, const GemmArgs&)>* dot2d,
                    long long* launches, const GOp* fused_clamp = nullptr, const GraphExec::OperandSrc* osrc = nullptr) {
   Post post = {0, 0, 0.f, 0.f};
