@@ -6,4 +6,5 @@ exporter for model shapes the reference does not ship (export.py) and the build 
 """
 from .backend import (BF16, BOOL, F16, F32, F64, I32, I64, Backend, BackendError, DeviceBuffer,  # noqa: F401
                       load_library)
-from .export import NanochatConfig, NanoGPTConfig, nanochat_forward_mlir, nanogpt_forward_mlir  # noqa: F401
+from .export import (NanochatConfig, NanoGPTConfig, QwenConfig, nanochat_forward_mlir, nanogpt_forward_mlir,  # noqa: F401
+                     qwen_forward_mlir)

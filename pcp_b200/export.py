@@ -476,3 +476,170 @@ def nanogpt_forward_mlir(cfg: NanoGPTConfig) -> str:
     out += e.lines
     out += [f"    return {loss[0]} : tensor<f32>", "  }", "}", ""]
     return "\n".join(out)
+
+
+# ------------------------------------------------------------------------------------------------
+# Qwen3-style decoder (the architecture of tools/export_qwen3_generation.py, as a training graph)
+# ------------------------------------------------------------------------------------------------
+@dataclass
+class QwenConfig:
+    """A third architecture, neither of the two families the fused kernels cover: RMSNorm with a weight, q / k
+    normalised per head with a weight BEFORE RoPE, grouped-query attention, SwiGLU MLP, plain cross entropy with
+    ignore index -100.  The reference exports this model for generation only (tools/export_qwen3_generation.py wraps
+    Qwen3ForCausalLM for the rollout workers); as a forward graph (params..., ids, targets) -> loss it is what the
+    Shepherd would hand to workers to fine-tune that model, and it runs through the general front end."""
+    vocab: int = 97
+    d_model: int = 64
+    n_layer: int = 2
+    n_head: int = 4
+    n_kv_head: int = 2
+    head_dim: int = 16
+    d_ff: int = 128
+    seq_len: int = 32
+    batch: int = 4
+    dtype: str = "f32"            # "f32" | "bf16"
+    rope_base: float = 10000.0
+    eps: float = 1e-6
+
+    def param_shapes(self):
+        d, hq, hk, f = self.d_model, self.n_head * self.head_dim, self.n_kv_head * self.head_dim, self.d_ff
+        s = [(self.vocab, d)]
+        for _ in range(self.n_layer):
+            s += [(d,), (hq, d), (hk, d), (hk, d), (self.head_dim,), (self.head_dim,), (d, hq), (d,), (f, d), (f, d), (d, f)]
+        s += [(d,), (self.vocab, d)]
+        return s
+
+    def num_params(self):
+        return int(sum(int(np.prod(x)) for x in self.param_shapes()))
+
+
+def qwen_forward_mlir(cfg: QwenConfig) -> str:
+    """Forward graph: x = embed[ids]; per layer  h = rms(x, ln1); q, k, v = h W^T; q = rope(rms_head(q, q_norm)),
+    k = rope(rms_head(k, k_norm)); causal softmax attention (f32 softmax, GQA by broadcasting k / v); x += o W_o^T;
+    h = rms(x, ln2); x += (silu(h W_gate^T) * (h W_up^T)) W_down^T;  logits = rms(x, norm) lm_head^T in f32;
+    mean NLL over targets != -100.  rms(x, w) = w * (x * rsqrt(mean(x^2) + eps)) with the statistics in f32."""
+    e = _Emitter()
+    B, T, d, V = cfg.batch, cfg.seq_len, cfg.d_model, cfg.vocab
+    H, Hkv, hd, F, dt = cfg.n_head, cfg.n_kv_head, cfg.head_dim, cfg.d_ff, cfg.dtype
+    hq, hk, M = H * hd, Hkv * hd, B * T
+    assert H % Hkv == 0 and hd % 2 == 0 and dt in ("f32", "bf16")
+    shapes = cfg.param_shapes()
+    nP = len(shapes)
+    args = [f"%arg{i}: {e.ty(s, dt)}" for i, s in enumerate(shapes)]
+    args += [f"%arg{nP}: {e.ty((B, T), 'i64')}", f"%arg{nP + 1}: {e.ty((B, T), 'i64')}"]
+    P = [(f"%arg{i}", tuple(s), dt) for i, s in enumerate(shapes)]
+    idx = (f"%arg{nP}", (B, T), "i64")
+    tgt = (f"%arg{nP + 1}", (B, T), "i64")
+
+    zero_f32 = e.const("0.000000e+00", (), "f32")
+    ninf_f32 = e.const("0xFF800000", (), "f32")
+    mask_fill = e.const("-6.553600e+04", (), "bf16") if dt == "bf16" else ninf_f32
+    cos_t = e.resource("rope_cos", (1, T, 1, hd // 2), "bf16")
+    sin_t = e.resource("rope_sin", (1, T, 1, hd // 2), "bf16")
+    two_f32 = e.scalar("2", "i64", "f32")
+    eps_f32 = e.scalar(repr(cfg.eps), "f64", "f32")
+
+    def rms(x, w, width):
+        """RMSNorm over the last dimension with the weight w [width]."""
+        shp = x[1]
+        xf = e.convert(x, "f32") if dt != "f32" else x
+        s = e.reduce("add", e.bin("power", xf, e.splat(two_f32, shp)), zero_f32, [len(shp) - 1])
+        s = e.reshape(s, shp[:-1] + (1,))
+        ms = e.bin("divide", s, e.splat(e.scalar(str(width), "i64", "f32"), s[1]))
+        r = e.un("rsqrt", e.bin("add", ms, e.splat(eps_f32, s[1])))
+        y = e.bin("multiply", xf, e.bcast(r, shp, list(range(len(shp)))))
+        if dt != "f32":
+            y = e.convert(y, dt)
+        return e.bin("multiply", e.bcast(w, shp, [len(shp) - 1]), y)
+
+    def linear(x2d, w):
+        return e.dot(x2d, e.transpose(w, [1, 0]))
+
+    def rope(x):
+        nh, half = x[1][2], hd // 2
+        x1 = e.slice(x, [(0, B), (0, T), (0, nh), (0, half)])
+        x2 = e.slice(x, [(0, B), (0, T), (0, nh), (half, hd)])
+        cv = (lambda t: t) if dt == "bf16" else (lambda t: e.convert(t, dt))
+        c = e.bcast(cv(cos_t), x1[1], [0, 1, 2, 3])
+        s = e.bcast(cv(sin_t), x1[1], [0, 1, 2, 3])
+        # rotate_half: (x1, x2) -> (x1 cos - x2 sin, x2 cos + x1 sin)
+        y1 = e.bin("subtract", e.bin("multiply", x1, c), e.bin("multiply", x2, s))
+        y2 = e.bin("add", e.bin("multiply", x2, c), e.bin("multiply", x1, s))
+        return e.concat(y1, y2, 3)
+
+    ar = e.iota((T,), 0)
+    col = e.bcast(e.reshape(ar, (1, T)), (T, T), [0, 1])
+    row = e.bcast(e.reshape(ar, (T, 1)), (T, T), [0, 1])
+    mask2d = e.compare("GT", col, row)
+    mask = e.bcast(e.reshape(mask2d, (1, 1, T, T)), (B, H, T, T), [0, 1, 2, 3])
+    fill = e.splat(mask_fill, (B, H, T, T))
+    scale = e.scalar(repr(1.0 / math.sqrt(hd)), "f64", dt)
+
+    x = e.emit(
+        f'"stablehlo.gather"({P[0][0]}, {idx[0]}) <{{dimension_numbers = #stablehlo.gather<offset_dims = [2], '
+        f'collapsed_slice_dims = [0], start_index_map = [0], index_vector_dim = 2>, indices_are_sorted = false, '
+        f'slice_sizes = array<i64: 1, {d}>}}>', (B, T, d), dt,
+        f"({e.ty((V, d), dt)}, {e.ty((B, T), 'i64')}) -> {e.ty((B, T, d), dt)}")
+
+    for l in range(cfg.n_layer):
+        ln1, wq, wk, wv, qn, kn, wo, ln2, wg, wu, wd = P[1 + 11 * l: 12 + 11 * l]
+        h = e.reshape(rms(x, ln1, d), (M, d))
+        q = e.reshape(linear(h, wq), (B, T, H, hd))
+        k = e.reshape(linear(h, wk), (B, T, Hkv, hd))
+        v = e.reshape(linear(h, wv), (B, T, Hkv, hd))
+        q, k = rope(rms(q, qn, hd)), rope(rms(k, kn, hd))
+        q = e.transpose(q, [0, 2, 1, 3])
+        k = e.transpose(k, [0, 2, 1, 3])
+        v = e.transpose(v, [0, 2, 1, 3])
+        if Hkv != H:
+            g = H // Hkv
+            k = e.reshape(e.bcast(e.reshape(k, (B, Hkv, 1, T, hd)), (B, Hkv, g, T, hd), [0, 1, 2, 3, 4]), (B, H, T, hd))
+            v = e.reshape(e.bcast(e.reshape(v, (B, Hkv, 1, T, hd)), (B, Hkv, g, T, hd), [0, 1, 2, 3, 4]), (B, H, T, hd))
+        kt = e.transpose(k, [0, 1, 3, 2])
+        s = e.dot(e.reshape(q, (B * H, T, hd)), e.reshape(kt, (B * H, hd, T)), batched=True)
+        s = e.bin("multiply", e.reshape(s, (B, H, T, T)), e.splat(scale, (B, H, T, T)))
+        s = e.select(mask, fill, s)
+        sf = e.convert(s, "f32") if dt != "f32" else s
+        mx = e.reshape(e.reduce("maximum", sf, ninf_f32, [3]), (B, H, T, 1))
+        ex = e.un("exponential", e.bin("subtract", sf, e.bcast(mx, (B, H, T, T), [0, 1, 2, 3])))
+        sm = e.reshape(e.reduce("add", ex, zero_f32, [3]), (B, H, T, 1))
+        p = e.bin("divide", ex, e.bcast(sm, (B, H, T, T), [0, 1, 2, 3]))
+        if dt != "f32":
+            p = e.convert(p, dt)
+        o = e.dot(e.reshape(p, (B * H, T, T)), e.reshape(v, (B * H, T, hd)), batched=True)
+        o = e.reshape(e.transpose(e.reshape(o, (B, H, T, hd)), [0, 2, 1, 3]), (M, hq))
+        x = e.bin("add", x, e.reshape(linear(o, wo), (B, T, d)))
+        h = e.reshape(rms(x, ln2, d), (M, d))
+        gate, up = linear(h, wg), linear(h, wu)
+        act = e.bin("multiply", e.bin("multiply", gate, e.un("logistic", gate)), up)       # silu(gate) * up
+        x = e.bin("add", x, e.reshape(linear(act, wd), (B, T, d)))
+
+    hf = e.reshape(rms(x, P[-2], d), (M, d))
+    z = linear(hf, P[-1])
+    if dt != "f32":
+        z = e.convert(z, "f32")
+    t1 = e.reshape(tgt, (M,))
+    mx = e.bcast(e.reshape(e.reduce("maximum", z, ninf_f32, [1]), (M, 1)), (M, V), [0, 1])
+    sh = e.bin("subtract", z, mx)
+    se = e.reshape(e.reduce("add", e.un("exponential", sh), zero_f32, [1]), (M, 1))
+    logp = e.bin("subtract", sh, e.bcast(e.un("log", se), (M, V), [0, 1]))
+    valid = e.compare("NE", t1, e.const("-100", (M,), "i64"))
+    safe_t = e.select(valid, t1, e.const("0", (M,), "i64"))
+    ij = e.concat(e.iota((M, 1, 1), 0), e.reshape(e.reshape(safe_t, (M, 1)), (M, 1, 1)), 2)
+    picked = e.emit(
+        f'"stablehlo.gather"({logp[0]}, {ij[0]}) <{{dimension_numbers = #stablehlo.gather<collapsed_slice_dims = [0, 1], '
+        f'start_index_map = [0, 1], index_vector_dim = 2>, slice_sizes = array<i64: 1, 1>}}>', (M, 1), "f32",
+        f"({e.ty((M, V), 'f32')}, {e.ty((M, 1, 2), 'i64')}) -> {e.ty((M, 1), 'f32')}")
+    nll = e.select(valid, e.un("negate", e.reshape(picked, (M,))), e.splat(zero_f32, (M,)))
+    cnt = e.convert(e.reduce("add", e.convert(valid, "i64"), e.const("0", (), "i64"), [0]), "f32")
+    loss = e.bin("divide", e.reduce("add", nll, zero_f32, [0]), cnt)
+
+    cos_b, sin_b = rope_tables(T, hd, cfg.rope_base)
+    hdr = "02000000"
+    out = ["module {", f"  func.func @main({', '.join(args)}) -> tensor<f32> {{"]
+    out += e.lines
+    out += [f"    return {loss[0]} : tensor<f32>", "  }", "}", "", "{-#", "  dialect_resources: {", "    builtin: {",
+            f'      rope_sin: "0x{hdr}{sin_b.astype("<u2").tobytes().hex().upper()}",',
+            f'      rope_cos: "0x{hdr}{cos_b.astype("<u2").tobytes().hex().upper()}"',
+            "    }", "  }", "#-}", ""]
+    return "\n".join(out)

@@ -128,3 +128,44 @@ def test_op_zoo_on_the_gpu(dtype):
         got, loss = _grads_via_abi(be, None, params, x, y)
     assert abs(loss - float(loss_ref)) <= (1e-5 if dtype == "f32" else 2e-2) * abs(float(loss_ref))
     assert max(rel_err(a, b.numpy()) for a, b in zip(got, g_ref)) <= (1e-4 if dtype == "f32" else 4e-2)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_a_third_architecture_trains_like_the_oracle(dtype):
+    """The Qwen3-style training graph (weighted RMSNorm, per-head q / k norm before RoPE, GQA, SwiGLU, plain cross
+    entropy): no fused kernel knows it; the general front end runs it — gradients against the oracle, then a worker
+    round of three AdamW steps (losses and parameters after the round)."""
+    from pcp_b200.export import QwenConfig, qwen_forward_mlir
+    from test_qwen_graph import qwen_batch, qwen_params
+    cfg = QwenConfig(dtype=dtype)
+    text = qwen_forward_mlir(cfg)
+    mod = TrainingModule(text)
+    f32 = dtype == "f32"
+    params = qwen_params(cfg)
+    ids, tg = qwen_batch(cfg)
+    g_ref, loss_ref = mod.compute_gradients(params, ids, tg)
+    dt = F32 if f32 else BF16
+    master = params if f32 else [torch.from_numpy(helpers.bf16_bits_to_f32(helpers.f32_to_bf16_trunc_bits(p.numpy())).reshape(p.shape)) for p in params]
+    tau = 3
+    toks = helpers.uniform_tokens(tau * (cfg.batch * cfg.seq_len + 1), cfg.vocab, 7)
+    conf = AdamConf(learning_rate=1e-3)
+    rec = []
+    d_ref, _, _, _ = inner_loop(mod, master, FifoU16(toks), tau, cfg.batch, cfg.seq_len, conf, record=rec)
+    with Backend(0) as be:
+        be.load_session(text)
+        assert be.param_shapes() == [tuple(s) for s in cfg.param_shapes()]
+        got, loss = _grads_via_abi(be, None, params, ids.numpy(), tg.numpy())
+        be.set_adam(conf.learning_rate, conf.beta1, conf.beta2, conf.epsilon, conf.weight_decay, conf.max_grad_norm)
+        blob = flat(master) if f32 else helpers.f32_to_bf16_trunc_bits(flat(master))
+        be.worker_begin_round(tau, blob, param_dtype=dt)
+        be.worker_set_tokens(toks)
+        for _ in range(tau):
+            be.worker_step()
+        delta, losses = be.worker_end_round(tau, param_dtype=dt)
+    assert abs(loss - float(loss_ref)) <= (1e-4 if f32 else 2e-2) * abs(float(loss_ref))
+    worst = max(rel_err(a, b.numpy()) for a, b in zip(got, g_ref))
+    l2 = max(float(np.linalg.norm(a - b.numpy()) / (np.linalg.norm(b.numpy()) + 1e-30)) for a, b in zip(got, g_ref))
+    assert (worst <= 1e-4) if f32 else (l2 <= 4e-2 and worst <= 0.25), (worst, l2)
+    np.testing.assert_allclose(losses, [r[0] for r in rec], rtol=1e-4 if f32 else 2e-2)
+    dgpu = delta if f32 else helpers.bf16_bits_to_f32(delta)
+    assert rel_err(flat(master) - dgpu, flat(master) - flat(d_ref)) <= (1e-4 if f32 else 2e-2)
