@@ -150,13 +150,22 @@ def _plan(text):
     return prog, {k: int(v) for k, v in head.items()}, pv, po
 
 
-@pytest.mark.parametrize("name", ["SMALL_F32", "GPT_SMALL_BF16", "GPT_HD64_F32"])
+def _shipped_or_exported(name):
+    if name.endswith(".mlir"):
+        path = os.path.join(REF, "models", name)
+        if not os.path.exists(path):
+            pytest.skip("reference tree not present")
+        return open(path).read()
+    return make_model(getattr(helpers, name))[1]
+
+
+@pytest.mark.parametrize("name", ["SMALL_F32", "GPT_SMALL_BF16", "GPT_HD64_F32", "nanochat_d4_b4_t2048_bf16.mlir", "nanogpt_medium.mlir"])
 def test_executor_plan_invariants(lib_built, name):
     """The executor's plan of a program, checked without a device: every kernel reads values that exist when it runs
     (defined earlier, not yet released), two values whose lifetimes overlap never share arena bytes, results are never
     released, dropped guards and views share storage with their operand, an absorbed broadcast has no storage and its
     one reader takes the source."""
-    cfg, text = make_model(getattr(helpers, name))
+    text = _shipped_or_exported(name)
     prog, head, pv, po = _plan(text)
     INF = 10 ** 9
     root = {v: d["root"] for v, d in pv.items()}
