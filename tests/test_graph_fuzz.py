@@ -2,7 +2,7 @@
 tensor program — forward ops, stability patches, gradient rules, adjoint edges, accumulation order — evaluated with
 torch must reproduce the oracle's loss and gradients exactly.  The graphs mix element-wise ops, broadcasts, transposes,
 reshapes, strided slices, concatenates, reductions over random dimensions, plain and batched dot_generals, compare +
-select and f32 <-> bf16 converts over small shapes; values stay finite by construction."""
+select, row gathers by the integer inputs, iota masks, f64 stretches, integer and f32 <-> bf16 converts over small shapes; values stay finite by construction."""
 import random
 
 import pytest
@@ -34,7 +34,7 @@ def _random_graph(seed, dt):
 
     for _ in range(rng.randint(10, 24)):
         kind = rng.choice(["unary", "binary", "bcast", "transpose", "reshape", "slice", "concat", "reduce", "dot", "bdot",
-                           "select", "convert", "safe_div", "rsqrt", "power"])
+                           "select", "convert", "safe_div", "rsqrt", "power", "gather", "f64", "iota_mask", "ids"])
         x = pick()
         if kind == "unary":
             y = e.un(rng.choice(["tanh", "logistic", "negate", "sine", "cosine"]), x)
@@ -109,6 +109,36 @@ def _random_graph(seed, dt):
         elif kind == "select":
             z = pick(lambda t: t[1] == x[1] and t[2] == x[2])
             y = e.select(e.compare(rng.choice(["GT", "LE", "NE"]), x, z, "FLOAT"), x, e.un("negate", z))
+        elif kind == "gather":                         # rows of a 2-D value picked by the ids argument (values 0..3)
+            t = pick(lambda t: len(t[1]) == 2 and t[1][0] >= 4)
+            if not t:
+                continue
+            y = e.emit(
+                f'"stablehlo.gather"({t[0]}, %arg{len(PARAM_SHAPES)}) <{{dimension_numbers = #stablehlo.gather<offset_dims = [2], '
+                f'collapsed_slice_dims = [0], start_index_map = [0], index_vector_dim = 2>, indices_are_sorted = false, '
+                f'slice_sizes = array<i64: 1, {t[1][1]}>}}>', (2, 3, t[1][1]), t[2],
+                f"({e.ty(t[1], t[2])}, {e.ty((2, 3), 'i64')}) -> {e.ty((2, 3, t[1][1]), t[2])}")
+        elif kind == "f64":                            # a stretch in f64, as the LayerNorm variance of the nanoGPT exports
+            if x[2] != "f32":
+                continue
+            d = e.convert(x, "f64")
+            d = e.bin("multiply", d, d)
+            if d[1]:
+                k = rng.randrange(len(d[1]))
+                d = e.reduce("add", d, e.const("0.000000e+00", (), "f64"), [k])
+            y = e.convert(d, "f32")
+        elif kind == "iota_mask":                      # keep the entries whose index along one dimension is below a bound
+            if not x[1]:
+                continue
+            k = rng.randrange(len(x[1]))
+            io = e.iota(x[1], k)
+            m = e.compare("LT", io, e.const(str(rng.randint(1, x[1][k])), x[1], "i64"))
+            y = e.select(m, x, const_like(x, "0.000000e+00"))
+        elif kind == "ids":                            # the integer inputs as numbers: x[0, 0] scaled by (ids + 1) summed
+            f = e.convert(e.convert((f"%arg{len(PARAM_SHAPES) + 1}", (2, 3), "i64"), "i32"), x[2])
+            one = e.const("1.000000e+00", (2, 3), x[2])
+            sc = e.reduce("add", e.bin("add", f, one), e.const("0.000000e+00", (), x[2]), [0, 1])
+            y = e.bin("multiply", x, e.bcast(sc, x[1], []))
         else:                                          # convert to the other float type and back
             other = "bf16" if x[2] == "f32" else "f32"
             y = e.convert(x, other)
@@ -130,7 +160,7 @@ def _random_graph(seed, dt):
 
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
 def test_random_graphs_match_the_oracle_exactly(lib_built, dt):
-    ids = torch.zeros((2, 3), dtype=torch.int64)
+    ids = torch.tensor([[0, 3, 1], [2, 2, 0]], dtype=torch.int64)
     for seed in range(40):
         text = _random_graph(seed, dt)
         mod = TrainingModule(text)
